@@ -1,0 +1,269 @@
+"""TEST INFRASTRUCTURE: ctypes loaders for the CPU checkers.
+
+`lib()` is the plain-C restatement (oracle/psb_oracle.c, parity pinned against the reference's
+own CPU code).  `ref()` is that reference CPU code itself, compiled in place by oracle/Makefile
+into oracle/_ref/ (present only where it was built).  Only tests, the smoke entry and the
+bench's CPU legs may import this package; the shipped library never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "_build", "libpsb_oracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libpsb_ref.so")
+_lib = None
+_ref = None
+
+f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+i64p = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+
+
+def build(ref_too: bool = True) -> None:
+    """Compile the restatement and, when the reference checkout is present, oracle/_ref."""
+    targets = ["oracle"] + (["ref"] if ref_too else [])
+    subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
+
+
+def _ptr(a, ctype=None):
+    if a is None:
+        return None
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(ORACLE_SO):
+            build(ref_too=False)
+        _lib = C.CDLL(ORACLE_SO)
+        _lib.psbo_l2_exact.restype = C.c_float
+        _lib.psbo_recall.restype = C.c_double
+    return _lib
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_SO)
+
+
+def ref():
+    global _ref
+    if _ref is None:
+        _ref = C.CDLL(REF_SO)
+        _ref.psbref_last_error.restype = C.c_char_p
+        _ref.psbref_fp32_isa.restype = C.c_char_p
+    return _ref
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+# ---------------------------------------------------------------- restatement wrappers
+def l2_exact(q, v):
+    q = _c(q, np.float32); v = _c(v, np.float32)
+    return float(lib().psbo_l2_exact(_ptr(q), _ptr(v), C.c_int(q.size)))
+
+
+def coarse(queries, centroids, nprobe):
+    queries = _c(queries, np.float32); centroids = _c(centroids, np.float32)
+    nq, dim = queries.shape
+    ids = np.empty((nq, nprobe), np.int64); dist = np.empty((nq, nprobe), np.float32)
+    rc = lib().psbo_coarse(_ptr(queries), nq, _ptr(centroids), centroids.shape[0], dim, nprobe, _ptr(ids), _ptr(dist))
+    if rc:
+        raise ValueError("oracle coarse: invalid arguments")
+    return ids, dist
+
+
+def pq_lut(queries, codebook):
+    queries = _c(queries, np.float32); codebook = _c(codebook, np.float32)
+    nq, dim = queries.shape
+    M, K, _ = codebook.shape
+    luts = np.empty((nq, M, K), np.float32)
+    rc = lib().psbo_pq_lut_batch(_ptr(queries), nq, dim, _ptr(codebook), M, K, _ptr(luts))
+    if rc:
+        raise ValueError("oracle lut: invalid arguments")
+    return luts
+
+
+def pq_lut_u8(lut, residual=False):
+    lut = _c(lut, np.float32)
+    M, K = lut.shape
+    q8 = np.empty((M, K), np.uint8); scales = np.empty(M, np.float32)
+    lo = C.c_float(); inf = C.c_float()
+    lib().psbo_pq_lut_u8(_ptr(lut), M, K, int(residual), _ptr(q8), _ptr(scales), C.byref(lo), C.byref(inf))
+    return q8, scales, lo.value, inf.value
+
+
+def pq_scan(queries, probes, offsets, codes, codebook, stage1_k):
+    queries = _c(queries, np.float32); probes = _c(probes, np.int64); offsets = _c(offsets, np.int64)
+    codes = _c(codes, np.uint8); codebook = _c(codebook, np.float32)
+    nq, dim = queries.shape
+    M, K, _ = codebook.shape
+    rows = np.empty((nq, stage1_k), np.int32); dist = np.empty((nq, stage1_k), np.float32)
+    cnt = np.empty(nq, np.int32); scanned = C.c_longlong()
+    rc = lib().psbo_pq_scan(_ptr(queries), nq, dim, _ptr(probes), probes.shape[1], _ptr(offsets), offsets.size - 1,
+                            _ptr(codes), _ptr(codebook), M, K, stage1_k, _ptr(rows), _ptr(dist), _ptr(cnt),
+                            C.byref(scanned))
+    if rc:
+        raise ValueError("oracle scan: invalid arguments")
+    return rows, dist, cnt, scanned.value
+
+
+def rerank(base, queries, candidates, topk, candidate_count=None, counts=None):
+    """base/queries fp32 or uint8 (matching); candidates int32 [batch][stride]."""
+    u8 = base.dtype == np.uint8
+    base = _c(base, np.uint8 if u8 else np.float32); queries = _c(queries, np.uint8 if u8 else np.float32)
+    candidates = _c(candidates, np.int32)
+    batch, stride = candidates.shape
+    cc = stride if candidate_count is None else candidate_count
+    ids = np.empty((batch, topk), np.int32); dist = np.empty((batch, topk), np.float32)
+    cnts = None if counts is None else _c(counts, np.int32)
+    rc = lib().psbo_rerank(None if u8 else _ptr(base), _ptr(base) if u8 else None, C.c_int64(base.shape[0]),
+                           base.shape[1], None if u8 else _ptr(queries), _ptr(queries) if u8 else None,
+                           _ptr(candidates), batch, cc, stride, topk, _ptr(cnts), _ptr(ids), _ptr(dist))
+    if rc:
+        raise ValueError("oracle rerank: invalid arguments")
+    return ids, dist
+
+
+def map_ids(local, reordered_ids):
+    local = _c(local, np.int32); reordered_ids = _c(reordered_ids, np.int64)
+    out = np.empty(local.shape, np.int64)
+    lib().psbo_map_ids(_ptr(local), C.c_int64(local.size), _ptr(reordered_ids), _ptr(out))
+    return out
+
+
+def ivfpq_search(index, queries, nprobe, topk, n_rerank):
+    """index: dict(centroids, offsets, reordered_ids, codes, codebook[M,K,dsub], vectors or None)."""
+    queries = _c(queries, np.float32)
+    nq, dim = queries.shape
+    cen = _c(index["centroids"], np.float32); off = _c(index["offsets"], np.int64)
+    rid = _c(index["reordered_ids"], np.int64); codes = _c(index["codes"], np.uint8)
+    cb = _c(index["codebook"], np.float32)
+    vec = index.get("vectors")
+    vec = None if vec is None else _c(vec, np.float32)
+    M, K, _ = cb.shape
+    n = codes.shape[0]
+    rr = vec is not None and n_rerank > topk
+    s1 = min(n_rerank, n) if rr else topk
+    out_i = np.empty((nq, topk), np.int64); out_d = np.empty((nq, topk), np.float32)
+    out_c = np.empty((nq, nprobe), np.int64); out_s = np.empty((nq, s1), np.int32)
+    scanned = C.c_longlong()
+    rc = lib().psbo_ivfpq_search(_ptr(cen), cen.shape[0], dim, _ptr(off), _ptr(rid), C.c_int64(n), _ptr(codes),
+                                 _ptr(cb), M, K, _ptr(vec), _ptr(queries), nq, nprobe, topk, n_rerank,
+                                 _ptr(out_i), _ptr(out_d), _ptr(out_c), _ptr(out_s), C.byref(scanned))
+    if rc:
+        raise ValueError("oracle ivfpq_search: invalid arguments")
+    return dict(indices=out_i, distances=out_d, coarse=out_c, stage1=out_s, scanned=scanned.value)
+
+
+def ivfflat_search(centroids, offsets, reordered_ids, base, queries, nprobe, topk):
+    queries = _c(queries, np.float32); centroids = _c(centroids, np.float32); base = _c(base, np.float32)
+    offsets = _c(offsets, np.int64)
+    rid = None if reordered_ids is None else _c(reordered_ids, np.int64)
+    nq, dim = queries.shape
+    out_i = np.empty((nq, topk), np.int64); out_d = np.empty((nq, topk), np.float32)
+    rc = lib().psbo_ivfflat_search(_ptr(centroids), centroids.shape[0], dim, _ptr(offsets), _ptr(rid), _ptr(base),
+                                   _ptr(queries), nq, nprobe, topk, _ptr(out_i), _ptr(out_d))
+    if rc:
+        raise ValueError("oracle ivfflat_search: invalid arguments")
+    return out_i, out_d
+
+
+def kmeans_lloyd(data, init_centroids, iters):
+    data = _c(data, np.float32); cen = np.array(init_centroids, dtype=np.float32, order="C", copy=True)
+    n, dim = data.shape
+    assign = np.empty(n, np.int32); obj = np.empty(iters + 1, np.float64)
+    lib().psbo_kmeans_lloyd(_ptr(data), C.c_int64(n), dim, _ptr(cen), cen.shape[0], iters, _ptr(assign), _ptr(obj))
+    return cen, assign, obj
+
+
+def kmeans_assign(data, centroids):
+    data = _c(data, np.float32); centroids = _c(centroids, np.float32)
+    n, dim = data.shape
+    assign = np.empty(n, np.int32); dist = np.empty(n, np.float32)
+    lib().psbo_kmeans_assign(_ptr(data), C.c_int64(n), dim, _ptr(centroids), centroids.shape[0], _ptr(assign), _ptr(dist))
+    return assign, dist
+
+
+def pq_encode(data, codebook):
+    data = _c(data, np.float32); codebook = _c(codebook, np.float32)
+    n, dim = data.shape
+    M, K, _ = codebook.shape
+    codes = np.empty((n, M), np.uint8)
+    rc = lib().psbo_pq_encode(_ptr(data), C.c_int64(n), dim, _ptr(codebook), M, K, _ptr(codes))
+    if rc:
+        raise ValueError("oracle pq_encode: invalid arguments")
+    return codes
+
+
+def recall(got, truth):
+    got = _c(got, np.int64); truth = _c(truth, np.int64)
+    return float(lib().psbo_recall(_ptr(got), _ptr(truth), got.shape[0], got.shape[1]))
+
+
+# ---------------------------------------------------------------- reference (oracle/_ref) wrappers
+def ref_info():
+    r = ref()
+    return dict(isa=r.psbref_fp32_isa().decode(), physical_cores=int(r.psbref_physical_cores()))
+
+
+def ref_coarse(queries, centroids, nprobe, threads=0):
+    queries = _c(queries, np.float32); centroids = _c(centroids, np.float32)
+    nq, dim = queries.shape
+    ids = np.empty((nq, nprobe), np.int64); dist = np.empty((nq, nprobe), np.float32)
+    rc = ref().psbref_coarse(_ptr(queries), nq, _ptr(centroids), centroids.shape[0], dim, nprobe, _ptr(ids), _ptr(dist), threads)
+    if rc:
+        raise ValueError(ref().psbref_last_error().decode())
+    return ids, dist
+
+
+def ref_ivfpq_search(index, queries, probes, topk, n_rerank, fine_threads=1, rerank_threads=0):
+    queries = _c(queries, np.float32); probes = _c(probes, np.int64)
+    nq, dim = queries.shape
+    nprobe = probes.shape[1]
+    cen = _c(index["centroids"], np.float32); off = _c(index["offsets"], np.int64)
+    rid = _c(index["reordered_ids"], np.int64); codes = _c(index["codes"], np.uint8)
+    cb = _c(index["codebook"], np.float32)
+    vec = index.get("vectors")
+    vec = None if vec is None else _c(vec, np.float32)
+    M, K, _ = cb.shape
+    n = codes.shape[0]
+    rr = vec is not None and n_rerank > topk
+    s1 = min(n_rerank, n) if rr else topk
+    out_i = np.empty((nq, topk), np.int64); out_d = np.empty((nq, topk), np.float32)
+    out_s = np.empty((nq, s1), np.int32)
+    times = np.zeros(3, np.float64); scanned = C.c_longlong()
+    rc = ref().psbref_ivfpq_search(_ptr(cen), cen.shape[0], dim, _ptr(off), _ptr(rid), C.c_int64(n), _ptr(codes),
+                                   _ptr(cb), M, K, _ptr(vec), _ptr(queries), nq, _ptr(probes), nprobe, topk, n_rerank,
+                                   fine_threads, rerank_threads, _ptr(out_i), _ptr(out_d), _ptr(out_s),
+                                   _ptr(times), C.byref(scanned))
+    if rc:
+        raise RuntimeError(ref().psbref_last_error().decode())
+    return dict(indices=out_i, distances=out_d, stage1=out_s, times_ms=times, scanned=scanned.value)
+
+
+def ref_rerank(base, queries, candidates, topk, candidate_count=None, counts=None, threads=1, prefetch=4):
+    u8 = base.dtype == np.uint8
+    base = _c(base, np.uint8 if u8 else np.float32); queries = _c(queries, np.uint8 if u8 else np.float32)
+    candidates = _c(candidates, np.int32)
+    batch, stride = candidates.shape
+    cc = stride if candidate_count is None else candidate_count
+    ids = np.empty((batch, topk), np.int32); dist = np.empty((batch, topk), np.float32)
+    cnts = None if counts is None else _c(counts, np.int32)
+    rc = ref().psbref_rerank_host(None if u8 else _ptr(base), _ptr(base) if u8 else None, C.c_int64(base.shape[0]),
+                                  base.shape[1], None if u8 else _ptr(queries), _ptr(queries) if u8 else None,
+                                  _ptr(candidates), batch, cc, stride, topk, _ptr(cnts), threads, prefetch,
+                                  _ptr(ids), _ptr(dist))
+    if rc == 1:
+        raise ValueError(ref().psbref_last_error().decode())
+    if rc:
+        raise RuntimeError(ref().psbref_last_error().decode())
+    return ids, dist
