@@ -1,0 +1,288 @@
+/*
+ * psb.h - C ABI of the B200 (sm_100a) IVF-PQ search path.
+ *
+ * Drop-in boundary for ParaSelect's IVF search hot path: the structs below mirror the reference's
+ * caller-owned "views" (same fields, same order, same types) and the functions are what a binding of the
+ * reference's entry points for this path would call.  Each declaration names the reference interface it
+ * replaces as path:line inside the ParaSelect source tree.
+ *
+ * Conventions
+ *   - Every function returns a psb_status; nothing aborts, throws or resets the device (the reference's
+ *     CUDA_CHECK prints, resets the device and aborts: src/utils/check_cuda_error.cuh:64-82).
+ *     psb_last_error() gives the message of the calling thread's last failure.
+ *   - Pointers named h_* / in *_view structs are HOST pointers owned by the caller; pointers named d_*
+ *     are DEVICE pointers on the session's device.  The library never frees caller memory.
+ *   - Distances are squared L2.  Missing results are id -1 / distance FLT_MAX
+ *     (src/search/ivf_common/ivf_exact_topk.h:87-90).
+ *   - A session serves one caller thread at a time (src/search/ivfrespq/ivfrespq_search.cuh:118-119).
+ *   - There is no CPU fallback: every compute entry point fails with PSB_NO_DEVICE when no sm_100 GPU
+ *     is usable.
+ */
+#ifndef PSB_H
+#define PSB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int psb_status;
+enum {
+    PSB_OK = 0,
+    PSB_INVALID_ARGUMENT = 1,   /* std::invalid_argument in the reference (src/search/ivfpq/ivfpq_index.cu:52-93) */
+    PSB_UNSUPPORTED_SHAPE = 2,  /* shape outside the kernels' supported ranges */
+    PSB_CUDA_ERROR = 3,         /* a CUDA call failed; the message holds cudaGetErrorString */
+    PSB_OUT_OF_MEMORY = 4,
+    PSB_NO_DEVICE = 5,          /* no usable sm_100 device */
+    PSB_INTERNAL = 6,           /* device status word reported an inconsistency (bad list id, row overflow) */
+    PSB_TIMEOUT = 7             /* a bounded device-side wait gave up */
+};
+
+/* ---- views of caller-owned host memory ------------------------------------------------------- */
+
+/* IVFCoarseIndexView, src/search/ivf_common/ivf_search_types.h:41-45 */
+typedef struct psb_coarse_index_view {
+    const float* centroids; /* [nlist][dim] row-major */
+    int nlist;
+    int dim;
+} psb_coarse_index_view;
+
+/* IVFListLayoutView, src/search/ivf_common/ivf_list_layout.h:12-17 (validated as in :19-45) */
+typedef struct psb_list_layout_view {
+    const int64_t* offsets;       /* [nlist + 1], offsets[0] == 0, monotone, offsets[nlist] == n_vectors */
+    const int64_t* reordered_ids; /* [n_vectors] list-contiguous row -> original id */
+    int nlist;
+    int64_t n_vectors;
+} psb_list_layout_view;
+
+/* IVFPQCodeStorageView, src/search/ivf_common/ivf_storage.h:17-23 */
+typedef struct psb_pq_code_storage_view {
+    const uint8_t* codes;     /* [n_vectors][subvectors] list-contiguous */
+    const void* code_storage; /* reference's optional paged CPU view; must be NULL here */
+    const float* codebook;    /* [subvectors][codebook_size][dim / subvectors] */
+    int subvectors;
+    int codebook_size;
+} psb_pq_code_storage_view;
+
+/* IVFHostStorageView, src/search/ivf_common/ivf_host_storage.h:5-12 (exact rows for the rerank) */
+typedef struct psb_host_storage_view {
+    const float* fp32;      /* [count][dim] in list-contiguous order, or NULL */
+    const uint8_t* u8;      /* [count][dim], or NULL */
+    int64_t count;
+    int dim;
+    const int* source_rows; /* must be NULL (physical row == IVF row) */
+} psb_host_storage_view;
+
+/* IVFQueryBatchView, src/search/ivf_common/ivf_search_types.h:47-55 */
+typedef struct psb_query_batch_view {
+    const float* fp32;    /* [count][dim] */
+    const uint8_t* u8;    /* [count][dim], only for the u8 rerank */
+    int count;
+    int dim;
+    const uint16_t* fp16; /* ignored: the coarse stage converts on the device */
+} psb_query_batch_view;
+
+/* IVFSearchParams, src/search/ivf_common/ivf_search_types.h:63-69 */
+typedef struct psb_search_params {
+    int nprobe;
+    int topk;
+    int batch_size;            /* queries per internal batch */
+    int distance;              /* 0 = squared L2 (the only mode on this path) */
+    unsigned char fp16_coarse; /* accepted and ignored: results are always the exact fp32 ones */
+} psb_search_params;
+
+/* IVFSearchOutputView, src/search/ivf_common/ivf_search_types.h:71-75 */
+typedef struct psb_search_output_view {
+    int64_t* indices;  /* [count][topk] original ids */
+    float* distances;  /* [count][topk] */
+    int* coarse_ids;   /* optional [count][nprobe] */
+} psb_search_output_view;
+
+/* IVFPQIndexView, src/search/ivfpq/ivfpq_search_context.h:19-29 */
+typedef struct psb_index_view {
+    psb_coarse_index_view coarse;
+    psb_list_layout_view lists;
+    psb_pq_code_storage_view pq;
+    psb_host_storage_view exact; /* rerank rows; fp32 == u8 == NULL disables the rerank */
+} psb_index_view;
+
+/* How the exact rows reach the GPU during the rerank. */
+enum {
+    PSB_EXACT_HOST_MAPPED = 0, /* register (pin + map) the caller's host rows once; kernels gather rows over PCIe */
+    PSB_EXACT_HOST_STAGED = 1, /* host threads gather rows into pinned rings, cudaMemcpyAsync overlaps the copies */
+    PSB_EXACT_RESIDENT = 2     /* exact.fp32 / exact.u8 is already a device pointer (IVFExactStorageKind::Resident,
+                                  src/search/ivf_common/ivf_storage.h:25-30) */
+};
+
+/* IVFPQSearchOptions (src/search/ivfpq/ivfpq_search_context.h:31-45) reduced to what this path uses,
+ * plus the placement options the reference has no counterpart for. */
+typedef struct psb_options {
+    int device;         /* CUDA device ordinal */
+    int n_rerank;       /* candidates kept by the ADC stage for the exact rerank (<= topk disables it) */
+    int exact_mode;     /* PSB_EXACT_* */
+    int max_batch;      /* largest internal batch the workspaces are sized for (0 = 10000) */
+    int list_begin;     /* shard: this session scans lists [list_begin, list_end); 0,0 = all lists */
+    int list_end;
+    void* stream;       /* cudaStream_t to run on; NULL = a stream owned by the session */
+    int coarse_mode;    /* 0 = auto, 1 = exact SIMT kernel only, 2 = tensor-core filter + exact refinement */
+    int reserved[7];
+} psb_options;
+
+/* Counters and stage times of the last psb_session_search call; names follow the reference's
+ * IVFSearchStatsCollector fields (src/search/ivfpq/pipeline/ivfpq_pipeline.cu:41-71,84-103). */
+typedef struct psb_stats {
+    double total_ms;
+    double coarse_search_ms;
+    double pq_lut_build_ms;
+    double pq_adc_scan_ms;     /* schedule + seed + scan + selection */
+    double pq_rerank_ms;
+    double pq_map_ids_ms;
+    double h2d_ms;
+    double d2h_ms;
+    long long pq_scanned_codes;    /* sum over (query, probe) of the list's row count */
+    long long pq_adc_lookups;      /* pq_scanned_codes * subvectors */
+    long long threshold_candidates;/* rows admitted into the candidate pools */
+    long long fallback_queries;    /* queries re-scanned by the exact fallback */
+    long long h2d_bytes;
+    long long d2h_bytes;
+    long long kernel_launches;
+    int batches;
+    int reserved[7];
+} psb_stats;
+
+typedef struct psb_session psb_session;
+
+/* ---- library ------------------------------------------------------------------------------------ */
+
+/* Message of the calling thread's last failure ("" if none). */
+const char* psb_last_error(void);
+/* Number of usable sm_100 devices (0 when there is no GPU or no driver). */
+int psb_device_count(void);
+const char* psb_version(void);
+
+/* ---- session: prepare once, search many ----------------------------------------------------------- */
+
+/* Uploads centroids, list offsets, ids, codes and codebook, maps the exact rows and sizes the
+ * workspaces.  Replaces ivfpq_prepare_index + ivfpq_prepare (src/search/ivfpq/stage/ivfpq_prepare.cu:91-136,
+ * declared src/search/ivfpq/stage/ivfpq_stages.cuh:8-9) and the IVFResPQSession constructor
+ * (src/search/ivfrespq/ivfrespq_search.cuh:120-133).  Borrowed host assets must outlive the session. */
+psb_status psb_session_create(const psb_index_view* index, const psb_options* options, psb_session** out);
+
+/* ivfpq_release, src/search/ivfpq/stage/ivfpq_stages.cuh:10 */
+psb_status psb_session_destroy(psb_session* session);
+
+/* Whole search with HOST queries and HOST outputs: batches of params->batch_size through
+ * coarse -> LUT -> scan -> rerank -> id map, results written at the global query offset.
+ * Replaces IVFPQIndex::search (src/search/ivfpq/ivfpq_index.h:73-77), ivfpq_run_pipeline
+ * (src/search/ivfpq/pipeline/ivfpq_pipeline.cu:8-116) and ivfrespq_search / IVFResPQSession::search
+ * (src/search/ivfrespq/ivfrespq_search.cuh:114-133).  Returns after the results are in caller memory. */
+psb_status psb_session_search(psb_session* session, const psb_query_batch_view* queries,
+                              const psb_search_params* params, const psb_search_output_view* output,
+                              psb_stats* stats);
+
+/* Blocks until all work queued on the session's stream is done. */
+psb_status psb_session_sync(psb_session* session);
+
+/* ---- stage level, DEVICE pointers, asynchronous on the session's stream --------------------------- */
+/* These mirror the reference's stage functions ivfpq_coarse / ivfpq_fine_* / ivfpq_rerank_cpu /
+ * ivfpq_map_ids (src/search/ivfpq/stage/ivfpq_stages.cuh:11-19) with device buffers in place of the
+ * context's host vectors.  nq must not exceed the session's max_batch. */
+
+/* Coarse stage: per query the nprobe nearest centroids by exact fp32 squared L2, nearest first, ties by
+ * list id.  Replaces coarse::search (src/search/kernels/coarse/coarse.h:18-60,
+ * src/search/kernels/coarse/runtime/coarse_runtime.cu:340) and the CPU loop src/cpu/search/cpu_search.h:261-271.
+ * d_ids [nq][nprobe] int32, d_dist [nq][nprobe] fp32 (may be NULL). */
+psb_status psb_stage_coarse(psb_session* session, const float* d_queries, int nq, int nprobe,
+                            int* d_ids, float* d_dist);
+
+/* Per-query PQ lookup tables lut[q][m][c] = sum_d (q[m*dsub+d] - codebook[m][c][d])^2, built once per
+ * query and shared by every probed list.  Replaces pq_build_query_lut_gpu
+ * (src/search/kernels/fine/gpu_fine/pq_adc/pq_query_lut.cu:14-35) and
+ * src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:51-63.  d_lut [nq][subvectors][codebook_size]. */
+psb_status psb_stage_build_lut(psb_session* session, const float* d_queries, int nq, float* d_lut);
+
+/* ADC scan of the probed lists with per-query selection of the stage1_k smallest distances
+ * (ties by row).  Replaces ivfpq_fine_cpu_lut (src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:69-117) and
+ * pq_query_lut_threshold_search_gpu + pq_candidate_cap_select
+ * (src/search/kernels/fine/gpu_fine/pq_adc/pq_adc_gpu.cuh:98-112,
+ *  src/search/kernels/fine/gpu_fine/pq_adc/pq_candidate_cap_select.cuh:13-33).
+ * d_probes [nq][nprobe] int32 list ids (ids outside [0,nlist) are skipped);
+ * d_rows [nq][stage1_k] list-contiguous row (-1 pad), d_dist same shape (FLT_MAX pad, may be NULL),
+ * d_count [nq] (may be NULL). */
+psb_status psb_stage_scan(psb_session* session, const float* d_lut, int nq, const int* d_probes, int nprobe,
+                          int stage1_k, int* d_rows, float* d_dist, int* d_count);
+
+/* Exact rerank: drops candidates outside [0,count) and duplicates, recomputes fp32 squared L2 against the
+ * exact rows and keeps the topk by (distance, row).  Replaces ivfpq_rerank_cpu -> ivf_rerank_host
+ * (src/search/ivfpq/stage/ivfpq_rerank_cpu.cpp:14-66, src/search/ivf_common/ivf_host_rerank.h:7-27).
+ * d_candidates [nq][candidate_stride] rows, first candidate_count (or d_counts[q]) used;
+ * d_out_rows [nq][topk] int32, d_out_dist [nq][topk]. */
+psb_status psb_stage_rerank(psb_session* session, const float* d_queries, int nq, const int* d_candidates,
+                            int candidate_count, int candidate_stride, const int* d_counts, int topk,
+                            int* d_out_rows, float* d_out_dist);
+
+/* indices[i] = rows[i] >= 0 ? reordered_ids[rows[i]] : -1.  Replaces ivfpq_map_ids
+ * (src/search/ivfpq/stage/ivfpq_map_ids.cpp:4-15). */
+psb_status psb_stage_map_ids(psb_session* session, const int* d_rows, int64_t n, int64_t* d_indices);
+
+/* Merge of per-shard candidate lists (multi-GPU): d_rows/d_dist [parts][nq][k] -> the k smallest by
+ * (distance, row) per query.  No counterpart in the reference (its search is single-GPU). */
+psb_status psb_stage_merge(psb_session* session, const int* d_rows, const float* d_dist, int parts, int nq,
+                           int k, int* d_out_rows, float* d_out_dist);
+
+/* Counters gathered by the stage calls since the last reset (device-side counters are read back here). */
+psb_status psb_session_counters(psb_session* session, psb_stats* stats, int reset);
+
+/* ---- operator level with HOST pointers (one-shot; allocate, run, free) ------------------------------ */
+
+/* ivf_rerank_host, src/search/ivf_common/ivf_host_rerank.h:7-27: same argument meaning; fp32 rows when
+ * storage->fp32 is set, else u8 rows with u8 queries.  PSB_INVALID_ARGUMENT where the reference throws
+ * std::invalid_argument. */
+psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* h_queries_u8,
+                           const float* h_queries_fp32, const int* h_candidates, int batch_n,
+                           int candidate_count, int candidate_stride, int topk, int* h_output_ids,
+                           float* h_output_distances, const int* h_candidate_counts, int device);
+
+/* Coarse stage on host arrays (device copies made internally). */
+psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centroids, int nlist, int dim,
+                           int nprobe, int coarse_mode, int64_t* h_ids, float* h_dist, int device);
+
+/* ---- training and encoding ---------------------------------------------------------------------------- */
+
+/* Lloyd k-means on DEVICE data: assign = argmin squared L2 (strict <, lowest index wins), update = mean,
+ * empty cluster keeps its centroid.  Replaces gpu_kmeans_lloyd (src/clustering/kmeans/kmeans.cuh:47-59,
+ * src/clustering/kmeans/kmeans.cu:296-688).  d_centroids [k][dim] in/out, d_assign [n] out (may be NULL),
+ * h_objective [iters + 1] out (may be NULL). */
+psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_centroids, int k, int iters,
+                            int* d_assign, double* h_objective, int device, void* stream);
+
+/* PQ codebooks: one k-means (codebook_size codewords) per subspace, seeded sampling for the initial
+ * codewords.  Replaces train_plain_pq_codebooks_gpu (src/quantization/pq/pq_trainer.cuh:9-26,
+ * src/quantization/pq/pq_trainer.cu:30-95).  d_codebook [m][k][dim/m] out. */
+psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors, int codebook_size, int iters,
+                        uint64_t seed, float* d_codebook, int device, void* stream);
+
+/* PQ encode: per (row, m) the nearest codeword, ties to the smallest code.  Replaces PQEncoderGPU
+ * (src/quantization/pq/pq_encoder.cuh:10-26, src/quantization/pq/pq_encode.cuh:8-79).
+ * d_codes [n][subvectors] out. */
+psb_status psb_pq_encode(const float* d_data, int64_t n, int dim, const float* d_codebook, int subvectors,
+                         int codebook_size, uint8_t* d_codes, int device, void* stream);
+
+/* ---- synthetic data (bench and tests): counter-based generator, identical for any launch shape -------- */
+
+/* rows [row_begin, row_begin + n) of a Gaussian mixture in component-contiguous order:
+ * x = centre[component(row)] + sigma * N(0,1), component from d_offsets [ncomp + 1].
+ * d_out [n][dim]. */
+psb_status psb_gen_mixture_rows(const float* d_centres, const int64_t* d_offsets, int ncomp, int dim,
+                                float sigma, uint64_t seed, int64_t row_begin, int64_t n, float* d_out,
+                                int device, void* stream);
+/* d_out [n][dim] = scale * N(0,1), element e of the stream seeded by (seed, first_elem + e). */
+psb_status psb_gen_normal(uint64_t seed, int64_t first_elem, int64_t n_elems, float scale, float* d_out,
+                          int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PSB_H */

@@ -1,0 +1,317 @@
+"""ctypes binding of libpsb.so (the C ABI declared in include/psb.h) with numpy / torch conveniences.
+
+The names follow the reference's view API (IVFCoarseIndexView, IVFListLayoutView, IVFPQCodeStorageView,
+IVFQueryBatchView, IVFSearchParams, IVFSearchOutputView: src/search/ivf_common/ivf_search_types.h:41-75 in
+the ParaSelect tree).  There is no CPU path here: every compute call goes to the CUDA library and raises
+PsbError if the library or a usable sm_100 device is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpsb.so")
+
+PSB_OK = 0
+STATUS_NAMES = {0: "PSB_OK", 1: "PSB_INVALID_ARGUMENT", 2: "PSB_UNSUPPORTED_SHAPE", 3: "PSB_CUDA_ERROR",
+                4: "PSB_OUT_OF_MEMORY", 5: "PSB_NO_DEVICE", 6: "PSB_INTERNAL", 7: "PSB_TIMEOUT"}
+EXACT_HOST_MAPPED, EXACT_HOST_STAGED, EXACT_RESIDENT = 0, 1, 2
+
+
+class PsbError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("%s: %s" % (STATUS_NAMES.get(status, status), message))
+        self.status = status
+
+
+class InvalidArgument(PsbError, ValueError):
+    """PSB_INVALID_ARGUMENT: where the reference throws std::invalid_argument."""
+
+
+class CoarseIndexView(C.Structure):
+    _fields_ = [("centroids", C.c_void_p), ("nlist", C.c_int), ("dim", C.c_int)]
+
+
+class ListLayoutView(C.Structure):
+    _fields_ = [("offsets", C.c_void_p), ("reordered_ids", C.c_void_p), ("nlist", C.c_int), ("n_vectors", C.c_int64)]
+
+
+class PQCodeStorageView(C.Structure):
+    _fields_ = [("codes", C.c_void_p), ("code_storage", C.c_void_p), ("codebook", C.c_void_p),
+                ("subvectors", C.c_int), ("codebook_size", C.c_int)]
+
+
+class HostStorageView(C.Structure):
+    _fields_ = [("fp32", C.c_void_p), ("u8", C.c_void_p), ("count", C.c_int64), ("dim", C.c_int),
+                ("source_rows", C.c_void_p)]
+
+
+class QueryBatchView(C.Structure):
+    _fields_ = [("fp32", C.c_void_p), ("u8", C.c_void_p), ("count", C.c_int), ("dim", C.c_int), ("fp16", C.c_void_p)]
+
+
+class SearchParams(C.Structure):
+    _fields_ = [("nprobe", C.c_int), ("topk", C.c_int), ("batch_size", C.c_int), ("distance", C.c_int),
+                ("fp16_coarse", C.c_ubyte)]
+
+
+class SearchOutputView(C.Structure):
+    _fields_ = [("indices", C.c_void_p), ("distances", C.c_void_p), ("coarse_ids", C.c_void_p)]
+
+
+class IndexView(C.Structure):
+    _fields_ = [("coarse", CoarseIndexView), ("lists", ListLayoutView), ("pq", PQCodeStorageView),
+                ("exact", HostStorageView)]
+
+
+class Options(C.Structure):
+    _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
+                ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("coarse_mode", C.c_int),
+                ("reserved", C.c_int * 7)]
+
+
+class Stats(C.Structure):
+    _fields_ = [("total_ms", C.c_double), ("coarse_search_ms", C.c_double), ("pq_lut_build_ms", C.c_double),
+                ("pq_adc_scan_ms", C.c_double), ("pq_rerank_ms", C.c_double), ("pq_map_ids_ms", C.c_double),
+                ("h2d_ms", C.c_double), ("d2h_ms", C.c_double), ("pq_scanned_codes", C.c_longlong),
+                ("pq_adc_lookups", C.c_longlong), ("threshold_candidates", C.c_longlong),
+                ("fallback_queries", C.c_longlong), ("h2d_bytes", C.c_longlong), ("d2h_bytes", C.c_longlong),
+                ("kernel_launches", C.c_longlong), ("batches", C.c_int), ("reserved", C.c_int * 7)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
+
+
+EXPORTS = [
+    "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
+    "psb_session_search", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_scan",
+    "psb_stage_rerank", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
+    "psb_coarse_host", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
+]
+
+_lib = None
+
+
+def lib():
+    """The loaded CUDA library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise PsbError(-1, "libpsb.so is not built: run `python -m paraselect_b200.build`")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.psb_last_error.restype = C.c_char_p
+        _lib.psb_version.restype = C.c_char_p
+    return _lib
+
+
+def _check(status):
+    if status != PSB_OK:
+        msg = lib().psb_last_error().decode()
+        raise (InvalidArgument if status == 1 else PsbError)(status, msg)
+
+
+def device_count() -> int:
+    return int(lib().psb_device_count())
+
+
+def _np(a, dt):
+    return None if a is None else np.ascontiguousarray(a, dtype=dt)
+
+
+def _p(a):
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    return int(a.data_ptr())  # torch tensor
+
+
+class Session:
+    """Prepare once, search many (IVFResPQSession / IVFPQIndex of the reference).
+
+    index: dict with centroids [nlist,dim] f32, offsets [nlist+1] i64, reordered_ids [n] i64, codes [n,M] u8,
+    codebook [M,K,dsub] f32 and optionally vectors [n,dim] f32 (or u8) for the exact rerank.  The arrays are
+    borrowed: they must stay alive (and, in mapped mode, unmoved) for the session's lifetime.
+    """
+
+    def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
+                 list_end=0, stream=None, coarse_mode=0):
+        self._keep = []
+        cen = _np(index["centroids"], np.float32)
+        off = _np(index["offsets"], np.int64)
+        rid = _np(index["reordered_ids"], np.int64)
+        codes = _np(index["codes"], np.uint8)
+        cb = _np(index["codebook"], np.float32)
+        vec = index.get("vectors")
+        self._keep += [cen, off, rid, codes, cb]
+        iv = IndexView()
+        iv.coarse = CoarseIndexView(_p(cen), cen.shape[0], cen.shape[1])
+        n = int(codes.shape[0])
+        iv.lists = ListLayoutView(_p(off), _p(rid), int(index.get("nlist", cen.shape[0])), n)
+        iv.pq = PQCodeStorageView(_p(codes), None, _p(cb), cb.shape[0], cb.shape[1])
+        if vec is not None:
+            if exact_mode == EXACT_RESIDENT:
+                fp32 = vec.dtype != __import__("torch").uint8
+                ptr = int(vec.data_ptr())
+                rows, d = int(vec.shape[0]), int(vec.shape[1])
+            else:
+                fp32 = vec.dtype != np.uint8
+                vec = _np(vec, np.float32 if fp32 else np.uint8)
+                ptr, rows, d = _p(vec), int(vec.shape[0]), int(vec.shape[1])
+            self._keep.append(vec)
+            iv.exact = HostStorageView(ptr if fp32 else None, None if fp32 else ptr, rows, d, None)
+        self.dim, self.nlist, self.M, self.K, self.n = cen.shape[1], cen.shape[0], cb.shape[0], cb.shape[1], n
+        self.n_rerank = n_rerank
+        self.device = device
+        opt = Options(device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
+                      list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode)
+        self._h = C.c_void_p()
+        _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().psb_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    # ---- whole search, host arrays in and out -----------------------------------------------------
+    def search(self, queries, nprobe, topk, batch_size=10000, queries_u8=None, want_coarse=False, out=None):
+        q = _np(queries, np.float32)
+        if q.ndim != 2:
+            raise InvalidArgument(1, "queries must be [count, dim]")
+        nq = q.shape[0]
+        qu8 = _np(queries_u8, np.uint8)
+        if out is None:
+            ids = np.empty((nq, max(topk, 0)), np.int64)
+            dist = np.empty((nq, max(topk, 0)), np.float32)
+        else:
+            ids, dist = out
+        coarse = np.empty((nq, max(nprobe, 0)), np.int32) if want_coarse else None
+        qv = QueryBatchView(_p(q), _p(qu8), nq, q.shape[1], None)
+        pr = SearchParams(nprobe, topk, batch_size, 0, 0)
+        ov = SearchOutputView(_p(ids), _p(dist), _p(coarse))
+        st = Stats()
+        _check(lib().psb_session_search(self._h, C.byref(qv), C.byref(pr), C.byref(ov), C.byref(st)))
+        res = dict(indices=ids, distances=dist, stats=st.as_dict())
+        if want_coarse:
+            res["coarse"] = coarse
+        return res
+
+    def search_raw(self, q_ptr, nq, nprobe, topk, batch_size, ids_ptr, dist_ptr, stats=None):
+        """Same call with raw host pointers (pinned buffers in the bench)."""
+        qv = QueryBatchView(q_ptr, None, nq, self.dim, None)
+        pr = SearchParams(nprobe, topk, batch_size, 0, 0)
+        ov = SearchOutputView(ids_ptr, dist_ptr, None)
+        _check(lib().psb_session_search(self._h, C.byref(qv), C.byref(pr), C.byref(ov),
+                                        C.byref(stats) if stats is not None else None))
+
+    # ---- stage level, device pointers (torch tensors or ints) ---------------------------------------
+    def stage_coarse(self, d_queries, nq, nprobe, d_ids, d_dist=None):
+        _check(lib().psb_stage_coarse(self._h, C.c_void_p(_p(d_queries)), nq, nprobe, C.c_void_p(_p(d_ids)),
+                                      C.c_void_p(_p(d_dist)) if d_dist is not None else None))
+
+    def stage_build_lut(self, d_queries, nq, d_lut):
+        _check(lib().psb_stage_build_lut(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_lut))))
+
+    def stage_scan(self, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist=None, d_count=None):
+        _check(lib().psb_stage_scan(self._h, C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)), nprobe, stage1_k,
+                                    C.c_void_p(_p(d_rows)), C.c_void_p(_p(d_dist)) if d_dist is not None else None,
+                                    C.c_void_p(_p(d_count)) if d_count is not None else None))
+
+    def stage_rerank(self, d_queries, nq, d_cand, count, stride, d_counts, topk, d_out_rows, d_out_dist):
+        _check(lib().psb_stage_rerank(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_cand)), count, stride,
+                                      C.c_void_p(_p(d_counts)) if d_counts is not None else None, topk,
+                                      C.c_void_p(_p(d_out_rows)), C.c_void_p(_p(d_out_dist))))
+
+    def stage_map_ids(self, d_rows, n, d_indices):
+        _check(lib().psb_stage_map_ids(self._h, C.c_void_p(_p(d_rows)), C.c_int64(n), C.c_void_p(_p(d_indices))))
+
+    def stage_merge(self, d_rows, d_dist, parts, nq, k, d_out_rows, d_out_dist):
+        _check(lib().psb_stage_merge(self._h, C.c_void_p(_p(d_rows)), C.c_void_p(_p(d_dist)), parts, nq, k,
+                                     C.c_void_p(_p(d_out_rows)), C.c_void_p(_p(d_out_dist))))
+
+    def sync(self):
+        _check(lib().psb_session_sync(self._h))
+
+    def counters(self, reset=False):
+        st = Stats()
+        _check(lib().psb_session_counters(self._h, C.byref(st), int(reset)))
+        return st.as_dict()
+
+
+# ---- one-shot operators on host arrays ---------------------------------------------------------------
+def rerank_host(base, queries, candidates, topk, candidate_count=None, counts=None, device=0):
+    """ivf_rerank_host of the reference (src/search/ivf_common/ivf_host_rerank.h:7-27) on the GPU."""
+    u8 = base.dtype == np.uint8
+    base = _np(base, np.uint8 if u8 else np.float32)
+    queries = _np(queries, np.uint8 if u8 else np.float32)
+    cand = _np(candidates, np.int32)
+    batch, stride = cand.shape
+    cc = stride if candidate_count is None else candidate_count
+    ids = np.empty((batch, max(topk, 0)), np.int32)
+    dist = np.empty((batch, max(topk, 0)), np.float32)
+    cnt = _np(counts, np.int32)
+    st = HostStorageView(None if u8 else _p(base), _p(base) if u8 else None, base.shape[0], base.shape[1], None)
+    _check(lib().psb_rerank_host(C.byref(st), C.c_void_p(_p(queries)) if u8 else None,
+                                 None if u8 else C.c_void_p(_p(queries)), C.c_void_p(_p(cand)), batch, cc, stride, topk,
+                                 C.c_void_p(_p(ids)), C.c_void_p(_p(dist)), C.c_void_p(_p(cnt)) if cnt is not None else None,
+                                 device))
+    return ids, dist
+
+
+def coarse_host(queries, centroids, nprobe, coarse_mode=0, device=0):
+    q = _np(queries, np.float32)
+    c = _np(centroids, np.float32)
+    ids = np.empty((q.shape[0], max(nprobe, 0)), np.int64)
+    dist = np.empty((q.shape[0], max(nprobe, 0)), np.float32)
+    _check(lib().psb_coarse_host(C.c_void_p(_p(q)), q.shape[0], C.c_void_p(_p(c)), c.shape[0], c.shape[1], nprobe,
+                                 coarse_mode, C.c_void_p(_p(ids)), C.c_void_p(_p(dist)), device))
+    return ids, dist
+
+
+# ---- training / encoding / generators on device tensors -------------------------------------------------
+def _stream_ptr(stream):
+    return C.c_void_p(stream) if stream else None
+
+
+def kmeans_train(d_data, n, dim, d_centroids, k, iters, d_assign=None, device=0, stream=None):
+    obj = np.zeros(iters + 1, np.float64)
+    _check(lib().psb_kmeans_train(C.c_void_p(_p(d_data)), C.c_int64(n), dim, C.c_void_p(_p(d_centroids)), k, iters,
+                                  C.c_void_p(_p(d_assign)) if d_assign is not None else None, C.c_void_p(_p(obj)),
+                                  device, _stream_ptr(stream)))
+    return obj
+
+
+def pq_train(d_data, n, dim, M, K, iters, seed, d_codebook, device=0, stream=None):
+    _check(lib().psb_pq_train(C.c_void_p(_p(d_data)), C.c_int64(n), dim, M, K, iters, C.c_uint64(seed),
+                              C.c_void_p(_p(d_codebook)), device, _stream_ptr(stream)))
+
+
+def pq_encode(d_data, n, dim, d_codebook, M, K, d_codes, device=0, stream=None):
+    _check(lib().psb_pq_encode(C.c_void_p(_p(d_data)), C.c_int64(n), dim, C.c_void_p(_p(d_codebook)), M, K,
+                               C.c_void_p(_p(d_codes)), device, _stream_ptr(stream)))
+
+
+def gen_mixture_rows(d_centres, d_offsets, ncomp, dim, sigma, seed, row_begin, n, d_out, device=0, stream=None):
+    _check(lib().psb_gen_mixture_rows(C.c_void_p(_p(d_centres)), C.c_void_p(_p(d_offsets)), ncomp, dim, C.c_float(sigma),
+                                      C.c_uint64(seed), C.c_int64(row_begin), C.c_int64(n), C.c_void_p(_p(d_out)), device,
+                                      _stream_ptr(stream)))
+
+
+def gen_normal(seed, first, n, scale, d_out, device=0, stream=None):
+    _check(lib().psb_gen_normal(C.c_uint64(seed), C.c_int64(first), C.c_int64(n), C.c_float(scale), C.c_void_p(_p(d_out)),
+                                device, _stream_ptr(stream)))

@@ -1,0 +1,115 @@
+// Host-callable launchers of the CUDA kernels (all asynchronous on the given stream).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "../../include/psb.h"
+
+namespace psb {
+
+// ---- limits shared by host validation and kernels -----------------------------------------------
+constexpr int kMaxProbe = 4096;       // nprobe and coarse top-k
+constexpr int kMaxStage1 = 2048;      // candidates kept per query by the ADC stage
+constexpr int kMaxTopk = 2048;
+constexpr int kMaxRerankWidth = 4096; // candidates per query accepted by the rerank operator
+constexpr int kPoolCapMax = 16384;    // per-query admission pool entries
+constexpr int kSeedSampleMax = 16384; // rows scored per query by the threshold seed
+constexpr int kScanChunkRows = 16384; // rows per scan work item
+constexpr int kMaxCodebook = 256;
+
+// Power of two (the selection kernel sorts the pool padded to a power of two in shared memory).
+inline int pool_capacity(int stage1_k) {
+    int c = 1024;
+    while (c < 16 * stage1_k && c < kPoolCapMax) c <<= 1;
+    return c;
+}
+
+// ---- coarse ---------------------------------------------------------------------------------------
+// Exact fp32 distance matrix tile: dist[q][c] = sum_d (queries[q][d] - centroids[c][d])^2 evaluated as the
+// sequential non-fused sum.  dist is [nq][nlist].
+psb_status launch_coarse_dist_exact(const float* d_queries, int nq, const float* d_centroids, int nlist,
+                                    int dim, float* d_dist, cudaStream_t s);
+// Per query the k smallest (distance, id) pairs of a [nq][n] distance matrix, sorted ascending.
+psb_status launch_select_rows(const float* d_dist, int nq, int n, int k, int* d_ids, float* d_out,
+                              cudaStream_t s);
+
+// ---- PQ lookup tables --------------------------------------------------------------------------------
+psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
+                            float* d_lut, cudaStream_t s);
+
+// ---- schedule + scan -----------------------------------------------------------------------------------
+struct ScanWorkspace {
+    // per list
+    int* vis_count;      // [nlist]
+    int* vis_off;        // [nlist + 1]
+    int* vis_cursor;     // [nlist]
+    long long* item_off; // [nlist + 1]
+    // per (query, probe)
+    int* visitors;       // [max_batch * nprobe]
+    // per query
+    long long* q_rows;   // [max_batch] rows this query scans
+    float* thr;          // [max_batch] admission cutoff
+    int* pool_cnt;       // [max_batch]
+    uint64_t* pool;      // [max_batch][pool_cap]
+    int* fail_list;      // [max_batch]
+    // scalars (device)
+    int* n_fail;         // [1]
+    int* fail_cursor;    // [1]
+    unsigned long long* work_cursor; // [1]
+    unsigned long long* counters;    // [4]: scanned rows, admitted, fallback queries, status
+    int pool_cap;
+};
+
+struct ScanIndex {
+    const uint8_t* codes;      // device, shard rows only
+    const long long* offsets;  // device [nlist + 1], global rows
+    long long row_base;        // global row of codes[0]
+    int nlist;
+    int list_begin, list_end;  // shard
+    int m, k;
+};
+
+psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
+                       const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
+                       int* d_count, int sm_count, cudaStream_t s);
+
+// ---- rerank ------------------------------------------------------------------------------------------------
+// Copies the candidate rows (fp32 or u8, elem_bytes 4 or 1) from src (device-visible: mapped host or device)
+// to stage [nq][candidate_count][dim].
+psb_status launch_gather_rows(const void* src, long long count, int dim, int elem_bytes, const int* d_candidates,
+                              int nq, int candidate_count, int candidate_stride, const int* d_counts,
+                              void* d_stage, cudaStream_t s);
+// Scores the staged rows exactly and keeps the topk by (distance, row) without duplicates.
+psb_status launch_rerank_select(const void* d_stage, long long count, int dim, int elem_bytes,
+                                const void* d_queries, const int* d_candidates, int nq, int candidate_count,
+                                int candidate_stride, const int* d_counts, int topk, int* d_out_rows,
+                                float* d_out_dist, cudaStream_t s);
+psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, long long n_vectors,
+                          long long* d_out, cudaStream_t s);
+psb_status launch_merge(const int* d_rows, const float* d_dist, int parts, int nq, int k, int* d_out_rows,
+                        float* d_out_dist, cudaStream_t s);
+psb_status launch_widen_ids(const int* d_in, long long n, long long* d_out, cudaStream_t s);
+
+// ---- training ------------------------------------------------------------------------------------------------
+psb_status launch_pq_encode(const float* d_data, long long n, int dim, const float* d_codebook, int m, int k,
+                            uint8_t* d_codes, cudaStream_t s);
+psb_status launch_pq_accumulate(const float* d_data, long long n, int dim, const uint8_t* d_codes, int m, int k,
+                                double* d_sums, int* d_counts, cudaStream_t s);
+psb_status launch_pq_update(const double* d_sums, const int* d_counts, int m, int k, int dsub, float* d_codebook,
+                            cudaStream_t s);
+psb_status launch_pq_init(const float* d_data, long long n, int dim, int m, int k, uint64_t seed,
+                          float* d_codebook, cudaStream_t s);
+psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign,
+                                    const float* d_best, double* d_sums, int* d_counts, double* d_obj,
+                                    cudaStream_t s);
+psb_status launch_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids,
+                                cudaStream_t s);
+
+// ---- synthetic data --------------------------------------------------------------------------------------------
+psb_status launch_gen_mixture(const float* d_centres, const long long* d_offsets, int ncomp, int dim, float sigma,
+                              uint64_t seed, long long row_begin, long long n, float* d_out, cudaStream_t s);
+psb_status launch_gen_normal(uint64_t seed, long long first, long long n, float scale, float* d_out,
+                             cudaStream_t s);
+
+}  // namespace psb

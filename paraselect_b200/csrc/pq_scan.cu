@@ -1,0 +1,627 @@
+// PQ lookup tables, the list-centric probe schedule, and the ADC scan with per-query selection.
+//
+// Pipeline per batch (all kernels on one stream, no host synchronisation in between):
+//   k_build_lut        one table [M][K] per query, built once and shared by all probed lists
+//   k_count_visitors   inverts (query, probe) -> per-list visitor counts (+ rows each query will scan)
+//   k_scan_lists       exclusive scans: visitor offsets and work-item offsets per list
+//   k_fill_visitors    per-list visitor arrays
+//   k_seed_threshold   per query: ADC distances of a strided row sample -> admission cutoff
+//   k_scan<M,V>        persistent CTAs; work item = (list, chunk of rows, group of V visitors); each thread
+//                      keeps one code row in registers and scores it for the V visitors whose tables sit
+//                      interleaved in shared memory (one LDS.128 fetches 4 visitors' entries); rows with
+//                      dist <= cutoff are appended to the query's pool
+//   k_select_pool      per query: exact (distance,row) sort of the pool -> stage1_k candidates; flags
+//                      pools that overflowed or came up short
+//   k_exact_fallback   re-scans flagged queries exactly with a CTA-local running top-k (normally zero work)
+//
+// Arithmetic matches the CPU path bit for bit: table entries are the sequential non-fused fp32 sum of
+// (q-c)^2 and ADC distances are the sequential fp32 sum over m = 0..M-1
+// (reference: src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:51-63,76-80).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace psb {
+
+namespace {
+
+constexpr int kScanThreads = 512;
+constexpr int kSeedThreads = 512;
+constexpr int kSelectThreads = 1024;
+constexpr int kFallbackThreads = 1024;
+
+// ------------------------------------------------------------------------------------------------------
+__global__ void k_build_lut(const float* __restrict__ queries, int dim, const float* __restrict__ codebook,
+                            int m, int k, float* __restrict__ lut) {
+    extern __shared__ float s_q[];
+    const int q = blockIdx.x;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) s_q[i] = queries[(size_t)q * dim + i];
+    __syncthreads();
+    const int dsub = dim / m;
+    const int total = m * k;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        const int sub = e / k;
+        const float* c = codebook + (size_t)e * dsub;
+        const float* qs = s_q + sub * dsub;
+        float dist = 0.0f;
+        for (int d = 0; d < dsub; ++d) {
+            const float diff = __fsub_rn(qs[d], __ldg(c + d));
+            dist = __fadd_rn(dist, __fmul_rn(diff, diff));
+        }
+        lut[(size_t)q * total + e] = dist;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// One warp per query: counts visitors per local list and the rows the query will scan.
+__global__ void k_count_visitors(const int* __restrict__ probes, int nq, int nprobe,
+                                 const long long* __restrict__ offsets, int nlist, int lb, int le,
+                                 int* __restrict__ vis_count, long long* __restrict__ q_rows,
+                                 unsigned long long* __restrict__ counters) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= nq) return;
+    long long rows = 0;
+    for (int p = lane; p < nprobe; p += 32) {
+        const int l = probes[(size_t)warp * nprobe + p];
+        if (l < lb || l >= le || l < 0 || l >= nlist) continue;
+        atomicAdd(&vis_count[l], 1);
+        rows += offsets[l + 1] - offsets[l];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) rows += __shfl_xor_sync(0xffffffffu, rows, o);
+    if (lane == 0) {
+        q_rows[warp] = rows;
+        atomicAdd(&counters[0], (unsigned long long)rows);
+    }
+}
+
+// Single CTA: exclusive scans over the lists (visitor offsets, work-item offsets).
+__global__ void k_scan_lists(const int* __restrict__ vis_count, const long long* __restrict__ offsets, int nlist,
+                             int group, int chunk_rows, int* __restrict__ vis_off,
+                             long long* __restrict__ item_off, int* __restrict__ vis_cursor) {
+    __shared__ long long s_part_items[1024];
+    __shared__ int s_part_vis[1024];
+    const int t = threadIdx.x, nt = blockDim.x;
+    const int per = (nlist + nt - 1) / nt;
+    const int b = min(t * per, nlist), e = min(b + per, nlist);
+    long long items = 0; int vis = 0;
+    for (int l = b; l < e; ++l) {
+        const int v = vis_count[l];
+        const long long rows = offsets[l + 1] - offsets[l];
+        vis += v;
+        if (v > 0 && rows > 0) items += (long long)((v + group - 1) / group) * ((rows + chunk_rows - 1) / chunk_rows);
+    }
+    s_part_items[t] = items; s_part_vis[t] = vis;
+    __syncthreads();
+    if (t == 0) {
+        long long ai = 0; int av = 0;
+        for (int i = 0; i < nt; ++i) {
+            const long long ci = s_part_items[i]; const int cv = s_part_vis[i];
+            s_part_items[i] = ai; s_part_vis[i] = av;
+            ai += ci; av += cv;
+        }
+        item_off[nlist] = ai; vis_off[nlist] = av;
+    }
+    __syncthreads();
+    long long ai = s_part_items[t]; int av = s_part_vis[t];
+    for (int l = b; l < e; ++l) {
+        const int v = vis_count[l];
+        const long long rows = offsets[l + 1] - offsets[l];
+        item_off[l] = ai; vis_off[l] = av; vis_cursor[l] = 0;
+        av += v;
+        if (v > 0 && rows > 0) ai += (long long)((v + group - 1) / group) * ((rows + chunk_rows - 1) / chunk_rows);
+    }
+}
+
+__global__ void k_fill_visitors(const int* __restrict__ probes, int nq, int nprobe, int nlist, int lb, int le,
+                                const int* __restrict__ vis_off, int* __restrict__ vis_cursor,
+                                int* __restrict__ visitors) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)nq * nprobe) return;
+    const int l = probes[i];
+    if (l < lb || l >= le || l < 0 || l >= nlist) return;
+    const int pos = atomicAdd(&vis_cursor[l], 1);
+    visitors[vis_off[l] + pos] = (int)(i / nprobe);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// ADC distance of one code row against a table in shared memory laid out [m][k] (one visitor).
+template <int M>
+__device__ __forceinline__ float adc_row_1(const uint8_t* __restrict__ row, const float* __restrict__ s_lut, int k) {
+    float acc = 0.0f;
+    if constexpr (M % 16 == 0) {
+        const uint4* p = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+        for (int w = 0; w < M / 16; ++w) {
+            const uint4 c = __ldg(p + w);
+            const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int code = (cw[j >> 2] >> ((j & 3) * 8)) & 255;
+                acc = __fadd_rn(acc, s_lut[(w * 16 + j) * k + code]);
+            }
+        }
+    } else if constexpr (M % 4 == 0 && M > 0) {
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
+#pragma unroll
+        for (int w = 0; w < M / 4; ++w) {
+            const uint32_t c = __ldg(p + w);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc = __fadd_rn(acc, s_lut[(w * 4 + j) * k + ((c >> (j * 8)) & 255)]);
+        }
+    }
+    return acc;
+}
+// Generic M (runtime), byte loads.
+__device__ __forceinline__ float adc_row_dyn(const uint8_t* __restrict__ row, const float* __restrict__ s_lut,
+                                             int m, int k) {
+    float acc = 0.0f;
+    for (int j = 0; j < m; ++j) acc = __fadd_rn(acc, s_lut[j * k + __ldg(row + j)]);
+    return acc;
+}
+template <int M>
+__device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut, int m, int k) {
+    if constexpr (M > 0) return adc_row_1<M>(row, s_lut, k);
+    else return adc_row_dyn(row, s_lut, m, k);
+}
+
+// Per query: cutoff from a strided sample of the rows it will scan.
+//   N = rows the query scans.  N <= pool capacity: cutoff = +inf (everything is admitted).
+//   Otherwise every stride-th row of each probed list is scored (n_s rows) and the cutoff is the r-th smallest
+//   sample distance with r = ceil(mu + 4 sqrt(mu) + 2), mu = stage1_k * n_s / N: the stage1_k-th smallest of all
+//   N distances lies below it except with negligible probability; the selection kernel verifies the pool holds
+//   at least stage1_k rows and did not overflow, and the exact fallback handles the rest.
+template <int M>
+__global__ void __launch_bounds__(kSeedThreads)
+k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
+                 const long long* __restrict__ offsets, int nlist, int lb, int le,
+                 const uint8_t* __restrict__ codes, long long row_base, int m, int k,
+                 const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr) {
+    extern __shared__ float s_mem[];
+    float* s_lut = s_mem;                 // [m * k]
+    float* s_buf = s_mem + m * k;         // [kSeedSampleMax]
+    __shared__ int s_count;
+    __shared__ unsigned int s_hist[256];
+    __shared__ uint32_t s_prefix, s_rank;
+    const int q = blockIdx.x;
+    const long long N = q_rows[q];
+    if (N <= pool_cap) { if (threadIdx.x == 0) thr[q] = __int_as_float(0x7f800000); return; }
+    long long stride = (N + (kSeedSampleMax - nprobe) - 1) / (kSeedSampleMax - nprobe);
+    if (stride < 16) stride = 16;
+    for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    for (int p = warp; p < nprobe; p += nwarp) {
+        const int l = probes[(size_t)q * nprobe + p];
+        if (l < lb || l >= le || l < 0 || l >= nlist) continue;
+        const long long b = offsets[l], e = offsets[l + 1];
+        const int nj = (int)((e - b + stride - 1) / stride);
+        if (nj <= 0) continue;
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&s_count, nj);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        for (int j = lane; j < nj; j += 32) {
+            const long long r = b + (long long)j * stride;
+            const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k);
+            if (base + j < kSeedSampleMax) s_buf[base + j] = d;
+        }
+    }
+    __syncthreads();
+    const int ns = min(s_count, kSeedSampleMax);
+    const float mu = (float)stage1_k * (float)ns / (float)N;
+    int r = (int)ceilf(mu + 4.0f * sqrtf(mu) + 2.0f);
+    if (r >= ns) { if (threadIdx.x == 0) thr[q] = __int_as_float(0x7f800000); return; }
+    // radix select of the r-th smallest (1-based) of s_buf[0..ns)
+    if (threadIdx.x == 0) { s_prefix = 0; s_rank = (uint32_t)r; }
+    uint32_t mask = 0;
+    for (int pass = 3; pass >= 0; --pass) {
+        const int shift = pass * 8;
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        for (int i = threadIdx.x; i < ns; i += blockDim.x) {
+            const uint32_t key = f2o(s_buf[i]);
+            if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t cum = 0, rank = s_rank;
+            for (int b = 0; b < 256; ++b) {
+                const uint32_t h = s_hist[b];
+                if (cum + h >= rank) { s_prefix = prefix | ((uint32_t)b << shift); s_rank = rank - cum; break; }
+                cum += h;
+            }
+        }
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) thr[q] = o2f(s_prefix);
+}
+
+// ------------------------------------------------------------------------------------------------------
+template <int V> struct LutVec;
+template <> struct LutVec<1> { using T = float; };
+template <> struct LutVec<2> { using T = float2; };
+template <> struct LutVec<4> { using T = float4; };
+
+template <int V>
+__device__ __forceinline__ void lut_add(float (&acc)[V], const float* __restrict__ s_lut, int e) {
+    if constexpr (V == 1) {
+        acc[0] = __fadd_rn(acc[0], s_lut[e]);
+    } else if constexpr (V == 2) {
+        const float2 x = reinterpret_cast<const float2*>(s_lut)[e];
+        acc[0] = __fadd_rn(acc[0], x.x); acc[1] = __fadd_rn(acc[1], x.y);
+    } else if constexpr (V == 4) {
+        const float4 x = reinterpret_cast<const float4*>(s_lut)[e];
+        acc[0] = __fadd_rn(acc[0], x.x); acc[1] = __fadd_rn(acc[1], x.y);
+        acc[2] = __fadd_rn(acc[2], x.z); acc[3] = __fadd_rn(acc[3], x.w);
+    } else {
+        static_assert(V == 8, "visitor group");
+        const float4 x = reinterpret_cast<const float4*>(s_lut)[2 * e];
+        const float4 y = reinterpret_cast<const float4*>(s_lut)[2 * e + 1];
+        acc[0] = __fadd_rn(acc[0], x.x); acc[1] = __fadd_rn(acc[1], x.y);
+        acc[2] = __fadd_rn(acc[2], x.z); acc[3] = __fadd_rn(acc[3], x.w);
+        acc[4] = __fadd_rn(acc[4], y.x); acc[5] = __fadd_rn(acc[5], y.y);
+        acc[6] = __fadd_rn(acc[6], y.z); acc[7] = __fadd_rn(acc[7], y.w);
+    }
+}
+
+struct ScanArgs {
+    const float* lut;          // [nq][m*k]
+    const uint8_t* codes;
+    const long long* offsets;
+    long long row_base;
+    int nlist, m, k;
+    const int* vis_count; const int* vis_off; const int* visitors;
+    const long long* item_off;
+    const float* thr;
+    int* pool_cnt; uint64_t* pool; int pool_cap;
+    unsigned long long* work_cursor;
+    unsigned long long* counters;
+    int chunk_rows;
+};
+
+// Largest l in [0, nlist) with item_off[l] <= item, found by warp 0 with a 32-ary search.
+__device__ __forceinline__ int find_list(const long long* __restrict__ item_off, int nlist, long long item) {
+    const int lane = threadIdx.x & 31;
+    int lo = 0, hi = nlist;  // answer in [lo, hi)
+    while (hi - lo > 1) {
+        const int span = hi - lo;
+        const int step = (span + 31) / 32;
+        const int pos = min(lo + lane * step, hi - 1);
+        const bool ok = item_off[pos] <= item;  // monotone: true for a prefix of the lanes
+        const unsigned bal = __ballot_sync(0xffffffffu, ok);
+        const int last = 31 - __clz((int)bal);  // lane 0 always true (item_off[lo] <= item)
+        const int nlo = min(lo + last * step, hi - 1);
+        const int nhi = min(nlo + step, hi);
+        lo = nlo; hi = nhi;
+    }
+    return lo;
+}
+
+template <int M, int V>
+__global__ void __launch_bounds__(kScanThreads, 1) k_scan(const ScanArgs a) {
+    extern __shared__ __align__(16) float s_lut[];  // [m*k][V] visitor-interleaved
+    __shared__ long long s_item;
+    __shared__ int s_list, s_vq[V];
+    __shared__ float s_thr[V];
+    const int mk = a.m * a.k;
+    const long long total = a.item_off[a.nlist];
+    for (;;) {
+        __syncthreads();  // previous item fully consumed (tables, s_* words)
+        if (threadIdx.x < 32) {
+            long long item = 0;
+            if (threadIdx.x == 0) item = (long long)atomicAdd(a.work_cursor, 1ull);
+            item = __shfl_sync(0xffffffffu, item, 0);
+            int l = -1;
+            if (item < total) l = find_list(a.item_off, a.nlist, item);
+            if (threadIdx.x == 0) { s_item = item; s_list = l; }
+        }
+        __syncthreads();
+        const long long item = s_item;
+        if (item >= total) break;
+        const int l = s_list;
+        const int nvis = a.vis_count[l];
+        const int ngroups = (nvis + V - 1) / V;
+        const long long local = item - a.item_off[l];
+        const int group = (int)(local % ngroups);
+        const long long chunk = local / ngroups;
+        if (threadIdx.x < V) {
+            const int vi = group * V + threadIdx.x;
+            const int q = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;
+            s_vq[threadIdx.x] = q;
+            s_thr[threadIdx.x] = q >= 0 ? a.thr[q] : -1.0f;  // distances are >= 0: -1 admits nothing
+        }
+        __syncthreads();
+        int vq[V]; float thr[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) { vq[v] = s_vq[v]; thr[v] = s_thr[v]; }
+        // stage the V tables, interleaved by visitor (padding visitors reuse visitor 0's table)
+        {
+            const float* src[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) src[v] = a.lut + (size_t)(vq[v] >= 0 ? vq[v] : vq[0]) * mk;
+            for (int e = threadIdx.x; e < mk; e += kScanThreads) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) s_lut[e * V + v] = __ldg(src[v] + e);
+            }
+        }
+        __syncthreads();
+        const long long r0 = a.offsets[l] + chunk * a.chunk_rows;
+        const long long r1 = min(r0 + a.chunk_rows, a.offsets[l + 1]);
+        for (long long r = r0 + threadIdx.x; r < r1; r += kScanThreads) {
+            const uint8_t* row = a.codes + (size_t)(r - a.row_base) * a.m;
+            float acc[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[v] = 0.0f;
+            if constexpr (M > 0 && M % 16 == 0) {
+                const uint4* p = reinterpret_cast<const uint4*>(row);
+                uint4 c[M / 16];
+#pragma unroll
+                for (int w = 0; w < M / 16; ++w) c[w] = __ldg(p + w);
+#pragma unroll
+                for (int w = 0; w < M / 16; ++w) {
+                    const uint32_t cw[4] = {c[w].x, c[w].y, c[w].z, c[w].w};
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        lut_add<V>(acc, s_lut, (w * 16 + j) * a.k + (int)((cw[j >> 2] >> ((j & 3) * 8)) & 255));
+                }
+            } else if constexpr (M > 0 && M % 4 == 0) {
+                const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
+                uint32_t c[M / 4];
+#pragma unroll
+                for (int w = 0; w < M / 4; ++w) c[w] = __ldg(p + w);
+#pragma unroll
+                for (int w = 0; w < M / 4; ++w)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        lut_add<V>(acc, s_lut, (w * 4 + j) * a.k + (int)((c[w] >> (j * 8)) & 255));
+            } else {
+                for (int j = 0; j < a.m; ++j) lut_add<V>(acc, s_lut, j * a.k + (int)__ldg(row + j));
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                if (acc[v] <= thr[v]) {
+                    const int slot = atomicAdd(&a.pool_cnt[vq[v]], 1);
+                    if (slot < a.pool_cap) a.pool[(size_t)vq[v] * a.pool_cap + slot] = make_key(acc[v], (uint32_t)r);
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Per query: sort the pool by (distance,row), emit the first stage1_k.  A pool that overflowed, or that holds
+// fewer than min(stage1_k, rows scanned) entries, sends the query to the exact fallback.
+__global__ void __launch_bounds__(kSelectThreads)
+k_select_pool(const uint64_t* __restrict__ pool, const int* __restrict__ pool_cnt, int pool_cap,
+              const long long* __restrict__ q_rows, int stage1_k, int* __restrict__ out_rows,
+              float* __restrict__ out_dist, int* __restrict__ out_count, int* __restrict__ fail_list,
+              int* __restrict__ n_fail, unsigned long long* __restrict__ counters) {
+    extern __shared__ __align__(16) uint64_t s_keys[];
+    const int q = blockIdx.x;
+    const int c = pool_cnt[q];
+    const long long N = q_rows[q];
+    const long long need = N < stage1_k ? N : stage1_k;
+    if (c > pool_cap || c < need) {
+        if (threadIdx.x == 0) fail_list[atomicAdd(n_fail, 1)] = q;
+        return;  // the fallback writes this query's outputs
+    }
+    if (threadIdx.x == 0) atomicAdd(&counters[1], (unsigned long long)c);
+    const int n = next_pow2(max(c, 2));
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s_keys[i] = i < c ? pool[(size_t)q * pool_cap + i] : KEY_MAX;
+    __syncthreads();
+    block_bitonic_sort(s_keys, n);
+    const int keep = c < stage1_k ? c : stage1_k;
+    for (int i = threadIdx.x; i < stage1_k; i += blockDim.x) {
+        const bool ok = i < keep;
+        out_rows[(size_t)q * stage1_k + i] = ok ? (int)key_idx(s_keys[i]) : -1;
+        if (out_dist) out_dist[(size_t)q * stage1_k + i] = ok ? key_dist(s_keys[i]) : FLT_MAX;
+    }
+    if (out_count && threadIdx.x == 0) out_count[q] = keep;
+}
+
+// Exact per-query scan with a CTA-local running top-k: a buffer of keys below the current cutoff is compacted
+// (sorted, truncated to stage1_k, cutoff tightened) whenever it could overflow during the next block of rows.
+template <int M>
+__global__ void __launch_bounds__(kFallbackThreads)
+k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
+                 const long long* __restrict__ offsets, int nlist, int lb, int le,
+                 const uint8_t* __restrict__ codes, long long row_base, int m, int k, int stage1_k, int buf_n,
+                 const int* __restrict__ fail_list, const int* __restrict__ n_fail, int* __restrict__ fail_cursor,
+                 int* __restrict__ out_rows, float* __restrict__ out_dist, int* __restrict__ out_count,
+                 unsigned long long* __restrict__ counters) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);                 // [buf_n]
+    float* s_lut = reinterpret_cast<float*>(s_raw + (size_t)buf_n * 8);   // [m*k]
+    __shared__ int s_cnt, s_idx;
+    __shared__ uint64_t s_cut;
+    const int nf = *n_fail;
+    for (;;) {
+        __syncthreads();
+        if (threadIdx.x == 0) s_idx = atomicAdd(fail_cursor, 1);
+        __syncthreads();
+        const int idx = s_idx;
+        if (idx >= nf) return;
+        const int q = fail_list[idx];
+        for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
+        if (threadIdx.x == 0) { s_cnt = 0; s_cut = KEY_MAX; atomicAdd(&counters[2], 1ull); }
+        __syncthreads();
+        for (int p = 0; p < nprobe; ++p) {
+            const int l = probes[(size_t)q * nprobe + p];
+            if (l < lb || l >= le || l < 0 || l >= nlist) continue;
+            const long long b = offsets[l], e = offsets[l + 1];
+            for (long long base = b; base < e; base += blockDim.x) {
+                const int c_now = s_cnt;  // stable since the barrier that ended the previous block of rows
+                __syncthreads();          // every thread has read it before any thread appends again
+                if (c_now + (int)blockDim.x > buf_n) {  // uniform decision
+                    const int c = c_now;
+                    for (int i = c + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
+                    __syncthreads();
+                    block_bitonic_sort(s_keys, buf_n);
+                    if (threadIdx.x == 0) {
+                        const int keep = c < stage1_k ? c : stage1_k;
+                        s_cnt = keep;
+                        s_cut = keep == stage1_k ? s_keys[stage1_k - 1] : KEY_MAX;
+                    }
+                    __syncthreads();
+                }
+                const long long r = base + threadIdx.x;
+                if (r < e) {
+                    const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k);
+                    const uint64_t key = make_key(d, (uint32_t)r);
+                    if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
+                }
+                __syncthreads();
+            }
+        }
+        const int c = s_cnt;
+        for (int i = c + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
+        __syncthreads();
+        block_bitonic_sort(s_keys, buf_n);
+        const int keep = c < stage1_k ? c : stage1_k;
+        for (int i = threadIdx.x; i < stage1_k; i += blockDim.x) {
+            const bool ok = i < keep;
+            out_rows[(size_t)q * stage1_k + i] = ok ? (int)key_idx(s_keys[i]) : -1;
+            if (out_dist) out_dist[(size_t)q * stage1_k + i] = ok ? key_dist(s_keys[i]) : FLT_MAX;
+        }
+        if (out_count && threadIdx.x == 0) out_count[q] = keep;
+    }
+}
+
+template <typename F>
+psb_status set_smem(F kernel, size_t bytes) {
+    if (bytes > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return PSB_OK;
+}
+
+template <int M, int V>
+psb_status run_scan_kernel(const ScanArgs& a, int sm_count, cudaStream_t s) {
+    const size_t smem = (size_t)a.m * a.k * V * sizeof(float);
+    PSB_TRY(set_smem(k_scan<M, V>, smem));
+    int occ = 0;
+    PSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_scan<M, V>, kScanThreads, smem));
+    if (occ < 1) return fail(PSB_UNSUPPORTED_SHAPE, "scan kernel does not fit an SM");
+    k_scan<M, V><<<sm_count * occ, kScanThreads, smem, s>>>(a);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+// Visitor-group width: as many tables as fit ~200 KB of shared memory, 4 at most.
+int pick_group(int m, int k) {
+    const size_t one = (size_t)m * k * sizeof(float);
+    if (4 * one <= 200 * 1024) return 4;
+    if (2 * one <= 200 * 1024) return 2;
+    return 1;
+}
+
+template <int M>
+psb_status run_scan_m(const ScanArgs& a, int group, int sm_count, cudaStream_t s) {
+    switch (group) {
+        case 4: return run_scan_kernel<M, 4>(a, sm_count, s);
+        case 2: return run_scan_kernel<M, 2>(a, sm_count, s);
+        default: return run_scan_kernel<M, 1>(a, sm_count, s);
+    }
+}
+
+template <int M>
+psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq, const int* d_probes,
+                    int nprobe, int stage1_k, cudaStream_t s) {
+    const size_t smem = ((size_t)ix.m * ix.k + kSeedSampleMax) * sizeof(float);
+    PSB_TRY(set_smem(k_seed_threshold<M>, smem));
+    k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
+                                                         ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
+                                                         stage1_k, ws.pool_cap, ws.thr);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+template <int M>
+psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, const int* d_probes,
+                        int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count, int sm_count,
+                        cudaStream_t s) {
+    int buf_n = 2 * 1024;
+    while (buf_n < stage1_k + kFallbackThreads) buf_n <<= 1;
+    const size_t smem = (size_t)buf_n * 8 + (size_t)ix.m * ix.k * sizeof(float);
+    PSB_TRY(set_smem(k_exact_fallback<M>, smem));
+    k_exact_fallback<M><<<sm_count, kFallbackThreads, smem, s>>>(
+        d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.m, ix.k,
+        stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+#define PSB_DISPATCH_M(m_value, CALL)                 \
+    switch (m_value) {                                \
+        case 8: { constexpr int MM = 8; CALL; } break;   \
+        case 16: { constexpr int MM = 16; CALL; } break; \
+        case 20: { constexpr int MM = 20; CALL; } break; \
+        case 32: { constexpr int MM = 32; CALL; } break; \
+        case 48: { constexpr int MM = 48; CALL; } break; \
+        case 64: { constexpr int MM = 64; CALL; } break; \
+        default: { constexpr int MM = 0; CALL; } break;  \
+    }
+
+}  // namespace
+
+psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
+                            float* d_lut, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    k_build_lut<<<nq, 256, (size_t)dim * sizeof(float), s>>>(d_queries, dim, d_codebook, m, k, d_lut);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
+                       const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
+                       int* d_count, int sm_count, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    const int group = pick_group(ix.m, ix.k);
+    // schedule
+    PSB_CUDA(cudaMemsetAsync(ws.vis_count, 0, sizeof(int) * (size_t)ix.nlist, s));
+    PSB_CUDA(cudaMemsetAsync(ws.pool_cnt, 0, sizeof(int) * (size_t)nq, s));
+    PSB_CUDA(cudaMemsetAsync(ws.n_fail, 0, sizeof(int), s));
+    PSB_CUDA(cudaMemsetAsync(ws.fail_cursor, 0, sizeof(int), s));
+    PSB_CUDA(cudaMemsetAsync(ws.work_cursor, 0, sizeof(unsigned long long), s));
+    k_count_visitors<<<(nq * 32 + 255) / 256, 256, 0, s>>>(d_probes, nq, nprobe, ix.offsets, ix.nlist, ix.list_begin,
+                                                          ix.list_end, ws.vis_count, ws.q_rows, ws.counters);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    k_scan_lists<<<1, 1024, 0, s>>>(ws.vis_count, ix.offsets, ix.nlist, group, kScanChunkRows, ws.vis_off,
+                                    ws.item_off, ws.vis_cursor);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    const long long pairs = (long long)nq * nprobe;
+    k_fill_visitors<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(d_probes, nq, nprobe, ix.nlist, ix.list_begin,
+                                                                    ix.list_end, ws.vis_off, ws.vis_cursor, ws.visitors);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    // cutoff
+    PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s))));
+    // scan
+    ScanArgs a;
+    a.lut = d_lut; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base;
+    a.nlist = ix.nlist; a.m = ix.m; a.k = ix.k;
+    a.vis_count = ws.vis_count; a.vis_off = ws.vis_off; a.visitors = ws.visitors; a.item_off = ws.item_off;
+    a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
+    a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
+    PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_m<MM>(a, group, sm_count, s))));
+    // selection
+    {
+        const size_t smem = (size_t)ws.pool_cap * sizeof(uint64_t);
+        PSB_TRY(set_smem(k_select_pool, smem));
+        k_select_pool<<<nq, kSelectThreads, smem, s>>>(ws.pool, ws.pool_cnt, ws.pool_cap, ws.q_rows, stage1_k, d_rows,
+                                                       d_dist, d_count, ws.fail_list, ws.n_fail, ws.counters);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    }
+    PSB_DISPATCH_M(ix.m, PSB_TRY((run_fallback<MM>(ix, ws, d_lut, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count,
+                                                  sm_count, s))));
+    return PSB_OK;
+}
+
+}  // namespace psb

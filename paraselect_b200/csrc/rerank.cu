@@ -1,0 +1,257 @@
+// Exact rerank of the ADC candidates, id mapping and the multi-shard candidate merge.
+//
+//   k_gather_rows     copies each candidate's exact row (fp32 or u8) from the exact store - host memory mapped
+//                     into the device address space, read over PCIe, or device memory - into a dense staging
+//                     buffer in HBM; one warp per row, 16-byte loads
+//   k_rerank_select   one CTA per query: half-warps score staged rows in the accumulation order of the CPU
+//                     kernel the reference uses (four 16-lane FMA accumulators, pairwise combine, halving tree:
+//                     src/cpu/distance/fp32_l2_avx512.h:16-53), a bitonic sort orders (distance,row), duplicate
+//                     rows collapse, the first topk are written (reference semantics:
+//                     src/search/ivf_common/ivf_host_rerank.cpp:152-177, src/search/ivf_common/ivf_exact_topk.h:12-22)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace psb {
+namespace {
+
+__device__ __forceinline__ int cand_count(const int* counts, int q, int candidate_count) {
+    if (!counts) return candidate_count;
+    const int c = counts[q];
+    return c < 0 ? 0 : (c > candidate_count ? candidate_count : c);
+}
+
+__global__ void k_gather_rows(const unsigned char* __restrict__ src, long long count, int row_bytes,
+                              const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
+                              const int* __restrict__ counts, unsigned char* __restrict__ stage) {
+    const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long total = (long long)nq * candidate_count;
+    const bool vec = (row_bytes % 16) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(stage)) % 16) == 0;
+    for (long long w = warp0; w < total; w += nwarps) {
+        const int q = (int)(w / candidate_count), i = (int)(w % candidate_count);
+        if (i >= cand_count(counts, q, candidate_count)) continue;
+        const int row = cand[(size_t)q * candidate_stride + i];
+        if (row < 0 || row >= count) continue;
+        const unsigned char* s = src + (size_t)row * row_bytes;
+        unsigned char* d = stage + (size_t)w * row_bytes;
+        if (vec) {
+            const uint4* s4 = reinterpret_cast<const uint4*>(s);
+            uint4* d4 = reinterpret_cast<uint4*>(d);
+            for (int j = lane; j < row_bytes / 16; j += 32) d4[j] = s4[j];
+        } else if (row_bytes % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(stage)) % 4) == 0) {
+            const uint32_t* s4 = reinterpret_cast<const uint32_t*>(s);
+            uint32_t* d4 = reinterpret_cast<uint32_t*>(d);
+            for (int j = lane; j < row_bytes / 4; j += 32) d4[j] = s4[j];
+        } else {
+            for (int j = lane; j < row_bytes; j += 32) d[j] = s[j];
+        }
+    }
+}
+
+// fp32 squared L2 by a half-warp (16 lanes), bit-identical to the AVX-512 kernel's order.
+// All 16 lanes of the half-warp must call it together; hmask names exactly those lanes.
+__device__ __forceinline__ float l2_halfwarp(const float* __restrict__ q, const float* __restrict__ v, int dim, int j,
+                                             unsigned hmask) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int i = 0;
+    for (; i + 64 <= dim; i += 64) {
+        float d = __fsub_rn(q[i + j], v[i + j]); a0 = __fmaf_rn(d, d, a0);
+        d = __fsub_rn(q[i + 16 + j], v[i + 16 + j]); a1 = __fmaf_rn(d, d, a1);
+        d = __fsub_rn(q[i + 32 + j], v[i + 32 + j]); a2 = __fmaf_rn(d, d, a2);
+        d = __fsub_rn(q[i + 48 + j], v[i + 48 + j]); a3 = __fmaf_rn(d, d, a3);
+    }
+    for (; i + 16 <= dim; i += 16) {
+        const float d = __fsub_rn(q[i + j], v[i + j]); a0 = __fmaf_rn(d, d, a0);
+    }
+    float s = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
+    s = __fadd_rn(s, __shfl_xor_sync(hmask, s, 8));
+    s = __fadd_rn(s, __shfl_xor_sync(hmask, s, 4));
+    s = __fadd_rn(s, __shfl_xor_sync(hmask, s, 2));
+    s = __fadd_rn(s, __shfl_xor_sync(hmask, s, 1));
+    for (; i < dim; ++i) { const float d = __fsub_rn(q[i], v[i]); s = __fmaf_rn(d, d, s); }
+    return s;
+}
+
+__device__ __forceinline__ float l2_u8_halfwarp(const unsigned char* __restrict__ q, const unsigned char* __restrict__ v,
+                                                int dim, int j, unsigned hmask) {
+    int s = 0;
+    for (int i = j; i < dim; i += 16) { const int d = (int)q[i] - (int)v[i]; s += d * d; }
+    s += __shfl_xor_sync(hmask, s, 8);
+    s += __shfl_xor_sync(hmask, s, 4);
+    s += __shfl_xor_sync(hmask, s, 2);
+    s += __shfl_xor_sync(hmask, s, 1);
+    return (float)s;
+}
+
+constexpr int kRerankThreads = 256;
+__global__ void __launch_bounds__(kRerankThreads)
+k_rerank_select(const unsigned char* __restrict__ stage, long long count, int dim, int elem_bytes,
+                const unsigned char* __restrict__ queries, const int* __restrict__ cand, int candidate_count,
+                int candidate_stride, const int* __restrict__ counts, int topk, int np,
+                int* __restrict__ out_rows, float* __restrict__ out_dist) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);                   // [np]
+    int* s_rank = reinterpret_cast<int*>(s_raw + (size_t)np * 8);            // [np]
+    unsigned char* s_q = s_raw + (size_t)np * 12;                            // [dim * elem_bytes]
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    const int q = blockIdx.x;
+    const int row_bytes = dim * elem_bytes;
+    for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) s_q[i] = queries[(size_t)q * row_bytes + i];
+    __syncthreads();
+    const int n = cand_count(counts, q, candidate_count);
+    const int hw = threadIdx.x >> 4, j = threadIdx.x & 15, nhw = blockDim.x >> 4;
+    const unsigned hmask = 0xffffu << (threadIdx.x & 16);
+    for (int i = hw; i < np; i += nhw) {
+        uint64_t key = KEY_MAX;
+        int row = -1;
+        if (i < n) row = cand[(size_t)q * candidate_stride + i];
+        if (row >= 0 && row < count) {
+            const unsigned char* v = stage + ((size_t)q * candidate_count + i) * row_bytes;
+            const float d = elem_bytes == 4
+                ? l2_halfwarp(reinterpret_cast<const float*>(s_q), reinterpret_cast<const float*>(v), dim, j, hmask)
+                : l2_u8_halfwarp(s_q, v, dim, j, hmask);
+            key = make_key(d, (uint32_t)row);
+        }
+        if (j == 0) s_keys[i] = key;
+    }
+    __syncthreads();
+    block_bitonic_sort(s_keys, np);
+    // duplicates are adjacent (same row -> same distance -> same key): keep the first of each run
+    int base = 0;
+    for (int c0 = 0; c0 < np; c0 += blockDim.x) {
+        const int i = c0 + threadIdx.x;
+        int keep = 0;
+        if (i < np) {
+            const uint64_t key = s_keys[i];
+            keep = key != KEY_MAX && (i == 0 || s_keys[i - 1] != key);
+        }
+        const int ex = block_exclusive_scan(keep, s_warp, &s_total);
+        if (i < np) s_rank[i] = keep ? base + ex : -1;
+        base += s_total;
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        const int r = s_rank[i];
+        if (r >= 0 && r < topk) {
+            out_rows[(size_t)q * topk + r] = (int)key_idx(s_keys[i]);
+            out_dist[(size_t)q * topk + r] = key_dist(s_keys[i]);
+        }
+    }
+    for (int r = base + threadIdx.x; r < topk; r += blockDim.x) {
+        out_rows[(size_t)q * topk + r] = -1;
+        out_dist[(size_t)q * topk + r] = FLT_MAX;
+    }
+}
+
+__global__ void k_map_ids(const int* __restrict__ rows, long long n, const long long* __restrict__ reordered,
+                          long long n_vectors, long long* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = rows[i];
+    out[i] = (r >= 0 && r < n_vectors) ? reordered[r] : -1ll;
+}
+
+__global__ void k_widen_ids(const int* __restrict__ in, long long n, long long* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[i];
+}
+
+// Per query: the k smallest (distance,row) of parts*k shard candidates.
+__global__ void __launch_bounds__(1024)
+k_merge(const int* __restrict__ rows, const float* __restrict__ dist, int parts, int nq, int k, int np,
+        int* __restrict__ out_rows, float* __restrict__ out_dist) {
+    extern __shared__ __align__(16) uint64_t s_mkeys[];
+    const int q = blockIdx.x;
+    const int total = parts * k;
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        uint64_t key = KEY_MAX;
+        if (i < total) {
+            const int p = i / k, e = i % k;
+            const size_t at = ((size_t)p * nq + q) * k + e;
+            const int r = rows[at];
+            if (r >= 0) key = make_key(dist[at], (uint32_t)r);
+        }
+        s_mkeys[i] = key;
+    }
+    __syncthreads();
+    block_bitonic_sort(s_mkeys, np);
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        const uint64_t key = s_mkeys[i];
+        const bool ok = key != KEY_MAX;
+        out_rows[(size_t)q * k + i] = ok ? (int)key_idx(key) : -1;
+        out_dist[(size_t)q * k + i] = ok ? key_dist(key) : FLT_MAX;
+    }
+}
+
+}  // namespace
+
+psb_status launch_gather_rows(const void* src, long long count, int dim, int elem_bytes, const int* d_candidates,
+                              int nq, int candidate_count, int candidate_stride, const int* d_counts,
+                              void* d_stage, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    const long long total = (long long)nq * candidate_count;
+    long long blocks = (total * 32 + 255) / 256;
+    if (blocks > 148 * 64) blocks = 148 * 64;
+    k_gather_rows<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const unsigned char*>(src), count, dim * elem_bytes,
+                                                   d_candidates, nq, candidate_count, candidate_stride, d_counts,
+                                                   static_cast<unsigned char*>(d_stage));
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_rerank_select(const void* d_stage, long long count, int dim, int elem_bytes,
+                                const void* d_queries, const int* d_candidates, int nq, int candidate_count,
+                                int candidate_stride, const int* d_counts, int topk, int* d_out_rows,
+                                float* d_out_dist, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    if (candidate_count > kMaxRerankWidth) return fail(PSB_UNSUPPORTED_SHAPE, "rerank accepts at most 4096 candidates per query");
+    int np = 32;
+    while (np < candidate_count) np <<= 1;
+    const size_t smem = (size_t)np * 12 + (size_t)dim * elem_bytes + 16;
+    if (smem > 32 * 1024)
+        PSB_CUDA(cudaFuncSetAttribute(k_rerank_select, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_rerank_select<<<nq, kRerankThreads, smem, s>>>(static_cast<const unsigned char*>(d_stage), count, dim, elem_bytes,
+                                                     static_cast<const unsigned char*>(d_queries), d_candidates,
+                                                     candidate_count, candidate_stride, d_counts, topk, np,
+                                                     d_out_rows, d_out_dist);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, long long n_vectors,
+                          long long* d_out, cudaStream_t s) {
+    if (n <= 0) return PSB_OK;
+    k_map_ids<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_rows, n, d_reordered, n_vectors, d_out);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_widen_ids(const int* d_in, long long n, long long* d_out, cudaStream_t s) {
+    if (n <= 0) return PSB_OK;
+    k_widen_ids<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_in, n, d_out);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_merge(const int* d_rows, const float* d_dist, int parts, int nq, int k, int* d_out_rows,
+                        float* d_out_dist, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    const long long total = (long long)parts * k;
+    if (total > 16384) return fail(PSB_UNSUPPORTED_SHAPE, "merge accepts at most 16384 candidates per query");
+    int np = 2;
+    while (np < total) np <<= 1;
+    const size_t smem = (size_t)np * 8;
+    if (smem > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(k_merge, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_merge<<<nq, 1024, smem, s>>>(d_rows, d_dist, parts, nq, k, np, d_out_rows, d_out_dist);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+}  // namespace psb

@@ -1,0 +1,743 @@
+// Host side of the C ABI: sessions (device copies of the index, workspaces, the batch pipeline), the
+// stage-level and one-shot operator entry points, training drivers and the synthetic-data entry points.
+#include "common.cuh"
+#include "kernels.h"
+
+#include <algorithm>
+#include <atomic>
+#include <climits>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <thread>
+#include <vector>
+
+namespace psb {
+
+// ---- status plumbing ------------------------------------------------------------------------------
+std::string& last_error_ref() {
+    thread_local std::string e;
+    return e;
+}
+psb_status fail(psb_status code, const std::string& message) {
+    last_error_ref() = message;
+    return code;
+}
+psb_status cuda_fail(cudaError_t err, const char* what, const char* file, int line) {
+    const char* base = std::strrchr(file, '/');
+    last_error_ref() = std::string(cudaGetErrorString(err)) + " in " + what + " (" + (base ? base + 1 : file) + ":" +
+                       std::to_string(line) + ")";
+    if (err == cudaErrorMemoryAllocation) { cudaGetLastError(); return PSB_OUT_OF_MEMORY; }
+    return PSB_CUDA_ERROR;
+}
+static std::atomic<long long> g_launches{0};
+void count_launch(long long n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches_total() { return g_launches.load(std::memory_order_relaxed); }
+
+namespace {
+
+// Device buffer that grows on demand (contents are not preserved).
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    ~DevBuf() { release(); }
+    void release() { if (p) cudaFree(p); p = nullptr; bytes = 0; }
+    psb_status reserve(size_t need) {
+        if (need <= bytes) return PSB_OK;
+        release();
+        PSB_CUDA(cudaMalloc(&p, need ? need : 1));
+        bytes = need;
+        return PSB_OK;
+    }
+    template <typename T> T* as() const { return static_cast<T*>(p); }
+};
+
+psb_status check_device(int device, cudaDeviceProp* prop_out = nullptr) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return fail(PSB_NO_DEVICE, "no CUDA device is usable; this library has no CPU path");
+    }
+    if (device < 0 || device >= n) return fail(PSB_INVALID_ARGUMENT, "device ordinal out of range");
+    cudaDeviceProp prop;
+    PSB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(PSB_NO_DEVICE, "device is not sm_100 (kernels are built for sm_100a only)");
+    if (prop_out) *prop_out = prop;
+    PSB_CUDA(cudaSetDevice(device));
+    return PSB_OK;
+}
+
+struct EventTimer {
+    std::vector<cudaEvent_t> ev;
+    ~EventTimer() { for (auto e : ev) cudaEventDestroy(e); }
+    psb_status mark(cudaStream_t s) {
+        cudaEvent_t e;
+        PSB_CUDA(cudaEventCreate(&e));
+        ev.push_back(e);
+        PSB_CUDA(cudaEventRecord(e, s));
+        return PSB_OK;
+    }
+    double ms(size_t a, size_t b) const {
+        float t = 0.f;
+        if (a < ev.size() && b < ev.size()) cudaEventElapsedTime(&t, ev[a], ev[b]);
+        return t;
+    }
+};
+
+}  // namespace
+}  // namespace psb
+
+using namespace psb;
+
+struct psb_session {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    psb_options opt{};
+    // index shape
+    int nlist = 0, dim = 0, m = 0, k = 0;
+    long long n_vectors = 0;
+    int list_begin = 0, list_end = 0;
+    long long row_base = 0, shard_rows = 0;
+    // device copies
+    DevBuf centroids, offsets, reordered, codes, codebook;
+    // exact rows
+    int exact_elem = 0;            // 4 = fp32, 1 = u8, 0 = rerank disabled
+    const void* exact_host = nullptr;
+    const void* exact_dev = nullptr;  // device-visible pointer (mapped host or resident)
+    bool registered = false;
+    long long exact_count = 0;
+    // staged mode
+    void* pinned[2] = {nullptr, nullptr};
+    size_t pinned_bytes = 0;
+    cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
+    std::vector<int> h_cand;
+    // workspaces
+    DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
+        pool_cnt, pool, fail_list, scalars, cand_rows, cand_dist, cand_count, stage, out_rows, out_dist, out_ids;
+    int ws_batch = 0, ws_nprobe = 0, ws_stage1 = 0, ws_topk = 0;
+    int pool_cap = 0;
+    unsigned long long* d_counters = nullptr;
+
+    ScanIndex scan_index() const {
+        ScanIndex ix;
+        ix.codes = codes.as<uint8_t>(); ix.offsets = offsets.as<long long>(); ix.row_base = row_base;
+        ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
+        return ix;
+    }
+    ScanWorkspace scan_ws() const {
+        ScanWorkspace w;
+        w.vis_count = vis_count.as<int>(); w.vis_off = vis_off.as<int>(); w.vis_cursor = vis_cursor.as<int>();
+        w.item_off = item_off.as<long long>(); w.visitors = visitors.as<int>(); w.q_rows = q_rows.as<long long>();
+        w.thr = thr.as<float>(); w.pool_cnt = pool_cnt.as<int>(); w.pool = pool.as<uint64_t>();
+        w.fail_list = fail_list.as<int>();
+        unsigned long long* sc = scalars.as<unsigned long long>();
+        w.counters = sc;                                   // [0..3]
+        w.work_cursor = sc + 4;
+        w.n_fail = reinterpret_cast<int*>(sc + 5);
+        w.fail_cursor = reinterpret_cast<int*>(sc + 6);
+        w.pool_cap = pool_cap;
+        return w;
+    }
+};
+
+namespace {
+
+int stage1_width(const psb_session* s, int topk) {
+    const bool rerank = s->exact_elem != 0 && s->opt.n_rerank > topk;
+    if (!rerank) return topk;
+    return (int)std::min<long long>(s->opt.n_rerank, s->n_vectors);
+}
+
+psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
+    PSB_TRY(s->vis_count.reserve(sizeof(int) * (size_t)s->nlist));
+    PSB_TRY(s->vis_off.reserve(sizeof(int) * ((size_t)s->nlist + 1)));
+    PSB_TRY(s->vis_cursor.reserve(sizeof(int) * (size_t)s->nlist));
+    PSB_TRY(s->item_off.reserve(sizeof(long long) * ((size_t)s->nlist + 1)));
+    PSB_TRY(s->visitors.reserve(sizeof(int) * (size_t)nq * nprobe));
+    PSB_TRY(s->q_rows.reserve(sizeof(long long) * (size_t)nq));
+    PSB_TRY(s->thr.reserve(sizeof(float) * (size_t)nq));
+    PSB_TRY(s->pool_cnt.reserve(sizeof(int) * (size_t)nq));
+    const int cap = pool_capacity(stage1_k);
+    PSB_TRY(s->pool.reserve(sizeof(uint64_t) * (size_t)nq * cap));
+    s->pool_cap = cap;
+    PSB_TRY(s->fail_list.reserve(sizeof(int) * (size_t)nq));
+    if (!s->scalars.p) {
+        PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 8));
+        PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(unsigned long long) * 8, s->stream));
+    }
+    return PSB_OK;
+}
+
+psb_status ensure_pipeline_ws(psb_session* s, int nq, int nprobe, int topk, int stage1_k) {
+    PSB_TRY(s->q.reserve(sizeof(float) * (size_t)nq * s->dim));
+    PSB_TRY(s->probes.reserve(sizeof(int) * (size_t)nq * nprobe));
+    PSB_TRY(s->probe_dist.reserve(sizeof(float) * (size_t)nq * nprobe));
+    PSB_TRY(s->lut.reserve(sizeof(float) * (size_t)nq * s->m * s->k));
+    PSB_TRY(s->cand_rows.reserve(sizeof(int) * (size_t)nq * stage1_k));
+    PSB_TRY(s->cand_dist.reserve(sizeof(float) * (size_t)nq * stage1_k));
+    PSB_TRY(s->cand_count.reserve(sizeof(int) * (size_t)nq));
+    PSB_TRY(s->out_rows.reserve(sizeof(int) * (size_t)nq * topk));
+    PSB_TRY(s->out_dist.reserve(sizeof(float) * (size_t)nq * topk));
+    PSB_TRY(s->out_ids.reserve(sizeof(long long) * (size_t)nq * topk));
+    return ensure_scan_ws(s, nq, nprobe, stage1_k);
+}
+
+// Coarse stage on device queries: exact distance tiles + row selection, query-chunked so the distance tile
+// stays below ~1 GiB.
+psb_status coarse_exact(psb_session* s, const float* d_queries, int nq, int nprobe, int* d_ids, float* d_dist) {
+    const size_t row_bytes = sizeof(float) * (size_t)s->nlist;
+    int chunk = (int)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
+    chunk = std::min(chunk, nq);
+    PSB_TRY(s->dist_tile.reserve(row_bytes * (size_t)chunk));
+    for (int q0 = 0; q0 < nq; q0 += chunk) {
+        const int n = std::min(chunk, nq - q0);
+        PSB_TRY(launch_coarse_dist_exact(d_queries + (size_t)q0 * s->dim, n, s->centroids.as<float>(), s->nlist, s->dim,
+                                         s->dist_tile.as<float>(), s->stream));
+        PSB_TRY(launch_select_rows(s->dist_tile.as<float>(), n, s->nlist, nprobe, d_ids + (size_t)q0 * nprobe,
+                                   d_dist ? d_dist + (size_t)q0 * nprobe : nullptr, s->stream));
+    }
+    return PSB_OK;
+}
+
+psb_status validate_index(const psb_index_view* ix) {
+    if (!ix) return fail(PSB_INVALID_ARGUMENT, "index view is null");
+    const auto& L = ix->lists;
+    if (!L.offsets) return fail(PSB_INVALID_ARGUMENT, "IVF list offsets are null");
+    if (L.nlist <= 0 || L.n_vectors < 0) return fail(PSB_INVALID_ARGUMENT, "invalid IVF list layout shape");
+    if (L.n_vectors > 0 && !L.reordered_ids) return fail(PSB_INVALID_ARGUMENT, "IVF reordered IDs are null");
+    if (L.offsets[0] != 0) return fail(PSB_INVALID_ARGUMENT, "IVF list offsets must start at zero");
+    for (int l = 0; l < L.nlist; ++l) {
+        const int64_t b = L.offsets[l], e = L.offsets[l + 1];
+        if (e < b) return fail(PSB_INVALID_ARGUMENT, "IVF list offsets must be monotonic");
+        if (e - b > INT_MAX) return fail(PSB_INVALID_ARGUMENT, "IVF list size exceeds int32 backend limit");
+    }
+    if (L.offsets[L.nlist] != L.n_vectors) return fail(PSB_INVALID_ARGUMENT, "IVF terminal offset does not match n_vectors");
+    if (L.n_vectors > INT_MAX) return fail(PSB_INVALID_ARGUMENT, "n_vectors exceeds int32 row index limit");
+    const auto& C = ix->coarse;
+    if (!C.centroids || C.nlist != L.nlist || C.dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid IVF coarse index view");
+    const auto& P = ix->pq;
+    if (!P.codes && L.n_vectors > 0) return fail(PSB_INVALID_ARGUMENT, "PQ codes are null");
+    if (P.code_storage) return fail(PSB_UNSUPPORTED_SHAPE, "paged CPU code storage is not supported; pass row-major codes");
+    if (!P.codebook || P.subvectors <= 0 || C.dim % P.subvectors != 0)
+        return fail(PSB_INVALID_ARGUMENT, "PQ subvectors must divide dim");
+    if (P.codebook_size <= 0 || P.codebook_size > kMaxCodebook) return fail(PSB_INVALID_ARGUMENT, "PQ codebook_size must be in 1..256");
+    const auto& E = ix->exact;
+    if (E.fp32 || E.u8) {
+        if (E.count != L.n_vectors || E.dim != C.dim) return fail(PSB_INVALID_ARGUMENT, "exact storage shape does not match the index");
+        if (E.source_rows) return fail(PSB_UNSUPPORTED_SHAPE, "exact storage with a row permutation is not supported");
+    }
+    return PSB_OK;
+}
+
+psb_status validate_params(const psb_session* s, const psb_query_batch_view* qv, const psb_search_params* p,
+                           const psb_search_output_view* out) {
+    if (!qv || !p || !out) return fail(PSB_INVALID_ARGUMENT, "null query, params or output view");
+    if (qv->count < 0 || qv->dim != s->dim) return fail(PSB_INVALID_ARGUMENT, "query dim does not match the index");
+    if (qv->count > 0 && !qv->fp32) return fail(PSB_INVALID_ARGUMENT, "fp32 queries are required");
+    if (p->nprobe <= 0 || p->nprobe > s->nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
+    if (p->topk <= 0) return fail(PSB_INVALID_ARGUMENT, "topk must be positive");
+    if (p->batch_size <= 0) return fail(PSB_INVALID_ARGUMENT, "batch_size must be positive");
+    if (p->distance != 0) return fail(PSB_UNSUPPORTED_SHAPE, "only squared L2 is supported on this path");
+    if (p->nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
+    if (p->topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "topk above 2048 is not supported");
+    if (qv->count > 0 && (!out->indices || !out->distances)) return fail(PSB_INVALID_ARGUMENT, "output buffers are null");
+    if (s->exact_elem == 1 && s->opt.n_rerank > p->topk && !qv->u8) return fail(PSB_INVALID_ARGUMENT, "u8 rerank needs u8 queries");
+    return PSB_OK;
+}
+
+// Staged rerank transport: candidate rows come back to the host, host threads gather the exact rows into two
+// pinned buffers, and cudaMemcpyAsync moves each filled buffer while the other is being filled.
+psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, int stride, const int* d_counts) {
+    (void)d_counts;
+    const size_t row_bytes = (size_t)s->dim * s->exact_elem;
+    s->h_cand.resize((size_t)nq * stride);
+    PSB_CUDA(cudaMemcpyAsync(s->h_cand.data(), d_cand, sizeof(int) * (size_t)nq * stride, cudaMemcpyDeviceToHost, s->stream));
+    PSB_CUDA(cudaStreamSynchronize(s->stream));
+    const size_t chunk_q = std::max<size_t>(1, ((size_t)64 << 20) / std::max<size_t>(1, row_bytes * width));
+    const size_t need = chunk_q * width * row_bytes;
+    if (s->pinned_bytes < need) {
+        for (int i = 0; i < 2; ++i) {
+            if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
+            s->pinned[i] = nullptr;
+            PSB_CUDA(cudaHostAlloc(&s->pinned[i], need, cudaHostAllocDefault));
+            if (!s->pinned_ev[i]) PSB_CUDA(cudaEventCreateWithFlags(&s->pinned_ev[i], cudaEventDisableTiming));
+        }
+        s->pinned_bytes = need;
+    }
+    const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
+    const int nthreads = (int)std::min<unsigned>(hc, 32);
+    int slot = 0;
+    bool used[2] = {false, false};
+    for (size_t q0 = 0; q0 < (size_t)nq; q0 += chunk_q, slot ^= 1) {
+        const size_t n = std::min(chunk_q, (size_t)nq - q0);
+        if (used[slot]) PSB_CUDA(cudaEventSynchronize(s->pinned_ev[slot]));
+        unsigned char* dst = static_cast<unsigned char*>(s->pinned[slot]);
+        const unsigned char* src = static_cast<const unsigned char*>(s->exact_host);
+        const size_t total = n * width;
+        std::vector<std::thread> pool;
+        for (int t = 0; t < nthreads; ++t)
+            pool.emplace_back([&, t]() {
+                const size_t b = total * t / nthreads, e = total * (t + 1) / nthreads;
+                for (size_t i = b; i < e; ++i) {
+                    const size_t q = q0 + i / width, c = i % width;
+                    const int row = s->h_cand[q * stride + c];
+                    if (row >= 0 && row < s->exact_count) std::memcpy(dst + i * row_bytes, src + (size_t)row * row_bytes, row_bytes);
+                }
+            });
+        for (auto& th : pool) th.join();
+        PSB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(s->stage.p) + q0 * width * row_bytes, dst, total * row_bytes,
+                                 cudaMemcpyHostToDevice, s->stream));
+        PSB_CUDA(cudaEventRecord(s->pinned_ev[slot], s->stream));
+        used[slot] = true;
+    }
+    return PSB_OK;
+}
+
+psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int* d_cand, int width, int stride,
+                       const int* d_counts, int topk, int* d_out_rows, float* d_out_dist) {
+    if (!s->exact_elem) return fail(PSB_INVALID_ARGUMENT, "session has no exact rows for the rerank");
+    if (width <= 0 || stride < width || topk <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid rerank request");
+    if (width > kMaxRerankWidth || topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "rerank width above 4096 or topk above 2048");
+    PSB_TRY(s->stage.reserve((size_t)nq * width * s->dim * s->exact_elem));
+    if (s->opt.exact_mode == PSB_EXACT_HOST_STAGED) {
+        PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
+    } else {
+        PSB_TRY(launch_gather_rows(s->exact_dev, s->exact_count, s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
+                                   s->stage.p, s->stream));
+    }
+    return launch_rerank_select(s->stage.p, s->exact_count, s->dim, s->exact_elem, d_queries, d_cand, nq, width, stride,
+                                d_counts, topk, d_out_rows, d_out_dist, s->stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* psb_last_error(void) { return last_error_ref().c_str(); }
+const char* psb_version(void) { return "paraselect-b200 0.1 (sm_100a)"; }
+
+int psb_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    int ok = 0;
+    for (int i = 0; i < n; ++i) {
+        cudaDeviceProp p;
+        if (cudaGetDeviceProperties(&p, i) == cudaSuccess && p.major == 10) ++ok;
+    }
+    return ok;
+}
+
+psb_status psb_session_create(const psb_index_view* index, const psb_options* options, psb_session** out) {
+    if (!out) return fail(PSB_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    PSB_TRY(validate_index(index));
+    psb_options opt{};
+    if (options) opt = *options;
+    if (opt.max_batch <= 0) opt.max_batch = 10000;
+    if (opt.exact_mode < 0 || opt.exact_mode > PSB_EXACT_RESIDENT) return fail(PSB_INVALID_ARGUMENT, "unknown exact_mode");
+    const int nlist = index->lists.nlist;
+    int lb = opt.list_begin, le = opt.list_end;
+    if (lb == 0 && le == 0) le = nlist;
+    if (lb < 0 || le > nlist || lb > le) return fail(PSB_INVALID_ARGUMENT, "invalid list shard range");
+    if (opt.n_rerank > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "n_rerank above 2048 is not supported");
+    cudaDeviceProp prop;
+    PSB_TRY(check_device(opt.device, &prop));
+    std::unique_ptr<psb_session> s(new (std::nothrow) psb_session());
+    if (!s) return fail(PSB_OUT_OF_MEMORY, "host allocation failed");
+    s->device = opt.device; s->sm_count = prop.multiProcessorCount; s->opt = opt;
+    s->nlist = nlist; s->dim = index->coarse.dim; s->m = index->pq.subvectors; s->k = index->pq.codebook_size;
+    s->n_vectors = index->lists.n_vectors; s->list_begin = lb; s->list_end = le;
+    s->row_base = index->lists.offsets[lb];
+    s->shard_rows = index->lists.offsets[le] - s->row_base;
+    if (opt.stream) s->stream = static_cast<cudaStream_t>(opt.stream);
+    else { PSB_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking)); s->own_stream = true; }
+    cudaStream_t st = s->stream;
+    PSB_TRY(s->centroids.reserve(sizeof(float) * (size_t)nlist * s->dim));
+    PSB_CUDA(cudaMemcpyAsync(s->centroids.p, index->coarse.centroids, sizeof(float) * (size_t)nlist * s->dim, cudaMemcpyHostToDevice, st));
+    PSB_TRY(s->offsets.reserve(sizeof(long long) * ((size_t)nlist + 1)));
+    PSB_CUDA(cudaMemcpyAsync(s->offsets.p, index->lists.offsets, sizeof(long long) * ((size_t)nlist + 1), cudaMemcpyHostToDevice, st));
+    PSB_TRY(s->reordered.reserve(sizeof(long long) * (size_t)std::max<long long>(1, s->n_vectors)));
+    if (s->n_vectors > 0)
+        PSB_CUDA(cudaMemcpyAsync(s->reordered.p, index->lists.reordered_ids, sizeof(long long) * (size_t)s->n_vectors, cudaMemcpyHostToDevice, st));
+    PSB_TRY(s->codes.reserve((size_t)std::max<long long>(1, s->shard_rows) * s->m + 16));
+    if (s->shard_rows > 0)
+        PSB_CUDA(cudaMemcpyAsync(s->codes.p, index->pq.codes + (size_t)s->row_base * s->m, (size_t)s->shard_rows * s->m, cudaMemcpyHostToDevice, st));
+    const size_t cb_bytes = sizeof(float) * (size_t)s->m * s->k * (s->dim / s->m);
+    PSB_TRY(s->codebook.reserve(cb_bytes));
+    PSB_CUDA(cudaMemcpyAsync(s->codebook.p, index->pq.codebook, cb_bytes, cudaMemcpyHostToDevice, st));
+    // exact rows
+    const auto& E = index->exact;
+    if (E.fp32 || E.u8) {
+        s->exact_elem = E.fp32 ? 4 : 1;
+        s->exact_host = E.fp32 ? static_cast<const void*>(E.fp32) : static_cast<const void*>(E.u8);
+        s->exact_count = E.count;
+        const size_t bytes = (size_t)E.count * E.dim * s->exact_elem;
+        if (opt.exact_mode == PSB_EXACT_RESIDENT) {
+            s->exact_dev = s->exact_host;
+        } else if (opt.exact_mode == PSB_EXACT_HOST_MAPPED && bytes > 0) {
+            cudaError_t e = cudaHostRegister(const_cast<void*>(s->exact_host), bytes, cudaHostRegisterMapped | cudaHostRegisterReadOnly);
+            if (e == cudaErrorHostMemoryAlreadyRegistered) { cudaGetLastError(); e = cudaSuccess; }
+            else if (e != cudaSuccess) {
+                cudaGetLastError();
+                e = cudaHostRegister(const_cast<void*>(s->exact_host), bytes, cudaHostRegisterMapped);
+                if (e == cudaSuccess) s->registered = true;
+            } else s->registered = true;
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return fail(PSB_CUDA_ERROR, std::string("cannot map the exact rows into the device address space (") +
+                                                cudaGetErrorString(e) + "); use PSB_EXACT_HOST_STAGED");
+            }
+            void* dp = nullptr;
+            PSB_CUDA(cudaHostGetDevicePointer(&dp, const_cast<void*>(s->exact_host), 0));
+            s->exact_dev = dp;
+        }
+    }
+    PSB_CUDA(cudaStreamSynchronize(st));
+    *out = s.release();
+    return PSB_OK;
+}
+
+psb_status psb_session_destroy(psb_session* s) {
+    if (!s) return PSB_OK;
+    cudaSetDevice(s->device);
+    cudaStreamSynchronize(s->stream);
+    if (s->registered) cudaHostUnregister(const_cast<void*>(s->exact_host));
+    for (int i = 0; i < 2; ++i) {
+        if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
+        if (s->pinned_ev[i]) cudaEventDestroy(s->pinned_ev[i]);
+    }
+    if (s->own_stream) cudaStreamDestroy(s->stream);
+    delete s;
+    cudaGetLastError();
+    return PSB_OK;
+}
+
+psb_status psb_session_sync(psb_session* s) {
+    if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
+    PSB_CUDA(cudaStreamSynchronize(s->stream));
+    return PSB_OK;
+}
+
+psb_status psb_stage_coarse(psb_session* s, const float* d_queries, int nq, int nprobe, int* d_ids, float* d_dist) {
+    if (!s || !d_queries || !d_ids) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (nprobe <= 0 || nprobe > s->nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
+    if (nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return coarse_exact(s, d_queries, nq, nprobe, d_ids, d_dist);
+}
+
+psb_status psb_stage_build_lut(psb_session* s, const float* d_queries, int nq, float* d_lut) {
+    if (!s || !d_queries || !d_lut) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_build_lut(d_queries, nq, s->dim, s->codebook.as<float>(), s->m, s->k, d_lut, s->stream);
+}
+
+psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int* d_probes, int nprobe,
+                          int stage1_k, int* d_rows, float* d_dist, int* d_count) {
+    if (!s || !d_lut || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (nprobe <= 0 || stage1_k <= 0) return fail(PSB_INVALID_ARGUMENT, "nprobe and stage1_k must be positive");
+    if (nprobe > kMaxProbe || stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or stage1_k above 2048");
+    PSB_CUDA(cudaSetDevice(s->device));
+    PSB_TRY(ensure_scan_ws(s, nq, nprobe, stage1_k));
+    return launch_scan(s->scan_index(), s->scan_ws(), d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count,
+                       s->sm_count, s->stream);
+}
+
+psb_status psb_stage_rerank(psb_session* s, const float* d_queries, int nq, const int* d_candidates,
+                            int candidate_count, int candidate_stride, const int* d_counts, int topk,
+                            int* d_out_rows, float* d_out_dist) {
+    if (!s || !d_queries || !d_candidates || !d_out_rows || !d_out_dist) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return rerank_impl(s, d_queries, nq, d_candidates, candidate_count, candidate_stride, d_counts, topk, d_out_rows, d_out_dist);
+}
+
+psb_status psb_stage_map_ids(psb_session* s, const int* d_rows, int64_t n, int64_t* d_indices) {
+    if (!s || !d_rows || !d_indices) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_map_ids(d_rows, n, s->reordered.as<long long>(), s->n_vectors, reinterpret_cast<long long*>(d_indices), s->stream);
+}
+
+psb_status psb_stage_merge(psb_session* s, const int* d_rows, const float* d_dist, int parts, int nq, int k,
+                           int* d_out_rows, float* d_out_dist) {
+    if (!s || !d_rows || !d_dist || !d_out_rows || !d_out_dist || parts <= 0 || k <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid merge request");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_merge(d_rows, d_dist, parts, nq, k, d_out_rows, d_out_dist, s->stream);
+}
+
+psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
+    if (!s || !stats) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    unsigned long long h[4] = {0, 0, 0, 0};
+    if (s->scalars.p) {
+        PSB_CUDA(cudaMemcpyAsync(h, s->scalars.p, sizeof(h), cudaMemcpyDeviceToHost, s->stream));
+        if (reset) PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(h), s->stream));
+        PSB_CUDA(cudaStreamSynchronize(s->stream));
+    }
+    stats->pq_scanned_codes = (long long)h[0];
+    stats->pq_adc_lookups = (long long)h[0] * s->m;
+    stats->threshold_candidates = (long long)h[1];
+    stats->fallback_queries = (long long)h[2];
+    stats->kernel_launches = launches_total();
+    return PSB_OK;
+}
+
+psb_status psb_session_search(psb_session* s, const psb_query_batch_view* queries, const psb_search_params* params,
+                              const psb_search_output_view* output, psb_stats* stats) {
+    if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
+    PSB_TRY(validate_params(s, queries, params, output));
+    PSB_CUDA(cudaSetDevice(s->device));
+    if (stats) std::memset(stats, 0, sizeof(*stats));
+    const int total = queries->count;
+    if (total == 0) return PSB_OK;
+    const int nprobe = params->nprobe, topk = params->topk;
+    const int batch = std::min(std::min(params->batch_size, s->opt.max_batch), total);
+    const int stage1_k = stage1_width(s, topk);
+    const bool rerank = s->exact_elem != 0 && s->opt.n_rerank > topk;
+    if (stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "candidate width above 2048 is not supported");
+    PSB_TRY(ensure_pipeline_ws(s, batch, nprobe, topk, stage1_k));
+    if (rerank && s->exact_elem == 1) PSB_TRY(s->q_u8.reserve((size_t)batch * s->dim));
+    cudaStream_t st = s->stream;
+    const long long launches0 = launches_total();
+    unsigned long long c0[4] = {0, 0, 0, 0};
+    if (stats) {
+        PSB_CUDA(cudaMemcpyAsync(c0, s->scalars.p, sizeof(c0), cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaStreamSynchronize(st));
+    }
+    double t_h2d = 0, t_coarse = 0, t_lut = 0, t_scan = 0, t_rr = 0, t_map = 0, t_d2h = 0;
+    long long h2d = 0, d2h = 0;
+    int nb = 0;
+    for (int q0 = 0; q0 < total; q0 += batch, ++nb) {
+        const int n = std::min(batch, total - q0);
+        EventTimer tm;
+        if (stats) PSB_TRY(tm.mark(st));
+        PSB_CUDA(cudaMemcpyAsync(s->q.p, queries->fp32 + (size_t)q0 * s->dim, sizeof(float) * (size_t)n * s->dim, cudaMemcpyHostToDevice, st));
+        h2d += (long long)sizeof(float) * n * s->dim;
+        if (rerank && s->exact_elem == 1) {
+            PSB_CUDA(cudaMemcpyAsync(s->q_u8.p, queries->u8 + (size_t)q0 * s->dim, (size_t)n * s->dim, cudaMemcpyHostToDevice, st));
+            h2d += (long long)n * s->dim;
+        }
+        if (stats) PSB_TRY(tm.mark(st));
+        PSB_TRY(coarse_exact(s, s->q.as<float>(), n, nprobe, s->probes.as<int>(), nullptr));
+        if (stats) PSB_TRY(tm.mark(st));
+        PSB_TRY(launch_build_lut(s->q.as<float>(), n, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st));
+        if (stats) PSB_TRY(tm.mark(st));
+        int* rows_out = rerank ? s->cand_rows.as<int>() : s->out_rows.as<int>();
+        float* dist_out = rerank ? s->cand_dist.as<float>() : s->out_dist.as<float>();
+        PSB_TRY(launch_scan(s->scan_index(), s->scan_ws(), s->lut.as<float>(), n, s->probes.as<int>(), nprobe, stage1_k,
+                            rows_out, dist_out, s->cand_count.as<int>(), s->sm_count, st));
+        if (stats) PSB_TRY(tm.mark(st));
+        if (rerank) {
+            const void* dq = s->exact_elem == 4 ? s->q.p : s->q_u8.p;
+            PSB_TRY(rerank_impl(s, dq, n, s->cand_rows.as<int>(), stage1_k, stage1_k, s->cand_count.as<int>(), topk,
+                                s->out_rows.as<int>(), s->out_dist.as<float>()));
+        }
+        if (stats) PSB_TRY(tm.mark(st));
+        PSB_TRY(launch_map_ids(s->out_rows.as<int>(), (long long)n * topk, s->reordered.as<long long>(), s->n_vectors,
+                               s->out_ids.as<long long>(), st));
+        if (stats) PSB_TRY(tm.mark(st));
+        PSB_CUDA(cudaMemcpyAsync(output->indices + (size_t)q0 * topk, s->out_ids.p, sizeof(long long) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaMemcpyAsync(output->distances + (size_t)q0 * topk, s->out_dist.p, sizeof(float) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
+        d2h += (long long)(sizeof(long long) + sizeof(float)) * n * topk;
+        if (output->coarse_ids) {
+            PSB_CUDA(cudaMemcpyAsync(output->coarse_ids + (size_t)q0 * nprobe, s->probes.p, sizeof(int) * (size_t)n * nprobe, cudaMemcpyDeviceToHost, st));
+            d2h += (long long)sizeof(int) * n * nprobe;
+        }
+        if (stats) PSB_TRY(tm.mark(st));
+        PSB_CUDA(cudaStreamSynchronize(st));
+        if (stats) {
+            t_h2d += tm.ms(0, 1); t_coarse += tm.ms(1, 2); t_lut += tm.ms(2, 3); t_scan += tm.ms(3, 4);
+            t_rr += tm.ms(4, 5); t_map += tm.ms(5, 6); t_d2h += tm.ms(6, 7);
+        }
+    }
+    if (stats) {
+        unsigned long long c1[4];
+        PSB_CUDA(cudaMemcpyAsync(c1, s->scalars.p, sizeof(c1), cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaStreamSynchronize(st));
+        stats->h2d_ms = t_h2d; stats->coarse_search_ms = t_coarse; stats->pq_lut_build_ms = t_lut;
+        stats->pq_adc_scan_ms = t_scan; stats->pq_rerank_ms = t_rr; stats->pq_map_ids_ms = t_map; stats->d2h_ms = t_d2h;
+        stats->total_ms = t_h2d + t_coarse + t_lut + t_scan + t_rr + t_map + t_d2h;
+        stats->pq_scanned_codes = (long long)(c1[0] - c0[0]);
+        stats->pq_adc_lookups = stats->pq_scanned_codes * s->m;
+        stats->threshold_candidates = (long long)(c1[1] - c0[1]);
+        stats->fallback_queries = (long long)(c1[2] - c0[2]);
+        stats->h2d_bytes = h2d; stats->d2h_bytes = d2h;
+        stats->kernel_launches = launches_total() - launches0;
+        stats->batches = nb;
+    }
+    return PSB_OK;
+}
+
+// ---- one-shot operators on host arrays ------------------------------------------------------------------
+
+psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* h_queries_u8,
+                           const float* h_queries_fp32, const int* h_candidates, int batch_n,
+                           int candidate_count, int candidate_stride, int topk, int* h_output_ids,
+                           float* h_output_distances, const int* h_candidate_counts, int device) {
+    if (!storage || !h_candidates || !h_output_ids || !h_output_distances || batch_n <= 0 || candidate_count <= 0 ||
+        candidate_stride < candidate_count || topk <= 0 || storage->count <= 0 || storage->dim <= 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid host IVF rerank request");
+    const bool use_float = storage->fp32 != nullptr;
+    if ((use_float && !h_queries_fp32) || (!use_float && (!storage->u8 || !h_queries_u8)))
+        return fail(PSB_INVALID_ARGUMENT, "host IVF rerank dtype does not match storage");
+    if (storage->source_rows) return fail(PSB_UNSUPPORTED_SHAPE, "exact storage with a row permutation is not supported");
+    if (h_candidate_counts)
+        for (int q = 0; q < batch_n; ++q)
+            if (h_candidate_counts[q] < 0 || h_candidate_counts[q] > candidate_count)
+                return fail(PSB_INVALID_ARGUMENT, "host rerank candidate count exceeds row width");
+    if (candidate_count > kMaxRerankWidth || topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "rerank width above 4096 or topk above 2048");
+    PSB_TRY(check_device(device));
+    const int elem = use_float ? 4 : 1;
+    const int dim = storage->dim;
+    const size_t base_bytes = (size_t)storage->count * dim * elem;
+    DevBuf base, q, cand, counts, stage, out_rows, out_dist;
+    PSB_TRY(base.reserve(base_bytes)); PSB_TRY(q.reserve((size_t)batch_n * dim * elem));
+    PSB_TRY(cand.reserve(sizeof(int) * (size_t)batch_n * candidate_stride));
+    PSB_TRY(stage.reserve((size_t)batch_n * candidate_count * dim * elem));
+    PSB_TRY(out_rows.reserve(sizeof(int) * (size_t)batch_n * topk)); PSB_TRY(out_dist.reserve(sizeof(float) * (size_t)batch_n * topk));
+    cudaStream_t st = nullptr;
+    PSB_CUDA(cudaMemcpy(base.p, use_float ? (const void*)storage->fp32 : (const void*)storage->u8, base_bytes, cudaMemcpyHostToDevice));
+    PSB_CUDA(cudaMemcpy(q.p, use_float ? (const void*)h_queries_fp32 : (const void*)h_queries_u8, (size_t)batch_n * dim * elem, cudaMemcpyHostToDevice));
+    PSB_CUDA(cudaMemcpy(cand.p, h_candidates, sizeof(int) * (size_t)batch_n * candidate_stride, cudaMemcpyHostToDevice));
+    const int* d_counts = nullptr;
+    if (h_candidate_counts) {
+        PSB_TRY(counts.reserve(sizeof(int) * (size_t)batch_n));
+        PSB_CUDA(cudaMemcpy(counts.p, h_candidate_counts, sizeof(int) * (size_t)batch_n, cudaMemcpyHostToDevice));
+        d_counts = counts.as<int>();
+    }
+    PSB_TRY(launch_gather_rows(base.p, storage->count, dim, elem, cand.as<int>(), batch_n, candidate_count, candidate_stride,
+                               d_counts, stage.p, st));
+    PSB_TRY(launch_rerank_select(stage.p, storage->count, dim, elem, q.p, cand.as<int>(), batch_n, candidate_count,
+                                 candidate_stride, d_counts, topk, out_rows.as<int>(), out_dist.as<float>(), st));
+    PSB_CUDA(cudaMemcpy(h_output_ids, out_rows.p, sizeof(int) * (size_t)batch_n * topk, cudaMemcpyDeviceToHost));
+    PSB_CUDA(cudaMemcpy(h_output_distances, out_dist.p, sizeof(float) * (size_t)batch_n * topk, cudaMemcpyDeviceToHost));
+    return PSB_OK;
+}
+
+psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centroids, int nlist, int dim,
+                           int nprobe, int coarse_mode, int64_t* h_ids, float* h_dist, int device) {
+    (void)coarse_mode;
+    if (!h_queries || !h_centroids || !h_ids || nq < 0 || nlist <= 0 || dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid coarse request");
+    if (nprobe <= 0 || nprobe > nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
+    if (nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
+    PSB_TRY(check_device(device));
+    if (nq == 0) return PSB_OK;
+    DevBuf q, c, tile, ids, ids64, dist;
+    PSB_TRY(q.reserve(sizeof(float) * (size_t)nq * dim)); PSB_TRY(c.reserve(sizeof(float) * (size_t)nlist * dim));
+    PSB_TRY(ids.reserve(sizeof(int) * (size_t)nq * nprobe)); PSB_TRY(ids64.reserve(sizeof(long long) * (size_t)nq * nprobe));
+    PSB_TRY(dist.reserve(sizeof(float) * (size_t)nq * nprobe));
+    PSB_CUDA(cudaMemcpy(q.p, h_queries, sizeof(float) * (size_t)nq * dim, cudaMemcpyHostToDevice));
+    PSB_CUDA(cudaMemcpy(c.p, h_centroids, sizeof(float) * (size_t)nlist * dim, cudaMemcpyHostToDevice));
+    const size_t row_bytes = sizeof(float) * (size_t)nlist;
+    int chunk = (int)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
+    chunk = std::min(chunk, nq);
+    PSB_TRY(tile.reserve(row_bytes * (size_t)chunk));
+    for (int q0 = 0; q0 < nq; q0 += chunk) {
+        const int n = std::min(chunk, nq - q0);
+        PSB_TRY(launch_coarse_dist_exact(q.as<float>() + (size_t)q0 * dim, n, c.as<float>(), nlist, dim, tile.as<float>(), nullptr));
+        PSB_TRY(launch_select_rows(tile.as<float>(), n, nlist, nprobe, ids.as<int>() + (size_t)q0 * nprobe,
+                                   dist.as<float>() + (size_t)q0 * nprobe, nullptr));
+    }
+    PSB_TRY(launch_widen_ids(ids.as<int>(), (long long)nq * nprobe, ids64.as<long long>(), nullptr));
+    PSB_CUDA(cudaMemcpy(h_ids, ids64.p, sizeof(long long) * (size_t)nq * nprobe, cudaMemcpyDeviceToHost));
+    if (h_dist) PSB_CUDA(cudaMemcpy(h_dist, dist.p, sizeof(float) * (size_t)nq * nprobe, cudaMemcpyDeviceToHost));
+    return PSB_OK;
+}
+
+// ---- training ---------------------------------------------------------------------------------------------
+
+psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_centroids, int k, int iters,
+                            int* d_assign, double* h_objective, int device, void* stream) {
+    if (!d_data || !d_centroids || n <= 0 || dim <= 0 || k <= 0 || iters < 0) return fail(PSB_INVALID_ARGUMENT, "invalid k-means request");
+    PSB_TRY(check_device(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DevBuf tile, assign, best, sums, counts, obj;
+    const size_t row_bytes = sizeof(float) * (size_t)k;
+    long long chunk = (long long)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
+    chunk = std::min<long long>(chunk, n);
+    PSB_TRY(tile.reserve(row_bytes * (size_t)chunk));
+    PSB_TRY(best.reserve(sizeof(float) * (size_t)n));
+    int* d_as = d_assign;
+    if (!d_as) { PSB_TRY(assign.reserve(sizeof(int) * (size_t)n)); d_as = assign.as<int>(); }
+    PSB_TRY(sums.reserve(sizeof(double) * (size_t)k * dim)); PSB_TRY(counts.reserve(sizeof(int) * (size_t)k));
+    PSB_TRY(obj.reserve(sizeof(double) * ((size_t)iters + 1)));
+    PSB_CUDA(cudaMemsetAsync(obj.p, 0, sizeof(double) * ((size_t)iters + 1), st));
+    for (int it = 0; it <= iters; ++it) {
+        for (long long r0 = 0; r0 < n; r0 += chunk) {
+            const int nn = (int)std::min<long long>(chunk, n - r0);
+            PSB_TRY(launch_coarse_dist_exact(d_data + (size_t)r0 * dim, nn, d_centroids, k, dim, tile.as<float>(), st));
+            PSB_TRY(launch_select_rows(tile.as<float>(), nn, k, 1, d_as + r0, best.as<float>() + r0, st));
+        }
+        PSB_CUDA(cudaMemsetAsync(sums.p, 0, sizeof(double) * (size_t)k * dim, st));
+        PSB_CUDA(cudaMemsetAsync(counts.p, 0, sizeof(int) * (size_t)k, st));
+        PSB_TRY(launch_kmeans_accumulate(d_data, n, dim, d_as, best.as<float>(), sums.as<double>(), counts.as<int>(),
+                                         obj.as<double>() + it, st));
+        if (it < iters) PSB_TRY(launch_kmeans_update(sums.as<double>(), counts.as<int>(), k, dim, d_centroids, st));
+    }
+    if (h_objective) PSB_CUDA(cudaMemcpyAsync(h_objective, obj.p, sizeof(double) * ((size_t)iters + 1), cudaMemcpyDeviceToHost, st));
+    PSB_CUDA(cudaStreamSynchronize(st));
+    return PSB_OK;
+}
+
+psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors, int codebook_size, int iters,
+                        uint64_t seed, float* d_codebook, int device, void* stream) {
+    if (!d_data || !d_codebook || n <= 0 || dim <= 0 || subvectors <= 0 || dim % subvectors || codebook_size <= 0 ||
+        codebook_size > kMaxCodebook || iters < 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid PQ training request");
+    PSB_TRY(check_device(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int dsub = dim / subvectors;
+    DevBuf codes, sums, counts;
+    PSB_TRY(codes.reserve((size_t)n * subvectors));
+    PSB_TRY(sums.reserve(sizeof(double) * (size_t)subvectors * codebook_size * dsub));
+    PSB_TRY(counts.reserve(sizeof(int) * (size_t)subvectors * codebook_size));
+    PSB_TRY(launch_pq_init(d_data, n, dim, subvectors, codebook_size, seed, d_codebook, st));
+    for (int it = 0; it < iters; ++it) {
+        PSB_TRY(launch_pq_encode(d_data, n, dim, d_codebook, subvectors, codebook_size, codes.as<uint8_t>(), st));
+        PSB_CUDA(cudaMemsetAsync(sums.p, 0, sums.bytes, st));
+        PSB_CUDA(cudaMemsetAsync(counts.p, 0, counts.bytes, st));
+        PSB_TRY(launch_pq_accumulate(d_data, n, dim, codes.as<uint8_t>(), subvectors, codebook_size, sums.as<double>(), counts.as<int>(), st));
+        PSB_TRY(launch_pq_update(sums.as<double>(), counts.as<int>(), subvectors, codebook_size, dsub, d_codebook, st));
+    }
+    PSB_CUDA(cudaStreamSynchronize(st));
+    return PSB_OK;
+}
+
+psb_status psb_pq_encode(const float* d_data, int64_t n, int dim, const float* d_codebook, int subvectors,
+                         int codebook_size, uint8_t* d_codes, int device, void* stream) {
+    if (!d_data || !d_codebook || !d_codes || n < 0 || dim <= 0 || subvectors <= 0 || dim % subvectors ||
+        codebook_size <= 0 || codebook_size > kMaxCodebook)
+        return fail(PSB_INVALID_ARGUMENT, "invalid PQ encode request");
+    PSB_TRY(check_device(device));
+    return launch_pq_encode(d_data, n, dim, d_codebook, subvectors, codebook_size, d_codes, static_cast<cudaStream_t>(stream));
+}
+
+// ---- synthetic data -------------------------------------------------------------------------------------------
+
+psb_status psb_gen_mixture_rows(const float* d_centres, const int64_t* d_offsets, int ncomp, int dim,
+                                float sigma, uint64_t seed, int64_t row_begin, int64_t n, float* d_out,
+                                int device, void* stream) {
+    if (!d_centres || !d_offsets || !d_out || ncomp <= 0 || dim <= 0 || n < 0) return fail(PSB_INVALID_ARGUMENT, "invalid generator request");
+    PSB_TRY(check_device(device));
+    const long long step = ((long long)1 << 31) / dim;  // rows per launch
+    for (long long r = 0; r < n; r += step)
+        PSB_TRY(launch_gen_mixture(d_centres, reinterpret_cast<const long long*>(d_offsets), ncomp, dim, sigma, seed,
+                                   row_begin + r, std::min<long long>(step, n - r), d_out + (size_t)r * dim,
+                                   static_cast<cudaStream_t>(stream)));
+    return PSB_OK;
+}
+
+psb_status psb_gen_normal(uint64_t seed, int64_t first_elem, int64_t n_elems, float scale, float* d_out,
+                          int device, void* stream) {
+    if (!d_out || n_elems < 0) return fail(PSB_INVALID_ARGUMENT, "invalid generator request");
+    PSB_TRY(check_device(device));
+    const long long step = (long long)1 << 31;
+    for (long long r = 0; r < n_elems; r += step)
+        PSB_TRY(launch_gen_normal(seed, first_elem + r, std::min<long long>(step, n_elems - r), scale, d_out + r,
+                                  static_cast<cudaStream_t>(stream)));
+    return PSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,295 @@
+"""GPU parity tests: every stage of the CUDA path, called through the C ABI, against the CPU checker on
+the same seeded inputs - bit-exact ids, rows and distances."""
+import numpy as np
+import pytest
+
+import cases
+import oracle
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def dev(a):
+    torch = _torch()
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+# ---------------------------------------------------------------------------------------------- coarse
+@pytest.mark.parametrize("nq,nlist,dim,nprobe", [(37, 300, 96, 8), (5, 64, 100, 17), (130, 1000, 128, 64),
+                                                  (3, 7, 8, 7), (64, 4096, 96, 1), (9, 5000, 32, 513)])
+def test_coarse_matches_checker(psb, nq, nlist, dim, nprobe):
+    rng = np.random.default_rng(nq * 7 + nlist)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    c = rng.standard_normal((nlist, dim)).astype(np.float32)
+    ids, dist = psb.coarse_host(q, c, nprobe)
+    oi, od = oracle.coarse(q, c, nprobe)
+    assert np.array_equal(ids, oi)
+    assert np.array_equal(dist, od)
+
+
+def test_coarse_integer_grid_with_ties(psb):
+    # integer-valued inputs: many exactly equal distances; ties resolve by list id
+    rng = np.random.default_rng(3)
+    q = rng.integers(-3, 4, (40, 16)).astype(np.float32)
+    c = rng.integers(-3, 4, (500, 16)).astype(np.float32)
+    ids, dist = psb.coarse_host(q, c, 65)
+    oi, od = oracle.coarse(q, c, 65)
+    assert np.array_equal(ids, oi) and np.array_equal(dist, od)
+    zeros = np.zeros((4, 16), np.float32)
+    ids, dist = psb.coarse_host(q[:2], zeros, 4)
+    assert np.array_equal(ids, np.tile(np.arange(4), (2, 1)))
+
+
+def test_coarse_rejects_bad_nprobe(psb):
+    with pytest.raises(psb.InvalidArgument):
+        psb.coarse_host(np.zeros((1, 8), np.float32), np.zeros((4, 8), np.float32), 5)
+
+
+# ---------------------------------------------------------------------------------------------- LUT + scan
+def run_stage_scan(psb, ix, q, probes, stage1_k, **kw):
+    torch = _torch()
+    nq = q.shape[0]
+    with psb.Session(dict(ix, vectors=None), **kw) as s:
+        dq = dev(q)
+        lut = torch.empty((nq, s.M, s.K), dtype=torch.float32, device="cuda")
+        s.stage_build_lut(dq, nq, lut)
+        dp = dev(probes.astype(np.int32))
+        rows = torch.empty((nq, stage1_k), dtype=torch.int32, device="cuda")
+        dist = torch.empty((nq, stage1_k), dtype=torch.float32, device="cuda")
+        cnt = torch.empty((nq,), dtype=torch.int32, device="cuda")
+        s.stage_scan(lut, nq, dp, probes.shape[1], stage1_k, rows, dist, cnt)
+        s.sync()
+        counters = s.counters()
+        return lut.cpu().numpy(), rows.cpu().numpy(), dist.cpu().numpy(), cnt.cpu().numpy(), counters
+
+
+@pytest.mark.parametrize("M,dim", [(8, 32), (16, 96), (20, 100), (32, 128), (48, 96), (64, 128), (12, 48)])
+def test_lut_and_scan_match_checker(psb, M, dim):
+    ix = synth.make_index(6000, dim, 24, M, seed=M, zipf=(M % 16 == 0))
+    q = synth.make_queries(ix, 33, seed=M + 1)
+    probes, _ = oracle.coarse(q, ix["centroids"], 6)
+    lut, rows, dist, cnt, _ = run_stage_scan(psb, ix, q, probes, 50)
+    assert np.array_equal(lut, oracle.pq_lut(q, ix["codebook"]))
+    orow, odist, ocnt, _ = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], 50)
+    assert np.array_equal(cnt, ocnt)
+    assert np.array_equal(rows, orow)
+    assert np.array_equal(dist, odist)
+
+
+@pytest.mark.parametrize("stage1_k,n,nprobe", [(10, 40000, 8), (100, 60000, 12), (1000, 120000, 16), (2048, 90000, 16)])
+def test_scan_with_threshold_admission(psb, stage1_k, n, nprobe):
+    # enough rows per query that the sampled cutoff, the pools and the selection are all exercised
+    ix = synth.make_index(n, 32, 16, 8, seed=stage1_k, zipf=True)
+    q = synth.make_queries(ix, 40, seed=7, weights=synth.zipf_weights(16))
+    probes, _ = oracle.coarse(q, ix["centroids"], nprobe)
+    _, rows, dist, cnt, counters = run_stage_scan(psb, ix, q, probes, stage1_k)
+    orow, odist, ocnt, scanned = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], stage1_k)
+    assert counters["pq_scanned_codes"] == scanned
+    assert np.array_equal(cnt, ocnt)
+    assert np.array_equal(rows, orow)
+    assert np.array_equal(dist, odist)
+    assert counters["threshold_candidates"] < scanned  # the cutoff pruned
+
+
+def test_scan_edge_cases(psb):
+    ix = synth.make_index(3000, 32, 8, 8, seed=5, empty_lists=(2, 5))
+    q = synth.make_queries(ix, 6, seed=9)
+    probes = np.array([[2, 5, -1, 99], [0, 2, 1, 5], [7, 7, 7, 7], [3, -5, 4, 8], [5, 2, 5, 2], [6, 1, 0, 3]], np.int64)
+    # duplicate probes (row 2) would visit a list twice on both sides; keep them out of the comparison
+    keep = [0, 1, 3, 4, 5]
+    _, rows, dist, cnt, _ = run_stage_scan(psb, ix, q[keep], probes[keep], 64)
+    orow, odist, ocnt, _ = oracle.pq_scan(q[keep], probes[keep], ix["offsets"], ix["codes"], ix["codebook"], 64)
+    assert np.array_equal(cnt, ocnt) and np.array_equal(rows, orow) and np.array_equal(dist, odist)
+    assert cnt[0] == 0 and np.all(rows[0] == -1) and np.all(dist[0] == cases.FLT_MAX)
+
+
+def test_scan_exact_fallback_on_pool_overflow(psb):
+    # every row has the same code -> every distance ties with the cutoff -> pools overflow -> exact fallback
+    ix = synth.make_index(50000, 32, 4, 8, seed=1)
+    ix["codes"][:] = ix["codes"][0]
+    q = synth.make_queries(ix, 5, seed=2)
+    probes = np.tile(np.arange(4), (5, 1)).astype(np.int64)
+    _, rows, dist, cnt, counters = run_stage_scan(psb, ix, q, probes, 100)
+    orow, odist, ocnt, _ = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], 100)
+    assert counters["fallback_queries"] == 5
+    assert np.array_equal(rows, orow) and np.array_equal(dist, odist) and np.array_equal(cnt, ocnt)
+
+
+def test_scan_shard_ranges_partition_the_work(psb):
+    ix = synth.make_index(30000, 32, 16, 8, seed=8, zipf=True)
+    q = synth.make_queries(ix, 20, seed=3)
+    probes, _ = oracle.coarse(q, ix["centroids"], 8)
+    full = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], 100)
+    parts_r, parts_d = [], []
+    for lb, le in ((0, 5), (5, 11), (11, 16)):
+        _, rows, dist, cnt, _ = run_stage_scan(psb, ix, q, probes, 100, list_begin=lb, list_end=le)
+        masked = np.where((probes >= lb) & (probes < le), probes, -1)
+        orow, odist, ocnt, _ = oracle.pq_scan(q, masked, ix["offsets"], ix["codes"], ix["codebook"], 100)
+        assert np.array_equal(rows, orow) and np.array_equal(dist, odist)
+        parts_r.append(rows); parts_d.append(dist)
+    torch = _torch()
+    with psb.Session(dict(ix, vectors=None)) as s:
+        out_r = torch.empty((20, 100), dtype=torch.int32, device="cuda")
+        out_d = torch.empty((20, 100), dtype=torch.float32, device="cuda")
+        s.stage_merge(dev(np.stack(parts_r)), dev(np.stack(parts_d)), 3, 20, 100, out_r, out_d)
+        s.sync()
+    assert np.array_equal(out_r.cpu().numpy(), full[0])
+    assert np.array_equal(out_d.cpu().numpy(), full[1])
+
+
+# ---------------------------------------------------------------------------------------------- rerank
+@pytest.mark.parametrize("dtype", [np.uint8, np.float32])
+@pytest.mark.parametrize("dim", [100, 128])
+@pytest.mark.parametrize("width", [128, 256, 512, 1024, 2048])
+def test_host_rerank_known_answer(psb, dtype, dim, width):
+    c = cases.host_rerank_case(dtype, dim, width)
+    ids, dist = psb.rerank_host(c["base"], c["queries"], c["cand"], c["topk"], candidate_count=width, counts=c["counts"])
+    assert np.array_equal(ids, c["exp_ids"])
+    assert np.array_equal(dist, c["exp_d"])
+    with pytest.raises(psb.InvalidArgument):
+        psb.rerank_host(c["base"], c["queries"], c["cand"], c["topk"], candidate_count=width,
+                        counts=np.array([0, width + 1, 0, 0], np.int32))
+
+
+def test_rerank_adapter_known_answer(psb):
+    c = cases.adapter_case()
+    ids, dist = psb.rerank_host(c["base"], c["queries"], c["cand"], c["topk"], counts=c["counts"])
+    assert np.array_equal(ids, c["exp_ids"])
+    assert np.array_equal(dist, c["exp_d"])
+
+
+@pytest.mark.parametrize("name", ["rerank_d96", "rerank_d100"])
+def test_rerank_matches_reference_golden(psb, name):
+    g = cases.load_golden(name)
+    width, topk = (int(x) for x in g["params"])
+    ids, dist = psb.rerank_host(g["base"], g["queries"], g["candidates"], topk, candidate_count=width, counts=g["counts"])
+    assert np.array_equal(ids, g["ref_ids"])
+    assert np.array_equal(dist, g["ref_dist"])  # bit-exact with the reference's AVX-512 kernel order
+
+
+@pytest.mark.parametrize("dim", [8, 24, 96, 100, 128, 200])
+def test_rerank_random_matches_checker(psb, dim):
+    rng = np.random.default_rng(dim)
+    base = rng.standard_normal((500, dim)).astype(np.float32)
+    q = rng.standard_normal((11, dim)).astype(np.float32)
+    cand = rng.integers(-2, 503, (11, 300)).astype(np.int32)
+    ids, dist = psb.rerank_host(base, q, cand, 25)
+    oi, od = oracle.rerank(base, q, cand, 25)
+    assert np.array_equal(ids, oi) and np.array_equal(dist, od)
+
+
+# ---------------------------------------------------------------------------------------------- whole search
+@pytest.mark.parametrize("name", ["ivfpq_d32_m8", "ivfpq_d96_m48_zipf", "ivfpq_d100_m20"])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_search_matches_reference_golden(psb, name, mode):
+    g = cases.load_golden(name)
+    nprobe, topk, n_rerank = (int(x) for x in g["params"])
+    ix = cases.golden_index(g)
+    with psb.Session(ix, n_rerank=n_rerank, exact_mode=mode) as s:
+        r = s.search(g["queries"], nprobe, topk, batch_size=7, want_coarse=True)  # tail batch on purpose
+    assert np.array_equal(r["coarse"], g["ref_probes"])
+    assert np.array_equal(r["indices"], g["ref_indices"])
+    assert np.array_equal(r["distances"], g["ref_distances"])
+    with psb.Session(dict(ix, vectors=None)) as s:
+        r = s.search(g["queries"], nprobe, topk)
+    assert np.array_equal(r["distances"], g["ref_norerank_distances"])
+
+
+@pytest.mark.parametrize("m,dim,rerank,empty", [(16, 96, 512, False), (16, 96, 512, True), (20, 100, 2048, False),
+                                                 (16, 128, 2048, False)])
+def test_plain_pq_pipeline_equals_exhaustive(psb, m, dim, rerank, empty):
+    c = cases.plain_pq_pipeline_case(m, dim, rerank, empty)
+    with psb.Session(c["index"], n_rerank=c["n_rerank"]) as s:
+        r = s.search(c["queries"], c["nprobe"], c["topk"], batch_size=8)
+    assert np.array_equal(r["indices"], c["exp_ids"])
+    assert np.array_equal(r["distances"], c["exp_d"])
+
+
+@pytest.mark.parametrize("n,dim,nlist,M,nprobe,topk,n_rerank,zipf", [
+    (50000, 128, 64, 32, 8, 10, 100, False),    # IVF-PQ 1M configuration, cut down
+    (80000, 96, 128, 48, 16, 100, 1000, True),  # IVF-PQ 100M sharded configuration, cut down
+    (20000, 64, 32, 16, 32, 10, 0, False),      # no rerank: ADC distances out
+])
+def test_search_matches_checker(psb, n, dim, nlist, M, nprobe, topk, n_rerank, zipf):
+    ix = synth.make_index(n, dim, nlist, M, seed=n % 97, zipf=zipf)
+    w = synth.zipf_weights(nlist) if zipf else None
+    q = synth.make_queries(ix, 64, seed=17, weights=w)
+    o = oracle.ivfpq_search(ix if n_rerank else dict(ix, vectors=None), q, nprobe, topk, n_rerank)
+    with psb.Session(ix if n_rerank else dict(ix, vectors=None), n_rerank=n_rerank) as s:
+        r = s.search(q, nprobe, topk, batch_size=50, want_coarse=True)
+    assert np.array_equal(r["coarse"], o["coarse"])
+    assert np.array_equal(r["indices"], o["indices"])
+    assert np.array_equal(r["distances"], o["distances"])
+    assert r["stats"]["pq_scanned_codes"] == o["scanned"]
+    assert r["stats"]["kernel_launches"] > 0
+
+
+def test_search_argument_errors(psb):
+    ix = synth.make_index(2000, 32, 8, 8, seed=4)
+    q = synth.make_queries(ix, 4)
+    with psb.Session(ix, n_rerank=50) as s:
+        for bad in (dict(nprobe=0, topk=5), dict(nprobe=9, topk=5), dict(nprobe=4, topk=0)):
+            with pytest.raises(psb.InvalidArgument):
+                s.search(q, **bad)
+        with pytest.raises(psb.InvalidArgument):
+            s.search(q[:, :16], 4, 5)
+        empty = s.search(q[:0], 4, 5)
+        assert empty["indices"].shape == (0, 5)
+
+
+# ---------------------------------------------------------------------------------------------- training
+def test_pq_encode_matches_checker(psb):
+    torch = _torch()
+    for M, dim in ((8, 32), (48, 96), (20, 100)):
+        ix = synth.make_index(3000, dim, 8, M, seed=M + 40)
+        codes = torch.empty((3000, M), dtype=torch.uint8, device="cuda")
+        psb.pq_encode(dev(ix["vectors"]), 3000, dim, dev(ix["codebook"]), M, 256, codes)
+        torch.cuda.synchronize()
+        assert np.array_equal(codes.cpu().numpy(), oracle.pq_encode(ix["vectors"], ix["codebook"]))
+
+
+def test_kmeans_matches_checker_objective(psb):
+    torch = _torch()
+    centres, data, _ = synth.mixture(20000, 32, 40, 0.3, seed=6)
+    init = data[:64].copy()
+    ocen, oassign, oobj = oracle.kmeans_lloyd(data, init, 5)
+    dcen = dev(init)
+    dassign = torch.empty((20000,), dtype=torch.int32, device="cuda")
+    obj = psb.kmeans_train(dev(data), 20000, 32, dcen, 64, 5, dassign)
+    # same criterion as the reference's own k-means test: relative objective error and centroid RMSE
+    assert np.allclose(obj, oobj, rtol=1e-5)
+    assert np.sqrt(np.mean((dcen.cpu().numpy() - ocen) ** 2)) < 1e-5
+    assert np.mean(dassign.cpu().numpy() == oassign) > 0.9999
+    assert np.all(np.diff(obj) <= 1e-6 * obj[0])
+
+
+def test_pq_train_reduces_quantisation_error(psb):
+    torch = _torch()
+    _, data, _ = synth.mixture(30000, 32, 16, 0.5, seed=9)
+    cb = torch.empty((8, 256, 4), dtype=torch.float32, device="cuda")
+    d = dev(data)
+    errs = []
+    for iters in (0, 8):
+        psb.pq_train(d, 30000, 32, 8, 256, iters, 1234, cb)
+        codes = oracle.pq_encode(data, cb.cpu().numpy())
+        rec = cb.cpu().numpy()[np.arange(8)[None, :], codes].reshape(30000, 32)
+        errs.append(float(((rec - data) ** 2).sum(1).mean()))
+    assert errs[1] < 0.8 * errs[0]
+
+
+def test_generators_are_deterministic_and_gaussian(psb):
+    torch = _torch()
+    a = torch.empty((1 << 20,), dtype=torch.float32, device="cuda")
+    b = torch.empty((1 << 20,), dtype=torch.float32, device="cuda")
+    psb.gen_normal(77, 0, 1 << 20, 1.0, a)
+    psb.gen_normal(77, 1 << 19, 1 << 19, 1.0, b)
+    torch.cuda.synchronize()
+    assert torch.equal(a[1 << 19:], b[: 1 << 19])  # counter-based: independent of the launch shape
+    assert abs(float(a.mean())) < 5e-3 and abs(float(a.std()) - 1.0) < 5e-3
+    assert abs(float((a ** 4).mean()) - 3.0) < 0.05

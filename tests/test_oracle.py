@@ -1,0 +1,136 @@
+"""CPU tests: the plain-C restatement (oracle/psb_oracle.c) against the reference's golden outputs, the
+reference's own known-answer tests, and - where oracle/_ref is built - the reference's code itself."""
+import numpy as np
+import pytest
+
+import cases
+import oracle
+import synth
+
+GOLDEN_IVFPQ = ["ivfpq_d32_m8", "ivfpq_d96_m48_zipf", "ivfpq_d100_m20"]
+
+
+@pytest.mark.parametrize("name", GOLDEN_IVFPQ)
+def test_restatement_matches_reference_golden(name):
+    g = cases.load_golden(name)
+    nprobe, topk, n_rerank = (int(x) for x in g["params"])
+    ix = cases.golden_index(g)
+    o = oracle.ivfpq_search(ix, g["queries"], nprobe, topk, n_rerank)
+    assert np.array_equal(o["coarse"], g["ref_probes"])
+    assert np.array_equal(o["indices"], g["ref_indices"])
+    assert np.array_equal(o["distances"], g["ref_distances"])  # bit-exact
+    assert o["scanned"] == int(g["ref_scanned"])
+    luts = oracle.pq_lut(g["queries"], g["codebook"])
+
+    def adc(q, row):
+        return _adc(luts[q], g["codes"][row])
+    assert cases.stage1_sets_match(o["stage1"], g["ref_stage1"], adc)
+    nr = oracle.ivfpq_search(dict(ix, vectors=None), g["queries"], nprobe, topk, 0)
+    assert np.array_equal(nr["distances"], g["ref_norerank_distances"])  # ADC distances, bit-exact
+    same = nr["indices"] == g["ref_norerank_indices"]
+    # ids may differ only inside groups of equal ADC distance
+    assert np.array_equal(np.sort(nr["distances"][~same]), np.sort(g["ref_norerank_distances"][~same]))
+
+
+def _adc(lut, code):
+    d = np.float32(0)
+    for m in range(lut.shape[0]):
+        d = np.float32(d + lut[m, code[m]])
+    return float(d)
+
+
+@pytest.mark.parametrize("name", ["rerank_d96", "rerank_d100"])
+def test_rerank_matches_reference_golden(name):
+    g = cases.load_golden(name)
+    width, topk = (int(x) for x in g["params"])
+    ids, dist = oracle.rerank(g["base"], g["queries"], g["candidates"], topk, candidate_count=width, counts=g["counts"])
+    assert np.array_equal(ids, g["ref_ids"])
+    assert np.array_equal(dist, g["ref_dist"])
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.float32])
+@pytest.mark.parametrize("dim", [100, 128])
+@pytest.mark.parametrize("width", [128, 512, 2048])
+def test_host_rerank_known_answer(dtype, dim, width):
+    c = cases.host_rerank_case(dtype, dim, width)
+    ids, dist = oracle.rerank(c["base"], c["queries"], c["cand"], c["topk"], candidate_count=width, counts=c["counts"])
+    assert np.array_equal(ids, c["exp_ids"])
+    assert np.array_equal(dist, c["exp_d"])  # integer-valued data: every summation order is exact
+    with pytest.raises(ValueError):
+        oracle.rerank(c["base"], c["queries"], c["cand"], c["topk"], candidate_count=width,
+                      counts=np.array([0, width + 1, 0, 0], np.int32))
+
+
+def test_rerank_adapter_known_answer():
+    c = cases.adapter_case()
+    ids, dist = oracle.rerank(c["base"], c["queries"], c["cand"], c["topk"], counts=c["counts"])
+    assert np.array_equal(ids, c["exp_ids"])
+    assert np.array_equal(dist, c["exp_d"])
+
+
+@pytest.mark.parametrize("m,dim,rerank,empty", [(16, 96, 512, False), (16, 96, 512, True), (20, 100, 2048, False),
+                                                 (16, 128, 512, False)])
+def test_plain_pq_pipeline_equals_exhaustive(m, dim, rerank, empty):
+    c = cases.plain_pq_pipeline_case(m, dim, rerank, empty)
+    o = oracle.ivfpq_search(c["index"], c["queries"], c["nprobe"], c["topk"], c["n_rerank"])
+    assert np.array_equal(o["indices"], c["exp_ids"])
+    assert np.array_equal(o["distances"], c["exp_d"])
+
+
+def test_u8_lut_identities():
+    rng = np.random.default_rng(5)
+    for M, dsub in ((16, 8), (20, 5)):
+        cb = rng.standard_normal((M, 256, dsub)).astype(np.float32)
+        q = rng.standard_normal((1, M * dsub)).astype(np.float32)
+        lut = oracle.pq_lut(q, cb)[0]
+        ref = ((q.reshape(M, 1, dsub) - cb) ** 2).sum(-1)
+        assert np.allclose(lut, ref, rtol=1e-5, atol=1e-5)
+        q8, scales, lo_sum, infl = oracle.pq_lut_u8(lut)
+        lo = lut.min(axis=1)
+        assert np.all(np.abs(lo[:, None] + scales[:, None] * q8 - lut) <= 0.5001 * scales[:, None])
+        assert np.isclose(lo_sum, lo.sum(), rtol=1e-6)
+        assert np.isclose(infl, 0.5 * scales.sum(), rtol=1e-6)
+        _, _, _, infl_r = oracle.pq_lut_u8(lut, residual=True)
+        assert np.isclose(infl_r, scales.sum(), rtol=1e-6)
+
+
+def test_ivfflat_config1_shape_small():
+    """IVF-Flat CPU configuration (cut down): exact search over probed lists equals brute force when nprobe = nlist."""
+    centres, data, offsets = synth.mixture(3000, 32, 16, 0.3, seed=0)
+    rng = np.random.default_rng(1)
+    q = (centres[rng.integers(0, 16, 20)] + 0.3 * rng.standard_normal((20, 32))).astype(np.float32)
+    ids, dist = oracle.ivfflat_search(centres, offsets, None, data, q, 16, 10)
+    d2 = ((q[:, None, :].astype(np.float64) - data[None].astype(np.float64)) ** 2).sum(-1)
+    assert np.array_equal(ids, np.argsort(d2, axis=1, kind="stable")[:, :10])
+    assert np.allclose(dist, np.sort(d2, axis=1)[:, :10], rtol=1e-5)
+
+
+def test_edge_cases():
+    ix = synth.make_index(400, 16, 4, 4, seed=2, empty_lists=(1,))
+    q = synth.make_queries(ix, 3)
+    # fewer rows than topk in the probed lists: padding -1 / FLT_MAX
+    small = dict(ix)
+    o = oracle.ivfpq_search(small, q, 4, 10, 500)  # n_rerank > n_vectors -> stage1_k = n_vectors
+    assert o["stage1"].shape[1] == 400
+    rows, dist, cnt, _ = oracle.pq_scan(q, np.array([[1, -1, 99]] * 3, np.int64), ix["offsets"], ix["codes"],
+                                        ix["codebook"], 5)
+    assert np.all(rows == -1) and np.all(cnt == 0) and np.all(dist == cases.FLT_MAX)
+    with pytest.raises(ValueError):
+        oracle.coarse(q, ix["centroids"], 5)  # nprobe > nlist
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="oracle/_ref (reference compiled in place) not built")
+@pytest.mark.parametrize("seed,dim,M,nlist,zipf", [(31, 96, 48, 24, True), (32, 128, 32, 16, False), (33, 100, 20, 8, False)])
+def test_restatement_vs_reference_live(seed, dim, M, nlist, zipf):
+    ix = synth.make_index(3000, dim, nlist, M, seed=seed, zipf=zipf)
+    q = synth.make_queries(ix, 30, seed=seed + 1)
+    o = oracle.ivfpq_search(ix, q, 5, 10, 50)
+    pr, pd = oracle.ref_coarse(q, ix["centroids"], 5)
+    assert np.array_equal(pr, o["coarse"])
+    r = oracle.ref_ivfpq_search(ix, q, pr, 10, 50, fine_threads=2, rerank_threads=2)
+    assert np.array_equal(r["indices"], o["indices"])
+    if oracle.ref_info()["isa"] == "avx512":
+        assert np.array_equal(r["distances"], o["distances"])
+    else:
+        assert np.allclose(r["distances"], o["distances"], rtol=1e-5)
+    assert r["scanned"] == o["scanned"]
