@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the IVF-PQ search hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's own CPU path (oracle/_ref)
+
+One "step" = one batch of queries through coarse -> LUT -> ADC scan -> exact rerank -> id map.
+Workload (default "c4"): IVF-PQ, 100M x 96 fp32 base from a 65,536-component Gaussian mixture with Zipf(1.1)
+populations, nlist 65,536, PQ M=48 x 8 bit, batch 10,000, nprobe 128, k 100, rerank top-1000 from host-resident
+fp32 rows.  Data are synthetic and seeded (counter-based generators on the GPU); the inverted lists are the
+mixture components (a row's list is its generating component), centroids are the component centres, and the
+PQ codebook is trained on a 1M-row sample.
+
+Prints ONE JSON line.  `value` is queries/s with the queries already in HBM; `e2e` is queries/s through
+psb_session_search with host (pinned) queries and host outputs.  `roofline` describes the ADC scan kernel;
+`cpu_baseline` is the reference's CPU path timed on a bounded sample of the same batch on this host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE configuration "IVF-PQ at scale" (the one the headline metric is quoted on)
+    "c4": dict(n=100_000_000, dim=96, nlist=65536, M=48, sigma=0.25, zipf=1.1, nq=10000, nprobe=128, topk=100,
+               n_rerank=1000, seed=3, desc="IVF-PQ 100Mx96 nlist=65536 M=48 nprobe=128 k=100 rerank=1000 batch=10000"),
+    # BASELINE configuration "IVF-PQ fp32 1M"
+    "c2": dict(n=1_000_000, dim=128, nlist=1024, M=32, sigma=0.25, zipf=None, nq=10000, nprobe=32, topk=10,
+               n_rerank=100, seed=1, desc="IVF-PQ 1Mx128 nlist=1024 M=32 nprobe=32 k=10 rerank=100 batch=10000"),
+}
+
+
+def log(*a):
+    if int(os.environ.get("RANK", "0")) == 0:
+        print("[bench]", *a, file=sys.stderr, flush=True)
+
+
+def populations(n, nlist, zipf):
+    w = np.ones(nlist) if not zipf else 1.0 / np.arange(1, nlist + 1) ** zipf
+    w = w / w.sum()
+    counts = np.floor(w * n).astype(np.int64)
+    rem = int(n - counts.sum())
+    order = np.argsort(-(w * n - counts), kind="stable")
+    counts[order[:rem]] += 1
+    offsets = np.zeros(nlist + 1, np.int64)
+    offsets[1:] = np.cumsum(counts)
+    return w, offsets
+
+
+def coprime_multiplier(n):
+    a = 2654435761 % n
+    from math import gcd
+    while gcd(a, n) != 1:
+        a += 1
+    return a
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                pass
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def build_index(cfg, torch, api, device, row_lo=0, row_hi=None, gt_queries=None, gt_k=0):
+    """Generates rows [row_lo,row_hi) of the synthetic base on the GPU, trains the PQ codebook, encodes, and
+    returns host arrays.  Optionally accumulates exact ground truth for gt_queries over the generated rows."""
+    n, dim, nlist, M = cfg["n"], cfg["dim"], cfg["nlist"], cfg["M"]
+    seed = cfg["seed"]
+    row_hi = n if row_hi is None else row_hi
+    t0 = time.time()
+    w, offsets = populations(n, nlist, cfg["zipf"])
+    d_off = torch.from_numpy(offsets).cuda()
+    centres = torch.empty((nlist, dim), dtype=torch.float32, device="cuda")
+    api.gen_normal(seed * 1000 + 1, 0, nlist * dim, 1.0, centres, device=device)
+    # PQ training sample: 64 evenly spaced blocks of rows (the same on every rank)
+    blocks, per = 64, min(16384, max(1, n // 64))
+    sample = torch.empty((blocks * per, dim), dtype=torch.float32, device="cuda")
+    for b in range(blocks):
+        r0 = (n // blocks) * b
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, per, sample[b * per:],
+                             device=device)
+    codebook = torch.empty((M, 256, dim // M), dtype=torch.float32, device="cuda")
+    api.pq_train(sample, blocks * per, dim, M, 256, 8, seed * 1000 + 3, codebook, device=device)
+    del sample
+    rows = row_hi - row_lo
+    vectors = np.empty((rows, dim), np.float32)
+    codes = np.empty((rows, M), np.uint8)
+    chunk = 2_000_000
+    buf = torch.empty((min(chunk, rows), dim), dtype=torch.float32, device="cuda")
+    cbuf = torch.empty((min(chunk, rows), M), dtype=torch.uint8, device="cuda")
+    gt_d = gt_i = None
+    for r0 in range(row_lo, row_hi, chunk):
+        m = min(chunk, row_hi - r0)
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, m, buf, device=device)
+        api.pq_encode(buf, m, dim, codebook, M, 256, cbuf, device=device)
+        if gt_queries is not None:
+            k = min(gt_k, m)
+            ti = torch.empty((gt_queries.shape[0], k), dtype=torch.int32, device="cuda")
+            td = torch.empty((gt_queries.shape[0], k), dtype=torch.float32, device="cuda")
+            api.knn_exact(gt_queries, gt_queries.shape[0], buf, m, dim, k, ti, td, device=device)
+            ti = ti.long() + r0
+            if gt_d is None:
+                gt_d, gt_i = td, ti
+            else:
+                cd, ci = torch.cat([gt_d, td], 1), torch.cat([gt_i, ti], 1)
+                o = torch.argsort(cd, dim=1, stable=True)[:, :gt_k]
+                gt_d, gt_i = torch.gather(cd, 1, o), torch.gather(ci, 1, o)
+        torch.cuda.synchronize()
+        torch.from_numpy(vectors[r0 - row_lo:r0 - row_lo + m]).copy_(buf[:m])
+        torch.from_numpy(codes[r0 - row_lo:r0 - row_lo + m]).copy_(cbuf[:m])
+    del buf, cbuf
+    a = coprime_multiplier(n)
+    ids = (np.arange(row_lo, row_hi, dtype=np.int64) * a + 12345) % n
+    index = dict(centroids=centres.cpu().numpy(), offsets=offsets, reordered_ids=ids, codes=codes,
+                 codebook=codebook.cpu().numpy(), vectors=vectors, nlist=nlist)
+    log("index built in %.1fs (%d rows, %.1f GB vectors on the host)" % (time.time() - t0, rows, vectors.nbytes / 1e9))
+    return index, w, centres, (gt_i.cpu().numpy() if gt_i is not None else None)
+
+
+def make_queries(cfg, torch, api, centres, w, device):
+    rng = np.random.default_rng(cfg["seed"] * 1000 + 7)
+    comp = rng.choice(cfg["nlist"], size=cfg["nq"], p=w)
+    noise = torch.empty((cfg["nq"], cfg["dim"]), dtype=torch.float32, device="cuda")
+    api.gen_normal(cfg["seed"] * 1000 + 8, 0, cfg["nq"] * cfg["dim"], cfg["sigma"], noise, device=device)
+    return (centres[torch.from_numpy(comp).cuda()] + noise).contiguous()
+
+
+def recall_at(got, truth, k):
+    hit = 0
+    for g, t in zip(got[:, :k], truth[:, :k]):
+        hit += len(set(g.tolist()) & set(t.tolist()))
+    return hit / float(truth.shape[0] * k)
+
+
+def cpu_reference_run(index, q_host, cfg, nsample, threads):
+    """The reference's CPU path (coarse loop + ivfpq_fine_cpu_lut + ivfpq_rerank_cpu + ivfpq_map_ids) on nsample queries."""
+    import oracle
+    q = np.ascontiguousarray(q_host[:nsample])
+    t0 = time.time()
+    if oracle.have_ref():
+        probes, _ = oracle.ref_coarse(q, index["centroids"], cfg["nprobe"], threads=threads)
+        r = oracle.ref_ivfpq_search(index, q, probes, cfg["topk"], cfg["n_rerank"], fine_threads=threads,
+                                    rerank_threads=threads)
+        kind = "reference"
+    else:
+        r = oracle.ivfpq_search(index, q, cfg["nprobe"], cfg["topk"], cfg["n_rerank"])
+        kind = "port"
+    dt = time.time() - t0
+    return r, dt, kind
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows", type=int, default=0, help="override the base size (scaled-down runs)")
+    ap.add_argument("--queries", type=int, default=0, help="override the batch size")
+    ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU baseline sample (0 = auto)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and rank != 0:
+        return 0
+
+    import torch
+    from paraselect_b200 import api
+    from paraselect_b200 import build as psb_build
+    if rank == 0:
+        psb_build.ensure_built()
+    cfg = dict(WORKLOADS[args.workload])
+    if args.rows:
+        cfg["n"] = args.rows
+        cfg["nlist"] = max(16, min(cfg["nlist"], args.rows // 256))
+        cfg["nprobe"] = min(cfg["nprobe"], cfg["nlist"])
+    if args.queries:
+        cfg["nq"] = args.queries
+    if not torch.cuda.is_available() or api.device_count() < 1:
+        raise SystemExit("bench.py needs a B200: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = local_rank
+    if world > 1 and args.impl == "ours":
+        import torch.distributed as dist
+        dist.init_process_group("nccl")
+    if args.impl == "ours" and world > 1:
+        from paraselect_b200 import multi
+        return multi.bench_main(args, cfg, rank, world, local_rank)
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        gt_n = 64
+        # queries need the centres: build a tiny first pass for them
+        w, offsets = populations(cfg["n"], cfg["nlist"], cfg["zipf"])
+        centres = torch.empty((cfg["nlist"], cfg["dim"]), dtype=torch.float32, device="cuda")
+        api.gen_normal(cfg["seed"] * 1000 + 1, 0, cfg["nlist"] * cfg["dim"], 1.0, centres, device=device)
+        dq = make_queries(cfg, torch, api, centres, w, device)
+        torch.cuda.synchronize()
+        index, w, centres, gt = build_index(cfg, torch, api, device, gt_queries=dq[:gt_n].contiguous(), gt_k=cfg["topk"])
+        nq, dim, nprobe, topk, R = cfg["nq"], cfg["dim"], cfg["nprobe"], cfg["topk"], cfg["n_rerank"]
+        q_pinned = torch.empty((nq, dim), dtype=torch.float32).pin_memory()
+        q_pinned.copy_(dq)
+        torch.cuda.synchronize()
+        q_host = q_pinned.numpy()
+
+        if args.impl == "reference":
+            return reference_arm(args, cfg, index, q_host, gt)
+
+        t0 = time.time()
+        sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True)
+        log("session created in %.1fs" % (time.time() - t0))
+        stage1 = min(R, cfg["n"]) if R > topk else topk
+        d_probes = torch.empty((nq, nprobe), dtype=torch.int32, device="cuda")
+        d_lut = torch.empty((nq, cfg["M"], 256), dtype=torch.float32, device="cuda")
+        d_cand = torch.empty((nq, stage1), dtype=torch.int32, device="cuda")
+        d_cdist = torch.empty((nq, stage1), dtype=torch.float32, device="cuda")
+        d_ccnt = torch.empty((nq,), dtype=torch.int32, device="cuda")
+        d_rows = torch.empty((nq, topk), dtype=torch.int32, device="cuda")
+        d_dist = torch.empty((nq, topk), dtype=torch.float32, device="cuda")
+        d_ids = torch.empty((nq, topk), dtype=torch.int64, device="cuda")
+
+        def device_step():
+            sess.stage_coarse(dq, nq, nprobe, d_probes)
+            sess.stage_build_lut(dq, nq, d_lut)
+            sess.stage_scan(d_lut, nq, d_probes, nprobe, stage1, d_cand, d_cdist, d_ccnt)
+            if R > topk:
+                sess.stage_rerank(dq, nq, d_cand, stage1, stage1, d_ccnt, topk, d_rows, d_dist)
+                sess.stage_map_ids(d_rows, nq * topk, d_ids)
+            else:
+                sess.stage_map_ids(d_cand, nq * topk, d_ids)
+
+        for _ in range(max(args.warmup, 3)):
+            device_step()
+        torch.cuda.synchronize()
+        sess.counters(reset=True)
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            device_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_dev = e0.elapsed_time(e1) / args.steps
+        c = sess.counters(reset=True)
+        dev_ids = d_ids.cpu().numpy()
+
+        # end to end: host queries -> host results through psb_session_search
+        out_ids = torch.empty((nq, topk), dtype=torch.int64).pin_memory()
+        out_dist = torch.empty((nq, topk), dtype=torch.float32).pin_memory()
+        st = api.Stats()
+        for _ in range(2):
+            sess.search_raw(q_pinned.data_ptr(), nq, nprobe, topk, nq, out_ids.data_ptr(), out_dist.data_ptr(), st)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            sess.search_raw(q_pinned.data_ptr(), nq, nprobe, topk, nq, out_ids.data_ptr(), out_dist.data_ptr(), st)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+        stats = st.as_dict()
+        e2e_ids = out_ids.numpy().copy()
+        e2e_dist = out_dist.numpy().copy()
+        assert np.array_equal(dev_ids, e2e_ids), "stage-level and end-to-end results differ"
+
+    launches = int(c["kernel_launches"] - 0)
+    scan_ms = c["scan_kernel_ms"] / max(1, c["scan_kernel_launches"])
+    S = c["pq_scanned_codes"] / max(1, args.steps)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = S * cfg["M"] / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+    roofline = dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak, unit="GB/s",
+                    frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
+                    algorithmic_bytes_per_launch=int(S * cfg["M"]), rows_per_launch=int(S), ms_per_launch=round(scan_ms, 3),
+                    traffic=None,
+                    lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / 148 / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
+
+    # CPU baseline + parity on a bounded sample of the same batch
+    cores = os.cpu_count() or 1
+    ns = args.cpu_sample or 16
+    ref, dt, kind = cpu_reference_run(index, q_host, cfg, ns, cores)
+    if not args.cpu_sample and dt < 6.0:
+        ns2 = int(min(512, nq, max(ns, ns * 12.0 / max(dt, 1e-3))))
+        if ns2 >= 2 * ns:
+            ns = ns2
+            ref, dt, kind = cpu_reference_run(index, q_host, cfg, ns, cores)
+    ids_equal = bool(np.array_equal(ref["indices"], e2e_ids[:ns]))
+    rel = float(np.max(np.abs(ref["distances"] - e2e_dist[:ns]) / np.maximum(np.abs(ref["distances"]), 1e-30)))
+    gtn = min(gt.shape[0], ns) if gt is not None else 0
+    gt_ids = index["reordered_ids"][gt] if gt is not None else None
+    parity = dict(sample_queries=ns, ids_equal=ids_equal, max_rel_dist_err=rel,
+                  recall_at_k_gpu=recall_at(e2e_ids[:gtn], gt_ids[:gtn], topk) if gtn else None,
+                  recall_at_k_cpu=recall_at(ref["indices"][:gtn], gt_ids[:gtn], topk) if gtn else None,
+                  recall_at_10_gpu=recall_at(e2e_ids[:gtn], gt_ids[:gtn], min(10, topk)) if gtn else None,
+                  recall_at_10_cpu=recall_at(ref["indices"][:gtn], gt_ids[:gtn], min(10, topk)) if gtn else None)
+    line = dict(
+        metric="QPS (IVF-PQ search, recall@k equal to the reference CPU path)", value=round(nq / (ms_dev * 1e-3), 1),
+        unit="queries/s", n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
+        higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+        config=dict(workload=args.workload, desc=cfg["desc"], rows=cfg["n"], dim=dim, nlist=cfg["nlist"], M=cfg["M"],
+                    batch=nq, nprobe=nprobe, topk=topk, n_rerank=R, exact_rows="host-mapped fp32",
+                    l2="inputs larger than L2 (codes %.1f GB)" % (index["codes"].nbytes / 1e9)),
+        e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
+                 h2d_bytes_per_step=int(stats["h2d_bytes"]), d2h_bytes_per_step=int(stats["d2h_bytes"]),
+                 pcie_gather_bytes_per_step=int(nq * stage1 * dim * 4) if R > topk else 0),
+        gpu_launches=launches, roofline=roofline,
+        cpu_baseline=dict(value=round(ns / dt, 2), unit="queries/s", cores=cores, kind=kind,
+                          sample="first %d queries of the batch, all %d host threads" % (ns, cores)),
+        stages_ms=dict(coarse=round(stats["coarse_search_ms"], 3), lut=round(stats["pq_lut_build_ms"], 3),
+                       scan=round(stats["pq_adc_scan_ms"], 3), rerank=round(stats["pq_rerank_ms"], 3),
+                       map_ids=round(stats["pq_map_ids_ms"], 3), h2d=round(stats["h2d_ms"], 3), d2h=round(stats["d2h_ms"], 3)),
+        counters=dict(scanned_codes_per_step=int(S), admitted_per_step=int(c["threshold_candidates"] / max(1, args.steps)),
+                      fallback_queries_per_step=c["fallback_queries"] / max(1, args.steps)),
+        parity=parity, clocks=clocks)
+    print(json.dumps(line), flush=True)
+    sess.close()
+    return 0
+
+
+def reference_arm(args, cfg, index, q_host, gt):
+    """Times the reference's own CPU implementation on bounded samples of the batch (rank 0 only)."""
+    cores = os.cpu_count() or 1
+    ns = args.cpu_sample or 32
+    times = []
+    for i in range(args.warmup + args.steps):
+        lo = (i * ns) % max(1, cfg["nq"] - ns + 1)
+        _, dt, kind = cpu_reference_run(index, q_host[lo:lo + ns], cfg, ns, cores)
+        if i >= args.warmup:
+            times.append(dt)
+    ms = 1e3 * float(np.mean(times))
+    v = round(ns / (ms * 1e-3), 2)
+    line = dict(impl="reference", metric="QPS (IVF-PQ search, recall@k equal to the reference CPU path)", value=v,
+                unit="queries/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=round(ms, 3),
+                higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=args.workload, desc=cfg["desc"], rows=cfg["n"], dim=cfg["dim"], nlist=cfg["nlist"],
+                            M=cfg["M"], batch=cfg["nq"], nprobe=cfg["nprobe"], topk=cfg["topk"], n_rerank=cfg["n_rerank"]),
+                cpu_baseline=dict(value=v, unit="queries/s", cores=cores, kind=kind,
+                                  sample="%d queries of the batch per step, all %d host threads" % (ns, cores)),
+                e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

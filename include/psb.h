@@ -127,7 +127,8 @@ typedef struct psb_options {
     int list_end;
     void* stream;       /* cudaStream_t to run on; NULL = a stream owned by the session */
     int coarse_mode;    /* 0 = auto, 1 = exact SIMT kernel only, 2 = tensor-core filter + exact refinement */
-    int reserved[7];
+    int time_kernels;   /* 1 = bracket the ADC scan kernel with CUDA events (read back by psb_session_counters) */
+    int reserved[6];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -148,6 +149,8 @@ typedef struct psb_stats {
     long long h2d_bytes;
     long long d2h_bytes;
     long long kernel_launches;
+    double scan_kernel_ms;          /* device time of the ADC scan kernel alone (options.time_kernels) */
+    long long scan_kernel_launches;
     int batches;
     int reserved[7];
 } psb_stats;
@@ -248,6 +251,12 @@ psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* 
 /* Coarse stage on host arrays (device copies made internally). */
 psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centroids, int nlist, int dim,
                            int nprobe, int coarse_mode, int64_t* h_ids, float* h_dist, int device);
+
+/* Exact brute-force k nearest rows of d_base [n][dim] for each query (sequential fp32 squared L2, ties by
+ * row): ground truth for recall.  The reference's counterpart is its brute-force scan helper
+ * (src/search/kernels/brute_force/brute_force_scan.cu).  d_rows [nq][k] int32, d_dist [nq][k]; k <= 4096. */
+psb_status psb_knn_exact(const float* d_queries, int nq, const float* d_base, int64_t n, int dim, int k,
+                         int* d_rows, float* d_dist, int device, void* stream);
 
 /* ---- training and encoding ---------------------------------------------------------------------------- */
 

@@ -70,7 +70,7 @@ class IndexView(C.Structure):
 class Options(C.Structure):
     _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
                 ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("coarse_mode", C.c_int),
-                ("reserved", C.c_int * 7)]
+                ("time_kernels", C.c_int), ("reserved", C.c_int * 6)]
 
 
 class Stats(C.Structure):
@@ -79,7 +79,8 @@ class Stats(C.Structure):
                 ("h2d_ms", C.c_double), ("d2h_ms", C.c_double), ("pq_scanned_codes", C.c_longlong),
                 ("pq_adc_lookups", C.c_longlong), ("threshold_candidates", C.c_longlong),
                 ("fallback_queries", C.c_longlong), ("h2d_bytes", C.c_longlong), ("d2h_bytes", C.c_longlong),
-                ("kernel_launches", C.c_longlong), ("batches", C.c_int), ("reserved", C.c_int * 7)]
+                ("kernel_launches", C.c_longlong), ("scan_kernel_ms", C.c_double), ("scan_kernel_launches", C.c_longlong),
+                ("batches", C.c_int), ("reserved", C.c_int * 7)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
@@ -89,7 +90,7 @@ EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
     "psb_session_search", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_scan",
     "psb_stage_rerank", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
-    "psb_coarse_host", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
+    "psb_coarse_host", "psb_knn_exact", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
 _lib = None
@@ -138,7 +139,7 @@ class Session:
     """
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
-                 list_end=0, stream=None, coarse_mode=0):
+                 list_end=0, stream=None, coarse_mode=0, time_kernels=False):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -167,7 +168,8 @@ class Session:
         self.n_rerank = n_rerank
         self.device = device
         opt = Options(device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
-                      list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode)
+                      list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
+                      time_kernels=int(time_kernels))
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 
@@ -281,6 +283,11 @@ def coarse_host(queries, centroids, nprobe, coarse_mode=0, device=0):
     _check(lib().psb_coarse_host(C.c_void_p(_p(q)), q.shape[0], C.c_void_p(_p(c)), c.shape[0], c.shape[1], nprobe,
                                  coarse_mode, C.c_void_p(_p(ids)), C.c_void_p(_p(dist)), device))
     return ids, dist
+
+
+def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):
+    _check(lib().psb_knn_exact(C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_base)), C.c_int64(n), dim, k,
+                               C.c_void_p(_p(d_rows)), C.c_void_p(_p(d_dist)), device, C.c_void_p(stream) if stream else None))
 
 
 # ---- training / encoding / generators on device tensors -------------------------------------------------

@@ -59,6 +59,7 @@ struct ScanWorkspace {
     unsigned long long* work_cursor; // [1]
     unsigned long long* counters;    // [4]: scanned rows, admitted, fallback queries, status
     int pool_cap;
+    cudaEvent_t ev_begin = nullptr, ev_end = nullptr;  // optional: bracket the scan kernel
 };
 
 struct ScanIndex {
@@ -89,6 +90,7 @@ psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reo
                           long long* d_out, cudaStream_t s);
 psb_status launch_merge(const int* d_rows, const float* d_dist, int parts, int nq, int k, int* d_out_rows,
                         float* d_out_dist, cudaStream_t s);
+psb_status launch_offset_rows(int* d_rows, long long n, int delta, cudaStream_t s);
 psb_status launch_widen_ids(const int* d_in, long long n, long long* d_out, cudaStream_t s);
 
 // ---- training ------------------------------------------------------------------------------------------------

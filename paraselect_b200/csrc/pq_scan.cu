@@ -609,7 +609,9 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     a.vis_count = ws.vis_count; a.vis_off = ws.vis_off; a.visitors = ws.visitors; a.item_off = ws.item_off;
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
+    if (ws.ev_begin) PSB_CUDA(cudaEventRecord(ws.ev_begin, s));
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_m<MM>(a, group, sm_count, s))));
+    if (ws.ev_end) PSB_CUDA(cudaEventRecord(ws.ev_end, s));
     // selection
     {
         const size_t smem = (size_t)ws.pool_cap * sizeof(uint64_t);

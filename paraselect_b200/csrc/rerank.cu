@@ -158,6 +158,11 @@ __global__ void k_widen_ids(const int* __restrict__ in, long long n, long long* 
     if (i < n) out[i] = in[i];
 }
 
+__global__ void k_offset_rows(int* __restrict__ rows, long long n, int delta) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && rows[i] >= 0) rows[i] += delta;
+}
+
 // Per query: the k smallest (distance,row) of parts*k shard candidates.
 __global__ void __launch_bounds__(1024)
 k_merge(const int* __restrict__ rows, const float* __restrict__ dist, int parts, int nq, int k, int np,
@@ -234,6 +239,14 @@ psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reo
 psb_status launch_widen_ids(const int* d_in, long long n, long long* d_out, cudaStream_t s) {
     if (n <= 0) return PSB_OK;
     k_widen_ids<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_in, n, d_out);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_offset_rows(int* d_rows, long long n, int delta, cudaStream_t s) {
+    if (n <= 0 || delta == 0) return PSB_OK;
+    k_offset_rows<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_rows, n, delta);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

@@ -119,7 +119,9 @@ struct psb_session {
         pool_cnt, pool, fail_list, scalars, cand_rows, cand_dist, cand_count, stage, out_rows, out_dist, out_ids;
     int ws_batch = 0, ws_nprobe = 0, ws_stage1 = 0, ws_topk = 0;
     int pool_cap = 0;
-    unsigned long long* d_counters = nullptr;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> scan_events;  // pending (options.time_kernels)
+    double scan_ms_total = 0.0;
+    long long scan_launches_total = 0;
 
     ScanIndex scan_index() const {
         ScanIndex ix;
@@ -140,6 +142,27 @@ struct psb_session {
         w.fail_cursor = reinterpret_cast<int*>(sc + 6);
         w.pool_cap = pool_cap;
         return w;
+    }
+    // Scan workspace with a fresh event pair when kernel timing is on.
+    psb_status timed_scan_ws(ScanWorkspace* w) {
+        *w = scan_ws();
+        if (!opt.time_kernels) return PSB_OK;
+        cudaEvent_t a, b;
+        PSB_CUDA(cudaEventCreate(&a));
+        PSB_CUDA(cudaEventCreate(&b));
+        scan_events.emplace_back(a, b);
+        w->ev_begin = a; w->ev_end = b;
+        return PSB_OK;
+    }
+    // Folds finished event pairs into the totals (call after a stream synchronisation).
+    void collect_scan_events() {
+        for (auto& pr : scan_events) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, pr.first, pr.second) == cudaSuccess) { scan_ms_total += t; ++scan_launches_total; }
+            cudaEventDestroy(pr.first); cudaEventDestroy(pr.second);
+        }
+        scan_events.clear();
+        cudaGetLastError();
     }
 };
 
@@ -404,6 +427,7 @@ psb_status psb_session_destroy(psb_session* s) {
     if (!s) return PSB_OK;
     cudaSetDevice(s->device);
     cudaStreamSynchronize(s->stream);
+    s->collect_scan_events();
     if (s->registered) cudaHostUnregister(const_cast<void*>(s->exact_host));
     for (int i = 0; i < 2; ++i) {
         if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
@@ -442,7 +466,9 @@ psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int*
     if (nprobe > kMaxProbe || stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or stage1_k above 2048");
     PSB_CUDA(cudaSetDevice(s->device));
     PSB_TRY(ensure_scan_ws(s, nq, nprobe, stage1_k));
-    return launch_scan(s->scan_index(), s->scan_ws(), d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count,
+    ScanWorkspace ws;
+    PSB_TRY(s->timed_scan_ws(&ws));
+    return launch_scan(s->scan_index(), ws, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count,
                        s->sm_count, s->stream);
 }
 
@@ -481,6 +507,11 @@ psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     stats->threshold_candidates = (long long)h[1];
     stats->fallback_queries = (long long)h[2];
     stats->kernel_launches = launches_total();
+    if (!s->scalars.p) PSB_CUDA(cudaStreamSynchronize(s->stream));
+    s->collect_scan_events();
+    stats->scan_kernel_ms = s->scan_ms_total;
+    stats->scan_kernel_launches = s->scan_launches_total;
+    if (reset) { s->scan_ms_total = 0.0; s->scan_launches_total = 0; }
     return PSB_OK;
 }
 
@@ -506,6 +537,9 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         PSB_CUDA(cudaMemcpyAsync(c0, s->scalars.p, sizeof(c0), cudaMemcpyDeviceToHost, st));
         PSB_CUDA(cudaStreamSynchronize(st));
     }
+    s->collect_scan_events();
+    const double scan_ms0 = s->scan_ms_total;
+    const long long scan_n0 = s->scan_launches_total;
     double t_h2d = 0, t_coarse = 0, t_lut = 0, t_scan = 0, t_rr = 0, t_map = 0, t_d2h = 0;
     long long h2d = 0, d2h = 0;
     int nb = 0;
@@ -526,7 +560,9 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         if (stats) PSB_TRY(tm.mark(st));
         int* rows_out = rerank ? s->cand_rows.as<int>() : s->out_rows.as<int>();
         float* dist_out = rerank ? s->cand_dist.as<float>() : s->out_dist.as<float>();
-        PSB_TRY(launch_scan(s->scan_index(), s->scan_ws(), s->lut.as<float>(), n, s->probes.as<int>(), nprobe, stage1_k,
+        ScanWorkspace sws;
+        PSB_TRY(s->timed_scan_ws(&sws));
+        PSB_TRY(launch_scan(s->scan_index(), sws, s->lut.as<float>(), n, s->probes.as<int>(), nprobe, stage1_k,
                             rows_out, dist_out, s->cand_count.as<int>(), s->sm_count, st));
         if (stats) PSB_TRY(tm.mark(st));
         if (rerank) {
@@ -565,6 +601,9 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         stats->fallback_queries = (long long)(c1[2] - c0[2]);
         stats->h2d_bytes = h2d; stats->d2h_bytes = d2h;
         stats->kernel_launches = launches_total() - launches0;
+        s->collect_scan_events();
+        stats->scan_kernel_ms = s->scan_ms_total - scan_ms0;
+        stats->scan_kernel_launches = s->scan_launches_total - scan_n0;
         stats->batches = nb;
     }
     return PSB_OK;
@@ -643,6 +682,43 @@ psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centro
     PSB_TRY(launch_widen_ids(ids.as<int>(), (long long)nq * nprobe, ids64.as<long long>(), nullptr));
     PSB_CUDA(cudaMemcpy(h_ids, ids64.p, sizeof(long long) * (size_t)nq * nprobe, cudaMemcpyDeviceToHost));
     if (h_dist) PSB_CUDA(cudaMemcpy(h_dist, dist.p, sizeof(float) * (size_t)nq * nprobe, cudaMemcpyDeviceToHost));
+    return PSB_OK;
+}
+
+psb_status psb_knn_exact(const float* d_queries, int nq, const float* d_base, int64_t n, int dim, int k,
+                         int* d_rows, float* d_dist, int device, void* stream) {
+    if (!d_queries || !d_base || !d_rows || !d_dist || nq <= 0 || n <= 0 || dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid knn request");
+    if (k <= 0 || k > n) return fail(PSB_INVALID_ARGUMENT, "k must be in 1..n");
+    if (k > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "k above 4096 is not supported");
+    if (n > INT_MAX) return fail(PSB_UNSUPPORTED_SHAPE, "more than 2^31-1 base rows");
+    PSB_TRY(check_device(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // tiles of base rows, each at most 1 GiB of distances, then a merge of the per-tile winners
+    long long tile = std::max<long long>(4096, ((long long)1 << 28) / nq);
+    tile = std::min<long long>(tile, n);
+    const int tiles = (int)((n + tile - 1) / tile);
+    if ((long long)tiles * k > 16384) return fail(PSB_UNSUPPORTED_SHAPE, "knn: too many tiles for the merge; pass fewer base rows per call");
+    DevBuf dist, trows, tdist;
+    PSB_TRY(dist.reserve(sizeof(float) * (size_t)nq * tile));
+    PSB_TRY(trows.reserve(sizeof(int) * (size_t)tiles * nq * k));
+    PSB_TRY(tdist.reserve(sizeof(float) * (size_t)tiles * nq * k));
+    for (int t = 0; t < tiles; ++t) {
+        const long long r0 = (long long)t * tile;
+        const int rows = (int)std::min<long long>(tile, n - r0);
+        PSB_TRY(launch_coarse_dist_exact(d_queries, nq, d_base + (size_t)r0 * dim, rows, dim, dist.as<float>(), st));
+        const int kk = std::min(k, rows);
+        if (kk < k) {
+            PSB_CUDA(cudaMemsetAsync(trows.as<int>() + (size_t)t * nq * k, 0xff, sizeof(int) * (size_t)nq * k, st));
+        }
+        // select kk per query into a [nq][k] slab (row stride k): run per-tile with k, rows >= k is the common case
+        if (kk == k) {
+            PSB_TRY(launch_select_rows(dist.as<float>(), nq, rows, k, trows.as<int>() + (size_t)t * nq * k,
+                                       tdist.as<float>() + (size_t)t * nq * k, st));
+            PSB_TRY(launch_offset_rows(trows.as<int>() + (size_t)t * nq * k, (long long)nq * k, (int)r0, st));
+        }
+    }
+    PSB_TRY(launch_merge(trows.as<int>(), tdist.as<float>(), tiles, nq, k, d_rows, d_dist, st));
+    PSB_CUDA(cudaStreamSynchronize(st));
     return PSB_OK;
 }
 
