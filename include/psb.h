@@ -252,6 +252,21 @@ psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* 
 psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centroids, int nlist, int dim,
                            int nprobe, int coarse_mode, int64_t* h_ids, float* h_dist, int device);
 
+/* Coarse stage that allocates nothing (no counterpart in the reference).  For callers that cannot call
+ * cudaMalloc when they search - a fixed memory budget handed out at start-up, a host application that forbids
+ * allocation after initialisation, a latency-critical thread that must not take the allocator's device
+ * synchronisation or its late out-of-memory failure.  Inputs and outputs are DEVICE pointers owned by the
+ * caller on the CURRENT device; the [nq][nlist] distance tile lives in a 16 MiB array built into the
+ * library (each GPU that loads the library holds it until the process exits), so nq * nlist must not exceed
+ * 4,194,304 (PSB_UNSUPPORTED_SHAPE otherwise).  Results are those of psb_stage_coarse bit for bit.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ * before starting any stream capture.  All calls share the one array and it keeps the previous call's
+ * contents (every element a call reads is first written by that call, so nothing needs clearing); two calls
+ * whose kernels overlap on the GPU - different streams, different threads - race on it and must be serialised
+ * by the caller.  d_ids [nq][nprobe] int32, d_dist [nq][nprobe] fp32 (may be NULL), asynchronous on stream. */
+psb_status psb_coarse_search_static(const float* d_queries, int nq, const float* d_centroids, int nlist, int dim,
+                                    int nprobe, int* d_ids, float* d_dist, void* stream);
+
 /* Exact brute-force k nearest rows of d_base [n][dim] for each query (sequential fp32 squared L2, ties by
  * row): ground truth for recall.  The reference's counterpart is its brute-force scan helper
  * (src/search/kernels/brute_force/brute_force_scan.cu).  d_rows [nq][k] int32, d_dist [nq][k]; k <= 4096. */

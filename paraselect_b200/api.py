@@ -90,7 +90,7 @@ EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
     "psb_session_search", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_scan",
     "psb_stage_rerank", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
-    "psb_coarse_host", "psb_knn_exact", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
+    "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
 _lib = None
@@ -283,6 +283,14 @@ def coarse_host(queries, centroids, nprobe, coarse_mode=0, device=0):
     _check(lib().psb_coarse_host(C.c_void_p(_p(q)), q.shape[0], C.c_void_p(_p(c)), c.shape[0], c.shape[1], nprobe,
                                  coarse_mode, C.c_void_p(_p(ids)), C.c_void_p(_p(dist)), device))
     return ids, dist
+
+
+def coarse_search_static(d_queries, nq, d_centroids, nlist, dim, nprobe, d_ids, d_dist=None, stream=None):
+    """Coarse stage on device tensors that allocates nothing: its scratch is a fixed array inside the library
+    (nq * nlist <= 4,194,304).  For callers that may not allocate device memory when they search."""
+    _check(lib().psb_coarse_search_static(C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_centroids)), nlist, dim, nprobe,
+                                          C.c_void_p(_p(d_ids)), C.c_void_p(_p(d_dist)) if d_dist is not None else None,
+                                          C.c_void_p(stream) if stream else None))
 
 
 def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):

@@ -153,3 +153,45 @@ psb_status launch_select_rows(const float* d_dist, int nq, int n, int k, int* d_
 }
 
 }  // namespace psb
+
+// ---- coarse search without any allocation ---------------------------------------------------------------
+// Some callers may not allocate device memory at the moment they need a coarse search: a serving thread that
+// holds a fixed memory budget granted at start-up, code that runs under a memory pool it must not touch, or a
+// plugin host that forbids cudaMalloc after initialisation because an allocation synchronises the device and
+// can fail late.  For them the distance tile [nq][nlist] lives in the array below, which every GPU that loads
+// this library holds until the process exits.
+namespace psb {
+namespace {
+constexpr size_t kStaticCoarseFloats = (size_t)4 << 20;  // 4 Mi distances = 16 MiB: nq * nlist must not exceed it
+static __device__ __align__(256) float g_coarse_scratch[kStaticCoarseFloats];
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {};  // per device: the array's DEVICE address (the symbol itself is a host stand-in)
+}  // namespace
+}  // namespace psb
+
+extern "C" psb_status psb_coarse_search_static(const float* d_queries, int nq, const float* d_centroids, int nlist,
+                                               int dim, int nprobe, int* d_ids, float* d_dist, void* stream) {
+    using namespace psb;
+    if (!d_queries || !d_centroids || !d_ids || nq < 0 || nlist <= 0 || dim <= 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid coarse request");
+    if (nprobe <= 0 || nprobe > nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
+    if (nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
+    if ((size_t)nq * (size_t)nlist > kStaticCoarseFloats)
+        return fail(PSB_UNSUPPORTED_SHAPE,
+                    "psb_coarse_search_static: nq * nlist exceeds the 4,194,304 distances of the built-in scratch; "
+                    "split the query batch or use psb_stage_coarse");
+    if (nq == 0) return PSB_OK;
+    int device = -1;
+    PSB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail(PSB_UNSUPPORTED_SHAPE, "device ordinal above 63");
+    if (!g_scratch_ptr[device]) {
+        // First call on this device: resolve the array's device address (this device is current).
+        float* p = nullptr;
+        PSB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_coarse_scratch));
+        g_scratch_ptr[device] = p;
+    }
+    float* tile = g_scratch_ptr[device];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PSB_TRY(launch_coarse_dist_exact(d_queries, nq, d_centroids, nlist, dim, tile, st));
+    return launch_select_rows(tile, nq, nlist, nprobe, d_ids, d_dist, st);
+}
