@@ -371,7 +371,10 @@ def main():
                        map_ids=round(stats["pq_map_ids_ms"], 3), h2d=round(stats["h2d_ms"], 3), d2h=round(stats["d2h_ms"], 3)),
         counters=dict(scanned_codes_per_step=int(S), admitted_per_step=int(c["threshold_candidates"] / max(1, args.steps)),
                       fallback_queries_per_step=c["fallback_queries"] / max(1, args.steps)),
-        parity=parity, clocks=clocks)
+        parity=parity,
+        result_checksum=int(np.bitwise_xor.reduce((e2e_ids.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel())
+                            & np.uint64((1 << 62) - 1)),
+        clocks=clocks)
     print(json.dumps(line), flush=True)
     sess.close()
     return 0

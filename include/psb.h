@@ -126,6 +126,10 @@ typedef struct psb_options {
     int list_begin;     /* shard: this session scans lists [list_begin, list_end); 0,0 = all lists */
     int list_end;
     void* stream;       /* cudaStream_t to run on; NULL = a stream owned by the session */
+    const int64_t* list_global_begin; /* striped shard (multi-GPU): the index view holds, for every list l, a contiguous
+                           slice of the list; HOST array [nlist], list_global_begin[l] = index-wide row of the slice's
+                           first row.  Candidate rows reported and accepted by the stage calls are index-wide rows.
+                           NULL = the view is the whole index. */
     int coarse_mode;    /* 0 = auto, 1 = exact SIMT kernel only, 2 = tensor-core filter + exact refinement */
     int time_kernels;   /* 1 = bracket the ADC scan kernel with CUDA events (read back by psb_session_counters) */
     int reserved[6];
@@ -226,7 +230,18 @@ psb_status psb_stage_rerank(psb_session* session, const float* d_queries, int nq
                             int candidate_count, int candidate_stride, const int* d_counts, int topk,
                             int* d_out_rows, float* d_out_dist);
 
-/* indices[i] = rows[i] >= 0 ? reordered_ids[rows[i]] : -1.  Replaces ivfpq_map_ids
+/* Multi-GPU halves of the rerank (no counterpart in the reference, whose search is single-GPU).
+ * psb_stage_rerank_partial: d_dist [nq][candidate_count] = exact distance of every candidate whose row this
+ * session holds, +inf for the others; the caller combines shards with an elementwise minimum.
+ * psb_stage_select_topk: the topk (distance,row) pairs without duplicates from such a combined d_dist. */
+psb_status psb_stage_rerank_partial(psb_session* session, const float* d_queries, int nq, const int* d_candidates,
+                                    int candidate_count, int candidate_stride, const int* d_counts, float* d_dist);
+psb_status psb_stage_select_topk(psb_session* session, const float* d_dist, const int* d_candidates, int nq,
+                                 int candidate_count, int candidate_stride, const int* d_counts, int topk,
+                                 int* d_out_rows, float* d_out_dist);
+
+/* indices[i] = original id of row rows[i] when this session holds the row (always, for a whole index), else -1;
+ * rows[i] < 0 gives -1.  Replaces ivfpq_map_ids
  * (src/search/ivfpq/stage/ivfpq_map_ids.cpp:4-15). */
 psb_status psb_stage_map_ids(psb_session* session, const int* d_rows, int64_t n, int64_t* d_indices);
 

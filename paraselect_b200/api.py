@@ -69,7 +69,8 @@ class IndexView(C.Structure):
 
 class Options(C.Structure):
     _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
-                ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("coarse_mode", C.c_int),
+                ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("list_global_begin", C.c_void_p),
+                ("coarse_mode", C.c_int),
                 ("time_kernels", C.c_int), ("reserved", C.c_int * 6)]
 
 
@@ -89,7 +90,7 @@ class Stats(C.Structure):
 EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
     "psb_session_search", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_scan",
-    "psb_stage_rerank", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
+    "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
@@ -139,7 +140,7 @@ class Session:
     """
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
-                 list_end=0, stream=None, coarse_mode=0, time_kernels=False):
+                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -167,7 +168,9 @@ class Session:
         self.dim, self.nlist, self.M, self.K, self.n = cen.shape[1], cen.shape[0], cb.shape[0], cb.shape[1], n
         self.n_rerank = n_rerank
         self.device = device
-        opt = Options(device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
+        gb = _np(list_global_begin, np.int64)
+        self._keep.append(gb)
+        opt = Options(list_global_begin=_p(gb), device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
                       time_kernels=int(time_kernels))
         self._h = C.c_void_p()
@@ -238,6 +241,16 @@ class Session:
         _check(lib().psb_stage_rerank(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_cand)), count, stride,
                                       C.c_void_p(_p(d_counts)) if d_counts is not None else None, topk,
                                       C.c_void_p(_p(d_out_rows)), C.c_void_p(_p(d_out_dist))))
+
+    def stage_rerank_partial(self, d_queries, nq, d_cand, count, stride, d_counts, d_dist):
+        _check(lib().psb_stage_rerank_partial(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_cand)), count, stride,
+                                              C.c_void_p(_p(d_counts)) if d_counts is not None else None,
+                                              C.c_void_p(_p(d_dist))))
+
+    def stage_select_topk(self, d_dist, d_cand, nq, count, stride, d_counts, topk, d_out_rows, d_out_dist):
+        _check(lib().psb_stage_select_topk(self._h, C.c_void_p(_p(d_dist)), C.c_void_p(_p(d_cand)), nq, count, stride,
+                                           C.c_void_p(_p(d_counts)) if d_counts is not None else None, topk,
+                                           C.c_void_p(_p(d_out_rows)), C.c_void_p(_p(d_out_dist))))
 
     def stage_map_ids(self, d_rows, n, d_indices):
         _check(lib().psb_stage_map_ids(self._h, C.c_void_p(_p(d_rows)), C.c_int64(n), C.c_void_p(_p(d_indices))))

@@ -14,7 +14,6 @@ constexpr int kMaxStage1 = 2048;      // candidates kept per query by the ADC st
 constexpr int kMaxTopk = 2048;
 constexpr int kMaxRerankWidth = 4096; // candidates per query accepted by the rerank operator
 constexpr int kPoolCapMax = 16384;    // per-query admission pool entries
-constexpr int kSeedSampleMax = 16384; // rows scored per query by the threshold seed
 constexpr int kScanChunkRows = 16384; // rows per scan work item
 constexpr int kMaxCodebook = 256;
 
@@ -66,6 +65,7 @@ struct ScanIndex {
     const uint8_t* codes;      // device, shard rows only
     const long long* offsets;  // device [nlist + 1], global rows
     long long row_base;        // global row of codes[0]
+    const long long* row_delta = nullptr;  // device [nlist] or null: reported row = scanned row + row_delta[list]
     int nlist;
     int list_begin, list_end;  // shard
     int m, k;
@@ -76,17 +76,31 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
                        int* d_count, int sm_count, cudaStream_t s);
 
 // ---- rerank ------------------------------------------------------------------------------------------------
-// Copies the candidate rows (fp32 or u8, elem_bytes 4 or 1) from src (device-visible: mapped host or device)
-// to stage [nq][candidate_count][dim].
-psb_status launch_gather_rows(const void* src, long long count, int dim, int elem_bytes, const int* d_candidates,
+// Which rows of the index-wide (list-contiguous) numbering a session's exact store and id table hold.
+//   global_begin == nullptr: rows [base, base + count), stored in that order.
+//   otherwise (striped shard): for every list l the rows [global_begin[l], global_begin[l] + len_l), stored at local
+//   rows [local_offsets[l], local_offsets[l + 1]).
+struct RowMap {
+    const long long* global_begin = nullptr;   // device [nlist]
+    const long long* local_offsets = nullptr;  // device [nlist + 1]
+    int nlist = 0;
+    long long base = 0;
+    long long count = 0;
+};
+// Copies the candidate rows held here (fp32 or u8, elem_bytes 4 or 1) from src (device-visible: mapped host or
+// device) to stage [nq][candidate_count][dim].  Candidates are global rows.
+psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
                               void* d_stage, cudaStream_t s);
-// Scores the staged rows exactly and keeps the topk by (distance, row) without duplicates.
-psb_status launch_rerank_select(const void* d_stage, long long count, int dim, int elem_bytes,
-                                const void* d_queries, const int* d_candidates, int nq, int candidate_count,
-                                int candidate_stride, const int* d_counts, int topk, int* d_out_rows,
-                                float* d_out_dist, cudaStream_t s);
-psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, long long n_vectors,
+// d_out_dist [nq][candidate_count]: exact distance of each staged candidate, +inf for rows not held here.
+psb_status launch_rerank_score(const void* d_stage, const RowMap& mp, int dim, int elem_bytes, const void* d_queries,
+                               const int* d_candidates, int nq, int candidate_count, int candidate_stride,
+                               const int* d_counts, float* d_out_dist, cudaStream_t s);
+// Per query the topk (distance,row) pairs without duplicates from d_dist [nq][candidate_count].
+psb_status launch_topk_select(const float* d_dist, const int* d_candidates, int nq, int candidate_count,
+                              int candidate_stride, const int* d_counts, int topk, int* d_out_rows,
+                              float* d_out_dist, cudaStream_t s);
+psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, const RowMap& mp,
                           long long* d_out, cudaStream_t s);
 psb_status launch_merge(const int* d_rows, const float* d_dist, int parts, int nq, int k, int* d_out_rows,
                         float* d_out_dist, cudaStream_t s);

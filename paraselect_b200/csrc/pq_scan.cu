@@ -5,7 +5,7 @@
 //   k_count_visitors   inverts (query, probe) -> per-list visitor counts (+ rows each query will scan)
 //   k_scan_lists       exclusive scans: visitor offsets and work-item offsets per list
 //   k_fill_visitors    per-list visitor arrays
-//   k_seed_threshold   per query: ADC distances of a strided row sample -> admission cutoff
+//   k_seed_threshold   per query: ADC distances of a strided row sample (1/16 .. 1/64 of its rows) -> admission cutoff
 //   k_scan<M,V>        persistent CTAs; work item = (list, chunk of rows, group of V visitors); each thread
 //                      keeps one code row in registers and scores it for the V visitors whose tables sit
 //                      interleaved in shared memory (one LDS.128 fetches 4 visitors' entries); rows with
@@ -164,78 +164,85 @@ __device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut,
     else return adc_row_dyn(row, s_lut, m, k);
 }
 
-// Per query: cutoff from a strided sample of the rows it will scan.
+// Per query: admission cutoff from a strided sample of the rows it will scan.
 //   N = rows the query scans.  N <= pool capacity: cutoff = +inf (everything is admitted).
-//   Otherwise every stride-th row of each probed list is scored (n_s rows) and the cutoff is the r-th smallest
-//   sample distance with r = ceil(mu + 4 sqrt(mu) + 2), mu = stage1_k * n_s / N: the stage1_k-th smallest of all
-//   N distances lies below it except with negligible probability; the selection kernel verifies the pool holds
-//   at least stage1_k rows and did not overflow, and the exact fallback handles the rest.
+//   Otherwise every stride-th row of each probed list is scored, stride = clamp(stage1_k / 16, 16, 64), n_s rows in
+//   all, and the cutoff is the r-th smallest sample distance with r = ceil(mu + 4 sqrt(mu) + 2), mu = stage1_k * n_s / N:
+//   the stage1_k-th smallest of all N distances lies below it except with negligible probability, and about r * stride
+//   rows (2-4 x stage1_k) pass it.  The selection kernel verifies that each pool holds at least stage1_k rows and did
+//   not overflow; the exact fallback handles the rest.  The r smallest sample keys are kept with a running cutoff:
+//   keys below it go to a 2048-entry buffer that is sorted and cut back to r whenever it could overflow.
+constexpr int kSeedBuf = 2048;
 template <int M>
 __global__ void __launch_bounds__(kSeedThreads)
 k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
                  const long long* __restrict__ offsets, int nlist, int lb, int le,
                  const uint8_t* __restrict__ codes, long long row_base, int m, int k,
                  const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr) {
-    extern __shared__ float s_mem[];
-    float* s_lut = s_mem;                 // [m * k]
-    float* s_buf = s_mem + m * k;         // [kSeedSampleMax]
-    __shared__ int s_count;
-    __shared__ unsigned int s_hist[256];
-    __shared__ uint32_t s_prefix, s_rank;
+    extern __shared__ __align__(16) unsigned char s_seed_raw[];
+    float* s_lut = reinterpret_cast<float*>(s_seed_raw);                                  // [m * k]
+    uint32_t* s_keys = reinterpret_cast<uint32_t*>(s_seed_raw + (size_t)m * k * 4);       // [kSeedBuf]
+    int* s_pref = reinterpret_cast<int*>(s_seed_raw + (size_t)m * k * 4 + kSeedBuf * 4);  // [nprobe + 1]
+    __shared__ int s_warp[32];
+    __shared__ int s_total, s_cnt;
+    __shared__ uint32_t s_cut;
     const int q = blockIdx.x;
     const long long N = q_rows[q];
-    if (N <= pool_cap) { if (threadIdx.x == 0) thr[q] = __int_as_float(0x7f800000); return; }
-    long long stride = (N + (kSeedSampleMax - nprobe) - 1) / (kSeedSampleMax - nprobe);
-    if (stride < 16) stride = 16;
+    const float inf = __int_as_float(0x7f800000);
+    if (N <= pool_cap) { if (threadIdx.x == 0) thr[q] = inf; return; }
+    int stride = stage1_k / 16;
+    stride = stride < 16 ? 16 : (stride > 64 ? 64 : stride);
+    if ((N + 65535) / 65536 > stride) stride = (int)((N + 65535) / 65536);  // at most ~64K samples per query
     for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
-    if (threadIdx.x == 0) s_count = 0;
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-    for (int p = warp; p < nprobe; p += nwarp) {
-        const int l = probes[(size_t)q * nprobe + p];
-        if (l < lb || l >= le || l < 0 || l >= nlist) continue;
-        const long long b = offsets[l], e = offsets[l + 1];
-        const int nj = (int)((e - b + stride - 1) / stride);
-        if (nj <= 0) continue;
-        int base = 0;
-        if (lane == 0) base = atomicAdd(&s_count, nj);
-        base = __shfl_sync(0xffffffffu, base, 0);
-        for (int j = lane; j < nj; j += 32) {
-            const long long r = b + (long long)j * stride;
-            const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k);
-            if (base + j < kSeedSampleMax) s_buf[base + j] = d;
+    // samples per probe and their exclusive prefix
+    int carry = 0;
+    for (int p0 = 0; p0 < nprobe; p0 += blockDim.x) {
+        const int p = p0 + threadIdx.x;
+        int nj = 0;
+        if (p < nprobe) {
+            const int l = probes[(size_t)q * nprobe + p];
+            if (!(l < lb || l >= le || l < 0 || l >= nlist)) nj = (int)((offsets[l + 1] - offsets[l] + stride - 1) / stride);
         }
+        const int ex = block_exclusive_scan(nj, s_warp, &s_total);
+        if (p < nprobe) s_pref[p] = carry + ex;
+        carry += s_total;
+        __syncthreads();
     }
-    __syncthreads();
-    const int ns = min(s_count, kSeedSampleMax);
+    const int ns = carry;
+    if (threadIdx.x == 0) { s_pref[nprobe] = ns; s_cnt = 0; s_cut = 0xffffffffu; }
     const float mu = (float)stage1_k * (float)ns / (float)N;
-    int r = (int)ceilf(mu + 4.0f * sqrtf(mu) + 2.0f);
-    if (r >= ns) { if (threadIdx.x == 0) thr[q] = __int_as_float(0x7f800000); return; }
-    // radix select of the r-th smallest (1-based) of s_buf[0..ns)
-    if (threadIdx.x == 0) { s_prefix = 0; s_rank = (uint32_t)r; }
-    uint32_t mask = 0;
-    for (int pass = 3; pass >= 0; --pass) {
-        const int shift = pass * 8;
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0;
+    const int r = (int)ceilf(mu + 4.0f * sqrtf(mu) + 2.0f);
+    if (r >= ns || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; return; }
+    __syncthreads();
+    for (int base = 0; base < ns; base += blockDim.x) {
+        const int c_now = s_cnt;  // stable since the barrier that ended the previous round
         __syncthreads();
-        const uint32_t prefix = s_prefix;
-        for (int i = threadIdx.x; i < ns; i += blockDim.x) {
-            const uint32_t key = f2o(s_buf[i]);
-            if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255], 1u);
+        if (c_now + (int)blockDim.x > kSeedBuf) {  // uniform
+            for (int i = c_now + threadIdx.x; i < kSeedBuf; i += blockDim.x) s_keys[i] = 0xffffffffu;
+            __syncthreads();
+            block_bitonic_sort(s_keys, kSeedBuf);
+            if (threadIdx.x == 0) { s_cnt = r; s_cut = s_keys[r - 1]; }  // c_now >= r here
+            __syncthreads();
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            uint32_t cum = 0, rank = s_rank;
-            for (int b = 0; b < 256; ++b) {
-                const uint32_t h = s_hist[b];
-                if (cum + h >= rank) { s_prefix = prefix | ((uint32_t)b << shift); s_rank = rank - cum; break; }
-                cum += h;
+        const int idx = base + threadIdx.x;
+        if (idx < ns) {
+            int lo = 0, hi = nprobe;  // largest p with s_pref[p] <= idx
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (s_pref[mid] <= idx) lo = mid; else hi = mid;
             }
+            const int l = probes[(size_t)q * nprobe + lo];
+            const long long row = offsets[l] + (long long)(idx - s_pref[lo]) * stride;
+            const uint32_t key = f2o(adc_row<M>(codes + (size_t)(row - row_base) * m, s_lut, m, k));
+            if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
         }
-        mask |= 255u << shift;
         __syncthreads();
     }
-    if (threadIdx.x == 0) thr[q] = o2f(s_prefix);
+    const int c = s_cnt;
+    for (int i = c + threadIdx.x; i < kSeedBuf; i += blockDim.x) s_keys[i] = 0xffffffffu;
+    __syncthreads();
+    block_bitonic_sort(s_keys, kSeedBuf);
+    if (threadIdx.x == 0) thr[q] = c >= r ? o2f(s_keys[r - 1]) : inf;
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -271,6 +278,7 @@ struct ScanArgs {
     const uint8_t* codes;
     const long long* offsets;
     long long row_base;
+    const long long* row_delta;  // optional [nlist]: reported row = local row + row_delta[list]
     int nlist, m, k;
     const int* vis_count; const int* vis_off; const int* visitors;
     const long long* item_off;
@@ -347,6 +355,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_scan(const ScanArgs a) {
             }
         }
         __syncthreads();
+        const long long delta = a.row_delta ? a.row_delta[l] : 0;
         const long long r0 = a.offsets[l] + chunk * a.chunk_rows;
         const long long r1 = min(r0 + a.chunk_rows, a.offsets[l + 1]);
         for (long long r = r0 + threadIdx.x; r < r1; r += kScanThreads) {
@@ -383,7 +392,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) k_scan(const ScanArgs a) {
             for (int v = 0; v < V; ++v) {
                 if (acc[v] <= thr[v]) {
                     const int slot = atomicAdd(&a.pool_cnt[vq[v]], 1);
-                    if (slot < a.pool_cap) a.pool[(size_t)vq[v] * a.pool_cap + slot] = make_key(acc[v], (uint32_t)r);
+                    if (slot < a.pool_cap) a.pool[(size_t)vq[v] * a.pool_cap + slot] = make_key(acc[v], (uint32_t)(r + delta));
                 }
             }
         }
@@ -427,8 +436,8 @@ template <int M>
 __global__ void __launch_bounds__(kFallbackThreads)
 k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
                  const long long* __restrict__ offsets, int nlist, int lb, int le,
-                 const uint8_t* __restrict__ codes, long long row_base, int m, int k, int stage1_k, int buf_n,
-                 const int* __restrict__ fail_list, const int* __restrict__ n_fail, int* __restrict__ fail_cursor,
+                 const uint8_t* __restrict__ codes, long long row_base, const long long* __restrict__ row_delta,
+                 int m, int k, int stage1_k, int buf_n, const int* __restrict__ fail_list, const int* __restrict__ n_fail, int* __restrict__ fail_cursor,
                  int* __restrict__ out_rows, float* __restrict__ out_dist, int* __restrict__ out_count,
                  unsigned long long* __restrict__ counters) {
     extern __shared__ __align__(16) unsigned char s_raw[];
@@ -451,6 +460,7 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
             const int l = probes[(size_t)q * nprobe + p];
             if (l < lb || l >= le || l < 0 || l >= nlist) continue;
             const long long b = offsets[l], e = offsets[l + 1];
+            const long long delta = row_delta ? row_delta[l] : 0;
             for (long long base = b; base < e; base += blockDim.x) {
                 const int c_now = s_cnt;  // stable since the barrier that ended the previous block of rows
                 __syncthreads();          // every thread has read it before any thread appends again
@@ -469,7 +479,7 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
                 const long long r = base + threadIdx.x;
                 if (r < e) {
                     const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k);
-                    const uint64_t key = make_key(d, (uint32_t)r);
+                    const uint64_t key = make_key(d, (uint32_t)(r + delta));
                     if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
                 }
                 __syncthreads();
@@ -528,7 +538,7 @@ psb_status run_scan_m(const ScanArgs& a, int group, int sm_count, cudaStream_t s
 template <int M>
 psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq, const int* d_probes,
                     int nprobe, int stage1_k, cudaStream_t s) {
-    const size_t smem = ((size_t)ix.m * ix.k + kSeedSampleMax) * sizeof(float);
+    const size_t smem = (size_t)ix.m * ix.k * sizeof(float) + kSeedBuf * sizeof(uint32_t) + ((size_t)nprobe + 1) * sizeof(int);
     PSB_TRY(set_smem(k_seed_threshold<M>, smem));
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
@@ -547,7 +557,7 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     const size_t smem = (size_t)buf_n * 8 + (size_t)ix.m * ix.k * sizeof(float);
     PSB_TRY(set_smem(k_exact_fallback<M>, smem));
     k_exact_fallback<M><<<sm_count, kFallbackThreads, smem, s>>>(
-        d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.m, ix.k,
+        d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.row_delta, ix.m, ix.k,
         stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters);
     count_launch();
     PSB_LAUNCH_CHECK();
@@ -604,7 +614,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s))));
     // scan
     ScanArgs a;
-    a.lut = d_lut; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base;
+    a.lut = d_lut; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base; a.row_delta = ix.row_delta;
     a.nlist = ix.nlist; a.m = ix.m; a.k = ix.k;
     a.vis_count = ws.vis_count; a.vis_off = ws.vis_off; a.visitors = ws.visitors; a.item_off = ws.item_off;
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;

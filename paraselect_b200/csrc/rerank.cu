@@ -1,13 +1,15 @@
 // Exact rerank of the ADC candidates, id mapping and the multi-shard candidate merge.
 //
 //   k_gather_rows     copies each candidate's exact row (fp32 or u8) from the exact store - host memory mapped
-//                     into the device address space, read over PCIe, or device memory - into a dense staging
-//                     buffer in HBM; one warp per row, 16-byte loads
-//   k_rerank_select   one CTA per query: half-warps score staged rows in the accumulation order of the CPU
-//                     kernel the reference uses (four 16-lane FMA accumulators, pairwise combine, halving tree:
-//                     src/cpu/distance/fp32_l2_avx512.h:16-53), a bitonic sort orders (distance,row), duplicate
-//                     rows collapse, the first topk are written (reference semantics:
-//                     src/search/ivf_common/ivf_host_rerank.cpp:152-177, src/search/ivf_common/ivf_exact_topk.h:12-22)
+//                     into the device address space and read over PCIe, or device memory - into a dense staging
+//                     buffer in HBM; one warp per row, 16-byte loads.  Rows this session does not hold (other
+//                     shards' rows, invalid ids) are skipped.
+//   k_rerank_score    half-warps score staged rows in the accumulation order of the CPU kernel the reference uses
+//                     (four 16-lane FMA accumulators, pairwise combine, halving tree:
+//                     src/cpu/distance/fp32_l2_avx512.h:16-53); rows not held here score +inf
+//   k_topk_select     one CTA per query: bitonic sort of (distance,row) keys, duplicate rows collapse, the first
+//                     topk are written (reference semantics: src/search/ivf_common/ivf_host_rerank.cpp:152-177,
+//                     src/search/ivf_common/ivf_exact_topk.h:12-22)
 #include "common.cuh"
 #include "kernels.h"
 
@@ -20,26 +22,45 @@ __device__ __forceinline__ int cand_count(const int* counts, int q, int candidat
     return c < 0 ? 0 : (c > candidate_count ? candidate_count : c);
 }
 
-__global__ void k_gather_rows(const unsigned char* __restrict__ src, long long count, int row_bytes,
+// Global (index-wide, list-contiguous) row -> row of this session's exact store, or -1 when not held here.
+__device__ __forceinline__ long long local_row(const RowMap& mp, long long r) {
+    if (r < 0) return -1;
+    if (!mp.global_begin) {
+        const long long l = r - mp.base;
+        return (l >= 0 && l < mp.count) ? l : -1;
+    }
+    int lo = 0, hi = mp.nlist;  // largest list with global_begin[list] <= r
+    if (r < mp.global_begin[0]) return -1;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (mp.global_begin[mid] <= r) lo = mid; else hi = mid;
+    }
+    const long long l = mp.local_offsets[lo] + (r - mp.global_begin[lo]);
+    return l < mp.local_offsets[lo + 1] ? l : -1;
+}
+
+__global__ void k_gather_rows(const unsigned char* __restrict__ src, RowMap mp, int row_bytes,
                               const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
                               const int* __restrict__ counts, unsigned char* __restrict__ stage) {
     const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const int lane = threadIdx.x & 31;
     const long long total = (long long)nq * candidate_count;
-    const bool vec = (row_bytes % 16) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(stage)) % 16) == 0;
+    const uintptr_t both = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(stage);
+    const bool vec16 = (row_bytes % 16) == 0 && (both % 16) == 0;
+    const bool vec4 = (row_bytes % 4) == 0 && (both % 4) == 0;
     for (long long w = warp0; w < total; w += nwarps) {
         const int q = (int)(w / candidate_count), i = (int)(w % candidate_count);
         if (i >= cand_count(counts, q, candidate_count)) continue;
-        const int row = cand[(size_t)q * candidate_stride + i];
-        if (row < 0 || row >= count) continue;
+        const long long row = local_row(mp, cand[(size_t)q * candidate_stride + i]);
+        if (row < 0) continue;
         const unsigned char* s = src + (size_t)row * row_bytes;
         unsigned char* d = stage + (size_t)w * row_bytes;
-        if (vec) {
+        if (vec16) {
             const uint4* s4 = reinterpret_cast<const uint4*>(s);
             uint4* d4 = reinterpret_cast<uint4*>(d);
             for (int j = lane; j < row_bytes / 16; j += 32) d4[j] = s4[j];
-        } else if (row_bytes % 4 == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(stage)) % 4) == 0) {
+        } else if (vec4) {
             const uint32_t* s4 = reinterpret_cast<const uint32_t*>(s);
             uint32_t* d4 = reinterpret_cast<uint32_t*>(d);
             for (int j = lane; j < row_bytes / 4; j += 32) d4[j] = s4[j];
@@ -84,37 +105,54 @@ __device__ __forceinline__ float l2_u8_halfwarp(const unsigned char* __restrict_
     return (float)s;
 }
 
-constexpr int kRerankThreads = 256;
-__global__ void __launch_bounds__(kRerankThreads)
-k_rerank_select(const unsigned char* __restrict__ stage, long long count, int dim, int elem_bytes,
-                const unsigned char* __restrict__ queries, const int* __restrict__ cand, int candidate_count,
-                int candidate_stride, const int* __restrict__ counts, int topk, int np,
-                int* __restrict__ out_rows, float* __restrict__ out_dist) {
-    extern __shared__ __align__(16) unsigned char s_raw[];
-    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);                   // [np]
-    int* s_rank = reinterpret_cast<int*>(s_raw + (size_t)np * 8);            // [np]
-    unsigned char* s_q = s_raw + (size_t)np * 12;                            // [dim * elem_bytes]
-    __shared__ int s_warp[32];
-    __shared__ int s_total;
+constexpr int kScoreThreads = 256;
+// grid (nq, ceil(candidate_count / 16 half-warps)): dist[q][i] = exact distance of candidate i, +inf when the row is
+// invalid, beyond the query's count, or not held by this session.
+__global__ void __launch_bounds__(kScoreThreads)
+k_rerank_score(const unsigned char* __restrict__ stage, RowMap mp, int dim, int elem_bytes,
+               const unsigned char* __restrict__ queries, const int* __restrict__ cand, int candidate_count,
+               int candidate_stride, const int* __restrict__ counts, float* __restrict__ out_dist) {
+    extern __shared__ __align__(16) unsigned char s_q[];
     const int q = blockIdx.x;
     const int row_bytes = dim * elem_bytes;
     for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) s_q[i] = queries[(size_t)q * row_bytes + i];
     __syncthreads();
     const int n = cand_count(counts, q, candidate_count);
-    const int hw = threadIdx.x >> 4, j = threadIdx.x & 15, nhw = blockDim.x >> 4;
+    const int hw = threadIdx.x >> 4, j = threadIdx.x & 15;
     const unsigned hmask = 0xffffu << (threadIdx.x & 16);
-    for (int i = hw; i < np; i += nhw) {
+    const int i = blockIdx.y * (kScoreThreads / 16) + hw;
+    if (i >= candidate_count) return;
+    float d = __int_as_float(0x7f800000);
+    const long long row = i < n ? local_row(mp, cand[(size_t)q * candidate_stride + i]) : -1;
+    if (row >= 0) {
+        const unsigned char* v = stage + ((size_t)q * candidate_count + i) * row_bytes;
+        d = elem_bytes == 4
+            ? l2_halfwarp(reinterpret_cast<const float*>(s_q), reinterpret_cast<const float*>(v), dim, j, hmask)
+            : l2_u8_halfwarp(s_q, v, dim, j, hmask);
+    }
+    if (j == 0) out_dist[(size_t)q * candidate_count + i] = d;
+}
+
+constexpr int kSelectThreads = 256;
+// dist [nq][candidate_count] (dense), cand [nq][candidate_stride] global rows.
+__global__ void __launch_bounds__(kSelectThreads)
+k_topk_select(const float* __restrict__ dist, const int* __restrict__ cand, int candidate_count, int candidate_stride,
+              const int* __restrict__ counts, int topk, int np, int* __restrict__ out_rows, float* __restrict__ out_dist) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);         // [np]
+    int* s_rank = reinterpret_cast<int*>(s_raw + (size_t)np * 8);  // [np]
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    const int q = blockIdx.x;
+    const int n = cand_count(counts, q, candidate_count);
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
         uint64_t key = KEY_MAX;
-        int row = -1;
-        if (i < n) row = cand[(size_t)q * candidate_stride + i];
-        if (row >= 0 && row < count) {
-            const unsigned char* v = stage + ((size_t)q * candidate_count + i) * row_bytes;
-            const float d = elem_bytes == 4
-                ? l2_halfwarp(reinterpret_cast<const float*>(s_q), reinterpret_cast<const float*>(v), dim, j, hmask)
-                : l2_u8_halfwarp(s_q, v, dim, j, hmask);
-            key = make_key(d, (uint32_t)row);
+        if (i < n) {
+            const int row = cand[(size_t)q * candidate_stride + i];
+            const float d = dist[(size_t)q * candidate_count + i];
+            if (row >= 0 && d != __int_as_float(0x7f800000)) key = make_key(d, (uint32_t)row);
         }
-        if (j == 0) s_keys[i] = key;
+        s_keys[i] = key;
     }
     __syncthreads();
     block_bitonic_sort(s_keys, np);
@@ -145,12 +183,13 @@ k_rerank_select(const unsigned char* __restrict__ stage, long long count, int di
     }
 }
 
-__global__ void k_map_ids(const int* __restrict__ rows, long long n, const long long* __restrict__ reordered,
-                          long long n_vectors, long long* __restrict__ out) {
+// out[i] = original id of global row rows[i] when this session holds the row, else -1.
+__global__ void k_map_ids(const int* __restrict__ rows, long long n, const long long* __restrict__ reordered, RowMap mp,
+                          long long* __restrict__ out) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const int r = rows[i];
-    out[i] = (r >= 0 && r < n_vectors) ? reordered[r] : -1ll;
+    const long long l = local_row(mp, rows[i]);
+    out[i] = l >= 0 ? reordered[l] : -1ll;
 }
 
 __global__ void k_widen_ids(const int* __restrict__ in, long long n, long long* __restrict__ out) {
@@ -192,14 +231,14 @@ k_merge(const int* __restrict__ rows, const float* __restrict__ dist, int parts,
 
 }  // namespace
 
-psb_status launch_gather_rows(const void* src, long long count, int dim, int elem_bytes, const int* d_candidates,
+psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
                               void* d_stage, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
     const long long total = (long long)nq * candidate_count;
     long long blocks = (total * 32 + 255) / 256;
     if (blocks > 148 * 64) blocks = 148 * 64;
-    k_gather_rows<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const unsigned char*>(src), count, dim * elem_bytes,
+    k_gather_rows<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
                                                    d_candidates, nq, candidate_count, candidate_stride, d_counts,
                                                    static_cast<unsigned char*>(d_stage));
     count_launch();
@@ -207,30 +246,40 @@ psb_status launch_gather_rows(const void* src, long long count, int dim, int ele
     return PSB_OK;
 }
 
-psb_status launch_rerank_select(const void* d_stage, long long count, int dim, int elem_bytes,
-                                const void* d_queries, const int* d_candidates, int nq, int candidate_count,
-                                int candidate_stride, const int* d_counts, int topk, int* d_out_rows,
-                                float* d_out_dist, cudaStream_t s) {
+psb_status launch_rerank_score(const void* d_stage, const RowMap& mp, int dim, int elem_bytes, const void* d_queries,
+                               const int* d_candidates, int nq, int candidate_count, int candidate_stride,
+                               const int* d_counts, float* d_out_dist, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
-    if (candidate_count > kMaxRerankWidth) return fail(PSB_UNSUPPORTED_SHAPE, "rerank accepts at most 4096 candidates per query");
-    int np = 32;
-    while (np < candidate_count) np <<= 1;
-    const size_t smem = (size_t)np * 12 + (size_t)dim * elem_bytes + 16;
-    if (smem > 32 * 1024)
-        PSB_CUDA(cudaFuncSetAttribute(k_rerank_select, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_rerank_select<<<nq, kRerankThreads, smem, s>>>(static_cast<const unsigned char*>(d_stage), count, dim, elem_bytes,
-                                                     static_cast<const unsigned char*>(d_queries), d_candidates,
-                                                     candidate_count, candidate_stride, d_counts, topk, np,
-                                                     d_out_rows, d_out_dist);
+    dim3 grid(nq, (candidate_count + kScoreThreads / 16 - 1) / (kScoreThreads / 16));
+    k_rerank_score<<<grid, kScoreThreads, (size_t)dim * elem_bytes, s>>>(
+        static_cast<const unsigned char*>(d_stage), mp, dim, elem_bytes, static_cast<const unsigned char*>(d_queries),
+        d_candidates, candidate_count, candidate_stride, d_counts, d_out_dist);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
 }
 
-psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, long long n_vectors,
+psb_status launch_topk_select(const float* d_dist, const int* d_candidates, int nq, int candidate_count,
+                              int candidate_stride, const int* d_counts, int topk, int* d_out_rows,
+                              float* d_out_dist, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    if (candidate_count > kMaxRerankWidth) return fail(PSB_UNSUPPORTED_SHAPE, "rerank accepts at most 4096 candidates per query");
+    int np = 32;
+    while (np < candidate_count) np <<= 1;
+    const size_t smem = (size_t)np * 12;
+    if (smem > 32 * 1024)
+        PSB_CUDA(cudaFuncSetAttribute(k_topk_select, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_topk_select<<<nq, kSelectThreads, smem, s>>>(d_dist, d_candidates, candidate_count, candidate_stride, d_counts,
+                                                   topk, np, d_out_rows, d_out_dist);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, const RowMap& mp,
                           long long* d_out, cudaStream_t s) {
     if (n <= 0) return PSB_OK;
-    k_map_ids<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_rows, n, d_reordered, n_vectors, d_out);
+    k_map_ids<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_rows, n, d_reordered, mp, d_out);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

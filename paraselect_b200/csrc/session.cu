@@ -102,7 +102,8 @@ struct psb_session {
     int list_begin = 0, list_end = 0;
     long long row_base = 0, shard_rows = 0;
     // device copies
-    DevBuf centroids, offsets, reordered, codes, codebook;
+    DevBuf centroids, offsets, reordered, codes, codebook, global_begin, row_delta;
+    bool striped = false;          // shard holds a slice of every list (options.list_global_begin)
     // exact rows
     int exact_elem = 0;            // 4 = fp32, 1 = u8, 0 = rerank disabled
     const void* exact_host = nullptr;
@@ -114,9 +115,10 @@ struct psb_session {
     size_t pinned_bytes = 0;
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
     std::vector<int> h_cand;
+    std::vector<long long> h_global_begin, h_offsets;  // striped shards: host copies for the staged transport
     // workspaces
     DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
-        pool_cnt, pool, fail_list, scalars, cand_rows, cand_dist, cand_count, stage, out_rows, out_dist, out_ids;
+        pool_cnt, pool, fail_list, scalars, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
     int ws_batch = 0, ws_nprobe = 0, ws_stage1 = 0, ws_topk = 0;
     int pool_cap = 0;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> scan_events;  // pending (options.time_kernels)
@@ -127,7 +129,17 @@ struct psb_session {
         ScanIndex ix;
         ix.codes = codes.as<uint8_t>(); ix.offsets = offsets.as<long long>(); ix.row_base = row_base;
         ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
+        ix.row_delta = striped ? row_delta.as<long long>() : nullptr;
         return ix;
+    }
+    // Which index-wide rows the exact store and the id table of this session hold.
+    RowMap row_map() const {
+        RowMap mp;
+        if (striped) {
+            mp.global_begin = global_begin.as<long long>(); mp.local_offsets = offsets.as<long long>(); mp.nlist = nlist;
+        }
+        mp.base = 0; mp.count = n_vectors;
+        return mp;
     }
     ScanWorkspace scan_ws() const {
         ScanWorkspace w;
@@ -271,6 +283,18 @@ psb_status validate_params(const psb_session* s, const psb_query_batch_view* qv,
     return PSB_OK;
 }
 
+// Host-side twin of the device row mapping (staged transport only).
+long long host_local_row(const psb_session* s, long long r) {
+    if (r < 0) return -1;
+    if (!s->striped) return r < s->n_vectors ? r : -1;
+    const auto& gb = s->h_global_begin;
+    auto it = std::upper_bound(gb.begin(), gb.end(), r);
+    if (it == gb.begin()) return -1;
+    const size_t l = (size_t)(it - gb.begin()) - 1;
+    const long long loc = s->h_offsets[l] + (r - gb[l]);
+    return loc < s->h_offsets[l + 1] ? loc : -1;
+}
+
 // Staged rerank transport: candidate rows come back to the host, host threads gather the exact rows into two
 // pinned buffers, and cudaMemcpyAsync moves each filled buffer while the other is being filled.
 psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, int stride, const int* d_counts) {
@@ -306,7 +330,7 @@ psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, i
                 const size_t b = total * t / nthreads, e = total * (t + 1) / nthreads;
                 for (size_t i = b; i < e; ++i) {
                     const size_t q = q0 + i / width, c = i % width;
-                    const int row = s->h_cand[q * stride + c];
+                    const long long row = host_local_row(s, s->h_cand[q * stride + c]);
                     if (row >= 0 && row < s->exact_count) std::memcpy(dst + i * row_bytes, src + (size_t)row * row_bytes, row_bytes);
                 }
             });
@@ -320,7 +344,7 @@ psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, i
 }
 
 psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int* d_cand, int width, int stride,
-                       const int* d_counts, int topk, int* d_out_rows, float* d_out_dist) {
+                       const int* d_counts, int topk, int* d_out_rows, float* d_out_dist, float* d_score = nullptr) {
     if (!s->exact_elem) return fail(PSB_INVALID_ARGUMENT, "session has no exact rows for the rerank");
     if (width <= 0 || stride < width || topk <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid rerank request");
     if (width > kMaxRerankWidth || topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "rerank width above 4096 or topk above 2048");
@@ -328,11 +352,18 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
     if (s->opt.exact_mode == PSB_EXACT_HOST_STAGED) {
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
-        PSB_TRY(launch_gather_rows(s->exact_dev, s->exact_count, s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
+        PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
                                    s->stage.p, s->stream));
     }
-    return launch_rerank_select(s->stage.p, s->exact_count, s->dim, s->exact_elem, d_queries, d_cand, nq, width, stride,
-                                d_counts, topk, d_out_rows, d_out_dist, s->stream);
+    float* score = d_score;
+    if (!score) {
+        PSB_TRY(s->score.reserve(sizeof(float) * (size_t)nq * width));
+        score = s->score.as<float>();
+    }
+    PSB_TRY(launch_rerank_score(s->stage.p, s->row_map(), s->dim, s->exact_elem, d_queries, d_cand, nq, width, stride,
+                                d_counts, score, s->stream));
+    if (!d_out_rows) return PSB_OK;  // partial rerank: the caller combines the scores of all shards
+    return launch_topk_select(score, d_cand, nq, width, stride, d_counts, topk, d_out_rows, d_out_dist, s->stream);
 }
 
 }  // namespace
@@ -365,6 +396,15 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     int lb = opt.list_begin, le = opt.list_end;
     if (lb == 0 && le == 0) le = nlist;
     if (lb < 0 || le > nlist || lb > le) return fail(PSB_INVALID_ARGUMENT, "invalid list shard range");
+    const int64_t* gb = opt.list_global_begin;
+    if (gb) {
+        if (lb != 0 || le != nlist) return fail(PSB_INVALID_ARGUMENT, "list_global_begin excludes a list range");
+        for (int l = 0; l < nlist; ++l) {
+            const int64_t len = index->lists.offsets[l + 1] - index->lists.offsets[l];
+            if (gb[l] < 0 || gb[l] + len > INT_MAX || (l + 1 < nlist && gb[l] + len > gb[l + 1]))
+                return fail(PSB_INVALID_ARGUMENT, "list_global_begin must give disjoint ascending row ranges below 2^31");
+        }
+    }
     if (opt.n_rerank > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "n_rerank above 2048 is not supported");
     cudaDeviceProp prop;
     PSB_TRY(check_device(opt.device, &prop));
@@ -378,6 +418,17 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if (opt.stream) s->stream = static_cast<cudaStream_t>(opt.stream);
     else { PSB_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking)); s->own_stream = true; }
     cudaStream_t st = s->stream;
+    if (gb) {
+        s->striped = true;
+        s->h_global_begin.assign(gb, gb + nlist);
+        s->h_offsets.assign(index->lists.offsets, index->lists.offsets + nlist + 1);
+        std::vector<long long> delta((size_t)nlist);
+        for (int l = 0; l < nlist; ++l) delta[(size_t)l] = gb[l] - index->lists.offsets[l];
+        PSB_TRY(s->global_begin.reserve(sizeof(long long) * (size_t)nlist));
+        PSB_TRY(s->row_delta.reserve(sizeof(long long) * (size_t)nlist));
+        PSB_CUDA(cudaMemcpyAsync(s->global_begin.p, s->h_global_begin.data(), sizeof(long long) * (size_t)nlist, cudaMemcpyHostToDevice, st));
+        PSB_CUDA(cudaMemcpy(s->row_delta.p, delta.data(), sizeof(long long) * (size_t)nlist, cudaMemcpyHostToDevice));
+    }
     PSB_TRY(s->centroids.reserve(sizeof(float) * (size_t)nlist * s->dim));
     PSB_CUDA(cudaMemcpyAsync(s->centroids.p, index->coarse.centroids, sizeof(float) * (size_t)nlist * s->dim, cudaMemcpyHostToDevice, st));
     PSB_TRY(s->offsets.reserve(sizeof(long long) * ((size_t)nlist + 1)));
@@ -480,10 +531,28 @@ psb_status psb_stage_rerank(psb_session* s, const float* d_queries, int nq, cons
     return rerank_impl(s, d_queries, nq, d_candidates, candidate_count, candidate_stride, d_counts, topk, d_out_rows, d_out_dist);
 }
 
+psb_status psb_stage_rerank_partial(psb_session* s, const float* d_queries, int nq, const int* d_candidates,
+                                    int candidate_count, int candidate_stride, const int* d_counts, float* d_dist) {
+    if (!s || !d_queries || !d_candidates || !d_dist) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return rerank_impl(s, d_queries, nq, d_candidates, candidate_count, candidate_stride, d_counts, 1, nullptr, nullptr, d_dist);
+}
+
+psb_status psb_stage_select_topk(psb_session* s, const float* d_dist, const int* d_candidates, int nq,
+                                 int candidate_count, int candidate_stride, const int* d_counts, int topk,
+                                 int* d_out_rows, float* d_out_dist) {
+    if (!s || !d_dist || !d_candidates || !d_out_rows || !d_out_dist) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (candidate_count <= 0 || candidate_stride < candidate_count || topk <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid selection request");
+    if (topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "topk above 2048 is not supported");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_topk_select(d_dist, d_candidates, nq, candidate_count, candidate_stride, d_counts, topk, d_out_rows,
+                              d_out_dist, s->stream);
+}
+
 psb_status psb_stage_map_ids(psb_session* s, const int* d_rows, int64_t n, int64_t* d_indices) {
     if (!s || !d_rows || !d_indices) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
-    return launch_map_ids(d_rows, n, s->reordered.as<long long>(), s->n_vectors, reinterpret_cast<long long*>(d_indices), s->stream);
+    return launch_map_ids(d_rows, n, s->reordered.as<long long>(), s->row_map(), reinterpret_cast<long long*>(d_indices), s->stream);
 }
 
 psb_status psb_stage_merge(psb_session* s, const int* d_rows, const float* d_dist, int parts, int nq, int k,
@@ -571,7 +640,7 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
                                 s->out_rows.as<int>(), s->out_dist.as<float>()));
         }
         if (stats) PSB_TRY(tm.mark(st));
-        PSB_TRY(launch_map_ids(s->out_rows.as<int>(), (long long)n * topk, s->reordered.as<long long>(), s->n_vectors,
+        PSB_TRY(launch_map_ids(s->out_rows.as<int>(), (long long)n * topk, s->reordered.as<long long>(), s->row_map(),
                                s->out_ids.as<long long>(), st));
         if (stats) PSB_TRY(tm.mark(st));
         PSB_CUDA(cudaMemcpyAsync(output->indices + (size_t)q0 * topk, s->out_ids.p, sizeof(long long) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
@@ -646,10 +715,16 @@ psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* 
         PSB_CUDA(cudaMemcpy(counts.p, h_candidate_counts, sizeof(int) * (size_t)batch_n, cudaMemcpyHostToDevice));
         d_counts = counts.as<int>();
     }
-    PSB_TRY(launch_gather_rows(base.p, storage->count, dim, elem, cand.as<int>(), batch_n, candidate_count, candidate_stride,
+    RowMap mp;
+    mp.count = storage->count;
+    DevBuf score;
+    PSB_TRY(score.reserve(sizeof(float) * (size_t)batch_n * candidate_count));
+    PSB_TRY(launch_gather_rows(base.p, mp, dim, elem, cand.as<int>(), batch_n, candidate_count, candidate_stride,
                                d_counts, stage.p, st));
-    PSB_TRY(launch_rerank_select(stage.p, storage->count, dim, elem, q.p, cand.as<int>(), batch_n, candidate_count,
-                                 candidate_stride, d_counts, topk, out_rows.as<int>(), out_dist.as<float>(), st));
+    PSB_TRY(launch_rerank_score(stage.p, mp, dim, elem, q.p, cand.as<int>(), batch_n, candidate_count, candidate_stride,
+                                d_counts, score.as<float>(), st));
+    PSB_TRY(launch_topk_select(score.as<float>(), cand.as<int>(), batch_n, candidate_count, candidate_stride, d_counts,
+                               topk, out_rows.as<int>(), out_dist.as<float>(), st));
     PSB_CUDA(cudaMemcpy(h_output_ids, out_rows.p, sizeof(int) * (size_t)batch_n * topk, cudaMemcpyDeviceToHost));
     PSB_CUDA(cudaMemcpy(h_output_distances, out_dist.p, sizeof(float) * (size_t)batch_n * topk, cudaMemcpyDeviceToHost));
     return PSB_OK;

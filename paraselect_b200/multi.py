@@ -1,0 +1,297 @@
+"""Multi-GPU search: inverted lists striped across ranks, one exchange of candidates per batch.
+
+Every rank holds, for every inverted list, one contiguous slice of the list's rows (codes, exact rows and ids of
+that slice), plus replicated centroids and codebook.  Slicing every list - instead of giving each rank whole
+lists - keeps ranks balanced when list sizes are skewed (a Zipf head list would otherwise pin one rank).
+
+Per batch (`ShardedSearch.step`):
+  1. every rank: coarse (all queries, replicated centroids) -> LUT -> ADC scan of its slices -> local
+     top-stage1_k candidates, as index-wide row numbers with ADC distances
+  2. all-gather of the candidate lists, merge to the index-wide top-stage1_k (identical on every rank)
+  3. every rank scores exactly the candidates whose rows it holds (+inf elsewhere); all-reduce(min)
+  4. top-k by (distance,row) on the combined scores; ids come from the rank holding each row; all-reduce(max)
+The results are those of a single-GPU search of the whole index, bit for bit.
+
+The collective calls go through `torch.distributed` (NCCL on GPUs, gloo in the CPU tests).  The compute goes
+through an *engine*: `SessionEngine` drives the CUDA library; the CPU tests substitute their own engine to check
+this orchestration without a GPU.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+
+def stripe_layout(offsets, rank, world):
+    """Slice of every list held by `rank`: returns (global_begin [nlist], local_offsets [nlist+1]).
+
+    List l = rows [offsets[l], offsets[l+1]) is cut into `world` contiguous parts at floor(len * g / world)."""
+    offsets = np.asarray(offsets, np.int64)
+    length = offsets[1:] - offsets[:-1]
+    lo = offsets[:-1] + (length * rank) // world
+    hi = offsets[:-1] + (length * (rank + 1)) // world
+    local = np.zeros(offsets.size, np.int64)
+    local[1:] = np.cumsum(hi - lo)
+    return lo, local
+
+
+def owned_mask_rows(global_begin, local_offsets, r0, r1):
+    """Boolean mask over global rows [r0, r1): True where the row belongs to the stripe."""
+    rows = np.arange(r0, r1, dtype=np.int64)
+    l = np.searchsorted(global_begin, rows, side="right") - 1
+    ok = l >= 0
+    lc = np.clip(l, 0, None)
+    ok &= rows < global_begin[lc] + (local_offsets[lc + 1] - local_offsets[lc])
+    return ok
+
+
+class SessionEngine:
+    """The CUDA library as the compute engine of ShardedSearch (device tensors are torch CUDA tensors)."""
+
+    def __init__(self, session, torch):
+        self.s = session
+        self.torch = torch
+
+    def empty(self, shape, dtype):
+        return self.torch.empty(shape, dtype=dtype, device="cuda")
+
+    def coarse(self, dq, nq, nprobe, out):
+        self.s.stage_coarse(dq, nq, nprobe, out)
+
+    def lut(self, dq, nq, out):
+        self.s.stage_build_lut(dq, nq, out)
+
+    def scan(self, lut, nq, probes, nprobe, width, rows, dist, count):
+        self.s.stage_scan(lut, nq, probes, nprobe, width, rows, dist, count)
+
+    def merge(self, rows, dist, parts, nq, width, out_rows, out_dist):
+        self.s.stage_merge(rows, dist, parts, nq, width, out_rows, out_dist)
+
+    def rerank_partial(self, dq, nq, cand, width, out_dist):
+        self.s.stage_rerank_partial(dq, nq, cand, width, width, None, out_dist)
+
+    def select_topk(self, dist, cand, nq, width, topk, out_rows, out_dist):
+        self.s.stage_select_topk(dist, cand, nq, width, width, None, topk, out_rows, out_dist)
+
+    def map_ids(self, rows, n, out):
+        self.s.stage_map_ids(rows, n, out)
+
+
+class ShardedSearch:
+    def __init__(self, engine, dist, world, nq, dim, M, K, nprobe, topk, width, torch, rerank=True):
+        self.e, self.dist, self.world, self.torch = engine, dist, world, torch
+        self.nq, self.nprobe, self.topk, self.width, self.rerank = nq, nprobe, topk, width, rerank
+        t = torch
+        self.probes = engine.empty((nq, nprobe), t.int32)
+        self.lut = engine.empty((nq, M, K), t.float32)
+        self.l_rows = engine.empty((nq, width), t.int32)
+        self.l_dist = engine.empty((nq, width), t.float32)
+        self.l_cnt = engine.empty((nq,), t.int32)
+        self.g_rows = engine.empty((world, nq, width), t.int32)
+        self.g_dist = engine.empty((world, nq, width), t.float32)
+        self.m_rows = engine.empty((nq, width), t.int32)
+        self.m_dist = engine.empty((nq, width), t.float32)
+        self.p_dist = engine.empty((nq, width), t.float32)
+        self.o_rows = engine.empty((nq, topk), t.int32)
+        self.o_dist = engine.empty((nq, topk), t.float32)
+        self.o_ids = engine.empty((nq, topk), t.int64)
+
+    def step(self, dq):
+        e, d, nq = self.e, self.dist, self.nq
+        e.coarse(dq, nq, self.nprobe, self.probes)
+        e.lut(dq, nq, self.lut)
+        e.scan(self.lut, nq, self.probes, self.nprobe, self.width, self.l_rows, self.l_dist, self.l_cnt)
+        self._sync_to_collectives()
+        if self.world > 1:
+            d.all_gather_into_tensor(self.g_rows.view(self.world * nq, self.width), self.l_rows)
+            d.all_gather_into_tensor(self.g_dist.view(self.world * nq, self.width), self.l_dist)
+            self._sync_from_collectives()
+            e.merge(self.g_rows, self.g_dist, self.world, nq, self.width, self.m_rows, self.m_dist)
+        else:
+            self.m_rows, self.m_dist = self.l_rows, self.l_dist
+        if self.rerank:
+            e.rerank_partial(dq, nq, self.m_rows, self.width, self.p_dist)
+            self._sync_to_collectives()
+            if self.world > 1:
+                d.all_reduce(self.p_dist, op=d.ReduceOp.MIN)
+                self._sync_from_collectives()
+            e.select_topk(self.p_dist, self.m_rows, nq, self.width, self.topk, self.o_rows, self.o_dist)
+        else:
+            self.o_rows.copy_(self.m_rows[:, :self.topk])
+            self.o_dist.copy_(self.m_dist[:, :self.topk])
+        e.map_ids(self.o_rows, nq * self.topk, self.o_ids)
+        self._sync_to_collectives()
+        if self.world > 1:
+            d.all_reduce(self.o_ids, op=d.ReduceOp.MAX)
+            self._sync_from_collectives()
+        return self.o_ids, self.o_dist
+
+    # The engine and torch.distributed are driven from one stream (the bench makes it torch's current stream), so
+    # stream order already serialises kernels and collectives; these hooks exist for engines that need more.
+    def _sync_to_collectives(self):
+        pass
+
+    def _sync_from_collectives(self):
+        pass
+
+
+def bench_main(args, cfg, rank, world, local_rank):
+    """`bench.py --gpus N` for N > 1 (one process per GPU under torchrun)."""
+    import torch
+    import torch.distributed as dist
+    from . import api
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench as B
+
+    device = local_rank
+    n, dim, nlist, M = cfg["n"], cfg["dim"], cfg["nlist"], cfg["M"]
+    nq, nprobe, topk, R = cfg["nq"], cfg["nprobe"], cfg["topk"], cfg["n_rerank"]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        w, offsets = B.populations(n, nlist, cfg["zipf"])
+        gb, loff = stripe_layout(offsets, rank, world)
+        t0 = time.time()
+        index, centres = build_stripe(cfg, torch, api, device, offsets, gb, loff)
+        B.log("rank 0 stripe built in %.1fs (%d rows)" % (time.time() - t0, index["codes"].shape[0]))
+        dq = B.make_queries(cfg, torch, api, centres, w, device)
+        q_pinned = torch.empty((nq, dim), dtype=torch.float32).pin_memory()
+        q_pinned.copy_(dq)
+        torch.cuda.synchronize()
+        sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
+                           list_global_begin=gb)
+        width = min(R, n) if R > topk else topk
+        search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
+                               rerank=R > topk)
+        for _ in range(max(args.warmup, 3)):
+            search.step(dq)
+        torch.cuda.synchronize()
+        sess.counters(reset=True)
+        sampler = B.ClockSampler(local_rank)
+        sampler.start()
+
+        def timed(fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(args.steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device="cuda")
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item())
+
+        ms_dev = timed(lambda: search.step(dq))
+        c = sess.counters(reset=True)
+        out_ids = torch.empty((nq, topk), dtype=torch.int64).pin_memory()
+        out_dist = torch.empty((nq, topk), dtype=torch.float32).pin_memory()
+        dq2 = torch.empty_like(dq)
+
+        def e2e_step():
+            dq2.copy_(q_pinned, non_blocking=True)
+            ids, dd = search.step(dq2)
+            out_ids.copy_(ids, non_blocking=True)
+            out_dist.copy_(dd, non_blocking=True)
+            stream.synchronize()
+
+        e2e_step()
+        ms_e2e = timed(e2e_step)
+        clocks = sampler.stop()
+        torch.cuda.synchronize()
+        # totals over ranks
+        tot = torch.tensor([float(c["pq_scanned_codes"]), float(c["scan_kernel_ms"]), float(c["scan_kernel_launches"]),
+                            float(c["kernel_launches"]), float(c["fallback_queries"])], dtype=torch.float64, device="cuda")
+        mx = tot.clone()
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        ids_np = out_ids.numpy()
+        checksum = int(np.bitwise_xor.reduce((ids_np.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel()) & np.uint64((1 << 62) - 1))
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(B.ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        S = tot[0].item() / max(1, args.steps)                      # rows scanned per step, all ranks
+        scan_ms = mx[1].item() / max(1.0, mx[2].item())             # slowest rank's scan kernel, per launch
+        achieved = S * M / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+        line = dict(
+            metric="QPS (IVF-PQ search, recall@k equal to the reference CPU path)", value=round(nq / (ms_dev * 1e-3), 1),
+            unit="queries/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
+            higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+            config=dict(workload=args.workload, desc=cfg["desc"], rows=n, dim=dim, nlist=nlist, M=M, batch=nq, nprobe=nprobe,
+                        topk=topk, n_rerank=R, exact_rows="host-mapped fp32", sharding="every list striped over %d ranks" % world,
+                        l2="inputs larger than L2 (codes %.2f GB per rank)" % (index["codes"].nbytes / 1e9)),
+            e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
+                     h2d_bytes_per_step=int(nq * dim * 4), d2h_bytes_per_step=int(nq * topk * 12),
+                     pcie_gather_bytes_per_step=int(nq * width * dim * 4) if R > topk else 0),
+            gpu_launches=int(tot[3].item()),
+            roofline=dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak * world, unit="GB/s",
+                          frac=round(achieved / (peak * world), 4), peak_source="measured" if peaks else "fallback",
+                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3), traffic=None,
+                          note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
+            counters=dict(scanned_codes_per_step=int(S), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
+            result_checksum=checksum, clocks=clocks)
+        print(json.dumps(line), flush=True)
+    sess.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+def build_stripe(cfg, torch, api, device, offsets, gb, loff):
+    """Generates the whole synthetic base chunk by chunk on this rank's GPU and keeps the rows of its stripe."""
+    import bench as B
+    n, dim, nlist, M, seed = cfg["n"], cfg["dim"], cfg["nlist"], cfg["M"], cfg["seed"]
+    d_off = torch.from_numpy(offsets).cuda()
+    centres = torch.empty((nlist, dim), dtype=torch.float32, device="cuda")
+    api.gen_normal(seed * 1000 + 1, 0, nlist * dim, 1.0, centres, device=device)
+    blocks, per = 64, min(16384, max(1, n // 64))
+    sample = torch.empty((blocks * per, dim), dtype=torch.float32, device="cuda")
+    for b in range(blocks):
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, (n // blocks) * b, per,
+                             sample[b * per:], device=device)
+    codebook = torch.empty((M, 256, dim // M), dtype=torch.float32, device="cuda")
+    api.pq_train(sample, blocks * per, dim, M, 256, 8, seed * 1000 + 3, codebook, device=device)
+    del sample
+    rows = int(loff[-1])
+    vectors = np.empty((rows, dim), np.float32)
+    codes = np.empty((rows, M), np.uint8)
+    ids = np.empty(rows, np.int64)
+    a = B.coprime_multiplier(n)
+    d_gb = torch.from_numpy(gb).cuda()
+    d_len = torch.from_numpy(loff[1:] - loff[:-1]).cuda()
+    chunk = 2_000_000
+    buf = torch.empty((chunk, dim), dtype=torch.float32, device="cuda")
+    cbuf = torch.empty((chunk, M), dtype=torch.uint8, device="cuda")
+    at = 0
+    for r0 in range(0, n, chunk):
+        m = min(chunk, n - r0)
+        g = torch.arange(r0, r0 + m, dtype=torch.int64, device="cuda")
+        l = torch.searchsorted(d_gb, g, right=True) - 1
+        lc = l.clamp(min=0)
+        own = (l >= 0) & (g < d_gb[lc] + d_len[lc])
+        sel = torch.nonzero(own).squeeze(1)
+        k = int(sel.numel())
+        if k == 0:
+            continue
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, m, buf, device=device)
+        mine = buf[:m].index_select(0, sel)
+        api.pq_encode(mine, k, dim, codebook, M, 256, cbuf, device=device)
+        torch.cuda.synchronize()
+        torch.from_numpy(vectors[at:at + k]).copy_(mine)
+        torch.from_numpy(codes[at:at + k]).copy_(cbuf[:k])
+        ids[at:at + k] = ((sel.cpu().numpy() + r0) * a + 12345) % n
+        at += k
+    assert at == rows, (at, rows)
+    index = dict(centroids=centres.cpu().numpy(), offsets=loff, reordered_ids=ids, codes=codes,
+                 codebook=codebook.cpu().numpy(), vectors=vectors, nlist=nlist)
+    return index, centres

@@ -1,0 +1,99 @@
+"""TEST INFRASTRUCTURE: a CPU stand-in for the CUDA engine of paraselect_b200.multi.ShardedSearch, built on the
+CPU checker.  It lets the multi-rank orchestration (striping, candidate exchange, partial rerank, id ownership)
+run as gloo ranks without a GPU.  Tensors are torch CPU tensors."""
+import numpy as np
+import torch
+
+import oracle
+
+INF = np.float32(np.inf)
+FLT_MAX = np.finfo(np.float32).max
+
+
+class CpuCheckerEngine:
+    def __init__(self, index, global_begin):
+        self.ix = index                      # local (striped) index: offsets are local
+        self.gb = np.asarray(global_begin, np.int64)
+        self.loff = np.asarray(index["offsets"], np.int64)
+        self.q = None
+
+    def empty(self, shape, dtype):
+        return torch.zeros(shape, dtype=dtype)
+
+    def _local(self, rows):
+        rows = np.asarray(rows, np.int64)
+        l = np.searchsorted(self.gb, rows, side="right") - 1
+        lc = np.clip(l, 0, None)
+        loc = self.loff[lc] + (rows - self.gb[lc])
+        ok = (rows >= 0) & (l >= 0) & (loc < self.loff[lc + 1])
+        return np.where(ok, loc, -1)
+
+    def coarse(self, dq, nq, nprobe, out):
+        self.q = dq.numpy()
+        ids, _ = oracle.coarse(self.q, self.ix["centroids"], nprobe)
+        out.copy_(torch.from_numpy(ids.astype(np.int32)))
+
+    def lut(self, dq, nq, out):
+        out.copy_(torch.from_numpy(oracle.pq_lut(dq.numpy(), self.ix["codebook"])))
+
+    def scan(self, lut, nq, probes, nprobe, width, rows, dist, count):
+        r, d, c, _ = oracle.pq_scan(self.q, probes.numpy().astype(np.int64), self.loff, self.ix["codes"],
+                                    self.ix["codebook"], width)
+        # local rows -> index-wide rows; the checker orders ties by local row, which is monotone in the global row
+        lists = np.searchsorted(self.loff, np.clip(r, 0, None), side="right") - 1
+        g = np.where(r >= 0, r + (self.gb[lists] - self.loff[lists]), -1)
+        rows.copy_(torch.from_numpy(g.astype(np.int32)))
+        dist.copy_(torch.from_numpy(d))
+        count.copy_(torch.from_numpy(c))
+
+    def merge(self, rows, dist, parts, nq, width, out_rows, out_dist):
+        r = rows.numpy().transpose(1, 0, 2).reshape(nq, parts * width)
+        d = dist.numpy().transpose(1, 0, 2).reshape(nq, parts * width)
+        o_r = np.full((nq, width), -1, np.int32)
+        o_d = np.full((nq, width), FLT_MAX, np.float32)
+        for q in range(nq):
+            ok = r[q] >= 0
+            order = np.lexsort((r[q][ok], d[q][ok]))[:width]
+            o_r[q, :order.size] = r[q][ok][order]
+            o_d[q, :order.size] = d[q][ok][order]
+        out_rows.copy_(torch.from_numpy(o_r))
+        out_dist.copy_(torch.from_numpy(o_d))
+
+    def rerank_partial(self, dq, nq, cand, width, out_dist):
+        q = dq.numpy()
+        c = cand.numpy()
+        loc = self._local(c)
+        out = np.full((nq, width), INF, np.float32)
+        for i in range(nq):
+            for j in range(width):
+                if loc[i, j] >= 0:
+                    out[i, j] = oracle.l2_exact(q[i], self.ix["vectors"][loc[i, j]])
+        out_dist.copy_(torch.from_numpy(out))
+
+    def select_topk(self, dist, cand, nq, width, topk, out_rows, out_dist):
+        d, c = dist.numpy(), cand.numpy()
+        o_r = np.full((nq, topk), -1, np.int32)
+        o_d = np.full((nq, topk), FLT_MAX, np.float32)
+        for q in range(nq):
+            ok = (c[q] >= 0) & np.isfinite(d[q])
+            pairs = sorted(set(zip(d[q][ok].tolist(), c[q][ok].tolist())))[:topk]
+            for k, (dd, rr) in enumerate(pairs):
+                o_r[q, k], o_d[q, k] = rr, np.float32(dd)
+        out_rows.copy_(torch.from_numpy(o_r))
+        out_dist.copy_(torch.from_numpy(o_d))
+
+    def map_ids(self, rows, n, out):
+        loc = self._local(rows.numpy().reshape(-1))
+        ids = np.where(loc >= 0, self.ix["reordered_ids"][np.clip(loc, 0, None)], -1)
+        out.copy_(torch.from_numpy(ids.reshape(out.shape).astype(np.int64)))
+
+
+def stripe_index(ix, rank, world):
+    """Local (striped) view of a whole synthetic index for `rank`."""
+    from paraselect_b200.multi import stripe_layout
+    gb, loff = stripe_layout(ix["offsets"], rank, world)
+    keep = np.concatenate([np.arange(gb[l], gb[l] + (loff[l + 1] - loff[l])) for l in range(gb.size)]).astype(np.int64)
+    local = dict(ix)
+    local.update(offsets=loff, reordered_ids=ix["reordered_ids"][keep], codes=ix["codes"][keep],
+                 vectors=None if ix.get("vectors") is None else ix["vectors"][keep])
+    return local, gb

@@ -1,0 +1,40 @@
+"""Worker of tests/test_multi_cpu.py: one gloo rank of the sharded search with the CPU checker as engine."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import oracle  # noqa: E402
+import synth  # noqa: E402
+from fake_engine import CpuCheckerEngine, stripe_index  # noqa: E402
+from paraselect_b200.multi import ShardedSearch  # noqa: E402
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ix = synth.make_index(6000, 32, 12, 8, seed=77, zipf=True)
+    q = synth.make_queries(ix, 16, seed=78, weights=synth.zipf_weights(12))
+    nprobe, topk, width = 5, 7, 40
+    local, gb = stripe_index(ix, rank, world)
+    eng = CpuCheckerEngine(local, gb)
+    s = ShardedSearch(eng, dist, world, q.shape[0], 32, 8, 256, nprobe, topk, width, torch, rerank=True)
+    ids, dd = s.step(torch.from_numpy(q))
+    want = oracle.ivfpq_search(ix, q, nprobe, topk, width)
+    ok = np.array_equal(ids.numpy(), want["indices"]) and np.array_equal(dd.numpy(), want["distances"])
+    flag = torch.tensor([1 if ok else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    if rank == 0:
+        print("MULTI_OK" if int(flag.item()) == 1 else "MULTI_MISMATCH")
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -293,3 +293,54 @@ def test_generators_are_deterministic_and_gaussian(psb):
     assert torch.equal(a[1 << 19:], b[: 1 << 19])  # counter-based: independent of the launch shape
     assert abs(float(a.mean())) < 5e-3 and abs(float(a.std()) - 1.0) < 5e-3
     assert abs(float((a ** 4).mean()) - 3.0) < 0.05
+
+
+# ---------------------------------------------------------------------------------------------- striped shards
+def test_striped_shards_reproduce_the_whole_index_search(psb):
+    """Three striped shard sessions on one GPU, combined the way the ranks of a multi-GPU run combine them
+    (candidate merge, elementwise-min of partial rerank scores, max of partial ids)."""
+    torch = _torch()
+    from fake_engine import stripe_index
+    ix = synth.make_index(40000, 64, 24, 16, seed=55, zipf=True)
+    q = synth.make_queries(ix, 32, seed=56, weights=synth.zipf_weights(24))
+    nq, nprobe, topk, width, world = 32, 6, 10, 200, 3
+    want = oracle.ivfpq_search(ix, q, nprobe, topk, width)
+    dq = dev(q)
+    sessions = []
+    for r in range(world):
+        local, gb = stripe_index(ix, r, world)
+        sessions.append(psb.Session(local, n_rerank=width, list_global_begin=gb))
+    rows = torch.empty((world, nq, width), dtype=torch.int32, device="cuda")
+    dist = torch.empty((world, nq, width), dtype=torch.float32, device="cuda")
+    for r, s in enumerate(sessions):
+        probes = torch.empty((nq, nprobe), dtype=torch.int32, device="cuda")
+        lut = torch.empty((nq, s.M, s.K), dtype=torch.float32, device="cuda")
+        cnt = torch.empty((nq,), dtype=torch.int32, device="cuda")
+        s.stage_coarse(dq, nq, nprobe, probes)
+        s.stage_build_lut(dq, nq, lut)
+        s.stage_scan(lut, nq, probes, nprobe, width, rows[r], dist[r], cnt)
+        s.sync()
+    m_rows = torch.empty((nq, width), dtype=torch.int32, device="cuda")
+    m_dist = torch.empty((nq, width), dtype=torch.float32, device="cuda")
+    sessions[0].stage_merge(rows, dist, world, nq, width, m_rows, m_dist)
+    sessions[0].sync()
+    assert np.array_equal(m_rows.cpu().numpy(), want["stage1"])
+    part = torch.empty((world, nq, width), dtype=torch.float32, device="cuda")
+    for r, s in enumerate(sessions):
+        s.stage_rerank_partial(dq, nq, m_rows, width, width, None, part[r])
+        s.sync()
+    finite = torch.isfinite(part).sum(0)
+    assert int(finite.max()) == 1 and int(finite.min()) == 1  # every candidate row is held by exactly one shard
+    comb = part.min(0).values.contiguous()
+    o_rows = torch.empty((nq, topk), dtype=torch.int32, device="cuda")
+    o_dist = torch.empty((nq, topk), dtype=torch.float32, device="cuda")
+    sessions[1].stage_select_topk(comb, m_rows, nq, width, width, None, topk, o_rows, o_dist)
+    ids = torch.empty((world, nq, topk), dtype=torch.int64, device="cuda")
+    for r, s in enumerate(sessions):
+        s.stage_map_ids(o_rows, nq * topk, ids[r])
+        s.sync()
+    sessions[1].sync()
+    assert np.array_equal(ids.max(0).values.cpu().numpy(), want["indices"])
+    assert np.array_equal(o_dist.cpu().numpy(), want["distances"])
+    for s in sessions:
+        s.close()
