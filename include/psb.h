@@ -132,7 +132,9 @@ typedef struct psb_options {
                            NULL = the view is the whole index. */
     int coarse_mode;    /* 0 = auto, 1 = exact SIMT kernel only, 2 = tensor-core filter + exact refinement */
     int time_kernels;   /* 1 = bracket the ADC scan kernel with CUDA events (read back by psb_session_counters) */
-    int reserved[6];
+    int scan_mode;      /* 0 = auto (fp16 pre-filter scan with exact fp32 re-scoring when it fits), 1 = fp32 scan only;
+                           both give identical results */
+    int reserved[5];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's

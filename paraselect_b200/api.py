@@ -71,7 +71,7 @@ class Options(C.Structure):
     _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
                 ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("list_global_begin", C.c_void_p),
                 ("coarse_mode", C.c_int),
-                ("time_kernels", C.c_int), ("reserved", C.c_int * 6)]
+                ("time_kernels", C.c_int), ("scan_mode", C.c_int), ("reserved", C.c_int * 5)]
 
 
 class Stats(C.Structure):
@@ -140,7 +140,7 @@ class Session:
     """
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
-                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None):
+                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -172,7 +172,7 @@ class Session:
         self._keep.append(gb)
         opt = Options(list_global_begin=_p(gb), device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
-                      time_kernels=int(time_kernels))
+                      time_kernels=int(time_kernels), scan_mode=scan_mode)
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 

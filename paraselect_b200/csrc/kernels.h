@@ -58,6 +58,9 @@ struct ScanWorkspace {
     unsigned long long* work_cursor; // [1]
     unsigned long long* counters;    // [4]: scanned rows, admitted, fallback queries, status
     int pool_cap;
+    void* lut_h = nullptr;       // [max_batch][m*k] fp16 tables for the half pre-filter scan (null = fp32 scan only)
+    float* lut_scale = nullptr;  // [max_batch]
+    int scan_mode = 0;           // 0 = half pre-filter when it fits, 1 = fp32 scan
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;  // optional: bracket the scan kernel
 };
 

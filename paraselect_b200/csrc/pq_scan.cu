@@ -17,6 +17,8 @@
 // Arithmetic matches the CPU path bit for bit: table entries are the sequential non-fused fp32 sum of
 // (q-c)^2 and ADC distances are the sequential fp32 sum over m = 0..M-1
 // (reference: src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:51-63,76-80).
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -499,6 +501,261 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
     }
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Half-precision pre-filter variant of the scan: 8 visitors per work item.
+//
+// The 8 visitors' tables sit in shared memory as fp16, interleaved [m][code][8 visitors] = 16 bytes per entry, so one
+// LDS.128 fetches 8 table entries and four HADD2 accumulate them.  The fp16 sum only decides which (row, visitor)
+// pairs CAN be below the visitor's cutoff; those few are re-scored exactly (sequential fp32 sum from the fp32 table
+// in global memory) before they are admitted, so the pools - and everything downstream - are identical to the
+// fp32 kernel's.  No pair with exact distance <= cutoff is dropped:
+//   table entries are e = RD_half(lut * s) (rounded toward -inf, s a power of two chosen so that no sum overflows),
+//   half sums round to nearest: S~ <= (sum e)(1+2^-11)^(M-1) <= s * D * (1 + M * 2^-11 + 1e-4)   (D = exact fp32 sum),
+//   so D <= cutoff implies S~ <= T := RU_half(cutoff * s * (1 + M * 2^-11 + 1e-4)); the kernel keeps pairs with S~ <= T.
+
+constexpr int kHalfGroup = 8;
+constexpr int kQueuePerWarp = 64;
+
+// Per query: scale s (power of two) with sum_m max_c lut[m][c] * s <= 30000, and the fp16 table RD_half(lut * s).
+__global__ void k_lut_to_half(const float* __restrict__ lut, int m, int k, __half* __restrict__ lut_h,
+                              float* __restrict__ scale_out) {
+    __shared__ unsigned int s_max[64 + 1];
+    __shared__ float s_scale;
+    const int q = blockIdx.x;
+    const int mk = m * k;
+    for (int i = threadIdx.x; i < m; i += blockDim.x) s_max[i] = 0u;
+    __syncthreads();
+    for (int e = threadIdx.x; e < mk; e += blockDim.x) {
+        const float v = lut[(size_t)q * mk + e];
+        atomicMax(&s_max[e / k], __float_as_uint(v > 0.0f ? v : 0.0f));  // non-negative floats order like their bits
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float u = 0.0f;
+        for (int i = 0; i < m; ++i) u += __uint_as_float(s_max[i]);
+        int ex = 0;
+        if (u > 0.0f && u < 3.0e38f) ex = (int)floorf(log2f(30000.0f / u));
+        ex = ex < -40 ? -40 : (ex > 40 ? 40 : ex);
+        float sc = exp2f((float)ex);
+        while (u * sc > 30000.0f) sc *= 0.5f;  // guard against log2f rounding
+        s_scale = sc;
+        scale_out[q] = sc;
+    }
+    __syncthreads();
+    const float sc = s_scale;
+    for (int e = threadIdx.x; e < mk; e += blockDim.x)
+        lut_h[(size_t)q * mk + e] = __float2half_rd(lut[(size_t)q * mk + e] * sc);
+}
+
+struct ScanArgsH {
+    ScanArgs a;
+    const __half* lut_h;   // [nq][m*k]
+    const float* scale;    // [nq]
+};
+
+template <int M>
+__global__ void __launch_bounds__(kScanThreads, 1) k_scan_h(const ScanArgsH ah) {
+    const ScanArgs& a = ah.a;
+    constexpr int V = kHalfGroup;
+    extern __shared__ __align__(16) unsigned char s_raw_h[];
+    uint4* s_lut = reinterpret_cast<uint4*>(s_raw_h);  // [m*k] entries of 8 halves
+    const int mk = a.m * a.k;
+    unsigned long long* s_queue = reinterpret_cast<unsigned long long*>(s_raw_h + (size_t)mk * 16);  // [warps][kQueuePerWarp]
+    __shared__ long long s_item;
+    __shared__ int s_list, s_vq[V];
+    __shared__ float s_thr[V], s_T[V];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned long long* queue = s_queue + warp * kQueuePerWarp;
+    const long long total = a.item_off[a.nlist];
+    const float slack = 1.0f + (float)a.m * (1.0f / 2048.0f) + 1e-4f;
+
+    // Exact re-score of one queued (row, visitor) pair and admission into the visitor's pool.
+    auto rescore = [&](unsigned long long entry, long long delta) {
+        const long long r = (long long)(entry >> 3);
+        const int v = (int)(entry & 7);
+        const int q = s_vq[v];
+        const float* lq = a.lut + (size_t)q * mk;
+        const uint8_t* row = a.codes + (size_t)(r - a.row_base) * a.m;
+        float d = 0.0f;
+        if constexpr (M % 16 == 0) {
+            const uint4* p = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+            for (int w = 0; w < M / 16; ++w) {
+                const uint4 c = __ldg(p + w);
+                const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    d = __fadd_rn(d, __ldg(lq + (w * 16 + j) * a.k + (int)((cw[j >> 2] >> ((j & 3) * 8)) & 255)));
+            }
+        } else {
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
+#pragma unroll
+            for (int w = 0; w < M / 4; ++w) {
+                const uint32_t c = __ldg(p + w);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) d = __fadd_rn(d, __ldg(lq + (w * 4 + j) * a.k + (int)((c >> (j * 8)) & 255)));
+            }
+        }
+        if (d <= s_thr[v]) {
+            const int slot = atomicAdd(&a.pool_cnt[q], 1);
+            if (slot < a.pool_cap) a.pool[(size_t)q * a.pool_cap + slot] = make_key(d, (uint32_t)(r + delta));
+        }
+    };
+
+    for (;;) {
+        __syncthreads();  // previous item fully consumed
+        if (threadIdx.x < 32) {
+            long long item = 0;
+            if (threadIdx.x == 0) item = (long long)atomicAdd(a.work_cursor, 1ull);
+            item = __shfl_sync(0xffffffffu, item, 0);
+            int l = -1;
+            if (item < total) l = find_list(a.item_off, a.nlist, item);
+            if (threadIdx.x == 0) { s_item = item; s_list = l; }
+        }
+        __syncthreads();
+        const long long item = s_item;
+        if (item >= total) break;
+        const int l = s_list;
+        const int nvis = a.vis_count[l];
+        const int ngroups = (nvis + V - 1) / V;
+        const long long local = item - a.item_off[l];
+        const int group = (int)(local % ngroups);
+        const long long chunk = local / ngroups;
+        if (threadIdx.x < V) {
+            const int vi = group * V + threadIdx.x;
+            const int q = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;
+            s_vq[threadIdx.x] = q;
+            float t = -1.0f, T = -1.0f;  // padding visitors admit nothing
+            if (q >= 0) {
+                t = a.thr[q];
+                T = __half2float(__float2half_ru(t * ah.scale[q] * slack));  // +inf stays +inf
+            }
+            s_thr[threadIdx.x] = t;
+            s_T[threadIdx.x] = T;
+        }
+        __syncthreads();
+        float T[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) T[v] = s_T[v];
+        // stage the 8 fp16 tables, two consecutive entries per thread and round
+        {
+            const int q0 = s_vq[0];
+            const __half2* src[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+                src[v] = reinterpret_cast<const __half2*>(ah.lut_h + (size_t)(s_vq[v] >= 0 ? s_vq[v] : q0) * mk);
+            for (int e2 = threadIdx.x; e2 < mk / 2; e2 += kScanThreads) {
+                uint32_t w[V];
+#pragma unroll
+                for (int v = 0; v < V; ++v) w[v] = __ldg(reinterpret_cast<const unsigned int*>(src[v] + e2));
+                uint4 lo, hi;  // entry 2*e2 takes the low halves, entry 2*e2+1 the high halves
+                lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+                lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+                lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+                lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+                s_lut[2 * e2] = lo;
+                s_lut[2 * e2 + 1] = hi;
+            }
+        }
+        __syncthreads();
+        const long long delta = a.row_delta ? a.row_delta[l] : 0;
+        const long long r0 = a.offsets[l] + chunk * a.chunk_rows;
+        const long long r1 = min(r0 + a.chunk_rows, a.offsets[l + 1]);
+        int qcount = 0;  // warp-uniform
+        for (long long base = r0 + warp * 32; base < r1; base += kScanThreads) {
+            const long long r = base + lane;
+            const bool valid = r < r1;
+            const uint8_t* row = a.codes + (size_t)((valid ? r : r0) - a.row_base) * a.m;
+            __half2 acc[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] = __float2half2_rn(0.0f);
+            if constexpr (M % 16 == 0) {
+                const uint4* p = reinterpret_cast<const uint4*>(row);
+                uint4 c[M / 16];
+#pragma unroll
+                for (int w = 0; w < M / 16; ++w) c[w] = __ldg(p + w);
+#pragma unroll
+                for (int w = 0; w < M / 16; ++w) {
+                    const uint32_t cw[4] = {c[w].x, c[w].y, c[w].z, c[w].w};
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const uint4 x = s_lut[(w * 16 + j) * a.k + (int)((cw[j >> 2] >> ((j & 3) * 8)) & 255)];
+                        acc[0] = __hadd2(acc[0], *reinterpret_cast<const __half2*>(&x.x));
+                        acc[1] = __hadd2(acc[1], *reinterpret_cast<const __half2*>(&x.y));
+                        acc[2] = __hadd2(acc[2], *reinterpret_cast<const __half2*>(&x.z));
+                        acc[3] = __hadd2(acc[3], *reinterpret_cast<const __half2*>(&x.w));
+                    }
+                }
+            } else {
+                const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
+                uint32_t c[M / 4];
+#pragma unroll
+                for (int w = 0; w < M / 4; ++w) c[w] = __ldg(p + w);
+#pragma unroll
+                for (int w = 0; w < M / 4; ++w)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 x = s_lut[(w * 4 + j) * a.k + (int)((c[w] >> (j * 8)) & 255)];
+                        acc[0] = __hadd2(acc[0], *reinterpret_cast<const __half2*>(&x.x));
+                        acc[1] = __hadd2(acc[1], *reinterpret_cast<const __half2*>(&x.y));
+                        acc[2] = __hadd2(acc[2], *reinterpret_cast<const __half2*>(&x.z));
+                        acc[3] = __hadd2(acc[3], *reinterpret_cast<const __half2*>(&x.w));
+                    }
+            }
+            float f[V];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 t = __half22float2(acc[i]);
+                f[2 * i] = t.x; f[2 * i + 1] = t.y;
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const bool pass = valid && f[v] <= T[v];
+                const unsigned bal = __ballot_sync(0xffffffffu, pass);
+                if (bal) {
+                    if (pass) queue[qcount + __popc(bal & ((1u << lane) - 1u))] = ((unsigned long long)r << 3) | (unsigned)v;
+                    qcount += __popc(bal);
+                    __syncwarp();
+                    if (qcount >= 32) {
+                        rescore(queue[lane], delta);
+                        const unsigned long long moved = (32 + lane < qcount) ? queue[32 + lane] : 0ull;
+                        __syncwarp();
+                        if (32 + lane < qcount) queue[lane] = moved;
+                        qcount -= 32;
+                        __syncwarp();
+                    }
+                }
+            }
+        }
+        if (lane < qcount) rescore(queue[lane], delta);
+        __syncwarp();
+    }
+}
+
+template <int M>
+psb_status run_scan_h(const ScanArgsH& ah, int sm_count, cudaStream_t s) {
+    if constexpr (M <= 0 || M % 4 != 0) {
+        return fail(PSB_INTERNAL, "half scan needs a templated M");
+    } else {
+        const size_t smem = (size_t)ah.a.m * ah.a.k * 16 + (size_t)(kScanThreads / 32) * kQueuePerWarp * 8;
+        if (smem > 32 * 1024)
+            PSB_CUDA(cudaFuncSetAttribute(k_scan_h<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int occ = 0;
+        PSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_scan_h<M>, kScanThreads, smem));
+        if (occ < 1) return fail(PSB_UNSUPPORTED_SHAPE, "half scan kernel does not fit an SM");
+        k_scan_h<M><<<sm_count * occ, kScanThreads, smem, s>>>(ah);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+        return PSB_OK;
+    }
+}
+
+// The half pre-filter needs a templated M (a multiple of 4), K even, and 8 tables + queues within shared memory.
+bool half_scan_fits(int m, int k) {
+    const bool templated = m == 8 || m == 16 || m == 20 || m == 32 || m == 48 || m == 64;
+    return templated && (k % 2 == 0) && (size_t)m * k * 16 + (kScanThreads / 32) * kQueuePerWarp * 8 <= 220 * 1024;
+}
+
 template <typename F>
 psb_status set_smem(F kernel, size_t bytes) {
     if (bytes > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
@@ -590,7 +847,8 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
                        int* d_count, int sm_count, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
-    const int group = pick_group(ix.m, ix.k);
+    const bool use_half = ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(ix.m, ix.k);
+    const int group = use_half ? kHalfGroup : pick_group(ix.m, ix.k);
     // schedule
     PSB_CUDA(cudaMemsetAsync(ws.vis_count, 0, sizeof(int) * (size_t)ix.nlist, s));
     PSB_CUDA(cudaMemsetAsync(ws.pool_cnt, 0, sizeof(int) * (size_t)nq, s));
@@ -619,8 +877,19 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     a.vis_count = ws.vis_count; a.vis_off = ws.vis_off; a.visitors = ws.visitors; a.item_off = ws.item_off;
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
+    if (use_half) {
+        k_lut_to_half<<<nq, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    }
     if (ws.ev_begin) PSB_CUDA(cudaEventRecord(ws.ev_begin, s));
-    PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_m<MM>(a, group, sm_count, s))));
+    if (use_half) {
+        ScanArgsH ah;
+        ah.a = a; ah.lut_h = reinterpret_cast<const __half*>(ws.lut_h); ah.scale = ws.lut_scale;
+        PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_h<MM>(ah, sm_count, s))));
+    } else {
+        PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_m<MM>(a, group, sm_count, s))));
+    }
     if (ws.ev_end) PSB_CUDA(cudaEventRecord(ws.ev_end, s));
     // selection
     {

@@ -118,7 +118,7 @@ struct psb_session {
     std::vector<long long> h_global_begin, h_offsets;  // striped shards: host copies for the staged transport
     // workspaces
     DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
-        pool_cnt, pool, fail_list, scalars, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
+        pool_cnt, pool, fail_list, scalars, lut_h, lut_scale, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
     int ws_batch = 0, ws_nprobe = 0, ws_stage1 = 0, ws_topk = 0;
     int pool_cap = 0;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> scan_events;  // pending (options.time_kernels)
@@ -153,6 +153,7 @@ struct psb_session {
         w.n_fail = reinterpret_cast<int*>(sc + 5);
         w.fail_cursor = reinterpret_cast<int*>(sc + 6);
         w.pool_cap = pool_cap;
+        w.lut_h = lut_h.p; w.lut_scale = lut_scale.as<float>(); w.scan_mode = opt.scan_mode;
         return w;
     }
     // Scan workspace with a fresh event pair when kernel timing is on.
@@ -199,6 +200,10 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
     PSB_TRY(s->pool.reserve(sizeof(uint64_t) * (size_t)nq * cap));
     s->pool_cap = cap;
     PSB_TRY(s->fail_list.reserve(sizeof(int) * (size_t)nq));
+    if (s->opt.scan_mode != 1) {
+        PSB_TRY(s->lut_h.reserve(sizeof(unsigned short) * (size_t)nq * s->m * s->k));
+        PSB_TRY(s->lut_scale.reserve(sizeof(float) * (size_t)nq));
+    }
     if (!s->scalars.p) {
         PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 8));
         PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(unsigned long long) * 8, s->stream));

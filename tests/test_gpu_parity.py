@@ -344,3 +344,38 @@ def test_striped_shards_reproduce_the_whole_index_search(psb):
     assert np.array_equal(o_dist.cpu().numpy(), want["distances"])
     for s in sessions:
         s.close()
+
+
+# ---------------------------------------------------------------------------------------------- scan variants
+@pytest.mark.parametrize("M,dim,zipf", [(48, 96, True), (32, 128, False), (20, 100, True), (16, 64, False), (8, 32, True)])
+def test_half_prefilter_scan_equals_fp32_scan(psb, M, dim, zipf):
+    """The fp16 pre-filter scan (8 visitors per item, exact fp32 re-scoring of the pairs that pass) must admit
+    exactly the rows the fp32 scan admits and return the same candidates."""
+    nlist = 20
+    ix = synth.make_index(120000, dim, nlist, M, seed=M + 7, zipf=zipf)
+    q = synth.make_queries(ix, 48, seed=M + 8, weights=synth.zipf_weights(nlist) if zipf else None)
+    probes, _ = oracle.coarse(q, ix["centroids"], 10)
+    out = {}
+    for mode in (0, 1):
+        _, rows, dist, cnt, counters = run_stage_scan(psb, ix, q, probes, 300, scan_mode=mode)
+        out[mode] = (rows, dist, cnt, counters)
+    assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][1], out[1][1])
+    assert np.array_equal(out[0][2], out[1][2])
+    assert out[0][3]["threshold_candidates"] == out[1][3]["threshold_candidates"]
+    assert out[0][3]["fallback_queries"] == out[1][3]["fallback_queries"]
+    orow, odist, ocnt, _ = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], 300)
+    assert np.array_equal(out[0][0], orow) and np.array_equal(out[0][1], odist)
+
+
+def test_half_prefilter_scan_extreme_table_values(psb):
+    """Tables with tiny, huge and zero entries: the power-of-two scaling keeps fp16 sums finite and the lower bound valid."""
+    rng = np.random.default_rng(0)
+    for scale in (1e-4, 1.0, 3e3):
+        ix = synth.make_index(60000, 32, 8, 8, seed=3)
+        ix["codebook"] = (ix["codebook"] * scale).astype(np.float32)
+        ix["codebook"][:, :8, :] = 0.0  # exact zeros among the codewords
+        q = (synth.make_queries(ix, 16, seed=4) * scale).astype(np.float32)
+        probes = np.tile(np.arange(8), (16, 1)).astype(np.int64)
+        _, rows, dist, cnt, _ = run_stage_scan(psb, ix, q, probes, 200)
+        orow, odist, ocnt, _ = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], 200)
+        assert np.array_equal(rows, orow) and np.array_equal(dist, odist)
