@@ -236,6 +236,7 @@ def main():
     device = local_rank
     if world > 1 and args.impl == "ours":
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner out of stdout: one JSON line only
         dist.init_process_group("nccl")
     if args.impl == "ours" and world > 1:
         from paraselect_b200 import multi
