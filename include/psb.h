@@ -158,7 +158,8 @@ typedef struct psb_stats {
     double scan_kernel_ms;          /* device time of the ADC scan kernel alone (options.time_kernels) */
     long long scan_kernel_launches;
     int batches;
-    int reserved[7];
+    int coarse_fallback_queries;    /* queries the tensor-core coarse filter handed to the exact per-query kernel */
+    int reserved[6];
 } psb_stats;
 
 typedef struct psb_session psb_session;

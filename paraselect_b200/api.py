@@ -81,7 +81,7 @@ class Stats(C.Structure):
                 ("pq_adc_lookups", C.c_longlong), ("threshold_candidates", C.c_longlong),
                 ("fallback_queries", C.c_longlong), ("h2d_bytes", C.c_longlong), ("d2h_bytes", C.c_longlong),
                 ("kernel_launches", C.c_longlong), ("scan_kernel_ms", C.c_double), ("scan_kernel_launches", C.c_longlong),
-                ("batches", C.c_int), ("reserved", C.c_int * 7)]
+                ("batches", C.c_int), ("coarse_fallback_queries", C.c_int), ("reserved", C.c_int * 6)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}

@@ -33,6 +33,38 @@ psb_status launch_coarse_dist_exact(const float* d_queries, int nq, const float*
 psb_status launch_select_rows(const float* d_dist, int nq, int n, int k, int* d_ids, float* d_out,
                               cudaStream_t s);
 
+// ---- coarse, tensor-core filter (coarse_tc.cu) ----------------------------------------------------------------
+struct CoarseTcIndex {
+    const float* centroids;  // [nlist][dim] fp32 (exact re-scoring)
+    const void* cb;          // [nlist][dimp] bf16, centred on mu
+    const float* cn2;        // [tiles * 256] |c'|^2 (+inf padding)
+    const float* mu;         // [dim] mean centroid
+    float cmax;              // max |c'|
+    int nlist, dim;
+};
+struct CoarseTcWorkspace {
+    void* qb;        // [nq][dimp] bf16
+    float* qnorm;    // [nq]
+    float* gmin;     // [nq][groups]
+    float* seltop;   // [nq][nprobe]
+    int* selids;     // [nq][nprobe]
+    int* cand_cnt;   // [nq]
+    int* cand;       // [nq][cand cap]
+    int* fail_list;  // [nq]
+    int* n_fail;     // [2]: count, cursor
+    int* status;     // [1]
+};
+int coarse_tc_padded_dim(int dim);
+int coarse_tc_tiles(int nlist);
+int coarse_tc_cand_cap();
+int coarse_tc_group(int nlist, int nprobe);
+bool coarse_tc_supported(int nq, int nlist, int dim, int nprobe);
+// d_cb [nlist][dimp] bf16, d_cn2 [tiles*256], d_cnorm [nlist] out.
+psb_status launch_tc_prep_centroids(const float* d_centroids, int nlist, int dim, const float* d_mu, void* d_cb,
+                                    float* d_cn2, float* d_cnorm, cudaStream_t s);
+psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws, const float* d_queries, int nq,
+                            int nprobe, int* d_ids, float* d_dist, int sm_count, cudaStream_t s);
+
 // ---- PQ lookup tables --------------------------------------------------------------------------------
 psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
                             float* d_lut, cudaStream_t s);

@@ -85,12 +85,85 @@ struct EventTimer {
     }
 };
 
+// Centroid-side buffers of the tensor-core coarse filter (built once per index).
+struct TcIndexBuffers {
+    DevBuf cb, cn2, cnorm, mu;
+    float cmax = 0.f;
+    bool ready = false;
+    psb_status prepare(const float* h_centroids, const float* d_centroids, int nlist, int dim, cudaStream_t st) {
+        std::vector<double> acc((size_t)dim, 0.0);
+        for (int c = 0; c < nlist; ++c)
+            for (int d = 0; d < dim; ++d) acc[(size_t)d] += h_centroids[(size_t)c * dim + d];
+        std::vector<float> mean((size_t)dim);
+        for (int d = 0; d < dim; ++d) mean[(size_t)d] = (float)(acc[(size_t)d] / nlist);
+        const int dimp = coarse_tc_padded_dim(dim);
+        PSB_TRY(mu.reserve(sizeof(float) * (size_t)dim));
+        PSB_TRY(cb.reserve((size_t)2 * nlist * dimp));
+        PSB_TRY(cn2.reserve(sizeof(float) * (size_t)coarse_tc_tiles(nlist) * 256));
+        PSB_TRY(cnorm.reserve(sizeof(float) * (size_t)nlist));
+        PSB_CUDA(cudaMemcpyAsync(mu.p, mean.data(), sizeof(float) * (size_t)dim, cudaMemcpyHostToDevice, st));
+        PSB_TRY(launch_tc_prep_centroids(d_centroids, nlist, dim, mu.as<float>(), cb.p, cn2.as<float>(), cnorm.as<float>(), st));
+        std::vector<float> norms((size_t)nlist);
+        PSB_CUDA(cudaMemcpyAsync(norms.data(), cnorm.p, sizeof(float) * (size_t)nlist, cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaStreamSynchronize(st));
+        cmax = 0.f;
+        for (float v : norms) cmax = std::max(cmax, v);
+        ready = true;
+        return PSB_OK;
+    }
+    CoarseTcIndex view(const float* d_centroids, int nlist, int dim) const {
+        CoarseTcIndex ix;
+        ix.centroids = d_centroids; ix.cb = cb.p; ix.cn2 = cn2.as<float>(); ix.mu = mu.as<float>(); ix.cmax = cmax;
+        ix.nlist = nlist; ix.dim = dim;
+        return ix;
+    }
+};
+
+// Per-batch buffers of the tensor-core coarse filter.
+struct TcWorkBuffers {
+    DevBuf qb, qnorm, gmin, seltop, selids, cand_cnt, cand, fail_list, scalars;
+    psb_status ensure(int nq, int nlist, int dim, int nprobe, cudaStream_t st) {
+        const int dimp = coarse_tc_padded_dim(dim);
+        const int groups = coarse_tc_tiles(nlist) * (256 / coarse_tc_group(nlist, nprobe));
+        PSB_TRY(qb.reserve((size_t)2 * nq * dimp));
+        PSB_TRY(qnorm.reserve(sizeof(float) * (size_t)nq));
+        PSB_TRY(gmin.reserve(sizeof(float) * (size_t)nq * groups));
+        PSB_TRY(seltop.reserve(sizeof(float) * (size_t)nq * nprobe));
+        PSB_TRY(selids.reserve(sizeof(int) * (size_t)nq * nprobe));
+        PSB_TRY(cand_cnt.reserve(sizeof(int) * (size_t)nq));
+        PSB_TRY(cand.reserve(sizeof(int) * (size_t)nq * coarse_tc_cand_cap()));
+        PSB_TRY(fail_list.reserve(sizeof(int) * (size_t)nq));
+        if (!scalars.p) {
+            PSB_TRY(scalars.reserve(sizeof(int) * 4));
+            PSB_CUDA(cudaMemsetAsync(scalars.p, 0, sizeof(int) * 4, st));
+        }
+        return PSB_OK;
+    }
+    CoarseTcWorkspace view() const {
+        CoarseTcWorkspace w;
+        w.qb = qb.p; w.qnorm = qnorm.as<float>(); w.gmin = gmin.as<float>(); w.seltop = seltop.as<float>();
+        w.selids = selids.as<int>(); w.cand_cnt = cand_cnt.as<int>(); w.cand = cand.as<int>();
+        w.fail_list = fail_list.as<int>(); w.n_fail = scalars.as<int>(); w.status = scalars.as<int>() + 2;
+        return w;
+    }
+    // Reads the sticky time-out word (the stream must be idle).
+    psb_status check_status() const {
+        if (!scalars.p) return PSB_OK;
+        int st = 0;
+        PSB_CUDA(cudaMemcpy(&st, scalars.as<int>() + 2, sizeof(int), cudaMemcpyDeviceToHost));
+        if (st) return fail(PSB_TIMEOUT, "a bounded wait in the tensor-core coarse kernel gave up");
+        return PSB_OK;
+    }
+};
+
 }  // namespace
 }  // namespace psb
 
 using namespace psb;
 
 struct psb_session {
+    TcIndexBuffers tc_index;
+    TcWorkBuffers tc_work;
     int device = 0;
     int sm_count = 148;
     cudaStream_t stream = nullptr;
@@ -228,6 +301,14 @@ psb_status ensure_pipeline_ws(psb_session* s, int nq, int nprobe, int topk, int 
 // Coarse stage on device queries: exact distance tiles + row selection, query-chunked so the distance tile
 // stays below ~1 GiB.
 psb_status coarse_exact(psb_session* s, const float* d_queries, int nq, int nprobe, int* d_ids, float* d_dist) {
+    const int mode = s->opt.coarse_mode;
+    const bool tc_ok = s->tc_index.ready && coarse_tc_supported(nq, s->nlist, s->dim, nprobe);
+    if (mode == 2 && !tc_ok) return fail(PSB_UNSUPPORTED_SHAPE, "tensor-core coarse stage does not support this shape");
+    if (mode != 1 && tc_ok) {
+        PSB_TRY(s->tc_work.ensure(nq, s->nlist, s->dim, nprobe, s->stream));
+        return launch_coarse_tc(s->tc_index.view(s->centroids.as<float>(), s->nlist, s->dim), s->tc_work.view(), d_queries,
+                                nq, nprobe, d_ids, d_dist, s->sm_count, s->stream);
+    }
     const size_t row_bytes = sizeof(float) * (size_t)s->nlist;
     int chunk = (int)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
     chunk = std::min(chunk, nq);
@@ -436,6 +517,8 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     }
     PSB_TRY(s->centroids.reserve(sizeof(float) * (size_t)nlist * s->dim));
     PSB_CUDA(cudaMemcpyAsync(s->centroids.p, index->coarse.centroids, sizeof(float) * (size_t)nlist * s->dim, cudaMemcpyHostToDevice, st));
+    if (opt.coarse_mode != 1 && nlist >= 1024 && coarse_tc_padded_dim(s->dim) <= 256)
+        PSB_TRY(s->tc_index.prepare(index->coarse.centroids, s->centroids.as<float>(), nlist, s->dim, st));
     PSB_TRY(s->offsets.reserve(sizeof(long long) * ((size_t)nlist + 1)));
     PSB_CUDA(cudaMemcpyAsync(s->offsets.p, index->lists.offsets, sizeof(long long) * ((size_t)nlist + 1), cudaMemcpyHostToDevice, st));
     PSB_TRY(s->reordered.reserve(sizeof(long long) * (size_t)std::max<long long>(1, s->n_vectors)));
@@ -498,7 +581,7 @@ psb_status psb_session_destroy(psb_session* s) {
 psb_status psb_session_sync(psb_session* s) {
     if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
     PSB_CUDA(cudaStreamSynchronize(s->stream));
-    return PSB_OK;
+    return s->tc_work.check_status();
 }
 
 psb_status psb_stage_coarse(psb_session* s, const float* d_queries, int nq, int nprobe, int* d_ids, float* d_dist) {
@@ -585,6 +668,13 @@ psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     s->collect_scan_events();
     stats->scan_kernel_ms = s->scan_ms_total;
     stats->scan_kernel_launches = s->scan_launches_total;
+    stats->coarse_fallback_queries = 0;
+    if (s->tc_work.scalars.p) {
+        int v = 0;
+        PSB_CUDA(cudaMemcpy(&v, s->tc_work.scalars.as<int>() + 3, sizeof(int), cudaMemcpyDeviceToHost));
+        stats->coarse_fallback_queries = v;
+        if (reset) PSB_CUDA(cudaMemset(s->tc_work.scalars.as<int>() + 3, 0, sizeof(int)));
+    }
     if (reset) { s->scan_ms_total = 0.0; s->scan_launches_total = 0; }
     return PSB_OK;
 }
@@ -662,6 +752,7 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
             t_rr += tm.ms(4, 5); t_map += tm.ms(5, 6); t_d2h += tm.ms(6, 7);
         }
     }
+    PSB_TRY(s->tc_work.check_status());
     if (stats) {
         unsigned long long c1[4];
         PSB_CUDA(cudaMemcpyAsync(c1, s->scalars.p, sizeof(c1), cudaMemcpyDeviceToHost, st));
@@ -737,7 +828,6 @@ psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* 
 
 psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centroids, int nlist, int dim,
                            int nprobe, int coarse_mode, int64_t* h_ids, float* h_dist, int device) {
-    (void)coarse_mode;
     if (!h_queries || !h_centroids || !h_ids || nq < 0 || nlist <= 0 || dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid coarse request");
     if (nprobe <= 0 || nprobe > nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
     if (nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
@@ -749,15 +839,30 @@ psb_status psb_coarse_host(const float* h_queries, int nq, const float* h_centro
     PSB_TRY(dist.reserve(sizeof(float) * (size_t)nq * nprobe));
     PSB_CUDA(cudaMemcpy(q.p, h_queries, sizeof(float) * (size_t)nq * dim, cudaMemcpyHostToDevice));
     PSB_CUDA(cudaMemcpy(c.p, h_centroids, sizeof(float) * (size_t)nlist * dim, cudaMemcpyHostToDevice));
-    const size_t row_bytes = sizeof(float) * (size_t)nlist;
-    int chunk = (int)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
-    chunk = std::min(chunk, nq);
-    PSB_TRY(tile.reserve(row_bytes * (size_t)chunk));
-    for (int q0 = 0; q0 < nq; q0 += chunk) {
-        const int n = std::min(chunk, nq - q0);
-        PSB_TRY(launch_coarse_dist_exact(q.as<float>() + (size_t)q0 * dim, n, c.as<float>(), nlist, dim, tile.as<float>(), nullptr));
-        PSB_TRY(launch_select_rows(tile.as<float>(), n, nlist, nprobe, ids.as<int>() + (size_t)q0 * nprobe,
-                                   dist.as<float>() + (size_t)q0 * nprobe, nullptr));
+    const bool tc_ok = coarse_tc_supported(nq, nlist, dim, nprobe);
+    if (coarse_mode == 2 && !tc_ok) return fail(PSB_UNSUPPORTED_SHAPE, "tensor-core coarse stage does not support this shape");
+    if (coarse_mode != 1 && tc_ok) {
+        cudaDeviceProp prop;
+        PSB_CUDA(cudaGetDeviceProperties(&prop, device));
+        TcIndexBuffers tix;
+        TcWorkBuffers twk;
+        PSB_TRY(tix.prepare(h_centroids, c.as<float>(), nlist, dim, nullptr));
+        PSB_TRY(twk.ensure(nq, nlist, dim, nprobe, nullptr));
+        PSB_TRY(launch_coarse_tc(tix.view(c.as<float>(), nlist, dim), twk.view(), q.as<float>(), nq, nprobe, ids.as<int>(),
+                                 dist.as<float>(), prop.multiProcessorCount, nullptr));
+        PSB_CUDA(cudaDeviceSynchronize());
+        PSB_TRY(twk.check_status());
+    } else {
+        const size_t row_bytes = sizeof(float) * (size_t)nlist;
+        int chunk = (int)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
+        chunk = std::min(chunk, nq);
+        PSB_TRY(tile.reserve(row_bytes * (size_t)chunk));
+        for (int q0 = 0; q0 < nq; q0 += chunk) {
+            const int n = std::min(chunk, nq - q0);
+            PSB_TRY(launch_coarse_dist_exact(q.as<float>() + (size_t)q0 * dim, n, c.as<float>(), nlist, dim, tile.as<float>(), nullptr));
+            PSB_TRY(launch_select_rows(tile.as<float>(), n, nlist, nprobe, ids.as<int>() + (size_t)q0 * nprobe,
+                                       dist.as<float>() + (size_t)q0 * nprobe, nullptr));
+        }
     }
     PSB_TRY(launch_widen_ids(ids.as<int>(), (long long)nq * nprobe, ids64.as<long long>(), nullptr));
     PSB_CUDA(cudaMemcpy(h_ids, ids64.p, sizeof(long long) * (size_t)nq * nprobe, cudaMemcpyDeviceToHost));

@@ -1,0 +1,87 @@
+"""GPU parity tests of the tensor-core coarse stage (bf16 tcgen05 filter + exact fp32 refinement): its output must
+be bit-identical to the CPU checker's exact coarse search, ids and distances."""
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def check(psb, q, c, nprobe):
+    ids, dist = psb.coarse_host(q, c, nprobe, coarse_mode=2)
+    oi, od = oracle.coarse(q, c, nprobe)
+    assert np.array_equal(ids, oi)
+    assert np.array_equal(dist, od)
+
+
+@pytest.mark.parametrize("nq,nlist,dim,nprobe", [(300, 4096, 96, 64), (130, 1024, 128, 32), (200, 2148, 100, 16),
+                                                  (1000, 8192, 64, 128), (64, 5000, 192, 8), (257, 3000, 32, 1)])
+def test_tc_coarse_matches_checker_gaussian(psb, nq, nlist, dim, nprobe):
+    rng = np.random.default_rng(nq + nlist)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    c = rng.standard_normal((nlist, dim)).astype(np.float32)
+    check(psb, q, c, nprobe)
+
+
+def test_tc_coarse_unit_norm_inputs(psb):
+    # the "coarse stage only" configuration cut down: N(0,1) scaled to unit mean norm, d = 96, top-64
+    rng = np.random.default_rng(2)
+    q = rng.standard_normal((2000, 96)).astype(np.float32)
+    c = rng.standard_normal((16384, 96)).astype(np.float32)
+    q /= np.linalg.norm(q, axis=1).mean()
+    c /= np.linalg.norm(c, axis=1).mean()
+    check(psb, q, c, 64)
+
+
+def test_tc_coarse_far_from_origin(psb):
+    # data far from the origin: centring on the mean centroid keeps the bf16 error bound tight
+    rng = np.random.default_rng(3)
+    q = (rng.standard_normal((256, 64)) + 40.0).astype(np.float32)
+    c = (rng.standard_normal((2048, 64)) + 40.0).astype(np.float32)
+    check(psb, q, c, 32)
+
+
+def test_tc_coarse_integer_grid_with_ties(psb):
+    rng = np.random.default_rng(4)
+    q = rng.integers(-3, 4, (200, 32)).astype(np.float32)
+    c = rng.integers(-3, 4, (4096, 32)).astype(np.float32)
+    check(psb, q, c, 65)
+
+
+def test_tc_coarse_candidate_overflow_falls_back_to_exact_rows(psb):
+    # every centroid identical: every approximate distance ties, the candidate lists overflow, and the per-query
+    # exact kernel must return ids 0..nprobe-1
+    q = np.random.default_rng(5).standard_normal((128, 64)).astype(np.float32)
+    c = np.tile(np.random.default_rng(6).standard_normal((1, 64)).astype(np.float32), (4096, 1))
+    check(psb, q, c, 40)
+
+
+def test_tc_coarse_mode_rejects_unsupported_shapes(psb):
+    q = np.zeros((8, 16), np.float32)
+    c = np.zeros((64, 16), np.float32)
+    with pytest.raises(psb.PsbError) as e:
+        psb.coarse_host(q, c, 4, coarse_mode=2)
+    assert e.value.status == 2
+
+
+def test_tc_filter_does_the_work_not_the_fallback(psb):
+    """On ordinary data the tensor-core filter must hand (almost) no query to the exact per-query kernel, and the
+    session must give the same probes with the filter on and off."""
+    import torch
+    import synth
+    ix = synth.make_index(30000, 96, 2048, 48, seed=9)
+    q = synth.make_queries(ix, 500, seed=10)
+    dq = torch.from_numpy(q).cuda()
+    out = {}
+    for mode in (1, 2):
+        with psb.Session(dict(ix, vectors=None), coarse_mode=mode) as s:
+            ids = torch.empty((500, 64), dtype=torch.int32, device="cuda")
+            dist = torch.empty((500, 64), dtype=torch.float32, device="cuda")
+            s.stage_coarse(dq, 500, 64, ids, dist)
+            s.sync()
+            out[mode] = (ids.cpu().numpy(), dist.cpu().numpy(), s.counters()["coarse_fallback_queries"])
+    assert np.array_equal(out[1][0], out[2][0]) and np.array_equal(out[1][1], out[2][1])
+    assert out[2][2] == 0
+    oi, od = oracle.coarse(q, ix["centroids"], 64)
+    assert np.array_equal(out[2][0], oi) and np.array_equal(out[2][1], od)
