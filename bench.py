@@ -37,6 +37,9 @@ WORKLOADS = {
     # BASELINE configuration "IVF-PQ fp32 1M"
     "c2": dict(n=1_000_000, dim=128, nlist=1024, M=32, sigma=0.25, zipf=None, nq=10000, nprobe=32, topk=10,
                n_rerank=100, seed=1, desc="IVF-PQ 1Mx128 nlist=1024 M=32 nprobe=32 k=10 rerank=100 batch=10000"),
+    # BASELINE configuration "coarse stage only" (secondary line: tensor-core roofline of the fused coarse GEMM)
+    "c3": dict(n=65536, dim=96, nlist=65536, M=8, sigma=0.0, zipf=None, nq=100000, nprobe=64, topk=64, n_rerank=0, seed=2,
+               desc="coarse only: 100,000 queries x 65,536 centroids, d=96, unit-mean-norm N(0,1), top-64"),
 }
 
 
@@ -242,6 +245,9 @@ def main():
         from paraselect_b200 import multi
         return multi.bench_main(args, cfg, rank, world, local_rank)
 
+    if args.workload == "c3":
+        return coarse_only(args, cfg, torch, api, device)
+
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         gt_n = 64
@@ -376,6 +382,121 @@ def main():
         result_checksum=int(np.bitwise_xor.reduce((e2e_ids.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel())
                             & np.uint64((1 << 62) - 1)),
         clocks=clocks)
+    print(json.dumps(line), flush=True)
+    sess.close()
+    return 0
+
+
+def coarse_only(args, cfg, torch, api, device):
+    """Secondary workload: the coarse stage alone (queries x centroids squared L2 with per-query top-64)."""
+    import oracle
+    nq, nlist, dim, k = cfg["nq"], cfg["nlist"], cfg["dim"], cfg["nprobe"]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        c = torch.empty((nlist, dim), dtype=torch.float32, device="cuda")
+        q = torch.empty((nq, dim), dtype=torch.float32, device="cuda")
+        api.gen_normal(cfg["seed"] * 1000 + 1, 0, nlist * dim, 1.0, c, device=device)
+        api.gen_normal(cfg["seed"] * 1000 + 2, 0, nq * dim, 1.0, q, device=device)
+        c /= c.norm(dim=1).mean()
+        q /= q.norm(dim=1).mean()
+        torch.cuda.synchronize()
+        # a carrier index: one row per list, so that a session (which owns the coarse stage) can be created
+        index = dict(centroids=c.cpu().numpy(), offsets=np.arange(nlist + 1, dtype=np.int64),
+                     reordered_ids=np.arange(nlist, dtype=np.int64), codes=np.zeros((nlist, 8), np.uint8),
+                     codebook=np.zeros((8, 256, dim // 8), np.float32), vectors=None, nlist=nlist)
+        q_host = q.cpu().numpy()
+        if args.impl == "reference":
+            cores = os.cpu_count() or 1
+            ns = args.cpu_sample or 256
+            times = []
+            for i in range(args.warmup + args.steps):
+                t0 = time.time()
+                if oracle.have_ref():
+                    oracle.ref_coarse(q_host[i * ns:(i + 1) * ns], index["centroids"], k, threads=cores); kind = "reference"
+                else:
+                    oracle.coarse(q_host[i * ns:(i + 1) * ns], index["centroids"], k); kind = "port"
+                if i >= args.warmup:
+                    times.append(time.time() - t0)
+            v = round(ns / float(np.mean(times)), 2)
+            print(json.dumps(dict(impl="reference", metric="coarse queries/s (top-64 of 65,536 centroids)", value=v,
+                                  unit="queries/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                                  ms_per_step=round(1e3 * float(np.mean(times)), 3), higher_is_better=True, scaling="strong",
+                                  vs_baseline=None, dtype="f32", data="synthetic", config=dict(workload="c3", desc=cfg["desc"]),
+                                  cpu_baseline=dict(value=v, unit="queries/s", cores=cores, kind=kind,
+                                                    sample="%d queries per step, all %d host threads" % (ns, cores)),
+                                  e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))), flush=True)
+            return 0
+        sess = api.Session(index, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True)
+        ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+        dist = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+        for _ in range(max(args.warmup, 3)):
+            sess.stage_coarse(q, nq, k, ids, dist)
+        torch.cuda.synchronize()
+        sess.counters(reset=True)
+        sampler = ClockSampler(device)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            sess.stage_coarse(q, nq, k, ids, dist)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        cnt = sess.counters(reset=True)
+        # end to end: host queries in, host ids/distances out
+        qp = torch.empty((nq, dim), dtype=torch.float32).pin_memory(); qp.copy_(q)
+        oi = torch.empty((nq, k), dtype=torch.int32).pin_memory()
+        od = torch.empty((nq, k), dtype=torch.float32).pin_memory()
+        q2 = torch.empty_like(q)
+
+        def e2e_step():
+            q2.copy_(qp, non_blocking=True)
+            sess.stage_coarse(q2, nq, k, ids, dist)
+            oi.copy_(ids, non_blocking=True); od.copy_(dist, non_blocking=True)
+            stream.synchronize()
+        e2e_step()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+        got_i, got_d = oi.numpy().astype(np.int64), od.numpy().copy()
+    cores = os.cpu_count() or 1
+    ns = args.cpu_sample or 512
+    t0 = time.time()
+    if oracle.have_ref():
+        ri, rd = oracle.ref_coarse(q_host[:ns], index["centroids"], k, threads=cores); kind = "reference"
+    else:
+        ri, rd = oracle.coarse(q_host[:ns], index["centroids"], k); kind = "port"
+    dt = time.time() - t0
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    flops = 2.0 * nq * nlist * dim
+    gemm_ms = cnt["coarse_gemm_ms"] / max(1, cnt["coarse_gemm_launches"])  # one pass
+    line = dict(metric="coarse queries/s (top-64 of 65,536 centroids)", value=round(nq / (ms * 1e-3), 1), unit="queries/s",
+                n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms, 3), higher_is_better=True,
+                scaling="strong", vs_baseline=None, dtype="bf16 filter + f32 exact", data="synthetic",
+                config=dict(workload="c3", desc=cfg["desc"], l2="distance matrix never materialised; operands 64 MB"),
+                e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
+                         h2d_bytes_per_step=nq * dim * 4, d2h_bytes_per_step=nq * k * 8),
+                gpu_launches=int(cnt["kernel_launches"]),
+                roofline=dict(bound="tensor", kernel="k_coarse_tc (one of two passes)", achieved=round(flops / (gemm_ms * 1e-3) / 1e12, 1),
+                              peak=peak, unit="TFLOP/s", frac=round(flops / (gemm_ms * 1e-3) / 1e12 / peak, 4),
+                              peak_source="measured (burst)" if peaks else "fallback", ms_per_launch=round(gemm_ms, 3),
+                              algorithmic_flops_per_launch=flops, executed_flops_per_launch=2.0 * nq * nlist * 128, traffic=None,
+                              stage_achieved_tflops=round(flops / (ms * 1e-3) / 1e12, 1)),
+                cpu_baseline=dict(value=round(ns / dt, 2), unit="queries/s", cores=cores, kind=kind,
+                                  sample="first %d queries, all %d host threads" % (ns, cores)),
+                parity=dict(sample_queries=ns, ids_equal=bool(np.array_equal(ri, got_i[:ns])),
+                            dist_equal=bool(np.array_equal(rd, got_d[:ns])),
+                            coarse_fallback_queries=int(cnt["coarse_fallback_queries"])),
+                clocks=clocks)
     print(json.dumps(line), flush=True)
     sess.close()
     return 0

@@ -157,6 +157,8 @@ typedef struct psb_stats {
     long long kernel_launches;
     double scan_kernel_ms;          /* device time of the ADC scan kernel alone (options.time_kernels) */
     long long scan_kernel_launches;
+    double coarse_gemm_ms;          /* device time of the tensor-core coarse GEMM passes (options.time_kernels) */
+    long long coarse_gemm_launches; /* two per coarse call */
     int batches;
     int coarse_fallback_queries;    /* queries the tensor-core coarse filter handed to the exact per-query kernel */
     int reserved[6];

@@ -81,6 +81,7 @@ class Stats(C.Structure):
                 ("pq_adc_lookups", C.c_longlong), ("threshold_candidates", C.c_longlong),
                 ("fallback_queries", C.c_longlong), ("h2d_bytes", C.c_longlong), ("d2h_bytes", C.c_longlong),
                 ("kernel_launches", C.c_longlong), ("scan_kernel_ms", C.c_double), ("scan_kernel_launches", C.c_longlong),
+                ("coarse_gemm_ms", C.c_double), ("coarse_gemm_launches", C.c_longlong),
                 ("batches", C.c_int), ("coarse_fallback_queries", C.c_int), ("reserved", C.c_int * 6)]
 
     def as_dict(self):

@@ -106,10 +106,23 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
 // kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = 256.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TCOL >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
 
+// Minima of consecutive groups of G values of a 32-value chunk.
+template <int G>
+__device__ __forceinline__ void group_mins(const float (&v)[32], float* __restrict__ out) {
+#pragma unroll
+    for (int g = 0; g < 32 / G; ++g) {
+        float m = v[g * G];
+#pragma unroll
+        for (int j = 1; j < G; ++j) m = fminf(m, v[g * G + j]);
+        out[g] = m;
+    }
+}
+
 struct TcArgs {
     int nq, nlist, katoms;  // katoms = padded dim / 64
     int ntiles;             // centroid tiles of TCOL
     int group;              // G: centroids per minimum in pass 1 (power of two <= 32)
+    int lg_group;           // log2(G)
     int ngroups;            // minima per query row = ntiles * (TCOL / G)
     int nprobe;
     const float* cn2;       // [ntiles * TCOL] |c'|^2, +inf beyond nlist
@@ -200,24 +213,30 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
             tmem_ld32(lane_addr + (uint32_t)cb, r);
             tmem_ld_wait();
             if (q < a.nq) {
-                if (!kSecondPass) {
-                    float m = __int_as_float(0x7f800000);
+                float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float v = fmaf(-2.0f, __uint_as_float(r[j]), s_cn2[cb + j]);  // +inf beyond nlist
-                        m = fminf(m, v);
-                        if (((j + 1) & (a.group - 1)) == 0) {
-                            a.gmin[(size_t)q * a.ngroups + (c0 + cb + j) / a.group] = m;
-                            m = __int_as_float(0x7f800000);
-                        }
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(-2.0f, __uint_as_float(r[j]), s_cn2[cb + j]);  // +inf beyond nlist
+                if (!kSecondPass) {
+                    float* out = a.gmin + (size_t)q * a.ngroups + ((c0 + cb) >> a.lg_group);
+                    switch (a.lg_group) {  // uniform
+                        case 5: group_mins<32>(v, out); break;
+                        case 4: group_mins<16>(v, out); break;
+                        case 3: group_mins<8>(v, out); break;
+                        case 2: group_mins<4>(v, out); break;
+                        case 1: group_mins<2>(v, out); break;
+                        default: group_mins<1>(v, out); break;
                     }
                 } else {
+                    float m = v[0];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float v = fmaf(-2.0f, __uint_as_float(r[j]), s_cn2[cb + j]);
-                        if (v <= cut) {
-                            const int pos = atomicAdd(&a.cand_cnt[q], 1);
-                            if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + cb + j;
+                    for (int j = 1; j < 32; ++j) m = fminf(m, v[j]);
+                    if (m <= cut) {  // rare: some centroid of this chunk is a candidate
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (v[j] <= cut) {
+                                const int pos = atomicAdd(&a.cand_cnt[q], 1);
+                                if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + cb + j;
+                            }
                         }
                     }
                 }
@@ -439,6 +458,8 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     PSB_TRY(encode_rows_map(&map_c, ix.cb, ix.nlist, dimp, TCOL));
     TcArgs a;
     a.nq = nq; a.nlist = ix.nlist; a.katoms = katoms; a.ntiles = ntiles; a.group = group; a.ngroups = ngroups;
+    a.lg_group = 0;
+    while ((1 << a.lg_group) < group) ++a.lg_group;
     a.nprobe = nprobe; a.cn2 = ix.cn2; a.qnorm = ws.qnorm; a.cmax = ix.cmax; a.gmin = ws.gmin; a.seltop = ws.seltop;
     a.cand_cnt = ws.cand_cnt; a.cand = ws.cand; a.status = ws.status;
     const size_t smem = (size_t)katoms * (TQ + TCOL) * 128 + 1024;
@@ -450,11 +471,15 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     const dim3 grid(qtiles, slices);
     PSB_CUDA(cudaMemsetAsync(ws.cand_cnt, 0, sizeof(int) * (size_t)nq, s));
     PSB_CUDA(cudaMemsetAsync(ws.n_fail, 0, 2 * sizeof(int), s));  // n_fail, cursor
+    if (ws.ev[0]) PSB_CUDA(cudaEventRecord(ws.ev[0], s));
     k_coarse_tc<false><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
+    if (ws.ev[1]) PSB_CUDA(cudaEventRecord(ws.ev[1], s));
     count_launch();
     PSB_LAUNCH_CHECK();
     PSB_TRY(launch_select_rows(ws.gmin, nq, ngroups, nprobe, ws.selids, ws.seltop, s));
+    if (ws.ev[2]) PSB_CUDA(cudaEventRecord(ws.ev[2], s));
     k_coarse_tc<true><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
+    if (ws.ev[3]) PSB_CUDA(cudaEventRecord(ws.ev[3], s));
     count_launch();
     PSB_LAUNCH_CHECK();
     {

@@ -53,6 +53,7 @@ struct CoarseTcWorkspace {
     int* fail_list;  // [nq]
     int* n_fail;     // [2]: count, cursor
     int* status;     // [1]
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};  // optional: begin/end of GEMM pass 1 and pass 2
 };
 int coarse_tc_padded_dim(int dim);
 int coarse_tc_tiles(int nlist);

@@ -197,6 +197,9 @@ struct psb_session {
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> scan_events;  // pending (options.time_kernels)
     double scan_ms_total = 0.0;
     long long scan_launches_total = 0;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> gemm_events;  // pending coarse GEMM passes (options.time_kernels)
+    double gemm_ms_total = 0.0;
+    long long gemm_launches_total = 0;
 
     ScanIndex scan_index() const {
         ScanIndex ix;
@@ -248,6 +251,12 @@ struct psb_session {
             cudaEventDestroy(pr.first); cudaEventDestroy(pr.second);
         }
         scan_events.clear();
+        for (auto& pr : gemm_events) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, pr.first, pr.second) == cudaSuccess) { gemm_ms_total += t; ++gemm_launches_total; }
+            cudaEventDestroy(pr.first); cudaEventDestroy(pr.second);
+        }
+        gemm_events.clear();
         cudaGetLastError();
     }
 };
@@ -306,7 +315,13 @@ psb_status coarse_exact(psb_session* s, const float* d_queries, int nq, int npro
     if (mode == 2 && !tc_ok) return fail(PSB_UNSUPPORTED_SHAPE, "tensor-core coarse stage does not support this shape");
     if (mode != 1 && tc_ok) {
         PSB_TRY(s->tc_work.ensure(nq, s->nlist, s->dim, nprobe, s->stream));
-        return launch_coarse_tc(s->tc_index.view(s->centroids.as<float>(), s->nlist, s->dim), s->tc_work.view(), d_queries,
+        CoarseTcWorkspace tw = s->tc_work.view();
+        if (s->opt.time_kernels) {
+            for (int i = 0; i < 4; ++i) PSB_CUDA(cudaEventCreate(&tw.ev[i]));
+            s->gemm_events.emplace_back(tw.ev[0], tw.ev[1]);
+            s->gemm_events.emplace_back(tw.ev[2], tw.ev[3]);
+        }
+        return launch_coarse_tc(s->tc_index.view(s->centroids.as<float>(), s->nlist, s->dim), tw, d_queries,
                                 nq, nprobe, d_ids, d_dist, s->sm_count, s->stream);
     }
     const size_t row_bytes = sizeof(float) * (size_t)s->nlist;
@@ -668,6 +683,9 @@ psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     s->collect_scan_events();
     stats->scan_kernel_ms = s->scan_ms_total;
     stats->scan_kernel_launches = s->scan_launches_total;
+    stats->coarse_gemm_ms = s->gemm_ms_total;
+    stats->coarse_gemm_launches = s->gemm_launches_total;
+    if (reset) { s->gemm_ms_total = 0.0; s->gemm_launches_total = 0; }
     stats->coarse_fallback_queries = 0;
     if (s->tc_work.scalars.p) {
         int v = 0;
