@@ -281,14 +281,8 @@ def main():
         d_ids = torch.empty((nq, topk), dtype=torch.int64, device="cuda")
 
         def device_step():
-            sess.stage_coarse(dq, nq, nprobe, d_probes)
-            sess.stage_build_lut(dq, nq, d_lut)
-            sess.stage_scan(d_lut, nq, d_probes, nprobe, stage1, d_cand, d_cdist, d_ccnt)
-            if R > topk:
-                sess.stage_rerank(dq, nq, d_cand, stage1, stage1, d_ccnt, topk, d_rows, d_dist)
-                sess.stage_map_ids(d_rows, nq * topk, d_ids)
-            else:
-                sess.stage_map_ids(d_cand, nq * topk, d_ids)
+            # device-resident queries -> device-resident ids/distances (sub-batches overlap the PCIe rerank with the scan)
+            sess.search_device(dq, nq, nprobe, topk, d_ids, d_dist, d_probes)
 
         for _ in range(max(args.warmup, 3)):
             device_step()

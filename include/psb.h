@@ -132,9 +132,10 @@ typedef struct psb_options {
                            NULL = the view is the whole index. */
     int coarse_mode;    /* 0 = auto, 1 = exact SIMT kernel only, 2 = tensor-core filter + exact refinement */
     int time_kernels;   /* 1 = bracket the ADC scan kernel with CUDA events (read back by psb_session_counters) */
+    int serial_pipeline;/* 1 = never overlap the rerank of one sub-batch with the scan of the next (diagnostics) */
     int scan_mode;      /* 0 = auto (fp16 pre-filter scan with exact fp32 re-scoring when it fits), 1 = fp32 scan only;
                            both give identical results */
-    int reserved[5];
+    int reserved[4];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -193,6 +194,16 @@ psb_status psb_session_destroy(psb_session* session);
 psb_status psb_session_search(psb_session* session, const psb_query_batch_view* queries,
                               const psb_search_params* params, const psb_search_output_view* output,
                               psb_stats* stats);
+
+/* The same search with DEVICE queries and DEVICE outputs, asynchronous on the session's stream (nq <= max_batch):
+ * what psb_session_search runs per batch between its host copies.  When the rerank reads mapped or resident exact
+ * rows the batch is processed in sub-batches and the PCIe gather + exact scoring of one overlaps the scan of the
+ * next on a second stream (the GPU/CPU overlap of ivfrespq_pipeline_chunk_overlap,
+ * src/search/ivfrespq/pipeline/ivfrespq_pipeline_cpu.cu:543-708, done with two CUDA streams).
+ * d_queries_u8 only for a u8 rerank; d_coarse_ids optional [nq][nprobe]. */
+psb_status psb_session_search_device(psb_session* session, const float* d_queries, const uint8_t* d_queries_u8, int nq,
+                                     const psb_search_params* params, int64_t* d_indices, float* d_distances,
+                                     int* d_coarse_ids);
 
 /* Blocks until all work queued on the session's stream is done. */
 psb_status psb_session_sync(psb_session* session);

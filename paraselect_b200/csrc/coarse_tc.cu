@@ -30,7 +30,6 @@ constexpr int TQ = 128;          // queries per tile  (UMMA M)
 constexpr int TCOL = 256;        // centroids per tile (UMMA N)
 constexpr int KATOM = 64;        // bf16 elements per 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kTcThreads = 128;
 constexpr int kWaitLimit = 1 << 22;
 constexpr int kCandCap = 2048;
 
@@ -106,15 +105,19 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
 // kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = 256.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TCOL >> 3) << 17) | ((uint32_t)(TQ >> 4) << 24);
 
-// Minima of consecutive groups of G values of a 32-value chunk.
+// Per group of G consecutive values of a 32-value chunk: out = -2 * max(w), i.e. the minimum of a = -2 w.
 template <int G>
 __device__ __forceinline__ void group_mins(const float (&v)[32], float* __restrict__ out) {
 #pragma unroll
     for (int g = 0; g < 32 / G; ++g) {
-        float m = v[g * G];
+        float t[G];
 #pragma unroll
-        for (int j = 1; j < G; ++j) m = fminf(m, v[g * G + j]);
-        out[g] = m;
+        for (int j = 0; j < G; ++j) t[j] = v[g * G + j];
+#pragma unroll
+        for (int w = G / 2; w >= 1; w >>= 1)  // pairwise tree: short dependency chains
+#pragma unroll
+            for (int j = 0; j < w; ++j) t[j] = fmaxf(t[j], t[j + w]);
+        out[g] = -2.0f * t[0];
     }
 }
 
@@ -133,142 +136,211 @@ struct TcArgs {
     int* cand_cnt;          // pass 2 out: [nq]
     int* cand;              // pass 2 out: [nq][kCandCap]
     int* status;            // [1] != 0 after a bounded wait gave up
+    int cblocks, qtiles, qsplits;  // work units = cblocks (512 centroids each) x qsplits (ranges of query tiles)
 };
 
-template <bool kSecondPass>
-__global__ void __launch_bounds__(kTcThreads)
+// Persistent, warp-specialised kernel.  A work unit = (block of 512 centroids, range of query tiles).  The unit's
+// two centroid tiles (B operands) stay in shared memory while query tiles (A operand, 128 rows) stream through a
+// two-stage ring; each query tile is multiplied against both centroid tiles into two tensor-memory accumulators, so
+// the epilogue of one accumulator overlaps the MMAs of the other.
+//   warps 0-15 epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. +31 (one query row per thread) and the 64
+//              columns (w / 4) * 64 .. +63 of each accumulator, 32 columns per tcgen05.ld; folds |c'|^2 in;
+//              pass 1: group minima -> gmin, pass 2: compare with the row's cut-off -> candidate list.
+//              Sixteen warps because the epilogue (2+ instructions per matrix element), not the MMA, sets the pace.
+//   warp 16    TMA producer (one lane)
+//   warp 17    MMA issuer (one lane): 2 x katoms x 4 tcgen05.mma per query tile, tcgen05.commit -> mbarriers
+constexpr int kStagesA = 2;
+constexpr int kEpiWarps = 16;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kTcThreadsV2 = kEpiThreads + 64;
+constexpr int kBlockCols = 2 * TCOL;  // centroids per work unit
+
+// kAug: the operands carry 3 extra K slots (ones on the query side, minus the three-term bf16 split of |c'|^2 / 2 on the
+// centroid side), so the accumulator already holds w = q'.c' - |c'|^2 / 2 and the epilogue needs no norm arithmetic.
+template <bool kSecondPass, bool kAug>
+__global__ void __launch_bounds__(kTcThreadsV2, 1)
 k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_c, const TcArgs a) {
     extern __shared__ __align__(1024) unsigned char s_tc[];
-    // layout: A = katoms blocks of [TQ rows][128 B], then B = katoms blocks of [TCOL rows][128 B]; 1024-byte aligned
     unsigned char* s_base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_tc) + 1023) & ~uintptr_t(1023));
-    unsigned char* s_a = s_base;
-    unsigned char* s_b = s_base + (size_t)a.katoms * TQ * 128;
-    __shared__ __align__(8) uint64_t bar_a, bar_b, bar_mma;
+    const size_t a_bytes = (size_t)a.katoms * TQ * 128, b_bytes = (size_t)a.katoms * TCOL * 128;
+    unsigned char* s_a = s_base;                         // [kStagesA][katoms][TQ][128 B]
+    unsigned char* s_b = s_base + kStagesA * a_bytes;    // [2][katoms][TCOL][128 B]
+    __shared__ __align__(8) uint64_t a_full[kStagesA], a_empty[kStagesA], b_full, b_empty, acc_full[2], acc_empty[2];
     __shared__ uint32_t s_tmem;
-    __shared__ float s_cn2[TCOL];
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int q0 = blockIdx.x * TQ;
+    __shared__ __align__(16) float s_cn2[kBlockCols];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
-        mbar_init(&bar_a, 1); mbar_init(&bar_b, 1); mbar_init(&bar_mma, 1);
+        for (int i = 0; i < kStagesA; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+        mbar_init(&b_full, 1); mbar_init(&b_empty, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiThreads); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
-    if (warp == 0) tmem_alloc(&s_tmem, TCOL);
+    if (warp == 0) tmem_alloc(&s_tmem, 2 * TCOL);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-
-    if (tid == 0) {
-        mbar_expect_tx(&bar_a, (uint32_t)a.katoms * TQ * 128);
-        for (int ka = 0; ka < a.katoms; ++ka) tma_load_2d(s_a + (size_t)ka * TQ * 128, &map_q, ka * KATOM, q0, &bar_a);
-    }
-    const int q = q0 + tid;  // this thread's query row = tensor-memory lane
-    float cut = 0.0f;
-    if (kSecondPass && q < a.nq) {
-        const float T = a.seltop[(size_t)q * a.nprobe + a.nprobe - 1];
-        const float qn = a.qnorm[q];
-        const float E = 4.1f * 0.00390625f * qn * a.cmax;  // |a - exact| <= 2 |q'.c' - qb.cb| <= 2 * 2.01 * 2^-8 |q'||c'|
-        cut = T + 2.0f * E + 4e-5f * (qn + a.cmax) * (qn + a.cmax);
-    }
-    bool a_ready = false;
-    uint32_t phase = 0;
+    const int nunits = a.cblocks * a.qsplits;
     int failed = 0;
-    for (int t = blockIdx.y; t < a.ntiles; t += gridDim.y) {
-        const int c0 = t * TCOL;
-        if (tid == 0) {
-            mbar_expect_tx(&bar_b, (uint32_t)a.katoms * TCOL * 128);
-            for (int ka = 0; ka < a.katoms; ++ka) tma_load_2d(s_b + (size_t)ka * TCOL * 128, &map_c, ka * KATOM, c0, &bar_b);
-        }
-        for (int i = tid; i < TCOL; i += kTcThreads) s_cn2[i] = a.cn2[c0 + i];
-        int bad = 0;
-        if (tid == 0) {
-            if (!a_ready) { if (!mbar_wait(&bar_a, 0)) bad = 1; a_ready = true; }
-            if (!bad && !mbar_wait(&bar_b, phase)) bad = 1;
-            if (!bad) {
-                tc_fence_after();
-                const uint32_t sa = smem_u32(s_a), sb = smem_u32(s_b);
-                for (int ka = 0; ka < a.katoms; ++ka)
-                    for (int kk = 0; kk < KATOM / UMMA_K; ++kk) {
-                        const uint64_t da = make_sw128_desc(sa + ka * TQ * 128 + kk * UMMA_K * 2);
-                        const uint64_t db = make_sw128_desc(sb + ka * TCOL * 128 + kk * UMMA_K * 2);
-                        umma_bf16(tmem, da, db, kIdesc, (ka | kk) ? 1u : 0u);
-                    }
-                umma_commit(&bar_mma);
+
+    if (warp == kEpiWarps) {
+        if (lane == 0) {
+            uint32_t it = 0, un = 0;  // query tiles issued, units issued
+            for (int u = blockIdx.x; u < nunits && !failed; u += gridDim.x, ++un) {
+                const int cblock = u / a.qsplits, qs = u % a.qsplits;
+                const int t0 = (int)((long long)a.qtiles * qs / a.qsplits), t1 = (int)((long long)a.qtiles * (qs + 1) / a.qsplits);
+                if (!mbar_wait(&b_empty, (un & 1u) ^ 1u)) { failed = 1; break; }
+                mbar_expect_tx(&b_full, (uint32_t)(2 * b_bytes));
+                for (int h = 0; h < 2; ++h)
+                    for (int ka = 0; ka < a.katoms; ++ka)
+                        tma_load_2d(s_b + h * b_bytes + (size_t)ka * TCOL * 128, &map_c, ka * KATOM, cblock * kBlockCols + h * TCOL, &b_full);
+                for (int t = t0; t < t1; ++t, ++it) {
+                    const uint32_t st = it % kStagesA;
+                    if (!mbar_wait(&a_empty[st], ((it / kStagesA) & 1u) ^ 1u)) { failed = 1; break; }
+                    mbar_expect_tx(&a_full[st], (uint32_t)a_bytes);
+                    for (int ka = 0; ka < a.katoms; ++ka)
+                        tma_load_2d(s_a + st * a_bytes + (size_t)ka * TQ * 128, &map_q, ka * KATOM, t * TQ, &a_full[st]);
+                }
             }
         }
-        bad = __syncthreads_or(bad);  // also publishes s_cn2
-        if (!bad && !mbar_wait(&bar_mma, phase)) bad = 1;
-        bad = __syncthreads_or(bad);
-        if (bad) { failed = 1; break; }
-        tc_fence_after();
-        // epilogue: lane = query row, 256 fp32 accumulators = dot products with this tile's centroids
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-#pragma unroll 1
-        for (int cb = 0; cb < TCOL; cb += 32) {
-            uint32_t r[32];
-            __syncwarp();
-            tmem_ld32(lane_addr + (uint32_t)cb, r);
-            tmem_ld_wait();
-            if (q < a.nq) {
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = fmaf(-2.0f, __uint_as_float(r[j]), s_cn2[cb + j]);  // +inf beyond nlist
-                if (!kSecondPass) {
-                    float* out = a.gmin + (size_t)q * a.ngroups + ((c0 + cb) >> a.lg_group);
-                    switch (a.lg_group) {  // uniform
-                        case 5: group_mins<32>(v, out); break;
-                        case 4: group_mins<16>(v, out); break;
-                        case 3: group_mins<8>(v, out); break;
-                        case 2: group_mins<4>(v, out); break;
-                        case 1: group_mins<2>(v, out); break;
-                        default: group_mins<1>(v, out); break;
+    } else if (warp == kEpiWarps + 1) {
+        if (lane == 0) {
+            uint32_t it = 0, un = 0, nacc[2] = {0, 0};
+            for (int u = blockIdx.x; u < nunits && !failed; u += gridDim.x, ++un) {
+                const int qs = u % a.qsplits;
+                const int t0 = (int)((long long)a.qtiles * qs / a.qsplits), t1 = (int)((long long)a.qtiles * (qs + 1) / a.qsplits);
+                if (!mbar_wait(&b_full, un & 1u)) { failed = 1; break; }
+                for (int t = t0; t < t1 && !failed; ++t, ++it) {
+                    const uint32_t st = it % kStagesA;
+                    if (!mbar_wait(&a_full[st], (it / kStagesA) & 1u)) { failed = 1; break; }
+                    for (int h = 0; h < 2; ++h) {
+                        if (!mbar_wait(&acc_empty[h], (nacc[h] & 1u) ^ 1u)) { failed = 1; break; }
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(s_a + st * a_bytes), sb = smem_u32(s_b + h * b_bytes);
+                        for (int ka = 0; ka < a.katoms; ++ka)
+                            for (int kk = 0; kk < KATOM / UMMA_K; ++kk)
+                                umma_bf16(tmem + (uint32_t)(h * TCOL), make_sw128_desc(sa + ka * TQ * 128 + kk * UMMA_K * 2),
+                                          make_sw128_desc(sb + ka * TCOL * 128 + kk * UMMA_K * 2), kIdesc, (ka | kk) ? 1u : 0u);
+                        umma_commit(&acc_full[h]);
+                        ++nacc[h];
                     }
-                } else {
-                    float m = v[0];
+                    umma_commit(&a_empty[st]);  // stage reusable once both MMAs have read it
+                }
+                umma_commit(&b_empty);
+            }
+        }
+    } else {
+        // epilogue warps
+        uint32_t nacc[2] = {0, 0};
+        const int quad = warp & 3, part = warp >> 2;
+        const int row = quad * 32 + lane;  // tensor-memory lane = row of the current query tile
+        const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+        for (int u = blockIdx.x; u < nunits; u += gridDim.x) {  // every thread passes both barriers of every unit, failed or not
+            const int cblock = u / a.qsplits, qs = u % a.qsplits;
+            const int t0 = (int)((long long)a.qtiles * qs / a.qsplits), t1 = (int)((long long)a.qtiles * (qs + 1) / a.qsplits);
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // previous unit's readers of s_cn2 are done
+            for (int i = tid; i < kBlockCols; i += kEpiThreads) s_cn2[i] = a.cn2[(size_t)cblock * kBlockCols + i];
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            for (int t = t0; t < t1 && !failed; ++t) {
+                const int q = t * TQ + row;
+                float cut = 0.0f;
+                if (kSecondPass && q < a.nq) {
+                    const float T = a.seltop[(size_t)q * a.nprobe + a.nprobe - 1];
+                    const float qn = a.qnorm[q];
+                    const float E = 4.1f * 0.00390625f * qn * a.cmax;  // |a - exact| <= 2 |q'.c' - qb.cb| <= 2 * 2.01 * 2^-8 |q'||c'|
+                    cut = -0.5f * (T + 2.0f * E + 4e-5f * (qn + a.cmax) * (qn + a.cmax));  // candidates: w >= cut
+                }
+                const bool partial = (cblock + 1) * kBlockCols > a.nlist;  // block reaches past the last centroid
+                for (int h = 0; h < 2; ++h) {
+                    if (!mbar_wait(&acc_full[h], nacc[h] & 1u)) { failed = 1; break; }
+                    ++nacc[h];
+                    tc_fence_after();
+                    uint32_t r0[32], r1[32];
+                    const int cb0 = part * 64;
+                    __syncwarp();
+                    tmem_ld32(lane_addr + (uint32_t)(h * TCOL + cb0), r0);
+                    tmem_ld32(lane_addr + (uint32_t)(h * TCOL + cb0 + 32), r1);
+                    tmem_ld_wait();
+                    // the accumulators are in registers: hand the tensor memory back before the arithmetic
+                    tc_fence_before();
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[h])) : "memory");
+                    if (q < a.nq) {
 #pragma unroll
-                    for (int j = 1; j < 32; ++j) m = fminf(m, v[j]);
-                    if (m <= cut) {  // rare: some centroid of this chunk is a candidate
+                        for (int half = 0; half < 2; ++half) {
+                            const int cb = cb0 + half * 32;
+                            const int c0 = cblock * kBlockCols + h * TCOL + cb;
+                            float v[32];  // w = q'.c' - |c'|^2 / 2 = -a / 2; -inf beyond the last centroid
+                            const uint32_t* rr = half ? r1 : r0;
+                            if (kAug) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (v[j] <= cut) {
-                                const int pos = atomicAdd(&a.cand_cnt[q], 1);
-                                if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + cb + j;
+                                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[j]);
+                                if (partial) {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) if (c0 + j >= a.nlist) v[j] = __int_as_float(0xff800000);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    const float4 n4 = *reinterpret_cast<const float4*>(&s_cn2[h * TCOL + cb + j]);
+                                    v[j] = fmaf(-0.5f, n4.x, __uint_as_float(rr[j]));
+                                    v[j + 1] = fmaf(-0.5f, n4.y, __uint_as_float(rr[j + 1]));
+                                    v[j + 2] = fmaf(-0.5f, n4.z, __uint_as_float(rr[j + 2]));
+                                    v[j + 3] = fmaf(-0.5f, n4.w, __uint_as_float(rr[j + 3]));
+                                }
+                            }
+                            if (!kSecondPass) {
+                                float* out = a.gmin + (size_t)q * a.ngroups + (c0 >> a.lg_group);
+                                switch (a.lg_group) {  // uniform
+                                    case 5: group_mins<32>(v, out); break;
+                                    case 4: group_mins<16>(v, out); break;
+                                    case 3: group_mins<8>(v, out); break;
+                                    case 2: group_mins<4>(v, out); break;
+                                    case 1: group_mins<2>(v, out); break;
+                                    default: group_mins<1>(v, out); break;
+                                }
+                            } else {
+                                float m[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) m[j] = fmaxf(fmaxf(v[j], v[j + 8]), fmaxf(v[j + 16], v[j + 24]));
+                                const float mm = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
+                                if (mm >= cut) {  // rare: some centroid of this chunk is a candidate
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) {
+                                        if (v[j] >= cut) {
+                                            const int pos = atomicAdd(&a.cand_cnt[q], 1);
+                                            if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + j;
+                                        }
+                                    }
+                                }
                             }
                         }
                     }
                 }
             }
         }
-        tc_fence_before();
-        __syncthreads();  // accumulators and s_cn2 consumed: the next tile may overwrite them
-        phase ^= 1u;
     }
-    if (tid == 0) {
-        if (failed) {
-            atomicExch(a.status, 1);
-            mbar_wait(&bar_b, phase);  // best effort, bounded: let this CTA's own copies land before its memory is released
-        }
-        if (!a_ready) mbar_wait(&bar_a, 0);
-    }
+    if (failed) atomicExch(a.status, 1);
     tc_fence_before();
     __syncthreads();
     __syncwarp();
-    if (warp == 0) tmem_dealloc(tmem, TCOL);
+    if (warp == 0) tmem_dealloc(tmem, 2 * TCOL);
 }
 
 // q' = q - mu as bf16 rows padded with zeros to dimp, and |q'|.
+// aug: 0 = no extra slots, 1 = query rows (slots dim..dim+2 hold 1), 2 = centroid rows (slots hold minus the bf16
+// three-term split of |c'|^2 / 2).
 __global__ void k_tc_prep_rows(const float* __restrict__ x, int n, int dim, int dimp, const float* __restrict__ mu,
-                               __nv_bfloat16* __restrict__ out, float* __restrict__ norm, float* __restrict__ sq) {
+                               __nv_bfloat16* __restrict__ out, float* __restrict__ norm, float* __restrict__ sq, int aug) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n) return;
     float s = 0.0f;
     for (int d = lane; d < dimp; d += 32) {
         float v = 0.0f;
         if (d < dim) v = x[(size_t)warp * dim + d] - mu[d];
-        out[(size_t)warp * dimp + d] = __float2bfloat16_rn(v);
+        if (!(aug && d >= dim && d < dim + 3)) out[(size_t)warp * dimp + d] = __float2bfloat16_rn(v);
         s += v * v;
     }
 #pragma unroll
@@ -276,6 +348,16 @@ __global__ void k_tc_prep_rows(const float* __restrict__ x, int n, int dim, int 
     if (lane == 0) {
         if (norm) norm[warp] = sqrtf(s);
         if (sq) sq[warp] = s;
+        if (aug == 1) {
+            for (int i = 0; i < 3; ++i) out[(size_t)warp * dimp + dim + i] = __float2bfloat16_rn(1.0f);
+        } else if (aug == 2) {
+            float rest = 0.5f * s;
+            for (int i = 0; i < 3; ++i) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(rest);
+                out[(size_t)warp * dimp + dim + i] = __hneg(h);
+                rest -= __bfloat162float(h);
+            }
+        }
     }
 }
 
@@ -411,7 +493,7 @@ psb_status encode_rows_map(CUtensorMap* map, const void* base, long long rows, i
 }  // namespace
 
 int coarse_tc_padded_dim(int dim) { return (dim + KATOM - 1) / KATOM * KATOM; }
-int coarse_tc_tiles(int nlist) { return (nlist + TCOL - 1) / TCOL; }
+int coarse_tc_tiles(int nlist) { return (nlist + kBlockCols - 1) / kBlockCols * 2; }  // whole 512-centroid blocks
 int coarse_tc_cand_cap() { return kCandCap; }
 
 int coarse_tc_group(int nlist, int nprobe) {
@@ -422,7 +504,7 @@ int coarse_tc_group(int nlist, int nprobe) {
 
 bool coarse_tc_supported(int nq, int nlist, int dim, int nprobe) {
     const int dimp = coarse_tc_padded_dim(dim);
-    return nq >= 64 && nlist >= 1024 && dimp <= 256 && nprobe <= 512 && nlist >= 8 * nprobe &&
+    return nq >= 64 && nlist >= 1024 && dimp <= 128 && nprobe <= 512 && nlist >= 8 * nprobe &&
            nlist / coarse_tc_group(nlist, nprobe) >= 4 * nprobe;
 }
 
@@ -434,7 +516,8 @@ psb_status launch_tc_prep_centroids(const float* d_centroids, int nlist, int dim
     count_launch();
     PSB_LAUNCH_CHECK();
     k_tc_prep_rows<<<(nlist * 32 + 255) / 256, 256, 0, s>>>(d_centroids, nlist, dim, dimp, d_mu,
-                                                            static_cast<__nv_bfloat16*>(d_cb), d_cnorm, d_cn2);
+                                                            static_cast<__nv_bfloat16*>(d_cb), d_cnorm, d_cn2,
+                                                            dimp - dim >= 3 ? 2 : 0);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -448,9 +531,10 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     const int ntiles = coarse_tc_tiles(ix.nlist);
     const int group = coarse_tc_group(ix.nlist, nprobe);
     const int ngroups = ntiles * (TCOL / group);
+    const bool aug = dimp - ix.dim >= 3;
     // query side: centre, round to bf16, norms
     k_tc_prep_rows<<<(nq * 32 + 255) / 256, 256, 0, s>>>(d_queries, nq, ix.dim, dimp, ix.mu,
-                                                         static_cast<__nv_bfloat16*>(ws.qb), ws.qnorm, nullptr);
+                                                         static_cast<__nv_bfloat16*>(ws.qb), ws.qnorm, nullptr, aug ? 1 : 0);
     count_launch();
     PSB_LAUNCH_CHECK();
     CUtensorMap map_q, map_c;
@@ -462,23 +546,31 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     while ((1 << a.lg_group) < group) ++a.lg_group;
     a.nprobe = nprobe; a.cn2 = ix.cn2; a.qnorm = ws.qnorm; a.cmax = ix.cmax; a.gmin = ws.gmin; a.seltop = ws.seltop;
     a.cand_cnt = ws.cand_cnt; a.cand = ws.cand; a.status = ws.status;
-    const size_t smem = (size_t)katoms * (TQ + TCOL) * 128 + 1024;
-    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int qtiles = (nq + TQ - 1) / TQ;
-    int slices = (4 * sm_count + qtiles - 1) / qtiles;
-    slices = slices < 1 ? 1 : (slices > ntiles ? ntiles : slices);
-    const dim3 grid(qtiles, slices);
+    const size_t smem = (size_t)katoms * (kStagesA * TQ + 2 * TCOL) * 128 + 1024;
+    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    a.qtiles = (nq + TQ - 1) / TQ;
+    a.cblocks = ntiles / 2;
+    // enough units to fill the SMs a few times over, never more ranges than query tiles
+    a.qsplits = (3 * sm_count + a.cblocks - 1) / a.cblocks;
+    a.qsplits = a.qsplits < 1 ? 1 : (a.qsplits > a.qtiles ? a.qtiles : a.qsplits);
+    const int nunits = a.cblocks * a.qsplits;
+    const dim3 grid(nunits < sm_count ? nunits : sm_count);
+    constexpr int kTcThreads = kTcThreadsV2;
     PSB_CUDA(cudaMemsetAsync(ws.cand_cnt, 0, sizeof(int) * (size_t)nq, s));
     PSB_CUDA(cudaMemsetAsync(ws.n_fail, 0, 2 * sizeof(int), s));  // n_fail, cursor
     if (ws.ev[0]) PSB_CUDA(cudaEventRecord(ws.ev[0], s));
-    k_coarse_tc<false><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
+    if (aug) k_coarse_tc<false, true><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
+    else k_coarse_tc<false, false><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
     if (ws.ev[1]) PSB_CUDA(cudaEventRecord(ws.ev[1], s));
     count_launch();
     PSB_LAUNCH_CHECK();
     PSB_TRY(launch_select_rows(ws.gmin, nq, ngroups, nprobe, ws.selids, ws.seltop, s));
     if (ws.ev[2]) PSB_CUDA(cudaEventRecord(ws.ev[2], s));
-    k_coarse_tc<true><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
+    if (aug) k_coarse_tc<true, true><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
+    else k_coarse_tc<true, false><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
     if (ws.ev[3]) PSB_CUDA(cudaEventRecord(ws.ev[3], s));
     count_launch();
     PSB_LAUNCH_CHECK();

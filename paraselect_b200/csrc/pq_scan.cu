@@ -310,7 +310,7 @@ __device__ __forceinline__ int find_list(const long long* __restrict__ item_off,
 }
 
 template <int M, int V>
-__global__ void __launch_bounds__(kScanThreads, 1) k_scan(const ScanArgs a) {
+__global__ void __launch_bounds__(640, 1) k_scan(const ScanArgs a) {
     extern __shared__ __align__(16) float s_lut[];  // [m*k][V] visitor-interleaved
     __shared__ long long s_item;
     __shared__ int s_list, s_vq[V];
@@ -554,7 +554,9 @@ struct ScanArgsH {
 };
 
 template <int M>
-__global__ void __launch_bounds__(kScanThreads, 1) k_scan_h(const ScanArgsH ah) {
+// launch bound 640 (> the 512 threads launched) caps the kernel at 96 registers, which leaves register-file room for the
+// rerank's gather kernel to run beside it on every SM.
+__global__ void __launch_bounds__(640, 1) k_scan_h(const ScanArgsH ah) {
     const ScanArgs& a = ah.a;
     constexpr int V = kHalfGroup;
     extern __shared__ __align__(16) unsigned char s_raw_h[];

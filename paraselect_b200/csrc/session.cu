@@ -168,6 +168,7 @@ struct psb_session {
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     bool own_stream = false;
+    cudaStream_t aux_stream = nullptr;  // second stream of the overlapped pipeline (created on first use)
     psb_options opt{};
     // index shape
     int nlist = 0, dim = 0, m = 0, k = 0;
@@ -532,7 +533,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     }
     PSB_TRY(s->centroids.reserve(sizeof(float) * (size_t)nlist * s->dim));
     PSB_CUDA(cudaMemcpyAsync(s->centroids.p, index->coarse.centroids, sizeof(float) * (size_t)nlist * s->dim, cudaMemcpyHostToDevice, st));
-    if (opt.coarse_mode != 1 && nlist >= 1024 && coarse_tc_padded_dim(s->dim) <= 256)
+    if (opt.coarse_mode != 1 && nlist >= 1024 && coarse_tc_padded_dim(s->dim) <= 128)
         PSB_TRY(s->tc_index.prepare(index->coarse.centroids, s->centroids.as<float>(), nlist, s->dim, st));
     PSB_TRY(s->offsets.reserve(sizeof(long long) * ((size_t)nlist + 1)));
     PSB_CUDA(cudaMemcpyAsync(s->offsets.p, index->lists.offsets, sizeof(long long) * ((size_t)nlist + 1), cudaMemcpyHostToDevice, st));
@@ -587,6 +588,7 @@ psb_status psb_session_destroy(psb_session* s) {
         if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
         if (s->pinned_ev[i]) cudaEventDestroy(s->pinned_ev[i]);
     }
+    if (s->aux_stream) { cudaStreamSynchronize(s->aux_stream); cudaStreamDestroy(s->aux_stream); }
     if (s->own_stream) cudaStreamDestroy(s->stream);
     delete s;
     cudaGetLastError();
@@ -697,6 +699,120 @@ psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     return PSB_OK;
 }
 
+namespace {
+
+struct StageTimes { double coarse = 0, lut = 0, scan = 0, rerank = 0, map = 0; };
+
+// One batch, device in / device out.  With a rerank from mapped or resident exact rows the batch is cut into
+// sub-batches: coarse + LUT + scan of sub-batch i run on the session's stream while the PCIe gather, exact scoring,
+// selection and id map of sub-batch i-1 run on a second stream, so the transfer hides behind the scan.
+psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, int n, int nprobe, int topk, int stage1_k,
+                         bool rerank, long long* d_ids, float* d_dist, int* d_probes, StageTimes* times) {
+    cudaStream_t st = s->stream;
+    const bool overlap = rerank && s->opt.exact_mode != PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
+    const int parts = overlap ? 4 : 1;
+    const int sb = (n + parts - 1) / parts;
+    if (overlap && !s->aux_stream) PSB_CUDA(cudaStreamCreateWithFlags(&s->aux_stream, cudaStreamNonBlocking));
+    cudaStream_t sx = overlap ? s->aux_stream : st;
+    std::vector<cudaEvent_t> deps;
+    EventTimer tm_s, tm_x;
+    auto cleanup = [&]() { for (auto e : deps) cudaEventDestroy(e); };
+    if (overlap) {  // the second stream starts after everything already queued on the main stream
+        cudaEvent_t e0;
+        PSB_CUDA(cudaEventCreateWithFlags(&e0, cudaEventDisableTiming));
+        deps.push_back(e0);
+        PSB_CUDA(cudaEventRecord(e0, st));
+        PSB_CUDA(cudaStreamWaitEvent(sx, e0, 0));
+    }
+    psb_status rc = PSB_OK;
+    for (int p0 = 0; p0 < n && rc == PSB_OK; p0 += sb) {
+        const int m = std::min(sb, n - p0);
+        const float* q = dq + (size_t)p0 * s->dim;
+        int* probes = d_probes + (size_t)p0 * nprobe;
+        int* rows_out = rerank ? s->cand_rows.as<int>() + (size_t)p0 * stage1_k : s->out_rows.as<int>() + (size_t)p0 * topk;
+        float* dist_out = rerank ? s->cand_dist.as<float>() + (size_t)p0 * stage1_k : d_dist + (size_t)p0 * topk;
+        int* cnt_out = s->cand_count.as<int>() + p0;
+        if (times) rc = tm_s.mark(st);
+        if (rc == PSB_OK) rc = coarse_exact(s, q, m, nprobe, probes, nullptr);
+        if (rc == PSB_OK && times) rc = tm_s.mark(st);
+        if (rc == PSB_OK) rc = launch_build_lut(q, m, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st);
+        if (rc == PSB_OK && times) rc = tm_s.mark(st);
+        ScanWorkspace sws;
+        if (rc == PSB_OK) rc = s->timed_scan_ws(&sws);
+        if (rc == PSB_OK) rc = launch_scan(s->scan_index(), sws, s->lut.as<float>(), m, probes, nprobe, stage1_k, rows_out,
+                                           dist_out, cnt_out, s->sm_count, st);
+        if (rc == PSB_OK && times) rc = tm_s.mark(st);
+        if (rc != PSB_OK) break;
+        if (overlap) {
+            cudaEvent_t e;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { rc = fail(PSB_CUDA_ERROR, "event creation failed"); break; }
+            deps.push_back(e);
+            cudaEventRecord(e, st);
+            cudaStreamWaitEvent(sx, e, 0);
+        }
+        // second half of the sub-batch (on the second stream when overlapping)
+        cudaStream_t keep = s->stream;
+        s->stream = sx;  // rerank_impl and the launchers below run on s->stream
+        if (times) rc = tm_x.mark(sx);
+        if (rc == PSB_OK && rerank) {
+            const unsigned char* qe = static_cast<const unsigned char*>(dq_exact) + (size_t)p0 * s->dim * s->exact_elem;
+            rc = rerank_impl(s, qe, m, rows_out, stage1_k, stage1_k, cnt_out, topk, s->out_rows.as<int>() + (size_t)p0 * topk,
+                             d_dist + (size_t)p0 * topk);
+        }
+        if (rc == PSB_OK && times) rc = tm_x.mark(sx);
+        if (rc == PSB_OK)
+            rc = launch_map_ids(s->out_rows.as<int>() + (size_t)p0 * topk, (long long)m * topk, s->reordered.as<long long>(),
+                                s->row_map(), d_ids + (size_t)p0 * topk, sx);
+        if (rc == PSB_OK && times) rc = tm_x.mark(sx);
+        s->stream = keep;
+    }
+    if (overlap) {  // the main stream continues only after the second stream has finished this batch
+        cudaEvent_t e;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess) {
+            deps.push_back(e);
+            cudaEventRecord(e, sx);
+            cudaStreamWaitEvent(st, e, 0);
+        } else if (rc == PSB_OK) rc = fail(PSB_CUDA_ERROR, "event creation failed");
+    }
+    if (times && rc == PSB_OK) {
+        if (cudaStreamSynchronize(st) != cudaSuccess) rc = fail(PSB_CUDA_ERROR, "stream synchronisation failed");
+        for (size_t i = 0; i + 3 < tm_s.ev.size() + 0 && rc == PSB_OK; i += 4) {
+            times->coarse += tm_s.ms(i, i + 1); times->lut += tm_s.ms(i + 1, i + 2); times->scan += tm_s.ms(i + 2, i + 3);
+        }
+        for (size_t i = 0; i + 2 < tm_x.ev.size() + 0 && rc == PSB_OK; i += 3) {
+            times->rerank += tm_x.ms(i, i + 1); times->map += tm_x.ms(i + 1, i + 2);
+        }
+    }
+    if (deps.size()) {  // events may only be destroyed once the work that waits on them has been submitted: it has
+        cleanup();
+    }
+    return rc;
+}
+
+}  // namespace
+
+psb_status psb_session_search_device(psb_session* s, const float* d_queries, const uint8_t* d_queries_u8, int nq,
+                                     const psb_search_params* params, int64_t* d_indices, float* d_distances,
+                                     int* d_coarse_ids) {
+    if (!s || !params || !d_queries || !d_indices || !d_distances) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (nq < 0 || nq > s->opt.max_batch) return fail(PSB_INVALID_ARGUMENT, "nq must be in 0..max_batch");
+    if (params->nprobe <= 0 || params->nprobe > s->nlist || params->topk <= 0) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist and topk positive");
+    if (params->nprobe > kMaxProbe || params->topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or topk above 2048");
+    if (params->distance != 0) return fail(PSB_UNSUPPORTED_SHAPE, "only squared L2 is supported on this path");
+    if (nq == 0) return PSB_OK;
+    PSB_CUDA(cudaSetDevice(s->device));
+    const int topk = params->topk;
+    const int stage1_k = stage1_width(s, topk);
+    const bool rerank = s->exact_elem != 0 && s->opt.n_rerank > topk;
+    if (stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "candidate width above 2048 is not supported");
+    if (rerank && s->exact_elem == 1 && !d_queries_u8) return fail(PSB_INVALID_ARGUMENT, "u8 rerank needs u8 queries");
+    PSB_TRY(ensure_pipeline_ws(s, nq, params->nprobe, topk, stage1_k));
+    int* probes = d_coarse_ids ? d_coarse_ids : s->probes.as<int>();
+    const void* qe = s->exact_elem == 1 ? static_cast<const void*>(d_queries_u8) : static_cast<const void*>(d_queries);
+    return search_device(s, d_queries, qe, nq, params->nprobe, topk, stage1_k, rerank, reinterpret_cast<long long*>(d_indices),
+                         d_distances, probes, nullptr);
+}
+
 psb_status psb_session_search(psb_session* s, const psb_query_batch_view* queries, const psb_search_params* params,
                               const psb_search_output_view* output, psb_stats* stats) {
     if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
@@ -722,7 +838,8 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
     s->collect_scan_events();
     const double scan_ms0 = s->scan_ms_total;
     const long long scan_n0 = s->scan_launches_total;
-    double t_h2d = 0, t_coarse = 0, t_lut = 0, t_scan = 0, t_rr = 0, t_map = 0, t_d2h = 0;
+    StageTimes times;
+    double t_h2d = 0, t_d2h = 0, t_total = 0;
     long long h2d = 0, d2h = 0;
     int nb = 0;
     for (int q0 = 0; q0 < total; q0 += batch, ++nb) {
@@ -736,25 +853,9 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
             h2d += (long long)n * s->dim;
         }
         if (stats) PSB_TRY(tm.mark(st));
-        PSB_TRY(coarse_exact(s, s->q.as<float>(), n, nprobe, s->probes.as<int>(), nullptr));
-        if (stats) PSB_TRY(tm.mark(st));
-        PSB_TRY(launch_build_lut(s->q.as<float>(), n, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st));
-        if (stats) PSB_TRY(tm.mark(st));
-        int* rows_out = rerank ? s->cand_rows.as<int>() : s->out_rows.as<int>();
-        float* dist_out = rerank ? s->cand_dist.as<float>() : s->out_dist.as<float>();
-        ScanWorkspace sws;
-        PSB_TRY(s->timed_scan_ws(&sws));
-        PSB_TRY(launch_scan(s->scan_index(), sws, s->lut.as<float>(), n, s->probes.as<int>(), nprobe, stage1_k,
-                            rows_out, dist_out, s->cand_count.as<int>(), s->sm_count, st));
-        if (stats) PSB_TRY(tm.mark(st));
-        if (rerank) {
-            const void* dq = s->exact_elem == 4 ? s->q.p : s->q_u8.p;
-            PSB_TRY(rerank_impl(s, dq, n, s->cand_rows.as<int>(), stage1_k, stage1_k, s->cand_count.as<int>(), topk,
-                                s->out_rows.as<int>(), s->out_dist.as<float>()));
-        }
-        if (stats) PSB_TRY(tm.mark(st));
-        PSB_TRY(launch_map_ids(s->out_rows.as<int>(), (long long)n * topk, s->reordered.as<long long>(), s->row_map(),
-                               s->out_ids.as<long long>(), st));
+        const void* qe = s->exact_elem == 1 ? s->q_u8.p : s->q.p;
+        PSB_TRY(search_device(s, s->q.as<float>(), qe, n, nprobe, topk, stage1_k, rerank, s->out_ids.as<long long>(),
+                              s->out_dist.as<float>(), s->probes.as<int>(), stats ? &times : nullptr));
         if (stats) PSB_TRY(tm.mark(st));
         PSB_CUDA(cudaMemcpyAsync(output->indices + (size_t)q0 * topk, s->out_ids.p, sizeof(long long) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
         PSB_CUDA(cudaMemcpyAsync(output->distances + (size_t)q0 * topk, s->out_dist.p, sizeof(float) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
@@ -765,19 +866,16 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         }
         if (stats) PSB_TRY(tm.mark(st));
         PSB_CUDA(cudaStreamSynchronize(st));
-        if (stats) {
-            t_h2d += tm.ms(0, 1); t_coarse += tm.ms(1, 2); t_lut += tm.ms(2, 3); t_scan += tm.ms(3, 4);
-            t_rr += tm.ms(4, 5); t_map += tm.ms(5, 6); t_d2h += tm.ms(6, 7);
-        }
+        if (stats) { t_h2d += tm.ms(0, 1); t_d2h += tm.ms(2, 3); t_total += tm.ms(0, 3); }
     }
     PSB_TRY(s->tc_work.check_status());
     if (stats) {
         unsigned long long c1[4];
         PSB_CUDA(cudaMemcpyAsync(c1, s->scalars.p, sizeof(c1), cudaMemcpyDeviceToHost, st));
         PSB_CUDA(cudaStreamSynchronize(st));
-        stats->h2d_ms = t_h2d; stats->coarse_search_ms = t_coarse; stats->pq_lut_build_ms = t_lut;
-        stats->pq_adc_scan_ms = t_scan; stats->pq_rerank_ms = t_rr; stats->pq_map_ids_ms = t_map; stats->d2h_ms = t_d2h;
-        stats->total_ms = t_h2d + t_coarse + t_lut + t_scan + t_rr + t_map + t_d2h;
+        stats->h2d_ms = t_h2d; stats->coarse_search_ms = times.coarse; stats->pq_lut_build_ms = times.lut;
+        stats->pq_adc_scan_ms = times.scan; stats->pq_rerank_ms = times.rerank; stats->pq_map_ids_ms = times.map; stats->d2h_ms = t_d2h;
+        stats->total_ms = t_total;  // stage times can overlap: their sum may exceed the total
         stats->pq_scanned_codes = (long long)(c1[0] - c0[0]);
         stats->pq_adc_lookups = stats->pq_scanned_codes * s->m;
         stats->threshold_candidates = (long long)(c1[1] - c0[1]);

@@ -16,7 +16,7 @@ def check(psb, q, c, nprobe):
 
 
 @pytest.mark.parametrize("nq,nlist,dim,nprobe", [(300, 4096, 96, 64), (130, 1024, 128, 32), (200, 2148, 100, 16),
-                                                  (1000, 8192, 64, 128), (64, 5000, 192, 8), (257, 3000, 32, 1)])
+                                                  (1000, 8192, 64, 128), (64, 5000, 128, 8), (257, 3000, 32, 1)])
 def test_tc_coarse_matches_checker_gaussian(psb, nq, nlist, dim, nprobe):
     rng = np.random.default_rng(nq + nlist)
     q = rng.standard_normal((nq, dim)).astype(np.float32)

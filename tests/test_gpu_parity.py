@@ -379,3 +379,29 @@ def test_half_prefilter_scan_extreme_table_values(psb):
         _, rows, dist, cnt, _ = run_stage_scan(psb, ix, q, probes, 200)
         orow, odist, ocnt, _ = oracle.pq_scan(q, probes, ix["offsets"], ix["codes"], ix["codebook"], 200)
         assert np.array_equal(rows, orow) and np.array_equal(dist, odist)
+
+
+# ---------------------------------------------------------------------------------------------- overlapped pipeline
+def test_overlapped_pipeline_equals_serial_pipeline(psb):
+    """Batches of >= 2048 queries run as sub-batches whose rerank overlaps the next scan on a second stream; results
+    must equal the serial pipeline's and the checker's."""
+    torch = _torch()
+    ix = synth.make_index(60000, 64, 64, 16, seed=61, zipf=True)
+    q = synth.make_queries(ix, 2600, seed=62, weights=synth.zipf_weights(64))
+    res = {}
+    for serial in (False, True):
+        with psb.Session(ix, n_rerank=120, serial_pipeline=serial) as s:
+            res[serial] = s.search(q, 8, 10, batch_size=2600, want_coarse=True)
+    for k in ("indices", "distances", "coarse"):
+        assert np.array_equal(res[False][k], res[True][k])
+    want = oracle.ivfpq_search(ix, q[:200], 8, 10, 120)
+    assert np.array_equal(res[False]["indices"][:200], want["indices"])
+    assert np.array_equal(res[False]["distances"][:200], want["distances"])
+    # device-resident entry point
+    with psb.Session(ix, n_rerank=120, max_batch=2600) as s:
+        ids = torch.empty((2600, 10), dtype=torch.int64, device="cuda")
+        dd = torch.empty((2600, 10), dtype=torch.float32, device="cuda")
+        s.search_device(dev(q), 2600, 8, 10, ids, dd)
+        s.sync()
+        assert np.array_equal(ids.cpu().numpy(), res[True]["indices"])
+        assert np.array_equal(dd.cpu().numpy(), res[True]["distances"])
