@@ -321,8 +321,9 @@ def main():
         assert np.array_equal(dev_ids, e2e_ids), "stage-level and end-to-end results differ"
 
     launches = int(c["kernel_launches"] - 0)
+    launches_per_step = max(1, c["scan_kernel_launches"]) / max(1, args.steps)  # one per sub-batch
     scan_ms = c["scan_kernel_ms"] / max(1, c["scan_kernel_launches"])
-    S = c["pq_scanned_codes"] / max(1, args.steps)
+    S = c["pq_scanned_codes"] / max(1, args.steps) / launches_per_step  # rows per launch
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -333,6 +334,7 @@ def main():
     roofline = dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak, unit="GB/s",
                     frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
                     algorithmic_bytes_per_launch=int(S * cfg["M"]), rows_per_launch=int(S), ms_per_launch=round(scan_ms, 3),
+                    launches_per_step=launches_per_step,
                     traffic=None,
                     lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / 148 / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
 
@@ -370,7 +372,7 @@ def main():
         stages_ms=dict(coarse=round(stats["coarse_search_ms"], 3), lut=round(stats["pq_lut_build_ms"], 3),
                        scan=round(stats["pq_adc_scan_ms"], 3), rerank=round(stats["pq_rerank_ms"], 3),
                        map_ids=round(stats["pq_map_ids_ms"], 3), h2d=round(stats["h2d_ms"], 3), d2h=round(stats["d2h_ms"], 3)),
-        counters=dict(scanned_codes_per_step=int(S), admitted_per_step=int(c["threshold_candidates"] / max(1, args.steps)),
+        counters=dict(scanned_codes_per_step=int(S * launches_per_step), admitted_per_step=int(c["threshold_candidates"] / max(1, args.steps)),
                       fallback_queries_per_step=c["fallback_queries"] / max(1, args.steps)),
         parity=parity,
         result_checksum=int(np.bitwise_xor.reduce((e2e_ids.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel())

@@ -231,14 +231,27 @@ k_merge(const int* __restrict__ rows, const float* __restrict__ dist, int parts,
 
 }  // namespace
 
+// The rerank kernels ask for the maximum shared-memory carve-out although they use little or none: an SM can only run
+// kernels of one carve-out at a time, and the scan and coarse kernels they run beside (on the other stream of the
+// overlapped pipeline) need nearly all of it.  With the default carve-out the SMs would have to drain between them.
+template <typename F>
+psb_status prefer_max_shared(F kernel) {
+    PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    return PSB_OK;
+}
+
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
                               void* d_stage, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
+    // Few, fat CTAs on purpose: 32 CTAs of 512 threads keep ~200 KB of row reads in flight - more than the PCIe
+    // bandwidth-delay product - while touching only 32 SMs, so a scan kernel running beside it on the other stream keeps
+    // most SMs to itself (its dynamic work queue shifts work away from the shared ones).
     const long long total = (long long)nq * candidate_count;
-    long long blocks = (total * 32 + 255) / 256;
-    if (blocks > 148 * 64) blocks = 148 * 64;
-    k_gather_rows<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
+    long long blocks = (total * 32 + 511) / 512;
+    if (blocks > 32) blocks = 32;
+    PSB_TRY(prefer_max_shared(k_gather_rows));
+    k_gather_rows<<<(unsigned)blocks, 512, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
                                                    d_candidates, nq, candidate_count, candidate_stride, d_counts,
                                                    static_cast<unsigned char*>(d_stage));
     count_launch();
@@ -251,6 +264,7 @@ psb_status launch_rerank_score(const void* d_stage, const RowMap& mp, int dim, i
                                const int* d_counts, float* d_out_dist, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
     dim3 grid(nq, (candidate_count + kScoreThreads / 16 - 1) / (kScoreThreads / 16));
+    PSB_TRY(prefer_max_shared(k_rerank_score));
     k_rerank_score<<<grid, kScoreThreads, (size_t)dim * elem_bytes, s>>>(
         static_cast<const unsigned char*>(d_stage), mp, dim, elem_bytes, static_cast<const unsigned char*>(d_queries),
         d_candidates, candidate_count, candidate_stride, d_counts, d_out_dist);
@@ -269,6 +283,7 @@ psb_status launch_topk_select(const float* d_dist, const int* d_candidates, int 
     const size_t smem = (size_t)np * 12;
     if (smem > 32 * 1024)
         PSB_CUDA(cudaFuncSetAttribute(k_topk_select, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PSB_TRY(prefer_max_shared(k_topk_select));
     k_topk_select<<<nq, kSelectThreads, smem, s>>>(d_dist, d_candidates, candidate_count, candidate_stride, d_counts,
                                                    topk, np, d_out_rows, d_out_dist);
     count_launch();
@@ -279,6 +294,7 @@ psb_status launch_topk_select(const float* d_dist, const int* d_candidates, int 
 psb_status launch_map_ids(const int* d_rows, long long n, const long long* d_reordered, const RowMap& mp,
                           long long* d_out, cudaStream_t s) {
     if (n <= 0) return PSB_OK;
+    PSB_TRY(prefer_max_shared(k_map_ids));
     k_map_ids<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_rows, n, d_reordered, mp, d_out);
     count_launch();
     PSB_LAUNCH_CHECK();
