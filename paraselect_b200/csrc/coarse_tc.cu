@@ -306,12 +306,19 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) m[j] = fmaxf(fmaxf(v[j], v[j + 8]), fmaxf(v[j + 16], v[j + 24]));
                                 const float mm = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
-                                if (mm >= cut) {  // rare: some centroid of this chunk is a candidate
+                                if (mm >= cut) {  // some centroid of this chunk is a candidate (about one chunk in ten)
+                                    // m[j] covers v[j], v[j+8], v[j+16], v[j+24]: expand only the groups that hold one, so a
+                                    // warp whose lanes hit in different places executes a few short blocks, not all 32 tests
 #pragma unroll
-                                    for (int j = 0; j < 32; ++j) {
-                                        if (v[j] >= cut) {
-                                            const int pos = atomicAdd(&a.cand_cnt[q], 1);
-                                            if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + j;
+                                    for (int j = 0; j < 8; ++j) {
+                                        if (m[j] >= cut) {
+#pragma unroll
+                                            for (int i = 0; i < 4; ++i) {
+                                                if (v[j + 8 * i] >= cut) {
+                                                    const int pos = atomicAdd(&a.cand_cnt[q], 1);
+                                                    if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + j + 8 * i;
+                                                }
+                                            }
                                         }
                                     }
                                 }

@@ -127,7 +127,7 @@ struct RowMap {
 // device) to stage [nq][candidate_count][dim].  Candidates are global rows.
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
-                              void* d_stage, cudaStream_t s);
+                              void* d_stage, cudaStream_t s, bool compact = false);
 // d_out_dist [nq][candidate_count]: exact distance of each staged candidate, +inf for rows not held here.
 psb_status launch_rerank_score(const void* d_stage, const RowMap& mp, int dim, int elem_bytes, const void* d_queries,
                                const int* d_candidates, int nq, int candidate_count, int candidate_stride,

@@ -242,18 +242,26 @@ psb_status prefer_max_shared(F kernel) {
 
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
-                              void* d_stage, cudaStream_t s) {
+                              void* d_stage, cudaStream_t s, bool compact) {
     if (nq <= 0) return PSB_OK;
-    // Few, fat CTAs on purpose: 32 CTAs of 512 threads keep ~200 KB of row reads in flight - more than the PCIe
-    // bandwidth-delay product - while touching only 32 SMs, so a scan kernel running beside it on the other stream keeps
-    // most SMs to itself (its dynamic work queue shifts work away from the shared ones).
     const long long total = (long long)nq * candidate_count;
-    long long blocks = (total * 32 + 511) / 512;
-    if (blocks > 32) blocks = 32;
     PSB_TRY(prefer_max_shared(k_gather_rows));
-    k_gather_rows<<<(unsigned)blocks, 512, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
-                                                   d_candidates, nq, candidate_count, candidate_stride, d_counts,
-                                                   static_cast<unsigned char*>(d_stage));
+    if (compact) {
+        // Beside a scan kernel on the other stream of the overlapped pipeline: few, fat CTAs.  32 CTAs of 512 threads keep
+        // ~200 KB of row reads in flight - more than the PCIe bandwidth-delay product - while touching only 32 SMs, so the
+        // scan keeps most SMs to itself (its dynamic work queue shifts work away from the shared ones).
+        long long blocks = (total * 32 + 511) / 512;
+        if (blocks > 32) blocks = 32;
+        k_gather_rows<<<(unsigned)blocks, 512, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
+                                                       d_candidates, nq, candidate_count, candidate_stride, d_counts,
+                                                       static_cast<unsigned char*>(d_stage));
+    } else {
+        long long blocks = (total * 32 + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        k_gather_rows<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
+                                                       d_candidates, nq, candidate_count, candidate_stride, d_counts,
+                                                       static_cast<unsigned char*>(d_stage));
+    }
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

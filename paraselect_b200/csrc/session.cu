@@ -455,7 +455,7 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
         PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
-                                   s->stage.p, s->stream));
+                                   s->stage.p, s->stream, s->aux_stream != nullptr && s->stream == s->aux_stream));
     }
     float* score = d_score;
     if (!score) {

@@ -26,14 +26,20 @@ import time
 import numpy as np
 
 
-def stripe_layout(offsets, rank, world):
-    """Slice of every list held by `rank`: returns (global_begin [nlist], local_offsets [nlist+1]).
+def stripe_layout(offsets, rank, world, min_slice=4096):
+    """Rows of every list held by `rank`: returns (global_begin [nlist], local_offsets [nlist+1]).
 
-    List l = rows [offsets[l], offsets[l+1]) is cut into `world` contiguous parts at floor(len * g / world)."""
+    A list with at least world * min_slice rows is cut into `world` contiguous slices at floor(len * g / world), one per
+    rank, so that a few huge lists cannot pin one rank.  A shorter list goes whole to rank (list % world): slicing it
+    would leave every rank with the same number of (tiny) work items and nothing to gain.  The other ranks hold an
+    empty range of it."""
     offsets = np.asarray(offsets, np.int64)
+    nlist = offsets.size - 1
     length = offsets[1:] - offsets[:-1]
-    lo = offsets[:-1] + (length * rank) // world
-    hi = offsets[:-1] + (length * (rank + 1)) // world
+    big = length >= world * min_slice
+    mine = (np.arange(nlist) % world) == rank
+    lo = np.where(big, offsets[:-1] + (length * rank) // world, offsets[:-1])
+    hi = np.where(big, offsets[:-1] + (length * (rank + 1)) // world, np.where(mine, offsets[1:], offsets[:-1]))
     local = np.zeros(offsets.size, np.int64)
     local[1:] = np.cumsum(hi - lo)
     return lo, local
@@ -99,27 +105,48 @@ class ShardedSearch:
         self.o_rows = engine.empty((nq, topk), t.int32)
         self.o_dist = engine.empty((nq, topk), t.float32)
         self.o_ids = engine.empty((nq, topk), t.int64)
+        self.marks = None
 
-    def step(self, dq):
+    def _mark(self, name):
+        if self.marks is not None:
+            ev = self.torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
+
+    def stage_times(self):
+        """Milliseconds between the marks of the last profiled step (after a device synchronisation)."""
+        m = self.marks or []
+        return {m[i + 1][0]: round(m[i][1].elapsed_time(m[i + 1][1]), 3) for i in range(len(m) - 1)}
+
+    def step(self, dq, profile=False):
         e, d, nq = self.e, self.dist, self.nq
+        self.marks = [] if profile else None
+        self._mark("start")
         e.coarse(dq, nq, self.nprobe, self.probes)
+        self._mark("coarse")
         e.lut(dq, nq, self.lut)
         e.scan(self.lut, nq, self.probes, self.nprobe, self.width, self.l_rows, self.l_dist, self.l_cnt)
+        self._mark("lut+scan")
         self._sync_to_collectives()
         if self.world > 1:
             d.all_gather_into_tensor(self.g_rows.view(self.world * nq, self.width), self.l_rows)
             d.all_gather_into_tensor(self.g_dist.view(self.world * nq, self.width), self.l_dist)
             self._sync_from_collectives()
+            self._mark("all_gather")
             e.merge(self.g_rows, self.g_dist, self.world, nq, self.width, self.m_rows, self.m_dist)
+            self._mark("merge")
         else:
             self.m_rows, self.m_dist = self.l_rows, self.l_dist
         if self.rerank:
             e.rerank_partial(dq, nq, self.m_rows, self.width, self.p_dist)
+            self._mark("rerank_partial")
             self._sync_to_collectives()
             if self.world > 1:
                 d.all_reduce(self.p_dist, op=d.ReduceOp.MIN)
                 self._sync_from_collectives()
+                self._mark("all_reduce_min")
             e.select_topk(self.p_dist, self.m_rows, nq, self.width, self.topk, self.o_rows, self.o_dist)
+            self._mark("select_topk")
         else:
             self.o_rows.copy_(self.m_rows[:, :self.topk])
             self.o_dist.copy_(self.m_dist[:, :self.topk])
@@ -128,6 +155,7 @@ class ShardedSearch:
         if self.world > 1:
             d.all_reduce(self.o_ids, op=d.ReduceOp.MAX)
             self._sync_from_collectives()
+        self._mark("map_ids+all_reduce_max")
         return self.o_ids, self.o_dist
 
     # The engine and torch.distributed are driven from one stream (the bench makes it torch's current stream), so
@@ -203,6 +231,9 @@ def bench_main(args, cfg, rank, world, local_rank):
 
         e2e_step()
         ms_e2e = timed(e2e_step)
+        search.step(dq, profile=True)
+        torch.cuda.synchronize()
+        stage_ms = search.stage_times()
         clocks = sampler.stop()
         torch.cuda.synchronize()
         # totals over ranks
@@ -239,7 +270,7 @@ def bench_main(args, cfg, rank, world, local_rank):
                           algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3), traffic=None,
                           note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
             counters=dict(scanned_codes_per_step=int(S), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
-            result_checksum=checksum, clocks=clocks)
+            stages_ms_rank0=stage_ms, result_checksum=checksum, clocks=clocks)
         print(json.dumps(line), flush=True)
     sess.close()
     dist.barrier()

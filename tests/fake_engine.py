@@ -88,10 +88,10 @@ class CpuCheckerEngine:
         out.copy_(torch.from_numpy(ids.reshape(out.shape).astype(np.int64)))
 
 
-def stripe_index(ix, rank, world):
-    """Local (striped) view of a whole synthetic index for `rank`."""
+def stripe_index(ix, rank, world, min_slice=64):
+    """Local (striped) view of a whole synthetic index for `rank` (small min_slice: the test lists are small)."""
     from paraselect_b200.multi import stripe_layout
-    gb, loff = stripe_layout(ix["offsets"], rank, world)
+    gb, loff = stripe_layout(ix["offsets"], rank, world, min_slice=min_slice)
     keep = np.concatenate([np.arange(gb[l], gb[l] + (loff[l + 1] - loff[l])) for l in range(gb.size)]).astype(np.int64)
     local = dict(ix)
     local.update(offsets=loff, reordered_ids=ix["reordered_ids"][keep], codes=ix["codes"][keep],

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 @pytest.mark.parametrize("world", [1, 2, 3, 8])
 def test_stripes_partition_every_list(world):
     rng = np.random.default_rng(world)
-    sizes = np.concatenate([rng.integers(0, 50, 40), [0, 1, 5000, 7]])
+    sizes = np.concatenate([rng.integers(0, 50, 40), [0, 1, 5000, 7, 40000, 100001]])
     offsets = np.zeros(sizes.size + 1, np.int64)
     offsets[1:] = np.cumsum(sizes)
     seen = np.zeros(offsets[-1], np.int32)
@@ -23,7 +23,9 @@ def test_stripes_partition_every_list(world):
         gb, loff = stripe_layout(offsets, r, world)
         length = loff[1:] - loff[:-1]
         assert np.all(gb >= offsets[:-1]) and np.all(gb + length <= offsets[1:])
-        assert np.all(length >= sizes // world) and np.all(length <= sizes // world + 1)
+        big = sizes >= world * 4096
+        assert np.all(length[big] >= sizes[big] // world) and np.all(length[big] <= sizes[big] // world + 1)
+        assert np.all((length[~big] == 0) | (length[~big] == sizes[~big]))
         mask = owned_mask_rows(gb, loff, 0, int(offsets[-1]))
         assert mask.sum() == loff[-1]
         seen += mask
