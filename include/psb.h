@@ -135,7 +135,12 @@ typedef struct psb_options {
     int serial_pipeline;/* 1 = never overlap the rerank of one sub-batch with the scan of the next (diagnostics) */
     int scan_mode;      /* 0 = auto (fp16 pre-filter scan with exact fp32 re-scoring when it fits), 1 = fp32 scan only;
                            both give identical results */
-    int reserved[4];
+    int adc_mode;       /* PQAdcDistanceMode (src/search/kernels/fine/fine_search_strategy.h:21-24): 0 = Plain (codes
+                           encode the row), 1 = Residual (codes encode row - centroid[list]).  Residual mode follows
+                           cpu_fine_kernel_pq_resid_cpu_lut_timed (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:594-735):
+                           one table per (query, probe) on q - centroid, candidate width max(n_rerank, topk, 512), and
+                           the exact rerank always runs (exact rows are required). */
+    int reserved[3];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -225,6 +230,15 @@ psb_status psb_stage_coarse(psb_session* session, const float* d_queries, int nq
  * (src/search/kernels/fine/gpu_fine/pq_adc/pq_query_lut.cu:14-35) and
  * src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:51-63.  d_lut [nq][subvectors][codebook_size]. */
 psb_status psb_stage_build_lut(psb_session* session, const float* d_queries, int nq, float* d_lut);
+
+/* Residual mode tables: lut[q][p][m][c] = sum_d ((q - centroid[probes[q][p]])[m*dsub+d] - codebook[m][c][d])^2, one
+ * table per (query, probe) pair.  Replaces build_query_residual + build_lut of the reference's CPU residual path
+ * (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:87-130,440-451) and has the layout of its precomputed-LUT
+ * argument (src/search/ivfrespq/stage/ivfrespq_query_scheduler.h:226-228).  d_probes [nq][nprobe] int32 (entries
+ * outside [0, nlist) leave their table untouched), d_lut [nq][nprobe][subvectors][codebook_size].  A session created
+ * with adc_mode = 1 expects this layout in psb_stage_scan. */
+psb_status psb_stage_build_lut_residual(psb_session* session, const float* d_queries, int nq, const int* d_probes,
+                                        int nprobe, float* d_lut);
 
 /* ADC scan of the probed lists with per-query selection of the stage1_k smallest distances
  * (ties by row).  Replaces ivfpq_fine_cpu_lut (src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:69-117) and

@@ -164,6 +164,48 @@ def ivfpq_search(index, queries, nprobe, topk, n_rerank):
     return dict(indices=out_i, distances=out_d, coarse=out_c, stage1=out_s, scanned=scanned.value)
 
 
+def pq_scan_residual(queries, probes, centroids, offsets, codes, codebook, stage1_k, want_luts=False):
+    """Stage 1 of the residual mode; returns rows, dist, count, scanned (and the tables [nq][nprobe][M*K])."""
+    queries = _c(queries, np.float32); probes = _c(probes, np.int64); offsets = _c(offsets, np.int64)
+    centroids = _c(centroids, np.float32); codes = _c(codes, np.uint8); codebook = _c(codebook, np.float32)
+    nq, dim = queries.shape
+    M, K, _ = codebook.shape
+    rows = np.empty((nq, stage1_k), np.int32); dist = np.empty((nq, stage1_k), np.float32)
+    cnt = np.empty(nq, np.int32); scanned = C.c_longlong()
+    luts = np.zeros((nq, probes.shape[1], M * K), np.float32) if want_luts else None
+    rc = lib().psbo_pq_scan_residual(_ptr(queries), nq, dim, _ptr(probes), probes.shape[1], _ptr(centroids),
+                                     _ptr(offsets), offsets.size - 1, _ptr(codes), _ptr(codebook), M, K, stage1_k,
+                                     _ptr(rows), _ptr(dist), _ptr(cnt), _ptr(luts), C.byref(scanned))
+    if rc:
+        raise ValueError("oracle residual scan: invalid arguments")
+    return (rows, dist, cnt, scanned.value, luts) if want_luts else (rows, dist, cnt, scanned.value)
+
+
+def residual_stage1_width(topk, n_rerank):
+    return int(lib().psbo_residual_stage1_width(topk, n_rerank))
+
+
+def ivfrespq_search(index, queries, nprobe, topk, n_rerank):
+    """Residual ADC mode (codes encode x - centroid[list]); index as for ivfpq_search, vectors required."""
+    queries = _c(queries, np.float32)
+    nq, dim = queries.shape
+    cen = _c(index["centroids"], np.float32); off = _c(index["offsets"], np.int64)
+    rid = _c(index["reordered_ids"], np.int64); codes = _c(index["codes"], np.uint8)
+    cb = _c(index["codebook"], np.float32); vec = _c(index["vectors"], np.float32)
+    M, K, _ = cb.shape
+    n = codes.shape[0]
+    s1 = residual_stage1_width(topk, n_rerank)
+    out_i = np.empty((nq, topk), np.int64); out_d = np.empty((nq, topk), np.float32)
+    out_c = np.empty((nq, nprobe), np.int64); out_s = np.empty((nq, s1), np.int32); out_n = np.empty(nq, np.int32)
+    scanned = C.c_longlong()
+    rc = lib().psbo_ivfrespq_search(_ptr(cen), cen.shape[0], dim, _ptr(off), _ptr(rid), C.c_int64(n), _ptr(codes),
+                                    _ptr(cb), M, K, _ptr(vec), _ptr(queries), nq, nprobe, topk, n_rerank,
+                                    _ptr(out_i), _ptr(out_d), _ptr(out_c), _ptr(out_s), _ptr(out_n), C.byref(scanned))
+    if rc:
+        raise ValueError("oracle ivfrespq_search: invalid arguments")
+    return dict(indices=out_i, distances=out_d, coarse=out_c, stage1=out_s, stage1_count=out_n, scanned=scanned.value)
+
+
 def ivfflat_search(centroids, offsets, reordered_ids, base, queries, nprobe, topk):
     queries = _c(queries, np.float32); centroids = _c(centroids, np.float32); base = _c(base, np.float32)
     offsets = _c(offsets, np.int64)
@@ -248,6 +290,27 @@ def ref_ivfpq_search(index, queries, probes, topk, n_rerank, fine_threads=1, rer
     if rc:
         raise RuntimeError(ref().psbref_last_error().decode())
     return dict(indices=out_i, distances=out_d, stage1=out_s, times_ms=times, scanned=scanned.value)
+
+
+def ref_ivfrespq_search(index, queries, probes, topk, n_rerank, threads=1):
+    queries = _c(queries, np.float32); probes = _c(probes, np.int64)
+    nq, dim = queries.shape
+    nprobe = probes.shape[1]
+    cen = _c(index["centroids"], np.float32); off = _c(index["offsets"], np.int64)
+    rid = _c(index["reordered_ids"], np.int64); codes = _c(index["codes"], np.uint8)
+    cb = _c(index["codebook"], np.float32); vec = _c(index["vectors"], np.float32)
+    M, K, _ = cb.shape
+    n = codes.shape[0]
+    out_l = np.empty((nq, topk), np.int32); out_i = np.empty((nq, topk), np.int64)
+    out_d = np.full((nq, topk), np.finfo(np.float32).max, np.float32)
+    times = np.zeros(3, np.float64); scanned = C.c_longlong()
+    rc = ref().psbref_ivfrespq_search(_ptr(cen), cen.shape[0], dim, _ptr(off), _ptr(rid), C.c_int64(n), _ptr(codes),
+                                      _ptr(cb), M, K, _ptr(vec), _ptr(queries), nq, _ptr(probes), nprobe, topk,
+                                      n_rerank, threads, _ptr(out_l), _ptr(out_i), _ptr(out_d), _ptr(times),
+                                      C.byref(scanned))
+    if rc:
+        raise RuntimeError(ref().psbref_last_error().decode())
+    return dict(indices=out_i, distances=out_d, local=out_l, times_ms=times, scanned=scanned.value)
 
 
 def ref_rerank(base, queries, candidates, topk, candidate_count=None, counts=None, threads=1, prefetch=4):

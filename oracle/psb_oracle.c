@@ -335,6 +335,105 @@ int psbo_ivfpq_search(const float* centroids, int nlist, int dim,
     return rc;
 }
 
+/* ---- residual IVF-PQ (codes encode x - centroid[list]) ------------------------- */
+
+/* ADC sum in the order of src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:
+ *   M == 16, K == 256 (:226-242) and M == 8, K == 256 (:250-259): balanced pairwise tree,
+ *   every other shape (:203-217): sequential. */
+static float resid_adc(const float* lut, const uint8_t* code, int pq_m, int pq_k) {
+    if (pq_k == 256 && (pq_m == 16 || pq_m == 8)) {
+        float s[16];
+        for (int j = 0; j < pq_m; ++j) s[j] = lut[(size_t)j * 256 + code[j]];
+        for (int n = pq_m; n > 1; n >>= 1)
+            for (int j = 0; j < n / 2; ++j) s[j] = s[2 * j] + s[2 * j + 1];
+        return s[0];
+    }
+    float d = 0.0f;
+    for (int j = 0; j < pq_m; ++j) d += lut[(size_t)j * pq_k + code[j]];
+    return d;
+}
+
+/* Stage 1 of the residual mode: per (query, probe) table on q - centroid[list]
+ * (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:440-451 residual, :113-128 table entries:
+ * sequential fp32 sum, no FMA; src/search/ivfrespq/stage/ivfrespq_query_scheduler.h:142-254 probe loop),
+ * the stage1_k smallest ADC distances per query.  luts_out (optional) [nq][nprobe][M][K].
+ * Ties by (distance, row) ascending. */
+int psbo_pq_scan_residual(const float* queries, int nq, int dim, const int64_t* probes, int nprobe,
+                          const float* centroids, const int64_t* offsets, int nlist, const uint8_t* codes,
+                          const float* codebook, int pq_m, int pq_k, int stage1_k, int* out_rows, float* out_dist,
+                          int* out_count, float* luts_out, long long* scanned_rows) {
+    if (pq_m <= 0 || dim % pq_m || stage1_k <= 0) return 1;
+    const int dsub = dim / pq_m;
+    long long scanned_total = 0;
+#pragma omp parallel reduction(+ : scanned_total)
+    {
+        float* lut = (float*)malloc(sizeof(float) * (size_t)pq_m * pq_k);
+        float* resid = (float*)malloc(sizeof(float) * (size_t)dim);
+        pair_t* heap = (pair_t*)malloc(sizeof(pair_t) * (size_t)stage1_k);
+#pragma omp for schedule(dynamic, 1)
+        for (int q = 0; q < nq; ++q) {
+            topk_t t; topk_init(&t, heap, stage1_k);
+            for (int p = 0; p < nprobe; ++p) {
+                int64_t list = probes[(size_t)q * nprobe + p];
+                if (list < 0 || list >= nlist) continue;
+                if (offsets[list + 1] <= offsets[list] && !luts_out) continue;
+                for (int d = 0; d < dim; ++d) resid[d] = queries[(size_t)q * dim + d] - centroids[(size_t)list * dim + d];
+                psbo_pq_lut(resid, codebook, pq_m, pq_k, dsub, lut);
+                if (luts_out) memcpy(luts_out + ((size_t)q * nprobe + p) * pq_m * pq_k, lut, sizeof(float) * (size_t)pq_m * pq_k);
+                for (int64_t row = offsets[list]; row < offsets[list + 1]; ++row) {
+                    topk_push(&t, resid_adc(lut, codes + (size_t)row * pq_m, pq_m, pq_k), row);
+                    ++scanned_total;
+                }
+            }
+            topk_finish(&t);
+            for (int i = 0; i < stage1_k; ++i) {
+                out_rows[(size_t)q * stage1_k + i] = i < t.n ? (int)heap[i].i : -1;
+                if (out_dist) out_dist[(size_t)q * stage1_k + i] = i < t.n ? heap[i].d : FLT_MAX;
+            }
+            if (out_count) out_count[q] = t.n;
+        }
+        free(lut); free(resid); free(heap);
+    }
+    if (scanned_rows) *scanned_rows = scanned_total;
+    return 0;
+}
+
+/* Candidate width of the residual mode: max(n_rerank, topk, 512)
+ * (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:623-625). */
+int psbo_residual_stage1_width(int topk, int n_rerank) {
+    int w = n_rerank < topk ? topk : n_rerank;
+    return w < 512 ? 512 : w;
+}
+
+/* Whole residual search: coarse, stage 1 above, exact rerank of the candidates (always, with their counts:
+ * src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:722-730), id map.  out_stage1 [nq][width] (optional). */
+int psbo_ivfrespq_search(const float* centroids, int nlist, int dim,
+                         const int64_t* offsets, const int64_t* reordered_ids, int64_t n_vectors,
+                         const uint8_t* codes, const float* codebook, int pq_m, int pq_k,
+                         const float* rerank_fp32, const float* queries, int nq,
+                         int nprobe, int topk, int n_rerank,
+                         int64_t* out_indices, float* out_distances, int64_t* out_coarse,
+                         int* out_stage1, int* out_stage1_count, long long* scanned_rows) {
+    if (nprobe <= 0 || nprobe > nlist || topk <= 0 || nq < 0 || !rerank_fp32) return 1;
+    if (nq == 0) return 0;
+    const int width = psbo_residual_stage1_width(topk, n_rerank);
+    int64_t* probes = (int64_t*)malloc(sizeof(int64_t) * (size_t)nq * nprobe);
+    int* rows = (int*)malloc(sizeof(int) * (size_t)nq * width);
+    int* counts = (int*)malloc(sizeof(int) * (size_t)nq);
+    int* local = (int*)malloc(sizeof(int) * (size_t)nq * topk);
+    int rc = psbo_coarse(queries, nq, centroids, nlist, dim, nprobe, probes, NULL);
+    if (!rc) rc = psbo_pq_scan_residual(queries, nq, dim, probes, nprobe, centroids, offsets, nlist, codes, codebook,
+                                        pq_m, pq_k, width, rows, NULL, counts, NULL, scanned_rows);
+    if (!rc) rc = psbo_rerank(rerank_fp32, NULL, n_vectors, dim, queries, NULL, rows, nq, width, width, topk, counts,
+                              local, out_distances);
+    if (!rc) psbo_map_ids(local, (int64_t)nq * topk, reordered_ids, out_indices);
+    if (!rc && out_coarse) memcpy(out_coarse, probes, sizeof(int64_t) * (size_t)nq * nprobe);
+    if (!rc && out_stage1) memcpy(out_stage1, rows, sizeof(int) * (size_t)nq * width);
+    if (!rc && out_stage1_count) memcpy(out_stage1_count, counts, sizeof(int) * (size_t)nq);
+    free(probes); free(rows); free(counts); free(local);
+    return rc;
+}
+
 /* ---- IVF-Flat (exact fp32 fine scan) ------------------------------------------ */
 
 /* src/cpu/search/cpu_search.h:226-332: coarse as above, every row of each probed

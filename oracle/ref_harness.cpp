@@ -12,9 +12,14 @@
 //   - ivfpq_rerank_cpu        src/search/ivfpq/stage/ivfpq_rerank_cpu.cpp:14
 //   - ivfpq_map_ids           src/search/ivfpq/stage/ivfpq_map_ids.cpp:4
 //   - ivf_rerank_host         src/search/ivf_common/ivf_host_rerank.cpp:55
+//   - cpu_fine_kernel_pq_resid_cpu_lut_timed (residual ADC mode, stage 1 + exact rerank)
+//                             src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:594
 #include "search/ivfpq/ivfpq_search_context.h"
 #include "search/ivfpq/stage/ivfpq_stages.cuh"
 #include "search/ivf_common/ivf_host_rerank.h"
+#include "search/ivfrespq/ivfrespq_search.cuh"
+#include "search/ivfrespq/stage/ivfrespq_cpu_rerank.h"
+#include "search/ivfrespq/stage/ivfrespq_pq_storage.h"
 #include "cpu/distance/distance_dispatch.h"
 #include "cpu/utils/cpu_distance.h"
 #include "cpu/utils/cpu_affinity.h"
@@ -185,6 +190,40 @@ int psbref_rerank_host(const float* base_fp32, const uint8_t* base_u8, int64_t c
         return 0;
     } catch (const std::invalid_argument& e) { g_err = e.what(); return 1; }
     catch (const std::exception& e) { g_err = e.what(); return 2; }
+}
+
+// Residual ADC mode: the reference's CPU stage-1 + exact rerank for queries whose probes are given
+// (query-balanced scheduler, row-major codes, fp32 rerank rows), then the id map through reordered_ids.
+// out_local [nq][topk] = list-contiguous rows (-1 padded), out_indices (optional) = mapped ids.
+int psbref_ivfrespq_search(const float* centroids, int nlist, int dim,
+                           const int64_t* offsets, const int64_t* reordered_ids, int64_t n_vectors,
+                           const uint8_t* codes, const float* codebook, int pq_m, int pq_k,
+                           const float* rerank_fp32, const float* queries, int nq, const int64_t* probes,
+                           int nprobe, int topk, int n_rerank, int threads,
+                           int* out_local, int64_t* out_indices, float* out_distances,
+                           double* times_ms, long long* scanned_codes) {
+    try {
+        std::vector<long long> off((size_t)nlist + 1);
+        std::vector<int> cnt((size_t)nlist);
+        for (int i = 0; i <= nlist; ++i) off[(size_t)i] = offsets[i];
+        for (int i = 0; i < nlist; ++i) cnt[(size_t)i] = (int)(offsets[i + 1] - offsets[i]);
+        const paraselect::cpu_fine::CpuPqCodeStorageView storage = paraselect::cpu_fine::make_pq_row_major_storage(
+            codes, off.data(), cnt.data(), pq_m, nlist, (int)n_vectors);
+        paraselect::cpu_fine::PQResidCpuLUTTiming timing;
+        std::fill(out_local, out_local + (size_t)nq * topk, -1);
+        (void)paraselect::cpu_fine::cpu_fine_kernel_pq_resid_cpu_lut_timed(
+            nullptr, off.data(), cnt.data(), storage, codebook, centroids, nullptr, queries, nullptr, rerank_fp32, 1,
+            probes, nq, dim, nlist, nprobe, topk, n_rerank, pq_m, pq_k, threads, out_local, out_distances,
+            paraselect::search::IVFResPQCpuScheduler::QueryBalanced, 1, &timing);
+        if (out_indices)
+            for (size_t i = 0; i < (size_t)nq * topk; ++i) {
+                const int r = out_local[i];
+                out_indices[i] = (r >= 0 && r < n_vectors) ? (reordered_ids ? reordered_ids[r] : (int64_t)r) : -1;
+            }
+        if (times_ms) { times_ms[0] = timing.adc_lut_scan_ms; times_ms[1] = timing.rerank_ms; times_ms[2] = 0; }
+        if (scanned_codes) *scanned_codes = timing.scanned_codes;
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return 3; }
 }
 
 }  // extern "C"

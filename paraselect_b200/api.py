@@ -71,7 +71,7 @@ class Options(C.Structure):
     _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
                 ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("list_global_begin", C.c_void_p),
                 ("coarse_mode", C.c_int),
-                ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("reserved", C.c_int * 4)]
+                ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserved", C.c_int * 3)]
 
 
 class Stats(C.Structure):
@@ -90,7 +90,7 @@ class Stats(C.Structure):
 
 EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
-    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_scan",
+    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_scan",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -141,7 +141,7 @@ class Session:
     """
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
-                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False):
+                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -168,12 +168,13 @@ class Session:
             iv.exact = HostStorageView(ptr if fp32 else None, None if fp32 else ptr, rows, d, None)
         self.dim, self.nlist, self.M, self.K, self.n = cen.shape[1], cen.shape[0], cb.shape[0], cb.shape[1], n
         self.n_rerank = n_rerank
+        self.residual = bool(residual)
         self.device = device
         gb = _np(list_global_begin, np.int64)
         self._keep.append(gb)
         opt = Options(list_global_begin=_p(gb), device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
-                      time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline))
+                      time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)))
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 
@@ -240,6 +241,10 @@ class Session:
 
     def stage_build_lut(self, d_queries, nq, d_lut):
         _check(lib().psb_stage_build_lut(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_lut))))
+
+    def stage_build_lut_residual(self, d_queries, nq, d_probes, nprobe, d_lut):
+        _check(lib().psb_stage_build_lut_residual(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_probes)), nprobe,
+                                                  C.c_void_p(_p(d_lut))))
 
     def stage_scan(self, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist=None, d_count=None):
         _check(lib().psb_stage_scan(self._h, C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)), nprobe, stage1_k,

@@ -91,8 +91,8 @@ struct ScanWorkspace {
     unsigned long long* work_cursor; // [1]
     unsigned long long* counters;    // [4]: scanned rows, admitted, fallback queries, status
     int pool_cap;
-    void* lut_h = nullptr;       // [max_batch][m*k] fp16 tables for the half pre-filter scan (null = fp32 scan only)
-    float* lut_scale = nullptr;  // [max_batch]
+    void* lut_h = nullptr;       // [tables][m*k] fp16 tables (tables = max_batch, x nprobe in residual mode) for the half pre-filter scan (null = fp32 scan only)
+    float* lut_scale = nullptr;  // [tables]
     int scan_mode = 0;           // 0 = half pre-filter when it fits, 1 = fp32 scan
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;  // optional: bracket the scan kernel
 };
@@ -105,7 +105,16 @@ struct ScanIndex {
     int nlist;
     int list_begin, list_end;  // shard
     int m, k;
+    // Residual ADC mode: codes encode x - centroid[list], so every (query, probe) pair has its own table.
+    // d_lut then holds [nq * nprobe][m*k] tables (pair order) and the visitor lists carry pair indices.
+    bool residual = false;
 };
+
+// Tables of the residual mode: table (q, p) is built on queries[q] - centroids[probes[q][p]] (pairs whose probe is
+// outside [0, nlist) are left untouched).  d_lut [nq * nprobe][m*k].
+psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
+                                     const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
+                                     float* d_lut, cudaStream_t s);
 
 psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,

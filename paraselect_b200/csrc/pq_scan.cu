@@ -53,6 +53,34 @@ __global__ void k_build_lut(const float* __restrict__ queries, int dim, const fl
     }
 }
 
+// Residual mode: one table per (query, probe) pair, built on q - centroid[probe] (fp32 subtraction, then the same
+// sequential non-fused sum; reference: src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:440-451 and :113-128).
+__global__ void k_build_lut_residual(const float* __restrict__ queries, int dim, const int* __restrict__ probes,
+                                     int nprobe, const float* __restrict__ centroids, int nlist,
+                                     const float* __restrict__ codebook, int m, int k, float* __restrict__ lut) {
+    extern __shared__ float s_q[];
+    const long long pair = blockIdx.x;
+    const int q = (int)(pair / nprobe);
+    const int l = probes[pair];
+    if (l < 0 || l >= nlist) return;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        s_q[i] = __fsub_rn(queries[(size_t)q * dim + i], __ldg(centroids + (size_t)l * dim + i));
+    __syncthreads();
+    const int dsub = dim / m;
+    const int total = m * k;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        const int sub = e / k;
+        const float* c = codebook + (size_t)e * dsub;
+        const float* qs = s_q + sub * dsub;
+        float dist = 0.0f;
+        for (int d = 0; d < dsub; ++d) {
+            const float diff = __fsub_rn(qs[d], __ldg(c + d));
+            dist = __fadd_rn(dist, __fmul_rn(diff, diff));
+        }
+        lut[(size_t)pair * total + e] = dist;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------
 // One warp per query: counts visitors per local list and the rows the query will scan.
 __global__ void k_count_visitors(const int* __restrict__ probes, int nq, int nprobe,
@@ -116,17 +144,41 @@ __global__ void k_scan_lists(const int* __restrict__ vis_count, const long long*
 
 __global__ void k_fill_visitors(const int* __restrict__ probes, int nq, int nprobe, int nlist, int lb, int le,
                                 const int* __restrict__ vis_off, int* __restrict__ vis_cursor,
-                                int* __restrict__ visitors) {
+                                int* __restrict__ visitors, int pair_ids) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)nq * nprobe) return;
     const int l = probes[i];
     if (l < lb || l >= le || l < 0 || l >= nlist) return;
     const int pos = atomicAdd(&vis_cursor[l], 1);
-    visitors[vis_off[l] + pos] = (int)(i / nprobe);
+    visitors[vis_off[l] + pos] = pair_ids ? (int)i : (int)(i / nprobe);  // table index: the pair in residual mode
 }
 
 // ------------------------------------------------------------------------------------------------------
 // ADC distance of one code row against a table in shared memory laid out [m][k] (one visitor).
+// Balanced pairwise sum of n (a power of two) terms, earlier term on the left: the order the reference's residual
+// CPU scan uses for M = 16 and M = 8 (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:226-259).
+template <int N>
+__device__ __forceinline__ float tree_sum(float (&t)[N]) {
+#pragma unroll
+    for (int n = N; n > 1; n >>= 1)
+#pragma unroll
+        for (int j = 0; j < n / 2; ++j) t[j] = __fadd_rn(t[2 * j], t[2 * j + 1]);
+    return t[0];
+}
+template <int M>
+__device__ __forceinline__ float adc_row_tree(const uint8_t* __restrict__ row, const float* __restrict__ lut, int k) {
+    static_assert(M == 8 || M == 16, "tree order exists for M = 8 and 16");
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
+    float t[M];
+#pragma unroll
+    for (int w = 0; w < M / 4; ++w) {
+        const uint32_t c = __ldg(p + w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) t[w * 4 + j] = lut[(w * 4 + j) * k + ((c >> (j * 8)) & 255)];
+    }
+    return tree_sum<M>(t);
+}
+
 template <int M>
 __device__ __forceinline__ float adc_row_1(const uint8_t* __restrict__ row, const float* __restrict__ s_lut, int k) {
     float acc = 0.0f;
@@ -161,7 +213,8 @@ __device__ __forceinline__ float adc_row_dyn(const uint8_t* __restrict__ row, co
     return acc;
 }
 template <int M>
-__device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut, int m, int k) {
+__device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut, int m, int k, bool tree = false) {
+    if constexpr (M == 8 || M == 16) { if (tree) return adc_row_tree<M>(row, s_lut, k); }
     if constexpr (M > 0) return adc_row_1<M>(row, s_lut, k);
     else return adc_row_dyn(row, s_lut, m, k);
 }
@@ -180,7 +233,10 @@ __global__ void __launch_bounds__(kSeedThreads)
 k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
                  const long long* __restrict__ offsets, int nlist, int lb, int le,
                  const uint8_t* __restrict__ codes, long long row_base, int m, int k,
-                 const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr) {
+                 const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr,
+                 int per_probe, int tree) {
+    // per_probe (residual mode): lut holds one table per (query, probe) pair; the probes are then sampled one after
+    // the other, each with its own table staged in shared memory.
     extern __shared__ __align__(16) unsigned char s_seed_raw[];
     float* s_lut = reinterpret_cast<float*>(s_seed_raw);                                  // [m * k]
     uint32_t* s_keys = reinterpret_cast<uint32_t*>(s_seed_raw + (size_t)m * k * 4);       // [kSeedBuf]
@@ -195,7 +251,8 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     int stride = stage1_k / 16;
     stride = stride < 16 ? 16 : (stride > 64 ? 64 : stride);
     if ((N + 65535) / 65536 > stride) stride = (int)((N + 65535) / 65536);  // at most ~64K samples per query
-    for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
+    if (!per_probe)
+        for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
     // samples per probe and their exclusive prefix
     int carry = 0;
     for (int p0 = 0; p0 < nprobe; p0 += blockDim.x) {
@@ -216,29 +273,43 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     const int r = (int)ceilf(mu + 4.0f * sqrtf(mu) + 2.0f);
     if (r >= ns || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; return; }
     __syncthreads();
-    for (int base = 0; base < ns; base += blockDim.x) {
-        const int c_now = s_cnt;  // stable since the barrier that ended the previous round
-        __syncthreads();
-        if (c_now + (int)blockDim.x > kSeedBuf) {  // uniform
-            for (int i = c_now + threadIdx.x; i < kSeedBuf; i += blockDim.x) s_keys[i] = 0xffffffffu;
-            __syncthreads();
-            block_bitonic_sort(s_keys, kSeedBuf);
-            if (threadIdx.x == 0) { s_cnt = r; s_cut = s_keys[r - 1]; }  // c_now >= r here
+    const int nseg = per_probe ? nprobe : 1;
+    for (int sg = 0; sg < nseg; ++sg) {
+        const int b0 = per_probe ? s_pref[sg] : 0, b1 = per_probe ? s_pref[sg + 1] : ns;  // uniform
+        if (b0 == b1) continue;
+        if (per_probe) {
+            __syncthreads();  // the previous probe's table is no longer read
+            const float* src = lut + ((size_t)q * nprobe + sg) * m * k;
+            for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = src[e];
             __syncthreads();
         }
-        const int idx = base + threadIdx.x;
-        if (idx < ns) {
-            int lo = 0, hi = nprobe;  // largest p with s_pref[p] <= idx
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (s_pref[mid] <= idx) lo = mid; else hi = mid;
+        for (int base = b0; base < b1; base += blockDim.x) {
+            const int c_now = s_cnt;  // stable since the barrier that ended the previous round
+            __syncthreads();
+            if (c_now + (int)blockDim.x > kSeedBuf) {  // uniform
+                for (int i = c_now + threadIdx.x; i < kSeedBuf; i += blockDim.x) s_keys[i] = 0xffffffffu;
+                __syncthreads();
+                block_bitonic_sort(s_keys, kSeedBuf);
+                if (threadIdx.x == 0) { s_cnt = r; s_cut = s_keys[r - 1]; }  // c_now >= r here
+                __syncthreads();
             }
-            const int l = probes[(size_t)q * nprobe + lo];
-            const long long row = offsets[l] + (long long)(idx - s_pref[lo]) * stride;
-            const uint32_t key = f2o(adc_row<M>(codes + (size_t)(row - row_base) * m, s_lut, m, k));
-            if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
+            const int idx = base + threadIdx.x;
+            if (idx < b1) {
+                int lo = sg, hi = nprobe;  // largest p with s_pref[p] <= idx
+                if (!per_probe) {
+                    lo = 0;
+                    while (hi - lo > 1) {
+                        const int mid = (lo + hi) >> 1;
+                        if (s_pref[mid] <= idx) lo = mid; else hi = mid;
+                    }
+                }
+                const int l = probes[(size_t)q * nprobe + lo];
+                const long long row = offsets[l] + (long long)(idx - s_pref[lo]) * stride;
+                const uint32_t key = f2o(adc_row<M>(codes + (size_t)(row - row_base) * m, s_lut, m, k, tree != 0));
+                if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
     const int c = s_cnt;
     for (int i = c + threadIdx.x; i < kSeedBuf; i += blockDim.x) s_keys[i] = 0xffffffffu;
@@ -276,7 +347,9 @@ __device__ __forceinline__ void lut_add(float (&acc)[V], const float* __restrict
 }
 
 struct ScanArgs {
-    const float* lut;          // [nq][m*k]
+    const float* lut;          // [tables][m*k]
+    int lut_div;               // visitor entry / lut_div = query (1: one table per query; nprobe: one per pair)
+    int tree;                  // pairwise-tree ADC order (residual mode, M = 8 or 16, K = 256)
     const uint8_t* codes;
     const long long* offsets;
     long long row_base;
@@ -313,7 +386,7 @@ template <int M, int V>
 __global__ void __launch_bounds__(640, 1) k_scan(const ScanArgs a) {
     extern __shared__ __align__(16) float s_lut[];  // [m*k][V] visitor-interleaved
     __shared__ long long s_item;
-    __shared__ int s_list, s_vq[V];
+    __shared__ int s_list, s_vq[V], s_pq[V];
     __shared__ float s_thr[V];
     const int mk = a.m * a.k;
     const long long total = a.item_off[a.nlist];
@@ -338,14 +411,16 @@ __global__ void __launch_bounds__(640, 1) k_scan(const ScanArgs a) {
         const long long chunk = local / ngroups;
         if (threadIdx.x < V) {
             const int vi = group * V + threadIdx.x;
-            const int q = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;
+            const int q = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;  // table index
+            const int pq = q >= 0 ? q / a.lut_div : -1;                     // query (pool, cutoff)
             s_vq[threadIdx.x] = q;
-            s_thr[threadIdx.x] = q >= 0 ? a.thr[q] : -1.0f;  // distances are >= 0: -1 admits nothing
+            s_pq[threadIdx.x] = pq;
+            s_thr[threadIdx.x] = q >= 0 ? a.thr[pq] : -1.0f;  // distances are >= 0: -1 admits nothing
         }
         __syncthreads();
-        int vq[V]; float thr[V];
+        int vq[V], pq[V]; float thr[V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) { vq[v] = s_vq[v]; thr[v] = s_thr[v]; }
+        for (int v = 0; v < V; ++v) { vq[v] = s_vq[v]; pq[v] = s_pq[v]; thr[v] = s_thr[v]; }
         // stage the V tables, interleaved by visitor (padding visitors reuse visitor 0's table)
         {
             const float* src[V];
@@ -390,11 +465,36 @@ __global__ void __launch_bounds__(640, 1) k_scan(const ScanArgs a) {
             } else {
                 for (int j = 0; j < a.m; ++j) lut_add<V>(acc, s_lut, j * a.k + (int)__ldg(row + j));
             }
+            if constexpr (M == 8 || M == 16) {
+                if (a.tree) {  // pairwise-tree order: pair sums first (0 + x is exact), then the balanced tree
+                    const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
+                    float part[M / 2][V];
+#pragma unroll
+                    for (int w = 0; w < M / 4; ++w) {
+                        const uint32_t c = __ldg(p + w);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) part[w * 2 + h][v] = 0.0f;
+                            lut_add<V>(part[w * 2 + h], s_lut, (w * 4 + 2 * h) * a.k + (int)((c >> (16 * h)) & 255));
+                            lut_add<V>(part[w * 2 + h], s_lut, (w * 4 + 2 * h + 1) * a.k + (int)((c >> (16 * h + 8)) & 255));
+                        }
+                    }
+#pragma unroll
+                    for (int n = M / 2; n > 1; n >>= 1)
+#pragma unroll
+                        for (int j = 0; j < n / 2; ++j)
+#pragma unroll
+                            for (int v = 0; v < V; ++v) part[j][v] = __fadd_rn(part[2 * j][v], part[2 * j + 1][v]);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[v] = part[0][v];
+                }
+            }
 #pragma unroll
             for (int v = 0; v < V; ++v) {
                 if (acc[v] <= thr[v]) {
-                    const int slot = atomicAdd(&a.pool_cnt[vq[v]], 1);
-                    if (slot < a.pool_cap) a.pool[(size_t)vq[v] * a.pool_cap + slot] = make_key(acc[v], (uint32_t)(r + delta));
+                    const int slot = atomicAdd(&a.pool_cnt[pq[v]], 1);
+                    if (slot < a.pool_cap) a.pool[(size_t)pq[v] * a.pool_cap + slot] = make_key(acc[v], (uint32_t)(r + delta));
                 }
             }
         }
@@ -441,7 +541,7 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
                  const uint8_t* __restrict__ codes, long long row_base, const long long* __restrict__ row_delta,
                  int m, int k, int stage1_k, int buf_n, const int* __restrict__ fail_list, const int* __restrict__ n_fail, int* __restrict__ fail_cursor,
                  int* __restrict__ out_rows, float* __restrict__ out_dist, int* __restrict__ out_count,
-                 unsigned long long* __restrict__ counters) {
+                 unsigned long long* __restrict__ counters, int per_probe, int tree) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);                 // [buf_n]
     float* s_lut = reinterpret_cast<float*>(s_raw + (size_t)buf_n * 8);   // [m*k]
@@ -455,13 +555,20 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
         const int idx = s_idx;
         if (idx >= nf) return;
         const int q = fail_list[idx];
-        for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
+        if (!per_probe)
+            for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
         if (threadIdx.x == 0) { s_cnt = 0; s_cut = KEY_MAX; atomicAdd(&counters[2], 1ull); }
         __syncthreads();
         for (int p = 0; p < nprobe; ++p) {
             const int l = probes[(size_t)q * nprobe + p];
             if (l < lb || l >= le || l < 0 || l >= nlist) continue;
             const long long b = offsets[l], e = offsets[l + 1];
+            if (per_probe && b < e) {  // residual mode: this probe's own table (uniform branch)
+                __syncthreads();
+                const float* src = lut + ((size_t)q * nprobe + p) * m * k;
+                for (int i = threadIdx.x; i < m * k; i += blockDim.x) s_lut[i] = src[i];
+                __syncthreads();
+            }
             const long long delta = row_delta ? row_delta[l] : 0;
             for (long long base = b; base < e; base += blockDim.x) {
                 const int c_now = s_cnt;  // stable since the barrier that ended the previous block of rows
@@ -480,7 +587,7 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
                 }
                 const long long r = base + threadIdx.x;
                 if (r < e) {
-                    const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k);
+                    const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k, tree != 0);
                     const uint64_t key = make_key(d, (uint32_t)(r + delta));
                     if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
                 }
@@ -564,7 +671,7 @@ __global__ void __launch_bounds__(640, 1) k_scan_h(const ScanArgsH ah) {
     const int mk = a.m * a.k;
     unsigned long long* s_queue = reinterpret_cast<unsigned long long*>(s_raw_h + (size_t)mk * 16);  // [warps][kQueuePerWarp]
     __shared__ long long s_item;
-    __shared__ int s_list, s_vq[V];
+    __shared__ int s_list, s_vq[V], s_pq[V];
     __shared__ float s_thr[V], s_T[V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned long long* queue = s_queue + warp * kQueuePerWarp;
@@ -575,11 +682,16 @@ __global__ void __launch_bounds__(640, 1) k_scan_h(const ScanArgsH ah) {
     auto rescore = [&](unsigned long long entry, long long delta) {
         const long long r = (long long)(entry >> 3);
         const int v = (int)(entry & 7);
-        const int q = s_vq[v];
-        const float* lq = a.lut + (size_t)q * mk;
+        const int q = s_pq[v];
+        const float* lq = a.lut + (size_t)s_vq[v] * mk;
         const uint8_t* row = a.codes + (size_t)(r - a.row_base) * a.m;
         float d = 0.0f;
-        if constexpr (M % 16 == 0) {
+        bool done = false;
+        if constexpr (M == 8 || M == 16) {
+            if (a.tree) { d = adc_row_tree<M>(row, lq, a.k); done = true; }
+        }
+        if (done) {
+        } else if constexpr (M % 16 == 0) {
             const uint4* p = reinterpret_cast<const uint4*>(row);
 #pragma unroll
             for (int w = 0; w < M / 16; ++w) {
@@ -625,11 +737,12 @@ __global__ void __launch_bounds__(640, 1) k_scan_h(const ScanArgsH ah) {
         const long long chunk = local / ngroups;
         if (threadIdx.x < V) {
             const int vi = group * V + threadIdx.x;
-            const int q = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;
+            const int q = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;  // table index
             s_vq[threadIdx.x] = q;
+            s_pq[threadIdx.x] = q >= 0 ? q / a.lut_div : -1;               // query (pool, cutoff)
             float t = -1.0f, T = -1.0f;  // padding visitors admit nothing
             if (q >= 0) {
-                t = a.thr[q];
+                t = a.thr[q / a.lut_div];
                 T = __half2float(__float2half_ru(t * ah.scale[q] * slack));  // +inf stays +inf
             }
             s_thr[threadIdx.x] = t;
@@ -758,6 +871,10 @@ bool half_scan_fits(int m, int k) {
     return templated && (k % 2 == 0) && (size_t)m * k * 16 + (kScanThreads / 32) * kQueuePerWarp * 8 <= 220 * 1024;
 }
 
+// The reference's residual CPU scan sums M = 16 and M = 8 (K = 256) rows as a balanced pairwise tree and every other
+// shape sequentially (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:307-341); the plain mode is always sequential.
+bool tree_order(const ScanIndex& ix) { return ix.residual && ix.k == 256 && (ix.m == 16 || ix.m == 8); }
+
 template <typename F>
 psb_status set_smem(F kernel, size_t bytes) {
     if (bytes > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
@@ -801,7 +918,8 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
     PSB_TRY(set_smem(k_seed_threshold<M>, smem));
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
-                                                         stage1_k, ws.pool_cap, ws.thr);
+                                                         stage1_k, ws.pool_cap, ws.thr, ix.residual ? 1 : 0,
+                                                         tree_order(ix) ? 1 : 0);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -817,7 +935,8 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     PSB_TRY(set_smem(k_exact_fallback<M>, smem));
     k_exact_fallback<M><<<sm_count, kFallbackThreads, smem, s>>>(
         d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.row_delta, ix.m, ix.k,
-        stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters);
+        stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters,
+        ix.residual ? 1 : 0, tree_order(ix) ? 1 : 0);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -845,10 +964,25 @@ psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float
     return PSB_OK;
 }
 
+psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
+                                     const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
+                                     float* d_lut, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    const long long pairs = (long long)nq * nprobe;
+    if (pairs > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
+    k_build_lut_residual<<<(unsigned)pairs, 256, (size_t)dim * sizeof(float), s>>>(d_queries, dim, d_probes, nprobe,
+                                                                                   d_centroids, nlist, d_codebook, m, k, d_lut);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
 psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
                        int* d_count, int sm_count, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
+    const long long tables = ix.residual ? (long long)nq * nprobe : nq;
+    if (tables > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
     const bool use_half = ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(ix.m, ix.k);
     const int group = use_half ? kHalfGroup : pick_group(ix.m, ix.k);
     // schedule
@@ -867,20 +1001,21 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     PSB_LAUNCH_CHECK();
     const long long pairs = (long long)nq * nprobe;
     k_fill_visitors<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(d_probes, nq, nprobe, ix.nlist, ix.list_begin,
-                                                                    ix.list_end, ws.vis_off, ws.vis_cursor, ws.visitors);
+                                                                    ix.list_end, ws.vis_off, ws.vis_cursor, ws.visitors,
+                                                                    ix.residual ? 1 : 0);
     count_launch();
     PSB_LAUNCH_CHECK();
     // cutoff
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s))));
     // scan
     ScanArgs a;
-    a.lut = d_lut; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base; a.row_delta = ix.row_delta;
+    a.lut = d_lut; a.lut_div = ix.residual ? nprobe : 1; a.tree = tree_order(ix) ? 1 : 0; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base; a.row_delta = ix.row_delta;
     a.nlist = ix.nlist; a.m = ix.m; a.k = ix.k;
     a.vis_count = ws.vis_count; a.vis_off = ws.vis_off; a.visitors = ws.visitors; a.item_off = ws.item_off;
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
     if (use_half) {
-        k_lut_to_half<<<nq, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
+        k_lut_to_half<<<(unsigned)tables, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
         count_launch();
         PSB_LAUNCH_CHECK();
     }

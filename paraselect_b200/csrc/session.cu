@@ -207,6 +207,7 @@ struct psb_session {
         ix.codes = codes.as<uint8_t>(); ix.offsets = offsets.as<long long>(); ix.row_base = row_base;
         ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
         ix.row_delta = striped ? row_delta.as<long long>() : nullptr;
+        ix.residual = opt.adc_mode == 1;
         return ix;
     }
     // Which index-wide rows the exact store and the id table of this session hold.
@@ -264,13 +265,42 @@ struct psb_session {
 
 namespace {
 
+// Plain mode: the rerank runs when exact rows exist and n_rerank > topk.  Residual mode: always (the rows are required).
+bool rerank_enabled(const psb_session* s, int topk) {
+    if (s->opt.adc_mode == 1) return true;
+    return s->exact_elem != 0 && s->opt.n_rerank > topk;
+}
+
 int stage1_width(const psb_session* s, int topk) {
-    const bool rerank = s->exact_elem != 0 && s->opt.n_rerank > topk;
-    if (!rerank) return topk;
+    if (s->opt.adc_mode == 1)  // src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:623-625
+        return std::max(std::max(s->opt.n_rerank, topk), 512);
+    if (!rerank_enabled(s, topk)) return topk;
     return (int)std::min<long long>(s->opt.n_rerank, s->n_vectors);
 }
 
+// Tables one scan call needs for nq queries.
+size_t table_count(const psb_session* s, int nq, int nprobe) {
+    return s->opt.adc_mode == 1 ? (size_t)nq * nprobe : (size_t)nq;
+}
+
+// Queries per sub-batch of the pipeline: a quarter of the batch when the rerank overlaps the scan, and in residual mode
+// few enough that the per-(query, probe) tables stay below ~16 GiB.
+int sub_batch_rows(const psb_session* s, int n, int nprobe, bool overlap) {
+    int parts = overlap ? 4 : 1;
+    if (s->opt.adc_mode == 1) {
+        const double bytes = (double)n * nprobe * s->m * s->k * sizeof(float);
+        parts = std::max(parts, (int)std::ceil(bytes / (16.0 * 1024 * 1024 * 1024)));
+    }
+    parts = std::min(parts, std::max(n, 1));
+    return (n + parts - 1) / parts;
+}
+
+bool overlap_enabled(const psb_session* s, int n, bool rerank) {
+    return rerank && s->opt.exact_mode != PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
+}
+
 psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
+    const size_t tables = table_count(s, nq, nprobe);
     PSB_TRY(s->vis_count.reserve(sizeof(int) * (size_t)s->nlist));
     PSB_TRY(s->vis_off.reserve(sizeof(int) * ((size_t)s->nlist + 1)));
     PSB_TRY(s->vis_cursor.reserve(sizeof(int) * (size_t)s->nlist));
@@ -284,8 +314,8 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
     s->pool_cap = cap;
     PSB_TRY(s->fail_list.reserve(sizeof(int) * (size_t)nq));
     if (s->opt.scan_mode != 1) {
-        PSB_TRY(s->lut_h.reserve(sizeof(unsigned short) * (size_t)nq * s->m * s->k));
-        PSB_TRY(s->lut_scale.reserve(sizeof(float) * (size_t)nq));
+        PSB_TRY(s->lut_h.reserve(sizeof(unsigned short) * tables * s->m * s->k));
+        PSB_TRY(s->lut_scale.reserve(sizeof(float) * tables));
     }
     if (!s->scalars.p) {
         PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 8));
@@ -295,17 +325,18 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
 }
 
 psb_status ensure_pipeline_ws(psb_session* s, int nq, int nprobe, int topk, int stage1_k) {
+    const int sb = sub_batch_rows(s, nq, nprobe, overlap_enabled(s, nq, rerank_enabled(s, topk)));
     PSB_TRY(s->q.reserve(sizeof(float) * (size_t)nq * s->dim));
     PSB_TRY(s->probes.reserve(sizeof(int) * (size_t)nq * nprobe));
     PSB_TRY(s->probe_dist.reserve(sizeof(float) * (size_t)nq * nprobe));
-    PSB_TRY(s->lut.reserve(sizeof(float) * (size_t)nq * s->m * s->k));
+    PSB_TRY(s->lut.reserve(sizeof(float) * table_count(s, sb, nprobe) * s->m * s->k));
     PSB_TRY(s->cand_rows.reserve(sizeof(int) * (size_t)nq * stage1_k));
     PSB_TRY(s->cand_dist.reserve(sizeof(float) * (size_t)nq * stage1_k));
     PSB_TRY(s->cand_count.reserve(sizeof(int) * (size_t)nq));
     PSB_TRY(s->out_rows.reserve(sizeof(int) * (size_t)nq * topk));
     PSB_TRY(s->out_dist.reserve(sizeof(float) * (size_t)nq * topk));
     PSB_TRY(s->out_ids.reserve(sizeof(long long) * (size_t)nq * topk));
-    return ensure_scan_ws(s, nq, nprobe, stage1_k);
+    return ensure_scan_ws(s, sb, nprobe, stage1_k);  // the scan runs one sub-batch at a time
 }
 
 // Coarse stage on device queries: exact distance tiles + row selection, query-chunked so the distance tile
@@ -508,6 +539,9 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
         }
     }
     if (opt.n_rerank > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "n_rerank above 2048 is not supported");
+    if (opt.adc_mode != 0 && opt.adc_mode != 1) return fail(PSB_INVALID_ARGUMENT, "unknown adc_mode");
+    if (opt.adc_mode == 1 && !index->exact.fp32 && !index->exact.u8)
+        return fail(PSB_INVALID_ARGUMENT, "residual mode always reranks: exact rows are required");
     cudaDeviceProp prop;
     PSB_TRY(check_device(opt.device, &prop));
     std::unique_ptr<psb_session> s(new (std::nothrow) psb_session());
@@ -615,6 +649,15 @@ psb_status psb_stage_build_lut(psb_session* s, const float* d_queries, int nq, f
     return launch_build_lut(d_queries, nq, s->dim, s->codebook.as<float>(), s->m, s->k, d_lut, s->stream);
 }
 
+psb_status psb_stage_build_lut_residual(psb_session* s, const float* d_queries, int nq, const int* d_probes, int nprobe,
+                                        float* d_lut) {
+    if (!s || !d_queries || !d_probes || !d_lut) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (nprobe <= 0 || nprobe > kMaxProbe) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..4096");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_build_lut_residual(d_queries, nq, s->dim, d_probes, nprobe, s->centroids.as<float>(), s->nlist,
+                                     s->codebook.as<float>(), s->m, s->k, d_lut, s->stream);
+}
+
 psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int* d_probes, int nprobe,
                           int stage1_k, int* d_rows, float* d_dist, int* d_count) {
     if (!s || !d_lut || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");
@@ -709,9 +752,9 @@ struct StageTimes { double coarse = 0, lut = 0, scan = 0, rerank = 0, map = 0; }
 psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, int n, int nprobe, int topk, int stage1_k,
                          bool rerank, long long* d_ids, float* d_dist, int* d_probes, StageTimes* times) {
     cudaStream_t st = s->stream;
-    const bool overlap = rerank && s->opt.exact_mode != PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
-    const int parts = overlap ? 4 : 1;
-    const int sb = (n + parts - 1) / parts;
+    const bool overlap = overlap_enabled(s, n, rerank);
+    const int sb = sub_batch_rows(s, n, nprobe, overlap);
+    const bool residual = s->opt.adc_mode == 1;
     if (overlap && !s->aux_stream) {
         int lo = 0, hi = 0;  // lowest priority: the scan's CTAs get the SMs first, the transfer fills the gaps
         PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -742,7 +785,10 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         float* dist_out = rerank ? s->cand_dist.as<float>() + (size_t)p0 * stage1_k : d_dist + (size_t)p0 * topk;
         int* cnt_out = s->cand_count.as<int>() + p0;
         if (times) rc = tm_s.mark(st);
-        if (rc == PSB_OK) rc = launch_build_lut(q, m, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st);
+        if (rc == PSB_OK)
+            rc = residual ? launch_build_lut_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
+                                                      s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st)
+                          : launch_build_lut(q, m, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st);
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
         ScanWorkspace sws;
         if (rc == PSB_OK) rc = s->timed_scan_ws(&sws);
@@ -811,7 +857,7 @@ psb_status psb_session_search_device(psb_session* s, const float* d_queries, con
     PSB_CUDA(cudaSetDevice(s->device));
     const int topk = params->topk;
     const int stage1_k = stage1_width(s, topk);
-    const bool rerank = s->exact_elem != 0 && s->opt.n_rerank > topk;
+    const bool rerank = rerank_enabled(s, topk);
     if (stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "candidate width above 2048 is not supported");
     if (rerank && s->exact_elem == 1 && !d_queries_u8) return fail(PSB_INVALID_ARGUMENT, "u8 rerank needs u8 queries");
     PSB_TRY(ensure_pipeline_ws(s, nq, params->nprobe, topk, stage1_k));
@@ -832,7 +878,7 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
     const int nprobe = params->nprobe, topk = params->topk;
     const int batch = std::min(std::min(params->batch_size, s->opt.max_batch), total);
     const int stage1_k = stage1_width(s, topk);
-    const bool rerank = s->exact_elem != 0 && s->opt.n_rerank > topk;
+    const bool rerank = rerank_enabled(s, topk);
     if (stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "candidate width above 2048 is not supported");
     PSB_TRY(ensure_pipeline_ws(s, batch, nprobe, topk, stage1_k));
     if (rerank && s->exact_elem == 1) PSB_TRY(s->q_u8.reserve((size_t)batch * s->dim));

@@ -59,6 +59,9 @@ class SessionEngine:
     """The CUDA library as the compute engine of ShardedSearch (device tensors are torch CUDA tensors)."""
 
     def __init__(self, session, torch):
+        if getattr(session, "residual", False):
+            raise NotImplementedError("the sharded step runs plain ADC sessions only (residual tables are per "
+                                      "(query, probe) and need the single-GPU pipeline's sub-batching)")
         self.s = session
         self.torch = torch
 

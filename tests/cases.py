@@ -96,6 +96,25 @@ def plain_pq_pipeline_case(m, dim, rerank=512, empty_first=False):
                 exp_ids=order.astype(np.int64), exp_d=exp_d)
 
 
+def residual_pq_pipeline_case(m, dim, rerank=512):
+    """The plain construction above moved into residual mode: list l has the integer centroid (3 l - 4, repeated), the
+    codes reproduce base - centroid[list] exactly, so ADC = exact distance and the search must equal exhaustive top-10."""
+    c = plain_pq_pipeline_case(m, dim, rerank)
+    ix = c["index"]
+    nlist = ix["centroids"].shape[0]
+    cen = np.repeat((3.0 * np.arange(nlist, dtype=np.float32) - 4.0)[:, None], dim, axis=1)
+    lists = np.repeat(np.arange(nlist), np.diff(ix["offsets"]))
+    base = ix["vectors"] + cen[lists]
+    rows, nq, topk = base.shape[0], c["queries"].shape[0], c["topk"]
+    queries = base[(np.arange(nq) * 47) % rows].copy()
+    d2 = ((queries[:, None, :].astype(np.float64) - base[None, :, :].astype(np.float64)) ** 2).sum(-1)
+    order = np.lexsort((np.broadcast_to(np.arange(rows), d2.shape), d2), axis=1)[:, :topk]
+    exp_d = np.take_along_axis(d2, order, axis=1).astype(np.float32)
+    index = dict(ix, centroids=cen, vectors=base)
+    return dict(index=index, queries=queries, nprobe=nlist, topk=topk, n_rerank=rerank,
+                exp_ids=order.astype(np.int64), exp_d=exp_d)
+
+
 def stage1_sets_match(got_rows, want_rows, want_dist_of):
     """Candidate sets must be equal except for members tied (equal ADC distance) at the boundary.
     want_dist_of(q, row) -> the checker's ADC distance."""

@@ -47,19 +47,24 @@ def train_codebook(data, M, K, seed, iters=4, sample=20000):
     return cb
 
 
-def make_index(n, dim, nlist, M, sigma=0.25, seed=0, zipf=False, K=256, empty_lists=(), keep_vectors=True):
+def make_index(n, dim, nlist, M, sigma=0.25, seed=0, zipf=False, K=256, empty_lists=(), keep_vectors=True,
+               residual=False):
+    """residual=True: the codebook is trained on, and the codes encode, x - centroid[list(x)]."""
     w = zipf_weights(nlist) if zipf else None
     if empty_lists:
         w = np.full(nlist, 1.0) if w is None else w.copy()
         w[list(empty_lists)] = 0.0
         w = w / w.sum()
     centres, data, offsets = mixture(n, dim, nlist, sigma, seed, w)
-    cb = train_codebook(data, M, K, seed + 1)
-    codes = oracle.pq_encode(data, cb)
+    coded = data
+    if residual:
+        coded = data - centres[np.repeat(np.arange(nlist), np.diff(offsets))]
+    cb = train_codebook(coded, M, K, seed + 1)
+    codes = oracle.pq_encode(coded, cb)
     rng = np.random.default_rng(seed + 2)
     reordered_ids = rng.permutation(n).astype(np.int64)
     return dict(centroids=centres, offsets=offsets, reordered_ids=reordered_ids, codes=codes, codebook=cb,
-                vectors=data if keep_vectors else None, dim=dim, M=M, K=K, n=n, nlist=nlist)
+                vectors=data if keep_vectors else None, dim=dim, M=M, K=K, n=n, nlist=nlist, residual=residual)
 
 
 def make_queries(index, nq, sigma=0.25, seed=100, weights=None):

@@ -77,6 +77,73 @@ def test_plain_pq_pipeline_equals_exhaustive(m, dim, rerank, empty):
     assert np.array_equal(o["distances"], c["exp_d"])
 
 
+GOLDEN_RESIDUAL = ["ivfrespq_d64_m16", "ivfrespq_d32_m8", "ivfrespq_d96_m48_zipf"]
+
+
+@pytest.mark.parametrize("name", GOLDEN_RESIDUAL)
+def test_residual_restatement_matches_reference_golden(name):
+    """Residual ADC mode against outputs of the reference's cpu_fine_kernel_pq_resid_cpu_lut_timed; the m16 fixture asks
+    for topk = candidate width, so its output is the whole stage-1 set."""
+    g = cases.load_golden(name)
+    nprobe, topk, n_rerank = (int(x) for x in g["params"])
+    o = oracle.ivfrespq_search(cases.golden_index(g), g["queries"], nprobe, topk, n_rerank)
+    assert np.array_equal(o["coarse"], g["ref_probes"])
+    assert np.array_equal(o["indices"], g["ref_indices"])
+    assert np.array_equal(o["distances"], g["ref_distances"])  # bit-exact
+    assert o["scanned"] == int(g["ref_scanned"])
+    assert o["stage1"].shape[1] == max(n_rerank, topk, 512)
+
+
+@pytest.mark.parametrize("m,dim,rerank", [(16, 96, 512), (8, 32, 512), (20, 100, 2048)])
+def test_residual_pq_pipeline_equals_exhaustive(m, dim, rerank):
+    c = cases.residual_pq_pipeline_case(m, dim, rerank)
+    o = oracle.ivfrespq_search(c["index"], c["queries"], c["nprobe"], c["topk"], c["n_rerank"])
+    assert np.array_equal(o["indices"], c["exp_ids"])
+    assert np.array_equal(o["distances"], c["exp_d"])
+
+
+def test_residual_tables_and_tree_order():
+    """Tables are built on q - centroid; M = 16 / 8 with K = 256 sum as a balanced pairwise tree, other shapes in order."""
+    for M, dim in ((16, 64), (8, 32), (12, 48)):
+        ix = synth.make_index(3000, dim, 12, M, seed=40 + M, residual=True)
+        q = synth.make_queries(ix, 9, seed=3)
+        probes, _ = oracle.coarse(q, ix["centroids"], 3)
+        rows, dist, cnt, scanned, luts = oracle.pq_scan_residual(q, probes, ix["centroids"], ix["offsets"], ix["codes"],
+                                                                 ix["codebook"], 20, want_luts=True)
+        for qi in range(q.shape[0]):
+            for p in range(3):
+                want = oracle.pq_lut((q[qi] - ix["centroids"][probes[qi, p]])[None, :], ix["codebook"])[0]
+                assert np.array_equal(luts[qi, p].reshape(want.shape), want)
+        lists = np.repeat(np.arange(12), np.diff(ix["offsets"]))
+        for qi in range(q.shape[0]):
+            for i in range(int(cnt[qi])):
+                row = rows[qi, i]
+                p = int(np.nonzero(probes[qi] == lists[row])[0][0])
+                t = luts[qi, p].reshape(M, 256)[np.arange(M), ix["codes"][row]].astype(np.float32)
+                if M in (8, 16):
+                    while t.size > 1:
+                        t = (t[0::2] + t[1::2]).astype(np.float32)
+                    want = t[0]
+                else:
+                    want = np.float32(0)
+                    for v in t:
+                        want = np.float32(want + v)
+                assert dist[qi, i] == want
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="oracle/_ref (reference compiled in place) not built")
+@pytest.mark.parametrize("seed,dim,M,nlist,zipf,topk,nr", [(41, 64, 16, 24, True, 10, 100), (42, 32, 8, 16, False, 512, 512),
+                                                           (43, 96, 48, 16, True, 100, 1000), (44, 48, 12, 8, False, 600, 0)])
+def test_residual_restatement_vs_reference_live(seed, dim, M, nlist, zipf, topk, nr):
+    ix = synth.make_index(4000, dim, nlist, M, seed=seed, zipf=zipf, residual=True)
+    q = synth.make_queries(ix, 30, seed=seed + 1)
+    o = oracle.ivfrespq_search(ix, q, 5, topk, nr)
+    r = oracle.ref_ivfrespq_search(ix, q, o["coarse"], topk, nr, threads=3)
+    assert np.array_equal(r["indices"], o["indices"])
+    assert np.array_equal(r["distances"], o["distances"])
+    assert r["scanned"] == o["scanned"]
+
+
 def test_u8_lut_identities():
     rng = np.random.default_rng(5)
     for M, dsub in ((16, 8), (20, 5)):
