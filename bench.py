@@ -34,6 +34,10 @@ WORKLOADS = {
     # BASELINE configuration "IVF-PQ at scale" (the one the headline metric is quoted on)
     "c4": dict(n=100_000_000, dim=96, nlist=65536, M=48, sigma=0.25, zipf=1.1, nq=10000, nprobe=128, topk=100,
                n_rerank=1000, seed=3, desc="IVF-PQ 100Mx96 nlist=65536 M=48 nprobe=128 k=100 rerank=1000 batch=10000"),
+    # the same index in residual ADC mode (codebook trained on, and codes encoding, row - centroid[list])
+    "c4r": dict(n=100_000_000, dim=96, nlist=65536, M=48, sigma=0.25, zipf=1.1, nq=10000, nprobe=128, topk=100,
+                n_rerank=1000, seed=3, residual=True,
+                desc="IVF-ResidualPQ 100Mx96 nlist=65536 M=48 nprobe=128 k=100 rerank=1000 batch=10000"),
     # BASELINE configuration "IVF-PQ fp32 1M"
     "c2": dict(n=1_000_000, dim=128, nlist=1024, M=32, sigma=0.25, zipf=None, nq=10000, nprobe=32, topk=10,
                n_rerank=100, seed=1, desc="IVF-PQ 1Mx128 nlist=1024 M=32 nprobe=32 k=10 rerank=100 batch=10000"),
@@ -128,11 +132,25 @@ def build_index(cfg, torch, api, device, row_lo=0, row_hi=None, gt_queries=None,
     api.gen_normal(seed * 1000 + 1, 0, nlist * dim, 1.0, centres, device=device)
     # PQ training sample: 64 evenly spaced blocks of rows (the same on every rank)
     blocks, per = 64, min(16384, max(1, n // 64))
+    residual = bool(cfg.get("residual"))
+
+    def coded(rows_t, r0, m):
+        """What the PQ codes encode: the row itself, or in residual mode row - centroid[list(row)]."""
+        if not residual:
+            return rows_t[:m]
+        torch.cuda.synchronize()  # the generators run on the default stream, torch on its own
+        lists = torch.searchsorted(d_off[1:], torch.arange(r0, r0 + m, device="cuda"), right=True)
+        out = (rows_t[:m] - centres[lists]).contiguous()
+        torch.cuda.synchronize()
+        return out
+
     sample = torch.empty((blocks * per, dim), dtype=torch.float32, device="cuda")
     for b in range(blocks):
         r0 = (n // blocks) * b
         api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, per, sample[b * per:],
                              device=device)
+        if residual:
+            sample[b * per:(b + 1) * per] = coded(sample[b * per:(b + 1) * per], r0, per)
     codebook = torch.empty((M, 256, dim // M), dtype=torch.float32, device="cuda")
     api.pq_train(sample, blocks * per, dim, M, 256, 8, seed * 1000 + 3, codebook, device=device)
     del sample
@@ -146,7 +164,7 @@ def build_index(cfg, torch, api, device, row_lo=0, row_hi=None, gt_queries=None,
     for r0 in range(row_lo, row_hi, chunk):
         m = min(chunk, row_hi - r0)
         api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, m, buf, device=device)
-        api.pq_encode(buf, m, dim, codebook, M, 256, cbuf, device=device)
+        api.pq_encode(coded(buf, r0, m), m, dim, codebook, M, 256, cbuf, device=device)
         if gt_queries is not None:
             k = min(gt_k, m)
             ti = torch.empty((gt_queries.shape[0], k), dtype=torch.int32, device="cuda")
@@ -191,13 +209,18 @@ def cpu_reference_run(index, q_host, cfg, nsample, threads):
     import oracle
     q = np.ascontiguousarray(q_host[:nsample])
     t0 = time.time()
+    residual = bool(cfg.get("residual"))
     if oracle.have_ref():
         probes, _ = oracle.ref_coarse(q, index["centroids"], cfg["nprobe"], threads=threads)
-        r = oracle.ref_ivfpq_search(index, q, probes, cfg["topk"], cfg["n_rerank"], fine_threads=threads,
-                                    rerank_threads=threads)
+        if residual:  # cpu_fine_kernel_pq_resid_cpu_lut_timed: stage 1 + exact rerank, then the id map
+            r = oracle.ref_ivfrespq_search(index, q, probes, cfg["topk"], cfg["n_rerank"], threads=threads)
+        else:
+            r = oracle.ref_ivfpq_search(index, q, probes, cfg["topk"], cfg["n_rerank"], fine_threads=threads,
+                                        rerank_threads=threads)
         kind = "reference"
     else:
-        r = oracle.ivfpq_search(index, q, cfg["nprobe"], cfg["topk"], cfg["n_rerank"])
+        search = oracle.ivfrespq_search if residual else oracle.ivfpq_search
+        r = search(index, q, cfg["nprobe"], cfg["topk"], cfg["n_rerank"])
         kind = "port"
     dt = time.time() - t0
     return r, dt, kind
@@ -268,7 +291,8 @@ def main():
             return reference_arm(args, cfg, index, q_host, gt)
 
         t0 = time.time()
-        sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True)
+        sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
+                           residual=bool(cfg.get("residual")))
         log("session created in %.1fs" % (time.time() - t0))
         stage1 = min(R, cfg["n"]) if R > topk else topk
         d_probes = torch.empty((nq, nprobe), dtype=torch.int32, device="cuda")
@@ -335,7 +359,11 @@ def main():
                     frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
                     algorithmic_bytes_per_launch=int(S * cfg["M"]), rows_per_launch=int(S), ms_per_launch=round(scan_ms, 3),
                     launches_per_step=launches_per_step,
-                    traffic=None,
+                    # DRAM bytes per launch: 2.62 B per scanned code row (dram read + write of one k_scan_h<48> launch in
+                    # an ncu capture of this workload cut to 8M rows x 2,000 queries: 1.42 GB for 5.415e8 rows), scaled
+                    # by the rows this launch scans - each code row is loaded once per group of 8 visiting queries
+                    traffic=int(2.62 * S) if cfg["M"] == 48 else None,
+                    traffic_source="ncu dram__bytes_read+write of a cut-down capture (8M rows, 2,000 queries), scaled by rows scanned",
                     lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / 148 / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
 
     # CPU baseline + parity on a bounded sample of the same batch
@@ -489,7 +517,10 @@ def coarse_only(args, cfg, torch, api, device):
                               stage_achieved_tflops=round(flops / (ms * 1e-3) / 1e12, 1)),
                 cpu_baseline=dict(value=round(ns / dt, 2), unit="queries/s", cores=cores, kind=kind,
                                   sample="first %d queries, all %d host threads" % (ns, cores)),
-                parity=dict(sample_queries=ns, ids_equal=bool(np.array_equal(ri, got_i[:ns])),
+                # the reference's partial_sort leaves the order of equal distances open; ids are compared against the
+                # restatement (ties by centroid id), distances against the reference's own output
+                parity=dict(sample_queries=ns, ids_equal=bool(np.array_equal(oracle.coarse(q_host[:ns], index["centroids"], k)[0], got_i[:ns])),
+                            ids_equal_reference_tie_order=bool(np.array_equal(ri, got_i[:ns])),
                             dist_equal=bool(np.array_equal(rd, got_d[:ns])),
                             coarse_fallback_queries=int(cnt["coarse_fallback_queries"])),
                 clocks=clocks)

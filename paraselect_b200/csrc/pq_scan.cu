@@ -222,7 +222,7 @@ __device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut,
 // Per query: admission cutoff from a strided sample of the rows it will scan.
 //   N = rows the query scans.  N <= pool capacity: cutoff = +inf (everything is admitted).
 //   Otherwise every stride-th row of each probed list is scored, stride = clamp(stage1_k / 16, 16, 64), n_s rows in
-//   all, and the cutoff is the r-th smallest sample distance with r = ceil(mu + 4 sqrt(mu) + 2), mu = stage1_k * n_s / N:
+//   all, and the cutoff is the r-th smallest sample distance with r = ceil(mu + 5 sqrt(mu) + 3), mu = stage1_k * n_s / N:
 //   the stage1_k-th smallest of all N distances lies below it except with negligible probability, and about r * stride
 //   rows (2-4 x stage1_k) pass it.  The selection kernel verifies that each pool holds at least stage1_k rows and did
 //   not overflow; the exact fallback handles the rest.  The r smallest sample keys are kept with a running cutoff:
@@ -270,7 +270,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     const int ns = carry;
     if (threadIdx.x == 0) { s_pref[nprobe] = ns; s_cnt = 0; s_cut = 0xffffffffu; }
     const float mu = (float)stage1_k * (float)ns / (float)N;
-    const int r = (int)ceilf(mu + 4.0f * sqrtf(mu) + 2.0f);
+    const int r = (int)ceilf(mu + 5.0f * sqrtf(mu) + 3.0f);
     if (r >= ns || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; return; }
     __syncthreads();
     const int nseg = per_probe ? nprobe : 1;

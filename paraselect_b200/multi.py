@@ -270,7 +270,8 @@ def bench_main(args, cfg, rank, world, local_rank):
             gpu_launches=int(tot[3].item()),
             roofline=dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak * world, unit="GB/s",
                           frac=round(achieved / (peak * world), 4), peak_source="measured" if peaks else "fallback",
-                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3), traffic=None,
+                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3),
+                          traffic=int(2.62 * S / world) if M == 48 else None,  # 2.62 DRAM bytes per scanned code row (ncu, cut-down case)
                           note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
             counters=dict(scanned_codes_per_step=int(S), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
             stages_ms_rank0=stage_ms, result_checksum=checksum, clocks=clocks)
