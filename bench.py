@@ -47,6 +47,27 @@ WORKLOADS = {
 }
 
 
+_OUT_FD = None
+
+
+def claim_stdout():
+    """Keeps a private handle on stdout for the one JSON line and points fd 1 at stderr, so that whatever libraries
+    print to stdout (NCCL's version banner, for one) cannot end up beside it."""
+    global _OUT_FD
+    if _OUT_FD is None:
+        sys.stdout.flush()
+        _OUT_FD = os.dup(1)
+        os.dup2(2, 1)
+        os.environ["PSB_BENCH_OUT_FD"] = str(_OUT_FD)  # this file may also be imported as a module beside __main__
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    fd = _OUT_FD if _OUT_FD is not None else int(os.environ.get("PSB_BENCH_OUT_FD", "1"))
+    os.write(fd, data)
+
+
 def log(*a):
     if int(os.environ.get("RANK", "0")) == 0:
         print("[bench]", *a, file=sys.stderr, flush=True)
@@ -170,6 +191,7 @@ def build_index(cfg, torch, api, device, row_lo=0, row_hi=None, gt_queries=None,
             ti = torch.empty((gt_queries.shape[0], k), dtype=torch.int32, device="cuda")
             td = torch.empty((gt_queries.shape[0], k), dtype=torch.float32, device="cuda")
             api.knn_exact(gt_queries, gt_queries.shape[0], buf, m, dim, k, ti, td, device=device)
+            torch.cuda.synchronize()  # library calls without a stream run on the default stream, torch on its own
             ti = ti.long() + r0
             if gt_d is None:
                 gt_d, gt_i = td, ti
@@ -194,6 +216,7 @@ def make_queries(cfg, torch, api, centres, w, device):
     comp = rng.choice(cfg["nlist"], size=cfg["nq"], p=w)
     noise = torch.empty((cfg["nq"], cfg["dim"]), dtype=torch.float32, device="cuda")
     api.gen_normal(cfg["seed"] * 1000 + 8, 0, cfg["nq"] * cfg["dim"], cfg["sigma"], noise, device=device)
+    torch.cuda.synchronize()
     return (centres[torch.from_numpy(comp).cuda()] + noise).contiguous()
 
 
@@ -237,6 +260,7 @@ def main():
     ap.add_argument("--queries", type=int, default=0, help="override the batch size")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU baseline sample (0 = auto)")
     args = ap.parse_args()
+    claim_stdout()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -262,7 +286,7 @@ def main():
     device = local_rank
     if world > 1 and args.impl == "ours":
         import torch.distributed as dist
-        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner out of stdout: one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's banner and warnings go to stderr: stdout is one JSON line
         dist.init_process_group("nccl")
     if args.impl == "ours" and world > 1:
         from paraselect_b200 import multi
@@ -406,7 +430,7 @@ def main():
         result_checksum=int(np.bitwise_xor.reduce((e2e_ids.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel())
                             & np.uint64((1 << 62) - 1)),
         clocks=clocks)
-    print(json.dumps(line), flush=True)
+    emit(line)
     sess.close()
     return 0
 
@@ -442,13 +466,13 @@ def coarse_only(args, cfg, torch, api, device):
                 if i >= args.warmup:
                     times.append(time.time() - t0)
             v = round(ns / float(np.mean(times)), 2)
-            print(json.dumps(dict(impl="reference", metric="coarse queries/s (top-64 of 65,536 centroids)", value=v,
+            emit(dict(impl="reference", metric="coarse queries/s (top-64 of 65,536 centroids)", value=v,
                                   unit="queries/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                                   ms_per_step=round(1e3 * float(np.mean(times)), 3), higher_is_better=True, scaling="strong",
                                   vs_baseline=None, dtype="f32", data="synthetic", config=dict(workload="c3", desc=cfg["desc"]),
                                   cpu_baseline=dict(value=v, unit="queries/s", cores=cores, kind=kind,
                                                     sample="%d queries per step, all %d host threads" % (ns, cores)),
-                                  e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))), flush=True)
+                                  e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0)))
             return 0
         sess = api.Session(index, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True)
         ids = torch.empty((nq, k), dtype=torch.int32, device="cuda")
@@ -524,7 +548,7 @@ def coarse_only(args, cfg, torch, api, device):
                             dist_equal=bool(np.array_equal(rd, got_d[:ns])),
                             coarse_fallback_queries=int(cnt["coarse_fallback_queries"])),
                 clocks=clocks)
-    print(json.dumps(line), flush=True)
+    emit(line)
     sess.close()
     return 0
 
@@ -549,7 +573,7 @@ def reference_arm(args, cfg, index, q_host, gt):
                 cpu_baseline=dict(value=v, unit="queries/s", cores=cores, kind=kind,
                                   sample="%d queries of the batch per step, all %d host threads" % (ns, cores)),
                 e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
-    print(json.dumps(line), flush=True)
+    emit(line)
     return 0
 
 

@@ -140,7 +140,10 @@ typedef struct psb_options {
                            cpu_fine_kernel_pq_resid_cpu_lut_timed (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:594-735):
                            one table per (query, probe) on q - centroid, candidate width max(n_rerank, topk, 512), and
                            the exact rerank always runs (exact rows are required). */
-    int reserved[3];
+    int reserve_sms;    /* SMs the ADC scan's persistent grid leaves free (0..64).  A multi-GPU caller that runs NCCL
+                           collectives on a second stream while the scan is in flight sets a few: a collective's CTA
+                           cannot share an SM with a scan CTA and would otherwise wait for the scan kernel to end. */
+    int reserved[2];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -212,6 +215,13 @@ psb_status psb_session_search_device(psb_session* session, const float* d_querie
 
 /* Blocks until all work queued on the session's stream is done. */
 psb_status psb_session_sync(psb_session* session);
+
+/* Redirects the stage-level calls below to another stream (stream = NULL: back to the stream the session was created
+ * with).  background != 0 marks the stream as the second stream of a caller-side pipeline: the PCIe row gather of the
+ * rerank then runs on a small grid so that a scan queued on the first stream keeps the SMs.  The caller orders the two
+ * streams with events; stage calls that share a workspace (two scans, two reranks) must not overlap.  No counterpart
+ * in the reference (its overlap executor owns its streams, src/search/ivfrespq/pipeline/ivfrespq_pipeline_cpu.cu:433-527). */
+psb_status psb_session_set_stream(psb_session* session, void* stream, int background);
 
 /* ---- stage level, DEVICE pointers, asynchronous on the session's stream --------------------------- */
 /* These mirror the reference's stage functions ivfpq_coarse / ivfpq_fine_* / ivfpq_rerank_cpu /

@@ -71,7 +71,7 @@ class Options(C.Structure):
     _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
                 ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("list_global_begin", C.c_void_p),
                 ("coarse_mode", C.c_int),
-                ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserved", C.c_int * 3)]
+                ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserve_sms", C.c_int), ("reserved", C.c_int * 2)]
 
 
 class Stats(C.Structure):
@@ -90,7 +90,7 @@ class Stats(C.Structure):
 
 EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
-    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_scan",
+    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_scan",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -141,7 +141,7 @@ class Session:
     """
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
-                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False):
+                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -174,7 +174,7 @@ class Session:
         self._keep.append(gb)
         opt = Options(list_global_begin=_p(gb), device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
-                      time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)))
+                      time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)), reserve_sms=reserve_sms)
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 
@@ -238,6 +238,10 @@ class Session:
     def stage_coarse(self, d_queries, nq, nprobe, d_ids, d_dist=None):
         _check(lib().psb_stage_coarse(self._h, C.c_void_p(_p(d_queries)), nq, nprobe, C.c_void_p(_p(d_ids)),
                                       C.c_void_p(_p(d_dist)) if d_dist is not None else None))
+
+    def set_stream(self, stream=None, background=False):
+        """Redirects the stage calls to `stream` (a cudaStream_t value; None = the session's own stream)."""
+        _check(lib().psb_session_set_stream(self._h, _stream_ptr(stream), int(background)))
 
     def stage_build_lut(self, d_queries, nq, d_lut):
         _check(lib().psb_stage_build_lut(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_lut))))

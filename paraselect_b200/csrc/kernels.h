@@ -94,6 +94,8 @@ struct ScanWorkspace {
     void* lut_h = nullptr;       // [tables][m*k] fp16 tables (tables = max_batch, x nprobe in residual mode) for the half pre-filter scan (null = fp32 scan only)
     float* lut_scale = nullptr;  // [tables]
     int scan_mode = 0;           // 0 = half pre-filter when it fits, 1 = fp32 scan
+    int reserve_ctas = 0;        // CTAs left out of the scan's persistent grid, so that kernels of another stream that
+                                 // cannot share an SM with a scan CTA (a collective's) still find a free SM
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;  // optional: bracket the scan kernel
 };
 

@@ -362,7 +362,14 @@ struct ScanArgs {
     unsigned long long* work_cursor;
     unsigned long long* counters;
     int chunk_rows;
+    int reserve_ctas;          // host side only: CTAs left out of the persistent grid (see ScanWorkspace::reserve_ctas)
 };
+
+// Persistent grid: every SM slot, minus the CTAs the caller wants kept free for kernels of another stream.
+inline unsigned scan_grid(int slots, int reserve) {
+    const int g = slots - (reserve > 0 ? reserve : 0);
+    return (unsigned)(g < 1 ? 1 : g);
+}
 
 // Largest l in [0, nlist) with item_off[l] <= item, found by warp 0 with a 32-ary search.
 __device__ __forceinline__ int find_list(const long long* __restrict__ item_off, int nlist, long long item) {
@@ -858,7 +865,7 @@ psb_status run_scan_h(const ScanArgsH& ah, int sm_count, cudaStream_t s) {
         int occ = 0;
         PSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_scan_h<M>, kScanThreads, smem));
         if (occ < 1) return fail(PSB_UNSUPPORTED_SHAPE, "half scan kernel does not fit an SM");
-        k_scan_h<M><<<sm_count * occ, kScanThreads, smem, s>>>(ah);
+        k_scan_h<M><<<scan_grid(sm_count * occ, ah.a.reserve_ctas), kScanThreads, smem, s>>>(ah);
         count_launch();
         PSB_LAUNCH_CHECK();
         return PSB_OK;
@@ -888,7 +895,7 @@ psb_status run_scan_kernel(const ScanArgs& a, int sm_count, cudaStream_t s) {
     int occ = 0;
     PSB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_scan<M, V>, kScanThreads, smem));
     if (occ < 1) return fail(PSB_UNSUPPORTED_SHAPE, "scan kernel does not fit an SM");
-    k_scan<M, V><<<sm_count * occ, kScanThreads, smem, s>>>(a);
+    k_scan<M, V><<<scan_grid(sm_count * occ, a.reserve_ctas), kScanThreads, smem, s>>>(a);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -1014,6 +1021,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     a.vis_count = ws.vis_count; a.vis_off = ws.vis_off; a.visitors = ws.visitors; a.item_off = ws.item_off;
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
+    a.reserve_ctas = ws.reserve_ctas;
     if (use_half) {
         k_lut_to_half<<<(unsigned)tables, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
         count_launch();

@@ -10,6 +10,7 @@
 //   k_topk_select     one CTA per query: bitonic sort of (distance,row) keys, duplicate rows collapse, the first
 //                     topk are written (reference semantics: src/search/ivf_common/ivf_host_rerank.cpp:152-177,
 //                     src/search/ivf_common/ivf_exact_topk.h:12-22)
+#include <cstdlib>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -250,8 +251,10 @@ psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int el
         // Beside a scan kernel on the other stream of the overlapped pipeline: few, fat CTAs.  32 CTAs of 512 threads keep
         // ~200 KB of row reads in flight - more than the PCIe bandwidth-delay product - while touching only 32 SMs, so the
         // scan keeps most SMs to itself (its dynamic work queue shifts work away from the shared ones).
+        // PSB_GATHER_CTAS overrides the CTA count (tuning knob, read once).
+        static const int cap = [] { const char* e = std::getenv("PSB_GATHER_CTAS"); const int v = e ? std::atoi(e) : 0; return v > 0 ? v : 32; }();
         long long blocks = (total * 32 + 511) / 512;
-        if (blocks > 32) blocks = 32;
+        if (blocks > cap) blocks = cap;
         k_gather_rows<<<(unsigned)blocks, 512, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
                                                        d_candidates, nq, candidate_count, candidate_stride, d_counts,
                                                        static_cast<unsigned char*>(d_stage));

@@ -169,6 +169,8 @@ struct psb_session {
     cudaStream_t stream = nullptr;
     bool own_stream = false;
     cudaStream_t aux_stream = nullptr;  // second stream of the overlapped pipeline (created on first use)
+    cudaStream_t home_stream = nullptr; // the stream the session was created with (psb_session_set_stream(NULL) returns to it)
+    bool background = false;            // stage calls currently run on a caller's second stream: small-grid gather
     psb_options opt{};
     // index shape
     int nlist = 0, dim = 0, m = 0, k = 0;
@@ -232,6 +234,7 @@ struct psb_session {
         w.fail_cursor = reinterpret_cast<int*>(sc + 6);
         w.pool_cap = pool_cap;
         w.lut_h = lut_h.p; w.lut_scale = lut_scale.as<float>(); w.scan_mode = opt.scan_mode;
+        w.reserve_ctas = opt.reserve_sms;
         return w;
     }
     // Scan workspace with a fresh event pair when kernel timing is on.
@@ -486,7 +489,7 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
         PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
-                                   s->stage.p, s->stream, s->aux_stream != nullptr && s->stream == s->aux_stream));
+                                   s->stage.p, s->stream, s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream)));
     }
     float* score = d_score;
     if (!score) {
@@ -540,6 +543,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     }
     if (opt.n_rerank > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "n_rerank above 2048 is not supported");
     if (opt.adc_mode != 0 && opt.adc_mode != 1) return fail(PSB_INVALID_ARGUMENT, "unknown adc_mode");
+    if (opt.reserve_sms < 0 || opt.reserve_sms > 64) return fail(PSB_INVALID_ARGUMENT, "reserve_sms must be in 0..64");
     if (opt.adc_mode == 1 && !index->exact.fp32 && !index->exact.u8)
         return fail(PSB_INVALID_ARGUMENT, "residual mode always reranks: exact rows are required");
     cudaDeviceProp prop;
@@ -616,6 +620,10 @@ psb_status psb_session_destroy(psb_session* s) {
     if (!s) return PSB_OK;
     cudaSetDevice(s->device);
     cudaStreamSynchronize(s->stream);
+    if (s->home_stream) {  // a redirected session: drain and return to the stream it was created with
+        cudaStreamSynchronize(s->home_stream);
+        s->stream = s->home_stream;
+    }
     s->collect_scan_events();
     if (s->registered) cudaHostUnregister(const_cast<void*>(s->exact_host));
     for (int i = 0; i < 2; ++i) {
@@ -633,6 +641,14 @@ psb_status psb_session_sync(psb_session* s) {
     if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
     PSB_CUDA(cudaStreamSynchronize(s->stream));
     return s->tc_work.check_status();
+}
+
+psb_status psb_session_set_stream(psb_session* s, void* stream, int background) {
+    if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
+    if (!s->home_stream) s->home_stream = s->stream;
+    s->stream = stream ? static_cast<cudaStream_t>(stream) : s->home_stream;
+    s->background = stream != nullptr && background != 0;
+    return PSB_OK;
 }
 
 psb_status psb_stage_coarse(psb_session* s, const float* d_queries, int nq, int nprobe, int* d_ids, float* d_dist) {

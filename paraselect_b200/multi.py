@@ -65,6 +65,11 @@ class SessionEngine:
         self.s = session
         self.torch = torch
 
+    streams = True  # stage calls can be redirected to a second CUDA stream
+
+    def set_stream(self, stream, background):
+        self.s.set_stream(stream, background)
+
     def empty(self, shape, dtype):
         return self.torch.empty(shape, dtype=dtype, device="cuda")
 
@@ -91,8 +96,9 @@ class SessionEngine:
 
 
 class ShardedSearch:
-    def __init__(self, engine, dist, world, nq, dim, M, K, nprobe, topk, width, torch, rerank=True):
+    def __init__(self, engine, dist, world, nq, dim, M, K, nprobe, topk, width, torch, rerank=True, parts=1):
         self.e, self.dist, self.world, self.torch = engine, dist, world, torch
+        self.parts, self.aux = parts, None
         self.nq, self.nprobe, self.topk, self.width, self.rerank = nq, nprobe, topk, width, rerank
         t = torch
         self.probes = engine.empty((nq, nprobe), t.int32)
@@ -121,53 +127,84 @@ class ShardedSearch:
         m = self.marks or []
         return {m[i + 1][0]: round(m[i][1].elapsed_time(m[i + 1][1]), 3) for i in range(len(m) - 1)}
 
-    def step(self, dq, profile=False):
-        e, d, nq = self.e, self.dist, self.nq
+    def _front(self, dq, q0, m):
+        """Local half of queries [q0, q0 + m): tables and ADC scan of this rank's slices -> local candidates."""
+        e = self.e
+        sl = slice(q0, q0 + m)
+        e.lut(dq[sl], m, self.lut[:m])
+        e.scan(self.lut[:m], m, self.probes[sl], self.nprobe, self.width, self.l_rows[sl], self.l_dist[sl], self.l_cnt[sl])
+        self._mark("lut+scan")
+
+    def _back(self, dq, q0, m):
+        """Exchange half of queries [q0, q0 + m): candidate all-gather and merge, partial exact scoring, combination."""
+        e, d, w, width = self.e, self.dist, self.world, self.width
+        sl = slice(q0, q0 + m)
+        m_rows, m_dist = self.l_rows[sl], self.l_dist[sl]
+        if w > 1:
+            g_rows = self.g_rows.view(-1)[:w * m * width].view(w, m, width)
+            g_dist = self.g_dist.view(-1)[:w * m * width].view(w, m, width)
+            d.all_gather_into_tensor(g_rows.view(w * m, width), self.l_rows[sl])
+            d.all_gather_into_tensor(g_dist.view(w * m, width), self.l_dist[sl])
+            self._mark("all_gather")
+            m_rows, m_dist = self.m_rows[sl], self.m_dist[sl]
+            e.merge(g_rows, g_dist, w, m, width, m_rows, m_dist)
+            self._mark("merge")
+        if self.rerank:
+            e.rerank_partial(dq[sl], m, m_rows, width, self.p_dist[sl])
+            self._mark("rerank_partial")
+            if w > 1:
+                d.all_reduce(self.p_dist[sl], op=d.ReduceOp.MIN)
+                self._mark("all_reduce_min")
+            e.select_topk(self.p_dist[sl], m_rows, m, width, self.topk, self.o_rows[sl], self.o_dist[sl])
+            self._mark("select_topk")
+        else:
+            self.o_rows[sl].copy_(m_rows[:, :self.topk])
+            self.o_dist[sl].copy_(m_dist[:, :self.topk])
+        e.map_ids(self.o_rows[sl], m * self.topk, self.o_ids[sl])
+        if w > 1:
+            d.all_reduce(self.o_ids[sl], op=d.ReduceOp.MAX)
+        self._mark("map_ids+all_reduce_max")
+
+    def step(self, dq, profile=False, parts=None):
+        """One batch.  parts > 1 cuts the batch into sub-batches; on an engine with streams the exchange half of
+        sub-batch i (collectives, PCIe rerank) then runs on a second stream beside the scan of sub-batch i + 1.
+        profile=True runs the batch serially in one piece and records per-stage times."""
+        e, nq = self.e, self.nq
+        parts = 1 if profile else (self.parts if parts is None else parts)
+        parts = max(1, min(parts, nq))
         self.marks = [] if profile else None
         self._mark("start")
         e.coarse(dq, nq, self.nprobe, self.probes)
         self._mark("coarse")
-        e.lut(dq, nq, self.lut)
-        e.scan(self.lut, nq, self.probes, self.nprobe, self.width, self.l_rows, self.l_dist, self.l_cnt)
-        self._mark("lut+scan")
-        self._sync_to_collectives()
-        if self.world > 1:
-            d.all_gather_into_tensor(self.g_rows.view(self.world * nq, self.width), self.l_rows)
-            d.all_gather_into_tensor(self.g_dist.view(self.world * nq, self.width), self.l_dist)
-            self._sync_from_collectives()
-            self._mark("all_gather")
-            e.merge(self.g_rows, self.g_dist, self.world, nq, self.width, self.m_rows, self.m_dist)
-            self._mark("merge")
-        else:
-            self.m_rows, self.m_dist = self.l_rows, self.l_dist
-        if self.rerank:
-            e.rerank_partial(dq, nq, self.m_rows, self.width, self.p_dist)
-            self._mark("rerank_partial")
-            self._sync_to_collectives()
-            if self.world > 1:
-                d.all_reduce(self.p_dist, op=d.ReduceOp.MIN)
-                self._sync_from_collectives()
-                self._mark("all_reduce_min")
-            e.select_topk(self.p_dist, self.m_rows, nq, self.width, self.topk, self.o_rows, self.o_dist)
-            self._mark("select_topk")
-        else:
-            self.o_rows.copy_(self.m_rows[:, :self.topk])
-            self.o_dist.copy_(self.m_dist[:, :self.topk])
-        e.map_ids(self.o_rows, nq * self.topk, self.o_ids)
-        self._sync_to_collectives()
-        if self.world > 1:
-            d.all_reduce(self.o_ids, op=d.ReduceOp.MAX)
-            self._sync_from_collectives()
-        self._mark("map_ids+all_reduce_max")
+        sb = (nq + parts - 1) // parts
+        streams = parts > 1 and getattr(e, "streams", False)
+        if not streams:
+            for q0 in range(0, nq, sb):
+                m = min(sb, nq - q0)
+                self._front(dq, q0, m)
+                self._back(dq, q0, m)
+            return self.o_ids, self.o_dist
+        t = self.torch
+        main = t.cuda.current_stream()
+        if self.aux is None:
+            self.aux = t.cuda.Stream(priority=0)
+        aux = self.aux
+        aux.wait_stream(main)  # the second stream starts after everything already queued
+        for q0 in range(0, nq, sb):
+            m = min(sb, nq - q0)
+            self._front(dq, q0, m)
+            aux.wait_stream(main)
+            e.set_stream(aux.cuda_stream, True)
+            try:
+                with t.cuda.stream(aux):
+                    self._back(dq, q0, m)
+            finally:
+                e.set_stream(None, False)
+        main.wait_stream(aux)
         return self.o_ids, self.o_dist
 
-    # The engine and torch.distributed are driven from one stream (the bench makes it torch's current stream), so
-    # stream order already serialises kernels and collectives; these hooks exist for engines that need more.
-    def _sync_to_collectives(self):
-        pass
-
-    def _sync_from_collectives(self):
-        pass
+    # The engine and torch.distributed are driven from torch's current stream (the bench creates the session on it, and
+    # the pipelined step redirects both to the second stream together), so stream order serialises kernels and collectives.
 
 
 def bench_main(args, cfg, rank, world, local_rank):
@@ -193,11 +230,15 @@ def bench_main(args, cfg, rank, world, local_rank):
         q_pinned = torch.empty((nq, dim), dtype=torch.float32).pin_memory()
         q_pinned.copy_(dq)
         torch.cuda.synchronize()
+        # The exchange half of a sub-batch (collectives, PCIe rerank) runs beside the next sub-batch's scan.  A collective's
+        # CTA cannot share an SM with a scan CTA, so the scan's persistent grid leaves a few SMs free for it.
+        reserve = int(os.environ.get("PSB_RESERVE_SMS", "8"))
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           list_global_begin=gb)
+                           list_global_begin=gb, reserve_sms=reserve)
         width = min(R, n) if R > topk else topk
         search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
-                               rerank=R > topk)
+                               rerank=R > topk, parts=int(os.environ.get("PSB_PARTS", "4")) if nq >= 2048 else 1)
+        search.step(dq, profile=True)  # first step in one piece: every workspace reaches its final size before streams overlap
         for _ in range(max(args.warmup, 3)):
             search.step(dq)
         torch.cuda.synchronize()
@@ -275,7 +316,7 @@ def bench_main(args, cfg, rank, world, local_rank):
                           note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
             counters=dict(scanned_codes_per_step=int(S), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
             stages_ms_rank0=stage_ms, result_checksum=checksum, clocks=clocks)
-        print(json.dumps(line), flush=True)
+        B.emit(line)
     sess.close()
     dist.barrier()
     dist.destroy_process_group()
@@ -319,7 +360,9 @@ def build_stripe(cfg, torch, api, device, offsets, gb, loff):
         if k == 0:
             continue
         api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, m, buf, device=device)
+        torch.cuda.synchronize()  # the generator runs on the default stream, torch on its own
         mine = buf[:m].index_select(0, sel)
+        torch.cuda.synchronize()
         api.pq_encode(mine, k, dim, codebook, M, 256, cbuf, device=device)
         torch.cuda.synchronize()
         torch.from_numpy(vectors[at:at + k]).copy_(mine)

@@ -34,10 +34,11 @@ class CpuCheckerEngine:
         out.copy_(torch.from_numpy(ids.astype(np.int32)))
 
     def lut(self, dq, nq, out):
-        out.copy_(torch.from_numpy(oracle.pq_lut(dq.numpy(), self.ix["codebook"])))
+        self.q_sub = dq.numpy()  # the scan below belongs to the same (sub-)batch of queries
+        out.copy_(torch.from_numpy(oracle.pq_lut(self.q_sub, self.ix["codebook"])))
 
     def scan(self, lut, nq, probes, nprobe, width, rows, dist, count):
-        r, d, c, _ = oracle.pq_scan(self.q, probes.numpy().astype(np.int64), self.loff, self.ix["codes"],
+        r, d, c, _ = oracle.pq_scan(self.q_sub, probes.numpy().astype(np.int64), self.loff, self.ix["codes"],
                                     self.ix["codebook"], width)
         # local rows -> index-wide rows; the checker orders ties by local row, which is monotone in the global row
         lists = np.searchsorted(self.loff, np.clip(r, 0, None), side="right") - 1

@@ -28,6 +28,9 @@ def main():
     ids, dd = s.step(torch.from_numpy(q))
     want = oracle.ivfpq_search(ix, q, nprobe, topk, width)
     ok = np.array_equal(ids.numpy(), want["indices"]) and np.array_equal(dd.numpy(), want["distances"])
+    # the same batch cut into three sub-batches (16 = 6 + 6 + 4): each runs its own exchange
+    ids3, dd3 = s.step(torch.from_numpy(q), parts=3)
+    ok = ok and np.array_equal(ids3.numpy(), want["indices"]) and np.array_equal(dd3.numpy(), want["distances"])
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

@@ -405,3 +405,24 @@ def test_overlapped_pipeline_equals_serial_pipeline(psb):
         s.sync()
         assert np.array_equal(ids.cpu().numpy(), res[True]["indices"])
         assert np.array_equal(dd.cpu().numpy(), res[True]["distances"])
+
+
+def test_sharded_step_with_second_stream_equals_search(psb):
+    """The sharded step on one rank, cut into sub-batches whose exchange half (rerank, id map) runs on a second stream
+    through psb_session_set_stream while the next sub-batch scans: same results as the session's own search."""
+    torch = _torch()
+    from paraselect_b200.multi import SessionEngine, ShardedSearch
+    ix = synth.make_index(60000, 64, 64, 16, seed=71, zipf=True)
+    q = synth.make_queries(ix, 700, seed=72, weights=synth.zipf_weights(64))
+    with psb.Session(ix, n_rerank=120) as s:
+        want = s.search(q, 8, 10, batch_size=700)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        with psb.Session(ix, n_rerank=120, max_batch=700, stream=stream.cuda_stream) as s:
+            search = ShardedSearch(SessionEngine(s, torch), None, 1, 700, 64, 16, 256, 8, 10, 120, torch, rerank=True, parts=3)
+            dq = dev(q)
+            for parts in (1, 3, 3):
+                ids, dd = search.step(dq, parts=parts)
+                torch.cuda.synchronize()
+                assert np.array_equal(ids.cpu().numpy(), want["indices"])
+                assert np.array_equal(dd.cpu().numpy(), want["distances"])
