@@ -296,7 +296,9 @@ def bench_main(args, cfg, rank, world, local_rank):
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         S = tot[0].item() / max(1, args.steps)                      # rows scanned per step, all ranks
+        launches_per_step = max(1.0, mx[2].item()) / max(1, args.steps)  # one scan launch per sub-batch
         scan_ms = mx[1].item() / max(1.0, mx[2].item())             # slowest rank's scan kernel, per launch
+        S = S / launches_per_step                                   # rows per launch, all ranks
         achieved = S * M / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
         line = dict(
             metric="QPS (IVF-PQ search, recall@k equal to the reference CPU path)", value=round(nq / (ms_dev * 1e-3), 1),
@@ -311,10 +313,10 @@ def bench_main(args, cfg, rank, world, local_rank):
             gpu_launches=int(tot[3].item()),
             roofline=dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak * world, unit="GB/s",
                           frac=round(achieved / (peak * world), 4), peak_source="measured" if peaks else "fallback",
-                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3),
+                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3), launches_per_step=launches_per_step,
                           traffic=int(2.62 * S / world) if M == 48 else None,  # 2.62 DRAM bytes per scanned code row (ncu, cut-down case)
                           note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
-            counters=dict(scanned_codes_per_step=int(S), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
+            counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
             stages_ms_rank0=stage_ms, result_checksum=checksum, clocks=clocks)
         B.emit(line)
     sess.close()
