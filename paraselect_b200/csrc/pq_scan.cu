@@ -17,6 +17,7 @@
 // Arithmetic matches the CPU path bit for bit: table entries are the sequential non-fused fp32 sum of
 // (q-c)^2 and ADC distances are the sequential fp32 sum over m = 0..M-1
 // (reference: src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:51-63,76-80).
+#include <cstdlib>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -234,7 +235,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
                  const long long* __restrict__ offsets, int nlist, int lb, int le,
                  const uint8_t* __restrict__ codes, long long row_base, int m, int k,
                  const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr,
-                 int per_probe, int tree) {
+                 int per_probe, int tree, float margin_sigma, float margin_add) {
     // per_probe (residual mode): lut holds one table per (query, probe) pair; the probes are then sampled one after
     // the other, each with its own table staged in shared memory.
     extern __shared__ __align__(16) unsigned char s_seed_raw[];
@@ -270,7 +271,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     const int ns = carry;
     if (threadIdx.x == 0) { s_pref[nprobe] = ns; s_cnt = 0; s_cut = 0xffffffffu; }
     const float mu = (float)stage1_k * (float)ns / (float)N;
-    const int r = (int)ceilf(mu + 5.0f * sqrtf(mu) + 3.0f);
+    const int r = (int)ceilf(mu + margin_sigma * sqrtf(mu) + margin_add);
     if (r >= ns || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; return; }
     __syncthreads();
     const int nseg = per_probe ? nprobe : 1;
@@ -918,6 +919,12 @@ psb_status run_scan_m(const ScanArgs& a, int group, int sm_count, cudaStream_t s
     }
 }
 
+// Safety margin of the sampled cutoff in standard deviations (PSB_SEED_SIGMA overrides it; tuning knob, read once).
+float seed_margin_sigma() {
+    static const float v = [] { const char* e = std::getenv("PSB_SEED_SIGMA"); const float x = e ? (float)std::atof(e) : 0.f; return x >= 2.f && x <= 10.f ? x : 5.0f; }();
+    return v;
+}
+
 template <int M>
 psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq, const int* d_probes,
                     int nprobe, int stage1_k, cudaStream_t s) {
@@ -926,7 +933,7 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
                                                          stage1_k, ws.pool_cap, ws.thr, ix.residual ? 1 : 0,
-                                                         tree_order(ix) ? 1 : 0);
+                                                         tree_order(ix) ? 1 : 0, seed_margin_sigma(), seed_margin_sigma() - 2.0f);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

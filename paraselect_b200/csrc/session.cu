@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <cstdlib>
 #include <algorithm>
 #include <atomic>
 #include <climits>
@@ -793,8 +794,14 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     if (times) rc = tm_s.mark(st);
     if (rc == PSB_OK) rc = coarse_exact(s, dq, n, nprobe, d_probes, nullptr);
     if (rc == PSB_OK && times) rc = tm_s.mark(st);
-    for (int p0 = 0; p0 < n && rc == PSB_OK; p0 += sb) {
-        const int m = std::min(sb, n - p0);
+    // Sub-batch boundaries: equal cuts (cuts that shrink toward the end, to shorten the last rerank that nothing hides,
+    // measured no better).
+    std::vector<int> cuts;
+    for (int p0 = 0; p0 < n; p0 += sb) cuts.push_back(p0);
+    cuts.push_back(n);
+    for (size_t ci = 0; ci + 1 < cuts.size() && rc == PSB_OK; ++ci) {
+        const int p0 = cuts[ci];
+        const int m = cuts[ci + 1] - p0;
         const float* q = dq + (size_t)p0 * s->dim;
         int* probes = d_probes + (size_t)p0 * nprobe;
         int* rows_out = rerank ? s->cand_rows.as<int>() + (size_t)p0 * stage1_k : s->out_rows.as<int>() + (size_t)p0 * topk;
@@ -1098,13 +1105,23 @@ psb_status psb_knn_exact(const float* d_queries, int nq, const float* d_base, in
 psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_centroids, int k, int iters,
                             int* d_assign, double* h_objective, int device, void* stream) {
     if (!d_data || !d_centroids || n <= 0 || dim <= 0 || k <= 0 || iters < 0) return fail(PSB_INVALID_ARGUMENT, "invalid k-means request");
-    PSB_TRY(check_device(device));
+    cudaDeviceProp prop;
+    PSB_TRY(check_device(device, &prop));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     DevBuf tile, assign, best, sums, counts, obj;
     const size_t row_bytes = sizeof(float) * (size_t)k;
     long long chunk = (long long)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes);
     chunk = std::min<long long>(chunk, n);
-    PSB_TRY(tile.reserve(row_bytes * (size_t)chunk));
+    // Assignment = nearest centroid = the coarse stage with nprobe 1.  Large problems take the tensor-core filter with
+    // exact refinement (identical assignments and distances: ties go to the lower centroid id on both paths); the bf16
+    // centroid operand is rebuilt from the current centroids at the start of every iteration.
+    const long long chunk_tc = std::min<long long>(n, 262144);
+    const bool tc = coarse_tc_supported((int)chunk_tc, k, dim, 1);
+    TcIndexBuffers tci;
+    TcWorkBuffers tcw;
+    std::vector<float> h_centroids;
+    if (tc) { chunk = chunk_tc; h_centroids.resize((size_t)k * dim); }
+    else PSB_TRY(tile.reserve(row_bytes * (size_t)chunk));
     PSB_TRY(best.reserve(sizeof(float) * (size_t)n));
     int* d_as = d_assign;
     if (!d_as) { PSB_TRY(assign.reserve(sizeof(int) * (size_t)n)); d_as = assign.as<int>(); }
@@ -1112,10 +1129,22 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
     PSB_TRY(obj.reserve(sizeof(double) * ((size_t)iters + 1)));
     PSB_CUDA(cudaMemsetAsync(obj.p, 0, sizeof(double) * ((size_t)iters + 1), st));
     for (int it = 0; it <= iters; ++it) {
+        if (tc) {
+            PSB_CUDA(cudaMemcpyAsync(h_centroids.data(), d_centroids, sizeof(float) * (size_t)k * dim, cudaMemcpyDeviceToHost, st));
+            PSB_CUDA(cudaStreamSynchronize(st));
+            PSB_TRY(tci.prepare(h_centroids.data(), d_centroids, k, dim, st));
+        }
         for (long long r0 = 0; r0 < n; r0 += chunk) {
             const int nn = (int)std::min<long long>(chunk, n - r0);
-            PSB_TRY(launch_coarse_dist_exact(d_data + (size_t)r0 * dim, nn, d_centroids, k, dim, tile.as<float>(), st));
-            PSB_TRY(launch_select_rows(tile.as<float>(), nn, k, 1, d_as + r0, best.as<float>() + r0, st));
+            if (tc && coarse_tc_supported(nn, k, dim, 1)) {
+                PSB_TRY(tcw.ensure(nn, k, dim, 1, st));
+                PSB_TRY(launch_coarse_tc(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, 1,
+                                         d_as + r0, best.as<float>() + r0, prop.multiProcessorCount, st));
+            } else {
+                PSB_TRY(tile.reserve(row_bytes * (size_t)nn));
+                PSB_TRY(launch_coarse_dist_exact(d_data + (size_t)r0 * dim, nn, d_centroids, k, dim, tile.as<float>(), st));
+                PSB_TRY(launch_select_rows(tile.as<float>(), nn, k, 1, d_as + r0, best.as<float>() + r0, st));
+            }
         }
         PSB_CUDA(cudaMemsetAsync(sums.p, 0, sizeof(double) * (size_t)k * dim, st));
         PSB_CUDA(cudaMemsetAsync(counts.p, 0, sizeof(int) * (size_t)k, st));
@@ -1125,6 +1154,7 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
     }
     if (h_objective) PSB_CUDA(cudaMemcpyAsync(h_objective, obj.p, sizeof(double) * ((size_t)iters + 1), cudaMemcpyDeviceToHost, st));
     PSB_CUDA(cudaStreamSynchronize(st));
+    if (tc) PSB_TRY(tcw.check_status());
     return PSB_OK;
 }
 

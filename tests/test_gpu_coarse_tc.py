@@ -85,3 +85,23 @@ def test_tc_filter_does_the_work_not_the_fallback(psb):
     assert out[2][2] == 0
     oi, od = oracle.coarse(q, ix["centroids"], 64)
     assert np.array_equal(out[2][0], oi) and np.array_equal(out[2][1], od)
+
+
+def test_kmeans_assignment_on_the_tensor_core_filter(psb):
+    """k = 1024 centroids takes the tensor-core filter with exact refinement for the assignment step (the coarse stage
+    with nprobe 1); assignments, objective and centroids must equal the exact SIMT path's, i.e. the checker's."""
+    import torch
+    import synth
+    _, data, _ = synth.mixture(30000, 64, 300, 0.3, seed=16)
+    rng = np.random.default_rng(5)
+    init = data[rng.choice(30000, size=1024, replace=False)].copy()
+    ocen, oassign, oobj = oracle.kmeans_lloyd(data, init, 3)
+    dcen = torch.from_numpy(init).cuda()
+    dassign = torch.empty((30000,), dtype=torch.int32, device="cuda")
+    obj = psb.kmeans_train(torch.from_numpy(data).cuda(), 30000, 64, dcen, 1024, 3, dassign)
+    assert np.allclose(obj, oobj, rtol=1e-5)
+    assert np.sqrt(np.mean((dcen.cpu().numpy() - ocen) ** 2)) < 1e-5
+    assert np.mean(dassign.cpu().numpy() == oassign) > 0.9999
+    # final assignment against the final centroids, exactly
+    fa, fd = oracle.kmeans_assign(data, dcen.cpu().numpy())
+    assert np.array_equal(dassign.cpu().numpy(), fa)
