@@ -133,13 +133,31 @@ struct TcArgs {
     float cmax;             // max |c'|
     float* gmin;            // pass 1 out: [nq][ngroups]
     const float* seltop;    // pass 2 in: [nq][nprobe] ascending group minima (T = last)
-    int* cand_cnt;          // pass 2 out: [nq]
-    int* cand;              // pass 2 out: [nq][kCandCap]
+    uint32_t* mask;         // pass 2 out: [nq][mwords] one bit per centroid (zeroed before the launch; only non-zero words are written)
+    int mwords;             // ntiles * TCOL / 32
     int* status;            // [1] != 0 after a bounded wait gave up
-    int cblocks, qtiles, qsplits;  // work units = cblocks (512 centroids each) x qsplits (ranges of query tiles)
+    int cblocks, qtiles;    // work = cblocks (512 centroids each) x qtiles (128 queries each) tile pairs
 };
 
-// Persistent, warp-specialised kernel.  A work unit = (block of 512 centroids, range of query tiles).  The unit's
+// Work split: the (centroid block, query tile) pairs are numbered block-major and CTA b takes the contiguous range
+// [total * b / grid, total * (b + 1) / grid), so every CTA gets the same number of tile pairs (+-1) and reloads its
+// resident centroid block at most once or twice.  A range is walked as segments of one centroid block each.
+__device__ __forceinline__ void cta_range(const TcArgs& a, long long& l0, long long& l1) {
+    const long long total = (long long)a.cblocks * a.qtiles;
+    l0 = total * blockIdx.x / gridDim.x;
+    l1 = total * (blockIdx.x + 1) / gridDim.x;
+}
+__device__ __forceinline__ int seg_count(const TcArgs& a, long long l0, long long l1) {
+    return l1 > l0 ? (int)((l1 - 1) / a.qtiles - l0 / a.qtiles) + 1 : 0;
+}
+__device__ __forceinline__ void seg_get(const TcArgs& a, long long l0, long long l1, int i, int& cblock, int& t0, int& t1) {
+    cblock = (int)(l0 / a.qtiles) + i;
+    const long long b = (long long)cblock * a.qtiles;
+    t0 = (int)((l0 > b ? l0 : b) - b);
+    t1 = (int)((l1 < b + a.qtiles ? l1 : b + a.qtiles) - b);
+}
+
+// Persistent, warp-specialised kernel.  A work unit = one segment of the CTA's range: (block of 512 centroids, range of query tiles).  The unit's
 // two centroid tiles (B operands) stay in shared memory while query tiles (A operand, 128 rows) stream through a
 // two-stage ring; each query tile is multiplied against both centroid tiles into two tensor-memory accumulators, so
 // the epilogue of one accumulator overlaps the MMAs of the other.
@@ -183,15 +201,17 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const int nunits = a.cblocks * a.qsplits;
+    long long l0, l1;
+    cta_range(a, l0, l1);
+    const int nunits = seg_count(a, l0, l1);
     int failed = 0;
 
     if (warp == kEpiWarps) {
         if (lane == 0) {
             uint32_t it = 0, un = 0;  // query tiles issued, units issued
-            for (int u = blockIdx.x; u < nunits && !failed; u += gridDim.x, ++un) {
-                const int cblock = u / a.qsplits, qs = u % a.qsplits;
-                const int t0 = (int)((long long)a.qtiles * qs / a.qsplits), t1 = (int)((long long)a.qtiles * (qs + 1) / a.qsplits);
+            for (; (int)un < nunits && !failed; ++un) {
+                int cblock, t0, t1;
+                seg_get(a, l0, l1, (int)un, cblock, t0, t1);
                 if (!mbar_wait(&b_empty, (un & 1u) ^ 1u)) { failed = 1; break; }
                 mbar_expect_tx(&b_full, (uint32_t)(2 * b_bytes));
                 for (int h = 0; h < 2; ++h)
@@ -209,9 +229,10 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     } else if (warp == kEpiWarps + 1) {
         if (lane == 0) {
             uint32_t it = 0, un = 0, nacc[2] = {0, 0};
-            for (int u = blockIdx.x; u < nunits && !failed; u += gridDim.x, ++un) {
-                const int qs = u % a.qsplits;
-                const int t0 = (int)((long long)a.qtiles * qs / a.qsplits), t1 = (int)((long long)a.qtiles * (qs + 1) / a.qsplits);
+            for (; (int)un < nunits && !failed; ++un) {
+                int cblock, t0, t1;
+                seg_get(a, l0, l1, (int)un, cblock, t0, t1);
+                (void)cblock;
                 if (!mbar_wait(&b_full, un & 1u)) { failed = 1; break; }
                 for (int t = t0; t < t1 && !failed; ++t, ++it) {
                     const uint32_t st = it % kStagesA;
@@ -238,9 +259,9 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
         const int quad = warp & 3, part = warp >> 2;
         const int row = quad * 32 + lane;  // tensor-memory lane = row of the current query tile
         const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-        for (int u = blockIdx.x; u < nunits; u += gridDim.x) {  // every thread passes both barriers of every unit, failed or not
-            const int cblock = u / a.qsplits, qs = u % a.qsplits;
-            const int t0 = (int)((long long)a.qtiles * qs / a.qsplits), t1 = (int)((long long)a.qtiles * (qs + 1) / a.qsplits);
+        for (int u = 0; u < nunits; ++u) {  // every thread passes both barriers of every unit, failed or not
+            int cblock, t0, t1;
+            seg_get(a, l0, l1, u, cblock, t0, t1);
             asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // previous unit's readers of s_cn2 are done
             for (int i = tid; i < kBlockCols; i += kEpiThreads) s_cn2[i] = a.cn2[(size_t)cblock * kBlockCols + i];
             asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
@@ -302,26 +323,11 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                                     default: group_mins<1>(v, out); break;
                                 }
                             } else {
-                                float m[8];
+                                // one bit per centroid of this 32-column chunk; most chunks hold none and write nothing
+                                uint32_t bits = 0;
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) m[j] = fmaxf(fmaxf(v[j], v[j + 8]), fmaxf(v[j + 16], v[j + 24]));
-                                const float mm = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
-                                if (mm >= cut) {  // some centroid of this chunk is a candidate (about one chunk in ten)
-                                    // m[j] covers v[j], v[j+8], v[j+16], v[j+24]: expand only the groups that hold one, so a
-                                    // warp whose lanes hit in different places executes a few short blocks, not all 32 tests
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) {
-                                        if (m[j] >= cut) {
-#pragma unroll
-                                            for (int i = 0; i < 4; ++i) {
-                                                if (v[j + 8 * i] >= cut) {
-                                                    const int pos = atomicAdd(&a.cand_cnt[q], 1);
-                                                    if (pos < kCandCap) a.cand[(size_t)q * kCandCap + pos] = c0 + j + 8 * i;
-                                                }
-                                            }
-                                        }
-                                    }
-                                }
+                                for (int j = 0; j < 32; ++j) bits |= (v[j] >= cut ? 1u : 0u) << j;
+                                if (bits) a.mask[(size_t)q * a.mwords + (c0 >> 5)] = bits;
                             }
                         }
                     }
@@ -373,17 +379,57 @@ __global__ void k_fill_inf(float* p, long long n) {
     if (i < n) p[i] = __int_as_float(0x7f800000);
 }
 
+// Per query row the k-th smallest of n <= 2048 values, written to out[q * out_stride + out_stride - 1].  One warp per row:
+// the values sit in registers as order-preserving integer keys and the answer is found by bisection on the key (32
+// counting rounds), which is exact.
+constexpr int kKthPerLane = 64;
+__global__ void __launch_bounds__(256)
+k_kth_smallest(const float* __restrict__ vals, int nq, int n, int k, float* __restrict__ out, int out_stride) {
+    const int q = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (q >= nq) return;
+    uint32_t key[kKthPerLane];
+#pragma unroll
+    for (int j = 0; j < kKthPerLane; ++j) {
+        const int i = j * 32 + lane;
+        key[j] = i < n ? f2o(vals[(size_t)q * n + i]) : 0xffffffffu;
+    }
+    uint32_t lo = 0u, hi = 0xffffffffu;
+    while (lo < hi) {
+        const uint32_t mid = lo + ((hi - lo) >> 1);
+        int c = 0;
+#pragma unroll
+        for (int j = 0; j < kKthPerLane; ++j) c += key[j] <= mid ? 1 : 0;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (c >= k) hi = mid; else lo = mid + 1;
+    }
+    if (lane == 0) out[(size_t)q * out_stride + out_stride - 1] = o2f(lo);
+}
+
 // Exact re-scoring of a query's candidates in the CPU path's arithmetic, sort by (distance, id), first nprobe out.
 constexpr int kRefineThreads = 256;
 __global__ void __launch_bounds__(kRefineThreads)
 k_coarse_refine(const float* __restrict__ queries, const float* __restrict__ centroids, int dim, int nlist, int nprobe,
-                const int* __restrict__ cand_cnt, const int* __restrict__ cand, int* __restrict__ out_ids,
+                const uint32_t* __restrict__ mask, int mwords, int* __restrict__ out_ids,
                 float* __restrict__ out_dist, int* __restrict__ fail_list, int* __restrict__ n_fail) {
     extern __shared__ __align__(16) unsigned char s_ref[];
     uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_ref);                        // [kCandCap]
     float* s_q = reinterpret_cast<float*>(s_ref + (size_t)kCandCap * 8);         // [dim]
+    int* s_cand = reinterpret_cast<int*>(s_ref + (size_t)kCandCap * 8 + (size_t)((dim + 3) & ~3) * 4);  // [kCandCap]
+    __shared__ int s_n;
     const int q = blockIdx.x;
-    const int n = cand_cnt[q];
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+    for (int w = threadIdx.x; w < mwords; w += blockDim.x) {  // the candidate bits of this query -> list of centroid ids
+        uint32_t bits = mask[(size_t)q * mwords + w];
+        while (bits) {
+            const int j = __ffs((int)bits) - 1;
+            bits &= bits - 1;
+            const int pos = atomicAdd(&s_n, 1);
+            if (pos < kCandCap) s_cand[pos] = w * 32 + j;
+        }
+    }
+    __syncthreads();
+    const int n = s_n;
     if (n > kCandCap || n < nprobe) {
         if (threadIdx.x == 0) {
             fail_list[atomicAdd(n_fail, 1)] = q;
@@ -397,12 +443,25 @@ k_coarse_refine(const float* __restrict__ queries, const float* __restrict__ cen
     for (int i = threadIdx.x; i < np; i += blockDim.x) {
         uint64_t key = KEY_MAX;
         if (i < n) {
-            const int c = cand[(size_t)q * kCandCap + i];
+            const int c = s_cand[i];
             const float* cp = centroids + (size_t)c * dim;
             float sum = 0.0f;
-            for (int d = 0; d < dim; ++d) {
-                const float diff = __fsub_rn(s_q[d], __ldg(cp + d));
-                sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+            if ((dim & 3) == 0) {  // 16-byte loads: a row's 32-byte sectors are fetched once or twice, not eight times
+                const float4* cp4 = reinterpret_cast<const float4*>(cp);
+                const float4* q4 = reinterpret_cast<const float4*>(s_q);
+                for (int d = 0; d < dim / 4; ++d) {
+                    const float4 x = __ldg(cp4 + d);
+                    const float4 y = q4[d];
+                    float diff = __fsub_rn(y.x, x.x); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                    diff = __fsub_rn(y.y, x.y); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                    diff = __fsub_rn(y.z, x.z); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                    diff = __fsub_rn(y.w, x.w); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                }
+            } else {
+                for (int d = 0; d < dim; ++d) {
+                    const float diff = __fsub_rn(s_q[d], __ldg(cp + d));
+                    sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                }
             }
             key = make_key(sum, (uint32_t)c);
         }
@@ -502,6 +561,7 @@ psb_status encode_rows_map(CUtensorMap* map, const void* base, long long rows, i
 int coarse_tc_padded_dim(int dim) { return (dim + KATOM - 1) / KATOM * KATOM; }
 int coarse_tc_tiles(int nlist) { return (nlist + kBlockCols - 1) / kBlockCols * 2; }  // whole 512-centroid blocks
 int coarse_tc_cand_cap() { return kCandCap; }
+int coarse_tc_mask_words(int nlist) { return coarse_tc_tiles(nlist) * TCOL / 32; }
 
 int coarse_tc_group(int nlist, int nprobe) {
     int g = 32;
@@ -552,7 +612,7 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     a.lg_group = 0;
     while ((1 << a.lg_group) < group) ++a.lg_group;
     a.nprobe = nprobe; a.cn2 = ix.cn2; a.qnorm = ws.qnorm; a.cmax = ix.cmax; a.gmin = ws.gmin; a.seltop = ws.seltop;
-    a.cand_cnt = ws.cand_cnt; a.cand = ws.cand; a.status = ws.status;
+    a.mask = reinterpret_cast<uint32_t*>(ws.cand); a.mwords = coarse_tc_mask_words(ix.nlist); a.status = ws.status;
     const size_t smem = (size_t)katoms * (kStagesA * TQ + 2 * TCOL) * 128 + 1024;
     PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -560,13 +620,10 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     a.qtiles = (nq + TQ - 1) / TQ;
     a.cblocks = ntiles / 2;
-    // enough units to fill the SMs a few times over, never more ranges than query tiles
-    a.qsplits = (3 * sm_count + a.cblocks - 1) / a.cblocks;
-    a.qsplits = a.qsplits < 1 ? 1 : (a.qsplits > a.qtiles ? a.qtiles : a.qsplits);
-    const int nunits = a.cblocks * a.qsplits;
-    const dim3 grid(nunits < sm_count ? nunits : sm_count);
+    const long long pairs = (long long)a.cblocks * a.qtiles;
+    const dim3 grid((unsigned)(pairs < sm_count ? pairs : sm_count));
     constexpr int kTcThreads = kTcThreadsV2;
-    PSB_CUDA(cudaMemsetAsync(ws.cand_cnt, 0, sizeof(int) * (size_t)nq, s));
+    PSB_CUDA(cudaMemsetAsync(ws.cand, 0, sizeof(uint32_t) * (size_t)nq * a.mwords, s));
     PSB_CUDA(cudaMemsetAsync(ws.n_fail, 0, 2 * sizeof(int), s));  // n_fail, cursor
     if (ws.ev[0]) PSB_CUDA(cudaEventRecord(ws.ev[0], s));
     if (aug) k_coarse_tc<false, true><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
@@ -574,7 +631,14 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     if (ws.ev[1]) PSB_CUDA(cudaEventRecord(ws.ev[1], s));
     count_launch();
     PSB_LAUNCH_CHECK();
-    PSB_TRY(launch_select_rows(ws.gmin, nq, ngroups, nprobe, ws.selids, ws.seltop, s));
+    // pass 2 needs only T = the nprobe-th smallest group minimum of each query
+    if (ngroups <= kKthPerLane * 32) {
+        k_kth_smallest<<<(unsigned)(((long long)nq * 32 + 255) / 256), 256, 0, s>>>(ws.gmin, nq, ngroups, nprobe, ws.seltop, nprobe);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    } else {
+        PSB_TRY(launch_select_rows(ws.gmin, nq, ngroups, nprobe, ws.selids, ws.seltop, s));
+    }
     if (ws.ev[2]) PSB_CUDA(cudaEventRecord(ws.ev[2], s));
     if (aug) k_coarse_tc<true, true><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
     else k_coarse_tc<true, false><<<grid, kTcThreads, smem, s>>>(map_q, map_c, a);
@@ -582,9 +646,10 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     count_launch();
     PSB_LAUNCH_CHECK();
     {
-        const size_t rsmem = (size_t)kCandCap * 8 + (size_t)ix.dim * sizeof(float);
-        k_coarse_refine<<<nq, kRefineThreads, rsmem, s>>>(d_queries, ix.centroids, ix.dim, ix.nlist, nprobe, ws.cand_cnt,
-                                                          ws.cand, d_ids, d_dist, ws.fail_list, ws.n_fail);
+        const size_t rsmem = (size_t)kCandCap * 8 + (size_t)((ix.dim + 3) & ~3) * sizeof(float) + (size_t)kCandCap * sizeof(int);
+        k_coarse_refine<<<nq, kRefineThreads, rsmem, s>>>(d_queries, ix.centroids, ix.dim, ix.nlist, nprobe,
+                                                          reinterpret_cast<const uint32_t*>(ws.cand), a.mwords, d_ids, d_dist,
+                                                          ws.fail_list, ws.n_fail);
         count_launch();
         PSB_LAUNCH_CHECK();
     }

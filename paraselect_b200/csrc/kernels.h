@@ -49,7 +49,7 @@ struct CoarseTcWorkspace {
     float* seltop;   // [nq][nprobe]
     int* selids;     // [nq][nprobe]
     int* cand_cnt;   // [nq]
-    int* cand;       // [nq][cand cap]
+    int* cand;       // [nq][mask words]: pass 2's candidate bit mask, one bit per (padded) centroid
     int* fail_list;  // [nq]
     int* n_fail;     // [2]: count, cursor
     int* status;     // [1]
@@ -58,6 +58,7 @@ struct CoarseTcWorkspace {
 int coarse_tc_padded_dim(int dim);
 int coarse_tc_tiles(int nlist);
 int coarse_tc_cand_cap();
+int coarse_tc_mask_words(int nlist);
 int coarse_tc_group(int nlist, int nprobe);
 bool coarse_tc_supported(int nq, int nlist, int dim, int nprobe);
 // d_cb [nlist][dimp] bf16, d_cn2 [tiles*256], d_cnorm [nlist] out.

@@ -132,7 +132,7 @@ struct TcWorkBuffers {
         PSB_TRY(seltop.reserve(sizeof(float) * (size_t)nq * nprobe));
         PSB_TRY(selids.reserve(sizeof(int) * (size_t)nq * nprobe));
         PSB_TRY(cand_cnt.reserve(sizeof(int) * (size_t)nq));
-        PSB_TRY(cand.reserve(sizeof(int) * (size_t)nq * coarse_tc_cand_cap()));
+        PSB_TRY(cand.reserve(sizeof(int) * (size_t)nq * coarse_tc_mask_words(nlist)));
         PSB_TRY(fail_list.reserve(sizeof(int) * (size_t)nq));
         if (!scalars.p) {
             PSB_TRY(scalars.reserve(sizeof(int) * 4));
