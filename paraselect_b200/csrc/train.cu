@@ -47,6 +47,64 @@ k_pq_encode(const float* __restrict__ data, long long n, int dim, const float* _
     for (long long i = threadIdx.x; i < rows_here * m; i += kEncThreads) codes[(size_t)row0 * m + i] = s_codes[i];
 }
 
+// Same result, rows staged in shared memory: the CTA's rows are read once with coalesced loads into a tile padded to
+// dim + 1 floats per row (conflict-free when every thread reads its own row), each thread keeps its sub-vector in
+// registers while it walks the 256 codewords (broadcast reads).  DSUB = 0: run-time sub-vector length.
+template <int DSUB>
+__global__ void __launch_bounds__(kEncThreads)
+k_pq_encode_tile(const float* __restrict__ data, long long n, int dim, const float* __restrict__ codebook, int m, int k,
+                 uint8_t* __restrict__ codes) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    const int dsub = DSUB > 0 ? DSUB : dim / m;
+    const int pitch = dim + 1;
+    float* s_x = reinterpret_cast<float*>(s_raw);                                            // [kEncThreads][pitch]
+    float* s_cb = s_x + (size_t)kEncThreads * pitch;                                         // [k * dsub]
+    uint8_t* s_codes = reinterpret_cast<uint8_t*>(s_cb + (size_t)k * dsub);                  // [kEncThreads * m]
+    const long long row0 = (long long)blockIdx.x * kEncThreads;
+    const long long rows_here = min((long long)kEncThreads, n - row0);
+    for (long long i = threadIdx.x; i < rows_here * dim; i += kEncThreads) {
+        const int r = (int)(i / dim), d = (int)(i % dim);
+        s_x[(size_t)r * pitch + d] = data[(size_t)row0 * dim + i];
+    }
+    const bool live = threadIdx.x < rows_here;
+    const float* xs = s_x + (size_t)threadIdx.x * pitch;
+    for (int sub = 0; sub < m; ++sub) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < k * dsub; i += kEncThreads) s_cb[i] = codebook[(size_t)sub * k * dsub + i];
+        __syncthreads();
+        if (live) {
+            float best = FLT_MAX; int bc = 0;
+            if constexpr (DSUB > 0) {
+                float xr[DSUB];
+#pragma unroll
+                for (int d = 0; d < DSUB; ++d) xr[d] = xs[sub * DSUB + d];
+#pragma unroll 4
+                for (int c = 0; c < k; ++c) {
+                    float dist = 0.0f;
+#pragma unroll
+                    for (int d = 0; d < DSUB; ++d) {
+                        const float diff = __fsub_rn(xr[d], s_cb[c * DSUB + d]);
+                        dist = __fadd_rn(dist, __fmul_rn(diff, diff));
+                    }
+                    if (dist < best) { best = dist; bc = c; }
+                }
+            } else {
+                for (int c = 0; c < k; ++c) {
+                    float dist = 0.0f;
+                    for (int d = 0; d < dsub; ++d) {
+                        const float diff = __fsub_rn(xs[sub * dsub + d], s_cb[c * dsub + d]);
+                        dist = __fadd_rn(dist, __fmul_rn(diff, diff));
+                    }
+                    if (dist < best) { best = dist; bc = c; }
+                }
+            }
+            s_codes[threadIdx.x * m + sub] = (uint8_t)bc;
+        }
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < rows_here * m; i += kEncThreads) codes[(size_t)row0 * m + i] = s_codes[i];
+}
+
 __global__ void k_pq_accumulate(const float* __restrict__ data, long long n, int dim, const uint8_t* __restrict__ codes,
                                 int m, int k, double* __restrict__ sums, int* __restrict__ counts) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -135,9 +193,27 @@ psb_status launch_pq_encode(const float* d_data, long long n, int dim, const flo
                             uint8_t* d_codes, cudaStream_t s) {
     if (n <= 0) return PSB_OK;
     const int dsub = dim / m;
+    const unsigned grid = (unsigned)((n + kEncThreads - 1) / kEncThreads);
+    const size_t tile = (size_t)kEncThreads * (dim + 1) * sizeof(float) + (size_t)k * dsub * sizeof(float) + (size_t)kEncThreads * m;
+    if (tile <= 200 * 1024) {  // rows staged in shared memory
+        auto run = [&](auto kernel) -> psb_status {
+            PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile));
+            kernel<<<grid, kEncThreads, tile, s>>>(d_data, n, dim, d_codebook, m, k, d_codes);
+            return PSB_OK;
+        };
+        switch (dsub) {
+            case 2: PSB_TRY(run(k_pq_encode_tile<2>)); break;
+            case 4: PSB_TRY(run(k_pq_encode_tile<4>)); break;
+            case 8: PSB_TRY(run(k_pq_encode_tile<8>)); break;
+            default: PSB_TRY(run(k_pq_encode_tile<0>)); break;
+        }
+        count_launch();
+        PSB_LAUNCH_CHECK();
+        return PSB_OK;
+    }
     const size_t smem = (size_t)k * dsub * sizeof(float) + (size_t)kEncThreads * m;
     if (smem > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(k_pq_encode, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_pq_encode<<<(unsigned)((n + kEncThreads - 1) / kEncThreads), kEncThreads, smem, s>>>(d_data, n, dim, d_codebook, m, k, d_codes);
+    k_pq_encode<<<grid, kEncThreads, smem, s>>>(d_data, n, dim, d_codebook, m, k, d_codes);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
