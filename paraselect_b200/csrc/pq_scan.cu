@@ -631,6 +631,79 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
 constexpr int kHalfGroup = 8;
 constexpr int kQueuePerWarp = 64;
 
+// Power-of-two scale of a half table: the largest s with u * s <= 30000, u = sum over m of the table's row maxima.
+__device__ __forceinline__ float half_table_scale(float u) {
+    int ex = 0;
+    if (u > 0.0f && u < 3.0e38f) ex = (int)floorf(log2f(30000.0f / u));
+    ex = ex < -40 ? -40 : (ex > 40 ? 40 : ex);
+    float sc = exp2f((float)ex);
+    while (u * sc > 30000.0f) sc *= 0.5f;  // guard against log2f rounding
+    return sc;
+}
+
+// Residual mode: the fp32 table of a (query, probe) pair and its fp16 copy in one kernel (k_build_lut_residual followed by
+// k_lut_to_half, without reading the fp32 table back).  One CTA of K threads per pair; thread c computes codeword c's
+// entry for every sub-quantiser and keeps the M entries in registers between the row-maximum reduction (which fixes the
+// scale) and the conversion.  Needs codebook_size <= 256 and a templated M.
+template <int M>
+__global__ void __launch_bounds__(256, 3)
+k_build_tables_residual(const float* __restrict__ queries, int dim, const int* __restrict__ probes, int nprobe,
+                        const float* __restrict__ centroids, int nlist, const float* __restrict__ codebook, int k,
+                        float* __restrict__ lut, __half* __restrict__ lut_h, float* __restrict__ scale_out) {
+    extern __shared__ float s_q[];  // [dim] residual
+    __shared__ float s_wmax[8][M];
+    __shared__ float s_scale;
+    const long long pair = blockIdx.x;
+    const int q = (int)(pair / nprobe);
+    const int l = probes[pair];
+    if (l < 0 || l >= nlist) return;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        s_q[i] = __fsub_rn(queries[(size_t)q * dim + i], __ldg(centroids + (size_t)l * dim + i));
+    __syncthreads();
+    const int dsub = dim / M;
+    const int c = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float ent[M];
+#pragma unroll
+    for (int j = 0; j < M; ++j) {
+        float e = 0.0f;
+        if (c < k) {
+            const float* cb = codebook + ((size_t)j * k + c) * dsub;
+            for (int d = 0; d < dsub; ++d) {
+                const float diff = __fsub_rn(s_q[j * dsub + d], __ldg(cb + d));
+                e = __fadd_rn(e, __fmul_rn(diff, diff));
+            }
+        }
+        ent[j] = e;
+        float mx = e;  // entries are >= 0; idle threads contribute 0
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) s_wmax[warp][j] = mx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float u = 0.0f;
+        for (int j = 0; j < M; ++j) {
+            float mx = s_wmax[0][j];
+            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, s_wmax[w][j]);
+            u += mx;
+        }
+        const float sc = half_table_scale(u);
+        s_scale = sc;
+        scale_out[pair] = sc;
+    }
+    __syncthreads();
+    const float sc = s_scale;
+    if (c < k) {
+        float* out = lut + (size_t)pair * M * k;
+        __half* out_h = lut_h + (size_t)pair * M * k;
+#pragma unroll
+        for (int j = 0; j < M; ++j) {
+            out[(size_t)j * k + c] = ent[j];
+            out_h[(size_t)j * k + c] = __float2half_rd(ent[j] * sc);
+        }
+    }
+}
+
 // Per query: scale s (power of two) with sum_m max_c lut[m][c] * s <= 30000, and the fp16 table RD_half(lut * s).
 __global__ void k_lut_to_half(const float* __restrict__ lut, int m, int k, __half* __restrict__ lut_h,
                               float* __restrict__ scale_out) {
@@ -648,11 +721,7 @@ __global__ void k_lut_to_half(const float* __restrict__ lut, int m, int k, __hal
     if (threadIdx.x == 0) {
         float u = 0.0f;
         for (int i = 0; i < m; ++i) u += __uint_as_float(s_max[i]);
-        int ex = 0;
-        if (u > 0.0f && u < 3.0e38f) ex = (int)floorf(log2f(30000.0f / u));
-        ex = ex < -40 ? -40 : (ex > 40 ? 40 : ex);
-        float sc = exp2f((float)ex);
-        while (u * sc > 30000.0f) sc *= 0.5f;  // guard against log2f rounding
+        const float sc = half_table_scale(u);
         s_scale = sc;
         scale_out[q] = sc;
     }
@@ -991,6 +1060,35 @@ psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, co
     return PSB_OK;
 }
 
+template <int M>
+psb_status run_build_tables_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
+                                     const float* d_centroids, int nlist, const float* d_codebook, int k, float* d_lut,
+                                     void* d_lut_h, float* d_scale, cudaStream_t s) {
+    if constexpr (M <= 0) {
+        return fail(PSB_INTERNAL, "fused residual tables need a templated M");
+    } else {
+        k_build_tables_residual<M><<<(unsigned)((long long)nq * nprobe), 256, (size_t)dim * sizeof(float), s>>>(
+            d_queries, dim, d_probes, nprobe, d_centroids, nlist, d_codebook, k, d_lut, static_cast<__half*>(d_lut_h), d_scale);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+        return PSB_OK;
+    }
+}
+
+bool residual_tables_fused(const ScanWorkspace& ws, int m, int k) {
+    return ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(m, k) && k <= 256;
+}
+
+psb_status launch_build_tables_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
+                                        const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
+                                        float* d_lut, const ScanWorkspace& ws, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    if ((long long)nq * nprobe > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
+    PSB_DISPATCH_M(m, PSB_TRY((run_build_tables_residual<MM>(d_queries, nq, dim, d_probes, nprobe, d_centroids, nlist, d_codebook,
+                                                             k, d_lut, ws.lut_h, ws.lut_scale, s))));
+    return PSB_OK;
+}
+
 psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
                        int* d_count, int sm_count, cudaStream_t s) {
@@ -1029,7 +1127,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
     a.reserve_ctas = ws.reserve_ctas;
-    if (use_half) {
+    if (use_half && !ws.half_tables_ready) {
         k_lut_to_half<<<(unsigned)tables, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
         count_launch();
         PSB_LAUNCH_CHECK();

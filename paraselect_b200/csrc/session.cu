@@ -808,13 +808,21 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         float* dist_out = rerank ? s->cand_dist.as<float>() + (size_t)p0 * stage1_k : d_dist + (size_t)p0 * topk;
         int* cnt_out = s->cand_count.as<int>() + p0;
         if (times) rc = tm_s.mark(st);
-        if (rc == PSB_OK)
-            rc = residual ? launch_build_lut_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
-                                                      s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st)
-                          : launch_build_lut(q, m, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st);
-        if (rc == PSB_OK && times) rc = tm_s.mark(st);
         ScanWorkspace sws;
         if (rc == PSB_OK) rc = s->timed_scan_ws(&sws);
+        if (rc == PSB_OK) {
+            if (residual && residual_tables_fused(sws, s->m, s->k)) {  // fp32 and fp16 tables in one kernel
+                rc = launch_build_tables_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
+                                                  s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), sws, st);
+                sws.half_tables_ready = true;
+            } else if (residual) {
+                rc = launch_build_lut_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
+                                               s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st);
+            } else {
+                rc = launch_build_lut(q, m, s->dim, s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), st);
+            }
+        }
+        if (rc == PSB_OK && times) rc = tm_s.mark(st);
         if (rc == PSB_OK) rc = launch_scan(s->scan_index(), sws, s->lut.as<float>(), m, probes, nprobe, stage1_k, rows_out,
                                            dist_out, cnt_out, s->sm_count, st);
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
