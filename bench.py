@@ -41,6 +41,11 @@ WORKLOADS = {
     # BASELINE configuration "IVF-PQ fp32 1M"
     "c2": dict(n=1_000_000, dim=128, nlist=1024, M=32, sigma=0.25, zipf=None, nq=10000, nprobe=32, topk=10,
                n_rerank=100, seed=1, desc="IVF-PQ 1Mx128 nlist=1024 M=32 nprobe=32 k=10 rerank=100 batch=10000"),
+    # BASELINE configuration "index training" (secondary line: k-means assignment on the tensor-core filter, PQ on residuals)
+    "c5": dict(n=10_000_000, dim=128, nlist=65536, components=4096, M=32, sigma=0.3, zipf=None, nq=0, nprobe=1, topk=1, n_rerank=0,
+               seed=4, iters=20, pq_iters=25,
+               desc="training: 10M x 128 rows (4,096-component mixture, sigma 0.3) -> k-means to 65,536 centroids (20 Lloyd iterations), "
+                    "PQ M=32 x 8 bit on residuals (25 iterations), encode"),
     # BASELINE configuration "coarse stage only" (secondary line: tensor-core roofline of the fused coarse GEMM)
     "c3": dict(n=65536, dim=96, nlist=65536, M=8, sigma=0.0, zipf=None, nq=100000, nprobe=64, topk=64, n_rerank=0, seed=2,
                desc="coarse only: 100,000 queries x 65,536 centroids, d=96, unit-mean-norm N(0,1), top-64"),
@@ -288,12 +293,16 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's banner and warnings go to stderr: stdout is one JSON line
         dist.init_process_group("nccl")
+    if args.impl == "ours" and world > 1 and args.workload in ("c3", "c5"):
+        raise SystemExit("workloads c3 and c5 are single-GPU lines")
     if args.impl == "ours" and world > 1:
         from paraselect_b200 import multi
         return multi.bench_main(args, cfg, rank, world, local_rank)
 
     if args.workload == "c3":
         return coarse_only(args, cfg, torch, api, device)
+    if args.workload == "c5":
+        return training(args, cfg, torch, api, device)
 
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -435,6 +444,128 @@ def main():
     return 0
 
 
+def training(args, cfg, torch, api, device):
+    """Secondary workload: index training.  A step = one Lloyd iteration (assignment of every row to its nearest of k
+    centroids + centroid update); then PQ codebook training on the residuals and encoding of all rows, each timed once."""
+    import oracle
+    n, dim, k, comps, M = cfg["n"], cfg["dim"], cfg["nlist"], cfg["components"], cfg["M"]
+    steps, warm = args.steps, max(args.warmup, 1)
+    if args.impl == "reference":
+        # the reference's assignment arithmetic (restated: the reference's k-means needs its CUDA build) on the host cores,
+        # a bounded sample of rows per step against all k centroids
+        rng = np.random.default_rng(cfg["seed"])
+        ns = args.cpu_sample or 4096
+        cen_h = rng.standard_normal((k, dim)).astype(np.float32)
+        times = []
+        for i in range(args.warmup + steps):
+            rows = rng.standard_normal((ns, dim)).astype(np.float32)
+            t0 = time.time()
+            oracle.kmeans_assign(rows, cen_h)
+            if i >= args.warmup:
+                times.append(time.time() - t0)
+        v = round(ns / float(np.mean(times)), 1)
+        cores = os.cpu_count() or 1
+        emit(dict(impl="reference", metric="k-means rows/s per Lloyd iteration (k = %d)" % k, value=v, unit="rows/s",
+                  n_gpus=args.gpus, steps=steps, warmup=args.warmup, ms_per_step=round(1e3 * float(np.mean(times)), 3),
+                  higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+                  config=dict(workload="c5", desc=cfg["desc"]),
+                  cpu_baseline=dict(value=v, unit="rows/s", cores=cores, kind="port",
+                                    sample="assignment of %d rows per step against all %d centroids, all %d host threads" % (ns, k, cores)),
+                  e2e=dict(value=v, unit="rows/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0)))
+        return 0
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        st = stream.cuda_stream
+        _, offsets = populations(n, comps, None)
+        d_off = torch.from_numpy(offsets).cuda()
+        centres = torch.empty((comps, dim), dtype=torch.float32, device="cuda")
+        api.gen_normal(cfg["seed"] * 1000 + 1, 0, comps * dim, 1.0, centres, device=device, stream=st)
+        x = torch.empty((n, dim), dtype=torch.float32, device="cuda")
+        api.gen_mixture_rows(centres, d_off, comps, dim, cfg["sigma"], cfg["seed"] * 1000 + 2, 0, n, x, device=device, stream=st)
+        g = torch.Generator(device="cuda"); g.manual_seed(cfg["seed"])
+        init = x[torch.randperm(n, device="cuda", generator=g)[:k]].clone()  # seeded sampling without replacement
+        assign = torch.empty((n,), dtype=torch.int32, device="cuda")
+        cen = init.clone()
+        api.kmeans_train(x, n, dim, cen, k, warm - 1, assign, device=device, stream=st)  # warm-up passes
+        torch.cuda.synchronize()
+        sampler = ClockSampler(device)
+        sampler.start()
+        cen.copy_(init)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        obj = api.kmeans_train(x, n, dim, cen, k, steps - 1, assign, device=device, stream=st)  # `steps` assignment passes
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        clocks = sampler.stop()
+        # end to end: host rows in, host centroids + assignment out
+        xh = torch.empty((n, dim), dtype=torch.float32).pin_memory()
+        xh.copy_(x)
+        ch = torch.empty((k, dim), dtype=torch.float32).pin_memory()
+        ah = torch.empty((n,), dtype=torch.int32).pin_memory()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        x.copy_(xh, non_blocking=True)
+        cen.copy_(init)
+        api.kmeans_train(x, n, dim, cen, k, steps - 1, assign, device=device, stream=st)
+        ch.copy_(cen, non_blocking=True); ah.copy_(assign, non_blocking=True)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / steps
+        # PQ on the residuals x - centroid[assign], then encoding
+        t0 = time.time()
+        x -= cen[assign.long()]
+        codebook = torch.empty((M, 256, dim // M), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        t1 = time.time()
+        api.pq_train(x, n, dim, M, 256, cfg["pq_iters"], cfg["seed"] * 1000 + 3, codebook, device=device, stream=st)
+        torch.cuda.synchronize()
+        t2 = time.time()
+        codes = torch.empty((n, M), dtype=torch.uint8, device="cuda")
+        api.pq_encode(x, n, dim, codebook, M, 256, codes, device=device, stream=st)
+        torch.cuda.synchronize()
+        t3 = time.time()
+        # CPU baseline + parity: one assignment pass of the reference arithmetic on a bounded sample of rows
+        ns = args.cpu_sample or 4096
+        rows = (x[:ns] + cen[assign[:ns].long()]).cpu().numpy()  # the sample's original rows
+        cen_h = cen.cpu().numpy()
+        c0 = time.time()
+        oa, od = oracle.kmeans_assign(rows, cen_h)
+        cdt = time.time() - c0
+        x[:ns] += cen[assign[:ns].long()]
+        chk = torch.empty((ns,), dtype=torch.int32, device="cuda")
+        api.kmeans_train(x[:ns].contiguous(), ns, dim, cen.clone(), k, 0, chk, device=device, stream=st)
+        torch.cuda.synchronize()
+        assign_equal = bool(np.array_equal(chk.cpu().numpy(), oa))
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1590.0)))
+    flops = 2.0 * n * k * dim
+    cores = os.cpu_count() or 1
+    line = dict(metric="k-means rows/s per Lloyd iteration (k = %d)" % k, value=round(n / (ms * 1e-3), 1), unit="rows/s", n_gpus=1,
+                steps=steps, warmup=warm, ms_per_step=round(ms, 3), higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="bf16 filter + f32 exact", data="synthetic",
+                config=dict(workload="c5", desc=cfg["desc"], l2="rows 5.1 GB, far above L2"),
+                e2e=dict(value=round(n / (ms_e2e * 1e-3), 1), unit="rows/s", ms_per_step=round(ms_e2e, 3),
+                         h2d_bytes_per_step=int(n * dim * 4 / steps), d2h_bytes_per_step=int((k * dim * 4 + n * 4) / steps)),
+                gpu_launches=steps * (-(-n // 262144) * 6 + 4),  # per pass: row prep, two filter passes, threshold, refinement, fallback per chunk; accumulate, update
+                roofline=dict(bound="tensor", kernel="k_coarse_tc (assignment: two filter passes + exact refinement)",
+                              achieved=round(flops / (ms * 1e-3) / 1e12, 1), peak=peak, unit="TFLOP/s",
+                              frac=round(flops / (ms * 1e-3) / 1e12 / peak, 4), peak_source="measured (sustained)" if peaks else "fallback",
+                              algorithmic_flops_per_step=flops, traffic=None,
+                              note="whole Lloyd iteration (both GEMM passes, refinement, update) against one algorithmic 2nkd"),
+                cpu_baseline=dict(value=round(ns / cdt, 1), unit="rows/s", cores=cores, kind="port",
+                                  sample="one assignment pass of %d rows against all %d centroids" % (ns, k)),
+                objective=[float(v) for v in obj], pq_train_s=round(t2 - t1, 3), pq_encode_s=round(t3 - t2, 3),
+                residual_s=round(t1 - t0, 3), total_training_estimate_s=round(ms * 1e-3 * (cfg["iters"] + 1) + (t3 - t0), 2),
+                parity=dict(sample_rows=ns, assign_equal=assign_equal), clocks=clocks)
+    emit(line)
+    return 0
+
+
 def coarse_only(args, cfg, torch, api, device):
     """Secondary workload: the coarse stage alone (queries x centroids squared L2 with per-query top-64)."""
     import oracle
@@ -445,6 +576,7 @@ def coarse_only(args, cfg, torch, api, device):
         q = torch.empty((nq, dim), dtype=torch.float32, device="cuda")
         api.gen_normal(cfg["seed"] * 1000 + 1, 0, nlist * dim, 1.0, c, device=device)
         api.gen_normal(cfg["seed"] * 1000 + 2, 0, nq * dim, 1.0, q, device=device)
+        torch.cuda.synchronize()  # the generators run on the default stream, torch on its own
         c /= c.norm(dim=1).mean()
         q /= q.norm(dim=1).mean()
         torch.cuda.synchronize()
