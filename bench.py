@@ -264,6 +264,9 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the base size (scaled-down runs)")
     ap.add_argument("--queries", type=int, default=0, help="override the batch size")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU baseline sample (0 = auto)")
+    ap.add_argument("--exact-mode", default="staged", choices=["mapped", "staged"],
+                    help="rerank transport on one GPU: host threads gather rows into pinned rings and cudaMemcpyAsync moves them "
+                         "(default; no SM time spent on the transfer), or kernels gather mapped host rows over PCIe")
     args = ap.parse_args()
     claim_stdout()
 
@@ -325,7 +328,8 @@ def main():
 
         t0 = time.time()
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           residual=bool(cfg.get("residual")))
+                           residual=bool(cfg.get("residual")),
+                           exact_mode=api.EXACT_HOST_STAGED if args.exact_mode == "staged" else api.EXACT_HOST_MAPPED)
         log("session created in %.1fs" % (time.time() - t0))
         stage1 = min(R, cfg["n"]) if R > topk else topk
         d_probes = torch.empty((nq, nprobe), dtype=torch.int32, device="cuda")
@@ -422,7 +426,7 @@ def main():
         unit="queries/s", n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
         higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
         config=dict(workload=args.workload, desc=cfg["desc"], rows=cfg["n"], dim=dim, nlist=cfg["nlist"], M=cfg["M"],
-                    batch=nq, nprobe=nprobe, topk=topk, n_rerank=R, exact_rows="host-mapped fp32",
+                    batch=nq, nprobe=nprobe, topk=topk, n_rerank=R, exact_rows="host-%s fp32" % args.exact_mode,
                     l2="inputs larger than L2 (codes %.1f GB)" % (index["codes"].nbytes / 1e9)),
         e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
                  h2d_bytes_per_step=int(stats["h2d_bytes"]), d2h_bytes_per_step=int(stats["d2h_bytes"]),

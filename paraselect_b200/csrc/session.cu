@@ -10,6 +10,10 @@
 #include <cstring>
 #include <memory>
 #include <new>
+#include <condition_variable>
+#include <deque>
+#include <mutex>
+#include <string>
 #include <thread>
 #include <vector>
 
@@ -192,6 +196,8 @@ struct psb_session {
     size_t pinned_bytes = 0;
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
     std::vector<int> h_cand;
+    int* h_cand_pinned = nullptr;        // candidates of the whole batch on the host (overlapped staged transport)
+    size_t h_cand_pinned_count = 0;
     std::vector<long long> h_global_begin, h_offsets;  // striped shards: host copies for the staged transport
     // workspaces
     DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
@@ -290,7 +296,8 @@ size_t table_count(const psb_session* s, int nq, int nprobe) {
 // Queries per sub-batch of the pipeline: a quarter of the batch when the rerank overlaps the scan, and in residual mode
 // few enough that the per-(query, probe) tables stay below ~16 GiB.
 int sub_batch_rows(const psb_session* s, int n, int nprobe, bool overlap) {
-    int parts = overlap ? 4 : 1;
+    static const int pipeline_parts = [] { const char* e = std::getenv("PSB_PIPELINE_PARTS"); const int v = e ? std::atoi(e) : 0; return v >= 2 && v <= 32 ? v : 4; }();  // tuning knob, read once
+    int parts = overlap ? pipeline_parts : 1;
     if (s->opt.adc_mode == 1) {
         const double bytes = (double)n * nprobe * s->m * s->k * sizeof(float);
         parts = std::max(parts, (int)std::ceil(bytes / (16.0 * 1024 * 1024 * 1024)));
@@ -434,12 +441,9 @@ long long host_local_row(const psb_session* s, long long r) {
 
 // Staged rerank transport: candidate rows come back to the host, host threads gather the exact rows into two
 // pinned buffers, and cudaMemcpyAsync moves each filled buffer while the other is being filled.
-psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, int stride, const int* d_counts) {
-    (void)d_counts;
+// h_cand: the candidates on the host; d_stage: destination [nq][width][row bytes]; copies are queued on `stream`.
+psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int width, int stride, void* d_stage, cudaStream_t stream) {
     const size_t row_bytes = (size_t)s->dim * s->exact_elem;
-    s->h_cand.resize((size_t)nq * stride);
-    PSB_CUDA(cudaMemcpyAsync(s->h_cand.data(), d_cand, sizeof(int) * (size_t)nq * stride, cudaMemcpyDeviceToHost, s->stream));
-    PSB_CUDA(cudaStreamSynchronize(s->stream));
     const size_t chunk_q = std::max<size_t>(1, ((size_t)64 << 20) / std::max<size_t>(1, row_bytes * width));
     const size_t need = chunk_q * width * row_bytes;
     if (s->pinned_bytes < need) {
@@ -467,17 +471,25 @@ psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, i
                 const size_t b = total * t / nthreads, e = total * (t + 1) / nthreads;
                 for (size_t i = b; i < e; ++i) {
                     const size_t q = q0 + i / width, c = i % width;
-                    const long long row = host_local_row(s, s->h_cand[q * stride + c]);
+                    const long long row = host_local_row(s, h_cand[q * stride + c]);
                     if (row >= 0 && row < s->exact_count) std::memcpy(dst + i * row_bytes, src + (size_t)row * row_bytes, row_bytes);
                 }
             });
         for (auto& th : pool) th.join();
-        PSB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(s->stage.p) + q0 * width * row_bytes, dst, total * row_bytes,
-                                 cudaMemcpyHostToDevice, s->stream));
-        PSB_CUDA(cudaEventRecord(s->pinned_ev[slot], s->stream));
+        PSB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(d_stage) + q0 * width * row_bytes, dst, total * row_bytes,
+                                 cudaMemcpyHostToDevice, stream));
+        PSB_CUDA(cudaEventRecord(s->pinned_ev[slot], stream));
         used[slot] = true;
     }
     return PSB_OK;
+}
+
+psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, int stride, const int* d_counts) {
+    (void)d_counts;
+    s->h_cand.resize((size_t)nq * stride);
+    PSB_CUDA(cudaMemcpyAsync(s->h_cand.data(), d_cand, sizeof(int) * (size_t)nq * stride, cudaMemcpyDeviceToHost, s->stream));
+    PSB_CUDA(cudaStreamSynchronize(s->stream));
+    return staged_gather_host(s, s->h_cand.data(), nq, width, stride, s->stage.p, s->stream);
 }
 
 psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int* d_cand, int width, int stride,
@@ -631,6 +643,7 @@ psb_status psb_session_destroy(psb_session* s) {
         if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
         if (s->pinned_ev[i]) cudaEventDestroy(s->pinned_ev[i]);
     }
+    if (s->h_cand_pinned) cudaFreeHost(s->h_cand_pinned);
     if (s->aux_stream) { cudaStreamSynchronize(s->aux_stream); cudaStreamDestroy(s->aux_stream); }
     if (s->own_stream) cudaStreamDestroy(s->stream);
     delete s;
@@ -770,18 +783,22 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
                          bool rerank, long long* d_ids, float* d_dist, int* d_probes, StageTimes* times) {
     cudaStream_t st = s->stream;
     const bool overlap = overlap_enabled(s, n, rerank);
-    const int sb = sub_batch_rows(s, n, nprobe, overlap);
+    // Staged transport, overlapped: a host worker thread takes each sub-batch's candidates as soon as its scan has finished,
+    // gathers the rows with the host cores into the pinned rings and queues copies + exact scoring on the second stream,
+    // while this thread goes on queueing the next sub-batch's scan.  No SM is spent on the transfer.
+    const bool staged_overlap = rerank && s->opt.exact_mode == PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
+    const int sb = sub_batch_rows(s, n, nprobe, overlap || staged_overlap);
     const bool residual = s->opt.adc_mode == 1;
-    if (overlap && !s->aux_stream) {
+    if ((overlap || staged_overlap) && !s->aux_stream) {
         int lo = 0, hi = 0;  // lowest priority: the scan's CTAs get the SMs first, the transfer fills the gaps
         PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         PSB_CUDA(cudaStreamCreateWithPriority(&s->aux_stream, cudaStreamNonBlocking, lo));
     }
-    cudaStream_t sx = overlap ? s->aux_stream : st;
+    cudaStream_t sx = (overlap || staged_overlap) ? s->aux_stream : st;
     std::vector<cudaEvent_t> deps;
     EventTimer tm_s, tm_x;
     auto cleanup = [&]() { for (auto e : deps) cudaEventDestroy(e); };
-    if (overlap) {  // the second stream starts after everything already queued on the main stream
+    if (overlap || staged_overlap) {  // the second stream starts after everything already queued on the main stream
         cudaEvent_t e0;
         PSB_CUDA(cudaEventCreateWithFlags(&e0, cudaEventDisableTiming));
         deps.push_back(e0);
@@ -789,6 +806,64 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         PSB_CUDA(cudaStreamWaitEvent(sx, e0, 0));
     }
     psb_status rc = PSB_OK;
+    struct Job { int p0, m; cudaEvent_t ready; };
+    std::mutex mu;
+    std::condition_variable cv;
+    std::deque<Job> jobs;
+    bool done = false;
+    psb_status worker_rc = PSB_OK;
+    std::string worker_msg;
+    std::thread worker;
+    if (staged_overlap) {
+        const size_t cand_count = (size_t)n * stage1_k;
+        if (s->h_cand_pinned_count < cand_count) {
+            if (s->h_cand_pinned) cudaFreeHost(s->h_cand_pinned);
+            s->h_cand_pinned = nullptr; s->h_cand_pinned_count = 0;
+            PSB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&s->h_cand_pinned), sizeof(int) * cand_count, cudaHostAllocDefault));
+            s->h_cand_pinned_count = cand_count;
+        }
+        PSB_TRY(s->stage.reserve((size_t)sb * stage1_k * s->dim * s->exact_elem));
+        PSB_TRY(s->score.reserve(sizeof(float) * (size_t)sb * stage1_k));
+        worker = std::thread([&]() {
+            cudaSetDevice(s->device);
+            auto process = [&](const Job& j) -> psb_status {
+                PSB_CUDA(cudaEventSynchronize(j.ready));
+                const int* cand_d = s->cand_rows.as<int>() + (size_t)j.p0 * stage1_k;
+                const int* cnt_d = s->cand_count.as<int>() + j.p0;
+                if (times) PSB_TRY(tm_x.mark(sx));
+                PSB_TRY(staged_gather_host(s, s->h_cand_pinned + (size_t)j.p0 * stage1_k, j.m, stage1_k, stage1_k, s->stage.p, sx));
+                const unsigned char* qe = static_cast<const unsigned char*>(dq_exact) + (size_t)j.p0 * s->dim * s->exact_elem;
+                PSB_TRY(launch_rerank_score(s->stage.p, s->row_map(), s->dim, s->exact_elem, qe, cand_d, j.m, stage1_k, stage1_k,
+                                            cnt_d, s->score.as<float>(), sx));
+                PSB_TRY(launch_topk_select(s->score.as<float>(), cand_d, j.m, stage1_k, stage1_k, cnt_d, topk,
+                                           s->out_rows.as<int>() + (size_t)j.p0 * topk, d_dist + (size_t)j.p0 * topk, sx));
+                if (times) PSB_TRY(tm_x.mark(sx));
+                PSB_TRY(launch_map_ids(s->out_rows.as<int>() + (size_t)j.p0 * topk, (long long)j.m * topk,
+                                       s->reordered.as<long long>(), s->row_map(), d_ids + (size_t)j.p0 * topk, sx));
+                if (times) PSB_TRY(tm_x.mark(sx));
+                return PSB_OK;
+            };
+            for (;;) {
+                Job j;
+                {
+                    std::unique_lock<std::mutex> lk(mu);
+                    cv.wait(lk, [&] { return !jobs.empty() || done; });
+                    if (jobs.empty()) return;
+                    j = jobs.front();
+                    jobs.pop_front();
+                }
+                if (worker_rc != PSB_OK) continue;  // drain
+                const psb_status r = process(j);
+                if (r != PSB_OK) { worker_rc = r; worker_msg = psb_last_error(); }
+            }
+        });
+    }
+    auto finish_worker = [&]() {
+        if (!worker.joinable()) return;
+        { std::lock_guard<std::mutex> lk(mu); done = true; }
+        cv.notify_all();
+        worker.join();
+    };
     // Coarse stage for the whole batch first: one large GEMM is more efficient than four small ones, and the tensor-core
     // kernel (a full SM's shared and tensor memory per CTA) then never has to share SMs with the transfer stream.
     if (times) rc = tm_s.mark(st);
@@ -827,6 +902,16 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
                                            dist_out, cnt_out, s->sm_count, st);
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
         if (rc != PSB_OK) break;
+        if (staged_overlap) {  // hand the sub-batch to the worker: candidates to the host, an event marks them ready
+            cudaEvent_t e;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { rc = fail(PSB_CUDA_ERROR, "event creation failed"); break; }
+            deps.push_back(e);
+            cudaMemcpyAsync(s->h_cand_pinned + (size_t)p0 * stage1_k, rows_out, sizeof(int) * (size_t)m * stage1_k, cudaMemcpyDeviceToHost, st);
+            cudaEventRecord(e, st);
+            { std::lock_guard<std::mutex> lk(mu); jobs.push_back(Job{p0, m, e}); }
+            cv.notify_all();
+            continue;
+        }
         if (overlap) {
             cudaEvent_t e;
             if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { rc = fail(PSB_CUDA_ERROR, "event creation failed"); break; }
@@ -850,7 +935,9 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         if (rc == PSB_OK && times) rc = tm_x.mark(sx);
         s->stream = keep;
     }
-    if (overlap) {  // the main stream continues only after the second stream has finished this batch
+    finish_worker();
+    if (worker_rc != PSB_OK && rc == PSB_OK) rc = fail(worker_rc, "rerank worker: " + worker_msg);
+    if (overlap || staged_overlap) {  // the main stream continues only after the second stream has finished this batch
         cudaEvent_t e;
         if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess) {
             deps.push_back(e);

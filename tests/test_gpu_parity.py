@@ -426,3 +426,20 @@ def test_sharded_step_with_second_stream_equals_search(psb):
                 torch.cuda.synchronize()
                 assert np.array_equal(ids.cpu().numpy(), want["indices"])
                 assert np.array_equal(dd.cpu().numpy(), want["distances"])
+
+
+def test_staged_transport_overlapped_by_a_host_worker_equals_mapped(psb):
+    """Host-staged rerank transport: batches of >= 2048 queries hand each sub-batch's candidates to a host worker thread that
+    gathers rows into pinned rings while the next sub-batch scans; results must equal the mapped transport's."""
+    ix = synth.make_index(60000, 64, 64, 16, seed=81, zipf=True)
+    q = synth.make_queries(ix, 2600, seed=82, weights=synth.zipf_weights(64))
+    res = {}
+    for name, kw in (("mapped", dict()), ("staged", dict(exact_mode=psb.EXACT_HOST_STAGED)),
+                     ("staged_serial", dict(exact_mode=psb.EXACT_HOST_STAGED, serial_pipeline=True))):
+        with psb.Session(ix, n_rerank=120, **kw) as s:
+            res[name] = s.search(q, 8, 10, batch_size=2600)
+            again = s.search(q, 8, 10, batch_size=2600)  # buffers are reused across batches
+            assert np.array_equal(again["indices"], res[name]["indices"])
+    for name in ("staged", "staged_serial"):
+        assert np.array_equal(res[name]["indices"], res["mapped"]["indices"])
+        assert np.array_equal(res[name]["distances"], res["mapped"]["distances"])
