@@ -264,9 +264,10 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the base size (scaled-down runs)")
     ap.add_argument("--queries", type=int, default=0, help="override the batch size")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU baseline sample (0 = auto)")
-    ap.add_argument("--exact-mode", default="staged", choices=["mapped", "staged"],
-                    help="rerank transport on one GPU: host threads gather rows into pinned rings and cudaMemcpyAsync moves them "
-                         "(default; no SM time spent on the transfer), or kernels gather mapped host rows over PCIe")
+    ap.add_argument("--exact-mode", default="auto", choices=["auto", "mapped", "staged"],
+                    help="rerank transport on one GPU: staged = host threads gather rows into pinned rings and cudaMemcpyAsync moves "
+                         "them (no SM time spent on the transfer), mapped = kernels gather mapped host rows over PCIe; auto = staged "
+                         "when a batch gathers at least 2 GB (the scan is then long enough to hide the host gather), else mapped")
     args = ap.parse_args()
     claim_stdout()
 
@@ -288,6 +289,9 @@ def main():
         cfg["nprobe"] = min(cfg["nprobe"], cfg["nlist"])
     if args.queries:
         cfg["nq"] = args.queries
+    if args.exact_mode == "auto":
+        gathered = cfg["nq"] * max(cfg["n_rerank"], cfg["topk"]) * cfg["dim"] * 4
+        args.exact_mode = "staged" if gathered >= 2e9 else "mapped"
     if not torch.cuda.is_available() or api.device_count() < 1:
         raise SystemExit("bench.py needs a B200: the library has no CPU path")
     torch.cuda.set_device(local_rank)

@@ -337,6 +337,20 @@ psb_status psb_knn_exact(const float* d_queries, int nq, const float* d_base, in
 psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_centroids, int k, int iters,
                             int* d_assign, double* h_objective, int device, void* stream);
 
+/* One Lloyd iteration in three calls, for data-parallel training over several GPUs: every rank assigns and accumulates
+ * its own rows, the caller all-reduces d_sums / d_counts / d_objective (NCCL), and every rank applies the same update.
+ * Replaces the per-GPU accumulation and host reduction of the reference's multi-GPU trainers
+ * (src/clustering/kmeans/kmeans_multigpu_train.cu:49-139, src/quantization/pq/residual_pq_multigpu_trainer.cu:336-411).
+ *   assign:     d_assign [n] int32, d_best [n] fp32 (exact squared distance to the assigned centroid)
+ *   accumulate: d_sums [k][dim] fp64, d_counts [k] int32, d_objective [1] fp64 - zeroed, then this rank's contribution
+ *   update:     centroid = sums / counts rounded once to fp32; an empty cluster keeps its centroid */
+psb_status psb_kmeans_assign(const float* d_data, int64_t n, int dim, const float* d_centroids, int k, int* d_assign,
+                             float* d_best, int device, void* stream);
+psb_status psb_kmeans_accumulate(const float* d_data, int64_t n, int dim, const int* d_assign, const float* d_best, int k,
+                                 double* d_sums, int* d_counts, double* d_objective, int device, void* stream);
+psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids, int device,
+                             void* stream);
+
 /* PQ codebooks: one k-means (codebook_size codewords) per subspace, seeded sampling for the initial
  * codewords.  Replaces train_plain_pq_codebooks_gpu (src/quantization/pq/pq_trainer.cuh:9-26,
  * src/quantization/pq/pq_trainer.cu:30-95).  d_codebook [m][k][dim/m] out. */

@@ -195,6 +195,8 @@ struct psb_session {
     void* pinned[2] = {nullptr, nullptr};
     size_t pinned_bytes = 0;
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
+    bool pinned_used[2] = {false, false};  // a copy out of the ring buffer may still be in flight (its event tells)
+    int pinned_slot = 0;
     std::vector<int> h_cand;
     int* h_cand_pinned = nullptr;        // candidates of the whole batch on the host (overlapped staged transport)
     size_t h_cand_pinned_count = 0;
@@ -448,6 +450,8 @@ psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int wid
     const size_t need = chunk_q * width * row_bytes;
     if (s->pinned_bytes < need) {
         for (int i = 0; i < 2; ++i) {
+            if (s->pinned_used[i]) PSB_CUDA(cudaEventSynchronize(s->pinned_ev[i]));  // no copy may still read the old buffer
+            s->pinned_used[i] = false;
             if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
             s->pinned[i] = nullptr;
             PSB_CUDA(cudaHostAlloc(&s->pinned[i], need, cudaHostAllocDefault));
@@ -457,11 +461,11 @@ psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int wid
     }
     const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
     const int nthreads = (int)std::min<unsigned>(hc, 32);
-    int slot = 0;
-    bool used[2] = {false, false};
-    for (size_t q0 = 0; q0 < (size_t)nq; q0 += chunk_q, slot ^= 1) {
+    // The ring state outlives the call: the next call may start while this call's last copy is still in flight.
+    for (size_t q0 = 0; q0 < (size_t)nq; q0 += chunk_q, s->pinned_slot ^= 1) {
+        const int slot = s->pinned_slot;
         const size_t n = std::min(chunk_q, (size_t)nq - q0);
-        if (used[slot]) PSB_CUDA(cudaEventSynchronize(s->pinned_ev[slot]));
+        if (s->pinned_used[slot]) PSB_CUDA(cudaEventSynchronize(s->pinned_ev[slot]));
         unsigned char* dst = static_cast<unsigned char*>(s->pinned[slot]);
         const unsigned char* src = static_cast<const unsigned char*>(s->exact_host);
         const size_t total = n * width;
@@ -479,7 +483,7 @@ psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int wid
         PSB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(d_stage) + q0 * width * row_bytes, dst, total * row_bytes,
                                  cudaMemcpyHostToDevice, stream));
         PSB_CUDA(cudaEventRecord(s->pinned_ev[slot], stream));
-        used[slot] = true;
+        s->pinned_used[slot] = true;
     }
     return PSB_OK;
 }
@@ -1251,6 +1255,65 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
     PSB_CUDA(cudaStreamSynchronize(st));
     if (tc) PSB_TRY(tcw.check_status());
     return PSB_OK;
+}
+
+// ---- one Lloyd iteration in three calls (data-parallel training: the caller all-reduces sums and counts in between) ----
+
+psb_status psb_kmeans_assign(const float* d_data, int64_t n, int dim, const float* d_centroids, int k, int* d_assign,
+                             float* d_best, int device, void* stream) {
+    if (!d_data || !d_centroids || !d_assign || !d_best || n <= 0 || dim <= 0 || k <= 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid k-means assignment request");
+    cudaDeviceProp prop;
+    PSB_TRY(check_device(device, &prop));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t row_bytes = sizeof(float) * (size_t)k;
+    long long chunk = std::min<long long>((long long)std::max<size_t>(64, ((size_t)1 << 30) / row_bytes), n);
+    const long long chunk_tc = std::min<long long>(n, 262144);
+    const bool tc = coarse_tc_supported((int)chunk_tc, k, dim, 1);
+    TcIndexBuffers tci;
+    TcWorkBuffers tcw;
+    DevBuf tile;
+    if (tc) {
+        chunk = chunk_tc;
+        std::vector<float> h_centroids((size_t)k * dim);
+        PSB_CUDA(cudaMemcpyAsync(h_centroids.data(), d_centroids, sizeof(float) * (size_t)k * dim, cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaStreamSynchronize(st));
+        PSB_TRY(tci.prepare(h_centroids.data(), d_centroids, k, dim, st));
+    }
+    for (long long r0 = 0; r0 < n; r0 += chunk) {
+        const int nn = (int)std::min<long long>(chunk, n - r0);
+        if (tc && coarse_tc_supported(nn, k, dim, 1)) {
+            PSB_TRY(tcw.ensure(nn, k, dim, 1, st));
+            PSB_TRY(launch_coarse_tc(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, 1, d_assign + r0,
+                                     d_best + r0, prop.multiProcessorCount, st));
+        } else {
+            PSB_TRY(tile.reserve(row_bytes * (size_t)nn));
+            PSB_TRY(launch_coarse_dist_exact(d_data + (size_t)r0 * dim, nn, d_centroids, k, dim, tile.as<float>(), st));
+            PSB_TRY(launch_select_rows(tile.as<float>(), nn, k, 1, d_assign + r0, d_best + r0, st));
+        }
+    }
+    PSB_CUDA(cudaStreamSynchronize(st));  // the work buffers above are released on return
+    if (tc) PSB_TRY(tcw.check_status());
+    return PSB_OK;
+}
+
+psb_status psb_kmeans_accumulate(const float* d_data, int64_t n, int dim, const int* d_assign, const float* d_best, int k,
+                                 double* d_sums, int* d_counts, double* d_objective, int device, void* stream) {
+    if (!d_data || !d_assign || !d_best || !d_sums || !d_counts || !d_objective || n < 0 || dim <= 0 || k <= 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid k-means accumulation request");
+    PSB_TRY(check_device(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PSB_CUDA(cudaMemsetAsync(d_sums, 0, sizeof(double) * (size_t)k * dim, st));
+    PSB_CUDA(cudaMemsetAsync(d_counts, 0, sizeof(int) * (size_t)k, st));
+    PSB_CUDA(cudaMemsetAsync(d_objective, 0, sizeof(double), st));
+    return launch_kmeans_accumulate(d_data, n, dim, d_assign, d_best, d_sums, d_counts, d_objective, st);
+}
+
+psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids, int device,
+                             void* stream) {
+    if (!d_sums || !d_counts || !d_centroids || k <= 0 || dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid k-means update request");
+    PSB_TRY(check_device(device));
+    return launch_kmeans_update(d_sums, d_counts, k, dim, d_centroids, static_cast<cudaStream_t>(stream));
 }
 
 psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors, int codebook_size, int iters,

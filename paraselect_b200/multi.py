@@ -375,3 +375,52 @@ def build_stripe(cfg, torch, api, device, offsets, gb, loff):
     index = dict(centroids=centres.cpu().numpy(), offsets=loff, reordered_ids=ids, codes=codes,
                  codebook=codebook.cpu().numpy(), vectors=vectors, nlist=nlist)
     return index, centres
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Data-parallel k-means: rows sharded across ranks, one all-reduce of the per-centroid sums and counts per iteration
+# (the reference's multi-GPU trainers reduce on the host instead: src/clustering/kmeans/kmeans_multigpu_train.cu:49-139).
+
+class TrainEngine:
+    """The CUDA library's three-call Lloyd iteration on torch CUDA tensors (calls run on torch's current stream)."""
+
+    def __init__(self, api, torch, device=0):
+        self.api, self.torch, self.device = api, torch, device
+
+    def _st(self):
+        return self.torch.cuda.current_stream().cuda_stream
+
+    def empty(self, shape, dtype):
+        return self.torch.empty(shape, dtype=dtype, device="cuda")
+
+    def assign(self, x, n, dim, cen, k, assign, best):
+        self.api.kmeans_assign(x, n, dim, cen, k, assign, best, device=self.device, stream=self._st())
+
+    def accumulate(self, x, n, dim, assign, best, k, sums, counts, obj):
+        self.api.kmeans_accumulate(x, n, dim, assign, best, k, sums, counts, obj, device=self.device, stream=self._st())
+
+    def update(self, sums, counts, k, dim, cen):
+        self.api.kmeans_update(sums, counts, k, dim, cen, device=self.device, stream=self._st())
+
+
+def sharded_kmeans(engine, dist, world, x, n, dim, cen, k, iters, torch):
+    """Lloyd k-means over row shards.  x [n][dim]: this rank's rows; cen [k][dim]: the same initial centroids on every
+    rank, updated in place (identically on every rank).  Returns (objective per iteration [iters + 1], assignment of the
+    local rows against the final centroids)."""
+    assign = engine.empty((n,), torch.int32)
+    best = engine.empty((n,), torch.float32)
+    sums = engine.empty((k, dim), torch.float64)
+    counts = engine.empty((k,), torch.int32)
+    obj = engine.empty((1,), torch.float64)
+    history = []
+    for it in range(iters + 1):
+        engine.assign(x, n, dim, cen, k, assign, best)
+        engine.accumulate(x, n, dim, assign, best, k, sums, counts, obj)
+        if world > 1:
+            dist.all_reduce(sums)
+            dist.all_reduce(counts)
+            dist.all_reduce(obj)
+        history.append(float(obj.item()))
+        if it < iters:
+            engine.update(sums, counts, k, dim, cen)
+    return history, assign

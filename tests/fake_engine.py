@@ -98,3 +98,28 @@ def stripe_index(ix, rank, world, min_slice=64):
     local.update(offsets=loff, reordered_ids=ix["reordered_ids"][keep], codes=ix["codes"][keep],
                  vectors=None if ix.get("vectors") is None else ix["vectors"][keep])
     return local, gb
+
+
+class CpuTrainEngine:
+    """CPU stand-in for paraselect_b200.multi.TrainEngine (the three-call Lloyd iteration) built on the CPU checker."""
+
+    def empty(self, shape, dtype):
+        return torch.zeros(shape, dtype=dtype)
+
+    def assign(self, x, n, dim, cen, k, assign, best):
+        a, d = oracle.kmeans_assign(x.numpy(), cen.numpy())
+        assign.copy_(torch.from_numpy(a)); best.copy_(torch.from_numpy(d))
+
+    def accumulate(self, x, n, dim, assign, best, k, sums, counts, obj):
+        s = np.zeros((k, dim), np.float64)
+        np.add.at(s, assign.numpy(), x.numpy().astype(np.float64))
+        sums.copy_(torch.from_numpy(s))
+        counts.copy_(torch.from_numpy(np.bincount(assign.numpy(), minlength=k).astype(np.int32)))
+        obj[0] = float(best.numpy().astype(np.float64).sum())
+
+    def update(self, sums, counts, k, dim, cen):
+        c = counts.numpy()
+        new = cen.numpy().copy()
+        nz = c > 0
+        new[nz] = (sums.numpy()[nz] / c[nz, None]).astype(np.float32)
+        cen.copy_(torch.from_numpy(new))

@@ -31,6 +31,17 @@ def main():
     # the same batch cut into three sub-batches (16 = 6 + 6 + 4): each runs its own exchange
     ids3, dd3 = s.step(torch.from_numpy(q), parts=3)
     ok = ok and np.array_equal(ids3.numpy(), want["indices"]) and np.array_equal(dd3.numpy(), want["distances"])
+    # data-parallel k-means: rows split between the ranks, sums and counts all-reduced every iteration
+    from fake_engine import CpuTrainEngine
+    from paraselect_b200.multi import sharded_kmeans
+    _, data, _ = synth.mixture(4000, 16, 20, 0.3, seed=91)
+    init = data[:50].copy()
+    want_cen, want_assign, want_obj = oracle.kmeans_lloyd(data, init, 4)
+    lo, hi = 4000 * rank // world, 4000 * (rank + 1) // world
+    cen = torch.from_numpy(init.copy())
+    hist, assign = sharded_kmeans(CpuTrainEngine(), dist, world, torch.from_numpy(data[lo:hi].copy()), hi - lo, 16, cen, 50, 4, torch)
+    ok = ok and np.allclose(hist, want_obj, rtol=1e-6) and np.allclose(cen.numpy(), want_cen, rtol=1e-6, atol=1e-7)
+    ok = ok and np.array_equal(assign.numpy(), want_assign[lo:hi])
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

@@ -105,3 +105,23 @@ def test_kmeans_assignment_on_the_tensor_core_filter(psb):
     # final assignment against the final centroids, exactly
     fa, fd = oracle.kmeans_assign(data, dcen.cpu().numpy())
     assert np.array_equal(dassign.cpu().numpy(), fa)
+
+
+def test_three_call_lloyd_iteration_equals_kmeans_train(psb):
+    """psb_kmeans_assign / accumulate / update, as the data-parallel trainer calls them, against psb_kmeans_train."""
+    import torch
+    import synth
+    from paraselect_b200.multi import TrainEngine, sharded_kmeans
+    _, data, _ = synth.mixture(30000, 64, 300, 0.3, seed=26)
+    rng = np.random.default_rng(7)
+    init = data[rng.choice(30000, size=1024, replace=False)].copy()
+    x = torch.from_numpy(data).cuda()
+    cen_a = torch.from_numpy(init).cuda()
+    assign_a = torch.empty((30000,), dtype=torch.int32, device="cuda")
+    obj_a = psb.kmeans_train(x, 30000, 64, cen_a, 1024, 3, assign_a)
+    cen_b = torch.from_numpy(init).cuda()
+    obj_b, assign_b = sharded_kmeans(TrainEngine(psb, torch), None, 1, x, 30000, 64, cen_b, 1024, 3, torch)
+    torch.cuda.synchronize()
+    assert np.allclose(obj_a, obj_b, rtol=1e-9)
+    assert np.allclose(cen_a.cpu().numpy(), cen_b.cpu().numpy(), rtol=1e-6, atol=1e-7)
+    assert np.mean(assign_a.cpu().numpy() == assign_b.cpu().numpy()) > 0.9999
