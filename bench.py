@@ -522,7 +522,7 @@ def training(args, cfg, torch, api, device):
         ms_e2e = e0.elapsed_time(e1) / steps
         # PQ on the residuals x - centroid[assign], then encoding
         t0 = time.time()
-        x -= cen[assign.long()]
+        api.residual_rows(x, n, dim, cen, assign, x, device=device, stream=st)  # in place
         codebook = torch.empty((M, 256, dim // M), dtype=torch.float32, device="cuda")
         torch.cuda.synchronize()
         t1 = time.time()

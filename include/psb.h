@@ -351,6 +351,12 @@ psb_status psb_kmeans_accumulate(const float* d_data, int64_t n, int dim, const 
 psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids, int device,
                              void* stream);
 
+/* Residual rows out[i] = data[i] - centroids[assign[i]] (fp32 subtraction; d_out may alias d_data): the input of
+ * psb_pq_train / psb_pq_encode for a residual-mode index.  Replaces the residual step of the reference's residual PQ
+ * trainer (src/quantization/pq/residual_pq_trainer.cuh:467-830). */
+psb_status psb_residual_rows(const float* d_data, int64_t n, int dim, const float* d_centroids, const int* d_assign,
+                             float* d_out, int device, void* stream);
+
 /* PQ codebooks: one k-means (codebook_size codewords) per subspace, seeded sampling for the initial
  * codewords.  Replaces train_plain_pq_codebooks_gpu (src/quantization/pq/pq_trainer.cuh:9-26,
  * src/quantization/pq/pq_trainer.cu:30-95).  d_codebook [m][k][dim/m] out. */

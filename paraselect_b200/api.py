@@ -92,7 +92,7 @@ EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
     "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_scan",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
-    "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
+    "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
 _lib = None
@@ -356,6 +356,11 @@ def kmeans_accumulate(d_data, n, dim, d_assign, d_best, k, d_sums, d_counts, d_o
 def kmeans_update(d_sums, d_counts, k, dim, d_centroids, device=0, stream=None):
     _check(lib().psb_kmeans_update(C.c_void_p(_p(d_sums)), C.c_void_p(_p(d_counts)), k, dim, C.c_void_p(_p(d_centroids)),
                                    device, _stream_ptr(stream)))
+
+
+def residual_rows(d_data, n, dim, d_centroids, d_assign, d_out, device=0, stream=None):
+    _check(lib().psb_residual_rows(C.c_void_p(_p(d_data)), C.c_int64(n), dim, C.c_void_p(_p(d_centroids)),
+                                   C.c_void_p(_p(d_assign)), C.c_void_p(_p(d_out)), device, _stream_ptr(stream)))
 
 
 def pq_train(d_data, n, dim, M, K, iters, seed, d_codebook, device=0, stream=None):

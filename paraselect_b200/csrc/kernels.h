@@ -175,6 +175,8 @@ psb_status launch_pq_init(const float* d_data, long long n, int dim, int m, int 
 psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign,
                                     const float* d_best, double* d_sums, int* d_counts, double* d_obj,
                                     cudaStream_t s);
+psb_status launch_residual_rows(const float* d_data, long long n, int dim, const float* d_centroids, const int* d_assign,
+                                float* d_out, cudaStream_t s);
 psb_status launch_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids,
                                 cudaStream_t s);
 

@@ -1316,6 +1316,14 @@ psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, i
     return launch_kmeans_update(d_sums, d_counts, k, dim, d_centroids, static_cast<cudaStream_t>(stream));
 }
 
+psb_status psb_residual_rows(const float* d_data, int64_t n, int dim, const float* d_centroids, const int* d_assign,
+                             float* d_out, int device, void* stream) {
+    if (!d_data || !d_centroids || !d_assign || !d_out || n < 0 || dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid residual request");
+    if ((long long)n * dim > 0x7fffffffLL * 256) return fail(PSB_UNSUPPORTED_SHAPE, "too many elements for one call");
+    PSB_TRY(check_device(device));
+    return launch_residual_rows(d_data, n, dim, d_centroids, d_assign, d_out, static_cast<cudaStream_t>(stream));
+}
+
 psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors, int codebook_size, int iters,
                         uint64_t seed, float* d_codebook, int device, void* stream) {
     if (!d_data || !d_codebook || n <= 0 || dim <= 0 || subvectors <= 0 || dim % subvectors || codebook_size <= 0 ||

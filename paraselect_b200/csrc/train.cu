@@ -125,6 +125,16 @@ __global__ void k_mean_update(const double* __restrict__ sums, const int* __rest
     if (c > 0) centres[i] = (float)(sums[i] / (double)c);
 }
 
+// out[row] = data[row] - centroids[assign[row]] (fp32 subtraction): what residual-mode PQ is trained on and encodes.
+__global__ void k_residual_rows(const float* __restrict__ data, long long n, int dim, const float* __restrict__ centroids,
+                                const int* __restrict__ assign, float* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * dim) return;
+    const long long row = i / dim;
+    const int d = (int)(i - row * dim);
+    out[i] = __fsub_rn(data[i], __ldg(centroids + (size_t)assign[row] * dim + d));
+}
+
 __host__ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
     x += 0x9E3779B97F4A7C15ull;
     x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -259,6 +269,15 @@ psb_status launch_kmeans_update(const double* d_sums, const int* d_counts, int k
                                 cudaStream_t s) {
     const long long total = (long long)k * dim;
     k_mean_update<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(d_sums, d_counts, k, dim, d_centroids);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_residual_rows(const float* d_data, long long n, int dim, const float* d_centroids, const int* d_assign,
+                                float* d_out, cudaStream_t s) {
+    if (n <= 0) return PSB_OK;
+    k_residual_rows<<<(unsigned)((n * dim + 255) / 256), 256, 0, s>>>(d_data, n, dim, d_centroids, d_assign, d_out);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

@@ -443,3 +443,21 @@ def test_staged_transport_overlapped_by_a_host_worker_equals_mapped(psb):
     for name in ("staged", "staged_serial"):
         assert np.array_equal(res[name]["indices"], res["mapped"]["indices"])
         assert np.array_equal(res[name]["distances"], res["mapped"]["distances"])
+
+
+def test_residual_rows_feed_residual_training(psb):
+    """psb_residual_rows (in place) = row - centroid[assign]; PQ trained on and encoding the residuals gives an index the
+    residual search accepts (codes equal the checker's encoding of the same residuals)."""
+    torch = _torch()
+    centres, data, offsets = synth.mixture(12000, 32, 24, 0.3, seed=33)
+    lists = np.repeat(np.arange(24), np.diff(offsets)).astype(np.int32)
+    x = dev(data)
+    psb.residual_rows(x, 12000, 32, dev(centres), dev(lists), x)
+    want = (data - centres[lists]).astype(np.float32)
+    assert np.array_equal(x.cpu().numpy(), want)
+    cb = torch.empty((8, 256, 4), dtype=torch.float32, device="cuda")
+    psb.pq_train(x, 12000, 32, 8, 256, 4, 5, cb)
+    codes = torch.empty((12000, 8), dtype=torch.uint8, device="cuda")
+    psb.pq_encode(x, 12000, 32, cb, 8, 256, codes)
+    torch.cuda.synchronize()
+    assert np.array_equal(codes.cpu().numpy(), oracle.pq_encode(want, cb.cpu().numpy()))
