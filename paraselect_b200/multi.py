@@ -108,6 +108,8 @@ class ShardedSearch:
         self.l_cnt = engine.empty((nq,), t.int32)
         self.g_rows = engine.empty((world, nq, width), t.int32)
         self.g_dist = engine.empty((world, nq, width), t.float32)
+        self.l_key = engine.empty((nq, width), t.int64)          # packed (distance bits << 32 | row) for the all-gather
+        self.g_key = engine.empty((world, nq, width), t.int64)
         self.m_rows = engine.empty((nq, width), t.int32)
         self.m_dist = engine.empty((nq, width), t.float32)
         self.p_dist = engine.empty((nq, width), t.float32)
@@ -141,10 +143,16 @@ class ShardedSearch:
         sl = slice(q0, q0 + m)
         m_rows, m_dist = self.l_rows[sl], self.l_dist[sl]
         if w > 1:
+            # one collective for rows and distances: 64-bit words (distance bits << 32 | row), unpacked after the gather
+            t = self.torch
             g_rows = self.g_rows.view(-1)[:w * m * width].view(w, m, width)
             g_dist = self.g_dist.view(-1)[:w * m * width].view(w, m, width)
-            d.all_gather_into_tensor(g_rows.view(w * m, width), self.l_rows[sl])
-            d.all_gather_into_tensor(g_dist.view(w * m, width), self.l_dist[sl])
+            g_key = self.g_key.view(-1)[:w * m * width].view(w * m, width)
+            key = self.l_key[sl]
+            t.bitwise_or(self.l_dist[sl].view(t.int32).to(t.int64) << 32, self.l_rows[sl].to(t.int64) & 0xFFFFFFFF, out=key)
+            d.all_gather_into_tensor(g_key, key)
+            g_rows.view(w * m, width).copy_(g_key & 0xFFFFFFFF)            # int64 -> int32 keeps the low word (-1 stays -1)
+            g_dist.view(w * m, width).view(t.int32).copy_(g_key >> 32)
             self._mark("all_gather")
             m_rows, m_dist = self.m_rows[sl], self.m_dist[sl]
             e.merge(g_rows, g_dist, w, m, width, m_rows, m_dist)
@@ -160,10 +168,14 @@ class ShardedSearch:
         else:
             self.o_rows[sl].copy_(m_rows[:, :self.topk])
             self.o_dist[sl].copy_(m_dist[:, :self.topk])
+        # ids of the rows this rank holds, -1 elsewhere; step() combines them with ONE all-reduce(max) for the whole batch
         e.map_ids(self.o_rows[sl], m * self.topk, self.o_ids[sl])
-        if w > 1:
-            d.all_reduce(self.o_ids[sl], op=d.ReduceOp.MAX)
-        self._mark("map_ids+all_reduce_max")
+        self._mark("map_ids")
+
+    def _combine_ids(self):
+        if self.world > 1:
+            self.dist.all_reduce(self.o_ids, op=self.dist.ReduceOp.MAX)
+        self._mark("all_reduce_max")
 
     def step(self, dq, profile=False, parts=None):
         """One batch.  parts > 1 cuts the batch into sub-batches; on an engine with streams the exchange half of
@@ -183,6 +195,7 @@ class ShardedSearch:
                 m = min(sb, nq - q0)
                 self._front(dq, q0, m)
                 self._back(dq, q0, m)
+            self._combine_ids()
             return self.o_ids, self.o_dist
         t = self.torch
         main = t.cuda.current_stream()
@@ -201,6 +214,7 @@ class ShardedSearch:
             finally:
                 e.set_stream(None, False)
         main.wait_stream(aux)
+        self._combine_ids()
         return self.o_ids, self.o_dist
 
     # The engine and torch.distributed are driven from torch's current stream (the bench creates the session on it, and
