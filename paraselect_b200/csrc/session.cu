@@ -793,6 +793,20 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     const bool staged_overlap = rerank && s->opt.exact_mode == PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
     const int sb = sub_batch_rows(s, n, nprobe, overlap || staged_overlap);
     const bool residual = s->opt.adc_mode == 1;
+    // Sub-batch boundaries.  Equal cuts, except with the overlapped staged transport: there the transfer costs the scan
+    // nothing, the host gather of a sub-batch is shorter than the next scan, and only the last sub-batch's rerank is
+    // exposed - so the last sub-batch is the small one (32/32/26/10 %).  (With the kernel gather, which slows the scan it
+    // runs beside, such cuts measured no better than equal ones.)
+    std::vector<int> cuts;
+    static const bool even_cuts = std::getenv("PSB_EVEN_CUTS") != nullptr;  // tuning knob, read once
+    if (staged_overlap && !residual && sb * 4 >= n && n >= 4096 && !even_cuts) {
+        cuts = {0, (int)(0.32 * n), (int)(0.64 * n), (int)(0.90 * n), n};
+    } else {
+        for (int p0 = 0; p0 < n; p0 += sb) cuts.push_back(p0);
+        cuts.push_back(n);
+    }
+    int sb_max = 0;
+    for (size_t ci = 0; ci + 1 < cuts.size(); ++ci) sb_max = std::max(sb_max, cuts[ci + 1] - cuts[ci]);
     if ((overlap || staged_overlap) && !s->aux_stream) {
         int lo = 0, hi = 0;  // lowest priority: the scan's CTAs get the SMs first, the transfer fills the gaps
         PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -826,8 +840,8 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
             PSB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&s->h_cand_pinned), sizeof(int) * cand_count, cudaHostAllocDefault));
             s->h_cand_pinned_count = cand_count;
         }
-        PSB_TRY(s->stage.reserve((size_t)sb * stage1_k * s->dim * s->exact_elem));
-        PSB_TRY(s->score.reserve(sizeof(float) * (size_t)sb * stage1_k));
+        PSB_TRY(s->stage.reserve((size_t)sb_max * stage1_k * s->dim * s->exact_elem));
+        PSB_TRY(s->score.reserve(sizeof(float) * (size_t)sb_max * stage1_k));
         worker = std::thread([&]() {
             cudaSetDevice(s->device);
             auto process = [&](const Job& j) -> psb_status {
@@ -873,11 +887,6 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     if (times) rc = tm_s.mark(st);
     if (rc == PSB_OK) rc = coarse_exact(s, dq, n, nprobe, d_probes, nullptr);
     if (rc == PSB_OK && times) rc = tm_s.mark(st);
-    // Sub-batch boundaries: equal cuts (cuts that shrink toward the end, to shorten the last rerank that nothing hides,
-    // measured no better).
-    std::vector<int> cuts;
-    for (int p0 = 0; p0 < n; p0 += sb) cuts.push_back(p0);
-    cuts.push_back(n);
     for (size_t ci = 0; ci + 1 < cuts.size() && rc == PSB_OK; ++ci) {
         const int p0 = cuts[ci];
         const int m = cuts[ci + 1] - p0;
