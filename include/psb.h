@@ -250,6 +250,16 @@ psb_status psb_stage_build_lut(psb_session* session, const float* d_queries, int
 psb_status psb_stage_build_lut_residual(psb_session* session, const float* d_queries, int nq, const int* d_probes,
                                         int nprobe, float* d_lut);
 
+/* Affine u8 quantisation of fp32 tables, per sub-quantiser: scale = max((hi - lo) / 255, 1e-6), u8 = clamp(rint((v - lo) /
+ * scale), 0, 255), lo_sum = sum of lo, inflation = sum of scale * (0.5 plain, 1 residual) - the amount by which a cutoff on
+ * u8 scores must be raised so that no true candidate is lost.  Replaces quantize_query_codeword_dot_lut_u8_kernel
+ * (src/search/kernels/fine/gpu_fine/pq_adc/pq_query_lut.cu:37-97).  d_lut [tables][M][K] (tables = nq, or nq * nprobe in
+ * residual mode), d_q8 the same shape in u8, d_scales [tables][M], d_lo_sum / d_inflation [tables].  This library's own scan
+ * does not use u8 scores (its fp16 pre-filter is followed by exact fp32 re-scoring); the operator exists for callers
+ * that keep the reference's u8 scoring elsewhere. */
+psb_status psb_stage_quantize_lut_u8(psb_session* session, const float* d_lut, int64_t tables, uint8_t* d_q8, float* d_scales,
+                                     float* d_lo_sum, float* d_inflation);
+
 /* ADC scan of the probed lists with per-query selection of the stage1_k smallest distances
  * (ties by row).  Replaces ivfpq_fine_cpu_lut (src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:69-117) and
  * pq_query_lut_threshold_search_gpu + pq_candidate_cap_select

@@ -90,7 +90,7 @@ class Stats(C.Structure):
 
 EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
-    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_scan",
+    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_quantize_lut_u8", "psb_stage_scan",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -249,6 +249,10 @@ class Session:
     def stage_build_lut_residual(self, d_queries, nq, d_probes, nprobe, d_lut):
         _check(lib().psb_stage_build_lut_residual(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_probes)), nprobe,
                                                   C.c_void_p(_p(d_lut))))
+
+    def stage_quantize_lut_u8(self, d_lut, tables, d_q8, d_scales, d_lo_sum, d_inflation):
+        _check(lib().psb_stage_quantize_lut_u8(self._h, C.c_void_p(_p(d_lut)), C.c_int64(tables), C.c_void_p(_p(d_q8)),
+                                               C.c_void_p(_p(d_scales)), C.c_void_p(_p(d_lo_sum)), C.c_void_p(_p(d_inflation))))
 
     def stage_scan(self, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist=None, d_count=None):
         _check(lib().psb_stage_scan(self._h, C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)), nprobe, stage1_k,

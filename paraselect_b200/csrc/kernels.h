@@ -120,6 +120,10 @@ psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, co
                                      const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
                                      float* d_lut, cudaStream_t s);
 
+// Affine u8 quantisation of `tables` fp32 tables [m][k]: d_q8 [tables][m][k], d_scales [tables][m], d_lo_sum / d_inflation [tables].
+psb_status launch_lut_to_u8(const float* d_lut, long long tables, int m, int k, int residual, uint8_t* d_q8, float* d_scales,
+                            float* d_lo_sum, float* d_inflation, cudaStream_t s);
+
 // Residual tables, fp32 and fp16 (ws.lut_h, ws.lut_scale) in one kernel, when residual_tables_fused(); the following
 // launch_scan takes ws.half_tables_ready = true and skips its own conversion.
 bool residual_tables_fused(const ScanWorkspace& ws, int m, int k);

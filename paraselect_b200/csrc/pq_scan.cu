@@ -731,6 +731,49 @@ __global__ void k_lut_to_half(const float* __restrict__ lut, int m, int k, __hal
         lut_h[(size_t)q * mk + e] = __float2half_rd(lut[(size_t)q * mk + e] * sc);
 }
 
+// Affine u8 quantisation of fp32 tables, per sub-quantiser (reference: quantize_query_codeword_dot_lut_u8_kernel,
+// src/search/kernels/fine/gpu_fine/pq_adc/pq_query_lut.cu:37-97): scale = max((hi - lo) / 255, 1e-6),
+// u8 = clamp(rint((v - lo) / scale), 0, 255), lo_sum = sum of lo, inflation = sum of scale * (0.5 plain | 1 residual).
+// One CTA per table; sub-quantisers one after the other, block-wide min / max.
+__global__ void __launch_bounds__(256)
+k_lut_to_u8(const float* __restrict__ lut, int m, int k, int residual, uint8_t* __restrict__ q8, float* __restrict__ scales,
+            float* __restrict__ lo_sum, float* __restrict__ inflation) {
+    __shared__ float s_lo[8], s_hi[8];
+    __shared__ float s_mlo, s_mscale;
+    const size_t t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float ls = 0.0f, inf = 0.0f;  // thread 0 only
+    for (int j = 0; j < m; ++j) {
+        const float* row = lut + (t * m + j) * k;
+        float lo = FLT_MAX, hi = -FLT_MAX;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) { const float v = row[c]; lo = fminf(lo, v); hi = fmaxf(hi, v); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+            hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+        }
+        if (lane == 0) { s_lo[warp] = lo; s_hi[warp] = hi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) { lo = fminf(lo, s_lo[w]); hi = fmaxf(hi, s_hi[w]); }
+            float scale = __fdiv_rn(__fsub_rn(hi, lo), 255.0f);
+            if (scale < 1e-6f) scale = 1e-6f;
+            s_mlo = lo; s_mscale = scale;
+            scales[t * m + j] = scale;
+            ls = __fadd_rn(ls, lo);
+            inf = __fadd_rn(inf, __fmul_rn(scale, residual ? 1.0f : 0.5f));
+        }
+        __syncthreads();
+        const float mlo = s_mlo, mscale = s_mscale;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            float r = rintf(__fdiv_rn(__fsub_rn(row[c], mlo), mscale));
+            r = r < 0.0f ? 0.0f : (r > 255.0f ? 255.0f : r);
+            q8[(t * m + j) * k + c] = (uint8_t)r;
+        }
+    }
+    if (threadIdx.x == 0) { lo_sum[t] = ls; inflation[t] = inf; }
+}
+
 struct ScanArgsH {
     ScanArgs a;
     const __half* lut_h;   // [nq][m*k]
@@ -1042,6 +1085,16 @@ psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float
                             float* d_lut, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
     k_build_lut<<<nq, 256, (size_t)dim * sizeof(float), s>>>(d_queries, dim, d_codebook, m, k, d_lut);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_lut_to_u8(const float* d_lut, long long tables, int m, int k, int residual, uint8_t* d_q8, float* d_scales,
+                            float* d_lo_sum, float* d_inflation, cudaStream_t s) {
+    if (tables <= 0) return PSB_OK;
+    if (tables > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many tables in one call");
+    k_lut_to_u8<<<(unsigned)tables, 256, 0, s>>>(d_lut, m, k, residual, d_q8, d_scales, d_lo_sum, d_inflation);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

@@ -40,6 +40,10 @@ __device__ __forceinline__ long long local_row(const RowMap& mp, long long r) {
     return l < mp.local_offsets[lo + 1] ? l : -1;
 }
 
+// Gathers candidate rows into the staging buffer.  A warp takes 32 candidates at a time: every lane resolves one candidate
+// to a local row (for a striped shard that is a binary search of 16 dependent loads - done for 32 candidates at once), then
+// the warp copies the rows four at a time, all four rows' loads issued before the first store, so that a few hundred KB
+// of PCIe reads stay in flight even on a small grid.
 __global__ void k_gather_rows(const unsigned char* __restrict__ src, RowMap mp, int row_bytes,
                               const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
                               const int* __restrict__ counts, unsigned char* __restrict__ stage) {
@@ -50,23 +54,43 @@ __global__ void k_gather_rows(const unsigned char* __restrict__ src, RowMap mp, 
     const uintptr_t both = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(stage);
     const bool vec16 = (row_bytes % 16) == 0 && (both % 16) == 0;
     const bool vec4 = (row_bytes % 4) == 0 && (both % 4) == 0;
-    for (long long w = warp0; w < total; w += nwarps) {
-        const int q = (int)(w / candidate_count), i = (int)(w % candidate_count);
-        if (i >= cand_count(counts, q, candidate_count)) continue;
-        const long long row = local_row(mp, cand[(size_t)q * candidate_stride + i]);
-        if (row < 0) continue;
-        const unsigned char* s = src + (size_t)row * row_bytes;
-        unsigned char* d = stage + (size_t)w * row_bytes;
-        if (vec16) {
-            const uint4* s4 = reinterpret_cast<const uint4*>(s);
-            uint4* d4 = reinterpret_cast<uint4*>(d);
-            for (int j = lane; j < row_bytes / 16; j += 32) d4[j] = s4[j];
-        } else if (vec4) {
-            const uint32_t* s4 = reinterpret_cast<const uint32_t*>(s);
-            uint32_t* d4 = reinterpret_cast<uint32_t*>(d);
-            for (int j = lane; j < row_bytes / 4; j += 32) d4[j] = s4[j];
+    const int n16 = row_bytes / 16;
+    for (long long base = warp0 * 32; base < total; base += nwarps * 32) {
+        long long mine = -1;
+        const long long w = base + lane;
+        if (w < total) {
+            const int q = (int)(w / candidate_count), i = (int)(w % candidate_count);
+            if (i < cand_count(counts, q, candidate_count)) mine = local_row(mp, cand[(size_t)q * candidate_stride + i]);
+        }
+        if (vec16 && n16 <= 32) {
+#pragma unroll 1
+            for (int k0 = 0; k0 < 32; k0 += 4) {
+                long long r[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) r[u] = __shfl_sync(0xffffffffu, mine, k0 + u);
+                if ((r[0] & r[1] & r[2] & r[3]) < 0) continue;  // all four absent (-1): uniform
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (r[u] >= 0 && lane < n16) v[u] = reinterpret_cast<const uint4*>(src + (size_t)r[u] * row_bytes)[lane];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (r[u] >= 0 && lane < n16) reinterpret_cast<uint4*>(stage + (size_t)(base + k0 + u) * row_bytes)[lane] = v[u];
+            }
         } else {
-            for (int j = lane; j < row_bytes; j += 32) d[j] = s[j];
+            for (int k = 0; k < 32; ++k) {
+                const long long row = __shfl_sync(0xffffffffu, mine, k);
+                if (row < 0) continue;
+                const unsigned char* sp = src + (size_t)row * row_bytes;
+                unsigned char* d = stage + (size_t)(base + k) * row_bytes;
+                if (vec16) {
+                    for (int j = lane; j < n16; j += 32) reinterpret_cast<uint4*>(d)[j] = reinterpret_cast<const uint4*>(sp)[j];
+                } else if (vec4) {
+                    for (int j = lane; j < row_bytes / 4; j += 32) reinterpret_cast<uint32_t*>(d)[j] = reinterpret_cast<const uint32_t*>(sp)[j];
+                } else {
+                    for (int j = lane; j < row_bytes; j += 32) d[j] = sp[j];
+                }
+            }
         }
     }
 }

@@ -692,6 +692,13 @@ psb_status psb_stage_build_lut_residual(psb_session* s, const float* d_queries, 
                                      s->codebook.as<float>(), s->m, s->k, d_lut, s->stream);
 }
 
+psb_status psb_stage_quantize_lut_u8(psb_session* s, const float* d_lut, int64_t tables, uint8_t* d_q8, float* d_scales,
+                                     float* d_lo_sum, float* d_inflation) {
+    if (!s || !d_lut || !d_q8 || !d_scales || !d_lo_sum || !d_inflation || tables < 0) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_lut_to_u8(d_lut, tables, s->m, s->k, s->opt.adc_mode == 1 ? 1 : 0, d_q8, d_scales, d_lo_sum, d_inflation, s->stream);
+}
+
 psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int* d_probes, int nprobe,
                           int stage1_k, int* d_rows, float* d_dist, int* d_count) {
     if (!s || !d_lut || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");

@@ -461,3 +461,27 @@ def test_residual_rows_feed_residual_training(psb):
     psb.pq_encode(x, 12000, 32, cb, 8, 256, codes)
     torch.cuda.synchronize()
     assert np.array_equal(codes.cpu().numpy(), oracle.pq_encode(want, cb.cpu().numpy()))
+
+
+@pytest.mark.parametrize("M,dim,residual", [(8, 32, False), (48, 96, False), (20, 100, True)])
+def test_u8_table_quantiser_matches_checker(psb, M, dim, residual):
+    """psb_stage_quantize_lut_u8 against the checker's restatement of the reference's u8 table quantiser: codes, scales,
+    lo_sum and inflation bit for bit."""
+    torch = _torch()
+    ix = synth.make_index(3000, dim, 8, M, seed=50 + M, residual=residual)
+    q = synth.make_queries(ix, 7, seed=4)
+    with psb.Session(ix, residual=residual) as s:
+        lut = torch.empty((7, M, 256), dtype=torch.float32, device="cuda")
+        s.stage_build_lut(dev(q), 7, lut)
+        q8 = torch.empty((7, M, 256), dtype=torch.uint8, device="cuda")
+        scales = torch.empty((7, M), dtype=torch.float32, device="cuda")
+        lo = torch.empty((7,), dtype=torch.float32, device="cuda")
+        infl = torch.empty((7,), dtype=torch.float32, device="cuda")
+        s.stage_quantize_lut_u8(lut, 7, q8, scales, lo, infl)
+        s.sync()
+    luts = lut.cpu().numpy()
+    for i in range(7):
+        oq8, osc, olo, oinf = oracle.pq_lut_u8(luts[i], residual=residual)
+        assert np.array_equal(q8[i].cpu().numpy(), oq8.reshape(M, 256))
+        assert np.array_equal(scales[i].cpu().numpy(), osc)
+        assert lo[i].item() == olo and infl[i].item() == oinf
