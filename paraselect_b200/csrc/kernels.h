@@ -95,6 +95,7 @@ struct ScanWorkspace {
     void* lut_h = nullptr;       // [tables][m*k] fp16 tables (tables = max_batch, x nprobe in residual mode) for the half pre-filter scan (null = fp32 scan only)
     float* lut_scale = nullptr;  // [tables]
     int scan_mode = 0;           // 0 = half pre-filter when it fits, 1 = fp32 scan
+    uint64_t* fallback_partial = nullptr;  // [fallback_partial_bytes(stage1_k)]: partial top lists of the split exact fallback
     bool half_tables_ready = false;  // lut_h / lut_scale already hold this call's tables (launch_build_tables_residual)
     int reserve_ctas = 0;        // CTAs left out of the scan's persistent grid, so that kernels of another stream that
                                  // cannot share an SM with a scan CTA (a collective's) still find a free SM
@@ -126,6 +127,7 @@ psb_status launch_lut_to_u8(const float* d_lut, long long tables, int m, int k, 
 
 // Residual tables, fp32 and fp16 (ws.lut_h, ws.lut_scale) in one kernel, when residual_tables_fused(); the following
 // launch_scan takes ws.half_tables_ready = true and skips its own conversion.
+size_t fallback_partial_bytes(int stage1_k);
 bool residual_tables_fused(const ScanWorkspace& ws, int m, int k);
 psb_status launch_build_tables_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
                                         const float* d_centroids, int nlist, const float* d_codebook, int m, int k,

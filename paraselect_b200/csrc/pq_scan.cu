@@ -223,7 +223,7 @@ __device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut,
 // Per query: admission cutoff from a strided sample of the rows it will scan.
 //   N = rows the query scans.  N <= pool capacity: cutoff = +inf (everything is admitted).
 //   Otherwise every stride-th row of each probed list is scored, stride = clamp(stage1_k / 16, 16, 64), n_s rows in
-//   all, and the cutoff is the r-th smallest sample distance with r = ceil(mu + 5 sqrt(mu) + 3), mu = stage1_k * n_s / N:
+//   all, and the cutoff is the r-th smallest sample distance with r = ceil(mu + 4 sqrt(mu) + 2), mu = stage1_k * n_s / N:
 //   the stage1_k-th smallest of all N distances lies below it except with negligible probability, and about r * stride
 //   rows (2-4 x stage1_k) pass it.  The selection kernel verifies that each pool holds at least stage1_k rows and did
 //   not overflow; the exact fallback handles the rest.  The r smallest sample keys are kept with a running cutoff:
@@ -540,8 +540,80 @@ k_select_pool(const uint64_t* __restrict__ pool, const int* __restrict__ pool_cn
     if (out_count && threadIdx.x == 0) out_count[q] = keep;
 }
 
-// Exact per-query scan with a CTA-local running top-k: a buffer of keys below the current cutoff is compacted
+// Exact fallback for the queries the selection kernel flagged.  The unit of work is a running top-k over the rows of some
+// of a query's probes, kept in a CTA-local buffer: keys below the current cutoff are appended, and the buffer is compacted
 // (sorted, truncated to stage1_k, cutoff tightened) whenever it could overflow during the next block of rows.
+// A flagged query usually scans millions of rows, so its probes are cut into kFallbackSplit ranges that different CTAs
+// scan; every range leaves its sorted top-stage1_k in global memory and k_fallback_merge combines the ranges of a query.
+// Only the first kFallbackCap flagged queries are split (the partial lists need memory); any beyond are scanned whole by
+// one CTA each, as a last resort.
+constexpr int kFallbackSplit = 16;
+constexpr int kFallbackCap = 128;
+
+// Leaves the sorted keys of probes [p_begin, p_end) of query q in s_keys (KEY_MAX padded) and returns how many are valid.
+template <int M>
+__device__ __forceinline__ int fallback_scan_probes(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
+                                                    int q, int p_begin, int p_end, const long long* __restrict__ offsets,
+                                                    int nlist, int lb, int le, const uint8_t* __restrict__ codes,
+                                                    long long row_base, const long long* __restrict__ row_delta, int m, int k,
+                                                    int stage1_k, int buf_n, int per_probe, int tree, uint64_t* s_keys,
+                                                    float* s_lut, int* s_cnt, uint64_t* s_cut) {
+    __syncthreads();  // the previous unit's readers of s_keys / s_lut are done
+    if (!per_probe)
+        for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
+    if (threadIdx.x == 0) { *s_cnt = 0; *s_cut = KEY_MAX; }
+    __syncthreads();
+    for (int p = p_begin; p < p_end; ++p) {
+        const int l = probes[(size_t)q * nprobe + p];
+        if (l < lb || l >= le || l < 0 || l >= nlist) continue;
+        const long long b = offsets[l], e = offsets[l + 1];
+        if (per_probe && b < e) {  // residual mode: this probe's own table (uniform branch)
+            __syncthreads();
+            const float* src = lut + ((size_t)q * nprobe + p) * m * k;
+            for (int i = threadIdx.x; i < m * k; i += blockDim.x) s_lut[i] = src[i];
+            __syncthreads();
+        }
+        const long long delta = row_delta ? row_delta[l] : 0;
+        for (long long base = b; base < e; base += blockDim.x) {
+            const int c_now = *s_cnt;  // stable since the barrier that ended the previous block of rows
+            __syncthreads();           // every thread has read it before any thread appends again
+            if (c_now + (int)blockDim.x > buf_n) {  // uniform decision
+                for (int i = c_now + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
+                __syncthreads();
+                block_bitonic_sort(s_keys, buf_n);
+                if (threadIdx.x == 0) {
+                    const int keep = c_now < stage1_k ? c_now : stage1_k;
+                    *s_cnt = keep;
+                    *s_cut = keep == stage1_k ? s_keys[stage1_k - 1] : KEY_MAX;
+                }
+                __syncthreads();
+            }
+            const long long r = base + threadIdx.x;
+            if (r < e) {
+                const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k, tree != 0);
+                const uint64_t key = make_key(d, (uint32_t)(r + delta));
+                if (key < *s_cut) s_keys[atomicAdd(s_cnt, 1)] = key;
+            }
+            __syncthreads();
+        }
+    }
+    const int c = *s_cnt;
+    for (int i = c + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
+    __syncthreads();
+    block_bitonic_sort(s_keys, buf_n);
+    return c < stage1_k ? c : stage1_k;
+}
+
+__device__ __forceinline__ void fallback_emit(const uint64_t* s_keys, int keep, int q, int stage1_k, int* __restrict__ out_rows,
+                                              float* __restrict__ out_dist, int* __restrict__ out_count) {
+    for (int i = threadIdx.x; i < stage1_k; i += blockDim.x) {
+        const bool ok = i < keep;
+        out_rows[(size_t)q * stage1_k + i] = ok ? (int)key_idx(s_keys[i]) : -1;
+        if (out_dist) out_dist[(size_t)q * stage1_k + i] = ok ? key_dist(s_keys[i]) : FLT_MAX;
+    }
+    if (out_count && threadIdx.x == 0) out_count[q] = keep;
+}
+
 template <int M>
 __global__ void __launch_bounds__(kFallbackThreads)
 k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, int nprobe,
@@ -549,71 +621,82 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
                  const uint8_t* __restrict__ codes, long long row_base, const long long* __restrict__ row_delta,
                  int m, int k, int stage1_k, int buf_n, const int* __restrict__ fail_list, const int* __restrict__ n_fail, int* __restrict__ fail_cursor,
                  int* __restrict__ out_rows, float* __restrict__ out_dist, int* __restrict__ out_count,
-                 unsigned long long* __restrict__ counters, int per_probe, int tree) {
+                 unsigned long long* __restrict__ counters, int per_probe, int tree, uint64_t* __restrict__ partial) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);                 // [buf_n]
     float* s_lut = reinterpret_cast<float*>(s_raw + (size_t)buf_n * 8);   // [m*k]
     __shared__ int s_cnt, s_idx;
     __shared__ uint64_t s_cut;
     const int nf = *n_fail;
+    const int nsplit = nf < kFallbackCap ? nf : kFallbackCap;        // queries whose probes are cut into ranges
+    const int items = nsplit * kFallbackSplit + (nf - nsplit);        // then whole queries
     for (;;) {
         __syncthreads();
         if (threadIdx.x == 0) s_idx = atomicAdd(fail_cursor, 1);
         __syncthreads();
-        const int idx = s_idx;
-        if (idx >= nf) return;
-        const int q = fail_list[idx];
-        if (!per_probe)
-            for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
-        if (threadIdx.x == 0) { s_cnt = 0; s_cut = KEY_MAX; atomicAdd(&counters[2], 1ull); }
-        __syncthreads();
-        for (int p = 0; p < nprobe; ++p) {
-            const int l = probes[(size_t)q * nprobe + p];
-            if (l < lb || l >= le || l < 0 || l >= nlist) continue;
-            const long long b = offsets[l], e = offsets[l + 1];
-            if (per_probe && b < e) {  // residual mode: this probe's own table (uniform branch)
-                __syncthreads();
-                const float* src = lut + ((size_t)q * nprobe + p) * m * k;
-                for (int i = threadIdx.x; i < m * k; i += blockDim.x) s_lut[i] = src[i];
-                __syncthreads();
-            }
-            const long long delta = row_delta ? row_delta[l] : 0;
-            for (long long base = b; base < e; base += blockDim.x) {
-                const int c_now = s_cnt;  // stable since the barrier that ended the previous block of rows
-                __syncthreads();          // every thread has read it before any thread appends again
-                if (c_now + (int)blockDim.x > buf_n) {  // uniform decision
-                    const int c = c_now;
-                    for (int i = c + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
-                    __syncthreads();
-                    block_bitonic_sort(s_keys, buf_n);
-                    if (threadIdx.x == 0) {
-                        const int keep = c < stage1_k ? c : stage1_k;
-                        s_cnt = keep;
-                        s_cut = keep == stage1_k ? s_keys[stage1_k - 1] : KEY_MAX;
-                    }
-                    __syncthreads();
-                }
-                const long long r = base + threadIdx.x;
-                if (r < e) {
-                    const float d = adc_row<M>(codes + (size_t)(r - row_base) * m, s_lut, m, k, tree != 0);
-                    const uint64_t key = make_key(d, (uint32_t)(r + delta));
-                    if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
-                }
-                __syncthreads();
-            }
+        const int item = s_idx;
+        if (item >= items) return;
+        if (item < nsplit * kFallbackSplit) {
+            const int f = item / kFallbackSplit, part = item % kFallbackSplit;
+            const int q = fail_list[f];
+            const int p0 = (int)((long long)nprobe * part / kFallbackSplit), p1 = (int)((long long)nprobe * (part + 1) / kFallbackSplit);
+            fallback_scan_probes<M>(lut, probes, nprobe, q, p0, p1, offsets, nlist, lb, le, codes, row_base, row_delta, m, k,
+                                    stage1_k, buf_n, per_probe, tree, s_keys, s_lut, &s_cnt, &s_cut);
+            uint64_t* out = partial + (size_t)item * stage1_k;  // KEY_MAX beyond the valid keys
+            for (int i = threadIdx.x; i < stage1_k; i += blockDim.x) out[i] = s_keys[i];
+        } else {
+            const int q = fail_list[nsplit + (item - nsplit * kFallbackSplit)];
+            const int keep = fallback_scan_probes<M>(lut, probes, nprobe, q, 0, nprobe, offsets, nlist, lb, le, codes, row_base,
+                                                     row_delta, m, k, stage1_k, buf_n, per_probe, tree, s_keys, s_lut, &s_cnt, &s_cut);
+            fallback_emit(s_keys, keep, q, stage1_k, out_rows, out_dist, out_count);
+            if (threadIdx.x == 0) atomicAdd(&counters[2], 1ull);
         }
-        const int c = s_cnt;
-        for (int i = c + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
-        __syncthreads();
-        block_bitonic_sort(s_keys, buf_n);
-        const int keep = c < stage1_k ? c : stage1_k;
-        for (int i = threadIdx.x; i < stage1_k; i += blockDim.x) {
-            const bool ok = i < keep;
-            out_rows[(size_t)q * stage1_k + i] = ok ? (int)key_idx(s_keys[i]) : -1;
-            if (out_dist) out_dist[(size_t)q * stage1_k + i] = ok ? key_dist(s_keys[i]) : FLT_MAX;
-        }
-        if (out_count && threadIdx.x == 0) out_count[q] = keep;
     }
+}
+
+// Combines the kFallbackSplit sorted partial lists of each split query: the same running top-k, fed with keys.
+__global__ void __launch_bounds__(kFallbackThreads)
+k_fallback_merge(const uint64_t* __restrict__ partial, int stage1_k, int buf_n, const int* __restrict__ fail_list,
+                 const int* __restrict__ n_fail, int* __restrict__ out_rows, float* __restrict__ out_dist,
+                 int* __restrict__ out_count, unsigned long long* __restrict__ counters) {
+    extern __shared__ __align__(16) unsigned char s_raw_m[];
+    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw_m);  // [buf_n]
+    __shared__ int s_cnt;
+    __shared__ uint64_t s_cut;
+    const int nf = *n_fail;
+    const int f = blockIdx.x;
+    if (f >= nf || f >= kFallbackCap) return;
+    const int q = fail_list[f];
+    if (threadIdx.x == 0) { s_cnt = 0; s_cut = KEY_MAX; atomicAdd(&counters[2], 1ull); }
+    __syncthreads();
+    const long long total = (long long)kFallbackSplit * stage1_k;
+    const uint64_t* src = partial + (size_t)f * kFallbackSplit * stage1_k;
+    for (long long base = 0; base < total; base += blockDim.x) {
+        const int c_now = s_cnt;
+        __syncthreads();
+        if (c_now + (int)blockDim.x > buf_n) {  // uniform
+            for (int i = c_now + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
+            __syncthreads();
+            block_bitonic_sort(s_keys, buf_n);
+            if (threadIdx.x == 0) {
+                const int keep = c_now < stage1_k ? c_now : stage1_k;
+                s_cnt = keep;
+                s_cut = keep == stage1_k ? s_keys[stage1_k - 1] : KEY_MAX;
+            }
+            __syncthreads();
+        }
+        const long long i = base + threadIdx.x;
+        if (i < total) {
+            const uint64_t key = src[i];
+            if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;  // KEY_MAX padding never passes
+        }
+        __syncthreads();
+    }
+    const int c = s_cnt;
+    for (int i = c + threadIdx.x; i < buf_n; i += blockDim.x) s_keys[i] = KEY_MAX;
+    __syncthreads();
+    block_bitonic_sort(s_keys, buf_n);
+    fallback_emit(s_keys, c < stage1_k ? c : stage1_k, q, stage1_k, out_rows, out_dist, out_count);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -1033,7 +1116,7 @@ psb_status run_scan_m(const ScanArgs& a, int group, int sm_count, cudaStream_t s
 
 // Safety margin of the sampled cutoff in standard deviations (PSB_SEED_SIGMA overrides it; tuning knob, read once).
 float seed_margin_sigma() {
-    static const float v = [] { const char* e = std::getenv("PSB_SEED_SIGMA"); const float x = e ? (float)std::atof(e) : 0.f; return x >= 2.f && x <= 10.f ? x : 5.0f; }();
+    static const float v = [] { const char* e = std::getenv("PSB_SEED_SIGMA"); const float x = e ? (float)std::atof(e) : 0.f; return x >= 2.f && x <= 10.f ? x : 4.0f; }();
     return v;
 }
 
@@ -1062,7 +1145,13 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     k_exact_fallback<M><<<sm_count, kFallbackThreads, smem, s>>>(
         d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.row_delta, ix.m, ix.k,
         stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters,
-        ix.residual ? 1 : 0, tree_order(ix) ? 1 : 0);
+        ix.residual ? 1 : 0, tree_order(ix) ? 1 : 0, ws.fallback_partial);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    const size_t msmem = (size_t)buf_n * 8;
+    PSB_TRY(set_smem(k_fallback_merge, msmem));
+    k_fallback_merge<<<kFallbackCap, kFallbackThreads, msmem, s>>>(ws.fallback_partial, stage1_k, buf_n, ws.fail_list, ws.n_fail,
+                                                                  d_rows, d_dist, d_count, ws.counters);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -1127,6 +1216,8 @@ psb_status run_build_tables_residual(const float* d_queries, int nq, int dim, co
         return PSB_OK;
     }
 }
+
+size_t fallback_partial_bytes(int stage1_k) { return (size_t)kFallbackCap * kFallbackSplit * stage1_k * sizeof(uint64_t); }
 
 bool residual_tables_fused(const ScanWorkspace& ws, int m, int k) {
     return ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(m, k) && k <= 256;

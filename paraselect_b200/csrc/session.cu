@@ -203,7 +203,7 @@ struct psb_session {
     std::vector<long long> h_global_begin, h_offsets;  // striped shards: host copies for the staged transport
     // workspaces
     DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
-        pool_cnt, pool, fail_list, scalars, lut_h, lut_scale, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
+        pool_cnt, pool, fail_list, fallback_partial, scalars, lut_h, lut_scale, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
     int ws_batch = 0, ws_nprobe = 0, ws_stage1 = 0, ws_topk = 0;
     int pool_cap = 0;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> scan_events;  // pending (options.time_kernels)
@@ -236,6 +236,7 @@ struct psb_session {
         w.item_off = item_off.as<long long>(); w.visitors = visitors.as<int>(); w.q_rows = q_rows.as<long long>();
         w.thr = thr.as<float>(); w.pool_cnt = pool_cnt.as<int>(); w.pool = pool.as<uint64_t>();
         w.fail_list = fail_list.as<int>();
+        w.fallback_partial = fallback_partial.as<uint64_t>();
         unsigned long long* sc = scalars.as<unsigned long long>();
         w.counters = sc;                                   // [0..3]
         w.work_cursor = sc + 4;
@@ -326,6 +327,7 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
     PSB_TRY(s->pool.reserve(sizeof(uint64_t) * (size_t)nq * cap));
     s->pool_cap = cap;
     PSB_TRY(s->fail_list.reserve(sizeof(int) * (size_t)nq));
+    PSB_TRY(s->fallback_partial.reserve(fallback_partial_bytes(stage1_k)));
     if (s->opt.scan_mode != 1) {
         PSB_TRY(s->lut_h.reserve(sizeof(unsigned short) * tables * s->m * s->k));
         PSB_TRY(s->lut_scale.reserve(sizeof(float) * tables));
