@@ -189,12 +189,15 @@ class ShardedSearch:
         e.coarse(dq, nq, self.nprobe, self.probes)
         self._mark("coarse")
         sb = (nq + parts - 1) // parts
+        cuts = list(range(0, nq, sb)) + [nq]
         streams = parts > 1 and getattr(e, "streams", False)
+        if streams and parts == 4 and nq >= 4096:
+            # only the last sub-batch's exchange half has nothing to hide behind: make it the small one
+            cuts = [0, int(0.32 * nq), int(0.64 * nq), int(0.90 * nq), nq]
         if not streams:
-            for q0 in range(0, nq, sb):
-                m = min(sb, nq - q0)
-                self._front(dq, q0, m)
-                self._back(dq, q0, m)
+            for q0, q1 in zip(cuts[:-1], cuts[1:]):
+                self._front(dq, q0, q1 - q0)
+                self._back(dq, q0, q1 - q0)
             self._combine_ids()
             return self.o_ids, self.o_dist
         t = self.torch
@@ -203,8 +206,8 @@ class ShardedSearch:
             self.aux = t.cuda.Stream(priority=0)
         aux = self.aux
         aux.wait_stream(main)  # the second stream starts after everything already queued
-        for q0 in range(0, nq, sb):
-            m = min(sb, nq - q0)
+        for q0, q1 in zip(cuts[:-1], cuts[1:]):
+            m = q1 - q0
             self._front(dq, q0, m)
             aux.wait_stream(main)
             e.set_stream(aux.cuda_stream, True)
