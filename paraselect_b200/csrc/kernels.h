@@ -125,13 +125,14 @@ psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, co
 psb_status launch_lut_to_u8(const float* d_lut, long long tables, int m, int k, int residual, uint8_t* d_q8, float* d_scales,
                             float* d_lo_sum, float* d_inflation, cudaStream_t s);
 
+// d_cb_maxnorm [m]: per sub-quantiser the largest codeword norm (bounds a table's entries without a pass over them).
 // Residual tables, fp32 and fp16 (ws.lut_h, ws.lut_scale) in one kernel, when residual_tables_fused(); the following
 // launch_scan takes ws.half_tables_ready = true and skips its own conversion.
 size_t fallback_partial_bytes(int stage1_k);
 bool residual_tables_fused(const ScanWorkspace& ws, int m, int k);
 psb_status launch_build_tables_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
                                         const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
-                                        float* d_lut, const ScanWorkspace& ws, cudaStream_t s);
+                                        const float* d_cb_maxnorm, float* d_lut, const ScanWorkspace& ws, cudaStream_t s);
 
 psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,

@@ -724,17 +724,21 @@ __device__ __forceinline__ float half_table_scale(float u) {
     return sc;
 }
 
-// Residual mode: the fp32 table of a (query, probe) pair and its fp16 copy in one kernel (k_build_lut_residual followed by
-// k_lut_to_half, without reading the fp32 table back).  One CTA of K threads per pair; thread c computes codeword c's
-// entry for every sub-quantiser and keeps the M entries in registers between the row-maximum reduction (which fixes the
-// scale) and the conversion.  Needs codebook_size <= 256 and a templated M.
+// Residual mode: the fp32 table of a (query, probe) pair and its fp16 copy in one kernel, without reading the fp32 table
+// back.  One CTA of 256 threads per pair; thread c computes codeword c's entry for every sub-quantiser and writes both
+// copies at once.  The fp16 scale needs no pass over the entries: an entry is at most (|r_m| + max_c |cb[m][c]|)^2
+// (r_m: the residual's sub-vector), so s = largest power of two with s * 1.001 * sum_m (|r_m| + cbmax[m])^2 <= 30000 keeps
+// every fp16 sum finite; fp16 being a floating-point format, a scale a few times below the tightest one costs no precision.
+// (The table's fp16 copy may differ from k_lut_to_half's, which scales by the exact row maxima; the scan's results do
+// not depend on the scale, only on the entries being rounded down and re-scored exactly.)  Needs codebook_size <= 256.
 template <int M>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256)
 k_build_tables_residual(const float* __restrict__ queries, int dim, const int* __restrict__ probes, int nprobe,
                         const float* __restrict__ centroids, int nlist, const float* __restrict__ codebook, int k,
-                        float* __restrict__ lut, __half* __restrict__ lut_h, float* __restrict__ scale_out) {
+                        const float* __restrict__ cb_maxnorm, float* __restrict__ lut, __half* __restrict__ lut_h,
+                        float* __restrict__ scale_out) {
     extern __shared__ float s_q[];  // [dim] residual
-    __shared__ float s_wmax[8][M];
+    __shared__ float s_term[M];
     __shared__ float s_scale;
     const long long pair = blockIdx.x;
     const int q = (int)(pair / nprobe);
@@ -744,46 +748,36 @@ k_build_tables_residual(const float* __restrict__ queries, int dim, const int* _
         s_q[i] = __fsub_rn(queries[(size_t)q * dim + i], __ldg(centroids + (size_t)l * dim + i));
     __syncthreads();
     const int dsub = dim / M;
-    const int c = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float ent[M];
-#pragma unroll
-    for (int j = 0; j < M; ++j) {
-        float e = 0.0f;
-        if (c < k) {
-            const float* cb = codebook + ((size_t)j * k + c) * dsub;
-            for (int d = 0; d < dsub; ++d) {
-                const float diff = __fsub_rn(s_q[j * dsub + d], __ldg(cb + d));
-                e = __fadd_rn(e, __fmul_rn(diff, diff));
-            }
-        }
-        ent[j] = e;
-        float mx = e;  // entries are >= 0; idle threads contribute 0
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) s_wmax[warp][j] = mx;
+    if (threadIdx.x < M) {
+        float n2 = 0.0f;
+        for (int d = 0; d < dsub; ++d) n2 += s_q[threadIdx.x * dsub + d] * s_q[threadIdx.x * dsub + d];
+        const float t = sqrtf(n2) + cb_maxnorm[threadIdx.x];
+        s_term[threadIdx.x] = t * t;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         float u = 0.0f;
-        for (int j = 0; j < M; ++j) {
-            float mx = s_wmax[0][j];
-            for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, s_wmax[w][j]);
-            u += mx;
-        }
-        const float sc = half_table_scale(u);
+        for (int j = 0; j < M; ++j) u += s_term[j];
+        const float sc = half_table_scale(u * 1.001f);
         s_scale = sc;
         scale_out[pair] = sc;
     }
     __syncthreads();
     const float sc = s_scale;
-    if (c < k) {
-        float* out = lut + (size_t)pair * M * k;
-        __half* out_h = lut_h + (size_t)pair * M * k;
-#pragma unroll
-        for (int j = 0; j < M; ++j) {
-            out[(size_t)j * k + c] = ent[j];
-            out_h[(size_t)j * k + c] = __float2half_rd(ent[j] * sc);
+    const int c = threadIdx.x;
+    if (c >= k) return;
+    float* out = lut + (size_t)pair * M * k;
+    __half* out_h = lut_h + (size_t)pair * M * k;
+#pragma unroll 4
+    for (int j = 0; j < M; ++j) {
+        const float* cb = codebook + ((size_t)j * k + c) * dsub;
+        float e = 0.0f;
+        for (int d = 0; d < dsub; ++d) {
+            const float diff = __fsub_rn(s_q[j * dsub + d], __ldg(cb + d));
+            e = __fadd_rn(e, __fmul_rn(diff, diff));
         }
+        out[(size_t)j * k + c] = e;
+        out_h[(size_t)j * k + c] = __float2half_rd(e * sc);
     }
 }
 
@@ -1204,13 +1198,14 @@ psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, co
 
 template <int M>
 psb_status run_build_tables_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
-                                     const float* d_centroids, int nlist, const float* d_codebook, int k, float* d_lut,
-                                     void* d_lut_h, float* d_scale, cudaStream_t s) {
+                                     const float* d_centroids, int nlist, const float* d_codebook, int k,
+                                     const float* d_cb_maxnorm, float* d_lut, void* d_lut_h, float* d_scale, cudaStream_t s) {
     if constexpr (M <= 0) {
         return fail(PSB_INTERNAL, "fused residual tables need a templated M");
     } else {
         k_build_tables_residual<M><<<(unsigned)((long long)nq * nprobe), 256, (size_t)dim * sizeof(float), s>>>(
-            d_queries, dim, d_probes, nprobe, d_centroids, nlist, d_codebook, k, d_lut, static_cast<__half*>(d_lut_h), d_scale);
+            d_queries, dim, d_probes, nprobe, d_centroids, nlist, d_codebook, k, d_cb_maxnorm, d_lut, static_cast<__half*>(d_lut_h),
+            d_scale);
         count_launch();
         PSB_LAUNCH_CHECK();
         return PSB_OK;
@@ -1225,11 +1220,12 @@ bool residual_tables_fused(const ScanWorkspace& ws, int m, int k) {
 
 psb_status launch_build_tables_residual(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe,
                                         const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
-                                        float* d_lut, const ScanWorkspace& ws, cudaStream_t s) {
+                                        const float* d_cb_maxnorm, float* d_lut, const ScanWorkspace& ws, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
     if ((long long)nq * nprobe > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
+    if (!d_cb_maxnorm) return fail(PSB_INTERNAL, "codeword norms missing");
     PSB_DISPATCH_M(m, PSB_TRY((run_build_tables_residual<MM>(d_queries, nq, dim, d_probes, nprobe, d_centroids, nlist, d_codebook,
-                                                             k, d_lut, ws.lut_h, ws.lut_scale, s))));
+                                                             k, d_cb_maxnorm, d_lut, ws.lut_h, ws.lut_scale, s))));
     return PSB_OK;
 }
 

@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <atomic>
 #include <climits>
+#include <cmath>
 #include <cstring>
 #include <memory>
 #include <new>
@@ -183,7 +184,7 @@ struct psb_session {
     int list_begin = 0, list_end = 0;
     long long row_base = 0, shard_rows = 0;
     // device copies
-    DevBuf centroids, offsets, reordered, codes, codebook, global_begin, row_delta;
+    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta;
     bool striped = false;          // shard holds a slice of every list (options.list_global_begin)
     // exact rows
     int exact_elem = 0;            // 4 = fp32, 1 = u8, 0 = rerank disabled
@@ -603,6 +604,18 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     const size_t cb_bytes = sizeof(float) * (size_t)s->m * s->k * (s->dim / s->m);
     PSB_TRY(s->codebook.reserve(cb_bytes));
     PSB_CUDA(cudaMemcpyAsync(s->codebook.p, index->pq.codebook, cb_bytes, cudaMemcpyHostToDevice, st));
+    {   // per sub-quantiser the largest codeword norm (residual-mode table builder)
+        const int dsub = s->dim / s->m;
+        std::vector<float> mx((size_t)s->m, 0.0f);
+        for (int j = 0; j < s->m; ++j)
+            for (int c = 0; c < s->k; ++c) {
+                double n2 = 0.0;
+                for (int d = 0; d < dsub; ++d) { const double v = index->pq.codebook[((size_t)j * s->k + c) * dsub + d]; n2 += v * v; }
+                mx[(size_t)j] = std::max(mx[(size_t)j], (float)(std::sqrt(n2) * 1.0001));
+            }
+        PSB_TRY(s->cb_maxnorm.reserve(sizeof(float) * (size_t)s->m));
+        PSB_CUDA(cudaMemcpy(s->cb_maxnorm.p, mx.data(), sizeof(float) * (size_t)s->m, cudaMemcpyHostToDevice));
+    }
     // exact rows
     const auto& E = index->exact;
     if (E.fp32 || E.u8) {
@@ -910,7 +923,8 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         if (rc == PSB_OK) {
             if (residual && residual_tables_fused(sws, s->m, s->k)) {  // fp32 and fp16 tables in one kernel
                 rc = launch_build_tables_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
-                                                  s->codebook.as<float>(), s->m, s->k, s->lut.as<float>(), sws, st);
+                                                  s->codebook.as<float>(), s->m, s->k, s->cb_maxnorm.as<float>(), s->lut.as<float>(),
+                                                  sws, st);
                 sws.half_tables_ready = true;
             } else if (residual) {
                 rc = launch_build_lut_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
