@@ -31,22 +31,22 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE configuration "IVF-PQ at scale" (the one the headline metric is quoted on)
+    # benchmark configuration "IVF-PQ at scale" (the one the headline metric is quoted on)
     "c4": dict(n=100_000_000, dim=96, nlist=65536, M=48, sigma=0.25, zipf=1.1, nq=10000, nprobe=128, topk=100,
                n_rerank=1000, seed=3, desc="IVF-PQ 100Mx96 nlist=65536 M=48 nprobe=128 k=100 rerank=1000 batch=10000"),
     # the same index in residual ADC mode (codebook trained on, and codes encoding, row - centroid[list])
     "c4r": dict(n=100_000_000, dim=96, nlist=65536, M=48, sigma=0.25, zipf=1.1, nq=10000, nprobe=128, topk=100,
                 n_rerank=1000, seed=3, residual=True,
                 desc="IVF-ResidualPQ 100Mx96 nlist=65536 M=48 nprobe=128 k=100 rerank=1000 batch=10000"),
-    # BASELINE configuration "IVF-PQ fp32 1M"
+    # benchmark configuration "IVF-PQ fp32 1M"
     "c2": dict(n=1_000_000, dim=128, nlist=1024, M=32, sigma=0.25, zipf=None, nq=10000, nprobe=32, topk=10,
                n_rerank=100, seed=1, desc="IVF-PQ 1Mx128 nlist=1024 M=32 nprobe=32 k=10 rerank=100 batch=10000"),
-    # BASELINE configuration "index training" (secondary line: k-means assignment on the tensor-core filter, PQ on residuals)
+    # benchmark configuration "index training" (secondary line: k-means assignment on the tensor-core filter, PQ on residuals)
     "c5": dict(n=10_000_000, dim=128, nlist=65536, components=4096, M=32, sigma=0.3, zipf=None, nq=0, nprobe=1, topk=1, n_rerank=0,
                seed=4, iters=20, pq_iters=25,
                desc="training: 10M x 128 rows (4,096-component mixture, sigma 0.3) -> k-means to 65,536 centroids (20 Lloyd iterations), "
                     "PQ M=32 x 8 bit on residuals (25 iterations), encode"),
-    # BASELINE configuration "coarse stage only" (secondary line: tensor-core roofline of the fused coarse GEMM)
+    # benchmark configuration "coarse stage only" (secondary line: tensor-core roofline of the fused coarse GEMM)
     "c3": dict(n=65536, dim=96, nlist=65536, M=8, sigma=0.0, zipf=None, nq=100000, nprobe=64, topk=64, n_rerank=0, seed=2,
                desc="coarse only: 100,000 queries x 65,536 centroids, d=96, unit-mean-norm N(0,1), top-64"),
 }
