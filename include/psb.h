@@ -112,8 +112,11 @@ typedef struct psb_index_view {
 enum {
     PSB_EXACT_HOST_MAPPED = 0, /* register (pin + map) the caller's host rows once; kernels gather rows over PCIe */
     PSB_EXACT_HOST_STAGED = 1, /* host threads gather rows into pinned rings, cudaMemcpyAsync overlaps the copies */
-    PSB_EXACT_RESIDENT = 2     /* exact.fp32 / exact.u8 is already a device pointer (IVFExactStorageKind::Resident,
+    PSB_EXACT_RESIDENT = 2,    /* exact.fp32 / exact.u8 is already a device pointer (IVFExactStorageKind::Resident,
                                   src/search/ivf_common/ivf_storage.h:25-30) */
+    PSB_EXACT_HOST_CACHED = 3  /* the session copies the caller's host rows into device memory once at creation and reranks from
+                                  there (refused with PSB_OUT_OF_MEMORY when they do not fit); no counterpart in the reference,
+                                  whose rerank rows stay on the host */
 };
 
 /* IVFPQSearchOptions (src/search/ivfpq/ivfpq_search_context.h:31-45) reduced to what this path uses,

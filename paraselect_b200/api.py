@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(_HERE, "libpsb.so")
 PSB_OK = 0
 STATUS_NAMES = {0: "PSB_OK", 1: "PSB_INVALID_ARGUMENT", 2: "PSB_UNSUPPORTED_SHAPE", 3: "PSB_CUDA_ERROR",
                 4: "PSB_OUT_OF_MEMORY", 5: "PSB_NO_DEVICE", 6: "PSB_INTERNAL", 7: "PSB_TIMEOUT"}
-EXACT_HOST_MAPPED, EXACT_HOST_STAGED, EXACT_RESIDENT = 0, 1, 2
+EXACT_HOST_MAPPED, EXACT_HOST_STAGED, EXACT_RESIDENT, EXACT_HOST_CACHED = 0, 1, 2, 3
 
 
 class PsbError(RuntimeError):

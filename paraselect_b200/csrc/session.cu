@@ -184,7 +184,7 @@ struct psb_session {
     int list_begin = 0, list_end = 0;
     long long row_base = 0, shard_rows = 0;
     // device copies
-    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta;
+    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta, exact_cache;
     bool striped = false;          // shard holds a slice of every list (options.list_global_begin)
     // exact rows
     int exact_elem = 0;            // 4 = fp32, 1 = u8, 0 = rerank disabled
@@ -547,7 +547,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     psb_options opt{};
     if (options) opt = *options;
     if (opt.max_batch <= 0) opt.max_batch = 10000;
-    if (opt.exact_mode < 0 || opt.exact_mode > PSB_EXACT_RESIDENT) return fail(PSB_INVALID_ARGUMENT, "unknown exact_mode");
+    if (opt.exact_mode < 0 || opt.exact_mode > PSB_EXACT_HOST_CACHED) return fail(PSB_INVALID_ARGUMENT, "unknown exact_mode");
     const int nlist = index->lists.nlist;
     int lb = opt.list_begin, le = opt.list_end;
     if (lb == 0 && le == 0) le = nlist;
@@ -625,6 +625,19 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
         const size_t bytes = (size_t)E.count * E.dim * s->exact_elem;
         if (opt.exact_mode == PSB_EXACT_RESIDENT) {
             s->exact_dev = s->exact_host;
+        } else if (opt.exact_mode == PSB_EXACT_HOST_CACHED && bytes > 0) {
+            // the session's own copy of the rows in device memory (a B200 holds 180 GB: C4's 38.4 GB of rows fit beside the index)
+            size_t free_b = 0, total_b = 0;
+            PSB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+            if (bytes + ((size_t)8 << 30) > free_b)
+                return fail(PSB_OUT_OF_MEMORY, "the exact rows do not fit in device memory beside the workspaces; use a host mode");
+            PSB_TRY(s->exact_cache.reserve(bytes));
+            const size_t chunk = (size_t)1 << 30;
+            for (size_t off = 0; off < bytes; off += chunk)
+                PSB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(s->exact_cache.p) + off,
+                                         static_cast<const unsigned char*>(s->exact_host) + off, std::min(chunk, bytes - off),
+                                         cudaMemcpyHostToDevice, st));
+            s->exact_dev = s->exact_cache.p;
         } else if (opt.exact_mode == PSB_EXACT_HOST_MAPPED && bytes > 0) {
             cudaError_t e = cudaHostRegister(const_cast<void*>(s->exact_host), bytes, cudaHostRegisterMapped | cudaHostRegisterReadOnly);
             if (e == cudaErrorHostMemoryAlreadyRegistered) { cudaGetLastError(); e = cudaSuccess; }

@@ -251,7 +251,8 @@ def bench_main(args, cfg, rank, world, local_rank):
         # CTA cannot share an SM with a scan CTA, so the scan's persistent grid leaves a few SMs free for it.
         reserve = int(os.environ.get("PSB_RESERVE_SMS", "8"))
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           list_global_begin=gb, reserve_sms=reserve)
+                           list_global_begin=gb, reserve_sms=reserve,
+                           exact_mode=api.EXACT_HOST_CACHED if getattr(args, "exact_mode", "") == "cached" else api.EXACT_HOST_MAPPED)
         width = min(R, n) if R > topk else topk
         search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
                                rerank=R > topk, parts=int(os.environ.get("PSB_PARTS", "4")) if nq >= 2048 else 1)
@@ -322,7 +323,7 @@ def bench_main(args, cfg, rank, world, local_rank):
             unit="queries/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
             higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
             config=dict(workload=args.workload, desc=cfg["desc"], rows=n, dim=dim, nlist=nlist, M=M, batch=nq, nprobe=nprobe,
-                        topk=topk, n_rerank=R, exact_rows="host-mapped fp32", sharding="every list striped over %d ranks" % world,
+                        topk=topk, n_rerank=R, exact_rows=("device-cached fp32" if getattr(args, "exact_mode", "") == "cached" else "host-mapped fp32"), sharding="every list striped over %d ranks" % world,
                         l2="inputs larger than L2 (codes %.2f GB per rank)" % (index["codes"].nbytes / 1e9)),
             e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
                      h2d_bytes_per_step=int(nq * dim * 4), d2h_bytes_per_step=int(nq * topk * 12),

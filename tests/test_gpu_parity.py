@@ -485,3 +485,15 @@ def test_u8_table_quantiser_matches_checker(psb, M, dim, residual):
         assert np.array_equal(q8[i].cpu().numpy(), oq8.reshape(M, 256))
         assert np.array_equal(scales[i].cpu().numpy(), osc)
         assert lo[i].item() == olo and infl[i].item() == oinf
+
+
+def test_device_cached_exact_rows_equal_host_rows(psb):
+    """PSB_EXACT_HOST_CACHED: the session's own device copy of the caller's host rows gives the same results."""
+    ix = synth.make_index(30000, 64, 32, 16, seed=91, zipf=True)
+    q = synth.make_queries(ix, 2300, seed=92, weights=synth.zipf_weights(32))
+    with psb.Session(ix, n_rerank=100) as s:
+        want = s.search(q, 8, 10, batch_size=2300)
+    with psb.Session(ix, n_rerank=100, exact_mode=psb.EXACT_HOST_CACHED) as s:
+        got = s.search(q, 8, 10, batch_size=2300)
+    assert np.array_equal(got["indices"], want["indices"])
+    assert np.array_equal(got["distances"], want["distances"])
