@@ -270,6 +270,8 @@ def main():
                          "when a batch gathers at least 2 GB (the scan is then long enough to hide the host gather), else mapped; "
                          "cached = the session copies the rows into device memory once (not the host-resident configuration the "
                          "headline metric names: an extra data point)")
+    ap.add_argument("--reserve-sms", type=int, default=8, help="N > 1: SMs the scan's persistent grid leaves to the collectives")
+    ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
     args = ap.parse_args()
     claim_stdout()
 
@@ -305,8 +307,7 @@ def main():
     if args.impl == "ours" and world > 1 and args.workload in ("c3", "c5"):
         raise SystemExit("workloads c3 and c5 are single-GPU lines")
     if args.impl == "ours" and world > 1:
-        from paraselect_b200 import multi
-        return multi.bench_main(args, cfg, rank, world, local_rank)
+        return multi_gpu_main(args, cfg, rank, world, local_rank)
 
     if args.workload == "c3":
         return coarse_only(args, cfg, torch, api, device)
@@ -408,7 +409,7 @@ def main():
                     # by the rows this launch scans - each code row is loaded once per group of 8 visiting queries
                     traffic=int(2.62 * S) if cfg["M"] == 48 else None,
                     traffic_source="ncu dram__bytes_read+write of a cut-down capture (8M rows, 2,000 queries), scaled by rows scanned",
-                    lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / 148 / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
+                    lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / torch.cuda.get_device_properties(device).multi_processor_count / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
 
     # CPU baseline + parity on a bounded sample of the same batch
     cores = os.cpu_count() or 1
@@ -453,6 +454,178 @@ def main():
     emit(line)
     sess.close()
     return 0
+
+
+def multi_gpu_main(args, cfg, rank, world, local_rank):
+    """`bench.py --gpus N` for N > 1 (one process per GPU under torchrun)."""
+    import torch
+    import torch.distributed as dist
+    from paraselect_b200 import api, multi
+    from paraselect_b200.multi import ShardedSearch, SessionEngine, stripe_layout
+
+    device = local_rank
+    n, dim, nlist, M = cfg["n"], cfg["dim"], cfg["nlist"], cfg["M"]
+    nq, nprobe, topk, R = cfg["nq"], cfg["nprobe"], cfg["topk"], cfg["n_rerank"]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        w, offsets = populations(n, nlist, cfg["zipf"])
+        gb, loff = stripe_layout(offsets, rank, world)
+        t0 = time.time()
+        index, centres = build_stripe(cfg, torch, api, device, offsets, gb, loff)
+        log("rank 0 stripe built in %.1fs (%d rows)" % (time.time() - t0, index["codes"].shape[0]))
+        dq = make_queries(cfg, torch, api, centres, w, device)
+        q_pinned = torch.empty((nq, dim), dtype=torch.float32).pin_memory()
+        q_pinned.copy_(dq)
+        torch.cuda.synchronize()
+        # The exchange half of a sub-batch (collectives, PCIe rerank) runs beside the next sub-batch's scan.  A collective's
+        # CTA cannot share an SM with a scan CTA, so the scan's persistent grid leaves a few SMs free for it.
+        reserve = args.reserve_sms
+        sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
+                           list_global_begin=gb, reserve_sms=reserve,
+                           exact_mode=api.EXACT_HOST_CACHED if getattr(args, "exact_mode", "") == "cached" else api.EXACT_HOST_MAPPED)
+        width = min(R, n) if R > topk else topk
+        search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
+                               rerank=R > topk, parts=args.parts if nq >= 2048 else 1)
+        search.step(dq, profile=True)  # first step in one piece: every workspace reaches its final size before streams overlap
+        for _ in range(max(args.warmup, 3)):
+            search.step(dq)
+        torch.cuda.synchronize()
+        sess.counters(reset=True)
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+
+        def timed(fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(args.steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device="cuda")
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item())
+
+        ms_dev = timed(lambda: search.step(dq))
+        c = sess.counters(reset=True)
+        out_ids = torch.empty((nq, topk), dtype=torch.int64).pin_memory()
+        out_dist = torch.empty((nq, topk), dtype=torch.float32).pin_memory()
+        dq2 = torch.empty_like(dq)
+
+        def e2e_step():
+            dq2.copy_(q_pinned, non_blocking=True)
+            ids, dd = search.step(dq2)
+            out_ids.copy_(ids, non_blocking=True)
+            out_dist.copy_(dd, non_blocking=True)
+            stream.synchronize()
+
+        e2e_step()
+        ms_e2e = timed(e2e_step)
+        search.step(dq, profile=True)
+        torch.cuda.synchronize()
+        stage_ms = search.stage_times()
+        clocks = sampler.stop()
+        torch.cuda.synchronize()
+        # totals over ranks
+        tot = torch.tensor([float(c["pq_scanned_codes"]), float(c["scan_kernel_ms"]), float(c["scan_kernel_launches"]),
+                            float(c["kernel_launches"]), float(c["fallback_queries"])], dtype=torch.float64, device="cuda")
+        mx = tot.clone()
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        torch.cuda.synchronize()  # the collectives run on this block's stream: finish them before the host reads
+        tot, mx = tot.cpu(), mx.cpu()
+        ids_np = out_ids.numpy()
+        checksum = int(np.bitwise_xor.reduce((ids_np.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel()) & np.uint64((1 << 62) - 1))
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        S = tot[0].item() / max(1, args.steps)                      # rows scanned per step, all ranks
+        launches_per_step = max(1.0, mx[2].item()) / max(1, args.steps)  # one scan launch per sub-batch
+        scan_ms = mx[1].item() / max(1.0, mx[2].item())             # slowest rank's scan kernel, per launch
+        S = S / launches_per_step                                   # rows per launch, all ranks
+        achieved = S * M / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+        line = dict(
+            metric="QPS (IVF-PQ search, recall@k equal to the reference CPU path)", value=round(nq / (ms_dev * 1e-3), 1),
+            unit="queries/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
+            higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+            config=dict(workload=args.workload, desc=cfg["desc"], rows=n, dim=dim, nlist=nlist, M=M, batch=nq, nprobe=nprobe,
+                        topk=topk, n_rerank=R, exact_rows=("device-cached fp32" if getattr(args, "exact_mode", "") == "cached" else "host-mapped fp32"), sharding="every list striped over %d ranks" % world,
+                        l2="inputs larger than L2 (codes %.2f GB per rank)" % (index["codes"].nbytes / 1e9)),
+            e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
+                     h2d_bytes_per_step=int(nq * dim * 4), d2h_bytes_per_step=int(nq * topk * 12),
+                     pcie_gather_bytes_per_step=int(nq * width * dim * 4) if R > topk else 0),
+            gpu_launches=int(tot[3].item()),
+            roofline=dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak * world, unit="GB/s",
+                          frac=round(achieved / (peak * world), 4), peak_source="measured" if peaks else "fallback",
+                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3), launches_per_step=launches_per_step,
+                          traffic=int(2.62 * S / world) if M == 48 else None,  # 2.62 DRAM bytes per scanned code row (ncu, cut-down case)
+                          note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
+            counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
+            stages_ms_rank0=stage_ms, result_checksum=checksum, clocks=clocks)
+        emit(line)
+    sess.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+def build_stripe(cfg, torch, api, device, offsets, gb, loff):
+    """Generates the whole synthetic base chunk by chunk on this rank's GPU and keeps the rows of its stripe."""
+    n, dim, nlist, M, seed = cfg["n"], cfg["dim"], cfg["nlist"], cfg["M"], cfg["seed"]
+    d_off = torch.from_numpy(offsets).cuda()
+    centres = torch.empty((nlist, dim), dtype=torch.float32, device="cuda")
+    api.gen_normal(seed * 1000 + 1, 0, nlist * dim, 1.0, centres, device=device)
+    blocks, per = 64, min(16384, max(1, n // 64))
+    sample = torch.empty((blocks * per, dim), dtype=torch.float32, device="cuda")
+    for b in range(blocks):
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, (n // blocks) * b, per,
+                             sample[b * per:], device=device)
+    codebook = torch.empty((M, 256, dim // M), dtype=torch.float32, device="cuda")
+    api.pq_train(sample, blocks * per, dim, M, 256, 8, seed * 1000 + 3, codebook, device=device)
+    del sample
+    rows = int(loff[-1])
+    vectors = np.empty((rows, dim), np.float32)
+    codes = np.empty((rows, M), np.uint8)
+    ids = np.empty(rows, np.int64)
+    a = coprime_multiplier(n)
+    d_gb = torch.from_numpy(gb).cuda()
+    d_len = torch.from_numpy(loff[1:] - loff[:-1]).cuda()
+    chunk = 2_000_000
+    buf = torch.empty((chunk, dim), dtype=torch.float32, device="cuda")
+    cbuf = torch.empty((chunk, M), dtype=torch.uint8, device="cuda")
+    at = 0
+    for r0 in range(0, n, chunk):
+        m = min(chunk, n - r0)
+        g = torch.arange(r0, r0 + m, dtype=torch.int64, device="cuda")
+        l = torch.searchsorted(d_gb, g, right=True) - 1
+        lc = l.clamp(min=0)
+        own = (l >= 0) & (g < d_gb[lc] + d_len[lc])
+        sel = torch.nonzero(own).squeeze(1)
+        k = int(sel.numel())
+        if k == 0:
+            continue
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], seed * 1000 + 2, r0, m, buf, device=device)
+        torch.cuda.synchronize()  # the generator runs on the default stream, torch on its own
+        mine = buf[:m].index_select(0, sel)
+        torch.cuda.synchronize()
+        api.pq_encode(mine, k, dim, codebook, M, 256, cbuf, device=device)
+        torch.cuda.synchronize()
+        torch.from_numpy(vectors[at:at + k]).copy_(mine)
+        torch.from_numpy(codes[at:at + k]).copy_(cbuf[:k])
+        ids[at:at + k] = ((sel.cpu().numpy() + r0) * a + 12345) % n
+        at += k
+    assert at == rows, (at, rows)
+    index = dict(centroids=centres.cpu().numpy(), offsets=loff, reordered_ids=ids, codes=codes,
+                 codebook=codebook.cpu().numpy(), vectors=vectors, nlist=nlist)
+    return index, centres
+
+
 
 
 def training(args, cfg, torch, api, device):
@@ -699,7 +872,12 @@ def coarse_only(args, cfg, torch, api, device):
 def reference_arm(args, cfg, index, q_host, gt):
     """Times the reference's own CPU implementation on bounded samples of the batch (rank 0 only)."""
     cores = os.cpu_count() or 1
-    ns = args.cpu_sample or 32
+    ns = args.cpu_sample
+    if not ns:
+        # The fine stage parallelises over queries: give every host thread at least 8 of them, and grow the sample until a
+        # step takes several seconds (the sizing of this library's own cpu_baseline leg), so the host cores are kept busy.
+        _, dt0, _ = cpu_reference_run(index, q_host, cfg, 16, cores)
+        ns = int(min(512, cfg["nq"], max(8 * cores, 16 * 8.0 / max(dt0, 1e-3))))
     times = []
     for i in range(args.warmup + args.steps):
         lo = (i * ns) % max(1, cfg["nq"] - ns + 1)

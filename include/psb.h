@@ -146,7 +146,13 @@ typedef struct psb_options {
     int reserve_sms;    /* SMs the ADC scan's persistent grid leaves free (0..64).  A multi-GPU caller that runs NCCL
                            collectives on a second stream while the scan is in flight sets a few: a collective's CTA
                            cannot share an SM with a scan CTA and would otherwise wait for the scan kernel to end. */
-    int reserved[2];
+    /* Tuning, all optional (0 = the default): */
+    float seed_sigma;   /* margin of the sampled admission cutoff in standard deviations (default 4; accepted 2..10).  Results do
+                           not depend on it: a too-tight cutoff only sends more queries to the exact fallback. */
+    int pipeline_parts; /* sub-batches per batch of the overlapped pipeline (default 4; accepted 2..32) */
+    int even_cuts;      /* 1 = equal sub-batches also with the staged transport (default: a short last sub-batch) */
+    int gather_ctas;    /* CTAs of the PCIe row-gather kernel when it runs beside a scan (default 32) */
+    int reserved[4];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's

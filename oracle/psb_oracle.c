@@ -5,8 +5,7 @@
  * the checker by the tests, the smoke entry and the bench's cpu_baseline leg.
  * The shipped library never links or calls anything in this file.
  *
- * Parity status: PINNED.  Every function here is checked (tests/test_oracle_vs_ref.py,
- * tests/test_golden.py) against the reference's own CPU code compiled in place
+ * Parity status: PINNED.  Every function here is checked (tests/test_oracle.py) against the reference's own CPU code compiled in place
  * (oracle/_ref, built by oracle/Makefile) and against the known-answer
  * constructions of the reference's unit tests.
  *

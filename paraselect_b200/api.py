@@ -71,7 +71,9 @@ class Options(C.Structure):
     _fields_ = [("device", C.c_int), ("n_rerank", C.c_int), ("exact_mode", C.c_int), ("max_batch", C.c_int),
                 ("list_begin", C.c_int), ("list_end", C.c_int), ("stream", C.c_void_p), ("list_global_begin", C.c_void_p),
                 ("coarse_mode", C.c_int),
-                ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserve_sms", C.c_int), ("reserved", C.c_int * 2)]
+                ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserve_sms", C.c_int),
+                ("seed_sigma", C.c_float), ("pipeline_parts", C.c_int), ("even_cuts", C.c_int), ("gather_ctas", C.c_int),
+                ("reserved", C.c_int * 4)]
 
 
 class Stats(C.Structure):
@@ -141,7 +143,8 @@ class Session:
     """
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
-                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0):
+                 list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0,
+                 seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -174,7 +177,9 @@ class Session:
         self._keep.append(gb)
         opt = Options(list_global_begin=_p(gb), device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
-                      time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)), reserve_sms=reserve_sms)
+                      time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)), reserve_sms=reserve_sms,
+                      seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(bool(even_cuts)),
+                      gather_ctas=int(gather_ctas))
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 

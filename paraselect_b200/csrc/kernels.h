@@ -97,6 +97,9 @@ struct ScanWorkspace {
     int scan_mode = 0;           // 0 = half pre-filter when it fits, 1 = fp32 scan
     uint64_t* fallback_partial = nullptr;  // [fallback_partial_bytes(stage1_k)]: partial top lists of the split exact fallback
     bool half_tables_ready = false;  // lut_h / lut_scale already hold this call's tables (launch_build_tables_residual)
+    float seed_sigma = 0.f;      // margin of the sampled cutoff in standard deviations (0 = default)
+    int cap_queries = 0;         // queries the per-query buffers above hold (launch_scan refuses more)
+    long long cap_tables = 0;    // tables lut_h / lut_scale hold
     int reserve_ctas = 0;        // CTAs left out of the scan's persistent grid, so that kernels of another stream that
                                  // cannot share an SM with a scan CTA (a collective's) still find a free SM
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;  // optional: bracket the scan kernel
@@ -151,10 +154,11 @@ struct RowMap {
     long long count = 0;
 };
 // Copies the candidate rows held here (fp32 or u8, elem_bytes 4 or 1) from src (device-visible: mapped host or
-// device) to stage [nq][candidate_count][dim].  Candidates are global rows.
+// device) to stage [nq][candidate_count][dim].  Candidates are global rows.  compact_ctas > 0: the kernel runs beside a scan
+// on another stream and is confined to that many fat CTAs.
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
-                              void* d_stage, cudaStream_t s, bool compact = false);
+                              void* d_stage, cudaStream_t s, int sm_count, int compact_ctas = 0);
 // d_out_dist [nq][candidate_count]: exact distance of each staged candidate, +inf for rows not held here.
 psb_status launch_rerank_score(const void* d_stage, const RowMap& mp, int dim, int elem_bytes, const void* d_queries,
                                const int* d_candidates, int nq, int candidate_count, int candidate_stride,

@@ -17,7 +17,7 @@
 // Arithmetic matches the CPU path bit for bit: table entries are the sequential non-fused fp32 sum of
 // (q-c)^2 and ADC distances are the sequential fp32 sum over m = 0..M-1
 // (reference: src/search/ivfpq/stage/ivfpq_fine_cpu_lut.cpp:51-63,76-80).
-#include <cstdlib>
+#include <string>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -1108,11 +1108,8 @@ psb_status run_scan_m(const ScanArgs& a, int group, int sm_count, cudaStream_t s
     }
 }
 
-// Safety margin of the sampled cutoff in standard deviations (PSB_SEED_SIGMA overrides it; tuning knob, read once).
-float seed_margin_sigma() {
-    static const float v = [] { const char* e = std::getenv("PSB_SEED_SIGMA"); const float x = e ? (float)std::atof(e) : 0.f; return x >= 2.f && x <= 10.f ? x : 4.0f; }();
-    return v;
-}
+// Safety margin of the sampled cutoff in standard deviations (ScanWorkspace::seed_sigma; 4 unless the caller set 2..10).
+float seed_margin_sigma(const ScanWorkspace& ws) { return ws.seed_sigma >= 2.f && ws.seed_sigma <= 10.f ? ws.seed_sigma : 4.0f; }
 
 template <int M>
 psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq, const int* d_probes,
@@ -1122,7 +1119,7 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
                                                          stage1_k, ws.pool_cap, ws.thr, ix.residual ? 1 : 0,
-                                                         tree_order(ix) ? 1 : 0, seed_margin_sigma(), seed_margin_sigma() - 2.0f);
+                                                         tree_order(ix) ? 1 : 0, seed_margin_sigma(ws), seed_margin_sigma(ws) - 2.0f);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -1236,6 +1233,9 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     const long long tables = ix.residual ? (long long)nq * nprobe : nq;
     if (tables > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
     const bool use_half = ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(ix.m, ix.k);
+    if (nq > ws.cap_queries || (use_half && tables > ws.cap_tables))
+        return fail(PSB_INTERNAL, "scan workspace holds " + std::to_string(ws.cap_queries) + " queries / " + std::to_string(ws.cap_tables) +
+                                      " tables, the call needs " + std::to_string(nq) + " / " + std::to_string(tables));
     const int group = use_half ? kHalfGroup : pick_group(ix.m, ix.k);
     // schedule
     PSB_CUDA(cudaMemsetAsync(ws.vis_count, 0, sizeof(int) * (size_t)ix.nlist, s));

@@ -267,16 +267,15 @@ psb_status prefer_max_shared(F kernel) {
 
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
-                              void* d_stage, cudaStream_t s, bool compact) {
+                              void* d_stage, cudaStream_t s, int sm_count, int compact_ctas) {
     if (nq <= 0) return PSB_OK;
     const long long total = (long long)nq * candidate_count;
     PSB_TRY(prefer_max_shared(k_gather_rows));
-    if (compact) {
+    if (compact_ctas > 0) {
         // Beside a scan kernel on the other stream of the overlapped pipeline: few, fat CTAs.  32 CTAs of 512 threads keep
         // ~200 KB of row reads in flight - more than the PCIe bandwidth-delay product - while touching only 32 SMs, so the
         // scan keeps most SMs to itself (its dynamic work queue shifts work away from the shared ones).
-        // PSB_GATHER_CTAS overrides the CTA count (tuning knob, read once).
-        static const int cap = [] { const char* e = std::getenv("PSB_GATHER_CTAS"); const int v = e ? std::atoi(e) : 0; return v > 0 ? v : 32; }();
+        const int cap = compact_ctas;
         long long blocks = (total * 32 + 511) / 512;
         if (blocks > cap) blocks = cap;
         k_gather_rows<<<(unsigned)blocks, 512, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
@@ -284,7 +283,7 @@ psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int el
                                                        static_cast<unsigned char*>(d_stage));
     } else {
         long long blocks = (total * 32 + 255) / 256;
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > (long long)sm_count * 8) blocks = (long long)sm_count * 8;
         k_gather_rows<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
                                                        d_candidates, nq, candidate_count, candidate_stride, d_counts,
                                                        static_cast<unsigned char*>(d_stage));

@@ -3,7 +3,6 @@
 #include "common.cuh"
 #include "kernels.h"
 
-#include <cstdlib>
 #include <algorithm>
 #include <atomic>
 #include <climits>
@@ -205,7 +204,8 @@ struct psb_session {
     // workspaces
     DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
         pool_cnt, pool, fail_list, fallback_partial, scalars, lut_h, lut_scale, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
-    int ws_batch = 0, ws_nprobe = 0, ws_stage1 = 0, ws_topk = 0;
+    int ws_scan_queries = 0;        // queries the scan workspace (visitors, pools, cutoffs) currently holds
+    long long ws_scan_tables = 0;   // tables the fp16 table buffer currently holds
     int pool_cap = 0;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> scan_events;  // pending (options.time_kernels)
     double scan_ms_total = 0.0;
@@ -213,6 +213,30 @@ struct psb_session {
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> gemm_events;  // pending coarse GEMM passes (options.time_kernels)
     double gemm_ms_total = 0.0;
     long long gemm_launches_total = 0;
+
+    psb_session() = default;
+    psb_session(const psb_session&) = delete;
+    psb_session& operator=(const psb_session&) = delete;
+    // Releases what the session owns; runs for a partially built session too (every failure path of psb_session_create),
+    // so the caller's rows never stay pinned after an error.
+    ~psb_session() {
+        cudaSetDevice(device);
+        if (stream) cudaStreamSynchronize(stream);
+        if (home_stream) {  // a redirected session: drain and return to the stream it was created with
+            cudaStreamSynchronize(home_stream);
+            stream = home_stream;
+        }
+        collect_scan_events();
+        if (registered) cudaHostUnregister(const_cast<void*>(exact_host));
+        for (int i = 0; i < 2; ++i) {
+            if (pinned[i]) cudaFreeHost(pinned[i]);
+            if (pinned_ev[i]) cudaEventDestroy(pinned_ev[i]);
+        }
+        if (h_cand_pinned) cudaFreeHost(h_cand_pinned);
+        if (aux_stream) { cudaStreamSynchronize(aux_stream); cudaStreamDestroy(aux_stream); }
+        if (own_stream && stream) cudaStreamDestroy(stream);
+        cudaGetLastError();
+    }
 
     ScanIndex scan_index() const {
         ScanIndex ix;
@@ -246,6 +270,8 @@ struct psb_session {
         w.pool_cap = pool_cap;
         w.lut_h = lut_h.p; w.lut_scale = lut_scale.as<float>(); w.scan_mode = opt.scan_mode;
         w.reserve_ctas = opt.reserve_sms;
+        w.seed_sigma = opt.seed_sigma;
+        w.cap_queries = ws_scan_queries; w.cap_tables = ws_scan_tables;
         return w;
     }
     // Scan workspace with a fresh event pair when kernel timing is on.
@@ -300,7 +326,7 @@ size_t table_count(const psb_session* s, int nq, int nprobe) {
 // Queries per sub-batch of the pipeline: a quarter of the batch when the rerank overlaps the scan, and in residual mode
 // few enough that the per-(query, probe) tables stay below ~16 GiB.
 int sub_batch_rows(const psb_session* s, int n, int nprobe, bool overlap) {
-    static const int pipeline_parts = [] { const char* e = std::getenv("PSB_PIPELINE_PARTS"); const int v = e ? std::atoi(e) : 0; return v >= 2 && v <= 32 ? v : 4; }();  // tuning knob, read once
+    const int pipeline_parts = s->opt.pipeline_parts >= 2 && s->opt.pipeline_parts <= 32 ? s->opt.pipeline_parts : 4;
     int parts = overlap ? pipeline_parts : 1;
     if (s->opt.adc_mode == 1) {
         const double bytes = (double)n * nprobe * s->m * s->k * sizeof(float);
@@ -314,8 +340,10 @@ bool overlap_enabled(const psb_session* s, int n, bool rerank) {
     return rerank && s->opt.exact_mode != PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
 }
 
+// Grows the scan workspace to hold nq queries (never shrinks; a growing buffer is freed first, which waits for the device).
 psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
     const size_t tables = table_count(s, nq, nprobe);
+    s->ws_scan_queries = 0; s->ws_scan_tables = 0;  // set again below once every buffer has its size
     PSB_TRY(s->vis_count.reserve(sizeof(int) * (size_t)s->nlist));
     PSB_TRY(s->vis_off.reserve(sizeof(int) * ((size_t)s->nlist + 1)));
     PSB_TRY(s->vis_cursor.reserve(sizeof(int) * (size_t)s->nlist));
@@ -337,6 +365,14 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
         PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 8));
         PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(unsigned long long) * 8, s->stream));
     }
+    // what the buffers hold now (reserve() keeps a larger buffer from an earlier call)
+    s->ws_scan_queries = (int)std::min<size_t>({s->q_rows.bytes / sizeof(long long), s->thr.bytes / sizeof(float),
+                                                s->pool_cnt.bytes / sizeof(int), s->fail_list.bytes / sizeof(int),
+                                                s->pool.bytes / (sizeof(uint64_t) * (size_t)cap),
+                                                s->visitors.bytes / (sizeof(int) * (size_t)nprobe), (size_t)INT_MAX});
+    s->ws_scan_tables = s->opt.scan_mode != 1 ? (long long)std::min(s->lut_h.bytes / (sizeof(unsigned short) * (size_t)s->m * s->k),
+                                                                    s->lut_scale.bytes / sizeof(float))
+                                              : (long long)tables;
     return PSB_OK;
 }
 
@@ -428,7 +464,7 @@ psb_status validate_params(const psb_session* s, const psb_query_batch_view* qv,
     if (p->nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
     if (p->topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "topk above 2048 is not supported");
     if (qv->count > 0 && (!out->indices || !out->distances)) return fail(PSB_INVALID_ARGUMENT, "output buffers are null");
-    if (s->exact_elem == 1 && s->opt.n_rerank > p->topk && !qv->u8) return fail(PSB_INVALID_ARGUMENT, "u8 rerank needs u8 queries");
+    if (qv->count > 0 && s->exact_elem == 1 && rerank_enabled(s, p->topk) && !qv->u8) return fail(PSB_INVALID_ARGUMENT, "u8 rerank needs u8 queries");
     return PSB_OK;
 }
 
@@ -509,7 +545,9 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
         PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
-                                   s->stage.p, s->stream, s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream)));
+                                   s->stage.p, s->stream, s->sm_count,
+                                   (s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream))
+                                       ? (s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 32) : 0));
     }
     float* score = d_score;
     if (!score) {
@@ -564,6 +602,9 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if (opt.n_rerank > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "n_rerank above 2048 is not supported");
     if (opt.adc_mode != 0 && opt.adc_mode != 1) return fail(PSB_INVALID_ARGUMENT, "unknown adc_mode");
     if (opt.reserve_sms < 0 || opt.reserve_sms > 64) return fail(PSB_INVALID_ARGUMENT, "reserve_sms must be in 0..64");
+    if (opt.seed_sigma != 0.f && !(opt.seed_sigma >= 2.f && opt.seed_sigma <= 10.f)) return fail(PSB_INVALID_ARGUMENT, "seed_sigma must be 0 or in 2..10");
+    if (opt.pipeline_parts != 0 && (opt.pipeline_parts < 2 || opt.pipeline_parts > 32)) return fail(PSB_INVALID_ARGUMENT, "pipeline_parts must be 0 or in 2..32");
+    if (opt.gather_ctas < 0 || opt.gather_ctas > 1024) return fail(PSB_INVALID_ARGUMENT, "gather_ctas must be in 0..1024");
     if (opt.adc_mode == 1 && !index->exact.fp32 && !index->exact.u8)
         return fail(PSB_INVALID_ARGUMENT, "residual mode always reranks: exact rows are required");
     cudaDeviceProp prop;
@@ -662,24 +703,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
 }
 
 psb_status psb_session_destroy(psb_session* s) {
-    if (!s) return PSB_OK;
-    cudaSetDevice(s->device);
-    cudaStreamSynchronize(s->stream);
-    if (s->home_stream) {  // a redirected session: drain and return to the stream it was created with
-        cudaStreamSynchronize(s->home_stream);
-        s->stream = s->home_stream;
-    }
-    s->collect_scan_events();
-    if (s->registered) cudaHostUnregister(const_cast<void*>(s->exact_host));
-    for (int i = 0; i < 2; ++i) {
-        if (s->pinned[i]) cudaFreeHost(s->pinned[i]);
-        if (s->pinned_ev[i]) cudaEventDestroy(s->pinned_ev[i]);
-    }
-    if (s->h_cand_pinned) cudaFreeHost(s->h_cand_pinned);
-    if (s->aux_stream) { cudaStreamSynchronize(s->aux_stream); cudaStreamDestroy(s->aux_stream); }
-    if (s->own_stream) cudaStreamDestroy(s->stream);
-    delete s;
-    cudaGetLastError();
+    delete s;  // the destructor releases everything the session owns (also a partially built one)
     return PSB_OK;
 }
 
@@ -833,7 +857,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     // exposed - so the last sub-batch is the small one (32/32/26/10 %).  (With the kernel gather, which slows the scan it
     // runs beside, such cuts measured no better than equal ones.)
     std::vector<int> cuts;
-    static const bool even_cuts = std::getenv("PSB_EVEN_CUTS") != nullptr;  // tuning knob, read once
+    const bool even_cuts = s->opt.even_cuts != 0;
     if (staged_overlap && !residual && sb * 4 >= n && n >= 4096 && !even_cuts) {
         cuts = {0, (int)(0.32 * n), (int)(0.64 * n), (int)(0.90 * n), n};
     } else {
@@ -842,15 +866,22 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     }
     int sb_max = 0;
     for (size_t ci = 0; ci + 1 < cuts.size(); ++ci) sb_max = std::max(sb_max, cuts[ci + 1] - cuts[ci]);
+    // The sub-batch size depends on this batch's own n (a short tail batch may run in one piece where the full batch ran
+    // in four), so the tables and the scan workspace are sized here, for the largest sub-batch of THIS batch.
+    PSB_TRY(s->lut.reserve(sizeof(float) * table_count(s, sb_max, nprobe) * s->m * s->k));
+    PSB_TRY(ensure_scan_ws(s, sb_max, nprobe, stage1_k));
     if ((overlap || staged_overlap) && !s->aux_stream) {
         int lo = 0, hi = 0;  // lowest priority: the scan's CTAs get the SMs first, the transfer fills the gaps
         PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         PSB_CUDA(cudaStreamCreateWithPriority(&s->aux_stream, cudaStreamNonBlocking, lo));
     }
     cudaStream_t sx = (overlap || staged_overlap) ? s->aux_stream : st;
-    std::vector<cudaEvent_t> deps;
+    struct EventList {  // destroyed on every way out of this function (an event may be destroyed once the waits on it are queued)
+        std::vector<cudaEvent_t> v;
+        ~EventList() { for (auto e : v) cudaEventDestroy(e); }
+        void push_back(cudaEvent_t e) { v.push_back(e); }
+    } deps;
     EventTimer tm_s, tm_x;
-    auto cleanup = [&]() { for (auto e : deps) cudaEventDestroy(e); };
     if (overlap || staged_overlap) {  // the second stream starts after everything already queued on the main stream
         cudaEvent_t e0;
         PSB_CUDA(cudaEventCreateWithFlags(&e0, cudaEventDisableTiming));
@@ -1004,9 +1035,6 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
             times->rerank += tm_x.ms(i, i + 1); times->map += tm_x.ms(i + 1, i + 2);
         }
     }
-    if (deps.size()) {  // events may only be destroyed once the work that waits on them has been submitted: it has
-        cleanup();
-    }
     return rc;
 }
 
@@ -1129,7 +1157,8 @@ psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* 
             if (h_candidate_counts[q] < 0 || h_candidate_counts[q] > candidate_count)
                 return fail(PSB_INVALID_ARGUMENT, "host rerank candidate count exceeds row width");
     if (candidate_count > kMaxRerankWidth || topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "rerank width above 4096 or topk above 2048");
-    PSB_TRY(check_device(device));
+    cudaDeviceProp prop;
+    PSB_TRY(check_device(device, &prop));
     const int elem = use_float ? 4 : 1;
     const int dim = storage->dim;
     const size_t base_bytes = (size_t)storage->count * dim * elem;
@@ -1153,7 +1182,7 @@ psb_status psb_rerank_host(const psb_host_storage_view* storage, const uint8_t* 
     DevBuf score;
     PSB_TRY(score.reserve(sizeof(float) * (size_t)batch_n * candidate_count));
     PSB_TRY(launch_gather_rows(base.p, mp, dim, elem, cand.as<int>(), batch_n, candidate_count, candidate_stride,
-                               d_counts, stage.p, st));
+                               d_counts, stage.p, st, prop.multiProcessorCount));
     PSB_TRY(launch_rerank_score(stage.p, mp, dim, elem, q.p, cand.as<int>(), batch_n, candidate_count, candidate_stride,
                                 d_counts, score.as<float>(), st));
     PSB_TRY(launch_topk_select(score.as<float>(), cand.as<int>(), batch_n, candidate_count, candidate_stride, d_counts,
@@ -1215,29 +1244,31 @@ psb_status psb_knn_exact(const float* d_queries, int nq, const float* d_base, in
     if (n > INT_MAX) return fail(PSB_UNSUPPORTED_SHAPE, "more than 2^31-1 base rows");
     PSB_TRY(check_device(device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // tiles of base rows, each at most 1 GiB of distances, then a merge of the per-tile winners
-    long long tile = std::max<long long>(4096, ((long long)1 << 28) / nq);
+    // tiles of base rows, each at most 1 GiB of distances, then a merge of the per-tile winners.  A last tile with fewer
+    // than k rows is folded into the tile before it, so every tile selects exactly k rows.
+    long long tile = std::max<long long>(std::max<long long>(4096, k), ((long long)1 << 28) / nq);
     tile = std::min<long long>(tile, n);
-    const int tiles = (int)((n + tile - 1) / tile);
+    std::vector<std::pair<long long, int>> spans;  // (first row, rows)
+    for (long long r0 = 0; r0 < n;) {
+        long long rows = std::min<long long>(tile, n - r0);
+        const long long rest = n - (r0 + rows);
+        if (rest > 0 && rest < k) rows += rest;
+        spans.emplace_back(r0, (int)rows);
+        r0 += rows;
+    }
+    const int tiles = (int)spans.size();
     if ((long long)tiles * k > 16384) return fail(PSB_UNSUPPORTED_SHAPE, "knn: too many tiles for the merge; pass fewer base rows per call");
     DevBuf dist, trows, tdist;
-    PSB_TRY(dist.reserve(sizeof(float) * (size_t)nq * tile));
+    PSB_TRY(dist.reserve(sizeof(float) * (size_t)nq * (size_t)(tile + k)));
     PSB_TRY(trows.reserve(sizeof(int) * (size_t)tiles * nq * k));
     PSB_TRY(tdist.reserve(sizeof(float) * (size_t)tiles * nq * k));
     for (int t = 0; t < tiles; ++t) {
-        const long long r0 = (long long)t * tile;
-        const int rows = (int)std::min<long long>(tile, n - r0);
+        const long long r0 = spans[(size_t)t].first;
+        const int rows = spans[(size_t)t].second;  // >= k: k <= n, and no span is shorter than k unless it is the only one
         PSB_TRY(launch_coarse_dist_exact(d_queries, nq, d_base + (size_t)r0 * dim, rows, dim, dist.as<float>(), st));
-        const int kk = std::min(k, rows);
-        if (kk < k) {
-            PSB_CUDA(cudaMemsetAsync(trows.as<int>() + (size_t)t * nq * k, 0xff, sizeof(int) * (size_t)nq * k, st));
-        }
-        // select kk per query into a [nq][k] slab (row stride k): run per-tile with k, rows >= k is the common case
-        if (kk == k) {
-            PSB_TRY(launch_select_rows(dist.as<float>(), nq, rows, k, trows.as<int>() + (size_t)t * nq * k,
-                                       tdist.as<float>() + (size_t)t * nq * k, st));
-            PSB_TRY(launch_offset_rows(trows.as<int>() + (size_t)t * nq * k, (long long)nq * k, (int)r0, st));
-        }
+        PSB_TRY(launch_select_rows(dist.as<float>(), nq, rows, k, trows.as<int>() + (size_t)t * nq * k,
+                                   tdist.as<float>() + (size_t)t * nq * k, st));
+        PSB_TRY(launch_offset_rows(trows.as<int>() + (size_t)t * nq * k, (long long)nq * k, (int)r0, st));
     }
     PSB_TRY(launch_merge(trows.as<int>(), tdist.as<float>(), tiles, nq, k, d_rows, d_dist, st));
     PSB_CUDA(cudaStreamSynchronize(st));
