@@ -136,8 +136,10 @@ typedef struct psb_options {
     int coarse_mode;    /* 0 = auto, 1 = exact SIMT kernel only, 2 = tensor-core filter + exact refinement */
     int time_kernels;   /* 1 = bracket the ADC scan kernel with CUDA events (read back by psb_session_counters) */
     int serial_pipeline;/* 1 = never overlap the rerank of one sub-batch with the scan of the next (diagnostics) */
-    int scan_mode;      /* 0 = auto (fp16 pre-filter scan with exact fp32 re-scoring when it fits), 1 = fp32 scan only;
-                           both give identical results */
+    int scan_mode;      /* which ADC scan runs; all give identical results.  0 = auto: the tensor-core pre-filter (bf16 tcgen05
+                           GEMM of visiting queries against code rows decoded on the fly, survivors re-scored exactly in fp32)
+                           when the shape fits, else the SIMT fp16 pre-filter scan, else the fp32 scan; 1 = fp32 SIMT scan only;
+                           2 = SIMT scans only; 3 = tensor-core pre-filter required (PSB_UNSUPPORTED_SHAPE when it cannot run) */
     int adc_mode;       /* PQAdcDistanceMode (src/search/kernels/fine/fine_search_strategy.h:21-24): 0 = Plain (codes
                            encode the row), 1 = Residual (codes encode row - centroid[list]).  Residual mode follows
                            cpu_fine_kernel_pq_resid_cpu_lut_timed (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:594-735):
@@ -152,7 +154,13 @@ typedef struct psb_options {
     int pipeline_parts; /* sub-batches per batch of the overlapped pipeline (default 4; accepted 2..32) */
     int even_cuts;      /* 1 = equal sub-batches also with the staged transport (default: a short last sub-batch) */
     int gather_ctas;    /* CTAs of the PCIe row-gather kernel when it runs beside a scan (default 32) */
-    int reserved[4];
+    int tc_min_visitors;/* lists with fewer visiting queries than this stay with the SIMT scan (default 1: none do) */
+    /* Test hooks of the time-out path of the tensor-core scan (leave 0): test_wait_limit = polls before a device-side wait
+       gives up; test_skip_mma = 1 makes the issuing warp skip its tcgen05.mma so that every waiting role runs into that limit
+       (nothing is left in flight; the kernel frees its tensor memory and returns; the call reports PSB_TIMEOUT). */
+    int test_wait_limit;
+    int test_skip_mma;
+    int reserved[1];
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -179,7 +187,8 @@ typedef struct psb_stats {
     long long coarse_gemm_launches; /* two per coarse call */
     int batches;
     int coarse_fallback_queries;    /* queries the tensor-core coarse filter handed to the exact per-query kernel */
-    int reserved[6];
+    long long prefilter_survivors;  /* (row, query) pairs the tensor-core scan filter let through to the exact re-scoring */
+    int reserved[4];
 } psb_stats;
 
 typedef struct psb_session psb_session;
@@ -279,6 +288,10 @@ psb_status psb_stage_quantize_lut_u8(psb_session* session, const float* d_lut, i
  * d_count [nq] (may be NULL). */
 psb_status psb_stage_scan(psb_session* session, const float* d_lut, int nq, const int* d_probes, int nprobe,
                           int stage1_k, int* d_rows, float* d_dist, int* d_count);
+/* The same stage with the queries at hand (d_queries [nq][dim]): lets the scan take the tensor-core pre-filter, which
+ * needs the query vectors besides their tables.  Same results as psb_stage_scan. */
+psb_status psb_stage_scan_queries(psb_session* session, const float* d_queries, const float* d_lut, int nq,
+                                  const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count);
 
 /* Exact rerank: drops candidates outside [0,count) and duplicates, recomputes fp32 squared L2 against the
  * exact rows and keeps the topk by (distance, row).  Replaces ivfpq_rerank_cpu -> ivf_rerank_host

@@ -73,7 +73,7 @@ class Options(C.Structure):
                 ("coarse_mode", C.c_int),
                 ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserve_sms", C.c_int),
                 ("seed_sigma", C.c_float), ("pipeline_parts", C.c_int), ("even_cuts", C.c_int), ("gather_ctas", C.c_int),
-                ("reserved", C.c_int * 4)]
+                ("tc_min_visitors", C.c_int), ("test_wait_limit", C.c_int), ("test_skip_mma", C.c_int), ("reserved", C.c_int * 1)]
 
 
 class Stats(C.Structure):
@@ -84,7 +84,8 @@ class Stats(C.Structure):
                 ("fallback_queries", C.c_longlong), ("h2d_bytes", C.c_longlong), ("d2h_bytes", C.c_longlong),
                 ("kernel_launches", C.c_longlong), ("scan_kernel_ms", C.c_double), ("scan_kernel_launches", C.c_longlong),
                 ("coarse_gemm_ms", C.c_double), ("coarse_gemm_launches", C.c_longlong),
-                ("batches", C.c_int), ("coarse_fallback_queries", C.c_int), ("reserved", C.c_int * 6)]
+                ("batches", C.c_int), ("coarse_fallback_queries", C.c_int), ("prefilter_survivors", C.c_longlong),
+                ("reserved", C.c_int * 4)]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
@@ -92,7 +93,7 @@ class Stats(C.Structure):
 
 EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
-    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_quantize_lut_u8", "psb_stage_scan",
+    "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_quantize_lut_u8", "psb_stage_scan", "psb_stage_scan_queries",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -144,7 +145,7 @@ class Session:
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
                  list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0,
-                 seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0):
+                 seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0, tc_min_visitors=0, test_wait_limit=0, test_skip_mma=0):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -179,7 +180,8 @@ class Session:
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
                       time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)), reserve_sms=reserve_sms,
                       seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(bool(even_cuts)),
-                      gather_ctas=int(gather_ctas))
+                      gather_ctas=int(gather_ctas), tc_min_visitors=int(tc_min_visitors), test_wait_limit=int(test_wait_limit),
+                      test_skip_mma=int(test_skip_mma))
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 
@@ -263,6 +265,12 @@ class Session:
         _check(lib().psb_stage_scan(self._h, C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)), nprobe, stage1_k,
                                     C.c_void_p(_p(d_rows)), C.c_void_p(_p(d_dist)) if d_dist is not None else None,
                                     C.c_void_p(_p(d_count)) if d_count is not None else None))
+
+    def stage_scan_queries(self, d_queries, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist=None, d_count=None):
+        _check(lib().psb_stage_scan_queries(self._h, C.c_void_p(_p(d_queries)), C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)),
+                                            nprobe, stage1_k, C.c_void_p(_p(d_rows)),
+                                            C.c_void_p(_p(d_dist)) if d_dist is not None else None,
+                                            C.c_void_p(_p(d_count)) if d_count is not None else None))
 
     def stage_rerank(self, d_queries, nq, d_cand, count, stride, d_counts, topk, d_out_rows, d_out_dist):
         _check(lib().psb_stage_rerank(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_cand)), count, stride,

@@ -90,11 +90,19 @@ struct ScanWorkspace {
     int* n_fail;         // [1]
     int* fail_cursor;    // [1]
     unsigned long long* work_cursor; // [1]
-    unsigned long long* counters;    // [4]: scanned rows, admitted, fallback queries, status
+    unsigned long long* counters;    // [4]: scanned rows, admitted, fallback queries, survivors of the tensor-core filter
+    // tensor-core pre-filter scan (scan_tc.cu)
+    long long* item_off_tc = nullptr;            // [nlist + 1] work items of the lists the tensor-core kernel takes
+    unsigned long long* work_cursor_tc = nullptr;
+    int* tc_status = nullptr;                    // [1] != 0 after a bounded wait of the tensor-core kernel gave up
+    int tc_min_visitors = 0;                     // lists with at least this many visiting queries go to the tensor-core kernel (0 = 1)
+    int tc_wait_limit = 0, tc_skip_mma = 0;      // test hooks of the time-out path
     int pool_cap;
     void* lut_h = nullptr;       // [tables][m*k] fp16 tables (tables = max_batch, x nprobe in residual mode) for the half pre-filter scan (null = fp32 scan only)
     float* lut_scale = nullptr;  // [tables]
-    int scan_mode = 0;           // 0 = half pre-filter when it fits, 1 = fp32 scan
+    int scan_mode = 0;           // 0 = auto: tensor-core pre-filter when the call has the queries and the shape fits, else the
+                                 //     SIMT half pre-filter, else the fp32 scan; 1 = fp32 SIMT scan only; 2 = SIMT scans only;
+                                 //     3 = tensor-core pre-filter required
     uint64_t* fallback_partial = nullptr;  // [fallback_partial_bytes(stage1_k)]: partial top lists of the split exact fallback
     bool half_tables_ready = false;  // lut_h / lut_scale already hold this call's tables (launch_build_tables_residual)
     float seed_sigma = 0.f;      // margin of the sampled cutoff in standard deviations (0 = default)
@@ -116,7 +124,34 @@ struct ScanIndex {
     // Residual ADC mode: codes encode x - centroid[list], so every (query, probe) pair has its own table.
     // d_lut then holds [nq * nprobe][m*k] tables (pair order) and the visitor lists carry pair indices.
     bool residual = false;
+    // for the tensor-core pre-filter scan and the re-scoring selection
+    const float* centroids = nullptr;  // device [nlist][dim]
+    const float* codebook = nullptr;   // device [m][k][dim / m]
+    int dim = 0;
 };
+
+// ---- tensor-core pre-filter scan (scan_tc.cu) ------------------------------------------------------------------
+// Code rows per tile for this shape (256 or 128), 0 when the tensor-core scan does not support it.
+int scan_tc_tile_rows(int dim, int m, int k);
+struct ScanTcLaunch {
+    const float* queries; const float* centroids; const float* codebook; const int* probes;
+    const uint8_t* codes; const long long* offsets; long long row_base;
+    int nlist, dim, m, k, lut_div; bool residual;
+    const int* vis_count; const int* vis_off; const int* visitors; const long long* item_off;
+    const float* thr; int* pool_cnt; uint64_t* pool; int pool_cap;
+    unsigned long long* work_cursor; unsigned long long* counters; int* status;
+    int chunk_rows, reserve_ctas, sm_count, wait_limit, skip_mma;
+};
+psb_status launch_scan_tc(const ScanTcLaunch& L, cudaStream_t s);
+// Selection over pools that may hold unscored survivors of the tensor-core filter (re-scored exactly here).
+struct SelectRescoreLaunch {
+    const uint64_t* pool; const int* pool_cnt; int pool_cap; const long long* q_rows; const float* thr; int stage1_k;
+    const float* lut; const float* queries; const float* centroids; const float* codebook; const int* probes;
+    int nprobe, dim, nlist; const uint8_t* codes; long long row_base; const long long* row_delta;
+    int m, k; bool residual, tree;
+    int* out_rows; float* out_dist; int* out_count; int* fail_list; int* n_fail; unsigned long long* counters;
+};
+psb_status launch_select_rescore(const SelectRescoreLaunch& L, int nq, cudaStream_t s);
 
 // Tables of the residual mode: table (q, p) is built on queries[q] - centroids[probes[q][p]] (pairs whose probe is
 // outside [0, nlist) are left untouched).  d_lut [nq * nprobe][m*k].
@@ -137,9 +172,10 @@ psb_status launch_build_tables_residual(const float* d_queries, int nq, int dim,
                                         const float* d_centroids, int nlist, const float* d_codebook, int m, int k,
                                         const float* d_cb_maxnorm, float* d_lut, const ScanWorkspace& ws, cudaStream_t s);
 
+// d_queries [nq][dim] may be null: the tensor-core pre-filter then stays out and the SIMT scans take every list.
 psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
-                       int* d_count, int sm_count, cudaStream_t s);
+                       int* d_count, int sm_count, cudaStream_t s, const float* d_queries = nullptr);
 
 // ---- rerank ------------------------------------------------------------------------------------------------
 // Which rows of the index-wide (list-contiguous) numbering a session's exact store and id table hold.

@@ -22,8 +22,11 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "scan_common.cuh"
 
 namespace psb {
+
+using namespace scan;
 
 namespace {
 
@@ -106,40 +109,53 @@ __global__ void k_count_visitors(const int* __restrict__ probes, int nq, int npr
 }
 
 // Single CTA: exclusive scans over the lists (visitor offsets, work-item offsets).
+// A list with at least tc_min_vis visitors (tc_min_vis > 0) belongs to the tensor-core kernel: its work items (groups of
+// tc_group visitors) are counted in item_off_tc and it gets none in item_off; every other list the other way round.
+__device__ __forceinline__ void list_items(int v, long long rows, int group, int tc_group, int tc_min_vis, int chunk_rows,
+                                           long long& simt, long long& tc) {
+    simt = 0; tc = 0;
+    if (v <= 0 || rows <= 0) return;
+    const long long chunks = (rows + chunk_rows - 1) / chunk_rows;
+    if (tc_min_vis > 0 && v >= tc_min_vis) tc = (long long)((v + tc_group - 1) / tc_group) * chunks;
+    else simt = (long long)((v + group - 1) / group) * chunks;
+}
 __global__ void k_scan_lists(const int* __restrict__ vis_count, const long long* __restrict__ offsets, int nlist,
                              int group, int chunk_rows, int* __restrict__ vis_off,
-                             long long* __restrict__ item_off, int* __restrict__ vis_cursor) {
-    __shared__ long long s_part_items[1024];
+                             long long* __restrict__ item_off, int* __restrict__ vis_cursor,
+                             int tc_group, int tc_min_vis, long long* __restrict__ item_off_tc) {
+    __shared__ long long s_part_items[1024], s_part_tc[1024];
     __shared__ int s_part_vis[1024];
     const int t = threadIdx.x, nt = blockDim.x;
     const int per = (nlist + nt - 1) / nt;
     const int b = min(t * per, nlist), e = min(b + per, nlist);
-    long long items = 0; int vis = 0;
+    long long items = 0, items_tc = 0; int vis = 0;
     for (int l = b; l < e; ++l) {
         const int v = vis_count[l];
-        const long long rows = offsets[l + 1] - offsets[l];
-        vis += v;
-        if (v > 0 && rows > 0) items += (long long)((v + group - 1) / group) * ((rows + chunk_rows - 1) / chunk_rows);
+        long long si, ti;
+        list_items(v, offsets[l + 1] - offsets[l], group, tc_group, tc_min_vis, chunk_rows, si, ti);
+        vis += v; items += si; items_tc += ti;
     }
-    s_part_items[t] = items; s_part_vis[t] = vis;
+    s_part_items[t] = items; s_part_tc[t] = items_tc; s_part_vis[t] = vis;
     __syncthreads();
     if (t == 0) {
-        long long ai = 0; int av = 0;
+        long long ai = 0, at = 0; int av = 0;
         for (int i = 0; i < nt; ++i) {
-            const long long ci = s_part_items[i]; const int cv = s_part_vis[i];
-            s_part_items[i] = ai; s_part_vis[i] = av;
-            ai += ci; av += cv;
+            const long long ci = s_part_items[i], ct = s_part_tc[i]; const int cv = s_part_vis[i];
+            s_part_items[i] = ai; s_part_tc[i] = at; s_part_vis[i] = av;
+            ai += ci; at += ct; av += cv;
         }
         item_off[nlist] = ai; vis_off[nlist] = av;
+        if (item_off_tc) item_off_tc[nlist] = at;
     }
     __syncthreads();
-    long long ai = s_part_items[t]; int av = s_part_vis[t];
+    long long ai = s_part_items[t], at = s_part_tc[t]; int av = s_part_vis[t];
     for (int l = b; l < e; ++l) {
         const int v = vis_count[l];
-        const long long rows = offsets[l + 1] - offsets[l];
+        long long si, ti;
+        list_items(v, offsets[l + 1] - offsets[l], group, tc_group, tc_min_vis, chunk_rows, si, ti);
         item_off[l] = ai; vis_off[l] = av; vis_cursor[l] = 0;
-        av += v;
-        if (v > 0 && rows > 0) ai += (long long)((v + group - 1) / group) * ((rows + chunk_rows - 1) / chunk_rows);
+        if (item_off_tc) item_off_tc[l] = at;
+        av += v; ai += si; at += ti;
     }
 }
 
@@ -155,71 +171,6 @@ __global__ void k_fill_visitors(const int* __restrict__ probes, int nq, int npro
 }
 
 // ------------------------------------------------------------------------------------------------------
-// ADC distance of one code row against a table in shared memory laid out [m][k] (one visitor).
-// Balanced pairwise sum of n (a power of two) terms, earlier term on the left: the order the reference's residual
-// CPU scan uses for M = 16 and M = 8 (src/search/ivfrespq/stage/ivfrespq_cpu_rerank.cpp:226-259).
-template <int N>
-__device__ __forceinline__ float tree_sum(float (&t)[N]) {
-#pragma unroll
-    for (int n = N; n > 1; n >>= 1)
-#pragma unroll
-        for (int j = 0; j < n / 2; ++j) t[j] = __fadd_rn(t[2 * j], t[2 * j + 1]);
-    return t[0];
-}
-template <int M>
-__device__ __forceinline__ float adc_row_tree(const uint8_t* __restrict__ row, const float* __restrict__ lut, int k) {
-    static_assert(M == 8 || M == 16, "tree order exists for M = 8 and 16");
-    const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
-    float t[M];
-#pragma unroll
-    for (int w = 0; w < M / 4; ++w) {
-        const uint32_t c = __ldg(p + w);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) t[w * 4 + j] = lut[(w * 4 + j) * k + ((c >> (j * 8)) & 255)];
-    }
-    return tree_sum<M>(t);
-}
-
-template <int M>
-__device__ __forceinline__ float adc_row_1(const uint8_t* __restrict__ row, const float* __restrict__ s_lut, int k) {
-    float acc = 0.0f;
-    if constexpr (M % 16 == 0) {
-        const uint4* p = reinterpret_cast<const uint4*>(row);
-#pragma unroll
-        for (int w = 0; w < M / 16; ++w) {
-            const uint4 c = __ldg(p + w);
-            const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int code = (cw[j >> 2] >> ((j & 3) * 8)) & 255;
-                acc = __fadd_rn(acc, s_lut[(w * 16 + j) * k + code]);
-            }
-        }
-    } else if constexpr (M % 4 == 0 && M > 0) {
-        const uint32_t* p = reinterpret_cast<const uint32_t*>(row);
-#pragma unroll
-        for (int w = 0; w < M / 4; ++w) {
-            const uint32_t c = __ldg(p + w);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc = __fadd_rn(acc, s_lut[(w * 4 + j) * k + ((c >> (j * 8)) & 255)]);
-        }
-    }
-    return acc;
-}
-// Generic M (runtime), byte loads.
-__device__ __forceinline__ float adc_row_dyn(const uint8_t* __restrict__ row, const float* __restrict__ s_lut,
-                                             int m, int k) {
-    float acc = 0.0f;
-    for (int j = 0; j < m; ++j) acc = __fadd_rn(acc, s_lut[j * k + __ldg(row + j)]);
-    return acc;
-}
-template <int M>
-__device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut, int m, int k, bool tree = false) {
-    if constexpr (M == 8 || M == 16) { if (tree) return adc_row_tree<M>(row, s_lut, k); }
-    if constexpr (M > 0) return adc_row_1<M>(row, s_lut, k);
-    else return adc_row_dyn(row, s_lut, m, k);
-}
-
 // Per query: admission cutoff from a strided sample of the rows it will scan.
 //   N = rows the query scans.  N <= pool capacity: cutoff = +inf (everything is admitted).
 //   Otherwise every stride-th row of each probed list is scored, stride = clamp(stage1_k / 16, 16, 64), n_s rows in
@@ -345,49 +296,6 @@ __device__ __forceinline__ void lut_add(float (&acc)[V], const float* __restrict
         acc[4] = __fadd_rn(acc[4], y.x); acc[5] = __fadd_rn(acc[5], y.y);
         acc[6] = __fadd_rn(acc[6], y.z); acc[7] = __fadd_rn(acc[7], y.w);
     }
-}
-
-struct ScanArgs {
-    const float* lut;          // [tables][m*k]
-    int lut_div;               // visitor entry / lut_div = query (1: one table per query; nprobe: one per pair)
-    int tree;                  // pairwise-tree ADC order (residual mode, M = 8 or 16, K = 256)
-    const uint8_t* codes;
-    const long long* offsets;
-    long long row_base;
-    const long long* row_delta;  // optional [nlist]: reported row = local row + row_delta[list]
-    int nlist, m, k;
-    const int* vis_count; const int* vis_off; const int* visitors;
-    const long long* item_off;
-    const float* thr;
-    int* pool_cnt; uint64_t* pool; int pool_cap;
-    unsigned long long* work_cursor;
-    unsigned long long* counters;
-    int chunk_rows;
-    int reserve_ctas;          // host side only: CTAs left out of the persistent grid (see ScanWorkspace::reserve_ctas)
-};
-
-// Persistent grid: every SM slot, minus the CTAs the caller wants kept free for kernels of another stream.
-inline unsigned scan_grid(int slots, int reserve) {
-    const int g = slots - (reserve > 0 ? reserve : 0);
-    return (unsigned)(g < 1 ? 1 : g);
-}
-
-// Largest l in [0, nlist) with item_off[l] <= item, found by warp 0 with a 32-ary search.
-__device__ __forceinline__ int find_list(const long long* __restrict__ item_off, int nlist, long long item) {
-    const int lane = threadIdx.x & 31;
-    int lo = 0, hi = nlist;  // answer in [lo, hi)
-    while (hi - lo > 1) {
-        const int span = hi - lo;
-        const int step = (span + 31) / 32;
-        const int pos = min(lo + lane * step, hi - 1);
-        const bool ok = item_off[pos] <= item;  // monotone: true for a prefix of the lanes
-        const unsigned bal = __ballot_sync(0xffffffffu, ok);
-        const int last = 31 - __clz((int)bal);  // lane 0 always true (item_off[lo] <= item)
-        const int nlo = min(lo + last * step, hi - 1);
-        const int nhi = min(nlo + step, hi);
-        lo = nlo; hi = nhi;
-    }
-    return lo;
 }
 
 template <int M, int V>
@@ -1228,11 +1136,20 @@ psb_status launch_build_tables_residual(const float* d_queries, int nq, int dim,
 
 psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq,
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
-                       int* d_count, int sm_count, cudaStream_t s) {
+                       int* d_count, int sm_count, cudaStream_t s, const float* d_queries) {
     if (nq <= 0) return PSB_OK;
     const long long tables = ix.residual ? (long long)nq * nprobe : nq;
     if (tables > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
-    const bool use_half = ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(ix.m, ix.k);
+    // Tensor-core pre-filter: needs the queries, the centroids and the codebook, a supported shape, and a selection that fits.
+    const bool tc_possible = d_queries != nullptr && ix.centroids != nullptr && ix.codebook != nullptr && ix.dim == ix.m * (ix.dim / ix.m) &&
+                             ws.item_off_tc != nullptr && ws.work_cursor_tc != nullptr && ws.tc_status != nullptr &&
+                             scan_tc_tile_rows(ix.dim, ix.m, ix.k) > 0 &&
+                             (size_t)ws.pool_cap * 8 + (ix.residual ? (size_t)ix.dim * 4 : (size_t)ix.m * ix.k * 4) <= (size_t)226 * 1024;
+    if (ws.scan_mode == 3 && !tc_possible) return fail(PSB_UNSUPPORTED_SHAPE, "the tensor-core scan does not support this call (shape, or no queries given)");
+    const bool use_tc = tc_possible && (ws.scan_mode == 0 || ws.scan_mode == 3);
+    const int tc_min_vis = use_tc ? (ws.tc_min_visitors > 0 ? ws.tc_min_visitors : 1) : 0;
+    const bool simt_needed = !use_tc || tc_min_vis > 1;  // lists below the visitor limit stay with the SIMT scan
+    const bool use_half = simt_needed && ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(ix.m, ix.k);
     if (nq > ws.cap_queries || (use_half && tables > ws.cap_tables))
         return fail(PSB_INTERNAL, "scan workspace holds " + std::to_string(ws.cap_queries) + " queries / " + std::to_string(ws.cap_tables) +
                                       " tables, the call needs " + std::to_string(nq) + " / " + std::to_string(tables));
@@ -1243,12 +1160,13 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     PSB_CUDA(cudaMemsetAsync(ws.n_fail, 0, sizeof(int), s));
     PSB_CUDA(cudaMemsetAsync(ws.fail_cursor, 0, sizeof(int), s));
     PSB_CUDA(cudaMemsetAsync(ws.work_cursor, 0, sizeof(unsigned long long), s));
+    if (use_tc) PSB_CUDA(cudaMemsetAsync(ws.work_cursor_tc, 0, sizeof(unsigned long long), s));
     k_count_visitors<<<(nq * 32 + 255) / 256, 256, 0, s>>>(d_probes, nq, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                           ix.list_end, ws.vis_count, ws.q_rows, ws.counters);
     count_launch();
     PSB_LAUNCH_CHECK();
     k_scan_lists<<<1, 1024, 0, s>>>(ws.vis_count, ix.offsets, ix.nlist, group, kScanChunkRows, ws.vis_off,
-                                    ws.item_off, ws.vis_cursor);
+                                    ws.item_off, ws.vis_cursor, 128, tc_min_vis, use_tc ? ws.item_off_tc : nullptr);
     count_launch();
     PSB_LAUNCH_CHECK();
     const long long pairs = (long long)nq * nprobe;
@@ -1267,22 +1185,43 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     a.thr = ws.thr; a.pool_cnt = ws.pool_cnt; a.pool = ws.pool; a.pool_cap = ws.pool_cap;
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
     a.reserve_ctas = ws.reserve_ctas;
-    if (use_half && !ws.half_tables_ready) {
+    if (use_half && !ws.half_tables_ready && simt_needed) {
         k_lut_to_half<<<(unsigned)tables, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
         count_launch();
         PSB_LAUNCH_CHECK();
     }
     if (ws.ev_begin) PSB_CUDA(cudaEventRecord(ws.ev_begin, s));
-    if (use_half) {
-        ScanArgsH ah;
-        ah.a = a; ah.lut_h = reinterpret_cast<const __half*>(ws.lut_h); ah.scale = ws.lut_scale;
-        PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_h<MM>(ah, sm_count, s))));
-    } else {
-        PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_m<MM>(a, group, sm_count, s))));
+    if (use_tc) {
+        ScanTcLaunch L;
+        L.queries = d_queries; L.centroids = ix.centroids; L.codebook = ix.codebook; L.probes = d_probes;
+        L.codes = ix.codes; L.offsets = ix.offsets; L.row_base = ix.row_base; L.nlist = ix.nlist; L.dim = ix.dim; L.m = ix.m; L.k = ix.k;
+        L.lut_div = a.lut_div; L.residual = ix.residual; L.vis_count = ws.vis_count; L.vis_off = ws.vis_off; L.visitors = ws.visitors;
+        L.item_off = ws.item_off_tc; L.thr = ws.thr; L.pool_cnt = ws.pool_cnt; L.pool = ws.pool; L.pool_cap = ws.pool_cap;
+        L.work_cursor = ws.work_cursor_tc; L.counters = ws.counters; L.status = ws.tc_status; L.chunk_rows = kScanChunkRows;
+        L.reserve_ctas = ws.reserve_ctas; L.sm_count = sm_count; L.wait_limit = ws.tc_wait_limit; L.skip_mma = ws.tc_skip_mma;
+        PSB_TRY(launch_scan_tc(L, s));
+    }
+    if (simt_needed) {
+        if (use_half) {
+            ScanArgsH ah;
+            ah.a = a; ah.lut_h = reinterpret_cast<const __half*>(ws.lut_h); ah.scale = ws.lut_scale;
+            PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_h<MM>(ah, sm_count, s))));
+        } else {
+            PSB_DISPATCH_M(ix.m, PSB_TRY((run_scan_m<MM>(a, group, sm_count, s))));
+        }
     }
     if (ws.ev_end) PSB_CUDA(cudaEventRecord(ws.ev_end, s));
     // selection
-    {
+    if (use_tc) {  // pools may hold unscored survivors of the tensor-core filter: the selection re-scores them exactly
+        SelectRescoreLaunch R;
+        R.pool = ws.pool; R.pool_cnt = ws.pool_cnt; R.pool_cap = ws.pool_cap; R.q_rows = ws.q_rows; R.thr = ws.thr; R.stage1_k = stage1_k;
+        R.lut = d_lut; R.queries = d_queries; R.centroids = ix.centroids; R.codebook = ix.codebook; R.probes = d_probes;
+        R.nprobe = nprobe; R.dim = ix.dim; R.nlist = ix.nlist; R.codes = ix.codes; R.row_base = ix.row_base; R.row_delta = ix.row_delta;
+        R.m = ix.m; R.k = ix.k; R.residual = ix.residual; R.tree = tree_order(ix);
+        R.out_rows = d_rows; R.out_dist = d_dist; R.out_count = d_count; R.fail_list = ws.fail_list; R.n_fail = ws.n_fail;
+        R.counters = ws.counters;
+        PSB_TRY(launch_select_rescore(R, nq, s));
+    } else {
         const size_t smem = (size_t)ws.pool_cap * sizeof(uint64_t);
         PSB_TRY(set_smem(k_select_pool, smem));
         k_select_pool<<<nq, kSelectThreads, smem, s>>>(ws.pool, ws.pool_cnt, ws.pool_cap, ws.q_rows, stage1_k, d_rows,

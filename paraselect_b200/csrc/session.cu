@@ -202,7 +202,7 @@ struct psb_session {
     size_t h_cand_pinned_count = 0;
     std::vector<long long> h_global_begin, h_offsets;  // striped shards: host copies for the staged transport
     // workspaces
-    DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, visitors, q_rows, thr,
+    DevBuf q, q_u8, dist_tile, probes, probe_dist, lut, vis_count, vis_off, vis_cursor, item_off, item_off_tc, visitors, q_rows, thr,
         pool_cnt, pool, fail_list, fallback_partial, scalars, lut_h, lut_scale, cand_rows, cand_dist, cand_count, stage, score, out_rows, out_dist, out_ids;
     int ws_scan_queries = 0;        // queries the scan workspace (visitors, pools, cutoffs) currently holds
     long long ws_scan_tables = 0;   // tables the fp16 table buffer currently holds
@@ -244,6 +244,7 @@ struct psb_session {
         ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
         ix.row_delta = striped ? row_delta.as<long long>() : nullptr;
         ix.residual = opt.adc_mode == 1;
+        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim;
         return ix;
     }
     // Which index-wide rows the exact store and the id table of this session hold.
@@ -254,6 +255,18 @@ struct psb_session {
         }
         mp.base = 0; mp.count = n_vectors;
         return mp;
+    }
+    // Reads (and clears) the time-out word of the tensor-core scan; the stream must be idle.
+    psb_status check_scan_status() {
+        if (!scalars.p) return PSB_OK;
+        int st = 0;
+        int* word = reinterpret_cast<int*>(scalars.as<unsigned long long>() + 8);
+        PSB_CUDA(cudaMemcpy(&st, word, sizeof(int), cudaMemcpyDeviceToHost));
+        if (st) {
+            PSB_CUDA(cudaMemset(word, 0, sizeof(int)));
+            return fail(PSB_TIMEOUT, "a bounded wait in the tensor-core scan kernel gave up");
+        }
+        return PSB_OK;
     }
     ScanWorkspace scan_ws() const {
         ScanWorkspace w;
@@ -271,6 +284,8 @@ struct psb_session {
         w.lut_h = lut_h.p; w.lut_scale = lut_scale.as<float>(); w.scan_mode = opt.scan_mode;
         w.reserve_ctas = opt.reserve_sms;
         w.seed_sigma = opt.seed_sigma;
+        w.item_off_tc = item_off_tc.as<long long>(); w.work_cursor_tc = sc + 7; w.tc_status = reinterpret_cast<int*>(sc + 8);
+        w.tc_min_visitors = opt.tc_min_visitors; w.tc_wait_limit = opt.test_wait_limit; w.tc_skip_mma = opt.test_skip_mma;
         w.cap_queries = ws_scan_queries; w.cap_tables = ws_scan_tables;
         return w;
     }
@@ -348,6 +363,7 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
     PSB_TRY(s->vis_off.reserve(sizeof(int) * ((size_t)s->nlist + 1)));
     PSB_TRY(s->vis_cursor.reserve(sizeof(int) * (size_t)s->nlist));
     PSB_TRY(s->item_off.reserve(sizeof(long long) * ((size_t)s->nlist + 1)));
+    PSB_TRY(s->item_off_tc.reserve(sizeof(long long) * ((size_t)s->nlist + 1)));
     PSB_TRY(s->visitors.reserve(sizeof(int) * (size_t)nq * nprobe));
     PSB_TRY(s->q_rows.reserve(sizeof(long long) * (size_t)nq));
     PSB_TRY(s->thr.reserve(sizeof(float) * (size_t)nq));
@@ -362,8 +378,8 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
         PSB_TRY(s->lut_scale.reserve(sizeof(float) * tables));
     }
     if (!s->scalars.p) {
-        PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 8));
-        PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(unsigned long long) * 8, s->stream));
+        PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 16));
+        PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(unsigned long long) * 16, s->stream));
     }
     // what the buffers hold now (reserve() keeps a larger buffer from an earlier call)
     s->ws_scan_queries = (int)std::min<size_t>({s->q_rows.bytes / sizeof(long long), s->thr.bytes / sizeof(float),
@@ -604,6 +620,8 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if (opt.reserve_sms < 0 || opt.reserve_sms > 64) return fail(PSB_INVALID_ARGUMENT, "reserve_sms must be in 0..64");
     if (opt.seed_sigma != 0.f && !(opt.seed_sigma >= 2.f && opt.seed_sigma <= 10.f)) return fail(PSB_INVALID_ARGUMENT, "seed_sigma must be 0 or in 2..10");
     if (opt.pipeline_parts != 0 && (opt.pipeline_parts < 2 || opt.pipeline_parts > 32)) return fail(PSB_INVALID_ARGUMENT, "pipeline_parts must be 0 or in 2..32");
+    if (opt.scan_mode < 0 || opt.scan_mode > 3) return fail(PSB_INVALID_ARGUMENT, "scan_mode must be in 0..3");
+    if (opt.tc_min_visitors < 0) return fail(PSB_INVALID_ARGUMENT, "tc_min_visitors must not be negative");
     if (opt.gather_ctas < 0 || opt.gather_ctas > 1024) return fail(PSB_INVALID_ARGUMENT, "gather_ctas must be in 0..1024");
     if (opt.adc_mode == 1 && !index->exact.fp32 && !index->exact.u8)
         return fail(PSB_INVALID_ARGUMENT, "residual mode always reranks: exact rows are required");
@@ -710,7 +728,8 @@ psb_status psb_session_destroy(psb_session* s) {
 psb_status psb_session_sync(psb_session* s) {
     if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
     PSB_CUDA(cudaStreamSynchronize(s->stream));
-    return s->tc_work.check_status();
+    PSB_TRY(s->tc_work.check_status());
+    return s->check_scan_status();
 }
 
 psb_status psb_session_set_stream(psb_session* s, void* stream, int background) {
@@ -753,6 +772,11 @@ psb_status psb_stage_quantize_lut_u8(psb_session* s, const float* d_lut, int64_t
 
 psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int* d_probes, int nprobe,
                           int stage1_k, int* d_rows, float* d_dist, int* d_count) {
+    return psb_stage_scan_queries(s, nullptr, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count);
+}
+
+psb_status psb_stage_scan_queries(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
+                                  int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count) {
     if (!s || !d_lut || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");
     if (nprobe <= 0 || stage1_k <= 0) return fail(PSB_INVALID_ARGUMENT, "nprobe and stage1_k must be positive");
     if (nprobe > kMaxProbe || stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or stage1_k above 2048");
@@ -761,7 +785,7 @@ psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int*
     ScanWorkspace ws;
     PSB_TRY(s->timed_scan_ws(&ws));
     return launch_scan(s->scan_index(), ws, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count,
-                       s->sm_count, s->stream);
+                       s->sm_count, s->stream, d_queries);
 }
 
 psb_status psb_stage_rerank(psb_session* s, const float* d_queries, int nq, const int* d_candidates,
@@ -816,6 +840,7 @@ psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     stats->pq_adc_lookups = (long long)h[0] * s->m;
     stats->threshold_candidates = (long long)h[1];
     stats->fallback_queries = (long long)h[2];
+    stats->prefilter_survivors = (long long)h[3];
     stats->kernel_launches = launches_total();
     if (!s->scalars.p) PSB_CUDA(cudaStreamSynchronize(s->stream));
     s->collect_scan_events();
@@ -979,7 +1004,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         }
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
         if (rc == PSB_OK) rc = launch_scan(s->scan_index(), sws, s->lut.as<float>(), m, probes, nprobe, stage1_k, rows_out,
-                                           dist_out, cnt_out, s->sm_count, st);
+                                           dist_out, cnt_out, s->sm_count, st, q);
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
         if (rc != PSB_OK) break;
         if (staged_overlap) {  // hand the sub-batch to the worker: candidates to the host, an event marks them ready
@@ -1118,6 +1143,7 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         if (stats) { t_h2d += tm.ms(0, 1); t_d2h += tm.ms(2, 3); t_total += tm.ms(0, 3); }
     }
     PSB_TRY(s->tc_work.check_status());
+    PSB_TRY(s->check_scan_status());
     if (stats) {
         unsigned long long c1[4];
         PSB_CUDA(cudaMemcpyAsync(c1, s->scalars.p, sizeof(c1), cudaMemcpyDeviceToHost, st));
@@ -1129,6 +1155,7 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         stats->pq_adc_lookups = stats->pq_scanned_codes * s->m;
         stats->threshold_candidates = (long long)(c1[1] - c0[1]);
         stats->fallback_queries = (long long)(c1[2] - c0[2]);
+        stats->prefilter_survivors = (long long)(c1[3] - c0[3]);
         stats->h2d_bytes = h2d; stats->d2h_bytes = d2h;
         stats->kernel_launches = launches_total() - launches0;
         s->collect_scan_events();

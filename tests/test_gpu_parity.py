@@ -407,6 +407,43 @@ def test_overlapped_pipeline_equals_serial_pipeline(psb):
         assert np.array_equal(dd.cpu().numpy(), res[True]["distances"])
 
 
+@pytest.mark.parametrize("residual", [False, True])
+def test_short_tail_batch_after_an_overlapped_batch(psb, residual):
+    """batch_size 2600 with 2600 + 1500 queries: the full batch runs as four overlapped sub-batches of 650, the tail batch
+    (below the overlap limit of 2048) runs in one piece of 1500 - larger than any sub-batch before it.  The workspaces
+    must follow; results equal the serial pipeline's and the checker's."""
+    ix = synth.make_index(60000, 64, 64, 16, seed=161, zipf=True, residual=residual)
+    q = synth.make_queries(ix, 4100, seed=162, weights=synth.zipf_weights(64))
+    res = {}
+    for serial in (False, True):
+        with psb.Session(ix, n_rerank=120, serial_pipeline=serial, residual=residual) as s:
+            res[serial] = s.search(q, 8, 10, batch_size=2600)
+    for k in ("indices", "distances"):
+        assert np.array_equal(res[False][k], res[True][k])
+    search = oracle.ivfrespq_search if residual else oracle.ivfpq_search
+    for lo in (0, 2600, 3900):  # first batch, start of the tail batch, its end
+        want = search(ix, q[lo:lo + 200], 8, 10, 120)
+        assert np.array_equal(res[False]["indices"][lo:lo + 200], want["indices"])
+        assert np.array_equal(res[False]["distances"][lo:lo + 200], want["distances"])
+
+
+def test_knn_exact_short_last_tile(psb):
+    """A base whose last tile would hold fewer than k rows: those rows must still be candidates."""
+    torch = _torch()
+    rng = np.random.default_rng(5)
+    n, dim, k, nq = 4096 * 3 + 7, 16, 10, 65536   # 65,536 queries -> tiles of 4,096 base rows; the last 7 rows are a short tail
+    base = rng.standard_normal((n, dim)).astype(np.float32)
+    q = rng.standard_normal((nq, dim)).astype(np.float32)
+    q[:3] = base[[n - 1, n - 3, 17]] + 1e-3   # two of the checked queries sit on rows of the short tail
+    rows = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+    dist = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+    psb.knn_exact(dev(q), nq, dev(base), n, dim, k, rows, dist)
+    torch.cuda.synchronize()
+    d2 = ((q[:3, None, :].astype(np.float64) - base[None, :, :]) ** 2).sum(-1)
+    want = np.argsort(d2, axis=1, kind="stable")[:, :k]
+    assert np.array_equal(rows[:3].cpu().numpy(), want)
+
+
 def test_sharded_step_with_second_stream_equals_search(psb):
     """The sharded step on one rank, cut into sub-batches whose exchange half (rerank, id map) runs on a second stream
     through psb_session_set_stream while the next sub-batch scans: same results as the session's own search."""
