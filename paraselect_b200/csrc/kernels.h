@@ -127,14 +127,19 @@ struct ScanIndex {
     // for the tensor-core pre-filter scan and the re-scoring selection
     const float* centroids = nullptr;  // device [nlist][dim]
     const float* codebook = nullptr;   // device [m][k][dim / m]
+    const void* row_aug = nullptr;     // device [shard rows] x 8 bytes (launch_row_aug), null: no tensor-core scan
     int dim = 0;
 };
 
 // ---- tensor-core pre-filter scan (scan_tc.cu) ------------------------------------------------------------------
-// Code rows per tile for this shape (256 or 128), 0 when the tensor-core scan does not support it.
-int scan_tc_tile_rows(int dim, int m, int k);
+// Whether the tensor-core scan supports the shape (dsub 2, 4 or 8, dim a multiple of 8, m of 4, operands within shared memory).
+bool scan_tc_supported(int dim, int m, int k);
+// Per-row terms of the tensor-core scan, computed once per index: d_out [rows] of 8 bytes (the extra K slots of each code row).
+psb_status launch_row_aug(const uint8_t* d_codes, long long rows, int dim, int m, int k, const float* d_codebook, void* d_out,
+                          cudaStream_t s);
 struct ScanTcLaunch {
     const float* queries; const float* centroids; const float* codebook; const int* probes;
+    const void* row_aug;
     const uint8_t* codes; const long long* offsets; long long row_base;
     int nlist, dim, m, k, lut_div; bool residual;
     const int* vis_count; const int* vis_off; const int* visitors; const long long* item_off;

@@ -1143,7 +1143,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     // Tensor-core pre-filter: needs the queries, the centroids and the codebook, a supported shape, and a selection that fits.
     const bool tc_possible = d_queries != nullptr && ix.centroids != nullptr && ix.codebook != nullptr && ix.dim == ix.m * (ix.dim / ix.m) &&
                              ws.item_off_tc != nullptr && ws.work_cursor_tc != nullptr && ws.tc_status != nullptr &&
-                             scan_tc_tile_rows(ix.dim, ix.m, ix.k) > 0 &&
+                             ix.row_aug != nullptr && scan_tc_supported(ix.dim, ix.m, ix.k) &&
                              (size_t)ws.pool_cap * 8 + (ix.residual ? (size_t)ix.dim * 4 : (size_t)ix.m * ix.k * 4) <= (size_t)226 * 1024;
     if (ws.scan_mode == 3 && !tc_possible) return fail(PSB_UNSUPPORTED_SHAPE, "the tensor-core scan does not support this call (shape, or no queries given)");
     const bool use_tc = tc_possible && (ws.scan_mode == 0 || ws.scan_mode == 3);
@@ -1193,7 +1193,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     if (ws.ev_begin) PSB_CUDA(cudaEventRecord(ws.ev_begin, s));
     if (use_tc) {
         ScanTcLaunch L;
-        L.queries = d_queries; L.centroids = ix.centroids; L.codebook = ix.codebook; L.probes = d_probes;
+        L.queries = d_queries; L.centroids = ix.centroids; L.codebook = ix.codebook; L.probes = d_probes; L.row_aug = ix.row_aug;
         L.codes = ix.codes; L.offsets = ix.offsets; L.row_base = ix.row_base; L.nlist = ix.nlist; L.dim = ix.dim; L.m = ix.m; L.k = ix.k;
         L.lut_div = a.lut_div; L.residual = ix.residual; L.vis_count = ws.vis_count; L.vis_off = ws.vis_off; L.visitors = ws.visitors;
         L.item_off = ws.item_off_tc; L.thr = ws.thr; L.pool_cnt = ws.pool_cnt; L.pool = ws.pool; L.pool_cap = ws.pool_cap;

@@ -27,6 +27,7 @@
 // Every mbarrier wait is bounded: a role that gives up raises a CTA-wide flag, the other roles see it in their own wait
 // loops, the CTA frees its tensor memory and returns, and the host reports PSB_TIMEOUT.
 #include <cuda_bf16.h>
+#include <algorithm>
 #include <string>
 
 #include "common.cuh"
@@ -42,27 +43,39 @@ using namespace tc;
 namespace {
 
 constexpr int TV = 128;            // visitors per tile (UMMA M)
-constexpr int kDecodeWarps = 8;    // warps 0-7: decode code rows into the B stages
-constexpr int kEpiWarps = 8;       // warps 8-15: read accumulators, compare, push survivors
-constexpr int kWorkers = (kDecodeWarps + kEpiWarps) * 32;
-constexpr int kTcScanThreads = kWorkers + 32;  // warp 16: MMA issuer
-constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int TN = 128;            // code rows per tile (UMMA N)
+constexpr int kDecodeGroups = 3;   // warps 0-11: three groups of four warps; group g decodes tiles g, g + 3, ... (one row per thread)
+constexpr int kDecodeWarps = 4 * kDecodeGroups;
+constexpr int kEpiGroups = 2;      // warps 12-19: two groups of four warps; group e reads the accumulators of tiles e, e + 2, ...
+constexpr int kEpiWarps = 4 * kEpiGroups;
+constexpr int kWarpMma = kDecodeWarps + kEpiWarps;  // warp 20: MMA issuer
+constexpr int kWarpSched = kWarpMma + 1;            // warp 21: fetches work items ahead of the others
+constexpr int kTcScanThreads = (kWarpSched + 1) * 32;
+constexpr int kProducers = kDecodeWarps * 32;
+constexpr int kItemRing = 4;       // work items in flight
+constexpr int kQueueCap = 128;     // survivors a warp collects before it pushes them to the pools
 constexpr int kAugSlots = 4;
 constexpr float kBeta = 0.001953125f * 1.001f;  // 2^-9 (1 + 1e-3)
+
+struct ItemDesc {
+    long long r0, r1;   // scanned rows of the item
+    int ntiles, stop;   // tiles of TN rows; stop: no more work
+    int list, vis_base, nvis;  // list id, first visitor entry, visitors of this group (<= TV)
+};
 
 struct ScanTcArgs {
     ScanArgs a;               // a.item_off: the tensor-core work items (lists the SIMT scan leaves out)
     const float* queries;     // [nq][dim]
-    const float* centroids;   // [nlist][dim]
+    const float* centroids;   // [nlist][dim] (residual mode)
     const float* codebook;    // [m][k][dsub]
-    const int* probes;        // residual mode: [nq * nprobe] list of every (query, probe) pair
-    int dim, kp, katoms, tn;  // kp: padded K (multiple of 16), katoms: 128-byte swizzle atoms along K, tn: code rows per tile
+    const uint2* row_aug;     // [rows of the shard]: the extra K slots of every code row (k_row_aug)
+    int dim, kp, katoms;      // kp: padded K (multiple of 16), katoms: 128-byte swizzle atoms along K
+    int na, ns;               // query-tile slots (1 or 2), row-tile stages = accumulators = decode warp groups in use (2 or 3)
     int residual;
     float eps;                // accumulation slack e
     int* status;              // != 0 after a bounded wait gave up
     int wait_limit;           // polls before a wait gives up (tests shorten it)
-    int skip_mma;             // test hook: the MMA warp issues nothing, so every waiting role runs into its limit
+    int skip_mma;             // test hook: the MMA warp issues nothing, so every role waiting for a result runs into its limit
 };
 
 // Bounded wait that also leaves when another role of the CTA has given up.
@@ -73,6 +86,9 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     }
     return false;
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 
 __device__ __forceinline__ uint32_t bf16_bits_rn(float x) { return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ uint32_t bf16_bits_up(float x) {  // x >= 0, finite: the smallest bf16 >= x
@@ -82,307 +98,416 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) { return 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
-// Address of 16-byte chunk c of operand row `row` in a K-major 128-byte-swizzled operand of `rows` rows.
-__device__ __forceinline__ unsigned char* chunk_ptr(unsigned char* base, int rows, int row, int c) {
-    return base + (size_t)(c >> 3) * rows * 128 + (size_t)row * 128 + (size_t)(((c & 7) ^ (row & 7)) << 4);
+// 16-byte chunk c of an operand row in the K-major 128-byte-swizzled layout: rowbase = operand + row * 128,
+// xs = (row & 7) << 4, atom_stride = rows * 128.
+__device__ __forceinline__ uint4* chunk_at(unsigned char* rowbase, uint32_t xs, int atom_stride, int c) {
+    return reinterpret_cast<uint4*>(rowbase + (size_t)(c >> 3) * atom_stride + ((((uint32_t)c & 7u) << 4) ^ xs));
 }
 
-template <int DSUB>
+// The extra K slots of a code row from |rt|^2: minus the three-term bf16 split of U = (|rt|^2 - (b^2 + e) w^2) / 2 and w rounded up.
+__device__ __forceinline__ uint2 row_aug_words(float rn, float cw2) {
+    const float wv = sqrtf(rn) * 1.003908f;  // >= |r'| (1 + 2^-8, and the square root's rounding)
+    float rest = 0.5f * (rn - cw2 * wv * wv);
+    uint32_t u[3];
+#pragma unroll
+    for (int x = 0; x < 3; ++x) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(rest);
+        u[x] = (uint32_t)__bfloat16_as_ushort(__hneg(h));
+        rest -= __bfloat162float(h);
+    }
+    return make_uint2(u[0] | (u[1] << 16), u[2] | (bf16_bits_up(wv) << 16));
+}
+
+// One code row -> its bf16 operand row (data chunks only).  s_tab: [m][k] entries of DSUB bf16.
+template <int DSUB, int M>
+__device__ __forceinline__ void decode_row(const uint8_t* __restrict__ row, int m_rt, int k, const unsigned char* __restrict__ s_tab,
+                                           unsigned char* rowbase, uint32_t xs, int atom_stride) {
+    constexpr int EB = DSUB * 2;  // bytes per table entry
+    const int kstride = k * EB;
+    auto word = [&](uint32_t cw, int w) {  // code word w: sub-quantisers 4w .. 4w+3
+        const unsigned char* t = s_tab + (size_t)(4 * w) * kstride;
+        if constexpr (DSUB == 2) {  // four codewords of 2 -> chunk w
+            uint4 o;
+            o.x = *reinterpret_cast<const uint32_t*>(t + (cw & 255u) * EB);
+            o.y = *reinterpret_cast<const uint32_t*>(t + kstride + ((cw >> 8) & 255u) * EB);
+            o.z = *reinterpret_cast<const uint32_t*>(t + 2 * kstride + ((cw >> 16) & 255u) * EB);
+            o.w = *reinterpret_cast<const uint32_t*>(t + 3 * kstride + (cw >> 24) * EB);
+            *chunk_at(rowbase, xs, atom_stride, w) = o;
+        } else if constexpr (DSUB == 4) {  // two codewords of 4 -> chunks 2w, 2w+1
+            const uint2 e0 = *reinterpret_cast<const uint2*>(t + (cw & 255u) * EB);
+            const uint2 e1 = *reinterpret_cast<const uint2*>(t + kstride + ((cw >> 8) & 255u) * EB);
+            const uint2 e2 = *reinterpret_cast<const uint2*>(t + 2 * kstride + ((cw >> 16) & 255u) * EB);
+            const uint2 e3 = *reinterpret_cast<const uint2*>(t + 3 * kstride + (cw >> 24) * EB);
+            *chunk_at(rowbase, xs, atom_stride, 2 * w) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+            *chunk_at(rowbase, xs, atom_stride, 2 * w + 1) = make_uint4(e2.x, e2.y, e3.x, e3.y);
+        } else {  // DSUB == 8: one codeword -> one chunk
+            *chunk_at(rowbase, xs, atom_stride, 4 * w) = *reinterpret_cast<const uint4*>(t + (cw & 255u) * EB);
+            *chunk_at(rowbase, xs, atom_stride, 4 * w + 1) = *reinterpret_cast<const uint4*>(t + kstride + ((cw >> 8) & 255u) * EB);
+            *chunk_at(rowbase, xs, atom_stride, 4 * w + 2) = *reinterpret_cast<const uint4*>(t + 2 * kstride + ((cw >> 16) & 255u) * EB);
+            *chunk_at(rowbase, xs, atom_stride, 4 * w + 3) = *reinterpret_cast<const uint4*>(t + 3 * kstride + (cw >> 24) * EB);
+        }
+    };
+    if constexpr (M > 0 && M % 16 == 0) {
+        uint4 c[M / 16];
+#pragma unroll
+        for (int i = 0; i < M / 16; ++i) c[i] = __ldg(reinterpret_cast<const uint4*>(row) + i);
+#pragma unroll
+        for (int i = 0; i < M / 16; ++i) {
+            word(c[i].x, 4 * i); word(c[i].y, 4 * i + 1); word(c[i].z, 4 * i + 2); word(c[i].w, 4 * i + 3);
+            asm volatile("" ::: "memory");  // keeps the next group's table loads below this group's stores: bounded register use
+        }
+    } else if constexpr (M > 0) {
+        uint32_t c[M / 4];
+#pragma unroll
+        for (int i = 0; i < M / 4; ++i) c[i] = __ldg(reinterpret_cast<const uint32_t*>(row) + i);
+#pragma unroll
+        for (int i = 0; i < M / 4; ++i) word(c[i], i);
+    } else {
+        for (int w = 0; w < (m_rt >> 2); ++w) word(__ldg(reinterpret_cast<const uint32_t*>(row) + w), w);
+    }
+}
+
+// Persistent, warp-specialised kernel without CTA-wide barriers in its main loop.  Work item = (list, chunk of rows, group
+// of up to 128 visiting queries); the roles hand items and tiles to one another through mbarriers:
+//   warp 21     scheduler: takes items off the global cursor, resolves them, fills a ring of item descriptors
+//   warps 0-11  producers: build the item's query tile (A operand, ring of `na` slots) and its per-visitor constants, then
+//               decode code rows into the ring of `ns` row tiles (B operand), three tiles in flight (one per warp group)
+//   warp 20     MMA issuer: kp / 16 tcgen05.mma per tile into accumulator `stage`, tcgen05.commit -> mbarriers
+//   warps 12-19 epilogue: tcgen05.ld the accumulator, one comparison per (visitor, row); survivors go to a per-warp queue in
+//               shared memory that is pushed to the visitors' pools 32 at a time (one round of global atomics per push)
+template <int DSUB, int M>
 __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs g) {
     const ScanArgs& a = g.a;
     extern __shared__ __align__(1024) unsigned char s_dyn[];
     unsigned char* s_base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_dyn) + 1023) & ~uintptr_t(1023));
-    const size_t a_bytes = (size_t)g.katoms * TV * 128, b_bytes = (size_t)g.katoms * g.tn * 128;
-    unsigned char* s_a = s_base;                    // [katoms][TV][128 B]
-    unsigned char* s_b = s_base + a_bytes;          // [2][katoms][tn][128 B]
-    unsigned char* s_tab = s_b + 2 * b_bytes;       // [m][k] entries of DSUB bf16: the list's centred codewords
-    float* s_c = reinterpret_cast<float*>(s_tab + (size_t)a.m * a.k * DSUB * 2);  // [dim] centroid of the list
-    __shared__ __align__(8) uint64_t b_full[2], b_empty[2], acc_full[2], acc_empty[2];
+    const int a_stride = TV * 128, b_stride = TN * 128;
+    const size_t a_bytes = (size_t)g.katoms * a_stride, b_bytes = (size_t)g.katoms * b_stride;
+    unsigned char* s_a = s_base;                             // [na][katoms][TV][128 B]
+    unsigned char* s_b = s_a + g.na * a_bytes;               // [ns][katoms][TN][128 B]
+    unsigned char* s_tab = s_b + g.ns * b_bytes;             // [m][k] entries of DSUB bf16: the codebook rounded to bf16
+    __shared__ __align__(8) uint64_t item_full[kItemRing], item_empty[kItemRing], vis_full[kItemRing];
+    __shared__ __align__(8) uint64_t a_full[2], a_empty[2], b_full[4], b_empty[4], acc_full[4], acc_empty[4];
+    __shared__ ItemDesc s_desc[kItemRing];
+    __shared__ float s_P[kItemRing][TV];
+    __shared__ int s_pq[kItemRing][TV], s_hi[kItemRing][TV];
+    __shared__ uint32_t s_queue[kEpiWarps][kQueueCap];
+    __shared__ int s_qcnt[kEpiWarps];
     __shared__ uint32_t s_tmem;
-    __shared__ long long s_item;
-    __shared__ int s_list, s_abort;
-    __shared__ int s_vq[TV], s_pq[TV];
-    __shared__ float s_P[TV];
+    __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunk_data = g.dim >> 3, nchunk = g.kp >> 3;
     const int limit = g.wait_limit;
+    const int NA = g.na, NS = g.ns;
+    const uint32_t tmem_cols = NS * TN <= 256 ? 256u : 512u;
 
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&b_full[i], kDecodeThreads); mbar_init(&b_empty[i], 1);
-            mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiThreads);
+        for (int i = 0; i < kItemRing; ++i) {
+            mbar_init(&item_full[i], 1);
+            mbar_init(&item_empty[i], kProducers + 1 + kEpiWarps * 32);
+            mbar_init(&vis_full[i], kProducers);
+        }
+        for (int i = 0; i < 2; ++i) { mbar_init(&a_full[i], kProducers); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&b_full[i], TN); mbar_init(&b_empty[i], 1);
+            mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128);
         }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (tid < kEpiWarps) s_qcnt[tid] = 0;
+    // the codebook rounded to bf16, once per CTA (all threads)
+    for (int e = tid; e < a.m * a.k; e += kTcScanThreads) {
+        const float* cb = g.codebook + (size_t)e * DSUB;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(s_tab + (size_t)e * DSUB * 2);
+#pragma unroll
+        for (int d = 0; d < DSUB; d += 2) dst[d / 2] = pack_bf16x2_rn(__ldg(cb + d), __ldg(cb + d + 1));
+    }
     __syncwarp();
-    if (warp == 0) tmem_alloc(&s_tmem, (uint32_t)(2 * g.tn));
+    if (warp == 0) tmem_alloc(&s_tmem, tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
     const long long total = a.item_off[a.nlist];
-    const uint32_t idesc = idesc_bf16(TV, g.tn);
     volatile int* abort_flag = &s_abort;
-    uint32_t it = 0;      // tiles this role has been through (all roles count alike)
-    int tab_list = -1;    // list whose codewords s_tab holds (-2: the list-independent residual table)
     bool failed = false;
     unsigned long long passes = 0;
 
-    for (;;) {
-        __syncthreads();  // every role is done with the previous item: operands, tables and s_* words may be rewritten
-        if (warp == 0) {
+    if (warp == kWarpSched) {
+        // ---- scheduler ----
+        for (uint32_t n = 0;; ++n) {
+            const int islot = n % kItemRing;
+            if (!__all_sync(0xffffffffu, wait_or_abort(&item_empty[islot], ((n / kItemRing) & 1u) ^ 1u, abort_flag, limit))) { failed = true; break; }
             long long item = 0;
             if (lane == 0) item = (long long)atomicAdd(a.work_cursor, 1ull);
             item = __shfl_sync(0xffffffffu, item, 0);
-            int l = -1;
-            if (item < total) l = find_list(a.item_off, a.nlist, item);
-            if (lane == 0) { s_item = item; s_list = l; }
+            const bool stop = item >= total;
+            int l = 0;
+            if (!stop) l = find_list(a.item_off, a.nlist, item);
+            if (lane == 0) {
+                ItemDesc d;
+                d.stop = stop ? 1 : 0; d.r0 = d.r1 = 0; d.ntiles = 0; d.list = l; d.vis_base = 0; d.nvis = 0;
+                if (!stop) {
+                    const int nvis = a.vis_count[l];
+                    const int ngroups = (nvis + TV - 1) / TV;
+                    const long long local = item - a.item_off[l];
+                    const int group = (int)(local % ngroups);
+                    const long long chunk = local / ngroups;
+                    d.r0 = a.offsets[l] + chunk * a.chunk_rows;
+                    d.r1 = min(d.r0 + a.chunk_rows, a.offsets[l + 1]);
+                    d.ntiles = (int)((d.r1 - d.r0 + TN - 1) / TN);
+                    d.vis_base = a.vis_off[l] + group * TV;
+                    d.nvis = min(TV, nvis - group * TV);
+                }
+                s_desc[islot] = d;
+                mbar_arrive(&item_full[islot]);  // release: the descriptor is visible to whoever sees the phase complete
+            }
+            __syncwarp();
+            if (stop) break;
         }
-        __syncthreads();
-        if (*abort_flag) break;
-        const long long item = s_item;
-        if (item >= total) break;
-        const int l = s_list;
-        const int nvis = a.vis_count[l];
-        const int ngroups = (nvis + TV - 1) / TV;
-        const long long local = item - a.item_off[l];
-        const int group = (int)(local % ngroups);
-        const long long chunk = local / ngroups;
-        const long long r0 = a.offsets[l] + chunk * a.chunk_rows;
-        const long long r1 = min(r0 + a.chunk_rows, a.offsets[l + 1]);
-        const int ntiles = (int)((r1 - r0 + g.tn - 1) / g.tn);
-
-        // ---- set-up by the 512 worker threads: centroid, codeword table, query tile, per-visitor constants ----
-        if (tid < kWorkers) {
-            for (int d = tid; d < g.dim; d += kWorkers) s_c[d] = __ldg(g.centroids + (size_t)l * g.dim + d);
-            asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory");
-            const int want = g.residual ? -2 : l;
-            if (tab_list != want) {  // uniform
-                const int entries = a.m * a.k;
-                for (int e = tid; e < entries; e += kWorkers) {
-                    const int sub = e / a.k;
-                    const float* cb = g.codebook + (size_t)e * DSUB;
-                    uint32_t w[DSUB / 2];
+    } else if (warp < kDecodeWarps) {
+        // ---- producers ----
+        const int grp = warp >> 2, lt = tid & (TN - 1);
+        const uint32_t xs = (uint32_t)(lt & 7) << 4;
+        uint32_t it0 = 0;
+        for (uint32_t n = 0;; ++n) {
+            const int islot = n % kItemRing;
+            if (!__all_sync(0xffffffffu, wait_or_abort(&item_full[islot], (n / kItemRing) & 1u, abort_flag, limit))) { failed = true; break; }
+            const ItemDesc d = s_desc[islot];
+            if (d.stop) break;
+            const int aslot = n % NA;
+            if (!__all_sync(0xffffffffu, wait_or_abort(&a_empty[aslot], ((n / NA) & 1u) ^ 1u, abort_flag, limit))) { failed = true; break; }
+            const float* cen = g.centroids + (size_t)d.list * g.dim;  // residual mode: the list's centroid (read through L1/L2)
+            if (tid < 2 * TV) {  // query tile: two threads per visitor row
+                const int i = tid >> 1, part = tid & 1;
+                unsigned char* arow = s_a + aslot * a_bytes + (size_t)i * 128;
+                const uint32_t axs = (uint32_t)(i & 7) << 4;
+                const int vq = i < d.nvis ? a.visitors[d.vis_base + i] : -1;    // table index: the query, or the pair in residual mode
+                const int pq = vq >= 0 ? vq / a.lut_div : -1;                    // query (pool, cutoff)
+                float qn = 0.0f, n2 = 0.0f;  // |qt|^2, |q'|^2 over this thread's chunks
+                float P = __int_as_float(0x7f800000), H = 0.0f;
+                if (pq >= 0) {
+                    const float* qrow = g.queries + (size_t)pq * g.dim;
+                    for (int c = part; c < nchunk_data; c += 2) {
+                        float4 x0 = __ldg(reinterpret_cast<const float4*>(qrow + c * 8));
+                        float4 x1 = __ldg(reinterpret_cast<const float4*>(qrow + c * 8 + 4));
+                        if (g.residual) {
+                            const float4 c0 = __ldg(reinterpret_cast<const float4*>(cen + c * 8));
+                            const float4 c1 = __ldg(reinterpret_cast<const float4*>(cen + c * 8 + 4));
+                            x0.x = __fsub_rn(x0.x, c0.x); x0.y = __fsub_rn(x0.y, c0.y); x0.z = __fsub_rn(x0.z, c0.z); x0.w = __fsub_rn(x0.w, c0.w);
+                            x1.x = __fsub_rn(x1.x, c1.x); x1.y = __fsub_rn(x1.y, c1.y); x1.z = __fsub_rn(x1.z, c1.z); x1.w = __fsub_rn(x1.w, c1.w);
+                        }
+                        const float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                        const uint32_t ow[4] = {pack_bf16x2_rn(v[0], v[1]), pack_bf16x2_rn(v[2], v[3]), pack_bf16x2_rn(v[4], v[5]),
+                                                pack_bf16x2_rn(v[6], v[7])};
 #pragma unroll
-                    for (int d = 0; d < DSUB; d += 2) {
-                        float x0 = __ldg(cb + d), x1 = __ldg(cb + d + 1);
-                        if (!g.residual) { x0 = __fsub_rn(x0, s_c[sub * DSUB + d]); x1 = __fsub_rn(x1, s_c[sub * DSUB + d + 1]); }
-                        w[d / 2] = pack_bf16x2_rn(x0, x1);
+                        for (int j = 0; j < 8; ++j) n2 = fmaf(v[j], v[j], n2);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { const float lo = bf16_lo(ow[j]), hi = bf16_hi(ow[j]); qn = fmaf(lo, lo, qn); qn = fmaf(hi, hi, qn); }
+                        *chunk_at(arow, axs, a_stride, c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
-                    uint32_t* dst = reinterpret_cast<uint32_t*>(s_tab + (size_t)e * DSUB * 2);
-#pragma unroll
-                    for (int d = 0; d < DSUB / 2; ++d) dst[d] = w[d];
-                }
-                tab_list = want;
-            }
-            // query tile: four threads per visitor row
-            const int i = tid >> 2, part = tid & 3;
-            const int vi = group * TV + i;
-            const int vq = vi < nvis ? a.visitors[a.vis_off[l] + vi] : -1;   // table index: the query, or the pair in residual mode
-            const int pq = vq >= 0 ? vq / a.lut_div : -1;                     // query (pool, cutoff)
-            float qn = 0.0f, n2 = 0.0f;  // |qt|^2 over this thread's chunks, |q'|^2
-            float P = __int_as_float(0x7f800000), H = 0.0f;
-            const float* qrow = g.queries + (size_t)(pq >= 0 ? pq : 0) * g.dim;
-            if (pq >= 0) {
-                for (int c = part; c < nchunk_data; c += 4) {
-                    const float4 x0 = __ldg(reinterpret_cast<const float4*>(qrow + c * 8));
-                    const float4 x1 = __ldg(reinterpret_cast<const float4*>(qrow + c * 8 + 4));
-                    const float4 c0 = *reinterpret_cast<const float4*>(s_c + c * 8);
-                    const float4 c1 = *reinterpret_cast<const float4*>(s_c + c * 8 + 4);
-                    const float v[8] = {__fsub_rn(x0.x, c0.x), __fsub_rn(x0.y, c0.y), __fsub_rn(x0.z, c0.z), __fsub_rn(x0.w, c0.w),
-                                        __fsub_rn(x1.x, c1.x), __fsub_rn(x1.y, c1.y), __fsub_rn(x1.z, c1.z), __fsub_rn(x1.w, c1.w)};
-                    uint4 o;
-                    o.x = pack_bf16x2_rn(v[0], v[1]); o.y = pack_bf16x2_rn(v[2], v[3]);
-                    o.z = pack_bf16x2_rn(v[4], v[5]); o.w = pack_bf16x2_rn(v[6], v[7]);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) n2 = fmaf(v[j], v[j], n2);
-                    const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) { const float lo = bf16_lo(ow[j]), hi = bf16_hi(ow[j]); qn = fmaf(lo, lo, qn); qn = fmaf(hi, hi, qn); }
-                    *reinterpret_cast<uint4*>(chunk_ptr(s_a, TV, i, c)) = o;
-                }
-            } else {
-                for (int c = part; c < nchunk_data; c += 4) *reinterpret_cast<uint4*>(chunk_ptr(s_a, TV, i, c)) = make_uint4(0, 0, 0, 0);
-            }
-            qn += __shfl_xor_sync(0xffffffffu, qn, 1); qn += __shfl_xor_sync(0xffffffffu, qn, 2);
-            n2 += __shfl_xor_sync(0xffffffffu, n2, 1); n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
-            if (pq >= 0) {
-                const float t = a.thr[pq];
-                if (t < 3.0e38f) {
-                    const float nq = sqrtf(n2) * 1.000001f;
-                    const float av = sqrtf(fmaxf(t, 0.0f) * 1.00001f) * 1.000001f + kBeta * nq;
-                    P = 0.5f * (qn - (av * av + g.eps * nq * nq));
-                    H = av * kBeta + g.eps * nq;
                 } else {
-                    P = __int_as_float(0xff800000);  // no cutoff: every row of the list is a candidate
+                    for (int c = part; c < nchunk_data; c += 2) *chunk_at(arow, axs, a_stride, c) = make_uint4(0, 0, 0, 0);
                 }
-            }
-            for (int c = nchunk_data + part; c < nchunk; c += 4) {  // the extra K slots, then zero padding
-                uint4 o = make_uint4(0, 0, 0, 0);
-                if (c == nchunk_data && pq >= 0) { o.x = 0x3F803F80u; o.y = 0x3F80u | (bf16_bits_up(H) << 16); }  // 1, 1, 1, H
-                *reinterpret_cast<uint4*>(chunk_ptr(s_a, TV, i, c)) = o;
-            }
-            if (part == 0) { s_vq[i] = g.residual ? vq : l; s_pq[i] = pq; s_P[i] = P; }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // operand stores -> visible to the tensor core
-        }
-        __syncthreads();
-
-        if (warp < kDecodeWarps) {
-            // ---- decode: thread j fills operand row j of every tile ----
-            const float cw2 = kBeta * kBeta + g.eps;
-            for (int t = 0; t < ntiles && !failed; ++t, ++it) {
-                const uint32_t st = it & 1u;
-                if (!__all_sync(0xffffffffu, wait_or_abort(&b_empty[st], ((it >> 1) & 1u) ^ 1u, abort_flag, limit))) { failed = true; break; }
-                unsigned char* sb = s_b + st * b_bytes;
-                if (tid < g.tn) {
-                    const long long r = r0 + (long long)t * g.tn + tid;
-                    if (r < r1) {
-                        const uint8_t* row = a.codes + (size_t)(r - a.row_base) * a.m;
-                        float rn = 0.0f;
-                        const int words = a.m >> 2;
-                        for (int w0 = 0; w0 < words; w0 += 4) {
-                            uint32_t cw[4];
-                            if ((a.m & 15) == 0) {
-                                const uint4 c4 = __ldg(reinterpret_cast<const uint4*>(row) + (w0 >> 2));
-                                cw[0] = c4.x; cw[1] = c4.y; cw[2] = c4.z; cw[3] = c4.w;
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) cw[j] = w0 + j < words ? __ldg(reinterpret_cast<const uint32_t*>(row) + w0 + j) : 0u;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int w = w0 + j;  // code word w holds sub-quantisers 4w .. 4w+3
-                                if (w < words) {
-                                    if constexpr (DSUB == 2) {  // four codewords of 2 -> one chunk
-                                        uint32_t o[4];
-#pragma unroll
-                                        for (int b = 0; b < 4; ++b) {
-                                            const int code = (cw[j] >> (8 * b)) & 255;
-                                            o[b] = *reinterpret_cast<const uint32_t*>(s_tab + ((size_t)(4 * w + b) * a.k + code) * 4);
-                                            const float lo = bf16_lo(o[b]), hi = bf16_hi(o[b]);
-                                            rn = fmaf(lo, lo, rn); rn = fmaf(hi, hi, rn);
-                                        }
-                                        *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, w)) = make_uint4(o[0], o[1], o[2], o[3]);
-                                    } else if constexpr (DSUB == 4) {  // two codewords of 4 -> one chunk
-#pragma unroll
-                                        for (int h = 0; h < 2; ++h) {
-                                            const int c0 = (cw[j] >> (16 * h)) & 255, c1 = (cw[j] >> (16 * h + 8)) & 255;
-                                            const uint2 e0 = *reinterpret_cast<const uint2*>(s_tab + ((size_t)(4 * w + 2 * h) * a.k + c0) * 8);
-                                            const uint2 e1 = *reinterpret_cast<const uint2*>(s_tab + ((size_t)(4 * w + 2 * h + 1) * a.k + c1) * 8);
-                                            const uint32_t o[4] = {e0.x, e0.y, e1.x, e1.y};
-#pragma unroll
-                                            for (int b = 0; b < 4; ++b) { const float lo = bf16_lo(o[b]), hi = bf16_hi(o[b]); rn = fmaf(lo, lo, rn); rn = fmaf(hi, hi, rn); }
-                                            *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, 2 * w + h)) = make_uint4(o[0], o[1], o[2], o[3]);
-                                        }
-                                    } else {  // DSUB == 8: one codeword -> one chunk
-#pragma unroll
-                                        for (int b = 0; b < 4; ++b) {
-                                            const int code = (cw[j] >> (8 * b)) & 255;
-                                            const uint4 e = *reinterpret_cast<const uint4*>(s_tab + ((size_t)(4 * w + b) * a.k + code) * 16);
-                                            const uint32_t o[4] = {e.x, e.y, e.z, e.w};
-#pragma unroll
-                                            for (int x = 0; x < 4; ++x) { const float lo = bf16_lo(o[x]), hi = bf16_hi(o[x]); rn = fmaf(lo, lo, rn); rn = fmaf(hi, hi, rn); }
-                                            *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, 4 * w + b)) = e;
-                                        }
-                                    }
-                                }
-                            }
-                        }
-                        // the extra K slots: minus the three-term split of U, then w rounded up
-                        const float wv = sqrtf(rn) * 1.003908f;  // >= |r'| (1 + 2^-8 and the square root's rounding)
-                        float rest = 0.5f * (rn - cw2 * wv * wv);
-                        uint32_t u[3];
-#pragma unroll
-                        for (int x = 0; x < 3; ++x) {
-                            const __nv_bfloat16 h = __float2bfloat16_rn(rest);
-                            u[x] = (uint32_t)__bfloat16_as_ushort(__hneg(h));
-                            rest -= __bfloat162float(h);
-                        }
-                        *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, nchunk_data)) =
-                            make_uint4(u[0] | (u[1] << 16), u[2] | (bf16_bits_up(wv) << 16), 0u, 0u);
+                qn += __shfl_xor_sync(0xffffffffu, qn, 1);
+                n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
+                if (pq >= 0) {
+                    const float t = a.thr[pq];
+                    if (t < 3.0e38f) {
+                        const float nq = sqrtf(n2) * 1.000001f;
+                        const float av = sqrtf(fmaxf(t, 0.0f) * 1.00001f) * 1.000001f + kBeta * nq;
+                        P = 0.5f * (qn - (av * av + g.eps * nq * nq));
+                        H = av * kBeta + g.eps * nq;
                     } else {
-                        // past the end of the chunk: a row no visitor can admit (score -1e30)
-                        for (int c = 0; c < nchunk_data; ++c) *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, c)) = make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, nchunk_data)) = make_uint4(bf16_bits_rn(-1.0e30f), 0u, 0u, 0u);
+                        P = __int_as_float(0xff800000);  // no cutoff: every row of the list is a candidate
                     }
-                    for (int c = nchunk_data + 1; c < nchunk; ++c) *reinterpret_cast<uint4*>(chunk_ptr(sb, g.tn, tid, c)) = make_uint4(0, 0, 0, 0);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&b_full[st])) : "memory");
+                for (int c = nchunk_data + part; c < nchunk; c += 2) {  // the extra K slots (1, 1, 1, H), then zero padding
+                    uint4 o = make_uint4(0, 0, 0, 0);
+                    if (c == nchunk_data && pq >= 0) { o.x = 0x3F803F80u; o.y = 0x3F80u | (bf16_bits_up(H) << 16); }
+                    *chunk_at(arow, axs, a_stride, c) = o;
+                }
+                if (part == 0) { s_P[islot][i] = P; s_pq[islot][i] = pq; s_hi[islot][i] = g.residual ? vq : d.list; }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // operand stores -> visible to the tensor core
             }
-        } else if (warp < kDecodeWarps + kEpiWarps) {
-            // ---- epilogue: one visitor per thread (tensor-memory lane), half of the tile's columns per warp ----
-            const int e = warp - kDecodeWarps, quad = e & 3, half = e >> 2;  // warp % 4 == quad: the lanes this warp may read
-            const int i = quad * 32 + lane;
-            const float P = s_P[i];
-            const int pq = s_pq[i];
-            const uint64_t hi_word = (uint64_t)(uint32_t)s_vq[i] << 32;
-            const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-            const int cols = g.tn >> 1;  // per warp
-            for (int t = 0; t < ntiles && !failed; ++t, ++it) {
-                const uint32_t acc = it & 1u;
-                if (!__all_sync(0xffffffffu, wait_or_abort(&acc_full[acc], (it >> 1) & 1u, abort_flag, limit))) { failed = true; break; }
+            mbar_arrive(&a_full[aslot]);
+            mbar_arrive(&vis_full[islot]);
+            // code rows of this warp group's tiles
+            for (int k = 0; k < d.ntiles; ++k) {
+                const uint32_t gi = it0 + (uint32_t)k;
+                // Tile -> warp group by stage (groups in use == stages): a group then meets the phases of its stage's
+                // barriers one after the other, never two apart, which parity waits could not tell from each other.
+                if ((int)(gi % (uint32_t)NS) != grp) continue;
+                const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+                if (!__all_sync(0xffffffffu, wait_or_abort(&b_empty[st], (use & 1u) ^ 1u, abort_flag, limit))) { failed = true; break; }
+                unsigned char* rowbase = s_b + st * b_bytes + (size_t)lt * 128;
+                const long long r = d.r0 + (long long)k * TN + lt;
+                if (r < d.r1) {
+                    const size_t lr = (size_t)(r - a.row_base);
+                    const uint2 aug = __ldg(g.row_aug + lr);
+                    decode_row<DSUB, M>(a.codes + lr * a.m, a.m, a.k, s_tab, rowbase, xs, b_stride);
+                    *chunk_at(rowbase, xs, b_stride, nchunk_data) = make_uint4(aug.x, aug.y, 0u, 0u);
+                } else {
+                    // past the end of the chunk: a row no visitor can admit (score -1e30)
+                    for (int c = 0; c < nchunk_data; ++c) *chunk_at(rowbase, xs, b_stride, c) = make_uint4(0, 0, 0, 0);
+                    *chunk_at(rowbase, xs, b_stride, nchunk_data) = make_uint4(bf16_bits_rn(-1.0e30f), 0u, 0u, 0u);
+                }
+                for (int c = nchunk_data + 1; c < nchunk; ++c) *chunk_at(rowbase, xs, b_stride, c) = make_uint4(0, 0, 0, 0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&b_full[st]);
+            }
+            if (failed) break;
+            it0 += (uint32_t)d.ntiles;
+            mbar_arrive(&item_empty[islot]);
+        }
+    } else if (warp < kDecodeWarps + kEpiWarps) {
+        // ---- epilogue: one visitor per thread (tensor-memory lane), all 128 rows of every second tile ----
+        const int e = warp - kDecodeWarps, quad = warp & 3, eg = e >> 2;  // warp % 4 == quad: the tensor-memory lanes this warp may read
+        const int i = quad * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+        uint32_t* queue = s_queue[e];
+        uint32_t it0 = 0;
+        for (uint32_t n = 0;; ++n) {
+            const int islot = n % kItemRing;
+            if (!__all_sync(0xffffffffu, wait_or_abort(&item_full[islot], (n / kItemRing) & 1u, abort_flag, limit))) { failed = true; break; }
+            const ItemDesc d = s_desc[islot];
+            if (d.stop) break;
+            if (!__all_sync(0xffffffffu, wait_or_abort(&vis_full[islot], (n / kItemRing) & 1u, abort_flag, limit))) { failed = true; break; }
+            const float P = s_P[islot][i];
+            // pushes the queued survivors of this item to their visitors' pools
+            auto flush = [&]() {
+                __syncwarp();
+                const int cnt = min(s_qcnt[e], kQueueCap);
+                for (int x = lane; x < cnt; x += 32) {
+                    const uint32_t en = queue[x];
+                    const int vi = (int)(en >> 24);
+                    const int pq = s_pq[islot][vi];
+                    const int slot = atomicAdd(&a.pool_cnt[pq], 1);
+                    if (slot < a.pool_cap)
+                        a.pool[(size_t)pq * a.pool_cap + slot] = ((uint64_t)(uint32_t)s_hi[islot][vi] << 32) | (uint32_t)(d.r0 + (en & 0xFFFFFFu));
+                }
+                __syncwarp();
+                if (lane == 0) s_qcnt[e] = 0;
+                __syncwarp();
+            };
+            for (int k = 0; k < d.ntiles; ++k) {
+                const uint32_t gi = it0 + (uint32_t)k;
+                if ((int)(gi & 1u) != eg) continue;
+                const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+                if (!__all_sync(0xffffffffu, wait_or_abort(&acc_full[st], use & 1u, abort_flag, limit))) { failed = true; break; }
                 tc_fence_after();
-                const long long rbase = r0 + (long long)t * g.tn + half * cols;
-                for (int cb = 0; cb < cols; cb += 64) {
-                    uint32_t v0[32], v1[32];
+                const uint32_t rel0 = (uint32_t)k * TN;       // tile's first row, relative to r0
+                const uint32_t nrows = (uint32_t)(d.r1 - d.r0);  // rows of the item
+                for (int cb = 0; cb < TN; cb += 32) {
+                    uint32_t v[32];
                     __syncwarp();
-                    tmem_ld32(lane_addr + (uint32_t)(acc * g.tn + half * cols + cb), v0);
-                    tmem_ld32(lane_addr + (uint32_t)(acc * g.tn + half * cols + cb + 32), v1);
+                    tmem_ld32(lane_addr + st * TN + (uint32_t)cb, v);
                     tmem_ld_wait();
-                    if (cb + 64 >= cols) {  // the accumulator is in registers: hand it back before the comparisons
+                    if (cb + 32 >= TN) {  // the accumulator is in registers: hand it back before the comparisons
                         tc_fence_before();
-                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+                        mbar_arrive(&acc_empty[st]);
                     }
+                    float m4[4];
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        const uint32_t* v = hh ? v1 : v0;
-                        float m = __uint_as_float(v[0]);
+                    for (int j = 0; j < 4; ++j) m4[j] = __uint_as_float(v[j]);
 #pragma unroll
-                        for (int j = 1; j < 32; ++j) m = fmaxf(m, __uint_as_float(v[j]));
-                        if (m >= P) {  // rare: a survivor among these 32 rows
+                    for (int j = 4; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+                    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                    if (mx >= P) {  // a survivor among these 32 rows
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const long long r = rbase + cb + hh * 32 + j;
-                                if (__uint_as_float(v[j]) >= P && r < r1) {  // r >= r1: padding rows of the last tile
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t rel = rel0 + (uint32_t)(cb + j);
+                            if (__uint_as_float(v[j]) >= P && rel < nrows) {  // rel >= nrows: padding rows of the last tile
+                                ++passes;
+                                const uint32_t en = ((uint32_t)i << 24) | rel;
+                                const int pos = atomicAdd(&s_qcnt[e], 1);
+                                if (pos < kQueueCap) {
+                                    queue[pos] = en;
+                                } else {  // queue full (a visitor without cutoff admits whole lists): straight to the pool
+                                    const int pq = s_pq[islot][i];
                                     const int slot = atomicAdd(&a.pool_cnt[pq], 1);
-                                    if (slot < a.pool_cap) a.pool[(size_t)pq * a.pool_cap + slot] = hi_word | (uint32_t)r;
-                                    ++passes;
+                                    if (slot < a.pool_cap)
+                                        a.pool[(size_t)pq * a.pool_cap + slot] = ((uint64_t)(uint32_t)s_hi[islot][i] << 32) | (uint32_t)(d.r0 + rel);
                                 }
                             }
                         }
                     }
                 }
+                __syncwarp();
+                if (s_qcnt[e] >= kQueueCap / 2) flush();  // warp-uniform: read after the barrier
             }
-        } else if (lane == 0) {
-            // ---- MMA issuer ----
-            for (int t = 0; t < ntiles && !failed; ++t, ++it) {
-                const uint32_t st = it & 1u;
-                if (!wait_or_abort(&b_full[st], (it >> 1) & 1u, abort_flag, limit)) { failed = true; break; }
-                if (!wait_or_abort(&acc_empty[st], ((it >> 1) & 1u) ^ 1u, abort_flag, limit)) { failed = true; break; }
-                if (g.skip_mma) continue;  // test hook: nothing is issued, nothing completes, every waiting role gives up
-                tc_fence_after();
-                const uint32_t sa = smem_u32(s_a), sb = smem_u32(s_b + st * b_bytes);
-                for (int ka = 0; ka < g.katoms; ++ka) {
-                    const int ksteps = min(4, (g.kp - ka * 64) >> 4);
-                    for (int kk = 0; kk < ksteps; ++kk)
-                        umma_bf16(tmem + (uint32_t)(st * g.tn), make_sw128_desc(sa + ka * TV * 128 + kk * 32),
-                                  make_sw128_desc(sb + ka * g.tn * 128 + kk * 32), idesc, (ka | kk) ? 1u : 0u);
+            if (failed) break;
+            flush();
+            it0 += (uint32_t)d.ntiles;
+            mbar_arrive(&item_empty[islot]);
+        }
+    } else if (warp == kWarpMma) {
+        // ---- MMA issuer (one lane) ----
+        if (lane == 0) {
+            const uint32_t idesc = idesc_bf16(TV, TN);
+            uint32_t it0 = 0;
+            for (uint32_t n = 0;; ++n) {
+                const int islot = n % kItemRing;
+                if (!wait_or_abort(&item_full[islot], (n / kItemRing) & 1u, abort_flag, limit)) { failed = true; break; }
+                const ItemDesc d = s_desc[islot];
+                if (d.stop) break;
+                const int aslot = n % NA;
+                if (!wait_or_abort(&a_full[aslot], (n / NA) & 1u, abort_flag, limit)) { failed = true; break; }
+                const uint32_t sa = smem_u32(s_a + aslot * a_bytes);
+                for (int k = 0; k < d.ntiles; ++k) {
+                    const uint32_t gi = it0 + (uint32_t)k;
+                    const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+                    if (!wait_or_abort(&b_full[st], use & 1u, abort_flag, limit)) { failed = true; break; }
+                    if (!wait_or_abort(&acc_empty[st], (use & 1u) ^ 1u, abort_flag, limit)) { failed = true; break; }
+                    if (g.skip_mma) continue;  // test hook: nothing is issued or committed, so the waiting roles give up
+                    tc_fence_after();
+                    const uint32_t sb = smem_u32(s_b + st * b_bytes);
+                    for (int ka = 0; ka < g.katoms; ++ka) {
+                        const int ksteps = min(4, (g.kp - ka * 64) >> 4);
+                        for (int kk = 0; kk < ksteps; ++kk)
+                            umma_bf16(tmem + st * TN, make_sw128_desc(sa + ka * a_stride + kk * 32),
+                                      make_sw128_desc(sb + ka * b_stride + kk * 32), idesc, (ka | kk) ? 1u : 0u);
+                    }
+                    umma_commit(&acc_full[st]);
+                    umma_commit(&b_empty[st]);
                 }
-                umma_commit(&acc_full[st]);
-                umma_commit(&b_empty[st]);
+                if (failed) break;
+                if (!g.skip_mma) umma_commit(&a_empty[aslot]);  // the query tile may be rebuilt once these MMAs have read it
+                it0 += (uint32_t)d.ntiles;
+                mbar_arrive(&item_empty[islot]);
             }
         }
-        if (failed) *abort_flag = 1;
     }
-    if (failed) atomicExch(g.status, 1);
+    if (failed) { *abort_flag = 1; atomicExch(g.status, 1); }
     if (passes) atomicAdd(&a.counters[3], passes);
     tc_fence_before();
     __syncthreads();
     __syncwarp();
-    if (warp == 0) tmem_dealloc(tmem, (uint32_t)(2 * g.tn));
+    if (warp == 0) tmem_dealloc(tmem, tmem_cols);
+}
+
+// The extra K slots of every code row, computed once per index: |rt|^2 of the row's codewords rounded to bf16.
+template <int DSUB>
+__global__ void k_row_aug(const uint8_t* __restrict__ codes, long long rows, int m, int k, const float* __restrict__ codebook,
+                          float cw2, uint2* __restrict__ out) {
+    extern __shared__ float s_n2[];  // [m * k]: squared norm of every rounded codeword
+    for (int e = threadIdx.x; e < m * k; e += blockDim.x) {
+        float n2 = 0.0f;
+#pragma unroll
+        for (int d = 0; d < DSUB; ++d) {
+            const float v = __bfloat162float(__float2bfloat16_rn(__ldg(codebook + (size_t)e * DSUB + d)));
+            n2 = fmaf(v, v, n2);
+        }
+        s_n2[e] = n2;
+    }
+    __syncthreads();
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x) {
+        const uint8_t* row = codes + (size_t)r * m;
+        float rn = 0.0f;
+        for (int j = 0; j < m; ++j) rn += s_n2[j * k + __ldg(row + j)];
+        out[r] = row_aug_words(rn, cw2);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -500,53 +625,111 @@ __global__ void __launch_bounds__(kRescoreThreads) k_select_rescore(const Rescor
     if (g.out_count && threadIdx.x == 0) g.out_count[q] = keep;
 }
 
-size_t tc_scan_smem(int dim, int m, int k, int tn) {
+// Shared-memory plan of k_scan_tc for a shape: query-tile slots, row-tile stages and the dynamic bytes; false when the
+// shape is outside the kernel's range or does not fit.
+bool tc_scan_plan(int dim, int m, int k, int* na, int* ns, size_t* bytes) {
+    if (m <= 0 || dim <= 0 || dim % m != 0) return false;
     const int dsub = dim / m;
+    if (!(dsub == 2 || dsub == 4 || dsub == 8) || dim % 8 != 0 || m % 4 != 0 || k > 256 || k < 1) return false;
     const int kp = (dim + kAugSlots + 15) / 16 * 16;
     const int katoms = (kp + 63) / 64;
-    return (size_t)katoms * TV * 128 + 2 * (size_t)katoms * tn * 128 + (size_t)m * k * dsub * 2 + (size_t)dim * 4 + 1024;
+    const size_t a_bytes = (size_t)katoms * TV * 128, b_bytes = (size_t)katoms * TN * 128, tab = (size_t)m * k * dsub * 2;
+    const size_t budget = (size_t)218 * 1024;  // dynamic part; ~11 KB of static shared memory and the 1 KB alignment come on top
+    for (int a_slots = 2; a_slots >= 1; --a_slots) {
+        if (tab + a_slots * a_bytes + 2 * b_bytes > budget) continue;
+        int stages = (int)((budget - tab - a_slots * a_bytes) / b_bytes);
+        stages = stages > kDecodeGroups ? kDecodeGroups : stages;  // one decode warp group per stage
+        *na = a_slots; *ns = stages; *bytes = tab + a_slots * a_bytes + stages * b_bytes + 1024;
+        return true;
+    }
+    return false;
 }
 
 }  // namespace
 
-// Rows per tile: 256 when the operands fit, else 128; 0 = the shape is outside this kernel's range.
-int scan_tc_tile_rows(int dim, int m, int k) {
-    if (m <= 0 || dim % m != 0) return 0;
-    const int dsub = dim / m;
-    if (!(dsub == 2 || dsub == 4 || dsub == 8) || dim % 8 != 0 || m % 4 != 0 || k > 256 || k < 1) return 0;
-    for (int tn : {256, 128})
-        if (tc_scan_smem(dim, m, k, tn) <= (size_t)222 * 1024) return tn;  // dynamic part; ~2 KB of static shared memory come on top
-    return 0;
+bool scan_tc_supported(int dim, int m, int k) {
+    int na, ns; size_t bytes;
+    return tc_scan_plan(dim, m, k, &na, &ns, &bytes);
 }
 
+float scan_tc_eps(int dim) {
+    const int kp = (dim + kAugSlots + 15) / 16 * 16;
+    return (float)kp * (1.0f / 4194304.0f) * 2.0f;  // kp * 2^-22 * 2: tensor-core accumulation plus the fp32 norms
+}
+
+psb_status launch_row_aug(const uint8_t* d_codes, long long rows, int dim, int m, int k, const float* d_codebook, void* d_out,
+                          cudaStream_t s) {
+    if (rows <= 0) return PSB_OK;
+    const int dsub = dim / m;
+    const float cw2 = kBeta * kBeta + scan_tc_eps(dim);
+    const size_t smem = (size_t)m * k * sizeof(float);
+    const unsigned grid = (unsigned)std::min<long long>((rows + 255) / 256, 148 * 16);
+#define PSB_AUG(D)                                                                                                      \
+    do {                                                                                                                \
+        if (smem > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(k_row_aug<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        k_row_aug<D><<<grid, 256, smem, s>>>(d_codes, rows, m, k, d_codebook, cw2, static_cast<uint2*>(d_out));          \
+    } while (0)
+    if (dsub == 2) PSB_AUG(2);
+    else if (dsub == 4) PSB_AUG(4);
+    else if (dsub == 8) PSB_AUG(8);
+    else return fail(PSB_UNSUPPORTED_SHAPE, "tensor-core scan does not support this shape");
+#undef PSB_AUG
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+namespace {
+template <int DSUB, int M>
+psb_status run_scan_tc(const ScanTcArgs& g, unsigned grid, size_t smem, cudaStream_t s) {
+    PSB_CUDA(cudaFuncSetAttribute(k_scan_tc<DSUB, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_scan_tc<DSUB, M><<<grid, kTcScanThreads, smem, s>>>(g);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+}  // namespace
+
 psb_status launch_scan_tc(const ScanTcLaunch& L, cudaStream_t s) {
-    const int tn = scan_tc_tile_rows(L.dim, L.m, L.k);
-    if (tn == 0) return fail(PSB_UNSUPPORTED_SHAPE, "tensor-core scan does not support this shape");
+    int na = 0, ns = 0;
+    size_t smem = 0;
+    if (!tc_scan_plan(L.dim, L.m, L.k, &na, &ns, &smem)) return fail(PSB_UNSUPPORTED_SHAPE, "tensor-core scan does not support this shape");
+    if (!L.row_aug) return fail(PSB_INTERNAL, "tensor-core scan: the per-row terms are missing");
     ScanTcArgs g;
     g.a.lut = nullptr; g.a.lut_div = L.lut_div; g.a.tree = 0; g.a.codes = L.codes; g.a.offsets = L.offsets; g.a.row_base = L.row_base;
     g.a.row_delta = nullptr; g.a.nlist = L.nlist; g.a.m = L.m; g.a.k = L.k; g.a.vis_count = L.vis_count; g.a.vis_off = L.vis_off;
     g.a.visitors = L.visitors; g.a.item_off = L.item_off; g.a.thr = L.thr; g.a.pool_cnt = L.pool_cnt; g.a.pool = L.pool;
     g.a.pool_cap = L.pool_cap; g.a.work_cursor = L.work_cursor; g.a.counters = L.counters; g.a.chunk_rows = L.chunk_rows;
     g.a.reserve_ctas = L.reserve_ctas;
-    g.queries = L.queries; g.centroids = L.centroids; g.codebook = L.codebook; g.probes = L.probes;
-    g.dim = L.dim; g.kp = (L.dim + kAugSlots + 15) / 16 * 16; g.katoms = (g.kp + 63) / 64; g.tn = tn; g.residual = L.residual ? 1 : 0;
-    g.eps = (float)g.kp * (1.0f / 4194304.0f) * 2.0f;  // kp * 2^-22 * 2: tensor-core accumulation plus the fp32 norms
+    g.queries = L.queries; g.centroids = L.centroids; g.codebook = L.codebook; g.row_aug = static_cast<const uint2*>(L.row_aug);
+    g.dim = L.dim; g.kp = (L.dim + kAugSlots + 15) / 16 * 16; g.katoms = (g.kp + 63) / 64; g.na = na; g.ns = ns;
+    g.residual = L.residual ? 1 : 0;
+    g.eps = scan_tc_eps(L.dim);
     g.status = L.status; g.wait_limit = L.wait_limit > 0 ? L.wait_limit : kWaitLimit; g.skip_mma = L.skip_mma;
-    const size_t smem = tc_scan_smem(L.dim, L.m, L.k, tn);
     const unsigned grid = scan_grid(L.sm_count, L.reserve_ctas);
     const int dsub = L.dim / L.m;
-#define PSB_TC_LAUNCH(D)                                                                                              \
-    do {                                                                                                              \
-        PSB_CUDA(cudaFuncSetAttribute(k_scan_tc<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));         \
-        k_scan_tc<D><<<grid, kTcScanThreads, smem, s>>>(g);                                                           \
-    } while (0)
-    if (dsub == 2) PSB_TC_LAUNCH(2);
-    else if (dsub == 4) PSB_TC_LAUNCH(4);
-    else PSB_TC_LAUNCH(8);
-#undef PSB_TC_LAUNCH
-    count_launch();
-    PSB_LAUNCH_CHECK();
-    return PSB_OK;
+    if (dsub == 2) {
+        switch (L.m) {
+            case 16: return run_scan_tc<2, 16>(g, grid, smem, s);
+            case 32: return run_scan_tc<2, 32>(g, grid, smem, s);
+            case 48: return run_scan_tc<2, 48>(g, grid, smem, s);
+            case 64: return run_scan_tc<2, 64>(g, grid, smem, s);
+            default: return run_scan_tc<2, 0>(g, grid, smem, s);
+        }
+    } else if (dsub == 4) {
+        switch (L.m) {
+            case 8: return run_scan_tc<4, 8>(g, grid, smem, s);
+            case 16: return run_scan_tc<4, 16>(g, grid, smem, s);
+            case 32: return run_scan_tc<4, 32>(g, grid, smem, s);
+            default: return run_scan_tc<4, 0>(g, grid, smem, s);
+        }
+    } else {
+        switch (L.m) {
+            case 8: return run_scan_tc<8, 8>(g, grid, smem, s);
+            case 16: return run_scan_tc<8, 16>(g, grid, smem, s);
+            default: return run_scan_tc<8, 0>(g, grid, smem, s);
+        }
+    }
 }
 
 namespace {

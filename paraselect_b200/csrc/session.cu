@@ -183,7 +183,7 @@ struct psb_session {
     int list_begin = 0, list_end = 0;
     long long row_base = 0, shard_rows = 0;
     // device copies
-    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta, exact_cache;
+    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta, exact_cache, row_aug;
     bool striped = false;          // shard holds a slice of every list (options.list_global_begin)
     // exact rows
     int exact_elem = 0;            // 4 = fp32, 1 = u8, 0 = rerank disabled
@@ -244,7 +244,7 @@ struct psb_session {
         ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
         ix.row_delta = striped ? row_delta.as<long long>() : nullptr;
         ix.residual = opt.adc_mode == 1;
-        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim;
+        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim; ix.row_aug = row_aug.p;
         return ix;
     }
     // Which index-wide rows the exact store and the id table of this session hold.
@@ -663,6 +663,11 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     const size_t cb_bytes = sizeof(float) * (size_t)s->m * s->k * (s->dim / s->m);
     PSB_TRY(s->codebook.reserve(cb_bytes));
     PSB_CUDA(cudaMemcpyAsync(s->codebook.p, index->pq.codebook, cb_bytes, cudaMemcpyHostToDevice, st));
+    // per-row terms of the tensor-core scan (8 bytes per code row), once per index
+    if ((opt.scan_mode == 0 || opt.scan_mode == 3) && s->shard_rows > 0 && scan_tc_supported(s->dim, s->m, s->k)) {
+        PSB_TRY(s->row_aug.reserve((size_t)s->shard_rows * 8));
+        PSB_TRY(launch_row_aug(s->codes.as<uint8_t>(), s->shard_rows, s->dim, s->m, s->k, s->codebook.as<float>(), s->row_aug.p, st));
+    }
     {   // per sub-quantiser the largest codeword norm (residual-mode table builder)
         const int dsub = s->dim / s->m;
         std::vector<float> mx((size_t)s->m, 0.0f);
