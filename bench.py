@@ -272,6 +272,8 @@ def main():
                          "headline metric names: an extra data point)")
     ap.add_argument("--reserve-sms", type=int, default=8, help="N > 1: SMs the scan's persistent grid leaves to the collectives")
     ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
+    ap.add_argument("--gather-ctas", type=int, default=0, help="CTAs of the PCIe gather kernel beside a scan (0 = library default)")
+    ap.add_argument("--n1-reserve-sms", type=int, default=-1, help="N = 1: SMs the scan leaves to the gather kernel (-1 = auto)")
     args = ap.parse_args()
     claim_stdout()
 
@@ -335,7 +337,8 @@ def main():
 
         t0 = time.time()
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           residual=bool(cfg.get("residual")),
+                           residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas,
+                           reserve_sms=max(0, args.n1_reserve_sms),
                            exact_mode={"staged": api.EXACT_HOST_STAGED, "cached": api.EXACT_HOST_CACHED}.get(args.exact_mode,
                                                                                                             api.EXACT_HOST_MAPPED))
         log("session created in %.1fs" % (time.time() - t0))
@@ -446,7 +449,13 @@ def main():
                        scan=round(stats["pq_adc_scan_ms"], 3), rerank=round(stats["pq_rerank_ms"], 3),
                        map_ids=round(stats["pq_map_ids_ms"], 3), h2d=round(stats["h2d_ms"], 3), d2h=round(stats["d2h_ms"], 3)),
         counters=dict(scanned_codes_per_step=int(S * launches_per_step), admitted_per_step=int(c["threshold_candidates"] / max(1, args.steps)),
-                      fallback_queries_per_step=c["fallback_queries"] / max(1, args.steps)),
+                      fallback_queries_per_step=c["fallback_queries"] / max(1, args.steps),
+                      prefilter_survivors_per_step=int(c["prefilter_survivors"] / max(1, args.steps)),
+                      tc_tiles_per_step=int(c["tc_tiles"] / max(1, args.steps)),
+                      staged_host_gather_gbs=round(c["staged_gather_bytes"] / max(1e-9, c["staged_gather_ms"] * 1e-3) / 1e9, 1) if c["staged_gather_ms"] > 0 else None,
+                      tc_issuer_wait_cycles_per_tile=dict(item=round(c["tc_wait_item_cycles"] / max(1, c["tc_tiles"]), 1),
+                                                          rows=round(c["tc_wait_rows_cycles"] / max(1, c["tc_tiles"]), 1),
+                                                          accumulator=round(c["tc_wait_acc_cycles"] / max(1, c["tc_tiles"]), 1))),
         parity=parity,
         result_checksum=int(np.bitwise_xor.reduce((e2e_ids.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)).ravel())
                             & np.uint64((1 << 62) - 1)),

@@ -153,7 +153,7 @@ typedef struct psb_options {
                            not depend on it: a too-tight cutoff only sends more queries to the exact fallback. */
     int pipeline_parts; /* sub-batches per batch of the overlapped pipeline (default 4; accepted 2..32) */
     int even_cuts;      /* 1 = equal sub-batches also with the staged transport (default: a short last sub-batch) */
-    int gather_ctas;    /* CTAs of the PCIe row-gather kernel when it runs beside a scan (default 32) */
+    int gather_ctas;    /* 128-thread CTAs of the PCIe row-gather kernel when it runs beside a scan (default: two per SM) */
     int tc_min_visitors;/* lists with fewer visiting queries than this stay with the SIMT scan (default 1: none do) */
     /* Test hooks of the time-out path of the tensor-core scan (leave 0): test_wait_limit = polls before a device-side wait
        gives up; test_skip_mma = 1 makes the issuing warp skip its tcgen05.mma so that every waiting role runs into that limit
@@ -188,6 +188,14 @@ typedef struct psb_stats {
     int batches;
     int coarse_fallback_queries;    /* queries the tensor-core coarse filter handed to the exact per-query kernel */
     long long prefilter_survivors;  /* (row, query) pairs the tensor-core scan filter let through to the exact re-scoring */
+    /* Diagnostics of the tensor-core scan (psb_session_counters only): SM cycles its MMA-issuing threads spent waiting, summed
+       over CTAs - for the next work item and its query tile, for decoded code rows, for a free accumulator - and the tiles
+       (128 visitors x 128 rows) they issued. */
+    long long tc_wait_item_cycles, tc_wait_rows_cycles, tc_wait_acc_cycles, tc_tiles;
+    /* Staged rerank transport (psb_session_counters only): host time spent gathering exact rows into the pinned rings and the
+       bytes gathered, since the last reset. */
+    double staged_gather_ms;
+    long long staged_gather_bytes;
     int reserved[4];
 } psb_stats;
 

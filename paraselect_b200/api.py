@@ -85,6 +85,8 @@ class Stats(C.Structure):
                 ("kernel_launches", C.c_longlong), ("scan_kernel_ms", C.c_double), ("scan_kernel_launches", C.c_longlong),
                 ("coarse_gemm_ms", C.c_double), ("coarse_gemm_launches", C.c_longlong),
                 ("batches", C.c_int), ("coarse_fallback_queries", C.c_int), ("prefilter_survivors", C.c_longlong),
+                ("tc_wait_item_cycles", C.c_longlong), ("tc_wait_rows_cycles", C.c_longlong), ("tc_wait_acc_cycles", C.c_longlong),
+                ("tc_tiles", C.c_longlong), ("staged_gather_ms", C.c_double), ("staged_gather_bytes", C.c_longlong),
                 ("reserved", C.c_int * 4)]
 
     def as_dict(self):

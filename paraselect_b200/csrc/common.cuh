@@ -63,6 +63,16 @@ __host__ __device__ __forceinline__ uint32_t key_idx(uint64_t k) { return static
 constexpr uint64_t KEY_MAX = ~0ull;
 
 #ifdef __CUDACC__
+// Asks for the maximum shared-memory carve-out for a kernel, whether or not it uses much shared memory.  An SM runs kernels of
+// one carve-out at a time; the scan, coarse and selection kernels need nearly all of it, so every kernel that may run beside
+// them on the other stream of the overlapped pipeline (and the small kernels queued between them) asks for the same
+// carve-out - otherwise the SMs drain between kernels instead of sharing.
+template <typename F>
+inline psb_status prefer_max_shared(F kernel) {
+    PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    return PSB_OK;
+}
+
 // ---- device: block-wide bitonic sort of n (power of two) keys in shared memory, ascending ---------
 template <typename K>
 __device__ __forceinline__ void block_bitonic_sort(K* s, int n) {

@@ -1024,6 +1024,7 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
                     int nprobe, int stage1_k, cudaStream_t s) {
     const size_t smem = (size_t)ix.m * ix.k * sizeof(float) + kSeedBuf * sizeof(uint32_t) + ((size_t)nprobe + 1) * sizeof(int);
     PSB_TRY(set_smem(k_seed_threshold<M>, smem));
+    PSB_TRY(prefer_max_shared(k_seed_threshold<M>));
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
                                                          stage1_k, ws.pool_cap, ws.thr, ix.residual ? 1 : 0,
@@ -1041,6 +1042,7 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     while (buf_n < stage1_k + kFallbackThreads) buf_n <<= 1;
     const size_t smem = (size_t)buf_n * 8 + (size_t)ix.m * ix.k * sizeof(float);
     PSB_TRY(set_smem(k_exact_fallback<M>, smem));
+    PSB_TRY(prefer_max_shared(k_exact_fallback<M>));
     k_exact_fallback<M><<<sm_count, kFallbackThreads, smem, s>>>(
         d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.row_delta, ix.m, ix.k,
         stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters,
@@ -1049,6 +1051,7 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     PSB_LAUNCH_CHECK();
     const size_t msmem = (size_t)buf_n * 8;
     PSB_TRY(set_smem(k_fallback_merge, msmem));
+    PSB_TRY(prefer_max_shared(k_fallback_merge));
     k_fallback_merge<<<kFallbackCap, kFallbackThreads, msmem, s>>>(ws.fallback_partial, stage1_k, buf_n, ws.fail_list, ws.n_fail,
                                                                   d_rows, d_dist, d_count, ws.counters);
     count_launch();
@@ -1072,6 +1075,7 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
 psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
                             float* d_lut, cudaStream_t s) {
     if (nq <= 0) return PSB_OK;
+    PSB_TRY(prefer_max_shared(k_build_lut));
     k_build_lut<<<nq, 256, (size_t)dim * sizeof(float), s>>>(d_queries, dim, d_codebook, m, k, d_lut);
     count_launch();
     PSB_LAUNCH_CHECK();
@@ -1094,6 +1098,7 @@ psb_status launch_build_lut_residual(const float* d_queries, int nq, int dim, co
     if (nq <= 0) return PSB_OK;
     const long long pairs = (long long)nq * nprobe;
     if (pairs > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "too many (query, probe) pairs in one batch");
+    PSB_TRY(prefer_max_shared(k_build_lut_residual));
     k_build_lut_residual<<<(unsigned)pairs, 256, (size_t)dim * sizeof(float), s>>>(d_queries, dim, d_probes, nprobe,
                                                                                    d_centroids, nlist, d_codebook, m, k, d_lut);
     count_launch();
@@ -1108,6 +1113,7 @@ psb_status run_build_tables_residual(const float* d_queries, int nq, int dim, co
     if constexpr (M <= 0) {
         return fail(PSB_INTERNAL, "fused residual tables need a templated M");
     } else {
+        PSB_TRY(prefer_max_shared(k_build_tables_residual<M>));
         k_build_tables_residual<M><<<(unsigned)((long long)nq * nprobe), 256, (size_t)dim * sizeof(float), s>>>(
             d_queries, dim, d_probes, nprobe, d_centroids, nlist, d_codebook, k, d_cb_maxnorm, d_lut, static_cast<__half*>(d_lut_h),
             d_scale);
@@ -1161,15 +1167,18 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     PSB_CUDA(cudaMemsetAsync(ws.fail_cursor, 0, sizeof(int), s));
     PSB_CUDA(cudaMemsetAsync(ws.work_cursor, 0, sizeof(unsigned long long), s));
     if (use_tc) PSB_CUDA(cudaMemsetAsync(ws.work_cursor_tc, 0, sizeof(unsigned long long), s));
+    PSB_TRY(prefer_max_shared(k_count_visitors));
     k_count_visitors<<<(nq * 32 + 255) / 256, 256, 0, s>>>(d_probes, nq, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                           ix.list_end, ws.vis_count, ws.q_rows, ws.counters);
     count_launch();
     PSB_LAUNCH_CHECK();
+    PSB_TRY(prefer_max_shared(k_scan_lists));
     k_scan_lists<<<1, 1024, 0, s>>>(ws.vis_count, ix.offsets, ix.nlist, group, kScanChunkRows, ws.vis_off,
                                     ws.item_off, ws.vis_cursor, 128, tc_min_vis, use_tc ? ws.item_off_tc : nullptr);
     count_launch();
     PSB_LAUNCH_CHECK();
     const long long pairs = (long long)nq * nprobe;
+    PSB_TRY(prefer_max_shared(k_fill_visitors));
     k_fill_visitors<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(d_probes, nq, nprobe, ix.nlist, ix.list_begin,
                                                                     ix.list_end, ws.vis_off, ws.vis_cursor, ws.visitors,
                                                                     ix.residual ? 1 : 0);
@@ -1186,6 +1195,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     a.work_cursor = ws.work_cursor; a.counters = ws.counters; a.chunk_rows = kScanChunkRows;
     a.reserve_ctas = ws.reserve_ctas;
     if (use_half && !ws.half_tables_ready && simt_needed) {
+        PSB_TRY(prefer_max_shared(k_lut_to_half));
         k_lut_to_half<<<(unsigned)tables, 256, 0, s>>>(d_lut, ix.m, ix.k, reinterpret_cast<__half*>(ws.lut_h), ws.lut_scale);
         count_launch();
         PSB_LAUNCH_CHECK();
@@ -1224,6 +1234,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     } else {
         const size_t smem = (size_t)ws.pool_cap * sizeof(uint64_t);
         PSB_TRY(set_smem(k_select_pool, smem));
+        PSB_TRY(prefer_max_shared(k_select_pool));
         k_select_pool<<<nq, kSelectThreads, smem, s>>>(ws.pool, ws.pool_cnt, ws.pool_cap, ws.q_rows, stage1_k, d_rows,
                                                        d_dist, d_count, ws.fail_list, ws.n_fail, ws.counters);
         count_launch();

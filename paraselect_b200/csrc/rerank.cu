@@ -44,9 +44,9 @@ __device__ __forceinline__ long long local_row(const RowMap& mp, long long r) {
 // to a local row (for a striped shard that is a binary search of 16 dependent loads - done for 32 candidates at once), then
 // the warp copies the rows four at a time, all four rows' loads issued before the first store, so that a few hundred KB
 // of PCIe reads stay in flight even on a small grid.
-__global__ void k_gather_rows(const unsigned char* __restrict__ src, RowMap mp, int row_bytes,
-                              const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
-                              const int* __restrict__ counts, unsigned char* __restrict__ stage) {
+__device__ __forceinline__ void gather_rows_body(const unsigned char* __restrict__ src, const RowMap& mp, int row_bytes,
+                                                 const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
+                                                 const int* __restrict__ counts, unsigned char* __restrict__ stage) {
     const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -93,6 +93,22 @@ __global__ void k_gather_rows(const unsigned char* __restrict__ src, RowMap mp, 
             }
         }
     }
+}
+
+__global__ void k_gather_rows(const unsigned char* __restrict__ src, RowMap mp, int row_bytes,
+                              const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
+                              const int* __restrict__ counts, unsigned char* __restrict__ stage) {
+    gather_rows_body(src, mp, row_bytes, cand, nq, candidate_count, candidate_stride, counts, stage);
+}
+// The same gather built to sit BESIDE a scan kernel that owns nearly a whole SM (one 576-thread CTA with ~55K registers and
+// ~200 KB of shared memory): 128-thread CTAs capped at 40 registers and no shared memory, two of which fit into what the
+// scan leaves of every SM.  Spread over all SMs they keep far more PCIe reads in flight than the link's bandwidth-delay
+// product while taking almost no issue slots (their warps wait on loads).
+__global__ void __launch_bounds__(256, 6) k_gather_rows_beside(const unsigned char* __restrict__ src, RowMap mp, int row_bytes,
+                                                               const int* __restrict__ cand, int nq, int candidate_count,
+                                                               int candidate_stride, const int* __restrict__ counts,
+                                                               unsigned char* __restrict__ stage) {
+    gather_rows_body(src, mp, row_bytes, cand, nq, candidate_count, candidate_stride, counts, stage);
 }
 
 // fp32 squared L2 by a half-warp (16 lanes), bit-identical to the AVX-512 kernel's order.
@@ -256,15 +272,6 @@ k_merge(const int* __restrict__ rows, const float* __restrict__ dist, int parts,
 
 }  // namespace
 
-// The rerank kernels ask for the maximum shared-memory carve-out although they use little or none: an SM can only run
-// kernels of one carve-out at a time, and the scan and coarse kernels they run beside (on the other stream of the
-// overlapped pipeline) need nearly all of it.  With the default carve-out the SMs would have to drain between them.
-template <typename F>
-psb_status prefer_max_shared(F kernel) {
-    PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-    return PSB_OK;
-}
-
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
                               void* d_stage, cudaStream_t s, int sm_count, int compact_ctas) {
@@ -272,15 +279,13 @@ psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int el
     const long long total = (long long)nq * candidate_count;
     PSB_TRY(prefer_max_shared(k_gather_rows));
     if (compact_ctas > 0) {
-        // Beside a scan kernel on the other stream of the overlapped pipeline: few, fat CTAs.  32 CTAs of 512 threads keep
-        // ~200 KB of row reads in flight - more than the PCIe bandwidth-delay product - while touching only 32 SMs, so the
-        // scan keeps most SMs to itself (its dynamic work queue shifts work away from the shared ones).
-        const int cap = compact_ctas;
-        long long blocks = (total * 32 + 511) / 512;
-        if (blocks > cap) blocks = cap;
-        k_gather_rows<<<(unsigned)blocks, 512, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
-                                                       d_candidates, nq, candidate_count, candidate_stride, d_counts,
-                                                       static_cast<unsigned char*>(d_stage));
+        // Beside a scan kernel on the other stream of the overlapped pipeline: small lean CTAs on every SM (compact_ctas of them).
+        PSB_TRY(prefer_max_shared(k_gather_rows_beside));
+        long long blocks = (total * 32 + 127) / 128;
+        if (blocks > compact_ctas) blocks = compact_ctas;
+        k_gather_rows_beside<<<(unsigned)blocks, 128, 0, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
+                                                              d_candidates, nq, candidate_count, candidate_stride, d_counts,
+                                                              static_cast<unsigned char*>(d_stage));
     } else {
         long long blocks = (total * 32 + 255) / 256;
         if (blocks > (long long)sm_count * 8) blocks = (long long)sm_count * 8;

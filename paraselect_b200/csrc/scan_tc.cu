@@ -44,16 +44,18 @@ namespace {
 
 constexpr int TV = 128;            // visitors per tile (UMMA M)
 constexpr int TN = 128;            // code rows per tile (UMMA N)
-constexpr int kDecodeGroups = 3;   // warps 0-11: three groups of four warps; group g decodes tiles g, g + 3, ... (one row per thread)
+constexpr int kDecodeGroups = 2;   // warps 0-7: two groups of four warps; group g decodes tiles g, g + 2, ... (one row per thread)
 constexpr int kDecodeWarps = 4 * kDecodeGroups;
-constexpr int kEpiGroups = 2;      // warps 12-19: two groups of four warps; group e reads the accumulators of tiles e, e + 2, ...
-constexpr int kEpiWarps = 4 * kEpiGroups;
-constexpr int kWarpMma = kDecodeWarps + kEpiWarps;  // warp 20: MMA issuer
-constexpr int kWarpSched = kWarpMma + 1;            // warp 21: fetches work items ahead of the others
+constexpr int kEpiGroups = 2;      // warps 8-15: two groups of four warps (one warp per tensor-memory lane quarter); group e reads
+constexpr int kEpiWarps = 4 * kEpiGroups;           // the accumulators of tiles e, e + 2, ...
+constexpr int kWarpMma = kDecodeWarps + kEpiWarps;  // warp 16: MMA issuer
+constexpr int kWarpSched = kWarpMma + 1;            // warp 17: fetches work items ahead of the others
+// 18 warps: 112 registers per thread, which the decode (two tiles of code words in flight) and the epilogue (two 32-column
+// accumulator loads in flight) both need.
 constexpr int kTcScanThreads = (kWarpSched + 1) * 32;
 constexpr int kProducers = kDecodeWarps * 32;
 constexpr int kItemRing = 4;       // work items in flight
-constexpr int kQueueCap = 128;     // survivors a warp collects before it pushes them to the pools
+constexpr int kQueueCap = 256;     // survivors a warp collects before it pushes them to the pools
 constexpr int kAugSlots = 4;
 constexpr float kBeta = 0.001953125f * 1.001f;  // 2^-9 (1 + 1e-3)
 
@@ -118,10 +120,27 @@ __device__ __forceinline__ uint2 row_aug_words(float rn, float cw2) {
     return make_uint2(u[0] | (u[1] << 16), u[2] | (bf16_bits_up(wv) << 16));
 }
 
-// One code row -> its bf16 operand row (data chunks only).  s_tab: [m][k] entries of DSUB bf16.
+// Code words of one row held in registers (templated M), so that the next tile's row can be fetched while this one is decoded.
+template <int M> struct RowCodes { uint32_t w[M > 0 ? M / 4 : 1]; };
+template <int M>
+__device__ __forceinline__ void load_codes(RowCodes<M>& c, const uint8_t* __restrict__ row) {
+    if constexpr (M > 0 && M % 16 == 0) {
+#pragma unroll
+        for (int i = 0; i < M / 16; ++i) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(row) + i);
+            c.w[4 * i] = x.x; c.w[4 * i + 1] = x.y; c.w[4 * i + 2] = x.z; c.w[4 * i + 3] = x.w;
+        }
+    } else if constexpr (M > 0) {
+#pragma unroll
+        for (int i = 0; i < M / 4; ++i) c.w[i] = __ldg(reinterpret_cast<const uint32_t*>(row) + i);
+    }
+}
+
+// One code row -> its bf16 operand row (data chunks only).  s_tab: [m][k] entries of DSUB bf16.  Templated M: the code words
+// come in registers; M = 0 (any m that is a multiple of 4): they are read from `row` as the loop goes.
 template <int DSUB, int M>
-__device__ __forceinline__ void decode_row(const uint8_t* __restrict__ row, int m_rt, int k, const unsigned char* __restrict__ s_tab,
-                                           unsigned char* rowbase, uint32_t xs, int atom_stride) {
+__device__ __forceinline__ void decode_row(const RowCodes<M>& codes, const uint8_t* __restrict__ row, int m_rt, int k,
+                                           const unsigned char* __restrict__ s_tab, unsigned char* rowbase, uint32_t xs, int atom_stride) {
     constexpr int EB = DSUB * 2;  // bytes per table entry
     const int kstride = k * EB;
     auto word = [&](uint32_t cw, int w) {  // code word w: sub-quantisers 4w .. 4w+3
@@ -147,21 +166,12 @@ __device__ __forceinline__ void decode_row(const uint8_t* __restrict__ row, int 
             *chunk_at(rowbase, xs, atom_stride, 4 * w + 3) = *reinterpret_cast<const uint4*>(t + 3 * kstride + (cw >> 24) * EB);
         }
     };
-    if constexpr (M > 0 && M % 16 == 0) {
-        uint4 c[M / 16];
+    if constexpr (M > 0) {
 #pragma unroll
-        for (int i = 0; i < M / 16; ++i) c[i] = __ldg(reinterpret_cast<const uint4*>(row) + i);
-#pragma unroll
-        for (int i = 0; i < M / 16; ++i) {
-            word(c[i].x, 4 * i); word(c[i].y, 4 * i + 1); word(c[i].z, 4 * i + 2); word(c[i].w, 4 * i + 3);
-            asm volatile("" ::: "memory");  // keeps the next group's table loads below this group's stores: bounded register use
+        for (int i = 0; i < M / 4; ++i) {
+            word(codes.w[i], i);
+            if ((i & 3) == 3) asm volatile("" ::: "memory");  // keeps later table loads below these stores: bounded register use
         }
-    } else if constexpr (M > 0) {
-        uint32_t c[M / 4];
-#pragma unroll
-        for (int i = 0; i < M / 4; ++i) c[i] = __ldg(reinterpret_cast<const uint32_t*>(row) + i);
-#pragma unroll
-        for (int i = 0; i < M / 4; ++i) word(c[i], i);
     } else {
         for (int w = 0; w < (m_rt >> 2); ++w) word(__ldg(reinterpret_cast<const uint32_t*>(row) + w), w);
     }
@@ -169,11 +179,11 @@ __device__ __forceinline__ void decode_row(const uint8_t* __restrict__ row, int 
 
 // Persistent, warp-specialised kernel without CTA-wide barriers in its main loop.  Work item = (list, chunk of rows, group
 // of up to 128 visiting queries); the roles hand items and tiles to one another through mbarriers:
-//   warp 21     scheduler: takes items off the global cursor, resolves them, fills a ring of item descriptors
-//   warps 0-11  producers: build the item's query tile (A operand, ring of `na` slots) and its per-visitor constants, then
-//               decode code rows into the ring of `ns` row tiles (B operand), three tiles in flight (one per warp group)
-//   warp 20     MMA issuer: kp / 16 tcgen05.mma per tile into accumulator `stage`, tcgen05.commit -> mbarriers
-//   warps 12-19 epilogue: tcgen05.ld the accumulator, one comparison per (visitor, row); survivors go to a per-warp queue in
+//   warp 17     scheduler: takes items off the global cursor, resolves them, fills a ring of item descriptors
+//   warps 0-7   producers: build the item's query tile (A operand, ring of `na` slots) and its per-visitor constants, then
+//               decode code rows into the ring of `ns` row tiles (B operand), one tile in flight per warp group
+//   warp 16     MMA issuer: kp / 16 tcgen05.mma per tile into accumulator `stage`, tcgen05.commit -> mbarriers
+//   warps 8-15  epilogue: tcgen05.ld the accumulator (two 32-column loads in flight), one comparison per (visitor, row); survivors go to a per-warp queue in
 //               shared memory that is pushed to the visitors' pools 32 at a time (one round of global atomics per push)
 template <int DSUB, int M>
 __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs g) {
@@ -209,7 +219,7 @@ __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs 
         for (int i = 0; i < 2; ++i) { mbar_init(&a_full[i], kProducers); mbar_init(&a_empty[i], 1); }
         for (int i = 0; i < 4; ++i) {
             mbar_init(&b_full[i], TN); mbar_init(&b_empty[i], 1);
-            mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128);
+            mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128);  // the four warps of one epilogue group
         }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -333,21 +343,32 @@ __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs 
             }
             mbar_arrive(&a_full[aslot]);
             mbar_arrive(&vis_full[islot]);
-            // code rows of this warp group's tiles
-            for (int k = 0; k < d.ntiles; ++k) {
+            // code rows of this warp group's tiles: tile k of the item has running number it0 + k and belongs to the group
+            // (it0 + k) % NS - groups in use == stages, so a group meets the phases of its stage's barriers one after the
+            // other, never two apart (parity waits could not tell those from each other).  The next tile's code words are
+            // fetched before the current tile is decoded.
+            int k = (int)(((uint32_t)grp + (uint32_t)NS - it0 % (uint32_t)NS) % (uint32_t)NS);
+            RowCodes<M> cur, nxt;
+            uint2 aug_cur = make_uint2(0, 0), aug_nxt = make_uint2(0, 0);
+            auto fetch = [&](int kk, RowCodes<M>& c, uint2& aug) {
+                const long long r = d.r0 + (long long)kk * TN + lt;
+                if (kk < d.ntiles && r < d.r1) {
+                    const size_t lr = (size_t)(r - a.row_base);
+                    aug = __ldg(g.row_aug + lr);
+                    load_codes<M>(c, a.codes + lr * a.m);
+                }
+            };
+            if (grp < NS) fetch(k, cur, aug_cur);
+            for (; grp < NS && k < d.ntiles; k += NS) {
                 const uint32_t gi = it0 + (uint32_t)k;
-                // Tile -> warp group by stage (groups in use == stages): a group then meets the phases of its stage's
-                // barriers one after the other, never two apart, which parity waits could not tell from each other.
-                if ((int)(gi % (uint32_t)NS) != grp) continue;
-                const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+                const uint32_t st = (uint32_t)grp, use = gi / (uint32_t)NS;
+                fetch(k + NS, nxt, aug_nxt);
                 if (!__all_sync(0xffffffffu, wait_or_abort(&b_empty[st], (use & 1u) ^ 1u, abort_flag, limit))) { failed = true; break; }
                 unsigned char* rowbase = s_b + st * b_bytes + (size_t)lt * 128;
                 const long long r = d.r0 + (long long)k * TN + lt;
                 if (r < d.r1) {
-                    const size_t lr = (size_t)(r - a.row_base);
-                    const uint2 aug = __ldg(g.row_aug + lr);
-                    decode_row<DSUB, M>(a.codes + lr * a.m, a.m, a.k, s_tab, rowbase, xs, b_stride);
-                    *chunk_at(rowbase, xs, b_stride, nchunk_data) = make_uint4(aug.x, aug.y, 0u, 0u);
+                    decode_row<DSUB, M>(cur, a.codes + (size_t)(r - a.row_base) * a.m, a.m, a.k, s_tab, rowbase, xs, b_stride);
+                    *chunk_at(rowbase, xs, b_stride, nchunk_data) = make_uint4(aug_cur.x, aug_cur.y, 0u, 0u);
                 } else {
                     // past the end of the chunk: a row no visitor can admit (score -1e30)
                     for (int c = 0; c < nchunk_data; ++c) *chunk_at(rowbase, xs, b_stride, c) = make_uint4(0, 0, 0, 0);
@@ -356,6 +377,7 @@ __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs 
                 for (int c = nchunk_data + 1; c < nchunk; ++c) *chunk_at(rowbase, xs, b_stride, c) = make_uint4(0, 0, 0, 0);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(&b_full[st]);
+                cur = nxt; aug_cur = aug_nxt;
             }
             if (failed) break;
             it0 += (uint32_t)d.ntiles;
@@ -375,9 +397,9 @@ __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs 
             if (d.stop) break;
             if (!__all_sync(0xffffffffu, wait_or_abort(&vis_full[islot], (n / kItemRing) & 1u, abort_flag, limit))) { failed = true; break; }
             const float P = s_P[islot][i];
+            const uint32_t nrows = (uint32_t)(d.r1 - d.r0);  // rows of the item
             // pushes the queued survivors of this item to their visitors' pools
             auto flush = [&]() {
-                __syncwarp();
                 const int cnt = min(s_qcnt[e], kQueueCap);
                 for (int x = lane; x < cnt; x += 32) {
                     const uint32_t en = queue[x];
@@ -391,51 +413,62 @@ __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs 
                 if (lane == 0) s_qcnt[e] = 0;
                 __syncwarp();
             };
-            for (int k = 0; k < d.ntiles; ++k) {
-                const uint32_t gi = it0 + (uint32_t)k;
-                if ((int)(gi & 1u) != eg) continue;
-                const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
-                if (!__all_sync(0xffffffffu, wait_or_abort(&acc_full[st], use & 1u, abort_flag, limit))) { failed = true; break; }
-                tc_fence_after();
-                const uint32_t rel0 = (uint32_t)k * TN;       // tile's first row, relative to r0
-                const uint32_t nrows = (uint32_t)(d.r1 - d.r0);  // rows of the item
-                for (int cb = 0; cb < TN; cb += 32) {
-                    uint32_t v[32];
-                    __syncwarp();
-                    tmem_ld32(lane_addr + st * TN + (uint32_t)cb, v);
-                    tmem_ld_wait();
-                    if (cb + 32 >= TN) {  // the accumulator is in registers: hand it back before the comparisons
-                        tc_fence_before();
-                        mbar_arrive(&acc_empty[st]);
-                    }
-                    float m4[4];
+            // 32 accumulator columns (rows rel .. rel + 31 of the item) against this thread's visitor: the maximum by three-input
+            // max, and only when it reaches the visitor's bound the hit mask and one queue entry per hit (no branch per column)
+            auto scan32 = [&](const uint32_t (&v)[32], uint32_t rel) {
+                float m0 = __uint_as_float(v[0]), m1 = __uint_as_float(v[1]);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) m4[j] = __uint_as_float(v[j]);
+                for (int j = 2; j < 32; j += 4) {
+                    asm("max.f32 %0, %0, %1, %2;" : "+f"(m0) : "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])));
+                    if (j + 3 < 32) asm("max.f32 %0, %0, %1, %2;" : "+f"(m1) : "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3])));
+                }
+                if (fmaxf(m0, m1) >= P) {
+                    uint32_t mask = 0;
 #pragma unroll
-                    for (int j = 4; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
-                    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                    if (mx >= P) {  // a survivor among these 32 rows
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const uint32_t rel = rel0 + (uint32_t)(cb + j);
-                            if (__uint_as_float(v[j]) >= P && rel < nrows) {  // rel >= nrows: padding rows of the last tile
-                                ++passes;
-                                const uint32_t en = ((uint32_t)i << 24) | rel;
-                                const int pos = atomicAdd(&s_qcnt[e], 1);
-                                if (pos < kQueueCap) {
-                                    queue[pos] = en;
-                                } else {  // queue full (a visitor without cutoff admits whole lists): straight to the pool
-                                    const int pq = s_pq[islot][i];
-                                    const int slot = atomicAdd(&a.pool_cnt[pq], 1);
-                                    if (slot < a.pool_cap)
-                                        a.pool[(size_t)pq * a.pool_cap + slot] = ((uint64_t)(uint32_t)s_hi[islot][i] << 32) | (uint32_t)(d.r0 + rel);
-                                }
-                            }
+                    for (int j = 0; j < 32; ++j) mask |= (__uint_as_float(v[j]) >= P ? 1u : 0u) << j;
+                    if (rel + 32 > nrows) mask &= rel < nrows ? (0xffffffffu >> (rel + 32 - nrows)) : 0u;  // padding rows of the last tile
+                    while (mask) {
+                        const uint32_t j = (uint32_t)__ffs((int)mask) - 1u;
+                        mask &= mask - 1u;
+                        ++passes;
+                        const int pos = atomicAdd(&s_qcnt[e], 1);
+                        if (pos < kQueueCap) {
+                            queue[pos] = ((uint32_t)i << 24) | (rel + j);
+                        } else {  // queue full (a visitor without cutoff admits whole lists): straight to the pool
+                            const int pq = s_pq[islot][i];
+                            const int slot = atomicAdd(&a.pool_cnt[pq], 1);
+                            if (slot < a.pool_cap)
+                                a.pool[(size_t)pq * a.pool_cap + slot] = ((uint64_t)(uint32_t)s_hi[islot][i] << 32) | (uint32_t)(d.r0 + rel + j);
                         }
                     }
                 }
+                __syncwarp();  // reconverged: the tcgen05 loads and waits that follow are warp-aligned
+                if (s_qcnt[e] >= kQueueCap / 2) flush();  // warp-uniform
+            };
+            for (int k = 0; k < d.ntiles; ++k) {
+                const uint32_t gi = it0 + (uint32_t)k;
+                if ((int)(gi & 1u) != eg) continue;  // tiles alternate between the two epilogue groups
+                const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+                if (!__all_sync(0xffffffffu, wait_or_abort(&acc_full[st], use & 1u, abort_flag, limit))) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t rel0 = (uint32_t)k * TN;  // tile's first row, relative to r0
+                const uint32_t col0 = lane_addr + st * TN;
+                uint32_t va[32], vb[32];  // two loads in flight: the next 32 columns arrive while these are compared
                 __syncwarp();
-                if (s_qcnt[e] >= kQueueCap / 2) flush();  // warp-uniform: read after the barrier
+                tmem_ld32(col0, va);
+                tmem_ld_wait();
+                tmem_ld32(col0 + 32, vb);
+                scan32(va, rel0);
+                tmem_ld_wait();
+                tmem_ld32(col0 + 64, va);
+                scan32(vb, rel0 + 32);
+                tmem_ld_wait();
+                tmem_ld32(col0 + 96, vb);
+                scan32(va, rel0 + 64);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(&acc_empty[st]);  // the accumulator is in registers: hand it back before the last comparisons
+                scan32(vb, rel0 + 96);
             }
             if (failed) break;
             flush();
@@ -445,38 +478,56 @@ __global__ void __launch_bounds__(kTcScanThreads, 1) k_scan_tc(const ScanTcArgs 
     } else if (warp == kWarpMma) {
         // ---- MMA issuer (one lane) ----
         if (lane == 0) {
+            // One thread issues everything, so its instruction count per tile is the pipeline's clock: the operand descriptors
+            // of every slot and stage are built once (shared-memory addresses never change), a K step only adds a constant to
+            // them (the address field counts 16-byte units; both operands have 16 KB swizzle atoms), and the K loop is unrolled.
             const uint32_t idesc = idesc_bf16(TV, TN);
+            const uint64_t da0 = make_sw128_desc(smem_u32(s_a)), da1 = make_sw128_desc(smem_u32(s_a + a_bytes));
+            const uint64_t db0 = make_sw128_desc(smem_u32(s_b)), db1 = make_sw128_desc(smem_u32(s_b + b_bytes)),
+                           db2 = make_sw128_desc(smem_u32(s_b + 2 * b_bytes));
+            const int nsteps = g.kp >> 4;  // <= 12
             uint32_t it0 = 0;
+            long long w_item = 0, w_rows = 0, w_acc = 0;  // cycles spent waiting: for an item and its query tile, for decoded rows, for a free accumulator
             for (uint32_t n = 0;; ++n) {
                 const int islot = n % kItemRing;
+                long long t0 = clock64();
                 if (!wait_or_abort(&item_full[islot], (n / kItemRing) & 1u, abort_flag, limit)) { failed = true; break; }
-                const ItemDesc d = s_desc[islot];
-                if (d.stop) break;
+                const int ntiles = s_desc[islot].ntiles;
+                if (s_desc[islot].stop) break;
                 const int aslot = n % NA;
                 if (!wait_or_abort(&a_full[aslot], (n / NA) & 1u, abort_flag, limit)) { failed = true; break; }
-                const uint32_t sa = smem_u32(s_a + aslot * a_bytes);
-                for (int k = 0; k < d.ntiles; ++k) {
+                w_item += clock64() - t0;
+                const uint64_t da = aslot ? da1 : da0;
+                for (int k = 0; k < ntiles; ++k) {
                     const uint32_t gi = it0 + (uint32_t)k;
                     const uint32_t st = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+                    t0 = clock64();
                     if (!wait_or_abort(&b_full[st], use & 1u, abort_flag, limit)) { failed = true; break; }
+                    const long long t1 = clock64();
                     if (!wait_or_abort(&acc_empty[st], (use & 1u) ^ 1u, abort_flag, limit)) { failed = true; break; }
+                    w_rows += t1 - t0; w_acc += clock64() - t1;
                     if (g.skip_mma) continue;  // test hook: nothing is issued or committed, so the waiting roles give up
                     tc_fence_after();
-                    const uint32_t sb = smem_u32(s_b + st * b_bytes);
-                    for (int ka = 0; ka < g.katoms; ++ka) {
-                        const int ksteps = min(4, (g.kp - ka * 64) >> 4);
-                        for (int kk = 0; kk < ksteps; ++kk)
-                            umma_bf16(tmem + st * TN, make_sw128_desc(sa + ka * a_stride + kk * 32),
-                                      make_sw128_desc(sb + ka * b_stride + kk * 32), idesc, (ka | kk) ? 1u : 0u);
+                    const uint64_t db = st == 0 ? db0 : (st == 1 ? db1 : db2);
+                    const uint32_t tacc = tmem + st * TN;
+#pragma unroll
+                    for (int s2 = 0; s2 < 12; ++s2) {
+                        const uint64_t off = (uint64_t)((s2 >> 2) * 1024 + (s2 & 3) * 2);  // atom (16 KB) and 32-byte K step, in 16-byte units
+                        if (s2 < nsteps) umma_bf16(tacc, da + off, db + off, idesc, s2 ? 1u : 0u);
                     }
                     umma_commit(&acc_full[st]);
                     umma_commit(&b_empty[st]);
                 }
                 if (failed) break;
                 if (!g.skip_mma) umma_commit(&a_empty[aslot]);  // the query tile may be rebuilt once these MMAs have read it
-                it0 += (uint32_t)d.ntiles;
+                it0 += (uint32_t)ntiles;
                 mbar_arrive(&item_empty[islot]);
             }
+            // where the issuer's time went (diagnostics, summed over CTAs): waiting for items, decoded rows, accumulators; tiles
+            atomicAdd(&a.counters[4], (unsigned long long)w_item);
+            atomicAdd(&a.counters[5], (unsigned long long)w_rows);
+            atomicAdd(&a.counters[6], (unsigned long long)w_acc);
+            atomicAdd(&a.counters[7], (unsigned long long)it0);
         }
     }
     if (failed) { *abort_flag = 1; atomicExch(g.status, 1); }
@@ -738,6 +789,7 @@ psb_status run_select_rescore(const RescoreArgs& g, int nq, cudaStream_t s) {
     const size_t smem = (size_t)g.pool_cap * 8 + (g.residual ? (size_t)g.dim * 4 : (size_t)g.m * g.k * 4);
     if (smem > (size_t)226 * 1024) return fail(PSB_UNSUPPORTED_SHAPE, "re-scoring selection does not fit shared memory");
     if (smem > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(k_select_rescore<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PSB_TRY(prefer_max_shared(k_select_rescore<M>));
     k_select_rescore<M><<<nq, kRescoreThreads, smem, s>>>(g);
     count_launch();
     PSB_LAUNCH_CHECK();

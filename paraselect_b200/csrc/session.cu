@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <climits>
 #include <cmath>
 #include <cstring>
@@ -12,6 +13,7 @@
 #include <new>
 #include <condition_variable>
 #include <deque>
+#include <functional>
 #include <mutex>
 #include <string>
 #include <thread>
@@ -72,6 +74,54 @@ psb_status check_device(int device, cudaDeviceProp* prop_out = nullptr) {
     PSB_CUDA(cudaSetDevice(device));
     return PSB_OK;
 }
+
+// Persistent fork-join pool of host threads for the staged rerank transport (the reference keeps a persistent rerank pool
+// too: src/search/ivf_common/ivf_host_rerank.cpp:42-51).  run(job) calls job(t) on every thread t and returns when all are done.
+class HostPool {
+public:
+    explicit HostPool(int n) : n_(n) {
+        for (int t = 0; t < n_; ++t) threads_.emplace_back([this, t] { loop(t); });
+    }
+    ~HostPool() {
+        { std::lock_guard<std::mutex> lk(mu_); stop_ = true; ++gen_; }
+        cv_.notify_all();
+        for (auto& th : threads_) th.join();
+    }
+    int size() const { return n_; }
+    template <typename F>
+    void run(F&& job) {
+        std::function<void(int)> f = std::forward<F>(job);
+        { std::lock_guard<std::mutex> lk(mu_); job_ = &f; pending_ = n_; ++gen_; }
+        cv_.notify_all();
+        std::unique_lock<std::mutex> lk(mu_);
+        done_.wait(lk, [this] { return pending_ == 0; });
+        job_ = nullptr;
+    }
+private:
+    void loop(int t) {
+        unsigned long long seen = 0;
+        for (;;) {
+            const std::function<void(int)>* f = nullptr;
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return gen_ != seen; });
+                seen = gen_;
+                if (stop_) return;
+                f = job_;
+            }
+            if (f) (*f)(t);
+            { std::lock_guard<std::mutex> lk(mu_); if (--pending_ == 0) done_.notify_all(); }
+        }
+    }
+    int n_;
+    std::vector<std::thread> threads_;
+    std::mutex mu_;
+    std::condition_variable cv_, done_;
+    const std::function<void(int)>* job_ = nullptr;
+    unsigned long long gen_ = 0;
+    int pending_ = 0;
+    bool stop_ = false;
+};
 
 struct EventTimer {
     std::vector<cudaEvent_t> ev;
@@ -197,6 +247,9 @@ struct psb_session {
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
     bool pinned_used[2] = {false, false};  // a copy out of the ring buffer may still be in flight (its event tells)
     int pinned_slot = 0;
+    std::unique_ptr<HostPool> host_pool;   // gather threads of the staged transport (created on first use)
+    double staged_gather_s = 0.0;          // host time spent gathering rows, and the bytes gathered (reported by the bench)
+    long long staged_gather_bytes = 0;
     std::vector<int> h_cand;
     int* h_cand_pinned = nullptr;        // candidates of the whole batch on the host (overlapped staged transport)
     size_t h_cand_pinned_count = 0;
@@ -260,7 +313,7 @@ struct psb_session {
     psb_status check_scan_status() {
         if (!scalars.p) return PSB_OK;
         int st = 0;
-        int* word = reinterpret_cast<int*>(scalars.as<unsigned long long>() + 8);
+        int* word = reinterpret_cast<int*>(scalars.as<unsigned long long>() + 12);
         PSB_CUDA(cudaMemcpy(&st, word, sizeof(int), cudaMemcpyDeviceToHost));
         if (st) {
             PSB_CUDA(cudaMemset(word, 0, sizeof(int)));
@@ -276,15 +329,15 @@ struct psb_session {
         w.fail_list = fail_list.as<int>();
         w.fallback_partial = fallback_partial.as<uint64_t>();
         unsigned long long* sc = scalars.as<unsigned long long>();
-        w.counters = sc;                                   // [0..3]
-        w.work_cursor = sc + 4;
-        w.n_fail = reinterpret_cast<int*>(sc + 5);
-        w.fail_cursor = reinterpret_cast<int*>(sc + 6);
+        w.counters = sc;                                   // [0..7]
+        w.work_cursor = sc + 8;
+        w.n_fail = reinterpret_cast<int*>(sc + 9);
+        w.fail_cursor = reinterpret_cast<int*>(sc + 10);
         w.pool_cap = pool_cap;
         w.lut_h = lut_h.p; w.lut_scale = lut_scale.as<float>(); w.scan_mode = opt.scan_mode;
         w.reserve_ctas = opt.reserve_sms;
         w.seed_sigma = opt.seed_sigma;
-        w.item_off_tc = item_off_tc.as<long long>(); w.work_cursor_tc = sc + 7; w.tc_status = reinterpret_cast<int*>(sc + 8);
+        w.item_off_tc = item_off_tc.as<long long>(); w.work_cursor_tc = sc + 11; w.tc_status = reinterpret_cast<int*>(sc + 12);
         w.tc_min_visitors = opt.tc_min_visitors; w.tc_wait_limit = opt.test_wait_limit; w.tc_skip_mma = opt.test_skip_mma;
         w.cap_queries = ws_scan_queries; w.cap_tables = ws_scan_tables;
         return w;
@@ -514,8 +567,11 @@ psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int wid
         }
         s->pinned_bytes = need;
     }
-    const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
-    const int nthreads = (int)std::min<unsigned>(hc, 32);
+    if (!s->host_pool) {
+        const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
+        s->host_pool.reset(new HostPool((int)std::min<unsigned>(hc, 64)));
+    }
+    const int nthreads = s->host_pool->size();
     // The ring state outlives the call: the next call may start while this call's last copy is still in flight.
     for (size_t q0 = 0; q0 < (size_t)nq; q0 += chunk_q, s->pinned_slot ^= 1) {
         const int slot = s->pinned_slot;
@@ -524,17 +580,37 @@ psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int wid
         unsigned char* dst = static_cast<unsigned char*>(s->pinned[slot]);
         const unsigned char* src = static_cast<const unsigned char*>(s->exact_host);
         const size_t total = n * width;
-        std::vector<std::thread> pool;
-        for (int t = 0; t < nthreads; ++t)
-            pool.emplace_back([&, t]() {
-                const size_t b = total * t / nthreads, e = total * (t + 1) / nthreads;
-                for (size_t i = b; i < e; ++i) {
-                    const size_t q = q0 + i / width, c = i % width;
-                    const long long row = host_local_row(s, h_cand[q * stride + c]);
-                    if (row >= 0 && row < s->exact_count) std::memcpy(dst + i * row_bytes, src + (size_t)row * row_bytes, row_bytes);
+        const auto t_begin = std::chrono::steady_clock::now();
+        s->host_pool->run([&](int t) {
+            // Rows sit at random places of a host array far larger than the caches: each copy would wait for DRAM.  The rows of
+            // the next kAhead candidates are resolved and prefetched while the current one is copied, so a thread keeps
+            // several misses in flight.
+            constexpr int kAhead = 8;
+            const size_t b = total * t / nthreads, e = total * (t + 1) / nthreads;
+            long long rows[kAhead];
+            auto resolve = [&](size_t i) -> long long {
+                const size_t q = q0 + i / width, c = i % width;
+                const long long row = host_local_row(s, h_cand[q * stride + c]);
+                return (row >= 0 && row < s->exact_count) ? row : -1;
+            };
+            for (size_t i = b; i < std::min(e, b + kAhead); ++i) {
+                rows[i % kAhead] = resolve(i);
+                if (rows[i % kAhead] >= 0)
+                    for (size_t off = 0; off < row_bytes; off += 64) __builtin_prefetch(src + (size_t)rows[i % kAhead] * row_bytes + off, 0, 0);
+            }
+            for (size_t i = b; i < e; ++i) {
+                const long long row = rows[i % kAhead];
+                if (i + kAhead < e) {
+                    const long long nx = resolve(i + kAhead);
+                    rows[i % kAhead] = nx;
+                    if (nx >= 0)
+                        for (size_t off = 0; off < row_bytes; off += 64) __builtin_prefetch(src + (size_t)nx * row_bytes + off, 0, 0);
                 }
-            });
-        for (auto& th : pool) th.join();
+                if (row >= 0) std::memcpy(dst + i * row_bytes, src + (size_t)row * row_bytes, row_bytes);
+            }
+        });
+        s->staged_gather_s += std::chrono::duration<double>(std::chrono::steady_clock::now() - t_begin).count();
+        s->staged_gather_bytes += (long long)(total * row_bytes);
         PSB_CUDA(cudaMemcpyAsync(static_cast<unsigned char*>(d_stage) + q0 * width * row_bytes, dst, total * row_bytes,
                                  cudaMemcpyHostToDevice, stream));
         PSB_CUDA(cudaEventRecord(s->pinned_ev[slot], stream));
@@ -563,7 +639,7 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
         PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
                                    s->stage.p, s->stream, s->sm_count,
                                    (s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream))
-                                       ? (s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 32) : 0));
+                                       ? (s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count) : 0));
     }
     float* score = d_score;
     if (!score) {
@@ -835,7 +911,7 @@ psb_status psb_stage_merge(psb_session* s, const int* d_rows, const float* d_dis
 psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     if (!s || !stats) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
-    unsigned long long h[4] = {0, 0, 0, 0};
+    unsigned long long h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (s->scalars.p) {
         PSB_CUDA(cudaMemcpyAsync(h, s->scalars.p, sizeof(h), cudaMemcpyDeviceToHost, s->stream));
         if (reset) PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(h), s->stream));
@@ -846,6 +922,10 @@ psb_status psb_session_counters(psb_session* s, psb_stats* stats, int reset) {
     stats->threshold_candidates = (long long)h[1];
     stats->fallback_queries = (long long)h[2];
     stats->prefilter_survivors = (long long)h[3];
+    stats->tc_wait_item_cycles = (long long)h[4]; stats->tc_wait_rows_cycles = (long long)h[5];
+    stats->tc_wait_acc_cycles = (long long)h[6]; stats->tc_tiles = (long long)h[7];
+    stats->staged_gather_ms = s->staged_gather_s * 1e3; stats->staged_gather_bytes = s->staged_gather_bytes;
+    if (reset) { s->staged_gather_s = 0.0; s->staged_gather_bytes = 0; }
     stats->kernel_launches = launches_total();
     if (!s->scalars.p) PSB_CUDA(cudaStreamSynchronize(s->stream));
     s->collect_scan_events();
