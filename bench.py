@@ -465,10 +465,34 @@ def main():
     return 0
 
 
+def pin_to_gpu_numa_node(torch, local_rank):
+    """Keeps this rank's threads - and so the pages of the host arrays it is about to fill - on the NUMA node its GPU hangs
+    off, so that the PCIe gather of the exact rows does not cross the socket interconnect.  Silently does nothing where the
+    topology cannot be read."""
+    try:
+        p = torch.cuda.get_device_properties(local_rank)
+        dev = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % dev).read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return node
+    except Exception:
+        pass
+    return None
+
+
 def multi_gpu_main(args, cfg, rank, world, local_rank):
     """`bench.py --gpus N` for N > 1 (one process per GPU under torchrun)."""
     import torch
     import torch.distributed as dist
+    numa_node = pin_to_gpu_numa_node(torch, local_rank)
     from paraselect_b200 import api, multi
     from paraselect_b200.multi import ShardedSearch, SessionEngine, stripe_layout
 
@@ -576,7 +600,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
                           traffic=int(2.62 * S / world) if M == 48 else None,  # 2.62 DRAM bytes per scanned code row (ncu, cut-down case)
                           note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
             counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
-            stages_ms_rank0=stage_ms, result_checksum=checksum, clocks=clocks)
+            stages_ms_rank0=stage_ms, host_numa_node_rank0=numa_node, result_checksum=checksum, clocks=clocks)
         emit(line)
     sess.close()
     dist.barrier()

@@ -7,7 +7,9 @@ lists - keeps ranks balanced when list sizes are skewed (a Zipf head list would 
 Per batch (`ShardedSearch.step`):
   1. every rank: coarse (all queries, replicated centroids) -> LUT -> ADC scan of its slices -> local
      top-stage1_k candidates, as index-wide row numbers with ADC distances
-  2. all-gather of the candidate lists, merge to the index-wide top-stage1_k (identical on every rank)
+  2. all-to-all of the candidate lists: rank g receives every rank's lists for ITS slice of the queries only and merges
+     them to the index-wide top-stage1_k of that slice (1/world of the bytes and of the merge work of an all-gather);
+     an all-gather of the merged rows (4 bytes per candidate) gives every rank the whole candidate table
   3. every rank scores exactly the candidates whose rows it holds (+inf elsewhere); all-reduce(min)
   4. top-k by (distance,row) on the combined scores; ids come from the rank holding each row; all-reduce(max)
 The results are those of a single-GPU search of the whole index, bit for bit.
@@ -74,8 +76,9 @@ class SessionEngine:
     def lut(self, dq, nq, out):
         self.s.stage_build_lut(dq, nq, out)
 
-    def scan(self, lut, nq, probes, nprobe, width, rows, dist, count):
-        self.s.stage_scan(lut, nq, probes, nprobe, width, rows, dist, count)
+    def scan(self, dq, lut, nq, probes, nprobe, width, rows, dist, count):
+        # with the queries at hand the scan can take the tensor-core pre-filter
+        self.s.stage_scan_queries(dq, lut, nq, probes, nprobe, width, rows, dist, count)
 
     def merge(self, rows, dist, parts, nq, width, out_rows, out_dist):
         self.s.stage_merge(rows, dist, parts, nq, width, out_rows, out_dist)
@@ -101,12 +104,15 @@ class ShardedSearch:
         self.l_rows = engine.empty((nq, width), t.int32)
         self.l_dist = engine.empty((nq, width), t.float32)
         self.l_cnt = engine.empty((nq,), t.int32)
-        self.g_rows = engine.empty((world, nq, width), t.int32)
-        self.g_dist = engine.empty((world, nq, width), t.float32)
-        self.l_key = engine.empty((nq, width), t.int64)          # packed (distance bits << 32 | row) for the all-gather
-        self.g_key = engine.empty((world, nq, width), t.int64)
-        self.m_rows = engine.empty((nq, width), t.int32)
-        self.m_dist = engine.empty((nq, width), t.float32)
+        # exchange buffers, sized for the whole batch in one piece; a query slice is ceil(nq / world) queries (the last is padded)
+        ms = (nq + world - 1) // world
+        self.s_key = engine.empty((world * ms, width), t.int64)   # send: packed (distance bits << 32 | row), all my local lists
+        self.r_key = engine.empty((world, ms, width), t.int64)    # receive: every rank's lists for my slice
+        self.g_rows = engine.empty((world, ms, width), t.int32)
+        self.g_dist = engine.empty((world, ms, width), t.float32)
+        self.mg_rows = engine.empty((ms, width), t.int32)         # merged candidates of my slice
+        self.mg_dist = engine.empty((ms, width), t.float32)
+        self.m_rows = engine.empty((world * ms, width), t.int32)  # merged candidates of every slice (all-gather)
         self.p_dist = engine.empty((nq, width), t.float32)
         self.o_rows = engine.empty((nq, topk), t.int32)
         self.o_dist = engine.empty((nq, topk), t.float32)
@@ -129,30 +135,38 @@ class ShardedSearch:
         e = self.e
         sl = slice(q0, q0 + m)
         e.lut(dq[sl], m, self.lut[:m])
-        e.scan(self.lut[:m], m, self.probes[sl], self.nprobe, self.width, self.l_rows[sl], self.l_dist[sl], self.l_cnt[sl])
+        e.scan(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, self.l_rows[sl], self.l_dist[sl], self.l_cnt[sl])
         self._mark("lut+scan")
 
     def _back(self, dq, q0, m):
-        """Exchange half of queries [q0, q0 + m): candidate all-gather and merge, partial exact scoring, combination."""
+        """Exchange half of queries [q0, q0 + m): candidate all-to-all and sliced merge, partial exact scoring, combination."""
         e, d, w, width = self.e, self.dist, self.world, self.width
         sl = slice(q0, q0 + m)
-        m_rows, m_dist = self.l_rows[sl], self.l_dist[sl]
+        m_rows = self.l_rows[sl]
         if w > 1:
-            # one collective for rows and distances: 64-bit words (distance bits << 32 | row), unpacked after the gather
             t = self.torch
-            g_rows = self.g_rows.view(-1)[:w * m * width].view(w, m, width)
-            g_dist = self.g_dist.view(-1)[:w * m * width].view(w, m, width)
-            g_key = self.g_key.view(-1)[:w * m * width].view(w * m, width)
-            key = self.l_key[sl]
-            t.bitwise_or(self.l_dist[sl].view(t.int32).to(t.int64) << 32, self.l_rows[sl].to(t.int64) & 0xFFFFFFFF, out=key)
-            d.all_gather_into_tensor(g_key, key)
-            halves = g_key.view(t.int32).view(w * m, width, 2)  # little-endian: [..., 0] = row, [..., 1] = distance bits
-            g_rows.view(w * m, width).copy_(halves[..., 0])      # reinterpreted, not value-converted: -1 stays -1
-            g_dist.view(w * m, width).view(t.int32).copy_(halves[..., 1])
-            self._mark("all_gather")
-            m_rows, m_dist = self.m_rows[sl], self.m_dist[sl]
-            e.merge(g_rows, g_dist, w, m, width, m_rows, m_dist)
+            ms = (m + w - 1) // w                      # queries per slice of this sub-batch (the last slice may be padded)
+            s_key = self.s_key.view(-1)[:w * ms * width].view(w * ms, width)
+            r_key = self.r_key.view(-1)[:w * ms * width].view(w, ms, width)
+            g_rows = self.g_rows.view(-1)[:w * ms * width].view(w, ms, width)
+            g_dist = self.g_dist.view(-1)[:w * ms * width].view(w, ms, width)
+            mg_rows = self.mg_rows.view(-1)[:ms * width].view(ms, width)
+            mg_dist = self.mg_dist.view(-1)[:ms * width].view(ms, width)
+            all_rows = self.m_rows.view(-1)[:w * ms * width].view(w * ms, width)
+            # one word per candidate: distance bits << 32 | row; padding queries carry (FLT_MAX, -1)
+            t.bitwise_or(self.l_dist[sl].view(t.int32).to(t.int64) << 32, self.l_rows[sl].to(t.int64) & 0xFFFFFFFF, out=s_key[:m])
+            if w * ms > m:
+                s_key[m:].fill_((0x7F7FFFFF << 32) | 0xFFFFFFFF)
+            d.all_to_all_single(r_key.view(w * ms, width), s_key)   # slice g of my lists -> rank g; I receive my slice from everyone
+            halves = r_key.view(t.int32).view(w, ms, width, 2)       # little-endian: [..., 0] = row, [..., 1] = distance bits
+            g_rows.copy_(halves[..., 0])                             # reinterpreted, not value-converted: -1 stays -1
+            g_dist.view(t.int32).copy_(halves[..., 1])
+            self._mark("all_to_all")
+            e.merge(g_rows, g_dist, w, ms, width, mg_rows, mg_dist)
             self._mark("merge")
+            d.all_gather_into_tensor(all_rows, mg_rows)              # 4 bytes per candidate: the whole sub-batch's candidate table
+            self._mark("all_gather")
+            m_rows = all_rows[:m]
         if self.rerank:
             e.rerank_partial(dq[sl], m, m_rows, width, self.p_dist[sl])
             self._mark("rerank_partial")
@@ -162,8 +176,14 @@ class ShardedSearch:
             e.select_topk(self.p_dist[sl], m_rows, m, width, self.topk, self.o_rows[sl], self.o_dist[sl])
             self._mark("select_topk")
         else:
-            self.o_rows[sl].copy_(m_rows[:, :self.topk])
-            self.o_dist[sl].copy_(m_dist[:, :self.topk])
+            if w > 1:  # no rerank: the merged ADC distances of my slice go round with the rows
+                all_dist = self.g_dist.view(-1)[:w * ms * width].view(w * ms, width)
+                d.all_gather_into_tensor(all_dist, mg_dist.clone())
+                self.o_rows[sl].copy_(m_rows[:, :self.topk])
+                self.o_dist[sl].copy_(all_dist[:m, :self.topk])
+            else:
+                self.o_rows[sl].copy_(m_rows[:, :self.topk])
+                self.o_dist[sl].copy_(self.l_dist[sl][:, :self.topk])
         # ids of the rows this rank holds, -1 elsewhere; step() combines them with ONE all-reduce(max) for the whole batch
         e.map_ids(self.o_rows[sl], m * self.topk, self.o_ids[sl])
         self._mark("map_ids")

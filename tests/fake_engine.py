@@ -37,7 +37,7 @@ class CpuCheckerEngine:
         self.q_sub = dq.numpy()  # the scan below belongs to the same (sub-)batch of queries
         out.copy_(torch.from_numpy(oracle.pq_lut(self.q_sub, self.ix["codebook"])))
 
-    def scan(self, lut, nq, probes, nprobe, width, rows, dist, count):
+    def scan(self, dq, lut, nq, probes, nprobe, width, rows, dist, count):
         r, d, c, _ = oracle.pq_scan(self.q_sub, probes.numpy().astype(np.int64), self.loff, self.ix["codes"],
                                     self.ix["codebook"], width)
         # local rows -> index-wide rows; the checker orders ties by local row, which is monotone in the global row

@@ -28,6 +28,16 @@ def main():
     ids, dd = s.step(torch.from_numpy(q))
     want = oracle.ivfpq_search(ix, q, nprobe, topk, width)
     ok = np.array_equal(ids.numpy(), want["indices"]) and np.array_equal(dd.numpy(), want["distances"])
+    # a batch size the ranks do not divide evenly: the last query slice of the exchange is padded
+    q5 = q[:5]
+    s5 = ShardedSearch(eng, dist, world, 5, 32, 8, 256, nprobe, topk, width, torch, rerank=True)
+    ids5, dd5 = s5.step(torch.from_numpy(q5))
+    ok = ok and np.array_equal(ids5.numpy(), want["indices"][:5]) and np.array_equal(dd5.numpy(), want["distances"][:5])
+    # without the rerank the merged ADC candidates are the result
+    sn = ShardedSearch(eng, dist, world, q.shape[0], 32, 8, 256, nprobe, topk, width, torch, rerank=False)
+    idn, ddn = sn.step(torch.from_numpy(q))
+    wantn = oracle.ivfpq_search(dict(ix, vectors=None), q, nprobe, topk, 0)
+    ok = ok and np.array_equal(idn.numpy(), wantn["indices"]) and np.array_equal(ddn.numpy(), wantn["distances"])
     # the same batch cut into three sub-batches (16 = 6 + 6 + 4): each runs its own exchange
     ids3, dd3 = s.step(torch.from_numpy(q), parts=3)
     ok = ok and np.array_equal(ids3.numpy(), want["indices"]) and np.array_equal(dd3.numpy(), want["distances"])
