@@ -272,6 +272,9 @@ def main():
                          "headline metric names: an extra data point)")
     ap.add_argument("--reserve-sms", type=int, default=8, help="N > 1: SMs the scan's persistent grid leaves to the collectives")
     ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
+    ap.add_argument("--serial", action="store_true", help="N = 1: no sub-batches (one scan launch per batch, then the rerank)")
+    ap.add_argument("--pipeline-parts", type=int, default=0, help="N = 1: sub-batches per batch (0 = library default)")
+    ap.add_argument("--cut-plan", type=int, default=0, help="N = 1, staged transport: sub-batch cut plan (see psb_options.even_cuts)")
     ap.add_argument("--gather-ctas", type=int, default=0, help="CTAs of the PCIe gather kernel beside a scan (0 = library default)")
     ap.add_argument("--n1-reserve-sms", type=int, default=-1, help="N = 1: SMs the scan leaves to the gather kernel (-1 = auto)")
     args = ap.parse_args()
@@ -337,7 +340,8 @@ def main():
 
         t0 = time.time()
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas,
+                           residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas, serial_pipeline=args.serial,
+                           pipeline_parts=args.pipeline_parts, even_cuts=args.cut_plan,
                            reserve_sms=max(0, args.n1_reserve_sms),
                            exact_mode={"staged": api.EXACT_HOST_STAGED, "cached": api.EXACT_HOST_CACHED}.get(args.exact_mode,
                                                                                                             api.EXACT_HOST_MAPPED))

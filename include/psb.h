@@ -152,7 +152,8 @@ typedef struct psb_options {
     float seed_sigma;   /* margin of the sampled admission cutoff in standard deviations (default 4; accepted 2..10).  Results do
                            not depend on it: a too-tight cutoff only sends more queries to the exact fallback. */
     int pipeline_parts; /* sub-batches per batch of the overlapped pipeline (default 4; accepted 2..32) */
-    int even_cuts;      /* 1 = equal sub-batches also with the staged transport (default: a short last sub-batch) */
+    int even_cuts;      /* staged transport: 0 = a short first sub-batch (10/30/30/30 %: the transfer, the longer half, starts early),
+                           1 = equal sub-batches, 2 = a short last sub-batch (32/32/26/10 %) */
     int gather_ctas;    /* 128-thread CTAs of the PCIe row-gather kernel when it runs beside a scan (default: two per SM) */
     int tc_min_visitors;/* lists with fewer visiting queries than this stay with the SIMT scan (default 1: none do) */
     /* Test hooks of the time-out path of the tensor-core scan (leave 0): test_wait_limit = polls before a device-side wait

@@ -181,7 +181,7 @@ class Session:
         opt = Options(list_global_begin=_p(gb), device=device, n_rerank=n_rerank, exact_mode=exact_mode, max_batch=max_batch,
                       list_begin=list_begin, list_end=list_end, stream=stream, coarse_mode=coarse_mode,
                       time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)), reserve_sms=reserve_sms,
-                      seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(bool(even_cuts)),
+                      seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(even_cuts),
                       gather_ctas=int(gather_ctas), tc_min_visitors=int(tc_min_visitors), test_wait_limit=int(test_wait_limit),
                       test_skip_mma=int(test_skip_mma))
         self._h = C.c_void_p()

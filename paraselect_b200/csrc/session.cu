@@ -962,14 +962,14 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     const bool staged_overlap = rerank && s->opt.exact_mode == PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
     const int sb = sub_batch_rows(s, n, nprobe, overlap || staged_overlap);
     const bool residual = s->opt.adc_mode == 1;
-    // Sub-batch boundaries.  Equal cuts, except with the overlapped staged transport: there the transfer costs the scan
-    // nothing, the host gather of a sub-batch is shorter than the next scan, and only the last sub-batch's rerank is
-    // exposed - so the last sub-batch is the small one (32/32/26/10 %).  (With the kernel gather, which slows the scan it
-    // runs beside, such cuts measured no better than equal ones.)
+    // Sub-batch boundaries.  Equal cuts, except with the overlapped staged transport.  There the transfer costs the scan
+    // nothing and is the longer of the two (3.84 GB per 10,000-query batch at the host's ~30 GB/s of random row reads, against
+    // ~60 ms of scanning), so it should start as early as possible: the first sub-batch is the small one (10/30/30/30 %).
     std::vector<int> cuts;
-    const bool even_cuts = s->opt.even_cuts != 0;
-    if (staged_overlap && !residual && sb * 4 >= n && n >= 4096 && !even_cuts) {
-        cuts = {0, (int)(0.32 * n), (int)(0.64 * n), (int)(0.90 * n), n};
+    const int plan = s->opt.even_cuts;
+    if (staged_overlap && !residual && sb * 4 >= n && n >= 4096 && plan != 1) {
+        if (plan == 2) cuts = {0, (int)(0.32 * n), (int)(0.64 * n), (int)(0.90 * n), n};  // short last sub-batch (scan-bound hosts)
+        else cuts = {0, (int)(0.10 * n), (int)(0.40 * n), (int)(0.70 * n), n};
     } else {
         for (int p0 = 0; p0 < n; p0 += sb) cuts.push_back(p0);
         cuts.push_back(n);

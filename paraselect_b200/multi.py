@@ -208,8 +208,8 @@ class ShardedSearch:
         cuts = list(range(0, nq, sb)) + [nq]
         streams = parts > 1 and getattr(e, "streams", False)
         if streams and parts == 4 and nq >= 4096:
-            # only the last sub-batch's exchange half has nothing to hide behind: make it the small one
-            cuts = [0, int(0.32 * nq), int(0.64 * nq), int(0.90 * nq), nq]
+            # the exchange half (PCIe rerank) is the longer one: a small first sub-batch lets it start early
+            cuts = [0, int(0.10 * nq), int(0.40 * nq), int(0.70 * nq), nq]
         if not streams:
             for q0, q1 in zip(cuts[:-1], cuts[1:]):
                 self._front(dq, q0, q1 - q0)
