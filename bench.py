@@ -254,6 +254,47 @@ def cpu_reference_run(index, q_host, cfg, nsample, threads):
     return r, dt, kind
 
 
+def scan_roofline(cfg, c, S, scan_ms, launches_per_step, peaks, clocks, sm_count, world):
+    """Roofline object of the dominant kernel, the ADC scan.  S = (row, query) pairs one launch scores, all ranks together.
+
+    Tensor-core pre-filter scan (k_scan_tc): a bf16 GEMM of visiting queries against decoded code rows, so the bound is the
+    tensor pipe: algorithmic FLOPs = 2 * S * dim per launch (executed: tiles * 2 * 128 * 128 * padded K).  The figure the
+    scan used to be reported by - S * M code bytes per launch over the HBM peak - is kept beside it: it is a LOGICAL byte
+    count (every visit of a row counted), and since a decoded row now serves 128 visiting queries it exceeds what HBM
+    could deliver; the physical DRAM traffic is `traffic`.
+    SIMT scans (k_scan_h / k_scan): the HBM-logical figure is the roofline, as before."""
+    hbm = float(peaks.get("hbm_gbs", 6650.0)) * world
+    logical = S * cfg["M"] / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+    src = "measured" if peaks else "fallback"
+    tiles = c.get("tc_tiles", 0) / max(1, c["scan_kernel_launches"]) * world  # per launch, all ranks (counters are one rank's)
+    if tiles > 0:
+        dim = cfg["dim"]
+        kp = (dim + 4 + 15) // 16 * 16
+        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1590.0))) * world
+        flops = 2.0 * S * dim
+        achieved = flops / (scan_ms * 1e-3) / 1e12 if scan_ms > 0 else 0.0
+        # DRAM bytes per launch: each decoded code row is read once per tile of up to 128 visitors - M code bytes + 8 bytes of
+        # per-row terms - plus the survivors written to the pools; 61.0 bytes per decoded row in the ncu capture of this workload
+        # cut to 8M rows x 2,000 queries (profiles/), scaled here by the rows this launch decodes (tiles * 128)
+        return dict(bound="tensor", kernel="k_scan_tc", achieved=round(achieved, 1), peak=peak, unit="TFLOP/s",
+                    frac=round(achieved / peak, 4), peak_source=src + " (cuBLAS bf16, sustained)",
+                    algorithmic_flops_per_launch=flops, executed_flops_per_launch=tiles * 2.0 * 128 * 128 * kp,
+                    pairs_per_launch=int(S), tiles_per_launch=int(tiles), ms_per_launch=round(scan_ms, 3),
+                    launches_per_step=launches_per_step,
+                    traffic=int(61.0 * tiles * 128) if cfg["M"] == 48 else None,
+                    traffic_source="ncu dram__bytes_read+write of a cut-down capture (8M rows, 2,000 queries), scaled by rows decoded",
+                    hbm_logical=dict(achieved=round(logical, 1), peak=hbm, unit="GB/s", frac=round(logical / hbm, 4),
+                                     algorithmic_bytes_per_launch=int(S * cfg["M"]),
+                                     note="S x M code bytes per launch: logical bytes, every visit of a row counted; above the HBM "
+                                          "peak because a decoded row serves up to 128 visiting queries"))
+    return dict(bound="hbm", kernel="k_scan_h", achieved=round(logical, 1), peak=hbm, unit="GB/s", frac=round(logical / hbm, 4),
+                peak_source=src, algorithmic_bytes_per_launch=int(S * cfg["M"]), rows_per_launch=int(S),
+                ms_per_launch=round(scan_ms, 3), launches_per_step=launches_per_step,
+                traffic=int(2.62 * S) if cfg["M"] == 48 else None,
+                traffic_source="ncu dram__bytes_read+write of a cut-down capture (8M rows, 2,000 queries), scaled by rows scanned",
+                lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / (sm_count * world) / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -405,18 +446,8 @@ def main():
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except Exception:
         pass
-    peak = float(peaks.get("hbm_gbs", 6650.0))
-    achieved = S * cfg["M"] / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
-    roofline = dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak, unit="GB/s",
-                    frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
-                    algorithmic_bytes_per_launch=int(S * cfg["M"]), rows_per_launch=int(S), ms_per_launch=round(scan_ms, 3),
-                    launches_per_step=launches_per_step,
-                    # DRAM bytes per launch: 2.62 B per scanned code row (dram read + write of one k_scan_h<48> launch in
-                    # an ncu capture of this workload cut to 8M rows x 2,000 queries: 1.42 GB for 5.415e8 rows), scaled
-                    # by the rows this launch scans - each code row is loaded once per group of 8 visiting queries
-                    traffic=int(2.62 * S) if cfg["M"] == 48 else None,
-                    traffic_source="ncu dram__bytes_read+write of a cut-down capture (8M rows, 2,000 queries), scaled by rows scanned",
-                    lookups_per_clk_per_sm=round(S * cfg["M"] / (scan_ms * 1e-3) / torch.cuda.get_device_properties(device).multi_processor_count / ((clocks.get("sm_mhz") or 1965.0) * 1e6), 2))
+    roofline = scan_roofline(cfg, c, S, scan_ms, launches_per_step, peaks, clocks,
+                             torch.cuda.get_device_properties(device).multi_processor_count, 1)
 
     # CPU baseline + parity on a bounded sample of the same batch
     cores = os.cpu_count() or 1
@@ -567,7 +598,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
         torch.cuda.synchronize()
         # totals over ranks
         tot = torch.tensor([float(c["pq_scanned_codes"]), float(c["scan_kernel_ms"]), float(c["scan_kernel_launches"]),
-                            float(c["kernel_launches"]), float(c["fallback_queries"])], dtype=torch.float64, device="cuda")
+                            float(c["kernel_launches"]), float(c["fallback_queries"]), float(c["tc_tiles"])], dtype=torch.float64, device="cuda")
         mx = tot.clone()
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -581,12 +612,14 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except Exception:
             pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
         S = tot[0].item() / max(1, args.steps)                      # rows scanned per step, all ranks
         launches_per_step = max(1.0, mx[2].item()) / max(1, args.steps)  # one scan launch per sub-batch
         scan_ms = mx[1].item() / max(1.0, mx[2].item())             # slowest rank's scan kernel, per launch
         S = S / launches_per_step                                   # rows per launch, all ranks
-        achieved = S * M / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+        c_tot = dict(c, tc_tiles=tot[5].item() / world, scan_kernel_launches=max(1.0, mx[2].item()))
+        roofline = scan_roofline(cfg, c_tot, S, scan_ms, launches_per_step, peaks, clocks,
+                                 torch.cuda.get_device_properties(device).multi_processor_count, world)
+        roofline["note"] = "aggregate over ranks: all ranks' work / slowest rank's kernel time, against world x peak"
         line = dict(
             metric="QPS (IVF-PQ search, recall@k equal to the reference CPU path)", value=round(nq / (ms_dev * 1e-3), 1),
             unit="queries/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
@@ -598,11 +631,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
                      h2d_bytes_per_step=int(nq * dim * 4), d2h_bytes_per_step=int(nq * topk * 12),
                      pcie_gather_bytes_per_step=int(nq * width * dim * 4) if R > topk else 0),
             gpu_launches=int(tot[3].item()),
-            roofline=dict(bound="hbm", kernel="k_scan", achieved=round(achieved, 1), peak=peak * world, unit="GB/s",
-                          frac=round(achieved / (peak * world), 4), peak_source="measured" if peaks else "fallback",
-                          algorithmic_bytes_per_launch=int(S * M / world), ms_per_launch=round(scan_ms, 3), launches_per_step=launches_per_step,
-                          traffic=int(2.62 * S / world) if M == 48 else None,  # 2.62 DRAM bytes per scanned code row (ncu, cut-down case)
-                          note="aggregate over ranks: all ranks' rows / slowest rank's kernel time, against world x peak"),
+            roofline=roofline,
             counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
             stages_ms_rank0=stage_ms, host_numa_node_rank0=numa_node, result_checksum=checksum, clocks=clocks)
         emit(line)

@@ -298,7 +298,10 @@ psb_status psb_stage_quantize_lut_u8(psb_session* session, const float* d_lut, i
 psb_status psb_stage_scan(psb_session* session, const float* d_lut, int nq, const int* d_probes, int nprobe,
                           int stage1_k, int* d_rows, float* d_dist, int* d_count);
 /* The same stage with the queries at hand (d_queries [nq][dim]): lets the scan take the tensor-core pre-filter, which
- * needs the query vectors besides their tables.  Same results as psb_stage_scan. */
+ * needs the query vectors besides their tables.  Same results as psb_stage_scan.  In residual mode d_lut may be NULL when
+ * the tensor-core scan takes every list (scan_mode 0 or 3 on a supported shape): no per-(query, probe) table is then
+ * materialised at all - the scan works on q - centroid directly, and the cutoff, re-scoring and fallback kernels compute
+ * the table entries they need from the query, the centroid and the codebook. */
 psb_status psb_stage_scan_queries(psb_session* session, const float* d_queries, const float* d_lut, int nq,
                                   const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count);
 

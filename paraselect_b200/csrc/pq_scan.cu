@@ -171,6 +171,39 @@ __global__ void k_fill_visitors(const int* __restrict__ probes, int nq, int npro
 }
 
 // ------------------------------------------------------------------------------------------------------
+// Where a residual-mode table (one per (query, probe) pair) comes from: the tables materialised in global memory, or - when
+// lut is null - the query, the probed list's centroid and the codebook, from which the block builds it in shared memory
+// with the arithmetic of k_build_lut_residual (fp32 subtraction, sequential non-fused sum over the sub-vector).
+struct ResidualSource {
+    const float* queries;    // [nq][dim]
+    const float* centroids;  // [nlist][dim]
+    const float* codebook;   // [m][k][dim / m]
+    int dim;
+};
+__device__ __forceinline__ void stage_residual_table(float* __restrict__ s_lut, const float* __restrict__ lut, const ResidualSource& rs,
+                                                     int q, int p, int nprobe, int list, int m, int k) {
+    const int mk = m * k;
+    if (lut) {
+        const float* src = lut + ((size_t)q * nprobe + p) * mk;
+        for (int e = threadIdx.x; e < mk; e += blockDim.x) s_lut[e] = src[e];
+        return;
+    }
+    const int dsub = rs.dim / m;
+    const float* qv = rs.queries + (size_t)q * rs.dim;
+    const float* cv = rs.centroids + (size_t)list * rs.dim;
+    for (int e = threadIdx.x; e < mk; e += blockDim.x) {
+        const int sub = e / k;
+        const float* c = rs.codebook + (size_t)e * dsub;
+        float dist = 0.0f;
+        for (int d = 0; d < dsub; ++d) {
+            const float r = __fsub_rn(__ldg(qv + sub * dsub + d), __ldg(cv + sub * dsub + d));
+            const float diff = __fsub_rn(r, __ldg(c + d));
+            dist = __fadd_rn(dist, __fmul_rn(diff, diff));
+        }
+        s_lut[e] = dist;
+    }
+}
+
 // Per query: admission cutoff from a strided sample of the rows it will scan.
 //   N = rows the query scans.  N <= pool capacity: cutoff = +inf (everything is admitted).
 //   Otherwise every stride-th row of each probed list is scored, stride = clamp(stage1_k / 16, 16, 64), n_s rows in
@@ -186,7 +219,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
                  const long long* __restrict__ offsets, int nlist, int lb, int le,
                  const uint8_t* __restrict__ codes, long long row_base, int m, int k,
                  const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr,
-                 int per_probe, int tree, float margin_sigma, float margin_add) {
+                 int per_probe, int tree, float margin_sigma, float margin_add, const ResidualSource rs) {
     // per_probe (residual mode): lut holds one table per (query, probe) pair; the probes are then sampled one after
     // the other, each with its own table staged in shared memory.
     extern __shared__ __align__(16) unsigned char s_seed_raw[];
@@ -231,8 +264,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
         if (b0 == b1) continue;
         if (per_probe) {
             __syncthreads();  // the previous probe's table is no longer read
-            const float* src = lut + ((size_t)q * nprobe + sg) * m * k;
-            for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = src[e];
+            stage_residual_table(s_lut, lut, rs, q, sg, nprobe, probes[(size_t)q * nprobe + sg], m, k);
             __syncthreads();
         }
         for (int base = b0; base < b1; base += blockDim.x) {
@@ -465,7 +497,7 @@ __device__ __forceinline__ int fallback_scan_probes(const float* __restrict__ lu
                                                     int nlist, int lb, int le, const uint8_t* __restrict__ codes,
                                                     long long row_base, const long long* __restrict__ row_delta, int m, int k,
                                                     int stage1_k, int buf_n, int per_probe, int tree, uint64_t* s_keys,
-                                                    float* s_lut, int* s_cnt, uint64_t* s_cut) {
+                                                    float* s_lut, int* s_cnt, uint64_t* s_cut, const ResidualSource& rs) {
     __syncthreads();  // the previous unit's readers of s_keys / s_lut are done
     if (!per_probe)
         for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
@@ -477,8 +509,7 @@ __device__ __forceinline__ int fallback_scan_probes(const float* __restrict__ lu
         const long long b = offsets[l], e = offsets[l + 1];
         if (per_probe && b < e) {  // residual mode: this probe's own table (uniform branch)
             __syncthreads();
-            const float* src = lut + ((size_t)q * nprobe + p) * m * k;
-            for (int i = threadIdx.x; i < m * k; i += blockDim.x) s_lut[i] = src[i];
+            stage_residual_table(s_lut, lut, rs, q, p, nprobe, l, m, k);
             __syncthreads();
         }
         const long long delta = row_delta ? row_delta[l] : 0;
@@ -529,7 +560,8 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
                  const uint8_t* __restrict__ codes, long long row_base, const long long* __restrict__ row_delta,
                  int m, int k, int stage1_k, int buf_n, const int* __restrict__ fail_list, const int* __restrict__ n_fail, int* __restrict__ fail_cursor,
                  int* __restrict__ out_rows, float* __restrict__ out_dist, int* __restrict__ out_count,
-                 unsigned long long* __restrict__ counters, int per_probe, int tree, uint64_t* __restrict__ partial) {
+                 unsigned long long* __restrict__ counters, int per_probe, int tree, uint64_t* __restrict__ partial,
+                 const ResidualSource rs) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_raw);                 // [buf_n]
     float* s_lut = reinterpret_cast<float*>(s_raw + (size_t)buf_n * 8);   // [m*k]
@@ -549,13 +581,13 @@ k_exact_fallback(const float* __restrict__ lut, const int* __restrict__ probes, 
             const int q = fail_list[f];
             const int p0 = (int)((long long)nprobe * part / kFallbackSplit), p1 = (int)((long long)nprobe * (part + 1) / kFallbackSplit);
             fallback_scan_probes<M>(lut, probes, nprobe, q, p0, p1, offsets, nlist, lb, le, codes, row_base, row_delta, m, k,
-                                    stage1_k, buf_n, per_probe, tree, s_keys, s_lut, &s_cnt, &s_cut);
+                                    stage1_k, buf_n, per_probe, tree, s_keys, s_lut, &s_cnt, &s_cut, rs);
             uint64_t* out = partial + (size_t)item * stage1_k;  // KEY_MAX beyond the valid keys
             for (int i = threadIdx.x; i < stage1_k; i += blockDim.x) out[i] = s_keys[i];
         } else {
             const int q = fail_list[nsplit + (item - nsplit * kFallbackSplit)];
             const int keep = fallback_scan_probes<M>(lut, probes, nprobe, q, 0, nprobe, offsets, nlist, lb, le, codes, row_base,
-                                                     row_delta, m, k, stage1_k, buf_n, per_probe, tree, s_keys, s_lut, &s_cnt, &s_cut);
+                                                     row_delta, m, k, stage1_k, buf_n, per_probe, tree, s_keys, s_lut, &s_cnt, &s_cut, rs);
             fallback_emit(s_keys, keep, q, stage1_k, out_rows, out_dist, out_count);
             if (threadIdx.x == 0) atomicAdd(&counters[2], 1ull);
         }
@@ -1021,14 +1053,14 @@ float seed_margin_sigma(const ScanWorkspace& ws) { return ws.seed_sigma >= 2.f &
 
 template <int M>
 psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq, const int* d_probes,
-                    int nprobe, int stage1_k, cudaStream_t s) {
+                    int nprobe, int stage1_k, cudaStream_t s, const ResidualSource& rs) {
     const size_t smem = (size_t)ix.m * ix.k * sizeof(float) + kSeedBuf * sizeof(uint32_t) + ((size_t)nprobe + 1) * sizeof(int);
     PSB_TRY(set_smem(k_seed_threshold<M>, smem));
     PSB_TRY(prefer_max_shared(k_seed_threshold<M>));
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
                                                          stage1_k, ws.pool_cap, ws.thr, ix.residual ? 1 : 0,
-                                                         tree_order(ix) ? 1 : 0, seed_margin_sigma(ws), seed_margin_sigma(ws) - 2.0f);
+                                                         tree_order(ix) ? 1 : 0, seed_margin_sigma(ws), seed_margin_sigma(ws) - 2.0f, rs);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -1037,7 +1069,7 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
 template <int M>
 psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, const int* d_probes,
                         int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count, int sm_count,
-                        cudaStream_t s) {
+                        cudaStream_t s, const ResidualSource& rs) {
     int buf_n = 2 * 1024;
     while (buf_n < stage1_k + kFallbackThreads) buf_n <<= 1;
     const size_t smem = (size_t)buf_n * 8 + (size_t)ix.m * ix.k * sizeof(float);
@@ -1046,7 +1078,7 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     k_exact_fallback<M><<<sm_count, kFallbackThreads, smem, s>>>(
         d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin, ix.list_end, ix.codes, ix.row_base, ix.row_delta, ix.m, ix.k,
         stage1_k, buf_n, ws.fail_list, ws.n_fail, ws.fail_cursor, d_rows, d_dist, d_count, ws.counters,
-        ix.residual ? 1 : 0, tree_order(ix) ? 1 : 0, ws.fallback_partial);
+        ix.residual ? 1 : 0, tree_order(ix) ? 1 : 0, ws.fallback_partial, rs);
     count_launch();
     PSB_LAUNCH_CHECK();
     const size_t msmem = (size_t)buf_n * 8;
@@ -1155,6 +1187,10 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     const bool use_tc = tc_possible && (ws.scan_mode == 0 || ws.scan_mode == 3);
     const int tc_min_vis = use_tc ? (ws.tc_min_visitors > 0 ? ws.tc_min_visitors : 1) : 0;
     const bool simt_needed = !use_tc || tc_min_vis > 1;  // lists below the visitor limit stay with the SIMT scan
+    // Without tables (d_lut null): residual mode only, and only when the tensor-core scan takes every list - the cutoff, the
+    // re-scoring and the fallback then build what they need from the queries, the centroids and the codebook.
+    if (!d_lut && !(ix.residual && use_tc && !simt_needed))
+        return fail(PSB_INVALID_ARGUMENT, "the scan needs the lookup tables (they may be left out only in residual mode with the tensor-core scan)");
     const bool use_half = simt_needed && ws.lut_h != nullptr && ws.scan_mode != 1 && half_scan_fits(ix.m, ix.k);
     if (nq > ws.cap_queries || (use_half && tables > ws.cap_tables))
         return fail(PSB_INTERNAL, "scan workspace holds " + std::to_string(ws.cap_queries) + " queries / " + std::to_string(ws.cap_tables) +
@@ -1185,7 +1221,9 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     count_launch();
     PSB_LAUNCH_CHECK();
     // cutoff
-    PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s))));
+    ResidualSource rs;
+    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.dim = ix.dim;
+    PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s, rs))));
     // scan
     ScanArgs a;
     a.lut = d_lut; a.lut_div = ix.residual ? nprobe : 1; a.tree = tree_order(ix) ? 1 : 0; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base; a.row_delta = ix.row_delta;
@@ -1241,7 +1279,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
         PSB_LAUNCH_CHECK();
     }
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_fallback<MM>(ix, ws, d_lut, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count,
-                                                  sm_count, s))));
+                                                  sm_count, s, rs))));
     return PSB_OK;
 }
 

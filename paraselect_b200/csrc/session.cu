@@ -386,6 +386,14 @@ int stage1_width(const psb_session* s, int topk) {
     return (int)std::min<long long>(s->opt.n_rerank, s->n_vectors);
 }
 
+// Residual mode without tables: when the tensor-core scan takes every list, nothing reads a materialised per-(query, probe)
+// table - the cutoff, the re-scoring selection and the fallback build entries from the query, the centroid and the codebook.
+bool residual_table_free(const psb_session* s, int stage1_k) {
+    return s->opt.adc_mode == 1 && s->row_aug.p != nullptr && (s->opt.scan_mode == 0 || s->opt.scan_mode == 3) &&
+           s->opt.tc_min_visitors <= 1 && scan_tc_supported(s->dim, s->m, s->k) &&
+           (size_t)pool_capacity(stage1_k) * 8 + (size_t)s->dim * 4 <= (size_t)226 * 1024;
+}
+
 // Tables one scan call needs for nq queries.
 size_t table_count(const psb_session* s, int nq, int nprobe) {
     return s->opt.adc_mode == 1 ? (size_t)nq * nprobe : (size_t)nq;
@@ -396,7 +404,7 @@ size_t table_count(const psb_session* s, int nq, int nprobe) {
 int sub_batch_rows(const psb_session* s, int n, int nprobe, bool overlap) {
     const int pipeline_parts = s->opt.pipeline_parts >= 2 && s->opt.pipeline_parts <= 32 ? s->opt.pipeline_parts : 4;
     int parts = overlap ? pipeline_parts : 1;
-    if (s->opt.adc_mode == 1) {
+    if (s->opt.adc_mode == 1 && !residual_table_free(s, stage1_width(s, 1))) {
         const double bytes = (double)n * nprobe * s->m * s->k * sizeof(float);
         parts = std::max(parts, (int)std::ceil(bytes / (16.0 * 1024 * 1024 * 1024)));
     }
@@ -426,7 +434,8 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
     s->pool_cap = cap;
     PSB_TRY(s->fail_list.reserve(sizeof(int) * (size_t)nq));
     PSB_TRY(s->fallback_partial.reserve(fallback_partial_bytes(stage1_k)));
-    if (s->opt.scan_mode != 1) {
+    const bool half_tables = s->opt.scan_mode != 1 && !residual_table_free(s, stage1_k);
+    if (half_tables) {
         PSB_TRY(s->lut_h.reserve(sizeof(unsigned short) * tables * s->m * s->k));
         PSB_TRY(s->lut_scale.reserve(sizeof(float) * tables));
     }
@@ -439,7 +448,7 @@ psb_status ensure_scan_ws(psb_session* s, int nq, int nprobe, int stage1_k) {
                                                 s->pool_cnt.bytes / sizeof(int), s->fail_list.bytes / sizeof(int),
                                                 s->pool.bytes / (sizeof(uint64_t) * (size_t)cap),
                                                 s->visitors.bytes / (sizeof(int) * (size_t)nprobe), (size_t)INT_MAX});
-    s->ws_scan_tables = s->opt.scan_mode != 1 ? (long long)std::min(s->lut_h.bytes / (sizeof(unsigned short) * (size_t)s->m * s->k),
+    s->ws_scan_tables = half_tables ? (long long)std::min(s->lut_h.bytes / (sizeof(unsigned short) * (size_t)s->m * s->k),
                                                                     s->lut_scale.bytes / sizeof(float))
                                               : (long long)tables;
     return PSB_OK;
@@ -450,7 +459,7 @@ psb_status ensure_pipeline_ws(psb_session* s, int nq, int nprobe, int topk, int 
     PSB_TRY(s->q.reserve(sizeof(float) * (size_t)nq * s->dim));
     PSB_TRY(s->probes.reserve(sizeof(int) * (size_t)nq * nprobe));
     PSB_TRY(s->probe_dist.reserve(sizeof(float) * (size_t)nq * nprobe));
-    PSB_TRY(s->lut.reserve(sizeof(float) * table_count(s, sb, nprobe) * s->m * s->k));
+    if (!residual_table_free(s, stage1_k)) PSB_TRY(s->lut.reserve(sizeof(float) * table_count(s, sb, nprobe) * s->m * s->k));
     PSB_TRY(s->cand_rows.reserve(sizeof(int) * (size_t)nq * stage1_k));
     PSB_TRY(s->cand_dist.reserve(sizeof(float) * (size_t)nq * stage1_k));
     PSB_TRY(s->cand_count.reserve(sizeof(int) * (size_t)nq));
@@ -858,7 +867,7 @@ psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int*
 
 psb_status psb_stage_scan_queries(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
                                   int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count) {
-    if (!s || !d_lut || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (!s || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");
     if (nprobe <= 0 || stage1_k <= 0) return fail(PSB_INVALID_ARGUMENT, "nprobe and stage1_k must be positive");
     if (nprobe > kMaxProbe || stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or stage1_k above 2048");
     PSB_CUDA(cudaSetDevice(s->device));
@@ -978,7 +987,8 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     for (size_t ci = 0; ci + 1 < cuts.size(); ++ci) sb_max = std::max(sb_max, cuts[ci + 1] - cuts[ci]);
     // The sub-batch size depends on this batch's own n (a short tail batch may run in one piece where the full batch ran
     // in four), so the tables and the scan workspace are sized here, for the largest sub-batch of THIS batch.
-    PSB_TRY(s->lut.reserve(sizeof(float) * table_count(s, sb_max, nprobe) * s->m * s->k));
+    const bool table_free = residual_table_free(s, stage1_k);
+    if (!table_free) PSB_TRY(s->lut.reserve(sizeof(float) * table_count(s, sb_max, nprobe) * s->m * s->k));
     PSB_TRY(ensure_scan_ws(s, sb_max, nprobe, stage1_k));
     if ((overlap || staged_overlap) && !s->aux_stream) {
         int lo = 0, hi = 0;  // lowest priority: the scan's CTAs get the SMs first, the transfer fills the gaps
@@ -1074,7 +1084,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         if (times) rc = tm_s.mark(st);
         ScanWorkspace sws;
         if (rc == PSB_OK) rc = s->timed_scan_ws(&sws);
-        if (rc == PSB_OK) {
+        if (rc == PSB_OK && !table_free) {
             if (residual && residual_tables_fused(sws, s->m, s->k)) {  // fp32 and fp16 tables in one kernel
                 rc = launch_build_tables_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
                                                   s->codebook.as<float>(), s->m, s->k, s->cb_maxnorm.as<float>(), s->lut.as<float>(),
@@ -1088,8 +1098,8 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
             }
         }
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
-        if (rc == PSB_OK) rc = launch_scan(s->scan_index(), sws, s->lut.as<float>(), m, probes, nprobe, stage1_k, rows_out,
-                                           dist_out, cnt_out, s->sm_count, st, q);
+        if (rc == PSB_OK) rc = launch_scan(s->scan_index(), sws, table_free ? nullptr : s->lut.as<float>(), m, probes, nprobe, stage1_k,
+                                           rows_out, dist_out, cnt_out, s->sm_count, st, q);
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
         if (rc != PSB_OK) break;
         if (staged_overlap) {  // hand the sub-batch to the worker: candidates to the host, an event marks them ready

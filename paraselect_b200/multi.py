@@ -56,11 +56,11 @@ class SessionEngine:
     """The CUDA library as the compute engine of ShardedSearch (device tensors are torch CUDA tensors)."""
 
     def __init__(self, session, torch):
-        if getattr(session, "residual", False):
-            raise NotImplementedError("the sharded step runs plain ADC sessions only (residual tables are per "
-                                      "(query, probe) and need the single-GPU pipeline's sub-batching)")
         self.s = session
         self.torch = torch
+        # residual sessions run without tables: the tensor-core scan works on q - centroid and the selection re-scores from
+        # the codebook (the session refuses the call where the shape does not allow that)
+        self.residual = bool(getattr(session, "residual", False))
 
     streams = True  # stage calls can be redirected to a second CUDA stream
 
@@ -74,11 +74,12 @@ class SessionEngine:
         self.s.stage_coarse(dq, nq, nprobe, out)
 
     def lut(self, dq, nq, out):
-        self.s.stage_build_lut(dq, nq, out)
+        if not self.residual:
+            self.s.stage_build_lut(dq, nq, out)
 
     def scan(self, dq, lut, nq, probes, nprobe, width, rows, dist, count):
         # with the queries at hand the scan can take the tensor-core pre-filter
-        self.s.stage_scan_queries(dq, lut, nq, probes, nprobe, width, rows, dist, count)
+        self.s.stage_scan_queries(dq, None if self.residual else lut, nq, probes, nprobe, width, rows, dist, count)
 
     def merge(self, rows, dist, parts, nq, width, out_rows, out_dist):
         self.s.stage_merge(rows, dist, parts, nq, width, out_rows, out_dist)

@@ -119,6 +119,43 @@ def test_tc_scan_residual_mode(psb, M, dim, stage1_k, n):
     check_against_fp32_scan(psb, ix, q, probes, stage1_k, residual=True)
 
 
+def test_tc_scan_residual_mode_without_tables(psb):
+    """Residual mode with no per-(query, probe) table at all (d_lut = NULL): the scan works on q - centroid, the cutoff, the
+    re-scoring selection and the fallback compute table entries from the query, the centroid and the codebook."""
+    torch = _torch()
+    ix = synth.make_index(90000, 96, 16, 48, seed=51, zipf=True, residual=True)
+    q = synth.make_queries(ix, 60, seed=7, weights=synth.zipf_weights(16))
+    probes, _ = oracle.coarse(q, ix["centroids"], 10)
+    orow, odist, ocnt, _ = oracle.pq_scan_residual(q, probes, ix["centroids"], ix["offsets"], ix["codes"], ix["codebook"], 700)[:4]
+    with psb.Session(ix, residual=True, scan_mode=3) as s:
+        dq, dp = dev(q), dev(probes.astype(np.int32))
+        rows = torch.empty((60, 700), dtype=torch.int32, device="cuda")
+        dist = torch.empty((60, 700), dtype=torch.float32, device="cuda")
+        cnt = torch.empty((60,), dtype=torch.int32, device="cuda")
+        s.stage_scan_queries(dq, None, 60, dp, 10, 700, rows, dist, cnt)
+        s.sync()
+        assert np.array_equal(cnt.cpu().numpy(), ocnt)
+        assert np.array_equal(rows.cpu().numpy(), orow) and np.array_equal(dist.cpu().numpy(), odist)
+    # every distance ties -> pools overflow -> the exact fallback builds its tables on the fly too
+    ix2 = synth.make_index(50000, 32, 4, 8, seed=1, residual=True)
+    ix2["codes"][:] = ix2["codes"][0]
+    q2 = synth.make_queries(ix2, 5, seed=2)
+    p2 = np.tile(np.arange(4), (5, 1)).astype(np.int64)
+    o2 = oracle.pq_scan_residual(q2, p2, ix2["centroids"], ix2["offsets"], ix2["codes"], ix2["codebook"], 512)[:3]
+    with psb.Session(ix2, residual=True, scan_mode=3) as s:
+        rows = torch.empty((5, 512), dtype=torch.int32, device="cuda")
+        dist = torch.empty((5, 512), dtype=torch.float32, device="cuda")
+        cnt = torch.empty((5,), dtype=torch.int32, device="cuda")
+        s.stage_scan_queries(dev(q2), None, 5, dev(p2.astype(np.int32)), 4, 512, rows, dist, cnt)
+        s.sync()
+        assert s.counters()["fallback_queries"] == 5
+        assert np.array_equal(rows.cpu().numpy(), o2[0]) and np.array_equal(dist.cpu().numpy(), o2[1])
+    # plain mode cannot go without its tables
+    with psb.Session(dict(synth.make_index(3000, 32, 8, 8, seed=5), vectors=None), scan_mode=3) as s:
+        with pytest.raises(psb.InvalidArgument):
+            s.stage_scan_queries(dev(q2), None, 5, dev(p2.astype(np.int32)), 4, 16, rows, dist, cnt)
+
+
 def test_tc_scan_split_by_visitor_count(psb):
     """tc_min_visitors = 20: lists with fewer visitors stay with the SIMT scan, the others go to the tensor-core kernel;
     the pools then hold exact keys and unscored survivors side by side."""
