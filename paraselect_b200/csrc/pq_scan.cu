@@ -178,6 +178,7 @@ struct ResidualSource {
     const float* queries;    // [nq][dim]
     const float* centroids;  // [nlist][dim]
     const float* codebook;   // [m][k][dim / m]
+    const float* row_bias;   // [shard rows] 2 <centroid[list(row)], recon(row)>, or null
     int dim;
 };
 __device__ __forceinline__ void stage_residual_table(float* __restrict__ s_lut, const float* __restrict__ lut, const ResidualSource& rs,
@@ -191,12 +192,18 @@ __device__ __forceinline__ void stage_residual_table(float* __restrict__ s_lut, 
     const int dsub = rs.dim / m;
     const float* qv = rs.queries + (size_t)q * rs.dim;
     const float* cv = rs.centroids + (size_t)list * rs.dim;
+    __shared__ float s_qres[256];  // q - centroid, staged once when it fits (the callers' barriers around this call order its reuse)
+    const bool staged = rs.dim <= 256;
+    if (staged) {
+        for (int d = threadIdx.x; d < rs.dim; d += blockDim.x) s_qres[d] = __fsub_rn(__ldg(qv + d), __ldg(cv + d));
+        __syncthreads();
+    }
     for (int e = threadIdx.x; e < mk; e += blockDim.x) {
         const int sub = e / k;
         const float* c = rs.codebook + (size_t)e * dsub;
         float dist = 0.0f;
         for (int d = 0; d < dsub; ++d) {
-            const float r = __fsub_rn(__ldg(qv + sub * dsub + d), __ldg(cv + sub * dsub + d));
+            const float r = staged ? s_qres[sub * dsub + d] : __fsub_rn(__ldg(qv + sub * dsub + d), __ldg(cv + sub * dsub + d));
             const float diff = __fsub_rn(r, __ldg(c + d));
             dist = __fadd_rn(dist, __fmul_rn(diff, diff));
         }
@@ -236,8 +243,40 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     int stride = stage1_k / 16;
     stride = stride < 16 ? 16 : (stride > 64 ? 64 : stride);
     if ((N + 65535) / 65536 > stride) stride = (int)((N + 65535) / 65536);  // at most ~64K samples per query
-    if (!per_probe)
+    // Residual mode without materialised tables: no per-probe staging.  With c the probed list's centroid,
+    //     |(q - c) - recon|^2 = |q - recon|^2 + (|c|^2 - 2 <c, q>) + 2 <c, recon>,
+    // so ONE table per query (the plain-mode table of q, built here) serves every probed list, plus a constant per probe and a
+    // bias per row that was computed once per index (the reference's shared-table form with a per-row correction:
+    // src/search/kernels/fine/gpu_fine/pq_adc/pq_query_lut_score.cuh:7-22, src/common/row_correction.h:37-45).  The sum is
+    // the same distance in a different rounding; it only places the CUTOFF, whose exact value does not matter: the selection
+    // counts the rows whose EXACT distance is within it and falls back to the exact scan when they are too few.
+    const bool flat_bias = per_probe && lut == nullptr;
+    float* s_pk = reinterpret_cast<float*>(s_pref + nprobe + 1);  // [nprobe] |c|^2 - 2 <c, q> per probe (flat_bias only)
+    if (!per_probe) {
         for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
+    } else if (flat_bias) {
+        const int dsub = rs.dim / m;
+        const float* qv = rs.queries + (size_t)q * rs.dim;
+        for (int e = threadIdx.x; e < m * k; e += blockDim.x) {
+            const int sub = e / k;
+            const float* c = rs.codebook + (size_t)e * dsub;
+            float dist = 0.0f;
+            for (int d = 0; d < dsub; ++d) { const float diff = __ldg(qv + sub * dsub + d) - __ldg(c + d); dist = fmaf(diff, diff, dist); }
+            s_lut[e] = dist;
+        }
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int p = warp; p < nprobe; p += (int)(blockDim.x >> 5)) {
+            const int l = probes[(size_t)q * nprobe + p];
+            float acc = 0.0f;
+            if (l >= 0 && l < nlist) {
+                const float* cv = rs.centroids + (size_t)l * rs.dim;
+                for (int d = lane; d < rs.dim; d += 32) { const float c = __ldg(cv + d); acc = fmaf(c, c - 2.0f * __ldg(qv + d), acc); }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) s_pk[p] = acc;
+        }
+    }
     // samples per probe and their exclusive prefix
     int carry = 0;
     for (int p0 = 0; p0 < nprobe; p0 += blockDim.x) {
@@ -258,11 +297,12 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     const int r = (int)ceilf(mu + margin_sigma * sqrtf(mu) + margin_add);
     if (r >= ns || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; return; }
     __syncthreads();
-    const int nseg = per_probe ? nprobe : 1;
+    const bool staged_probes = per_probe && !flat_bias;  // one table per probe, staged one after the other
+    const int nseg = staged_probes ? nprobe : 1;
     for (int sg = 0; sg < nseg; ++sg) {
-        const int b0 = per_probe ? s_pref[sg] : 0, b1 = per_probe ? s_pref[sg + 1] : ns;  // uniform
+        const int b0 = staged_probes ? s_pref[sg] : 0, b1 = staged_probes ? s_pref[sg + 1] : ns;  // uniform
         if (b0 == b1) continue;
-        if (per_probe) {
+        if (staged_probes) {
             __syncthreads();  // the previous probe's table is no longer read
             stage_residual_table(s_lut, lut, rs, q, sg, nprobe, probes[(size_t)q * nprobe + sg], m, k);
             __syncthreads();
@@ -280,7 +320,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
             const int idx = base + threadIdx.x;
             if (idx < b1) {
                 int lo = sg, hi = nprobe;  // largest p with s_pref[p] <= idx
-                if (!per_probe) {
+                if (!staged_probes) {
                     lo = 0;
                     while (hi - lo > 1) {
                         const int mid = (lo + hi) >> 1;
@@ -289,7 +329,10 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
                 }
                 const int l = probes[(size_t)q * nprobe + lo];
                 const long long row = offsets[l] + (long long)(idx - s_pref[lo]) * stride;
-                const uint32_t key = f2o(adc_row<M>(codes + (size_t)(row - row_base) * m, s_lut, m, k, tree != 0));
+                const uint8_t* rp = codes + (size_t)(row - row_base) * m;
+                float sd = adc_row<M>(rp, s_lut, m, k, tree != 0);
+                if (flat_bias) sd = fmaxf(sd + s_pk[lo] + __ldg(rs.row_bias + (row - row_base)), 0.0f);
+                const uint32_t key = f2o(sd);
                 if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
             }
             __syncthreads();
@@ -1054,7 +1097,9 @@ float seed_margin_sigma(const ScanWorkspace& ws) { return ws.seed_sigma >= 2.f &
 template <int M>
 psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d_lut, int nq, const int* d_probes,
                     int nprobe, int stage1_k, cudaStream_t s, const ResidualSource& rs) {
-    const size_t smem = (size_t)ix.m * ix.k * sizeof(float) + kSeedBuf * sizeof(uint32_t) + ((size_t)nprobe + 1) * sizeof(int);
+    const size_t smem = (size_t)ix.m * ix.k * sizeof(float) + kSeedBuf * sizeof(uint32_t) + ((size_t)nprobe + 1) * sizeof(int) +
+                        (size_t)nprobe * sizeof(float);
+    if (ix.residual && !d_lut && !rs.row_bias) return fail(PSB_INTERNAL, "residual scan without tables: the per-row bias is missing");
     PSB_TRY(set_smem(k_seed_threshold<M>, smem));
     PSB_TRY(prefer_max_shared(k_seed_threshold<M>));
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
@@ -1222,7 +1267,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     PSB_LAUNCH_CHECK();
     // cutoff
     ResidualSource rs;
-    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.dim = ix.dim;
+    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.row_bias = ix.row_bias; rs.dim = ix.dim;
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s, rs))));
     // scan
     ScanArgs a;

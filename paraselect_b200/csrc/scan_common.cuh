@@ -120,5 +120,46 @@ __device__ __forceinline__ float adc_row(const uint8_t* row, const float* s_lut,
 }
 
 
+// Residual-mode ADC distance of one code row WITHOUT a table: every entry is computed from the residual query (qres = q -
+// centroid, [dim]) and the codeword as k_build_lut_residual would store it - the sequential non-fused sum over the
+// sub-vector - and the entries are summed in the CPU path's order (sequential, or the pairwise tree for M = 8 / 16).
+// Worth it when a table (m * k entries) would serve fewer than k rows.  cen != null: qres holds the query itself and the
+// centroid is subtracted here (fp32, the same subtraction).
+template <int M>
+__device__ __forceinline__ float adc_row_direct(const uint8_t* __restrict__ row, const float* __restrict__ qres,
+                                                const float* __restrict__ codebook, int m, int k, int dsub, bool tree,
+                                                const float* __restrict__ cen = nullptr) {
+    auto entry = [&](int j, int code) {
+        const float* cb = codebook + ((size_t)j * k + code) * dsub;
+        float e = 0.0f;
+        for (int d = 0; d < dsub; ++d) {
+            float qv = qres[j * dsub + d];
+            if (cen) qv = __fsub_rn(qv, __ldg(cen + j * dsub + d));
+            const float diff = __fsub_rn(qv, __ldg(cb + d));
+            e = __fadd_rn(e, __fmul_rn(diff, diff));
+        }
+        return e;
+    };
+    if constexpr (M > 0 && M % 4 == 0) {
+        // templated M: the code words are loaded first and the loop is unrolled, so the codeword loads of all sub-quantisers are
+        // in flight together (a rolled loop would wait for one dependent load after the other)
+        uint32_t cw[M / 4];
+#pragma unroll
+        for (int w = 0; w < M / 4; ++w) cw[w] = __ldg(reinterpret_cast<const uint32_t*>(row) + w);
+        float t[M];
+#pragma unroll
+        for (int j = 0; j < M; ++j) t[j] = entry(j, (int)((cw[j >> 2] >> ((j & 3) * 8)) & 255u));
+        if constexpr (M == 8 || M == 16) { if (tree) return tree_sum<M>(t); }
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < M; ++j) acc = __fadd_rn(acc, t[j]);
+        return acc;
+    } else {
+        float acc = 0.0f;
+        for (int j = 0; j < m; ++j) acc = __fadd_rn(acc, entry(j, (int)__ldg(row + j)));
+        return acc;
+    }
+}
+
 }  // namespace scan
 }  // namespace psb

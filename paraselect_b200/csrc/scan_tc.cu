@@ -582,16 +582,6 @@ struct RescoreArgs {
     int* fail_list; int* n_fail; unsigned long long* counters;
 };
 
-// One table entry computed directly: the sequential non-fused sum over the sub-vector (what k_build_lut_residual stores).
-__device__ __forceinline__ float entry_direct(const float* __restrict__ qres, const float* __restrict__ cb, int dsub) {
-    float e = 0.0f;
-    for (int d = 0; d < dsub; ++d) {
-        const float diff = __fsub_rn(qres[d], __ldg(cb + d));
-        e = __fadd_rn(e, __fmul_rn(diff, diff));
-    }
-    return e;
-}
-
 template <int M>
 __global__ void __launch_bounds__(kRescoreThreads) k_select_rescore(const RescoreArgs g) {
     extern __shared__ __align__(16) unsigned char s_sel[];
@@ -637,17 +627,7 @@ __global__ void __launch_bounds__(kRescoreThreads) k_select_rescore(const Rescor
                 } else {
                     l = g.probes[hi];
                     const float* cen = g.centroids + (size_t)l * g.dim;
-                    float t[M > 0 ? M : 1];
-                    float acc = 0.0f;
-                    for (int j = 0; j < g.m; ++j) {
-                        float qres[8];  // dsub <= 8 on this path
-                        for (int x = 0; x < dsub; ++x) qres[x] = __fsub_rn(s_tab[j * dsub + x], __ldg(cen + j * dsub + x));
-                        const float en = entry_direct(qres, g.codebook + ((size_t)j * g.k + __ldg(row + j)) * dsub, dsub);
-                        if constexpr (M == 8 || M == 16) { if (g.tree) { t[j] = en; continue; } }
-                        acc = __fadd_rn(acc, en);
-                    }
-                    if constexpr (M == 8 || M == 16) { if (g.tree) acc = tree_sum<M>(t); }
-                    d = acc;
+                    d = adc_row_direct<M>(row, s_tab, g.codebook, g.m, g.k, dsub, g.tree != 0, cen);
                 }
                 if (d <= cut) {
                     const long long delta = g.row_delta ? g.row_delta[l] : 0;
@@ -706,6 +686,45 @@ bool scan_tc_supported(int dim, int m, int k) {
 float scan_tc_eps(int dim) {
     const int kp = (dim + kAugSlots + 15) / 16 * 16;
     return (float)kp * (1.0f / 4194304.0f) * 2.0f;  // kp * 2^-22 * 2: tensor-core accumulation plus the fp32 norms
+}
+
+namespace {
+// One CTA per (list, block of 1024 rows): the centroid sits in shared memory, every thread sums 2 c . codeword over its row.
+__global__ void __launch_bounds__(256) k_row_bias(const uint8_t* __restrict__ codes, const long long* __restrict__ offsets, long long row_base,
+                                                  int list_begin, int list_end, int dim, int m, int k, const float* __restrict__ codebook,
+                                                  const float* __restrict__ centroids, float* __restrict__ out) {
+    extern __shared__ float s_cen[];  // [dim]
+    const int dsub = dim / m;
+    for (int l = list_begin + blockIdx.y; l < list_end; l += gridDim.y) {
+        const long long b = offsets[l], e = offsets[l + 1];
+        if ((long long)blockIdx.x * 1024 >= e - b) continue;
+        __syncthreads();
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) s_cen[d] = centroids[(size_t)l * dim + d];
+        __syncthreads();
+        for (long long r0 = b + (long long)blockIdx.x * 1024; r0 < e; r0 += (long long)gridDim.x * 1024) {
+            for (long long r = r0 + threadIdx.x; r < min(r0 + 1024, e); r += blockDim.x) {
+                const uint8_t* row = codes + (size_t)(r - row_base) * m;
+                float acc = 0.0f;
+                for (int j = 0; j < m; ++j) {
+                    const float* cb = codebook + ((size_t)j * k + __ldg(row + j)) * dsub;
+                    for (int d = 0; d < dsub; ++d) acc = fmaf(s_cen[j * dsub + d], __ldg(cb + d), acc);
+                }
+                out[r - row_base] = 2.0f * acc;
+            }
+        }
+    }
+}
+}  // namespace
+
+psb_status launch_row_bias(const uint8_t* d_codes, const long long* d_offsets, long long row_base, int list_begin, int list_end,
+                           int dim, int m, int k, const float* d_codebook, const float* d_centroids, float* d_out, cudaStream_t s) {
+    if (list_end <= list_begin) return PSB_OK;
+    const dim3 grid(64, (unsigned)std::min(list_end - list_begin, 1024));
+    k_row_bias<<<grid, 256, (size_t)dim * sizeof(float), s>>>(d_codes, d_offsets, row_base, list_begin, list_end, dim, m, k, d_codebook,
+                                                               d_centroids, d_out);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
 }
 
 psb_status launch_row_aug(const uint8_t* d_codes, long long rows, int dim, int m, int k, const float* d_codebook, void* d_out,

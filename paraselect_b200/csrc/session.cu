@@ -233,7 +233,7 @@ struct psb_session {
     int list_begin = 0, list_end = 0;
     long long row_base = 0, shard_rows = 0;
     // device copies
-    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta, exact_cache, row_aug;
+    DevBuf centroids, offsets, reordered, codes, codebook, cb_maxnorm, global_begin, row_delta, exact_cache, row_aug, row_bias;
     bool striped = false;          // shard holds a slice of every list (options.list_global_begin)
     // exact rows
     int exact_elem = 0;            // 4 = fp32, 1 = u8, 0 = rerank disabled
@@ -297,7 +297,7 @@ struct psb_session {
         ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
         ix.row_delta = striped ? row_delta.as<long long>() : nullptr;
         ix.residual = opt.adc_mode == 1;
-        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim; ix.row_aug = row_aug.p;
+        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim; ix.row_aug = row_aug.p; ix.row_bias = row_bias.as<float>();
         return ix;
     }
     // Which index-wide rows the exact store and the id table of this session hold.
@@ -389,7 +389,7 @@ int stage1_width(const psb_session* s, int topk) {
 // Residual mode without tables: when the tensor-core scan takes every list, nothing reads a materialised per-(query, probe)
 // table - the cutoff, the re-scoring selection and the fallback build entries from the query, the centroid and the codebook.
 bool residual_table_free(const psb_session* s, int stage1_k) {
-    return s->opt.adc_mode == 1 && s->row_aug.p != nullptr && (s->opt.scan_mode == 0 || s->opt.scan_mode == 3) &&
+    return s->opt.adc_mode == 1 && s->row_aug.p != nullptr && s->row_bias.p != nullptr && (s->opt.scan_mode == 0 || s->opt.scan_mode == 3) &&
            s->opt.tc_min_visitors <= 1 && scan_tc_supported(s->dim, s->m, s->k) &&
            (size_t)pool_capacity(stage1_k) * 8 + (size_t)s->dim * 4 <= (size_t)226 * 1024;
 }
@@ -752,6 +752,11 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if ((opt.scan_mode == 0 || opt.scan_mode == 3) && s->shard_rows > 0 && scan_tc_supported(s->dim, s->m, s->k)) {
         PSB_TRY(s->row_aug.reserve((size_t)s->shard_rows * 8));
         PSB_TRY(launch_row_aug(s->codes.as<uint8_t>(), s->shard_rows, s->dim, s->m, s->k, s->codebook.as<float>(), s->row_aug.p, st));
+        if (opt.adc_mode == 1) {  // the per-row bias of the residual cutoff estimate
+            PSB_TRY(s->row_bias.reserve(sizeof(float) * (size_t)s->shard_rows));
+            PSB_TRY(launch_row_bias(s->codes.as<uint8_t>(), s->offsets.as<long long>(), s->row_base, lb, le, s->dim, s->m, s->k,
+                                    s->codebook.as<float>(), s->centroids.as<float>(), s->row_bias.as<float>(), st));
+        }
     }
     {   // per sub-quantiser the largest codeword norm (residual-mode table builder)
         const int dsub = s->dim / s->m;
