@@ -16,8 +16,10 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "_build", "libpsb_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libpsb_ref.so")
+REF_TRAIN_SO = os.path.join(_HERE, "_ref", "libpsb_ref_train.so")
 _lib = None
 _ref = None
+_ref_train = None
 
 f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
@@ -59,6 +61,18 @@ def ref():
         _ref.psbref_last_error.restype = C.c_char_p
         _ref.psbref_fp32_isa.restype = C.c_char_p
     return _ref
+
+
+def have_ref_train() -> bool:
+    return os.path.exists(REF_TRAIN_SO)
+
+
+def ref_train():
+    """The reference's IVF-Flat search, CPU Lloyd k-means and CPU PQ trainer / encoder (oracle/ref_train_harness.cu)."""
+    global _ref_train
+    if _ref_train is None:
+        _ref_train = C.CDLL(REF_TRAIN_SO)
+    return _ref_train
 
 
 def _c(a, dt):
@@ -330,3 +344,52 @@ def ref_rerank(base, queries, candidates, topk, candidate_count=None, counts=Non
     if rc:
         raise RuntimeError(ref().psbref_last_error().decode())
     return ids, dist
+
+
+# ---------------------------------------------------------------- reference wrappers: IVF-Flat, k-means, PQ training
+def ref_cpu_ivf_search(centroids, offsets, reordered_ids, base, queries, nprobe, topk):
+    """cpu_ivf_search (src/cpu/search/cpu_search.h:226-332): ids, distances, coarse ids, coarse distances."""
+    queries = _c(queries, np.float32); centroids = _c(centroids, np.float32); base = _c(base, np.float32)
+    offsets = _c(offsets, np.int64)
+    rid = None if reordered_ids is None else _c(reordered_ids, np.int64)
+    nq, dim = queries.shape
+    out_i = np.empty((nq, topk), np.int64); out_d = np.empty((nq, topk), np.float32)
+    c_i = np.empty((nq, nprobe), np.int64); c_d = np.empty((nq, nprobe), np.float32)
+    ref_train().psbref_cpu_ivf_search(_ptr(queries), nq, dim, _ptr(base), _ptr(centroids), centroids.shape[0], _ptr(offsets),
+                                      _ptr(rid), nprobe, topk, _ptr(out_i), _ptr(out_d), _ptr(c_i), _ptr(c_d))
+    return out_i, out_d, c_i, c_d
+
+
+def ref_kmeans_lloyd(data, init_centroids, iters):
+    """cpu_kmeans_lloyd (src/cpu/clustering/cpu_kmeans.h:27-143): centroids after `iters` iterations, the assignment made in
+    the last iteration (against the centroids it started from) and that iteration's objective."""
+    data = _c(data, np.float32); cen = np.array(init_centroids, dtype=np.float32, order="C", copy=True)
+    n, dim = data.shape
+    assign = np.empty(n, np.int32); obj = C.c_float()
+    ref_train().psbref_cpu_kmeans_lloyd(_ptr(data), n, dim, cen.shape[0], iters, _ptr(cen), _ptr(assign), C.byref(obj))
+    return cen, assign, float(obj.value)
+
+
+def ref_pq_train_encode(data, M, K):
+    """PQQuantizerCPU::train + ::encode (src/quantization/pq/pq_quantizer_cpu.cpp:26-68): codebook [M][K][dsub], codes [n][M]."""
+    data = _c(data, np.float32)
+    n, dim = data.shape
+    cb = np.empty((M, K, dim // M), np.float32); codes = np.empty((n, M), np.uint8)
+    rc = ref_train().psbref_pq_train_encode(_ptr(data), n, dim, M, K, _ptr(cb), _ptr(codes))
+    if rc:
+        raise ValueError("reference PQ training refused the shape")
+    return cb, codes
+
+
+def ref_pq_init_rows(n, K, seed):
+    rows = np.empty(K, np.int32)
+    ref_train().psbref_pq_init_rows(n, K, C.c_uint(seed), _ptr(rows))
+    return rows
+
+
+def ref_pq_kmeans_subspace(sub, K, iters, seed):
+    sub = _c(sub, np.float32)
+    n, dsub = sub.shape
+    out = np.empty((K, dsub), np.float32)
+    ref_train().psbref_pq_kmeans_subspace(_ptr(sub), n, dsub, K, iters, C.c_uint(seed), _ptr(out))
+    return out

@@ -201,3 +201,78 @@ def test_restatement_vs_reference_live(seed, dim, M, nlist, zipf):
     else:
         assert np.allclose(r["distances"], o["distances"], rtol=1e-5)
     assert r["scanned"] == o["scanned"]
+
+
+# ---------------------------------------------------------------------------------------------- IVF-Flat, k-means, PQ training
+# The restatement against more of the reference's own CPU code (oracle/ref_train_harness.cu): live where that library was built.
+needs_ref_train = pytest.mark.skipif(not oracle.have_ref_train(), reason="oracle/_ref/libpsb_ref_train.so is not built here")
+
+
+@needs_ref_train
+def test_ivfflat_and_coarse_match_the_reference_cpu_search():
+    # cpu_ivf_search (src/cpu/search/cpu_search.h:226-332); its partial_sort / nth_element leave the order of equal distances
+    # open, so ids are compared where distances are distinct (all of them, for real-valued data) and as sets inside ties
+    ix = synth.make_index(20000, 128, 64, 8, seed=9)
+    q = synth.make_queries(ix, 50, seed=10)
+    want_i, want_d, want_ci, want_cd = oracle.ref_cpu_ivf_search(ix["centroids"], ix["offsets"], ix["reordered_ids"], ix["vectors"], q, 8, 10)
+    got_i, got_d = oracle.ivfflat_search(ix["centroids"], ix["offsets"], ix["reordered_ids"], ix["vectors"], q, 8, 10)
+    assert np.array_equal(got_d, want_d)  # bit-exact distances
+    assert np.array_equal(got_i, want_i)
+    ci, cd = oracle.coarse(q, ix["centroids"], 8)
+    assert np.array_equal(cd, want_cd) and np.array_equal(ci, want_ci)
+    # integer grid: many exactly equal distances - the multiset of distances and, per distance, the id sets must agree
+    rng = np.random.default_rng(1)
+    base = rng.integers(-2, 3, (3000, 16)).astype(np.float32)
+    cen = rng.integers(-2, 3, (16, 16)).astype(np.float32)
+    cen[1] = cen[0] + 1  # keep centroids distinct enough that coarse ties stay rare
+    off = np.linspace(0, 3000, 17).astype(np.int64)
+    qq = rng.integers(-2, 3, (20, 16)).astype(np.float32)
+    wi, wd, _, _ = oracle.ref_cpu_ivf_search(cen, off, None, base, qq, 16, 25)
+    gi, gd = oracle.ivfflat_search(cen, off, None, base, qq, 16, 25)
+    assert np.array_equal(gd, wd)
+    for a, b, d in zip(gi, wi, gd):
+        inner = d < d[-1]  # below the boundary distance the sets are fully determined
+        assert set(a[inner].tolist()) == set(b[inner].tolist())
+
+
+@needs_ref_train
+def test_kmeans_assignment_and_update_match_the_reference_cpu_kmeans():
+    # cpu_kmeans_lloyd (src/cpu/clustering/cpu_kmeans.h:27-143): strict <, lowest index wins; empty clusters keep their centroid
+    _, data, _ = synth.mixture(6000, 24, 30, 0.3, seed=21)
+    init = data[:40].copy()
+    init[7] = 1e3  # a centroid no row is assigned to
+    cen1, assign0, obj0 = oracle.ref_kmeans_lloyd(data, init, 1)
+    a, d = oracle.kmeans_assign(data, init)
+    assert np.array_equal(a, assign0)                            # assignment: bit-exact
+    assert abs(float(d.astype(np.float64).sum()) - obj0) <= 1e-5 * obj0
+    mine, _, _ = oracle.kmeans_lloyd(data, init, 1)
+    assert np.array_equal(mine[7], init[7])                      # the empty cluster kept its centroid on both sides
+    assert np.array_equal(cen1[7], init[7])
+    # the reference accumulates the sums in fp32 per thread; the restatement's means agree to fp32 accumulation error
+    assert np.allclose(mine, cen1, rtol=2e-5, atol=2e-6)
+    cen5, assign4, obj4 = oracle.ref_kmeans_lloyd(data, init, 5)
+    mine5, _, objs = oracle.kmeans_lloyd(data, init, 5)
+    assert np.allclose(mine5, cen5, rtol=1e-3, atol=1e-4) and abs(objs[4] - obj4) <= 1e-4 * obj4
+
+
+@needs_ref_train
+def test_pq_encode_and_training_match_the_reference_cpu_quantiser():
+    # PQQuantizerCPU (src/quantization/pq/pq_quantizer_cpu.cpp:26-68) on top of pq_kmeans_subspace (pq_kmeans.cpp:12-74)
+    _, data, _ = synth.mixture(3000, 32, 20, 0.3, seed=31)
+    cb, codes = oracle.ref_pq_train_encode(data, 8, 64)
+    assert np.array_equal(oracle.pq_encode(data, cb), codes)     # encoding: nearest codeword, ties to the lowest code - bit-exact
+    # training: pq_kmeans_subspace draws its initial codewords with std::mt19937(42 + m) (with replacement) and runs Lloyd
+    # iterations accumulating in fp32 row by row.  One iteration from the same initial rows gives the same codewords as the
+    # restatement for every codeword that got rows; a codeword WITHOUT rows is zeroed by this CPU trainer, while the
+    # reference's GPU trainer (src/clustering/kmeans/kmeans_utils.cu:267-284) - the one the library follows - keeps it.
+    for m in (0, 5):
+        sub = np.ascontiguousarray(data[:, m * 4:(m + 1) * 4])
+        rows = oracle.ref_pq_init_rows(sub.shape[0], 64, 42 + m)
+        init = sub[rows]
+        ref1 = oracle.ref_pq_kmeans_subspace(sub, 64, 1, 42 + m)
+        mine, assign, _ = oracle.kmeans_lloyd(sub, init, 1)
+        a0, _ = oracle.kmeans_assign(sub, init)
+        used = np.bincount(a0, minlength=64) > 0
+        assert np.allclose(mine[used], ref1[used], rtol=2e-5, atol=2e-6)
+        assert np.all(ref1[~used] == 0) and np.array_equal(mine[~used], init[~used])
+        assert np.array_equal(oracle.ref_pq_kmeans_subspace(sub, 64, 25, 42 + m), cb[m])  # train() == 25 iterations of it
