@@ -38,6 +38,9 @@ WORKLOADS = {
     "c4r": dict(n=100_000_000, dim=96, nlist=65536, M=48, sigma=0.25, zipf=1.1, nq=10000, nprobe=128, topk=100,
                 n_rerank=1000, seed=3, residual=True,
                 desc="IVF-ResidualPQ 100Mx96 nlist=65536 M=48 nprobe=128 k=100 rerank=1000 batch=10000"),
+    # benchmark configuration "IVF-Flat fp32" (the reference's own CPU-runnable case): lists from 10 Lloyd iterations
+    "c1": dict(n=100_000, dim=128, nlist=256, M=0, sigma=0.3, zipf=None, nq=1000, nprobe=16, topk=10, n_rerank=0, seed=0, iters=10,
+               desc="IVF-Flat 100kx128 (256-component mixture, sigma 0.3) nlist=256 from 10 Lloyd iterations, 1,000 queries, nprobe=16 k=10, exact L2"),
     # benchmark configuration "IVF-PQ fp32 1M"
     "c2": dict(n=1_000_000, dim=128, nlist=1024, M=32, sigma=0.25, zipf=None, nq=10000, nprobe=32, topk=10,
                n_rerank=100, seed=1, desc="IVF-PQ 1Mx128 nlist=1024 M=32 nprobe=32 k=10 rerank=100 batch=10000"),
@@ -355,6 +358,10 @@ def main():
     if args.impl == "ours" and world > 1:
         return multi_gpu_main(args, cfg, rank, world, local_rank)
 
+    if args.workload == "c1":
+        if world > 1:
+            raise SystemExit("workload c1 is a single-GPU line")
+        return flat_search(args, cfg, torch, api, device)
     if args.workload == "c3":
         return coarse_only(args, cfg, torch, api, device)
     if args.workload == "c5":
@@ -692,6 +699,133 @@ def build_stripe(cfg, torch, api, device, offsets, gb, loff):
     return index, centres
 
 
+
+
+def flat_search(args, cfg, torch, api, device):
+    """Workload c1: IVF-Flat.  The reference's own CPU-runnable configuration; the library runs it with the rows resident in
+    device memory.  A step = the batch of 1,000 queries through coarse -> exact fine scan -> id map."""
+    import oracle
+    n, dim, nlist, nq, nprobe, topk = cfg["n"], cfg["dim"], cfg["nlist"], cfg["nq"], cfg["nprobe"], cfg["topk"]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        st = stream.cuda_stream
+        w, offsets = populations(n, nlist, None)
+        d_off = torch.from_numpy(offsets).cuda()
+        centres = torch.empty((nlist, dim), dtype=torch.float32, device="cuda")
+        api.gen_normal(cfg["seed"] * 1000 + 1, 0, nlist * dim, 1.0, centres, device=device, stream=st)
+        x = torch.empty((n, dim), dtype=torch.float32, device="cuda")
+        api.gen_mixture_rows(centres, d_off, nlist, dim, cfg["sigma"], cfg["seed"] * 1000 + 2, 0, n, x, device=device, stream=st)
+        torch.cuda.synchronize()
+        dq = make_queries(cfg, torch, api, centres, w, device)
+        # the index: 10 Lloyd iterations from a seeded sample of rows (k-means on the GPU), rows reordered by list
+        g = torch.Generator(device="cuda"); g.manual_seed(cfg["seed"])
+        cen = x[torch.randperm(n, device="cuda", generator=g)[:nlist]].clone()
+        assign = torch.empty((n,), dtype=torch.int32, device="cuda")
+        api.kmeans_train(x, n, dim, cen, nlist, cfg["iters"], assign, device=device, stream=st)
+        torch.cuda.synchronize()
+        order = torch.argsort(assign.long(), stable=True)
+        counts = torch.bincount(assign.long(), minlength=nlist).cpu().numpy()
+        loff = np.zeros(nlist + 1, np.int64); loff[1:] = np.cumsum(counts)
+        index = dict(centroids=cen.cpu().numpy(), offsets=loff, reordered_ids=order.cpu().numpy().astype(np.int64),
+                     vectors=x[order].cpu().numpy())
+        q_host = dq.cpu().numpy()
+        cores = os.cpu_count() or 1
+
+        def cpu_run(qs):
+            t0 = time.time()
+            if oracle.have_ref_train():
+                r = oracle.ref_cpu_ivf_search(index["centroids"], index["offsets"], index["reordered_ids"], index["vectors"], qs, nprobe, topk)[:2]
+                kind = "reference"
+            else:
+                r = oracle.ivfflat_search(index["centroids"], index["offsets"], index["reordered_ids"], index["vectors"], qs, nprobe, topk)
+                kind = "port"
+            return r, time.time() - t0, kind
+
+        if args.impl == "reference":
+            times = []
+            for i in range(args.warmup + args.steps):
+                _, dt, kind = cpu_run(q_host)   # the whole batch: this is the reference's own CPU-runnable case
+                if i >= args.warmup:
+                    times.append(dt)
+            ms = 1e3 * float(np.mean(times))
+            v = round(nq / (ms * 1e-3), 2)
+            emit(dict(impl="reference", metric="QPS (IVF-Flat search, exact L2)", value=v, unit="queries/s", n_gpus=args.gpus,
+                      steps=args.steps, warmup=args.warmup, ms_per_step=round(ms, 3), higher_is_better=True, scaling="strong",
+                      vs_baseline=None, dtype="f32", data="synthetic", config=dict(workload="c1", desc=cfg["desc"]),
+                      cpu_baseline=dict(value=v, unit="queries/s", cores=cores, kind=kind,
+                                        sample="all %d queries per step (cpu_ivf_search on the physical cores)" % nq),
+                      e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0)))
+            return 0
+        sess = api.FlatSession(index, device=device, max_batch=nq, stream=st, time_kernels=True)
+        d_ids = torch.empty((nq, topk), dtype=torch.int64, device="cuda")
+        d_dist = torch.empty((nq, topk), dtype=torch.float32, device="cuda")
+        reps = 20  # a step is short: time `reps` batches per step so the clock sampler sees the load
+        for _ in range(max(args.warmup, 3)):
+            sess.search_device(dq, nq, nprobe, topk, d_ids, d_dist)
+        torch.cuda.synchronize()
+        sess.counters(reset=True)
+        sampler = ClockSampler(device)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps * reps):
+            sess.search_device(dq, nq, nprobe, topk, d_ids, d_dist)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (args.steps * reps)
+        c = sess.counters(reset=True)
+        qp = torch.empty((nq, dim), dtype=torch.float32).pin_memory(); qp.copy_(dq)
+        oi = torch.empty((nq, topk), dtype=torch.int64).pin_memory()
+        od = torch.empty((nq, topk), dtype=torch.float32).pin_memory()
+        stt = api.Stats()
+        sess.search_raw(qp.data_ptr(), nq, nprobe, topk, nq, oi.data_ptr(), od.data_ptr(), stt)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps * reps):
+            sess.search_raw(qp.data_ptr(), nq, nprobe, topk, nq, oi.data_ptr(), od.data_ptr(), stt)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / (args.steps * reps)
+        clocks = sampler.stop()
+        stats = stt.as_dict()
+        got_i, got_d = oi.numpy().copy(), od.numpy().copy()
+        # exact ground truth for recall
+        gi = torch.empty((nq, topk), dtype=torch.int32, device="cuda")
+        gd = torch.empty((nq, topk), dtype=torch.float32, device="cuda")
+        api.knn_exact(dq, nq, x, n, dim, topk, gi, gd, device=device, stream=st)
+        torch.cuda.synchronize()
+        truth = gi.cpu().numpy().astype(np.int64)
+    (ri, rd), dt, kind = cpu_run(q_host)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    rows_per_launch = c["pq_scanned_codes"] / max(1, c["scan_kernel_launches"])
+    scan_ms = c["scan_kernel_ms"] / max(1, c["scan_kernel_launches"])
+    achieved = rows_per_launch * dim * 4 / (scan_ms * 1e-3) / 1e9 if scan_ms > 0 else 0.0
+    emit(dict(metric="QPS (IVF-Flat search, exact L2)", value=round(nq / (ms * 1e-3), 1), unit="queries/s", n_gpus=1, steps=args.steps,
+              warmup=max(args.warmup, 3), ms_per_step=round(ms, 4), higher_is_better=True, scaling="strong", vs_baseline=None,
+              dtype="f32", data="synthetic",
+              config=dict(workload="c1", desc=cfg["desc"], batches_per_step=reps,
+                          l2="rows 51 MB: resident in L2 after the first batch (the configuration is the reference's CPU-sized case)"),
+              e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 4),
+                       h2d_bytes_per_step=int(stats["h2d_bytes"]), d2h_bytes_per_step=int(stats["d2h_bytes"])),
+              gpu_launches=int(c["kernel_launches"]),
+              roofline=dict(bound="hbm", kernel="k_flat_scan", achieved=round(achieved, 1), peak=peak, unit="GB/s",
+                            frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
+                            algorithmic_bytes_per_launch=int(rows_per_launch * dim * 4), rows_per_launch=int(rows_per_launch),
+                            ms_per_launch=round(scan_ms, 4), traffic=None,
+                            note="bytes = probed rows x dim x 4; at this size the rows stay in L2, so the figure is an L2-fed rate"),
+              cpu_baseline=dict(value=round(nq / dt, 2), unit="queries/s", cores=cores, kind=kind,
+                                sample="all %d queries, cpu_ivf_search on the physical cores" % nq),
+              parity=dict(sample_queries=nq, ids_equal=bool(np.array_equal(ri, got_i)), dist_equal=bool(np.array_equal(rd, got_d)),
+                          recall_at_k_gpu=recall_at(got_i, truth, topk),
+                          recall_at_k_cpu=recall_at(ri, truth, topk)),
+              clocks=clocks))
+    sess.close()
+    return 0
 
 
 def training(args, cfg, torch, api, device):

@@ -372,6 +372,30 @@ psb_status psb_coarse_search_static(const float* d_queries, int nq, const float*
 psb_status psb_knn_exact(const float* d_queries, int nq, const float* d_base, int64_t n, int dim, int k,
                          int* d_rows, float* d_dist, int device, void* stream);
 
+/* ---- IVF-Flat: exact fine scan over device-resident rows -------------------------------------------------- */
+
+/* IVFFlatIndexView with row-major fp32 storage (src/search/ivfflat/ivfflat_search.cuh:11-29): caller-owned HOST memory. */
+typedef struct psb_flat_index_view {
+    psb_coarse_index_view coarse;
+    psb_list_layout_view lists;
+    const float* rowmajor_fp32; /* [n_vectors][dim] in list-contiguous order */
+} psb_flat_index_view;
+
+typedef struct psb_session psb_flat_session;
+
+/* Uploads centroids, list layout, ids and the rows (they stay resident in device memory: the reference's GPU-resident fine
+ * kind, IVFFlatFineKind, src/search/ivfflat/ivfflat_search.cuh:31-38).  options: device, max_batch, stream, coarse_mode. */
+psb_status psb_flat_session_create(const psb_flat_index_view* index, const psb_options* options, psb_flat_session** out);
+/* ivfflat_search (src/search/ivfflat/ivfflat_search.cuh:41-51): coarse top-nprobe, then the exact fp32 squared L2 distance to
+ * every row of the probed lists and the topk nearest, ties by row; HOST queries and outputs, batches of params->batch_size.
+ * Results equal the reference's CPU path cpu_ivf_search (src/cpu/search/cpu_search.h:226-332). */
+psb_status psb_flat_session_search(psb_flat_session* session, const psb_query_batch_view* queries, const psb_search_params* params,
+                                   const psb_search_output_view* output, psb_stats* stats);
+/* The same with DEVICE queries and outputs, asynchronous on the session's stream (nq <= max_batch). */
+psb_status psb_flat_session_search_device(psb_flat_session* session, const float* d_queries, int nq, const psb_search_params* params,
+                                          int64_t* d_indices, float* d_distances);
+psb_status psb_flat_session_destroy(psb_flat_session* session);
+
 /* ---- training and encoding ---------------------------------------------------------------------------- */
 
 /* Lloyd k-means on DEVICE data: assign = argmin squared L2 (strict <, lowest index wins), update = mean,

@@ -97,6 +97,7 @@ EXPORTS = [
     "psb_last_error", "psb_device_count", "psb_version", "psb_session_create", "psb_session_destroy",
     "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_quantize_lut_u8", "psb_stage_scan", "psb_stage_scan_queries",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
+    "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
     "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
@@ -303,6 +304,78 @@ class Session:
         st = Stats()
         _check(lib().psb_session_counters(self._h, C.byref(st), int(reset)))
         return st.as_dict()
+
+
+class FlatIndexView(C.Structure):
+    _fields_ = [("coarse", CoarseIndexView), ("lists", ListLayoutView), ("rowmajor_fp32", C.c_void_p)]
+
+
+class FlatSession:
+    """IVF-Flat with device-resident rows (ivfflat_search of the reference, src/search/ivfflat/ivfflat_search.cuh:41-51).
+
+    index: dict with centroids [nlist,dim] f32, offsets [nlist+1] i64, reordered_ids [n] i64, vectors [n,dim] f32 (list-contiguous).
+    """
+
+    def __init__(self, index, device=0, max_batch=0, stream=None, coarse_mode=0, time_kernels=False):
+        cen = _np(index["centroids"], np.float32)
+        off = _np(index["offsets"], np.int64)
+        rid = _np(index["reordered_ids"], np.int64)
+        vec = _np(index["vectors"], np.float32)
+        self._keep = [cen, off, rid, vec]
+        fv = FlatIndexView()
+        fv.coarse = CoarseIndexView(_p(cen), cen.shape[0], cen.shape[1])
+        fv.lists = ListLayoutView(_p(off), _p(rid), cen.shape[0], int(vec.shape[0]))
+        fv.rowmajor_fp32 = _p(vec)
+        self.dim, self.nlist = cen.shape[1], cen.shape[0]
+        opt = Options(device=device, max_batch=max_batch, stream=stream, coarse_mode=coarse_mode, time_kernels=int(time_kernels))
+        self._h = C.c_void_p()
+        _check(lib().psb_flat_session_create(C.byref(fv), C.byref(opt), C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().psb_flat_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def search(self, queries, nprobe, topk, batch_size=10000, want_coarse=False):
+        q = _np(queries, np.float32)
+        nq = q.shape[0]
+        ids = np.empty((nq, max(topk, 0)), np.int64)
+        dist = np.empty((nq, max(topk, 0)), np.float32)
+        coarse = np.empty((nq, max(nprobe, 0)), np.int32) if want_coarse else None
+        qv = QueryBatchView(_p(q), None, nq, q.shape[1], None)
+        pr = SearchParams(nprobe, topk, batch_size, 0, 0)
+        ov = SearchOutputView(_p(ids), _p(dist), _p(coarse))
+        st = Stats()
+        _check(lib().psb_flat_session_search(self._h, C.byref(qv), C.byref(pr), C.byref(ov), C.byref(st)))
+        res = dict(indices=ids, distances=dist, stats=st.as_dict())
+        if want_coarse:
+            res["coarse"] = coarse
+        return res
+
+    def search_raw(self, q_ptr, nq, nprobe, topk, batch_size, ids_ptr, dist_ptr, stats=None):
+        qv = QueryBatchView(q_ptr, None, nq, self.dim, None)
+        pr = SearchParams(nprobe, topk, batch_size, 0, 0)
+        ov = SearchOutputView(ids_ptr, dist_ptr, None)
+        _check(lib().psb_flat_session_search(self._h, C.byref(qv), C.byref(pr), C.byref(ov),
+                                             C.byref(stats) if stats is not None else None))
+
+    def counters(self, reset=False):
+        st = Stats()
+        _check(lib().psb_session_counters(self._h, C.byref(st), int(reset)))
+        return st.as_dict()
+
+    def search_device(self, d_queries, nq, nprobe, topk, d_ids, d_dist):
+        pr = SearchParams(nprobe, topk, nq, 0, 0)
+        _check(lib().psb_flat_session_search_device(self._h, C.c_void_p(_p(d_queries)), nq, C.byref(pr), C.c_void_p(_p(d_ids)),
+                                                    C.c_void_p(_p(d_dist))))
 
 
 # ---- one-shot operators on host arrays ---------------------------------------------------------------

@@ -187,6 +187,13 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
                        const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist,
                        int* d_count, int sm_count, cudaStream_t s, const float* d_queries = nullptr);
 
+// ---- IVF-Flat fine scan (flat.cu) ------------------------------------------------------------------------------
+// Exact fp32 distances of every query to the rows of its probed lists (device-resident rows, list-contiguous) and the topk
+// nearest by (distance, row).  d_out_rows [nq][topk] list-contiguous rows (-1 pad), d_out_dist (FLT_MAX pad).
+psb_status launch_flat_scan(const float* d_queries, int nq, int dim, const int* d_probes, int nprobe, const long long* d_offsets,
+                            int nlist, const float* d_rows, long long row_base, int topk, int* d_out_rows, float* d_out_dist,
+                            unsigned long long* d_counters, cudaStream_t s);
+
 // ---- rerank ------------------------------------------------------------------------------------------------
 // Which rows of the index-wide (list-contiguous) numbering a session's exact store and id table hold.
 //   global_begin == nullptr: rows [base, base + count), stored in that order.

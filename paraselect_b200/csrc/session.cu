@@ -247,6 +247,8 @@ struct psb_session {
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
     bool pinned_used[2] = {false, false};  // a copy out of the ring buffer may still be in flight (its event tells)
     int pinned_slot = 0;
+    bool flat = false;                     // IVF-Flat session: exact rows resident in flat_rows, no PQ parts
+    DevBuf flat_rows;
     std::unique_ptr<HostPool> host_pool;   // gather threads of the staged transport (created on first use)
     double staged_gather_s = 0.0;          // host time spent gathering rows, and the bytes gathered (reported by the bench)
     long long staged_gather_bytes = 0;
@@ -1261,6 +1263,146 @@ psb_status psb_session_search(psb_session* s, const psb_query_batch_view* querie
         s->collect_scan_events();
         stats->scan_kernel_ms = s->scan_ms_total - scan_ms0;
         stats->scan_kernel_launches = s->scan_launches_total - scan_n0;
+        stats->batches = nb;
+    }
+    return PSB_OK;
+}
+
+// ---- IVF-Flat ----------------------------------------------------------------------------------------------------
+
+psb_status psb_flat_session_create(const psb_flat_index_view* index, const psb_options* options, psb_flat_session** out) {
+    if (!out) return fail(PSB_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!index) return fail(PSB_INVALID_ARGUMENT, "index view is null");
+    {   // the list layout rules of the PQ index (src/search/ivf_common/ivf_list_layout.h:19-45)
+        psb_index_view probe{};
+        probe.coarse = index->coarse; probe.lists = index->lists;
+        static const float one_codeword = 0.0f;
+        static const uint8_t no_codes = 0;
+        probe.pq.codes = &no_codes; probe.pq.codebook = &one_codeword; probe.pq.subvectors = 1; probe.pq.codebook_size = 1;
+        if (index->coarse.dim <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid IVF coarse index view");
+        PSB_TRY(validate_index(&probe));
+    }
+    if (!index->rowmajor_fp32 && index->lists.n_vectors > 0) return fail(PSB_INVALID_ARGUMENT, "IVF-Flat rows are null");
+    psb_options opt{};
+    if (options) opt = *options;
+    if (opt.max_batch <= 0) opt.max_batch = 10000;
+    cudaDeviceProp prop;
+    PSB_TRY(check_device(opt.device, &prop));
+    std::unique_ptr<psb_session> s(new (std::nothrow) psb_session());
+    if (!s) return fail(PSB_OUT_OF_MEMORY, "host allocation failed");
+    s->flat = true;
+    s->device = opt.device; s->sm_count = prop.multiProcessorCount; s->opt = opt;
+    s->nlist = index->lists.nlist; s->dim = index->coarse.dim; s->n_vectors = index->lists.n_vectors;
+    s->list_begin = 0; s->list_end = s->nlist; s->row_base = 0; s->shard_rows = s->n_vectors;
+    if (opt.stream) s->stream = static_cast<cudaStream_t>(opt.stream);
+    else { PSB_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking)); s->own_stream = true; }
+    cudaStream_t st = s->stream;
+    const size_t nl = (size_t)s->nlist, n = (size_t)std::max<long long>(1, s->n_vectors);
+    PSB_TRY(s->centroids.reserve(sizeof(float) * nl * s->dim));
+    PSB_CUDA(cudaMemcpyAsync(s->centroids.p, index->coarse.centroids, sizeof(float) * nl * s->dim, cudaMemcpyHostToDevice, st));
+    if (opt.coarse_mode != 1 && s->nlist >= 1024 && coarse_tc_padded_dim(s->dim) <= 128)
+        PSB_TRY(s->tc_index.prepare(index->coarse.centroids, s->centroids.as<float>(), s->nlist, s->dim, st));
+    PSB_TRY(s->offsets.reserve(sizeof(long long) * (nl + 1)));
+    PSB_CUDA(cudaMemcpyAsync(s->offsets.p, index->lists.offsets, sizeof(long long) * (nl + 1), cudaMemcpyHostToDevice, st));
+    PSB_TRY(s->reordered.reserve(sizeof(long long) * n));
+    PSB_TRY(s->flat_rows.reserve(sizeof(float) * n * s->dim));
+    if (s->n_vectors > 0) {
+        PSB_CUDA(cudaMemcpyAsync(s->reordered.p, index->lists.reordered_ids, sizeof(long long) * n, cudaMemcpyHostToDevice, st));
+        PSB_CUDA(cudaMemcpyAsync(s->flat_rows.p, index->rowmajor_fp32, sizeof(float) * n * s->dim, cudaMemcpyHostToDevice, st));
+    }
+    PSB_TRY(s->scalars.reserve(sizeof(unsigned long long) * 16));
+    PSB_CUDA(cudaMemsetAsync(s->scalars.p, 0, sizeof(unsigned long long) * 16, st));
+    PSB_CUDA(cudaStreamSynchronize(st));
+    *out = s.release();
+    return PSB_OK;
+}
+
+psb_status psb_flat_session_destroy(psb_flat_session* s) {
+    delete s;
+    return PSB_OK;
+}
+
+namespace {
+psb_status flat_search_device(psb_session* s, const float* dq, int n, int nprobe, int topk, long long* d_ids, float* d_dist) {
+    PSB_TRY(s->probes.reserve(sizeof(int) * (size_t)n * nprobe));
+    PSB_TRY(s->out_rows.reserve(sizeof(int) * (size_t)n * topk));
+    PSB_TRY(coarse_exact(s, dq, n, nprobe, s->probes.as<int>(), nullptr));
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    if (s->opt.time_kernels) {  // bracket the fine-scan kernel (read back by psb_session_counters)
+        PSB_CUDA(cudaEventCreate(&ev0));
+        PSB_CUDA(cudaEventCreate(&ev1));
+        s->scan_events.emplace_back(ev0, ev1);
+        PSB_CUDA(cudaEventRecord(ev0, s->stream));
+    }
+    PSB_TRY(launch_flat_scan(dq, n, s->dim, s->probes.as<int>(), nprobe, s->offsets.as<long long>(), s->nlist, s->flat_rows.as<float>(),
+                             0, topk, s->out_rows.as<int>(), d_dist, s->scalars.as<unsigned long long>(), s->stream));
+    if (ev1) PSB_CUDA(cudaEventRecord(ev1, s->stream));
+    return launch_map_ids(s->out_rows.as<int>(), (long long)n * topk, s->reordered.as<long long>(), s->row_map(), d_ids, s->stream);
+}
+psb_status flat_check(const psb_session* s, const psb_search_params* p) {
+    if (!s || !s->flat) return fail(PSB_INVALID_ARGUMENT, "not an IVF-Flat session");
+    if (!p) return fail(PSB_INVALID_ARGUMENT, "params are null");
+    if (p->nprobe <= 0 || p->nprobe > s->nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
+    if (p->topk <= 0) return fail(PSB_INVALID_ARGUMENT, "topk must be positive");
+    if (p->batch_size <= 0) return fail(PSB_INVALID_ARGUMENT, "batch_size must be positive");
+    if (p->distance != 0) return fail(PSB_UNSUPPORTED_SHAPE, "only squared L2 is supported on this path");
+    if (p->nprobe > kMaxProbe || p->topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or topk above 2048");
+    return PSB_OK;
+}
+}  // namespace
+
+psb_status psb_flat_session_search_device(psb_flat_session* s, const float* d_queries, int nq, const psb_search_params* params,
+                                          int64_t* d_indices, float* d_distances) {
+    PSB_TRY(flat_check(s, params));
+    if (!d_queries || !d_indices || !d_distances) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (nq < 0 || nq > s->opt.max_batch) return fail(PSB_INVALID_ARGUMENT, "nq must be in 0..max_batch");
+    if (nq == 0) return PSB_OK;
+    PSB_CUDA(cudaSetDevice(s->device));
+    return flat_search_device(s, d_queries, nq, params->nprobe, params->topk, reinterpret_cast<long long*>(d_indices), d_distances);
+}
+
+psb_status psb_flat_session_search(psb_flat_session* s, const psb_query_batch_view* queries, const psb_search_params* params,
+                                   const psb_search_output_view* output, psb_stats* stats) {
+    PSB_TRY(flat_check(s, params));
+    if (!queries || !output) return fail(PSB_INVALID_ARGUMENT, "null query or output view");
+    if (queries->count < 0 || queries->dim != s->dim) return fail(PSB_INVALID_ARGUMENT, "query dim does not match the index");
+    if (queries->count > 0 && (!queries->fp32 || !output->indices || !output->distances)) return fail(PSB_INVALID_ARGUMENT, "null query or output buffers");
+    PSB_CUDA(cudaSetDevice(s->device));
+    if (stats) std::memset(stats, 0, sizeof(*stats));
+    const int total = queries->count, nprobe = params->nprobe, topk = params->topk;
+    if (total == 0) return PSB_OK;
+    const int batch = std::min(std::min(params->batch_size, s->opt.max_batch), total);
+    cudaStream_t st = s->stream;
+    PSB_TRY(s->q.reserve(sizeof(float) * (size_t)batch * s->dim));
+    PSB_TRY(s->out_ids.reserve(sizeof(long long) * (size_t)batch * topk));
+    PSB_TRY(s->out_dist.reserve(sizeof(float) * (size_t)batch * topk));
+    const long long launches0 = launches_total();
+    unsigned long long c0 = 0, c1 = 0;
+    PSB_CUDA(cudaMemcpyAsync(&c0, s->scalars.p, sizeof(c0), cudaMemcpyDeviceToHost, st));
+    EventTimer tm;
+    PSB_TRY(tm.mark(st));
+    int nb = 0;
+    for (int q0 = 0; q0 < total; q0 += batch, ++nb) {
+        const int n = std::min(batch, total - q0);
+        PSB_CUDA(cudaMemcpyAsync(s->q.p, queries->fp32 + (size_t)q0 * s->dim, sizeof(float) * (size_t)n * s->dim, cudaMemcpyHostToDevice, st));
+        PSB_TRY(flat_search_device(s, s->q.as<float>(), n, nprobe, topk, s->out_ids.as<long long>(), s->out_dist.as<float>()));
+        PSB_CUDA(cudaMemcpyAsync(output->indices + (size_t)q0 * topk, s->out_ids.p, sizeof(long long) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaMemcpyAsync(output->distances + (size_t)q0 * topk, s->out_dist.p, sizeof(float) * (size_t)n * topk, cudaMemcpyDeviceToHost, st));
+        if (output->coarse_ids)
+            PSB_CUDA(cudaMemcpyAsync(output->coarse_ids + (size_t)q0 * nprobe, s->probes.p, sizeof(int) * (size_t)n * nprobe, cudaMemcpyDeviceToHost, st));
+        PSB_CUDA(cudaStreamSynchronize(st));  // the batch buffers are reused
+    }
+    PSB_TRY(tm.mark(st));
+    PSB_CUDA(cudaMemcpyAsync(&c1, s->scalars.p, sizeof(c1), cudaMemcpyDeviceToHost, st));
+    PSB_CUDA(cudaStreamSynchronize(st));
+    PSB_TRY(s->tc_work.check_status());
+    if (stats) {
+        stats->total_ms = tm.ms(0, 1);
+        stats->pq_scanned_codes = (long long)(c1 - c0);  // rows scanned
+        stats->h2d_bytes = (long long)sizeof(float) * total * s->dim;
+        stats->d2h_bytes = (long long)(sizeof(long long) + sizeof(float)) * total * topk;
+        stats->kernel_launches = launches_total() - launches0;
         stats->batches = nb;
     }
     return PSB_OK;
