@@ -277,14 +277,14 @@ def scan_roofline(cfg, c, S, scan_ms, launches_per_step, peaks, clocks, sm_count
         flops = 2.0 * S * dim
         achieved = flops / (scan_ms * 1e-3) / 1e12 if scan_ms > 0 else 0.0
         # DRAM bytes per launch: each decoded code row is read once per tile of up to 128 visitors - M code bytes + 8 bytes of
-        # per-row terms - plus the survivors written to the pools; 61.0 bytes per decoded row in the ncu capture of this workload
-        # cut to 8M rows x 2,000 queries (profiles/), scaled here by the rows this launch decodes (tiles * 128)
+        # per-row terms - plus the survivors written to the pools; 5,019 bytes per 128-row tile in the ncu capture of this workload
+        # cut to 8M rows x 2,000 queries (profiles/k_scan_tc_M48_c4-8Mrows-2000q.md), scaled here by the tiles this launch issues
         return dict(bound="tensor", kernel="k_scan_tc", achieved=round(achieved, 1), peak=peak, unit="TFLOP/s",
                     frac=round(achieved / peak, 4), peak_source=src + " (cuBLAS bf16, sustained)",
                     algorithmic_flops_per_launch=flops, executed_flops_per_launch=tiles * 2.0 * 128 * 128 * kp,
                     pairs_per_launch=int(S), tiles_per_launch=int(tiles), ms_per_launch=round(scan_ms, 3),
                     launches_per_step=launches_per_step,
-                    traffic=int(61.0 * tiles * 128) if cfg["M"] == 48 else None,
+                    traffic=int(5019.0 * tiles) if cfg["M"] == 48 else None,
                     traffic_source="ncu dram__bytes_read+write of a cut-down capture (8M rows, 2,000 queries), scaled by rows decoded",
                     hbm_logical=dict(achieved=round(logical, 1), peak=hbm, unit="GB/s", frac=round(logical / hbm, 4),
                                      algorithmic_bytes_per_launch=int(S * cfg["M"]),
