@@ -437,6 +437,17 @@ psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors,
 psb_status psb_pq_encode(const float* d_data, int64_t n, int dim, const float* d_codebook, int subvectors,
                          int codebook_size, uint8_t* d_codes, int device, void* stream);
 
+/* ---- index-build glue (host side: layout only, no arithmetic) ------------------------------------------------ */
+
+/* From a list assignment to the IVF list layout: h_offsets [nlist + 1] and h_reordered_ids [n], rows ordered by
+ * (list, original id) - the reorder-by-cluster step of the reference's index build (the `reordered_indices` / offsets of
+ * its cluster cache, consumed by src/search/ivfpq/ivfpq_build.cu:150-209).  h_assign [n] list of every row, in 0..nlist-1
+ * (PSB_INVALID_ARGUMENT otherwise). */
+psb_status psb_ivf_layout_from_assignment(const int* h_assign, int64_t n, int nlist, int64_t* h_offsets, int64_t* h_reordered_ids);
+/* h_dst[local] = h_src[h_reordered_ids[local]] for rows of row_bytes bytes: materialize_reordered
+ * (src/search/ivfpq/ivfpq_build.cu:61-93), with its check that the ids are a permutation of 0..n-1. */
+psb_status psb_reorder_rows(const void* h_src, int64_t n, size_t row_bytes, const int64_t* h_reordered_ids, void* h_dst);
+
 /* ---- synthetic data (bench and tests): counter-based generator, identical for any launch shape -------- */
 
 /* rows [row_begin, row_begin + n) of a Gaussian mixture in component-contiguous order:

@@ -98,7 +98,7 @@ EXPORTS = [
     "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_quantize_lut_u8", "psb_stage_scan", "psb_stage_scan_queries",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
-    "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
+    "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
 _lib = None
@@ -414,6 +414,24 @@ def coarse_search_static(d_queries, nq, d_centroids, nlist, dim, nprobe, d_ids, 
     _check(lib().psb_coarse_search_static(C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_centroids)), nlist, dim, nprobe,
                                           C.c_void_p(_p(d_ids)), C.c_void_p(_p(d_dist)) if d_dist is not None else None,
                                           C.c_void_p(stream) if stream else None))
+
+
+def ivf_layout_from_assignment(assign, nlist):
+    """(offsets [nlist+1], reordered_ids [n]): rows ordered by (list, original id)."""
+    a = _np(assign, np.int32)
+    off = np.empty(nlist + 1, np.int64); rid = np.empty(a.shape[0], np.int64)
+    _check(lib().psb_ivf_layout_from_assignment(C.c_void_p(_p(a)), C.c_int64(a.shape[0]), nlist, C.c_void_p(_p(off)), C.c_void_p(_p(rid))))
+    return off, rid
+
+
+def reorder_rows(src, reordered_ids):
+    """dst[local] = src[reordered_ids[local]] (any row type)."""
+    src = np.ascontiguousarray(src)
+    rid = _np(reordered_ids, np.int64)
+    dst = np.empty_like(src)
+    _check(lib().psb_reorder_rows(C.c_void_p(_p(src)), C.c_int64(src.shape[0]), C.c_size_t(src.strides[0]), C.c_void_p(_p(rid)),
+                                  C.c_void_p(_p(dst))))
+    return dst
 
 
 def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):

@@ -1702,6 +1702,43 @@ psb_status psb_pq_encode(const float* d_data, int64_t n, int dim, const float* d
     return launch_pq_encode(d_data, n, dim, d_codebook, subvectors, codebook_size, d_codes, static_cast<cudaStream_t>(stream));
 }
 
+// ---- index-build glue (host) ---------------------------------------------------------------------------------
+
+psb_status psb_ivf_layout_from_assignment(const int* h_assign, int64_t n, int nlist, int64_t* h_offsets, int64_t* h_reordered_ids) {
+    if (!h_assign || !h_offsets || !h_reordered_ids || n < 0 || nlist <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid layout request");
+    std::fill(h_offsets, h_offsets + nlist + 1, (int64_t)0);
+    for (int64_t i = 0; i < n; ++i) {
+        const int l = h_assign[i];
+        if (l < 0 || l >= nlist) return fail(PSB_INVALID_ARGUMENT, "list assignment outside 0..nlist-1 at row " + std::to_string(i));
+        ++h_offsets[l + 1];
+    }
+    for (int l = 0; l < nlist; ++l) h_offsets[l + 1] += h_offsets[l];
+    std::vector<int64_t> cursor(h_offsets, h_offsets + nlist);
+    for (int64_t i = 0; i < n; ++i) h_reordered_ids[cursor[(size_t)h_assign[i]]++] = i;  // stable: ascending id within a list
+    return PSB_OK;
+}
+
+psb_status psb_reorder_rows(const void* h_src, int64_t n, size_t row_bytes, const int64_t* h_reordered_ids, void* h_dst) {
+    if (!h_src || !h_dst || !h_reordered_ids || n < 0 || row_bytes == 0) return fail(PSB_INVALID_ARGUMENT, "invalid reorder request");
+    std::vector<bool> seen((size_t)n, false);
+    for (int64_t local = 0; local < n; ++local) {
+        const int64_t id = h_reordered_ids[local];
+        if (id < 0 || id >= n || seen[(size_t)id]) return fail(PSB_INVALID_ARGUMENT, "invalid IVF reordered IDs");
+        seen[(size_t)id] = true;
+    }
+    const unsigned char* src = static_cast<const unsigned char*>(h_src);
+    unsigned char* dst = static_cast<unsigned char*>(h_dst);
+    const int threads = (int)std::min<unsigned>(std::max(1u, std::thread::hardware_concurrency()), 32u);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t)
+        pool.emplace_back([=]() {
+            for (int64_t local = n * t / threads; local < n * (t + 1) / threads; ++local)
+                std::memcpy(dst + (size_t)local * row_bytes, src + (size_t)h_reordered_ids[local] * row_bytes, row_bytes);
+        });
+    for (auto& th : pool) th.join();
+    return PSB_OK;
+}
+
 // ---- synthetic data -------------------------------------------------------------------------------------------
 
 psb_status psb_gen_mixture_rows(const float* d_centres, const int64_t* d_offsets, int ncomp, int dim,

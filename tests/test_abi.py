@@ -99,3 +99,27 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp", ".hpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("the oracle", ""), "%s mentions the oracle" % f
+
+
+def test_index_build_glue_layout_and_reorder():
+    """Host-side glue of the index build: list layout from an assignment (rows by (list, id)) and the reordered copy of the rows."""
+    import numpy as np
+    from paraselect_b200 import api
+    rng = np.random.default_rng(3)
+    n, nlist = 5000, 37
+    assign = rng.integers(0, nlist, n).astype(np.int32)
+    assign[assign == 5] = 6                      # an empty list
+    off, rid = api.ivf_layout_from_assignment(assign, nlist)
+    assert off[0] == 0 and off[-1] == n and off[5] == off[6]
+    order = np.lexsort((np.arange(n), assign))   # by list, then by id
+    assert np.array_equal(rid, order)
+    assert np.array_equal(np.diff(off), np.bincount(assign, minlength=nlist))
+    rows = rng.standard_normal((n, 12)).astype(np.float32)
+    assert np.array_equal(api.reorder_rows(rows, rid), rows[rid])
+    codes = rng.integers(0, 256, (n, 6)).astype(np.uint8)
+    assert np.array_equal(api.reorder_rows(codes, rid), codes[rid])
+    with pytest.raises(api.InvalidArgument):
+        api.ivf_layout_from_assignment(np.array([0, 37], np.int32), nlist)
+    bad = rid.copy(); bad[0] = bad[1]
+    with pytest.raises(api.InvalidArgument):
+        api.reorder_rows(rows, bad)
