@@ -162,6 +162,13 @@ typedef struct psb_options {
     int test_wait_limit;
     int test_skip_mma;
     int reserved[1];
+    /* Residual mode, optional: the per-row correction asset of the index, value[row] = |recon(row)|^2 + 2 <centroid[list(row)],
+       recon(row)> (src/common/row_correction.h:37-45), as HOST arrays over the rows of the view - either fp32 or the affine u16
+       form (value = rc_offset + rc_scale * u16, src/common/row_correction.h:7-20).  The residual cutoff estimate reads it;
+       without it the session computes the fp32 values itself at creation.  Results never depend on it. */
+    const float* row_correction_fp32;
+    const uint16_t* row_correction_u16;
+    float rc_scale, rc_offset;
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -447,6 +454,37 @@ psb_status psb_ivf_layout_from_assignment(const int* h_assign, int64_t n, int nl
 /* h_dst[local] = h_src[h_reordered_ids[local]] for rows of row_bytes bytes: materialize_reordered
  * (src/search/ivfpq/ivfpq_build.cu:61-93), with its check that the ids are a permutation of 0..n-1. */
 psb_status psb_reorder_rows(const void* h_src, int64_t n, size_t row_bytes, const int64_t* h_reordered_ids, void* h_dst);
+
+/* ---- per-row correction of residual-PQ indices (host side) ------------------------------------------------------ */
+
+/* The 32-byte header of the reference's affine u16 payload "row_correction.u16a" (src/common/row_correction.h:7-20). */
+typedef struct psb_row_correction_u16_header {
+    char magic[8];          /* "ISRC16\0\0" */
+    uint32_t version;       /* 2 */
+    uint32_t header_bytes;  /* 32 */
+    uint64_t count;
+    float scale;
+    float offset;
+} psb_row_correction_u16_header;
+
+/* value[row] = |recon(row)|^2 + 2 <centroid[list(row)], recon(row)>, accumulated in fp64 and rounded once to fp32 as the
+ * reference's builder does (src/index/row_correction/row_correction.cpp:143-169).  h_offsets [nlist + 1], h_codes [n][m]. */
+psb_status psb_row_correction_compute(const float* h_centroids, const int64_t* h_offsets, int nlist, int dim, const uint8_t* h_codes,
+                                      const float* h_codebook, int m, int k, float* h_values);
+/* Affine u16 form of the values: offset = floor(min), scale = nextafter((max - offset) / 65534, +inf), u16 = ceil((v - offset) /
+ * scale) - rounded UP, so a decoded value never undercuts the exact one (src/index/row_correction/row_correction.cpp:171-193).
+ * Fills the header and h_u16 [n]. */
+psb_status psb_row_correction_quantize_u16(const float* h_values, int64_t n, psb_row_correction_u16_header* header, uint16_t* h_u16);
+/* The fixed-model form: a range that holds for EVERY code combination of the model, so rows encoded later (other pages, other
+ * shards) share one scale / offset (src/quantization/row_correction/u16.h:28-91).  encode: u16 = ceil((v - offset) / scale),
+ * refusing non-finite values and values outside the range (:17-24); decoding is fma(scale, u16, offset). */
+psb_status psb_row_correction_model_u16(const float* h_centroids, int nlist, const float* h_codebook, int m, int k, int dsub,
+                                        float* scale, float* offset);
+psb_status psb_row_correction_encode_u16(const float* h_values, int64_t n, float scale, float offset, uint16_t* h_u16);
+/* Writes / reads the payload file (header + u16 array) in the reference's layout.  read: h_u16 may be NULL to fetch the
+ * header only; capacity = entries h_u16 can hold. */
+psb_status psb_row_correction_write_u16(const char* path, const psb_row_correction_u16_header* header, const uint16_t* h_u16);
+psb_status psb_row_correction_read_u16(const char* path, psb_row_correction_u16_header* header, uint16_t* h_u16, int64_t capacity);
 
 /* ---- synthetic data (bench and tests): counter-based generator, identical for any launch shape -------- */
 

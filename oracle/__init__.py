@@ -17,9 +17,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "_build", "libpsb_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libpsb_ref.so")
 REF_TRAIN_SO = os.path.join(_HERE, "_ref", "libpsb_ref_train.so")
+REF_ROWCORR_SO = os.path.join(_HERE, "_ref", "libpsb_ref_rowcorr.so")
 _lib = None
 _ref = None
 _ref_train = None
+_ref_rowcorr = None
 
 f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
@@ -393,3 +395,55 @@ def ref_pq_kmeans_subspace(sub, K, iters, seed):
     out = np.empty((K, dsub), np.float32)
     ref_train().psbref_pq_kmeans_subspace(_ptr(sub), n, dsub, K, iters, C.c_uint(seed), _ptr(out))
     return out
+
+
+# ---------------------------------------------------------------- the reference's row-correction code (oracle/ref_rowcorr_harness.cpp)
+def have_ref_rowcorr() -> bool:
+    return os.path.exists(REF_ROWCORR_SO)
+
+
+def ref_rowcorr():
+    global _ref_rowcorr
+    if _ref_rowcorr is None:
+        _ref_rowcorr = C.CDLL(REF_ROWCORR_SO)
+        _ref_rowcorr.ref_rc_value.restype = C.c_float
+        _ref_rowcorr.ref_rc_pq_value.restype = C.c_float
+        _ref_rowcorr.ref_rc_decode.restype = C.c_float
+    return _ref_rowcorr
+
+
+def ref_rc_build_pq(entry_dir, centroids, offsets, codes, codebook):
+    """Runs the reference's builder into entry_dir; returns (payload bytes, fp32 audit values)."""
+    cen = _c(centroids, np.float32); off = _c(offsets, np.int64); codes = _c(codes, np.uint8); cb = _c(codebook, np.float32)
+    m, k, dsub = cb.shape
+    rc = ref_rowcorr().ref_rc_build_pq(entry_dir.encode(), C.c_int64(codes.shape[0]), cen.shape[1], cen.shape[0], m, k,
+                                       _ptr(cen), _ptr(off), _ptr(codes), _ptr(cb))
+    if rc != 0:
+        raise RuntimeError(f"reference row-correction builder failed ({rc})")
+    payload = open(os.path.join(entry_dir, "row_correction.u16a"), "rb").read()
+    audit = np.fromfile(os.path.join(entry_dir, "row_correction.f32"), np.float32, offset=8)
+    return payload, audit
+
+
+def ref_rc_pq_value(centroid, codebook, code):
+    cb = _c(codebook, np.float32); cen = _c(centroid, np.float32); code = _c(code, np.uint8)
+    return float(ref_rowcorr().ref_rc_pq_value(_ptr(cen), _ptr(cb), _ptr(code), cb.shape[0], cb.shape[1], cb.shape[2]))
+
+
+def ref_rc_for_pq(centroids, codebook):
+    cen = _c(centroids, np.float32); cb = _c(codebook, np.float32)
+    sc = C.c_float(); off = C.c_float()
+    if ref_rowcorr().ref_rc_for_pq(_ptr(cen), cen.shape[0], _ptr(cb), cb.shape[0], cb.shape[1], cb.shape[2], C.byref(sc), C.byref(off)) != 0:
+        raise ValueError("reference quantiser refused the model")
+    return sc.value, off.value
+
+
+def ref_rc_encode(scale, offset, v):
+    out = C.c_uint16()
+    if ref_rowcorr().ref_rc_encode(C.c_float(scale), C.c_float(offset), C.c_float(v), C.byref(out)) != 0:
+        raise ValueError("reference quantiser refused the value")
+    return out.value
+
+
+def ref_rc_decode(scale, offset, code):
+    return float(ref_rowcorr().ref_rc_decode(C.c_float(scale), C.c_float(offset), C.c_uint16(code)))

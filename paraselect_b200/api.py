@@ -73,7 +73,8 @@ class Options(C.Structure):
                 ("coarse_mode", C.c_int),
                 ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserve_sms", C.c_int),
                 ("seed_sigma", C.c_float), ("pipeline_parts", C.c_int), ("even_cuts", C.c_int), ("gather_ctas", C.c_int),
-                ("tc_min_visitors", C.c_int), ("test_wait_limit", C.c_int), ("test_skip_mma", C.c_int), ("reserved", C.c_int * 1)]
+                ("tc_min_visitors", C.c_int), ("test_wait_limit", C.c_int), ("test_skip_mma", C.c_int), ("reserved", C.c_int * 1),
+                ("row_correction_fp32", C.c_void_p), ("row_correction_u16", C.c_void_p), ("rc_scale", C.c_float), ("rc_offset", C.c_float)]
 
 
 class Stats(C.Structure):
@@ -98,6 +99,8 @@ EXPORTS = [
     "psb_session_search", "psb_session_search_device", "psb_session_sync", "psb_session_set_stream", "psb_stage_coarse", "psb_stage_build_lut", "psb_stage_build_lut_residual", "psb_stage_quantize_lut_u8", "psb_stage_scan", "psb_stage_scan_queries",
     "psb_stage_rerank", "psb_stage_rerank_partial", "psb_stage_select_topk", "psb_stage_map_ids", "psb_stage_merge", "psb_session_counters", "psb_rerank_host",
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
+    "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
+    "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
@@ -148,7 +151,8 @@ class Session:
 
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
                  list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0,
-                 seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0, tc_min_visitors=0, test_wait_limit=0, test_skip_mma=0):
+                 seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0, tc_min_visitors=0, test_wait_limit=0, test_skip_mma=0,
+                 row_correction=None, rc_scale=0.0, rc_offset=0.0):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -185,6 +189,14 @@ class Session:
                       seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(even_cuts),
                       gather_ctas=int(gather_ctas), tc_min_visitors=int(tc_min_visitors), test_wait_limit=int(test_wait_limit),
                       test_skip_mma=int(test_skip_mma))
+        if row_correction is not None:  # residual mode: the index's per-row correction, fp32 or affine u16 (kept alive with the session)
+            rc = np.ascontiguousarray(row_correction)
+            self._keep.append(rc)
+            if rc.dtype == np.uint16:
+                opt.row_correction_u16, opt.rc_scale, opt.rc_offset = _p(rc), float(rc_scale), float(rc_offset)
+            else:
+                rc = _np(rc, np.float32); self._keep.append(rc)
+                opt.row_correction_fp32 = _p(rc)
         self._h = C.c_void_p()
         _check(lib().psb_session_create(C.byref(iv), C.byref(opt), C.byref(self._h)))
 
@@ -432,6 +444,55 @@ def reorder_rows(src, reordered_ids):
     _check(lib().psb_reorder_rows(C.c_void_p(_p(src)), C.c_int64(src.shape[0]), C.c_size_t(src.strides[0]), C.c_void_p(_p(rid)),
                                   C.c_void_p(_p(dst))))
     return dst
+
+
+class RowCorrectionHeader(C.Structure):
+    _fields_ = [("magic", C.c_char * 8), ("version", C.c_uint32), ("header_bytes", C.c_uint32), ("count", C.c_uint64),
+                ("scale", C.c_float), ("offset", C.c_float)]
+
+
+def row_correction_compute(centroids, offsets, codes, codebook):
+    """value[row] = |recon|^2 + 2 <centroid[list], recon> (fp64 accumulation, rounded once), host side."""
+    cen = _np(centroids, np.float32); off = _np(offsets, np.int64); codes = _np(codes, np.uint8); cb = _np(codebook, np.float32)
+    out = np.empty(codes.shape[0], np.float32)
+    _check(lib().psb_row_correction_compute(C.c_void_p(_p(cen)), C.c_void_p(_p(off)), cen.shape[0], cen.shape[1], C.c_void_p(_p(codes)),
+                                            C.c_void_p(_p(cb)), cb.shape[0], cb.shape[1], C.c_void_p(_p(out))))
+    return out
+
+
+def row_correction_quantize_u16(values):
+    v = _np(values, np.float32)
+    hdr = RowCorrectionHeader(); u = np.empty(v.shape[0], np.uint16)
+    _check(lib().psb_row_correction_quantize_u16(C.c_void_p(_p(v)), C.c_int64(v.shape[0]), C.byref(hdr), C.c_void_p(_p(u))))
+    return hdr, u
+
+
+def row_correction_model_u16(centroids, codebook):
+    """(scale, offset) of the fixed-model u16 form: valid for every code combination of (centroids, codebook [m][k][dsub])."""
+    cen = _np(centroids, np.float32); cb = _np(codebook, np.float32)
+    sc = C.c_float(); off = C.c_float()
+    _check(lib().psb_row_correction_model_u16(C.c_void_p(_p(cen)), cen.shape[0], C.c_void_p(_p(cb)), cb.shape[0], cb.shape[1], cb.shape[2],
+                                              C.byref(sc), C.byref(off)))
+    return sc.value, off.value
+
+
+def row_correction_encode_u16(values, scale, offset):
+    v = _np(values, np.float32); u = np.empty(v.shape[0], np.uint16)
+    _check(lib().psb_row_correction_encode_u16(C.c_void_p(_p(v)), C.c_int64(v.shape[0]), C.c_float(scale), C.c_float(offset), C.c_void_p(_p(u))))
+    return u
+
+
+def row_correction_write_u16(path, header, u16):
+    u = _np(u16, np.uint16)
+    _check(lib().psb_row_correction_write_u16(path.encode(), C.byref(header), C.c_void_p(_p(u))))
+
+
+def row_correction_read_u16(path):
+    hdr = RowCorrectionHeader()
+    _check(lib().psb_row_correction_read_u16(path.encode(), C.byref(hdr), None, C.c_int64(0)))
+    u = np.empty(int(hdr.count), np.uint16)
+    _check(lib().psb_row_correction_read_u16(path.encode(), C.byref(hdr), C.c_void_p(_p(u)), C.c_int64(u.shape[0])))
+    return hdr, u
 
 
 def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):

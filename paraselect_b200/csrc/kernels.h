@@ -128,7 +128,9 @@ struct ScanIndex {
     const float* centroids = nullptr;  // device [nlist][dim]
     const float* codebook = nullptr;   // device [m][k][dim / m]
     const void* row_aug = nullptr;     // device [shard rows] x 8 bytes (launch_row_aug), null: no tensor-core scan
-    const float* row_bias = nullptr;   // residual mode: device [shard rows] 2 <centroid[list(row)], recon(row)> (launch_row_bias)
+    const float* row_bias = nullptr;   // residual mode: device [shard rows] per-row correction as fp32 (launch_row_bias), or
+    const uint16_t* row_bias_u16 = nullptr;  // the caller's affine u16 form of it (value = rc_offset + rc_scale * u16)
+    float rc_scale = 0.f, rc_offset = 0.f;
     int dim = 0;
 };
 
@@ -136,8 +138,8 @@ struct ScanIndex {
 // Whether the tensor-core scan supports the shape (dsub 2, 4 or 8, dim a multiple of 8, m of 4, operands within shared memory).
 bool scan_tc_supported(int dim, int m, int k);
 // Per-row terms of the tensor-core scan, computed once per index: d_out [rows] of 8 bytes (the extra K slots of each code row).
-// Residual mode: bias[row] = 2 <centroid[list(row)], recon(row)> for every row of the shard (the per-row correction of the
-// reference's shared-table form, src/common/row_correction.h:37-45, without its |recon|^2 term, which the table carries here).
+// Residual mode: value[row] = |recon(row)|^2 + 2 <centroid[list(row)], recon(row)> for every row of the shard: the per-row
+// correction of the reference's shared-table form (src/common/row_correction.h:37-45).
 psb_status launch_row_bias(const uint8_t* d_codes, const long long* d_offsets, long long row_base, int list_begin, int list_end,
                            int dim, int m, int k, const float* d_codebook, const float* d_centroids, float* d_out, cudaStream_t s);
 psb_status launch_row_aug(const uint8_t* d_codes, long long rows, int dim, int m, int k, const float* d_codebook, void* d_out,

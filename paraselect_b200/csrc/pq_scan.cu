@@ -178,7 +178,9 @@ struct ResidualSource {
     const float* queries;    // [nq][dim]
     const float* centroids;  // [nlist][dim]
     const float* codebook;   // [m][k][dim / m]
-    const float* row_bias;   // [shard rows] 2 <centroid[list(row)], recon(row)>, or null
+    const float* row_bias;   // [shard rows] per-row correction |recon|^2 + 2 <centroid[list(row)], recon(row)> as fp32, or null
+    const uint16_t* row_bias_u16;  // the same in the affine u16 form (value = rc_offset + rc_scale * u16), or null
+    float rc_scale, rc_offset;
     int dim;
 };
 __device__ __forceinline__ void stage_residual_table(float* __restrict__ s_lut, const float* __restrict__ lut, const ResidualSource& rs,
@@ -244,14 +246,14 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     stride = stride < 16 ? 16 : (stride > 64 ? 64 : stride);
     if ((N + 65535) / 65536 > stride) stride = (int)((N + 65535) / 65536);  // at most ~64K samples per query
     // Residual mode without materialised tables: no per-probe staging.  With c the probed list's centroid,
-    //     |(q - c) - recon|^2 = |q - recon|^2 + (|c|^2 - 2 <c, q>) + 2 <c, recon>,
-    // so ONE table per query (the plain-mode table of q, built here) serves every probed list, plus a constant per probe and a
-    // bias per row that was computed once per index (the reference's shared-table form with a per-row correction:
-    // src/search/kernels/fine/gpu_fine/pq_adc/pq_query_lut_score.cuh:7-22, src/common/row_correction.h:37-45).  The sum is
-    // the same distance in a different rounding; it only places the CUTOFF, whose exact value does not matter: the selection
-    // counts the rows whose EXACT distance is within it and falls back to the exact scan when they are too few.
+    //     |(q - c) - recon|^2 = |q - c|^2 - 2 <q, recon> + (|recon|^2 + 2 <c, recon>),
+    // so ONE dot-product table per query (built here) serves every probed list, plus a constant per probe and the per-row
+    // correction of the index (the reference's shared-table form: src/search/kernels/fine/gpu_fine/pq_adc/
+    // pq_query_lut_score.cuh:7-22, src/common/row_correction.h:37-45; fp32 or affine u16).  The sum is the same distance in a
+    // different rounding; it only places the CUTOFF, whose exact value does not matter: the selection counts the rows whose
+    // EXACT distance is within it and falls back to the exact scan when they are too few.
     const bool flat_bias = per_probe && lut == nullptr;
-    float* s_pk = reinterpret_cast<float*>(s_pref + nprobe + 1);  // [nprobe] |c|^2 - 2 <c, q> per probe (flat_bias only)
+    float* s_pk = reinterpret_cast<float*>(s_pref + nprobe + 1);  // [nprobe] |q - c|^2 per probe (flat_bias only)
     if (!per_probe) {
         for (int e = threadIdx.x; e < m * k; e += blockDim.x) s_lut[e] = lut[(size_t)q * m * k + e];
     } else if (flat_bias) {
@@ -260,9 +262,9 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
         for (int e = threadIdx.x; e < m * k; e += blockDim.x) {
             const int sub = e / k;
             const float* c = rs.codebook + (size_t)e * dsub;
-            float dist = 0.0f;
-            for (int d = 0; d < dsub; ++d) { const float diff = __ldg(qv + sub * dsub + d) - __ldg(c + d); dist = fmaf(diff, diff, dist); }
-            s_lut[e] = dist;
+            float dot = 0.0f;
+            for (int d = 0; d < dsub; ++d) dot = fmaf(__ldg(qv + sub * dsub + d), __ldg(c + d), dot);
+            s_lut[e] = -2.0f * dot;
         }
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         for (int p = warp; p < nprobe; p += (int)(blockDim.x >> 5)) {
@@ -270,7 +272,7 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
             float acc = 0.0f;
             if (l >= 0 && l < nlist) {
                 const float* cv = rs.centroids + (size_t)l * rs.dim;
-                for (int d = lane; d < rs.dim; d += 32) { const float c = __ldg(cv + d); acc = fmaf(c, c - 2.0f * __ldg(qv + d), acc); }
+                for (int d = lane; d < rs.dim; d += 32) { const float diff = __ldg(qv + d) - __ldg(cv + d); acc = fmaf(diff, diff, acc); }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -331,7 +333,11 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
                 const long long row = offsets[l] + (long long)(idx - s_pref[lo]) * stride;
                 const uint8_t* rp = codes + (size_t)(row - row_base) * m;
                 float sd = adc_row<M>(rp, s_lut, m, k, tree != 0);
-                if (flat_bias) sd = fmaxf(sd + s_pk[lo] + __ldg(rs.row_bias + (row - row_base)), 0.0f);
+                if (flat_bias) {
+                    const float corr = rs.row_bias ? __ldg(rs.row_bias + (row - row_base))
+                                                   : fmaf(rs.rc_scale, (float)__ldg(rs.row_bias_u16 + (row - row_base)), rs.rc_offset);
+                    sd = fmaxf(sd + s_pk[lo] + corr, 0.0f);
+                }
                 const uint32_t key = f2o(sd);
                 if (key < s_cut) s_keys[atomicAdd(&s_cnt, 1)] = key;
             }
@@ -1099,7 +1105,7 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
                     int nprobe, int stage1_k, cudaStream_t s, const ResidualSource& rs) {
     const size_t smem = (size_t)ix.m * ix.k * sizeof(float) + kSeedBuf * sizeof(uint32_t) + ((size_t)nprobe + 1) * sizeof(int) +
                         (size_t)nprobe * sizeof(float);
-    if (ix.residual && !d_lut && !rs.row_bias) return fail(PSB_INTERNAL, "residual scan without tables: the per-row bias is missing");
+    if (ix.residual && !d_lut && !rs.row_bias && !rs.row_bias_u16) return fail(PSB_INTERNAL, "residual scan without tables: the per-row correction is missing");
     PSB_TRY(set_smem(k_seed_threshold<M>, smem));
     PSB_TRY(prefer_max_shared(k_seed_threshold<M>));
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
@@ -1267,7 +1273,7 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     PSB_LAUNCH_CHECK();
     // cutoff
     ResidualSource rs;
-    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.row_bias = ix.row_bias; rs.dim = ix.dim;
+    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.row_bias = ix.row_bias; rs.row_bias_u16 = ix.row_bias_u16; rs.rc_scale = ix.rc_scale; rs.rc_offset = ix.rc_offset; rs.dim = ix.dim;
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s, rs))));
     // scan
     ScanArgs a;

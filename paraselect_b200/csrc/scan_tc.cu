@@ -689,7 +689,7 @@ float scan_tc_eps(int dim) {
 }
 
 namespace {
-// One CTA per (list, block of 1024 rows): the centroid sits in shared memory, every thread sums 2 c . codeword over its row.
+// One CTA per (list, block of 1024 rows): the centroid sits in shared memory, every thread sums w (w + 2 c) over its row's codewords.
 __global__ void __launch_bounds__(256) k_row_bias(const uint8_t* __restrict__ codes, const long long* __restrict__ offsets, long long row_base,
                                                   int list_begin, int list_end, int dim, int m, int k, const float* __restrict__ codebook,
                                                   const float* __restrict__ centroids, float* __restrict__ out) {
@@ -707,9 +707,9 @@ __global__ void __launch_bounds__(256) k_row_bias(const uint8_t* __restrict__ co
                 float acc = 0.0f;
                 for (int j = 0; j < m; ++j) {
                     const float* cb = codebook + ((size_t)j * k + __ldg(row + j)) * dsub;
-                    for (int d = 0; d < dsub; ++d) acc = fmaf(s_cen[j * dsub + d], __ldg(cb + d), acc);
+                    for (int d = 0; d < dsub; ++d) { const float w = __ldg(cb + d); acc = fmaf(w, w + 2.0f * s_cen[j * dsub + d], acc); }
                 }
-                out[r - row_base] = 2.0f * acc;
+                out[r - row_base] = acc;
             }
         }
     }

@@ -9,6 +9,7 @@
 #include <climits>
 #include <cmath>
 #include <cstring>
+#include <limits>
 #include <memory>
 #include <new>
 #include <condition_variable>
@@ -247,6 +248,7 @@ struct psb_session {
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
     bool pinned_used[2] = {false, false};  // a copy out of the ring buffer may still be in flight (its event tells)
     int pinned_slot = 0;
+    bool row_bias_is_u16 = false;          // row_bias holds the caller's affine u16 row correction
     bool flat = false;                     // IVF-Flat session: exact rows resident in flat_rows, no PQ parts
     DevBuf flat_rows;
     std::unique_ptr<HostPool> host_pool;   // gather threads of the staged transport (created on first use)
@@ -299,7 +301,8 @@ struct psb_session {
         ix.nlist = nlist; ix.list_begin = list_begin; ix.list_end = list_end; ix.m = m; ix.k = k;
         ix.row_delta = striped ? row_delta.as<long long>() : nullptr;
         ix.residual = opt.adc_mode == 1;
-        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim; ix.row_aug = row_aug.p; ix.row_bias = row_bias.as<float>();
+        ix.centroids = centroids.as<float>(); ix.codebook = codebook.as<float>(); ix.dim = dim; ix.row_aug = row_aug.p; if (row_bias_is_u16) { ix.row_bias_u16 = row_bias.as<uint16_t>(); ix.rc_scale = opt.rc_scale; ix.rc_offset = opt.rc_offset; }
+        else ix.row_bias = row_bias.as<float>();
         return ix;
     }
     // Which index-wide rows the exact store and the id table of this session hold.
@@ -754,7 +757,15 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if ((opt.scan_mode == 0 || opt.scan_mode == 3) && s->shard_rows > 0 && scan_tc_supported(s->dim, s->m, s->k)) {
         PSB_TRY(s->row_aug.reserve((size_t)s->shard_rows * 8));
         PSB_TRY(launch_row_aug(s->codes.as<uint8_t>(), s->shard_rows, s->dim, s->m, s->k, s->codebook.as<float>(), s->row_aug.p, st));
-        if (opt.adc_mode == 1) {  // the per-row bias of the residual cutoff estimate
+        if (opt.adc_mode == 1 && opt.row_correction_u16) {  // the caller's row correction, affine u16
+            if (!(opt.rc_scale > 0.f)) return fail(PSB_INVALID_ARGUMENT, "row_correction_u16 needs a positive rc_scale");
+            PSB_TRY(s->row_bias.reserve(sizeof(uint16_t) * (size_t)s->shard_rows));
+            PSB_CUDA(cudaMemcpyAsync(s->row_bias.p, opt.row_correction_u16 + s->row_base, sizeof(uint16_t) * (size_t)s->shard_rows, cudaMemcpyHostToDevice, st));
+            s->row_bias_is_u16 = true;
+        } else if (opt.adc_mode == 1 && opt.row_correction_fp32) {
+            PSB_TRY(s->row_bias.reserve(sizeof(float) * (size_t)s->shard_rows));
+            PSB_CUDA(cudaMemcpyAsync(s->row_bias.p, opt.row_correction_fp32 + s->row_base, sizeof(float) * (size_t)s->shard_rows, cudaMemcpyHostToDevice, st));
+        } else if (opt.adc_mode == 1) {  // computed here: the per-row correction of the residual cutoff estimate
             PSB_TRY(s->row_bias.reserve(sizeof(float) * (size_t)s->shard_rows));
             PSB_TRY(launch_row_bias(s->codes.as<uint8_t>(), s->offsets.as<long long>(), s->row_base, lb, le, s->dim, s->m, s->k,
                                     s->codebook.as<float>(), s->centroids.as<float>(), s->row_bias.as<float>(), st));
@@ -1737,6 +1748,144 @@ psb_status psb_reorder_rows(const void* h_src, int64_t n, size_t row_bytes, cons
         });
     for (auto& th : pool) th.join();
     return PSB_OK;
+}
+
+// ---- per-row correction of residual-PQ indices (host) ---------------------------------------------------------------
+
+psb_status psb_row_correction_compute(const float* h_centroids, const int64_t* h_offsets, int nlist, int dim, const uint8_t* h_codes,
+                                      const float* h_codebook, int m, int k, float* h_values) {
+    if (!h_centroids || !h_offsets || !h_codes || !h_codebook || !h_values || nlist <= 0 || dim <= 0 || m <= 0 || k <= 0 || dim % m)
+        return fail(PSB_INVALID_ARGUMENT, "row-correction builder input is incomplete");
+    for (int l = 0; l < nlist; ++l)
+        if (h_offsets[l] < 0 || h_offsets[l + 1] < h_offsets[l]) return fail(PSB_INVALID_ARGUMENT, "row-correction cluster offsets are invalid");
+    const int dsub = dim / m;
+    const int threads = (int)std::min<unsigned>(std::max(1u, std::thread::hardware_concurrency()), 64u);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t)
+        pool.emplace_back([=]() {
+            for (int l = t; l < nlist; l += threads) {
+                const float* cen = h_centroids + (size_t)l * dim;
+                for (int64_t row = h_offsets[l]; row < h_offsets[l + 1]; ++row) {
+                    const uint8_t* code = h_codes + (size_t)row * m;
+                    double corr = 0.0;
+                    for (int sub = 0; sub < m; ++sub) {
+                        const float* cw = h_codebook + ((size_t)sub * k + code[sub]) * dsub;
+                        const float* cs = cen + sub * dsub;
+                        for (int d = 0; d < dsub; ++d) corr += (double)cw[d] * cw[d] + 2.0 * (double)cs[d] * cw[d];
+                    }
+                    h_values[row] = (float)corr;
+                }
+            }
+        });
+    for (auto& th : pool) th.join();
+    return PSB_OK;
+}
+
+psb_status psb_row_correction_quantize_u16(const float* h_values, int64_t n, psb_row_correction_u16_header* header, uint16_t* h_u16) {
+    if (!h_values || !header || !h_u16 || n <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid row-correction quantisation request");
+    float lo = h_values[0], hi = h_values[0];
+    for (int64_t i = 0; i < n; ++i) {
+        if (!std::isfinite(h_values[i])) return fail(PSB_INVALID_ARGUMENT, "row-correction values contain non-finite data");
+        lo = std::min(lo, h_values[i]); hi = std::max(hi, h_values[i]);
+    }
+    const float offset = std::floor(lo);
+    const float range = hi - offset;
+    const float scale = range > 0.0f ? std::nextafter(range / 65534.0f, std::numeric_limits<float>::infinity()) : 1.0f;
+    if (!(scale > 0.0f) || !std::isfinite(scale)) return fail(PSB_INVALID_ARGUMENT, "row-correction range cannot be quantized");
+    for (int64_t i = 0; i < n; ++i) {
+        const double qv = std::ceil(((double)h_values[i] - offset) / scale);
+        if (qv < 0.0 || qv > 65534.0) return fail(PSB_INTERNAL, "row-correction quantization overflow");
+        h_u16[i] = (uint16_t)qv;
+    }
+    std::memset(header, 0, sizeof(*header));
+    static const char magic[8] = {0x49, 0x53, 0x52, 0x43, 0x31, 0x36, 0x00, 0x00};
+    std::memcpy(header->magic, magic, 8);
+    header->version = 2; header->header_bytes = 32; header->count = (uint64_t)n; header->scale = scale; header->offset = offset;
+    return PSB_OK;
+}
+
+psb_status psb_row_correction_model_u16(const float* h_centroids, int nlist, const float* h_codebook, int m, int k, int dsub,
+                                        float* scale, float* offset) {
+    if (!h_centroids || !h_codebook || !scale || !offset || nlist <= 0 || m <= 0 || k <= 0 || k > 256 || dsub <= 0)
+        return fail(PSB_INVALID_ARGUMENT, "row correction: invalid PQ model");
+    const int64_t dim = (int64_t)m * dsub;
+    // slack for an fp32 producer's 2 dim + 8 roundings, relative to the magnitude, plus an absolute term for underflow
+    const long double ops = 2.L * dim + 8;
+    const long double err = ops * std::numeric_limits<float>::epsilon();
+    if (err >= 0.25L) return fail(PSB_INVALID_ARGUMENT, "row correction: PQ dimension exceeds the error-bound contract");
+    const long double gamma = err / (1 - err);
+    const long double inf_ld = std::numeric_limits<long double>::infinity();
+    long double lower = inf_ld, upper = -inf_ld;
+    for (int c = 0; c < nlist; ++c) {
+        long double lo = 0, hi = 0, mag = 0;
+        for (int sub = 0; sub < m; ++sub) {
+            long double s_lo = inf_ld, s_hi = -inf_ld, s_abs = 0;
+            for (int code = 0; code < k; ++code) {
+                long double score = 0, absolute = 0;
+                for (int j = 0; j < dsub; ++j) {
+                    const long double w = h_codebook[((size_t)sub * k + code) * dsub + j];
+                    const long double cv = h_centroids[(size_t)c * dim + sub * dsub + j];
+                    if (!std::isfinite(w) || !std::isfinite(cv)) return fail(PSB_INVALID_ARGUMENT, "row correction: non-finite PQ model");
+                    score += w * w + 2 * cv * w;
+                    absolute += w * w + 2 * std::abs(cv * w);
+                }
+                s_lo = std::min(s_lo, score); s_hi = std::max(s_hi, score); s_abs = std::max(s_abs, absolute);
+            }
+            lo += s_lo; hi += s_hi; mag += s_abs;
+        }
+        if (mag * (1 + gamma) >= std::numeric_limits<float>::max()) return fail(PSB_INVALID_ARGUMENT, "row correction: the model can overflow an fp32 producer");
+        const long double pad = gamma * mag + ops * std::numeric_limits<float>::min();
+        lower = std::min(lower, lo - pad); upper = std::max(upper, hi + pad);
+    }
+    const float inf = std::numeric_limits<float>::infinity();
+    const float off = std::nextafter((float)lower, -inf);
+    const float high = std::nextafter((float)upper, inf);
+    const float sc = std::nextafter((float)(((double)high - off) / 65534.), inf);
+    if (!std::isfinite(off) || !std::isfinite(high) || !std::isfinite(sc) || !(sc > 0.f) || !std::isfinite(std::fma(sc, 65534.f, off)))
+        return fail(PSB_INVALID_ARGUMENT, "row correction: the model has no finite u16 encoding");
+    *scale = sc; *offset = off;
+    return PSB_OK;
+}
+
+psb_status psb_row_correction_encode_u16(const float* h_values, int64_t n, float scale, float offset, uint16_t* h_u16) {
+    if (!h_values || !h_u16 || n < 0 || !(scale > 0.f) || !std::isfinite(scale) || !std::isfinite(offset))
+        return fail(PSB_INVALID_ARGUMENT, "row correction: invalid u16 scale or offset");
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = h_values[i];
+        if (!std::isfinite(v)) return fail(PSB_INVALID_ARGUMENT, "row correction: non-finite value");
+        const double code = std::ceil(((double)v - (double)offset) / (double)scale);
+        if (v < offset || !(code >= 0 && code <= 65534)) return fail(PSB_INVALID_ARGUMENT, "row correction: value outside the fixed u16 range");
+        h_u16[i] = (uint16_t)code;
+    }
+    return PSB_OK;
+}
+
+psb_status psb_row_correction_write_u16(const char* path, const psb_row_correction_u16_header* header, const uint16_t* h_u16) {
+    if (!path || !header || !h_u16) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    FILE* f = std::fopen(path, "wb");
+    if (!f) return fail(PSB_INVALID_ARGUMENT, std::string("failed to create row-correction payload ") + path);
+    const bool ok = std::fwrite(header, sizeof(*header), 1, f) == 1 &&
+                    std::fwrite(h_u16, sizeof(uint16_t), (size_t)header->count, f) == (size_t)header->count;
+    if (std::fclose(f) != 0 || !ok) return fail(PSB_INTERNAL, "failed to write row-correction payload");
+    return PSB_OK;
+}
+
+psb_status psb_row_correction_read_u16(const char* path, psb_row_correction_u16_header* header, uint16_t* h_u16, int64_t capacity) {
+    if (!path || !header) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    FILE* f = std::fopen(path, "rb");
+    if (!f) return fail(PSB_INVALID_ARGUMENT, std::string("cannot open row-correction payload ") + path);
+    psb_status st = PSB_OK;
+    static const char magic[8] = {0x49, 0x53, 0x52, 0x43, 0x31, 0x36, 0x00, 0x00};
+    if (std::fread(header, sizeof(*header), 1, f) != 1 || std::memcmp(header->magic, magic, 8) != 0 || header->version != 2 ||
+        header->header_bytes != 32 || !std::isfinite(header->scale) || !(header->scale > 0.0f) || !std::isfinite(header->offset))
+        st = fail(PSB_INVALID_ARGUMENT, "not a row-correction u16 payload (magic, version, header size, scale or offset)");
+    else if (h_u16) {
+        if ((int64_t)header->count > capacity) st = fail(PSB_INVALID_ARGUMENT, "row-correction payload holds more rows than the buffer");
+        else if (std::fread(h_u16, sizeof(uint16_t), (size_t)header->count, f) != (size_t)header->count)
+            st = fail(PSB_INVALID_ARGUMENT, "row-correction payload is truncated");
+    }
+    std::fclose(f);
+    return st;
 }
 
 // ---- synthetic data -------------------------------------------------------------------------------------------

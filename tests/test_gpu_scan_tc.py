@@ -156,6 +156,36 @@ def test_tc_scan_residual_mode_without_tables(psb):
             s.stage_scan_queries(dev(q2), None, 5, dev(p2.astype(np.int32)), 4, 16, rows, dist, cnt)
 
 
+@pytest.mark.parametrize("form", ["fp32", "u16", "u16_model"])
+def test_tc_scan_residual_with_the_callers_row_correction(psb, form):
+    """The per-row correction handed in by the caller (fp32, the affine u16 payload, or u16 on the fixed-model range) places
+    the cutoff; the selected rows and distances stay the exact ones and no query needs the fallback."""
+    torch = _torch()
+    ix = synth.make_index(90000, 96, 16, 48, seed=61, zipf=True, residual=True)
+    q = synth.make_queries(ix, 60, seed=8, weights=synth.zipf_weights(16))
+    probes, _ = oracle.coarse(q, ix["centroids"], 10)
+    orow, odist, ocnt, _ = oracle.pq_scan_residual(q, probes, ix["centroids"], ix["offsets"], ix["codes"], ix["codebook"], 700)[:4]
+    v = psb.row_correction_compute(ix["centroids"], ix["offsets"], ix["codes"], ix["codebook"])
+    kw = dict(row_correction=v)
+    if form == "u16":
+        hdr, u = psb.row_correction_quantize_u16(v)
+        kw = dict(row_correction=u, rc_scale=hdr.scale, rc_offset=hdr.offset)
+    elif form == "u16_model":
+        sc, off = psb.row_correction_model_u16(ix["centroids"], ix["codebook"])
+        kw = dict(row_correction=psb.row_correction_encode_u16(v, sc, off), rc_scale=sc, rc_offset=off)
+    with psb.Session(ix, residual=True, scan_mode=3, **kw) as s:
+        rows = torch.empty((60, 700), dtype=torch.int32, device="cuda")
+        dist = torch.empty((60, 700), dtype=torch.float32, device="cuda")
+        cnt = torch.empty((60,), dtype=torch.int32, device="cuda")
+        s.stage_scan_queries(dev(q), None, 60, dev(probes.astype(np.int32)), 10, 700, rows, dist, cnt)
+        s.sync()
+        assert s.counters()["fallback_queries"] == 0
+        assert np.array_equal(cnt.cpu().numpy(), ocnt)
+        assert np.array_equal(rows.cpu().numpy(), orow) and np.array_equal(dist.cpu().numpy(), odist)
+    with pytest.raises(psb.InvalidArgument):
+        psb.Session(ix, residual=True, scan_mode=3, row_correction=np.zeros(90000, np.uint16), rc_scale=0.0)
+
+
 def test_tc_scan_split_by_visitor_count(psb):
     """tc_min_visitors = 20: lists with fewer visitors stay with the SIMT scan, the others go to the tensor-core kernel;
     the pools then hold exact keys and unscored survivors side by side."""
