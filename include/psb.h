@@ -169,6 +169,10 @@ typedef struct psb_options {
     const float* row_correction_fp32;
     const uint16_t* row_correction_u16;
     float rc_scale, rc_offset;
+    /* Plain mode, optional: the OPQ rotation of the index (IVFPQTransformKind::OPQ), HOST row-major [dim][dim] as [out][in].
+       The PQ side of a search (tables, code scan) then works on R q while the coarse stage and the exact re-ranking keep the
+       caller's q, as src/search/ivfpq/ivfpq_index.cu:205-217 and stage/ivfpq_fine_cpu_lut.cpp:29-31 do. */
+    const float* opq_matrix;
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's
@@ -268,6 +272,14 @@ psb_status psb_session_set_stream(psb_session* session, void* stream, int backgr
  * d_ids [nq][nprobe] int32, d_dist [nq][nprobe] fp32 (may be NULL). */
 psb_status psb_stage_coarse(psb_session* session, const float* d_queries, int nq, int nprobe,
                             int* d_ids, float* d_dist);
+
+/* OPQ rotation of rows on the device: d_out[r][o] = sum_i matrix[o][i] d_in[r][i] (matrix row-major [out][in]), each element one
+ * in-order fp32 fma chain.  Replaces OPQTransform::apply_device (src/transform/opq_transform.cu:73-78,124-163), which runs a
+ * cuBLAS SGEMM whose summation order is unspecified; results agree to rounding.  d_out must not alias d_in. */
+psb_status psb_rotate_rows(const float* d_in, const float* d_matrix, int64_t n, int dim, float* d_out, int device, void* stream);
+/* The same with the session's own rotation (psb_options.opq_matrix): what a stage-by-stage caller feeds to
+ * psb_stage_build_lut and psb_stage_scan_queries. */
+psb_status psb_stage_rotate_queries(psb_session* session, const float* d_queries, int nq, float* d_rotated);
 
 /* Per-query PQ lookup tables lut[q][m][c] = sum_d (q[m*dsub+d] - codebook[m][c][d])^2, built once per
  * query and shared by every probed list.  Replaces pq_build_query_lut_gpu

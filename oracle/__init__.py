@@ -180,6 +180,32 @@ def ivfpq_search(index, queries, nprobe, topk, n_rerank):
     return dict(indices=out_i, distances=out_d, coarse=out_c, stage1=out_s, scanned=scanned.value)
 
 
+def rotate_rows(rows, matrix):
+    """rows @ matrix.T with the in-order fp32 fma chain (matrix row-major [out][in])."""
+    rows = _c(rows, np.float32); matrix = _c(matrix, np.float32)
+    out = np.empty_like(rows)
+    if lib().psbo_rotate_rows(_ptr(rows), _ptr(matrix), C.c_int64(rows.shape[0]), rows.shape[1], _ptr(out)):
+        raise ValueError("oracle rotate_rows: invalid arguments")
+    return out
+
+
+def ivfpq_search_opq(index, queries, nprobe, topk, n_rerank, opq_matrix):
+    """The plain pipeline on an OPQ index: coarse and exact re-ranking on the caller's queries, PQ tables and code scan on the
+    rotated ones (src/search/ivfpq/ivfpq_index.cu:205-217, stage/ivfpq_fine_cpu_lut.cpp:29-31)."""
+    queries = _c(queries, np.float32)
+    vec = index.get("vectors")
+    n = index["codes"].shape[0]
+    rr = vec is not None and n_rerank > topk
+    s1 = min(n_rerank, n) if rr else topk
+    probes, _ = coarse(queries, index["centroids"], nprobe)
+    rows, dist, cnt, scanned = pq_scan(rotate_rows(queries, opq_matrix), probes, index["offsets"], index["codes"], index["codebook"], s1)
+    if rr:
+        local, d = rerank(vec, queries, rows, topk, counts=cnt)
+    else:
+        local, d = rows[:, :topk].astype(np.int64), dist[:, :topk]
+    return dict(indices=map_ids(local, index["reordered_ids"]), distances=d, coarse=probes, stage1=rows, scanned=scanned)
+
+
 def pq_scan_residual(queries, probes, centroids, offsets, codes, codebook, stage1_k, want_luts=False):
     """Stage 1 of the residual mode; returns rows, dist, count, scanned (and the tables [nq][nprobe][M*K])."""
     queries = _c(queries, np.float32); probes = _c(probes, np.int64); offsets = _c(offsets, np.int64)

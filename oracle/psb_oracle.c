@@ -564,3 +564,20 @@ double psbo_recall(const int64_t* got, const int64_t* truth, int nq, int k) {
         }
     return tot ? (double)hit / (double)tot : 1.0;
 }
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * OPQ rotation of rows: out[r][o] = sum_i matrix[o][i] in[r][i], matrix row-major [out][in].  The reference runs this as
+ * one cuBLAS SGEMM (src/transform/opq_transform.cu:124-163), whose summation order is not specified, and its own test
+ * compares against an in-order host loop with a tolerance (tests/unit/transform/test_opq_transform.cu:22-39).  The chain is
+ * pinned here as fp32 fma in input order - the order the GPU kernel of the product uses. */
+int psbo_rotate_rows(const float* in, const float* matrix, int64_t n, int dim, float* out) {
+    if (!in || !matrix || !out || n < 0 || dim <= 0) return 1;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; ++r)
+        for (int o = 0; o < dim; ++o) {
+            float acc = 0.0f;
+            for (int i = 0; i < dim; ++i) acc = fmaf(matrix[(size_t)o * dim + i], in[(size_t)r * dim + i], acc);
+            out[(size_t)r * dim + o] = acc;
+        }
+    return 0;
+}

@@ -74,7 +74,8 @@ class Options(C.Structure):
                 ("time_kernels", C.c_int), ("serial_pipeline", C.c_int), ("scan_mode", C.c_int), ("adc_mode", C.c_int), ("reserve_sms", C.c_int),
                 ("seed_sigma", C.c_float), ("pipeline_parts", C.c_int), ("even_cuts", C.c_int), ("gather_ctas", C.c_int),
                 ("tc_min_visitors", C.c_int), ("test_wait_limit", C.c_int), ("test_skip_mma", C.c_int), ("reserved", C.c_int * 1),
-                ("row_correction_fp32", C.c_void_p), ("row_correction_u16", C.c_void_p), ("rc_scale", C.c_float), ("rc_offset", C.c_float)]
+                ("row_correction_fp32", C.c_void_p), ("row_correction_u16", C.c_void_p), ("rc_scale", C.c_float), ("rc_offset", C.c_float),
+                ("opq_matrix", C.c_void_p)]
 
 
 class Stats(C.Structure):
@@ -101,6 +102,7 @@ EXPORTS = [
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
     "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
     "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
+    "psb_rotate_rows", "psb_stage_rotate_queries",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
@@ -152,7 +154,7 @@ class Session:
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
                  list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0,
                  seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0, tc_min_visitors=0, test_wait_limit=0, test_skip_mma=0,
-                 row_correction=None, rc_scale=0.0, rc_offset=0.0):
+                 row_correction=None, rc_scale=0.0, rc_offset=0.0, opq_matrix=None):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -189,6 +191,12 @@ class Session:
                       seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(even_cuts),
                       gather_ctas=int(gather_ctas), tc_min_visitors=int(tc_min_visitors), test_wait_limit=int(test_wait_limit),
                       test_skip_mma=int(test_skip_mma))
+        if opq_matrix is not None:  # OPQ index: rotation [dim][dim], row-major [out][in]
+            rot = _np(opq_matrix, np.float32)
+            if rot.shape != (iv.coarse.dim, iv.coarse.dim):
+                raise InvalidArgument(1, "opq_matrix must be [dim, dim]")
+            self._keep.append(rot)
+            opt.opq_matrix = _p(rot)
         if row_correction is not None:  # residual mode: the index's per-row correction, fp32 or affine u16 (kept alive with the session)
             rc = np.ascontiguousarray(row_correction)
             self._keep.append(rc)
@@ -264,6 +272,9 @@ class Session:
     def set_stream(self, stream=None, background=False):
         """Redirects the stage calls to `stream` (a cudaStream_t value; None = the session's own stream)."""
         _check(lib().psb_session_set_stream(self._h, _stream_ptr(stream), int(background)))
+
+    def stage_rotate_queries(self, d_queries, nq, d_rotated):
+        _check(lib().psb_stage_rotate_queries(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_rotated))))
 
     def stage_build_lut(self, d_queries, nq, d_lut):
         _check(lib().psb_stage_build_lut(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_lut))))
@@ -493,6 +504,12 @@ def row_correction_read_u16(path):
     u = np.empty(int(hdr.count), np.uint16)
     _check(lib().psb_row_correction_read_u16(path.encode(), C.byref(hdr), C.c_void_p(_p(u)), C.c_int64(u.shape[0])))
     return hdr, u
+
+
+def rotate_rows(d_in, d_matrix, n, dim, d_out, device=0, stream=None):
+    """d_out[r] = matrix @ d_in[r] on the device (matrix row-major [out][in])."""
+    _check(lib().psb_rotate_rows(C.c_void_p(_p(d_in)), C.c_void_p(_p(d_matrix)), C.c_int64(n), dim, C.c_void_p(_p(d_out)), device,
+                                 _stream_ptr(stream)))
 
 
 def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):

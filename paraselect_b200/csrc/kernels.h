@@ -67,6 +67,11 @@ psb_status launch_tc_prep_centroids(const float* d_centroids, int nlist, int dim
 psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws, const float* d_queries, int nq,
                             int nprobe, int* d_ids, float* d_dist, int sm_count, cudaStream_t s);
 
+// ---- OPQ rotation --------------------------------------------------------------------------------------
+// d_out [n][dim] = rows of d_in times the transpose of d_matrix (row-major [out][in]): out[r][o] = sum_i M[o][i] in[r][i], one
+// in-order fp32 fma chain per element.  d_out must not alias d_in.
+psb_status launch_rotate_rows(const float* d_in, const float* d_matrix, long long n, int dim, float* d_out, cudaStream_t s);
+
 // ---- PQ lookup tables --------------------------------------------------------------------------------
 psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
                             float* d_lut, cudaStream_t s);

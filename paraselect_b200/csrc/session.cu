@@ -248,6 +248,7 @@ struct psb_session {
     cudaEvent_t pinned_ev[2] = {nullptr, nullptr};
     bool pinned_used[2] = {false, false};  // a copy out of the ring buffer may still be in flight (its event tells)
     int pinned_slot = 0;
+    DevBuf opq, q_rot;                     // OPQ rotation [dim][dim] and the rotated queries of the batch in flight
     bool row_bias_is_u16 = false;          // row_bias holds the caller's affine u16 row correction
     bool flat = false;                     // IVF-Flat session: exact rows resident in flat_rows, no PQ parts
     DevBuf flat_rows;
@@ -753,6 +754,11 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     const size_t cb_bytes = sizeof(float) * (size_t)s->m * s->k * (s->dim / s->m);
     PSB_TRY(s->codebook.reserve(cb_bytes));
     PSB_CUDA(cudaMemcpyAsync(s->codebook.p, index->pq.codebook, cb_bytes, cudaMemcpyHostToDevice, st));
+    if (opt.opq_matrix) {
+        if (opt.adc_mode == 1) return fail(PSB_INVALID_ARGUMENT, "the OPQ rotation belongs to the plain ADC mode");
+        PSB_TRY(s->opq.reserve(sizeof(float) * (size_t)s->dim * s->dim));
+        PSB_CUDA(cudaMemcpyAsync(s->opq.p, opt.opq_matrix, sizeof(float) * (size_t)s->dim * s->dim, cudaMemcpyHostToDevice, st));
+    }
     // per-row terms of the tensor-core scan (8 bytes per code row), once per index
     if ((opt.scan_mode == 0 || opt.scan_mode == 3) && s->shard_rows > 0 && scan_tc_supported(s->dim, s->m, s->k)) {
         PSB_TRY(s->row_aug.reserve((size_t)s->shard_rows * 8));
@@ -854,6 +860,19 @@ psb_status psb_stage_coarse(psb_session* s, const float* d_queries, int nq, int 
     if (nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
     PSB_CUDA(cudaSetDevice(s->device));
     return coarse_exact(s, d_queries, nq, nprobe, d_ids, d_dist);
+}
+
+psb_status psb_rotate_rows(const float* d_in, const float* d_matrix, int64_t n, int dim, float* d_out, int device, void* stream) {
+    if (!d_in || !d_matrix || !d_out || n < 0 || dim <= 0 || d_in == d_out) return fail(PSB_INVALID_ARGUMENT, "invalid rotation request");
+    PSB_TRY(check_device(device));
+    return launch_rotate_rows(d_in, d_matrix, n, dim, d_out, static_cast<cudaStream_t>(stream));
+}
+
+psb_status psb_stage_rotate_queries(psb_session* s, const float* d_queries, int nq, float* d_rotated) {
+    if (!s || !d_queries || !d_rotated || nq < 0 || d_queries == d_rotated) return fail(PSB_INVALID_ARGUMENT, "invalid rotation request");
+    if (!s->opq.p) return fail(PSB_INVALID_ARGUMENT, "the session has no OPQ rotation");
+    PSB_CUDA(cudaSetDevice(s->device));
+    return launch_rotate_rows(d_queries, s->opq.as<float>(), nq, s->dim, d_rotated, s->stream);
 }
 
 psb_status psb_stage_build_lut(psb_session* s, const float* d_queries, int nq, float* d_lut) {
@@ -1090,11 +1109,18 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     // kernel (a full SM's shared and tensor memory per CTA) then never has to share SMs with the transfer stream.
     if (times) rc = tm_s.mark(st);
     if (rc == PSB_OK) rc = coarse_exact(s, dq, n, nprobe, d_probes, nullptr);
+    // OPQ index: the PQ side works on the rotated queries (counted with the coarse stage's time)
+    const float* dq_pq = dq;
+    if (rc == PSB_OK && s->opq.p) {
+        rc = s->q_rot.reserve(sizeof(float) * (size_t)n * s->dim);
+        if (rc == PSB_OK) rc = launch_rotate_rows(dq, s->opq.as<float>(), n, s->dim, s->q_rot.as<float>(), st);
+        dq_pq = s->q_rot.as<float>();
+    }
     if (rc == PSB_OK && times) rc = tm_s.mark(st);
     for (size_t ci = 0; ci + 1 < cuts.size() && rc == PSB_OK; ++ci) {
         const int p0 = cuts[ci];
         const int m = cuts[ci + 1] - p0;
-        const float* q = dq + (size_t)p0 * s->dim;
+        const float* q = dq_pq + (size_t)p0 * s->dim;
         int* probes = d_probes + (size_t)p0 * nprobe;
         int* rows_out = rerank ? s->cand_rows.as<int>() + (size_t)p0 * stage1_k : s->out_rows.as<int>() + (size_t)p0 * topk;
         float* dist_out = rerank ? s->cand_dist.as<float>() + (size_t)p0 * stage1_k : d_dist + (size_t)p0 * topk;

@@ -276,3 +276,20 @@ def test_pq_encode_and_training_match_the_reference_cpu_quantiser():
         assert np.allclose(mine[used], ref1[used], rtol=2e-5, atol=2e-6)
         assert np.all(ref1[~used] == 0) and np.array_equal(mine[~used], init[~used])
         assert np.array_equal(oracle.ref_pq_kmeans_subspace(sub, 64, 25, 42 + m), cb[m])  # train() == 25 iterations of it
+
+
+def test_opq_pipeline_restatement_reduces_to_the_plain_one():
+    """Identity rotation: the composed OPQ pipeline is the plain pipeline; a true rotation changes only the PQ side."""
+    ix = synth.make_index(6000, 32, 12, 8, seed=91)
+    q = synth.make_queries(ix, 40, seed=92)
+    eye = np.eye(32, dtype=np.float32)
+    a = oracle.ivfpq_search(ix, q, 4, 5, 50)
+    b = oracle.ivfpq_search_opq(ix, q, 4, 5, 50, eye)
+    assert np.array_equal(a["indices"], b["indices"]) and np.array_equal(a["distances"], b["distances"])
+    a = oracle.ivfpq_search(dict(ix, vectors=None), q, 4, 5, 0)
+    b = oracle.ivfpq_search_opq(dict(ix, vectors=None), q, 4, 5, 0, eye)
+    assert np.array_equal(a["indices"], b["indices"]) and np.array_equal(a["distances"], b["distances"])
+    # orientation: matrix is [out][in]
+    rot = np.zeros((32, 32), np.float32); rot[0, 1] = 2.0
+    y = oracle.rotate_rows(q, rot)
+    assert np.array_equal(y[:, 0], 2.0 * q[:, 1]) and not y[:, 1:].any()
