@@ -308,12 +308,14 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="override the base size (scaled-down runs)")
     ap.add_argument("--queries", type=int, default=0, help="override the batch size")
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU baseline sample (0 = auto)")
-    ap.add_argument("--exact-mode", default="auto", choices=["auto", "mapped", "staged", "cached"],
+    ap.add_argument("--exact-mode", default="auto", choices=["auto", "mapped", "staged", "cached", "hybrid"],
                     help="rerank transport on one GPU: staged = host threads gather rows into pinned rings and cudaMemcpyAsync moves "
                          "them (no SM time spent on the transfer), mapped = kernels gather mapped host rows over PCIe; auto = staged "
                          "when a batch gathers at least 2 GB (the scan is then long enough to hide the host gather), else mapped; "
                          "cached = the session copies the rows into device memory once (not the host-resident configuration the "
-                         "headline metric names: an extra data point)")
+                         "headline metric names: an extra data point); hybrid = staged and mapped at once, --zero-copy-pct of every "
+                         "sub-batch through the kernel")
+    ap.add_argument("--zero-copy-pct", type=int, default=0, help="hybrid transport: share of each sub-batch gathered by the kernel (0 = library default)")
     ap.add_argument("--reserve-sms", type=int, default=8, help="N > 1: SMs the scan's persistent grid leaves to the collectives")
     ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
     ap.add_argument("--serial", action="store_true", help="N = 1: no sub-batches (one scan launch per batch, then the rerank)")
@@ -391,7 +393,8 @@ def main():
                            residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas, serial_pipeline=args.serial,
                            pipeline_parts=args.pipeline_parts, even_cuts=args.cut_plan,
                            reserve_sms=max(0, args.n1_reserve_sms),
-                           exact_mode={"staged": api.EXACT_HOST_STAGED, "cached": api.EXACT_HOST_CACHED}.get(args.exact_mode,
+                           zero_copy_pct=args.zero_copy_pct,
+                           exact_mode={"staged": api.EXACT_HOST_STAGED, "cached": api.EXACT_HOST_CACHED, "hybrid": api.EXACT_HOST_HYBRID}.get(args.exact_mode,
                                                                                                             api.EXACT_HOST_MAPPED))
         log("session created in %.1fs" % (time.time() - t0))
         stage1 = min(R, cfg["n"]) if R > topk else topk

@@ -114,9 +114,13 @@ enum {
     PSB_EXACT_HOST_STAGED = 1, /* host threads gather rows into pinned rings, cudaMemcpyAsync overlaps the copies */
     PSB_EXACT_RESIDENT = 2,    /* exact.fp32 / exact.u8 is already a device pointer (IVFExactStorageKind::Resident,
                                   src/search/ivf_common/ivf_storage.h:25-30) */
-    PSB_EXACT_HOST_CACHED = 3  /* the session copies the caller's host rows into device memory once at creation and reranks from
+    PSB_EXACT_HOST_CACHED = 3, /* the session copies the caller's host rows into device memory once at creation and reranks from
                                   there (refused with PSB_OUT_OF_MEMORY when they do not fit); no counterpart in the reference,
                                   whose rerank rows stay on the host */
+    PSB_EXACT_HOST_HYBRID = 4  /* both host transports at once: the rows are registered and mapped as in HOST_MAPPED, and of every
+                                  sub-batch psb_options.zero_copy_pct percent of the queries have their rows gathered by a kernel
+                                  over PCIe while host threads stage the others through the pinned rings; neither the host
+                                  cores nor the kernel's reads fill the link alone */
 };
 
 /* IVFPQSearchOptions (src/search/ivfpq/ivfpq_search_context.h:31-45) reduced to what this path uses,
@@ -161,7 +165,7 @@ typedef struct psb_options {
        (nothing is left in flight; the kernel frees its tensor memory and returns; the call reports PSB_TIMEOUT). */
     int test_wait_limit;
     int test_skip_mma;
-    int reserved[1];
+    int zero_copy_pct;  /* PSB_EXACT_HOST_HYBRID: share of each sub-batch gathered by the kernel, 1..99 (0 = 40) */
     /* Residual mode, optional: the per-row correction asset of the index, value[row] = |recon(row)|^2 + 2 <centroid[list(row)],
        recon(row)> (src/common/row_correction.h:37-45), as HOST arrays over the rows of the view - either fp32 or the affine u16
        form (value = rc_offset + rc_scale * u16, src/common/row_correction.h:7-20).  The residual cutoff estimate reads it;

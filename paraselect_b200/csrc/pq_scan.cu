@@ -119,43 +119,50 @@ __device__ __forceinline__ void list_items(int v, long long rows, int group, int
     if (tc_min_vis > 0 && v >= tc_min_vis) tc = (long long)((v + tc_group - 1) / tc_group) * chunks;
     else simt = (long long)((v + group - 1) / group) * chunks;
 }
-__global__ void k_scan_lists(const int* __restrict__ vis_count, const long long* __restrict__ offsets, int nlist,
+__global__ void __launch_bounds__(1024) k_scan_lists(const int* __restrict__ vis_count, const long long* __restrict__ offsets, int nlist,
                              int group, int chunk_rows, int* __restrict__ vis_off,
                              long long* __restrict__ item_off, int* __restrict__ vis_cursor,
                              int tc_group, int tc_min_vis, long long* __restrict__ item_off_tc) {
-    __shared__ long long s_part_items[1024], s_part_tc[1024];
-    __shared__ int s_part_vis[1024];
-    const int t = threadIdx.x, nt = blockDim.x;
-    const int per = (nlist + nt - 1) / nt;
-    const int b = min(t * per, nlist), e = min(b + per, nlist);
-    long long items = 0, items_tc = 0; int vis = 0;
-    for (int l = b; l < e; ++l) {
-        const int v = vis_count[l];
-        long long si, ti;
-        list_items(v, offsets[l + 1] - offsets[l], group, tc_group, tc_min_vis, chunk_rows, si, ti);
-        vis += v; items += si; items_tc += ti;
-    }
-    s_part_items[t] = items; s_part_tc[t] = items_tc; s_part_vis[t] = vis;
-    __syncthreads();
-    if (t == 0) {
-        long long ai = 0, at = 0; int av = 0;
-        for (int i = 0; i < nt; ++i) {
-            const long long ci = s_part_items[i], ct = s_part_tc[i]; const int cv = s_part_vis[i];
-            s_part_items[i] = ai; s_part_tc[i] = at; s_part_vis[i] = av;
-            ai += ci; at += ct; av += cv;
+    // Rounds of blockDim.x consecutive lists (coalesced reads and writes), each round one block-wide scan of the three
+    // per-list counts; the running totals carry over in registers.
+    __shared__ long long s_items[32], s_tc[32];
+    __shared__ int s_vis[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    long long carry_items = 0, carry_tc = 0; int carry_vis = 0;
+    for (int base = 0; base < nlist; base += blockDim.x) {
+        const int l = base + threadIdx.x;
+        int v = 0; long long si = 0, ti = 0;
+        if (l < nlist) {
+            v = vis_count[l];
+            list_items(v, offsets[l + 1] - offsets[l], group, tc_group, tc_min_vis, chunk_rows, si, ti);
         }
-        item_off[nlist] = ai; vis_off[nlist] = av;
-        if (item_off_tc) item_off_tc[nlist] = at;
+        int iv = v; long long ii = si, it = ti;   // inclusive within the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int nv = __shfl_up_sync(0xffffffffu, iv, o);
+            const long long ni = __shfl_up_sync(0xffffffffu, ii, o), nt = __shfl_up_sync(0xffffffffu, it, o);
+            if (lane >= o) { iv += nv; ii += ni; it += nt; }
+        }
+        if (lane == 31) { s_vis[warp] = iv; s_items[warp] = ii; s_tc[warp] = it; }
+        __syncthreads();
+        int wv = 0; long long wi = 0, wt = 0, tv = 0, tti = 0, ttt = 0;   // exclusive warp offsets and the round's totals
+        for (int w2 = 0; w2 < nwarps; ++w2) {
+            const int cv = s_vis[w2]; const long long ci = s_items[w2], ct = s_tc[w2];
+            if (w2 < warp) { wv += cv; wi += ci; wt += ct; }
+            tv += cv; tti += ci; ttt += ct;
+        }
+        if (l < nlist) {
+            vis_off[l] = carry_vis + wv + iv - v;
+            item_off[l] = carry_items + wi + ii - si;
+            if (item_off_tc) item_off_tc[l] = carry_tc + wt + it - ti;
+            vis_cursor[l] = 0;
+        }
+        carry_vis += (int)tv; carry_items += tti; carry_tc += ttt;
+        __syncthreads();   // the warp totals are rewritten next round
     }
-    __syncthreads();
-    long long ai = s_part_items[t], at = s_part_tc[t]; int av = s_part_vis[t];
-    for (int l = b; l < e; ++l) {
-        const int v = vis_count[l];
-        long long si, ti;
-        list_items(v, offsets[l + 1] - offsets[l], group, tc_group, tc_min_vis, chunk_rows, si, ti);
-        item_off[l] = ai; vis_off[l] = av; vis_cursor[l] = 0;
-        if (item_off_tc) item_off_tc[l] = at;
-        av += v; ai += si; at += ti;
+    if (threadIdx.x == 0) {
+        item_off[nlist] = carry_items; vis_off[nlist] = carry_vis;
+        if (item_off_tc) item_off_tc[nlist] = carry_tc;
     }
 }
 

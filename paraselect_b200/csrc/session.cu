@@ -225,6 +225,8 @@ struct psb_session {
     cudaStream_t stream = nullptr;
     bool own_stream = false;
     cudaStream_t aux_stream = nullptr;  // second stream of the overlapped pipeline (created on first use)
+    cudaStream_t zc_stream = nullptr;   // hybrid transport: the kernel gather runs here, beside the copies of aux_stream
+    cudaEvent_t zc_begin = nullptr, zc_end = nullptr;
     cudaStream_t home_stream = nullptr; // the stream the session was created with (psb_session_set_stream(NULL) returns to it)
     bool background = false;            // stage calls currently run on a caller's second stream: small-grid gather
     psb_options opt{};
@@ -292,6 +294,9 @@ struct psb_session {
         }
         if (h_cand_pinned) cudaFreeHost(h_cand_pinned);
         if (aux_stream) { cudaStreamSynchronize(aux_stream); cudaStreamDestroy(aux_stream); }
+        if (zc_stream) { cudaStreamSynchronize(zc_stream); cudaStreamDestroy(zc_stream); }
+        if (zc_begin) cudaEventDestroy(zc_begin);
+        if (zc_end) cudaEventDestroy(zc_end);
         if (own_stream && stream) cudaStreamDestroy(stream);
         cudaGetLastError();
     }
@@ -418,8 +423,11 @@ int sub_batch_rows(const psb_session* s, int n, int nprobe, bool overlap) {
     return (n + parts - 1) / parts;
 }
 
+// The staged transport (host gather threads + pinned rings), alone or with the kernel gather beside it.
+bool staged_mode(const psb_session* s) { return s->opt.exact_mode == PSB_EXACT_HOST_STAGED || s->opt.exact_mode == PSB_EXACT_HOST_HYBRID; }
+
 bool overlap_enabled(const psb_session* s, int n, bool rerank) {
-    return rerank && s->opt.exact_mode != PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
+    return rerank && !staged_mode(s) && n >= 2048 && !s->opt.serial_pipeline;
 }
 
 // Grows the scan workspace to hold nq queries (never shrinks; a growing buffer is freed first, which waits for the device).
@@ -648,7 +656,7 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
     if (width <= 0 || stride < width || topk <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid rerank request");
     if (width > kMaxRerankWidth || topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "rerank width above 4096 or topk above 2048");
     PSB_TRY(s->stage.reserve((size_t)nq * width * s->dim * s->exact_elem));
-    if (s->opt.exact_mode == PSB_EXACT_HOST_STAGED) {
+    if (staged_mode(s)) {
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
         PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
@@ -692,7 +700,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     psb_options opt{};
     if (options) opt = *options;
     if (opt.max_batch <= 0) opt.max_batch = 10000;
-    if (opt.exact_mode < 0 || opt.exact_mode > PSB_EXACT_HOST_CACHED) return fail(PSB_INVALID_ARGUMENT, "unknown exact_mode");
+    if (opt.exact_mode < 0 || opt.exact_mode > PSB_EXACT_HOST_HYBRID) return fail(PSB_INVALID_ARGUMENT, "unknown exact_mode");
     const int nlist = index->lists.nlist;
     int lb = opt.list_begin, le = opt.list_end;
     if (lb == 0 && le == 0) le = nlist;
@@ -713,6 +721,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if (opt.pipeline_parts != 0 && (opt.pipeline_parts < 2 || opt.pipeline_parts > 32)) return fail(PSB_INVALID_ARGUMENT, "pipeline_parts must be 0 or in 2..32");
     if (opt.scan_mode < 0 || opt.scan_mode > 3) return fail(PSB_INVALID_ARGUMENT, "scan_mode must be in 0..3");
     if (opt.tc_min_visitors < 0) return fail(PSB_INVALID_ARGUMENT, "tc_min_visitors must not be negative");
+    if (opt.zero_copy_pct < 0 || opt.zero_copy_pct > 99) return fail(PSB_INVALID_ARGUMENT, "zero_copy_pct must be in 0..99");
     if (opt.gather_ctas < 0 || opt.gather_ctas > 1024) return fail(PSB_INVALID_ARGUMENT, "gather_ctas must be in 0..1024");
     if (opt.adc_mode == 1 && !index->exact.fp32 && !index->exact.u8)
         return fail(PSB_INVALID_ARGUMENT, "residual mode always reranks: exact rows are required");
@@ -811,7 +820,7 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
                                          static_cast<const unsigned char*>(s->exact_host) + off, std::min(chunk, bytes - off),
                                          cudaMemcpyHostToDevice, st));
             s->exact_dev = s->exact_cache.p;
-        } else if (opt.exact_mode == PSB_EXACT_HOST_MAPPED && bytes > 0) {
+        } else if ((opt.exact_mode == PSB_EXACT_HOST_MAPPED || opt.exact_mode == PSB_EXACT_HOST_HYBRID) && bytes > 0) {
             cudaError_t e = cudaHostRegister(const_cast<void*>(s->exact_host), bytes, cudaHostRegisterMapped | cudaHostRegisterReadOnly);
             if (e == cudaErrorHostMemoryAlreadyRegistered) { cudaGetLastError(); e = cudaSuccess; }
             else if (e != cudaSuccess) {
@@ -1005,7 +1014,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     // Staged transport, overlapped: a host worker thread takes each sub-batch's candidates as soon as its scan has finished,
     // gathers the rows with the host cores into the pinned rings and queues copies + exact scoring on the second stream,
     // while this thread goes on queueing the next sub-batch's scan.  No SM is spent on the transfer.
-    const bool staged_overlap = rerank && s->opt.exact_mode == PSB_EXACT_HOST_STAGED && n >= 2048 && !s->opt.serial_pipeline;
+    const bool staged_overlap = rerank && staged_mode(s) && n >= 2048 && !s->opt.serial_pipeline;
     const int sb = sub_batch_rows(s, n, nprobe, overlap || staged_overlap);
     const bool residual = s->opt.adc_mode == 1;
     // Sub-batch boundaries.  Equal cuts, except with the overlapped staged transport.  There the transfer costs the scan
@@ -1055,6 +1064,15 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     psb_status worker_rc = PSB_OK;
     std::string worker_msg;
     std::thread worker;
+    const bool hybrid = staged_overlap && s->opt.exact_mode == PSB_EXACT_HOST_HYBRID && s->exact_dev != nullptr;
+    const int zc_pct = s->opt.zero_copy_pct > 0 ? s->opt.zero_copy_pct : 40;
+    if (hybrid && !s->zc_stream) {
+        int lo = 0, hi = 0;
+        PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        PSB_CUDA(cudaStreamCreateWithPriority(&s->zc_stream, cudaStreamNonBlocking, lo));
+        PSB_CUDA(cudaEventCreateWithFlags(&s->zc_begin, cudaEventDisableTiming));
+        PSB_CUDA(cudaEventCreateWithFlags(&s->zc_end, cudaEventDisableTiming));
+    }
     if (staged_overlap) {
         const size_t cand_count = (size_t)n * stage1_k;
         if (s->h_cand_pinned_count < cand_count) {
@@ -1072,7 +1090,22 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
                 const int* cand_d = s->cand_rows.as<int>() + (size_t)j.p0 * stage1_k;
                 const int* cnt_d = s->cand_count.as<int>() + j.p0;
                 if (times) PSB_TRY(tm_x.mark(sx));
-                PSB_TRY(staged_gather_host(s, s->h_cand_pinned + (size_t)j.p0 * stage1_k, j.m, stage1_k, stage1_k, s->stage.p, sx));
+                // Hybrid transport: the last mz queries' rows are fetched by the gather kernel on a stream of its own (it may not
+                // start before the previous sub-batch's scoring has let go of the staging buffer) while the host threads and
+                // the copy engine bring the others; the scoring waits for both.
+                const int mz = hybrid ? (int)((long long)j.m * zc_pct / 100) : 0;
+                const int mh = j.m - mz;
+                if (mz > 0) {
+                    PSB_CUDA(cudaEventRecord(s->zc_begin, sx));
+                    PSB_CUDA(cudaStreamWaitEvent(s->zc_stream, s->zc_begin, 0));
+                    PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, cand_d + (size_t)mh * stage1_k, mz, stage1_k,
+                                               stage1_k, cnt_d + mh,
+                                               static_cast<unsigned char*>(s->stage.p) + (size_t)mh * stage1_k * s->dim * s->exact_elem,
+                                               s->zc_stream, s->sm_count, s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count));
+                    PSB_CUDA(cudaEventRecord(s->zc_end, s->zc_stream));
+                }
+                if (mh > 0) PSB_TRY(staged_gather_host(s, s->h_cand_pinned + (size_t)j.p0 * stage1_k, mh, stage1_k, stage1_k, s->stage.p, sx));
+                if (mz > 0) PSB_CUDA(cudaStreamWaitEvent(sx, s->zc_end, 0));
                 const unsigned char* qe = static_cast<const unsigned char*>(dq_exact) + (size_t)j.p0 * s->dim * s->exact_elem;
                 PSB_TRY(launch_rerank_score(s->stage.p, s->row_map(), s->dim, s->exact_elem, qe, cand_d, j.m, stage1_k, stage1_k,
                                             cnt_d, s->score.as<float>(), sx));

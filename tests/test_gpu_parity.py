@@ -186,7 +186,7 @@ def test_rerank_random_matches_checker(psb, dim):
 
 # ---------------------------------------------------------------------------------------------- whole search
 @pytest.mark.parametrize("name", ["ivfpq_d32_m8", "ivfpq_d96_m48_zipf", "ivfpq_d100_m20"])
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 4])
 def test_search_matches_reference_golden(psb, name, mode):
     g = cases.load_golden(name)
     nprobe, topk, n_rerank = (int(x) for x in g["params"])
@@ -472,12 +472,15 @@ def test_staged_transport_overlapped_by_a_host_worker_equals_mapped(psb):
     q = synth.make_queries(ix, 2600, seed=82, weights=synth.zipf_weights(64))
     res = {}
     for name, kw in (("mapped", dict()), ("staged", dict(exact_mode=psb.EXACT_HOST_STAGED)),
-                     ("staged_serial", dict(exact_mode=psb.EXACT_HOST_STAGED, serial_pipeline=True))):
+                     ("staged_serial", dict(exact_mode=psb.EXACT_HOST_STAGED, serial_pipeline=True)),
+                     ("hybrid", dict(exact_mode=psb.EXACT_HOST_HYBRID)),
+                     ("hybrid_70", dict(exact_mode=psb.EXACT_HOST_HYBRID, zero_copy_pct=70)),
+                     ("hybrid_serial", dict(exact_mode=psb.EXACT_HOST_HYBRID, serial_pipeline=True))):
         with psb.Session(ix, n_rerank=120, **kw) as s:
             res[name] = s.search(q, 8, 10, batch_size=2600)
             again = s.search(q, 8, 10, batch_size=2600)  # buffers are reused across batches
             assert np.array_equal(again["indices"], res[name]["indices"])
-    for name in ("staged", "staged_serial"):
+    for name in ("staged", "staged_serial", "hybrid", "hybrid_70", "hybrid_serial"):
         assert np.array_equal(res[name]["indices"], res["mapped"]["indices"])
         assert np.array_equal(res[name]["distances"], res["mapped"]["distances"])
 
