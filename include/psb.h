@@ -328,6 +328,27 @@ psb_status psb_stage_scan(psb_session* session, const float* d_lut, int nq, cons
 psb_status psb_stage_scan_queries(psb_session* session, const float* d_queries, const float* d_lut, int nq,
                                   const int* d_probes, int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count);
 
+/* Sharded search (one session per shard of the index, e.g. one per GPU): the stage in two calls, so that the admission cutoff of
+ * a query is placed on the rows of ALL shards instead of every shard looking for stage1_k rows of its own - with N shards the
+ * shards then admit about 1/N of the rows each instead of as many as an unsharded search admits in all.
+ *   1. psb_stage_scan_sample: schedule + sampling.  d_samples [nq][psb_scan_sample_words(session, stage1_k)] uint32 receives, per
+ *      query, the smallest sample keys of this shard with their sampling stride and the rows the query scans here.
+ *   2. the caller gathers the records of all shards: d_all_samples [shards][nq][words] (any shard order, the same on every shard
+ *      is not required).
+ *   3. psb_stage_scan_shared: cutoff from all records, scan, selection.  Outputs as psb_stage_scan_queries, except that a query
+ *      may come back with fewer than stage1_k rows of this shard (d_count; -1 / FLT_MAX pad).  d_cutoff [nq] (optional) receives
+ *      the cutoff (+inf: every row was admitted), d_rows_scanned [nq] (optional) the rows the query scans on all shards.
+ * The caller must verify the outcome: after merging the shards' candidates, a query with a finite cutoff and fewer than
+ * min(stage1_k, rows scanned) candidates had its cutoff placed too low (probability ~1e-9 per query at the default margin) and
+ * must be searched again with psb_stage_scan_queries on every shard.  Both calls work on the session's scan workspace: no other
+ * scan of this session may run between them. */
+int psb_scan_sample_words(const psb_session* session, int stage1_k);
+psb_status psb_stage_scan_sample(psb_session* session, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
+                                 int nprobe, int stage1_k, uint32_t* d_samples);
+psb_status psb_stage_scan_shared(psb_session* session, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
+                                 int nprobe, int stage1_k, const uint32_t* d_all_samples, int shards, int* d_rows, float* d_dist,
+                                 int* d_count, float* d_cutoff, int64_t* d_rows_scanned);
+
 /* Exact rerank: drops candidates outside [0,count) and duplicates, recomputes fp32 squared L2 against the
  * exact rows and keeps the topk by (distance, row).  Replaces ivfpq_rerank_cpu -> ivf_rerank_host
  * (src/search/ivfpq/stage/ivfpq_rerank_cpu.cpp:14-66, src/search/ivf_common/ivf_host_rerank.h:7-27).

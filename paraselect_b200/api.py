@@ -102,7 +102,7 @@ EXPORTS = [
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
     "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
     "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
-    "psb_rotate_rows", "psb_stage_rotate_queries",
+    "psb_rotate_rows", "psb_stage_rotate_queries", "psb_scan_sample_words", "psb_stage_scan_sample", "psb_stage_scan_shared",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
@@ -272,6 +272,19 @@ class Session:
     def set_stream(self, stream=None, background=False):
         """Redirects the stage calls to `stream` (a cudaStream_t value; None = the session's own stream)."""
         _check(lib().psb_session_set_stream(self._h, _stream_ptr(stream), int(background)))
+
+    def scan_sample_words(self, stage1_k):
+        return int(lib().psb_scan_sample_words(self._h, stage1_k))
+
+    def stage_scan_sample(self, d_queries, d_lut, nq, d_probes, nprobe, stage1_k, d_samples):
+        _check(lib().psb_stage_scan_sample(self._h, C.c_void_p(_p(d_queries)), C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)), nprobe,
+                                           stage1_k, C.c_void_p(_p(d_samples))))
+
+    def stage_scan_shared(self, d_queries, d_lut, nq, d_probes, nprobe, stage1_k, d_all_samples, shards, d_rows, d_dist, d_count,
+                          d_cutoff=None, d_rows_scanned=None):
+        _check(lib().psb_stage_scan_shared(self._h, C.c_void_p(_p(d_queries)), C.c_void_p(_p(d_lut)), nq, C.c_void_p(_p(d_probes)), nprobe,
+                                           stage1_k, C.c_void_p(_p(d_all_samples)), shards, C.c_void_p(_p(d_rows)), C.c_void_p(_p(d_dist)),
+                                           C.c_void_p(_p(d_count)), C.c_void_p(_p(d_cutoff)), C.c_void_p(_p(d_rows_scanned))))
 
     def stage_rotate_queries(self, d_queries, nq, d_rotated):
         _check(lib().psb_stage_rotate_queries(self._h, C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_rotated))))

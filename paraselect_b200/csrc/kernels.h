@@ -116,7 +116,20 @@ struct ScanWorkspace {
     int reserve_ctas = 0;        // CTAs left out of the scan's persistent grid, so that kernels of another stream that
                                  // cannot share an SM with a scan CTA (a collective's) still find a free SM
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;  // optional: bracket the scan kernel
+    // Sharded search: the cutoff of a query is placed on the rows of ALL shards.  Phase 1 (schedule + sampling) leaves each
+    // query's smallest sample keys in seed_export; the caller exchanges these records between the shards; phase 2 places the
+    // cutoff from every shard's records (seed_all) and runs the scan and the selection, which then no longer asks for
+    // stage1_k rows of this shard alone.
+    int phase = 0;                         // 0 = the whole scan, 1 = schedule + sampling only, 2 = cutoff from seed_all + scan + selection
+    uint32_t* seed_export = nullptr;       // phase 1: [nq][seed_words]
+    const uint32_t* seed_all = nullptr;    // phase 2: [seed_shards][nq][seed_words]
+    int seed_shards = 0;
+    int seed_keys = 0;                     // keys per record; a record is seed_keys + kSeedTail words
+    long long* rows_global = nullptr;      // phase 2, optional: [nq] rows the query scans on all shards together
 };
+constexpr int kSeedTail = 4;               // words after the keys of a sample record: stride, key count, rows scanned (low, high)
+// Keys per sample record of launch_scan's phase 1 for a candidate count and margin (a multiple of 32).
+int seed_record_keys(int stage1_k, float sigma);
 
 struct ScanIndex {
     const uint8_t* codes;      // device, shard rows only
@@ -167,6 +180,7 @@ struct SelectRescoreLaunch {
     int nprobe, dim, nlist; const uint8_t* codes; long long row_base; const long long* row_delta;
     int m, k; bool residual, tree;
     int* out_rows; float* out_dist; int* out_count; int* fail_list; int* n_fail; unsigned long long* counters;
+    bool shared_cut = false;
 };
 psb_status launch_select_rescore(const SelectRescoreLaunch& L, int nq, cudaStream_t s);
 

@@ -235,7 +235,8 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
                  const long long* __restrict__ offsets, int nlist, int lb, int le,
                  const uint8_t* __restrict__ codes, long long row_base, int m, int k,
                  const long long* __restrict__ q_rows, int stage1_k, int pool_cap, float* __restrict__ thr,
-                 int per_probe, int tree, float margin_sigma, float margin_add, const ResidualSource rs) {
+                 int per_probe, int tree, float margin_sigma, float margin_add, const ResidualSource rs,
+                 uint32_t* __restrict__ seed_out, int seed_keys) {
     // per_probe (residual mode): lut holds one table per (query, probe) pair; the probes are then sampled one after
     // the other, each with its own table staged in shared memory.
     extern __shared__ __align__(16) unsigned char s_seed_raw[];
@@ -248,7 +249,16 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     const int q = blockIdx.x;
     const long long N = q_rows[q];
     const float inf = __int_as_float(0x7f800000);
-    if (N <= pool_cap) { if (threadIdx.x == 0) thr[q] = inf; return; }
+    // sample record for the other shards (sharded search): keys, then stride, key count, rows scanned
+    uint32_t* rec = seed_out ? seed_out + (size_t)q * (seed_keys + kSeedTail) : nullptr;
+    auto empty_record = [&](int stride_) {   // nothing to tell: this shard does not take part in placing the cutoff
+        if (!rec) return;
+        for (int i = threadIdx.x; i < seed_keys; i += blockDim.x) rec[i] = 0xffffffffu;
+        if (threadIdx.x == 0) { rec[seed_keys] = (uint32_t)stride_; rec[seed_keys + 1] = 0; rec[seed_keys + 2] = (uint32_t)N; rec[seed_keys + 3] = (uint32_t)(N >> 32); }
+    };
+    // (a shard that records for the others samples even what it would admit whole: its rows count towards the shared cutoff)
+    if (N <= pool_cap && !rec) { if (threadIdx.x == 0) thr[q] = inf; return; }
+    if (N <= 0) { if (threadIdx.x == 0) thr[q] = inf; empty_record(0); return; }
     int stride = stage1_k / 16;
     stride = stride < 16 ? 16 : (stride > 64 ? 64 : stride);
     if ((N + 65535) / 65536 > stride) stride = (int)((N + 65535) / 65536);  // at most ~64K samples per query
@@ -303,8 +313,16 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     const int ns = carry;
     if (threadIdx.x == 0) { s_pref[nprobe] = ns; s_cnt = 0; s_cut = 0xffffffffu; }
     const float mu = (float)stage1_k * (float)ns / (float)N;
-    const int r = (int)ceilf(mu + margin_sigma * sqrtf(mu) + margin_add);
-    if (r >= ns || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; return; }
+    int r = (int)ceilf(mu + margin_sigma * sqrtf(mu) + margin_add);
+    if (rec) {
+        // For the other shards: as many keys as the shared cutoff can ask of ONE shard - the case of a query whose near rows all
+        // lie here.  c keys of stride s put the cutoff once c - sigma sqrt(c) - 2 >= mu (k_pick_cutoff), so c solves that, plus a
+        // few for a larger stride elsewhere.
+        float c = mu;
+        for (int it = 0; it < 6; ++it) c = mu + margin_sigma * sqrtf(c) + 2.0f;
+        r = (int)ceilf(c) + 8;
+    }
+    if ((r >= ns && !rec) || r + (int)blockDim.x > kSeedBuf) { if (threadIdx.x == 0) thr[q] = inf; empty_record(0); return; }
     __syncthreads();
     const bool staged_probes = per_probe && !flat_bias;  // one table per probe, staged one after the other
     const int nseg = staged_probes ? nprobe : 1;
@@ -356,6 +374,77 @@ k_seed_threshold(const float* __restrict__ lut, const int* __restrict__ probes, 
     __syncthreads();
     block_bitonic_sort(s_keys, kSeedBuf);
     if (threadIdx.x == 0) thr[q] = c >= r ? o2f(s_keys[r - 1]) : inf;
+    if (rec) {   // the r smallest sample keys: no key beyond them can lie below a cutoff placed on all shards' samples
+        const int have = c < r ? c : r;
+        const int out = have < seed_keys ? have : seed_keys;
+        for (int i = threadIdx.x; i < seed_keys; i += blockDim.x) rec[i] = i < out ? s_keys[i] : 0xffffffffu;
+        if (threadIdx.x == 0) {
+            rec[seed_keys] = (uint32_t)stride;
+            rec[seed_keys + 1] = (uint32_t)out;
+            rec[seed_keys + 2] = (uint32_t)N; rec[seed_keys + 3] = (uint32_t)(N >> 32);
+        }
+    }
+}
+
+// Sharded search: the cutoff of query q from the sample records of all shards.  A key of shard g stands for stride_g rows of
+// that shard, so after the i smallest keys of the union the rows below key i number about A = sum stride, with variance at
+// most B = sum stride^2 (each stride-th row is a sample).  The cutoff is the first key with A - sigma sqrt(B) - 2 max stride
+// >= stage1_k: at least stage1_k rows of the shards together lie below it except with the probability of a sigma-deviation.
+// A record ends where its shard stopped recording, not where its samples end; keys of other shards beyond that point still
+// count rows that are there, so A only underestimates and the cutoff errs to the high side.  No such key (few rows): +inf,
+// every shard admits all its rows.  A shard whose record is empty (it admits everything it scans anyway, or has too few rows
+// to sample) adds nothing to the sum.
+// The caller verifies the outcome - the candidates of all shards together must number stage1_k - so a cutoff placed too low
+// costs a second pass, never a wrong answer.
+constexpr int kPickThreads = 256;
+__global__ void __launch_bounds__(kPickThreads)
+k_pick_cutoff(const uint32_t* __restrict__ all, int shards, int nq, int seed_keys, int stage1_k, float sigma,
+              float* __restrict__ thr, long long* __restrict__ rows_global) {
+    extern __shared__ __align__(16) uint64_t s_pick[];   // [next_pow2(shards * seed_keys)] key << 32 | stride
+    __shared__ unsigned int s_smax;
+    const int q = blockIdx.x;
+    const int words = seed_keys + kSeedTail;
+    const int total = shards * seed_keys;
+    const int n = next_pow2(max(total, 2));
+    if (threadIdx.x == 0) s_smax = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        uint64_t e = ~0ull;
+        if (i < total) {
+            const int g = i / seed_keys, j = i - g * seed_keys;
+            const uint32_t* rec = all + ((size_t)g * nq + q) * words;
+            const int have = (int)rec[seed_keys + 1];
+            if (j < have) {
+                const uint32_t stride = rec[seed_keys];
+                e = ((uint64_t)rec[j] << 32) | stride;
+                if (j == 0) atomicMax(&s_smax, stride);
+            }
+        }
+        s_pick[i] = e;
+    }
+    __syncthreads();
+    block_bitonic_sort(s_pick, n);
+    if (threadIdx.x == 0) {
+        const float inf = __int_as_float(0x7f800000);
+        const float smax = (float)s_smax;
+        float A = 0.f, B = 0.f, cut = inf;
+        for (int i = 0; i < total; ++i) {
+            const uint64_t e = s_pick[i];
+            if (e == ~0ull) break;
+            const float st = (float)(uint32_t)e;
+            A += st; B += st * st;
+            if (A - sigma * sqrtf(B) - 2.0f * smax >= (float)stage1_k) { cut = o2f((uint32_t)(e >> 32)); break; }
+        }
+        thr[q] = cut;
+        if (rows_global) {
+            long long N = 0;
+            for (int g = 0; g < shards; ++g) {
+                const uint32_t* rec = all + ((size_t)g * nq + q) * words;
+                N += (long long)(((uint64_t)rec[seed_keys + 3] << 32) | rec[seed_keys + 2]);
+            }
+            rows_global[q] = N;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -512,12 +601,14 @@ __global__ void __launch_bounds__(kSelectThreads)
 k_select_pool(const uint64_t* __restrict__ pool, const int* __restrict__ pool_cnt, int pool_cap,
               const long long* __restrict__ q_rows, int stage1_k, int* __restrict__ out_rows,
               float* __restrict__ out_dist, int* __restrict__ out_count, int* __restrict__ fail_list,
-              int* __restrict__ n_fail, unsigned long long* __restrict__ counters) {
+              int* __restrict__ n_fail, unsigned long long* __restrict__ counters, const float* __restrict__ shared_cut) {
     extern __shared__ __align__(16) uint64_t s_keys[];
     const int q = blockIdx.x;
     const int c = pool_cnt[q];
     const long long N = q_rows[q];
-    const long long need = N < stage1_k ? N : stage1_k;
+    // shared_cut (sharded search): the cutoff was placed on all shards' rows, so this shard alone owes no stage1_k rows
+    long long need = N < stage1_k ? N : stage1_k;
+    if (shared_cut && shared_cut[q] < __int_as_float(0x7f800000)) need = 0;
     if (c > pool_cap || c < need) {
         if (threadIdx.x == 0) fail_list[atomicAdd(n_fail, 1)] = q;
         return;  // the fallback writes this query's outputs
@@ -1105,6 +1196,9 @@ psb_status run_scan_m(const ScanArgs& a, int group, int sm_count, cudaStream_t s
 }
 
 // Safety margin of the sampled cutoff in standard deviations (ScanWorkspace::seed_sigma; 4 unless the caller set 2..10).
+// Margin of a cutoff shared by several shards: a cutoff placed too low there costs the caller a second pass over the whole
+// batch, so the margin is wider than for one shard, where the exact fallback repairs a single query.
+float shared_cut_sigma(const ScanWorkspace& ws) { return ws.seed_sigma >= 6.f && ws.seed_sigma <= 10.f ? ws.seed_sigma : 6.0f; }
 float seed_margin_sigma(const ScanWorkspace& ws) { return ws.seed_sigma >= 2.f && ws.seed_sigma <= 10.f ? ws.seed_sigma : 4.0f; }
 
 template <int M>
@@ -1118,7 +1212,8 @@ psb_status run_seed(const ScanIndex& ix, const ScanWorkspace& ws, const float* d
     k_seed_threshold<M><<<nq, kSeedThreads, smem, s>>>(d_lut, d_probes, nprobe, ix.offsets, ix.nlist, ix.list_begin,
                                                          ix.list_end, ix.codes, ix.row_base, ix.m, ix.k, ws.q_rows,
                                                          stage1_k, ws.pool_cap, ws.thr, ix.residual ? 1 : 0,
-                                                         tree_order(ix) ? 1 : 0, seed_margin_sigma(ws), seed_margin_sigma(ws) - 2.0f, rs);
+                                                         tree_order(ix) ? 1 : 0, ws.phase == 1 ? shared_cut_sigma(ws) : seed_margin_sigma(ws),
+                                                         seed_margin_sigma(ws) - 2.0f, rs, ws.phase == 1 ? ws.seed_export : nullptr, ws.seed_keys);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -1161,6 +1256,15 @@ psb_status run_fallback(const ScanIndex& ix, const ScanWorkspace& ws, const floa
     }
 
 }  // namespace
+
+int seed_record_keys(int stage1_k, float sigma) {
+    const float s = sigma >= 6.f && sigma <= 10.f ? sigma : 6.0f;   // the margin of the shared cutoff
+    const float mu = (float)stage1_k / 16.0f + 16.0f;   // the smallest stride is 16; the ceilings of the per-list sample counts add a little
+    float c = mu;
+    for (int it = 0; it < 6; ++it) c = mu + s * std::sqrt(c) + 2.0f;
+    const int r = (int)std::ceil(c) + 8;
+    return (r + 31) / 32 * 32;
+}
 
 psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
                             float* d_lut, cudaStream_t s) {
@@ -1254,6 +1358,11 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
         return fail(PSB_INTERNAL, "scan workspace holds " + std::to_string(ws.cap_queries) + " queries / " + std::to_string(ws.cap_tables) +
                                       " tables, the call needs " + std::to_string(nq) + " / " + std::to_string(tables));
     const int group = use_half ? kHalfGroup : pick_group(ix.m, ix.k);
+    if (ws.phase == 1 && (!ws.seed_export || ws.seed_keys <= 0)) return fail(PSB_INTERNAL, "scan phase 1 without a record buffer");
+    if (ws.phase == 2 && (!ws.seed_all || ws.seed_shards <= 0 || ws.seed_keys <= 0)) return fail(PSB_INTERNAL, "scan phase 2 without the shards' records");
+    ResidualSource rs;
+    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.row_bias = ix.row_bias; rs.row_bias_u16 = ix.row_bias_u16; rs.rc_scale = ix.rc_scale; rs.rc_offset = ix.rc_offset; rs.dim = ix.dim;
+    if (ws.phase != 2) {
     // schedule
     PSB_CUDA(cudaMemsetAsync(ws.vis_count, 0, sizeof(int) * (size_t)ix.nlist, s));
     PSB_CUDA(cudaMemsetAsync(ws.pool_cnt, 0, sizeof(int) * (size_t)nq, s));
@@ -1279,9 +1388,22 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
     count_launch();
     PSB_LAUNCH_CHECK();
     // cutoff
-    ResidualSource rs;
-    rs.queries = d_queries; rs.centroids = ix.centroids; rs.codebook = ix.codebook; rs.row_bias = ix.row_bias; rs.row_bias_u16 = ix.row_bias_u16; rs.rc_scale = ix.rc_scale; rs.rc_offset = ix.rc_offset; rs.dim = ix.dim;
     PSB_DISPATCH_M(ix.m, PSB_TRY((run_seed<MM>(ix, ws, d_lut, nq, d_probes, nprobe, stage1_k, s, rs))));
+    }
+    if (ws.phase == 1) return PSB_OK;
+    if (ws.phase == 2) {   // the cutoff from every shard's sample records
+        const int n = ws.seed_shards * ws.seed_keys;
+        int np = 2;
+        while (np < n) np <<= 1;
+        const size_t smem = (size_t)np * sizeof(uint64_t);
+        if (smem > (size_t)200 * 1024) return fail(PSB_UNSUPPORTED_SHAPE, "too many shards for the shared cutoff");
+        PSB_TRY(set_smem(k_pick_cutoff, smem));
+        PSB_TRY(prefer_max_shared(k_pick_cutoff));
+        k_pick_cutoff<<<nq, kPickThreads, smem, s>>>(ws.seed_all, ws.seed_shards, nq, ws.seed_keys, stage1_k, shared_cut_sigma(ws), ws.thr,
+                                                     ws.rows_global);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    }
     // scan
     ScanArgs a;
     a.lut = d_lut; a.lut_div = ix.residual ? nprobe : 1; a.tree = tree_order(ix) ? 1 : 0; a.codes = ix.codes; a.offsets = ix.offsets; a.row_base = ix.row_base; a.row_delta = ix.row_delta;
@@ -1325,14 +1447,15 @@ psb_status launch_scan(const ScanIndex& ix, const ScanWorkspace& ws, const float
         R.nprobe = nprobe; R.dim = ix.dim; R.nlist = ix.nlist; R.codes = ix.codes; R.row_base = ix.row_base; R.row_delta = ix.row_delta;
         R.m = ix.m; R.k = ix.k; R.residual = ix.residual; R.tree = tree_order(ix);
         R.out_rows = d_rows; R.out_dist = d_dist; R.out_count = d_count; R.fail_list = ws.fail_list; R.n_fail = ws.n_fail;
-        R.counters = ws.counters;
+        R.counters = ws.counters; R.shared_cut = ws.phase == 2;
         PSB_TRY(launch_select_rescore(R, nq, s));
     } else {
         const size_t smem = (size_t)ws.pool_cap * sizeof(uint64_t);
         PSB_TRY(set_smem(k_select_pool, smem));
         PSB_TRY(prefer_max_shared(k_select_pool));
         k_select_pool<<<nq, kSelectThreads, smem, s>>>(ws.pool, ws.pool_cnt, ws.pool_cap, ws.q_rows, stage1_k, d_rows,
-                                                       d_dist, d_count, ws.fail_list, ws.n_fail, ws.counters);
+                                                       d_dist, d_count, ws.fail_list, ws.n_fail, ws.counters,
+                                                       ws.phase == 2 ? ws.thr : nullptr);
         count_launch();
         PSB_LAUNCH_CHECK();
     }

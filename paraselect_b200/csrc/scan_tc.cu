@@ -580,6 +580,7 @@ struct RescoreArgs {
     int m, k, residual, tree;
     int* out_rows; float* out_dist; int* out_count;
     int* fail_list; int* n_fail; unsigned long long* counters;
+    int shared_cut;   // the cutoff covers the rows of all shards: this shard need not reach stage1_k rows
 };
 
 template <int M>
@@ -591,7 +592,8 @@ __global__ void __launch_bounds__(kRescoreThreads) k_select_rescore(const Rescor
     const int q = blockIdx.x;
     const int c = g.pool_cnt[q];
     const long long N = g.q_rows[q];
-    const long long need = N < g.stage1_k ? N : g.stage1_k;
+    long long need = N < g.stage1_k ? N : g.stage1_k;
+    if (g.shared_cut && g.thr[q] < __int_as_float(0x7f800000)) need = 0;   // sharded search: the shards owe stage1_k rows together
     if (c > g.pool_cap || c < need) {
         if (threadIdx.x == 0) g.fail_list[atomicAdd(g.n_fail, 1)] = q;
         return;  // the fallback writes this query's outputs
@@ -824,7 +826,7 @@ psb_status launch_select_rescore(const SelectRescoreLaunch& L, int nq, cudaStrea
     g.nprobe = L.nprobe; g.dim = L.dim; g.nlist = L.nlist; g.codes = L.codes; g.row_base = L.row_base; g.row_delta = L.row_delta;
     g.m = L.m; g.k = L.k; g.residual = L.residual ? 1 : 0; g.tree = L.tree ? 1 : 0;
     g.out_rows = L.out_rows; g.out_dist = L.out_dist; g.out_count = L.out_count; g.fail_list = L.fail_list; g.n_fail = L.n_fail;
-    g.counters = L.counters;
+    g.counters = L.counters; g.shared_cut = L.shared_cut ? 1 : 0;
     switch (L.m) {
         case 8: return run_select_rescore<8>(g, nq, s);
         case 16: return run_select_rescore<16>(g, nq, s);

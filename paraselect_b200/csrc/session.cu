@@ -924,6 +924,48 @@ psb_status psb_stage_scan_queries(psb_session* s, const float* d_queries, const 
                        s->sm_count, s->stream, d_queries);
 }
 
+int psb_scan_sample_words(const psb_session* s, int stage1_k) {
+    if (!s || stage1_k <= 0) return 0;
+    return seed_record_keys(stage1_k, s->opt.seed_sigma) + kSeedTail;
+}
+
+namespace {
+psb_status check_scan_stage(psb_session* s, const int* d_probes, int nprobe, int stage1_k) {
+    if (!s || !d_probes) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    if (nprobe <= 0 || stage1_k <= 0) return fail(PSB_INVALID_ARGUMENT, "nprobe and stage1_k must be positive");
+    if (nprobe > kMaxProbe || stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or stage1_k above 2048");
+    return PSB_OK;
+}
+}  // namespace
+
+psb_status psb_stage_scan_sample(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
+                                 int nprobe, int stage1_k, uint32_t* d_samples) {
+    PSB_TRY(check_scan_stage(s, d_probes, nprobe, stage1_k));
+    if (!d_samples) return fail(PSB_INVALID_ARGUMENT, "null argument");
+    PSB_CUDA(cudaSetDevice(s->device));
+    PSB_TRY(ensure_scan_ws(s, nq, nprobe, stage1_k));
+    ScanWorkspace ws;
+    PSB_TRY(s->timed_scan_ws(&ws));
+    ws.phase = 1; ws.seed_export = d_samples; ws.seed_keys = seed_record_keys(stage1_k, s->opt.seed_sigma);
+    return launch_scan(s->scan_index(), ws, d_lut, nq, d_probes, nprobe, stage1_k, nullptr, nullptr, nullptr, s->sm_count, s->stream, d_queries);
+}
+
+psb_status psb_stage_scan_shared(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
+                                 int nprobe, int stage1_k, const uint32_t* d_all_samples, int shards, int* d_rows, float* d_dist,
+                                 int* d_count, float* d_cutoff, int64_t* d_rows_scanned) {
+    PSB_TRY(check_scan_stage(s, d_probes, nprobe, stage1_k));
+    if (!d_all_samples || !d_rows || shards <= 0) return fail(PSB_INVALID_ARGUMENT, "null argument or no shards");
+    PSB_CUDA(cudaSetDevice(s->device));
+    if (nq > s->ws_scan_queries) return fail(PSB_INVALID_ARGUMENT, "psb_stage_scan_shared follows psb_stage_scan_sample of the same queries");
+    ScanWorkspace ws;
+    PSB_TRY(s->timed_scan_ws(&ws));
+    ws.phase = 2; ws.seed_all = d_all_samples; ws.seed_shards = shards; ws.seed_keys = seed_record_keys(stage1_k, s->opt.seed_sigma);
+    ws.rows_global = reinterpret_cast<long long*>(d_rows_scanned);
+    PSB_TRY(launch_scan(s->scan_index(), ws, d_lut, nq, d_probes, nprobe, stage1_k, d_rows, d_dist, d_count, s->sm_count, s->stream, d_queries));
+    if (d_cutoff) PSB_CUDA(cudaMemcpyAsync(d_cutoff, ws.thr, sizeof(float) * (size_t)nq, cudaMemcpyDeviceToDevice, s->stream));
+    return PSB_OK;
+}
+
 psb_status psb_stage_rerank(psb_session* s, const float* d_queries, int nq, const int* d_candidates,
                             int candidate_count, int candidate_stride, const int* d_counts, int topk,
                             int* d_out_rows, float* d_out_dist) {

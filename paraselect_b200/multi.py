@@ -81,6 +81,18 @@ class SessionEngine:
         # with the queries at hand the scan can take the tensor-core pre-filter
         self.s.stage_scan_queries(dq, None if self.residual else lut, nq, probes, nprobe, width, rows, dist, count)
 
+    shared_cutoff = True  # the scan can place its cutoffs on the rows of all shards (scan_sample / scan_shared)
+
+    def sample_words(self, width):
+        return self.s.scan_sample_words(width)
+
+    def scan_sample(self, dq, lut, nq, probes, nprobe, width, samples):
+        self.s.stage_scan_sample(dq, None if self.residual else lut, nq, probes, nprobe, width, samples)
+
+    def scan_shared(self, dq, lut, nq, probes, nprobe, width, all_samples, shards, rows, dist, count, cutoff, rows_scanned):
+        self.s.stage_scan_shared(dq, None if self.residual else lut, nq, probes, nprobe, width, all_samples, shards, rows, dist, count,
+                                 cutoff, rows_scanned)
+
     def merge(self, rows, dist, parts, nq, width, out_rows, out_dist):
         self.s.stage_merge(rows, dist, parts, nq, width, out_rows, out_dist)
 
@@ -95,8 +107,14 @@ class SessionEngine:
 
 
 class ShardedSearch:
-    def __init__(self, engine, dist, world, nq, dim, M, K, nprobe, topk, width, torch, rerank=True, parts=1):
+    def __init__(self, engine, dist, world, nq, dim, M, K, nprobe, topk, width, torch, rerank=True, parts=1, shared_cutoff=True):
         self.e, self.dist, self.world, self.torch = engine, dist, world, torch
+        # Cutoffs placed on all shards' rows: every rank then admits about 1 / world of what an unsharded scan admits instead of
+        # looking for `width` rows of its own.  The merged candidates are checked after every exchange; a batch in which a
+        # cutoff turned out too low (practically never) is searched again with per-shard cutoffs (self.redone counts them).
+        self.shared = bool(shared_cutoff) and world > 1 and getattr(engine, "shared_cutoff", False)
+        self.rank = dist.get_rank() if world > 1 else 0
+        self.redone = 0
         self.parts, self.aux = parts, None
         self.nq, self.nprobe, self.topk, self.width, self.rerank = nq, nprobe, topk, width, rerank
         t = torch
@@ -118,6 +136,13 @@ class ShardedSearch:
         self.o_rows = engine.empty((nq, topk), t.int32)
         self.o_dist = engine.empty((nq, topk), t.float32)
         self.o_ids = engine.empty((nq, topk), t.int64)
+        if self.shared:
+            self.words = engine.sample_words(width)
+            self.smp = engine.empty((nq, self.words), t.int32)            # this shard's sample records
+            self.smp_all = engine.empty((world, nq, self.words), t.int32)  # every shard's
+            self.cut = engine.empty((nq,), t.float32)
+            self.n_scan = engine.empty((nq,), t.int64)
+            self.low = engine.empty((1,), t.int32)                         # != 0: some query of the batch came back short
         self.marks = None
 
     def _mark(self, name):
@@ -136,7 +161,16 @@ class ShardedSearch:
         e = self.e
         sl = slice(q0, q0 + m)
         e.lut(dq[sl], m, self.lut[:m])
-        e.scan(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, self.l_rows[sl], self.l_dist[sl], self.l_cnt[sl])
+        if self.use_shared:
+            w, words = self.world, self.words
+            mine = self.smp.view(-1)[:m * words].view(m, words)
+            every = self.smp_all.view(-1)[:w * m * words].view(w, m, words)
+            e.scan_sample(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, mine)
+            self.dist.all_gather_into_tensor(every.view(w * m, words), mine)
+            e.scan_shared(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, every, w, self.l_rows[sl], self.l_dist[sl],
+                          self.l_cnt[sl], self.cut[sl], self.n_scan[sl])
+        else:
+            e.scan(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, self.l_rows[sl], self.l_dist[sl], self.l_cnt[sl])
         self._mark("lut+scan")
 
     def _back(self, dq, q0, m):
@@ -164,6 +198,14 @@ class ShardedSearch:
             g_dist.view(t.int32).copy_(halves[..., 1])
             self._mark("all_to_all")
             e.merge(g_rows, g_dist, w, ms, width, mg_rows, mg_dist)
+            if self.use_shared:   # my slice: a finite cutoff must have left min(width, rows scanned) candidates among all shards
+                a = min(q0 + self.rank * ms, q0 + m)
+                b = min(a + ms, q0 + m)
+                if b > a:
+                    have = (mg_rows[:b - a] >= 0).sum(dim=1)
+                    need = self.n_scan[a:b].clamp(max=width)
+                    short = ((have < need) & t.isfinite(self.cut[a:b])).any()
+                    self.low.add_(short.to(t.int32))
             self._mark("merge")
             d.all_gather_into_tensor(all_rows, mg_rows)              # 4 bytes per candidate: the whole sub-batch's candidate table
             self._mark("all_gather")
@@ -194,10 +236,22 @@ class ShardedSearch:
             self.dist.all_reduce(self.o_ids, op=self.dist.ReduceOp.MAX)
         self._mark("all_reduce_max")
 
-    def step(self, dq, profile=False, parts=None):
+    def step(self, dq, profile=False, parts=None, shared=None):
         """One batch.  parts > 1 cuts the batch into sub-batches; on an engine with streams the exchange half of
         sub-batch i (collectives, PCIe rerank) then runs on a second stream beside the scan of sub-batch i + 1.
         profile=True runs the batch serially in one piece and records per-stage times."""
+        self.use_shared = self.shared if shared is None else (bool(shared) and self.shared)
+        if self.use_shared:
+            self.low.zero_()
+        out = self._step(dq, profile, parts)
+        if self.use_shared:   # one word for the whole batch: did any rank see a query come back short?
+            self.dist.all_reduce(self.low, op=self.dist.ReduceOp.MAX)
+            if int(self.low.item()) != 0:
+                self.redone += 1
+                return self.step(dq, profile, parts, shared=False)
+        return out
+
+    def _step(self, dq, profile, parts):
         e, nq = self.e, self.nq
         parts = 1 if profile else (self.parts if parts is None else parts)
         parts = max(1, min(parts, nq))

@@ -10,12 +10,115 @@ INF = np.float32(np.inf)
 FLT_MAX = np.finfo(np.float32).max
 
 
+SEED_TAIL = 4  # words after the keys of a sample record: stride, key count, rows scanned (low, high)
+
+
+def _pool_capacity(stage1_k):
+    c = 1024
+    while c < 16 * stage1_k and c < 16384:
+        c <<= 1
+    return c
+
+
+def _export_count(mu, sigma):
+    c = mu
+    for _ in range(6):
+        c = mu + sigma * np.sqrt(c) + 2.0
+    return int(np.ceil(c)) + 8
+
+
+def _record_keys(stage1_k, sigma=6.0):
+    return (_export_count(stage1_k / 16.0 + 16.0, sigma) + 31) // 32 * 32
+
+
+def _f2key(d):
+    """Order-preserving uint32 image of non-negative fp32 distances."""
+    return (np.asarray(d, np.float32).view(np.uint32) | np.uint32(0x80000000)).astype(np.uint32)
+
+
+def _key2f(k):
+    return (np.asarray(k, np.uint32) & np.uint32(0x7FFFFFFF)).view(np.float32)
+
+
+def pick_shared_cutoff(records, keys, stage1_k, sigma):
+    """The cutoff of one query from every shard's record [shards][keys + SEED_TAIL]: the rule of the library's k_pick_cutoff."""
+    ents = []
+    smax = 0
+    for rec in records:
+        stride, have = int(rec[keys]), int(rec[keys + 1])
+        if have:
+            smax = max(smax, stride)
+        for j in range(have):
+            ents.append((int(rec[j]), stride))
+    ents.sort()
+    A = B = 0.0
+    for key, stride in ents:
+        A += stride; B += stride * stride
+        if A - sigma * np.sqrt(B) - 2.0 * smax >= stage1_k:
+            return float(_key2f(np.uint32(key)))
+    return float("inf")
+
+
 class CpuCheckerEngine:
-    def __init__(self, index, global_begin):
+    def __init__(self, index, global_begin, shared_sigma=6.0, cut_scale=1.0):
         self.ix = index                      # local (striped) index: offsets are local
         self.gb = np.asarray(global_begin, np.int64)
         self.loff = np.asarray(index["offsets"], np.int64)
         self.q = None
+        self.shared_sigma = shared_sigma     # margin of the shared cutoff (the library uses 6)
+        self.cut_scale = cut_scale           # < 1 puts every shared cutoff too low: exercises the caller's second pass
+        self.shared_calls = 0
+
+    shared_cutoff = True
+
+    def sample_words(self, width):
+        return _record_keys(width) + SEED_TAIL
+
+    def scan_sample(self, dq, lut, nq, probes, nprobe, width, samples):
+        """Per query the smallest sample keys of this shard (every stride-th row of each probed list), as the library's
+        sampling kernel records them."""
+        keys = _record_keys(width)
+        lut = oracle.pq_lut(self.q_sub, self.ix["codebook"])
+        M = lut.shape[1]
+        codes = self.ix["codes"]
+        out = np.full((nq, keys + SEED_TAIL), 0xFFFFFFFF, np.uint32)
+        pr = probes.numpy().astype(np.int64)
+        for q in range(nq):
+            lists = [l for l in pr[q] if 0 <= l < self.loff.size - 1]
+            N = int(sum(self.loff[l + 1] - self.loff[l] for l in lists))
+            out[q, keys:] = (0, 0, N & 0xFFFFFFFF, N >> 32)
+            if N <= 0:
+                continue
+            stride = min(max(width // 16, 16), 64)
+            rows = np.concatenate([np.arange(self.loff[l], self.loff[l + 1], stride) for l in lists])
+            ns = rows.size
+            mu = width * ns / N
+            r = _export_count(mu, self.shared_sigma)
+            d = np.zeros(ns, np.float32)
+            for m in range(M):
+                d += lut[q, m][codes[rows, m]]
+            k = np.sort(_f2key(d))[:r]
+            n_out = min(r, keys, k.size)
+            out[q, :n_out] = k[:n_out]
+            out[q, keys] = stride
+            out[q, keys + 1] = n_out
+        samples.copy_(torch.from_numpy(out.view(np.int32)))
+
+    def scan_shared(self, dq, lut, nq, probes, nprobe, width, all_samples, shards, rows, dist, count, cutoff, rows_scanned):
+        self.shared_calls += 1
+        keys = _record_keys(width)
+        rec = all_samples.numpy().view(np.uint32)
+        cut = np.array([pick_shared_cutoff(rec[:, q], keys, width, self.shared_sigma) for q in range(nq)], np.float32)
+        cut = np.where(np.isfinite(cut), cut * np.float32(self.cut_scale), cut).astype(np.float32)
+        self.scan(dq, lut, nq, probes, nprobe, width, rows, dist, count)
+        r, d = rows.numpy(), dist.numpy()
+        drop = d > cut[:, None]
+        r[drop] = -1
+        d[drop] = FLT_MAX
+        count.copy_(torch.from_numpy((r >= 0).sum(1).astype(np.int32)))
+        cutoff.copy_(torch.from_numpy(cut))
+        n_all = (rec[:, :, keys + 2].astype(np.int64) | (rec[:, :, keys + 3].astype(np.int64) << 32)).sum(0)
+        rows_scanned.copy_(torch.from_numpy(n_all))
 
     def empty(self, shape, dtype):
         return torch.zeros(shape, dtype=dtype)

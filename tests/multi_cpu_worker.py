@@ -41,6 +41,29 @@ def main():
     # the same batch cut into three sub-batches (16 = 6 + 6 + 4): each runs its own exchange
     ids3, dd3 = s.step(torch.from_numpy(q), parts=3)
     ok = ok and np.array_equal(ids3.numpy(), want["indices"]) and np.array_equal(dd3.numpy(), want["distances"])
+    # cutoffs placed on all shards' rows: a larger index, so that the sampled cutoffs are finite and the shards come back with
+    # fewer than `width` rows each; the result must not change
+    big = synth.make_index(40000, 32, 12, 8, seed=79, zipf=True)
+    qb = synth.make_queries(big, 12, seed=80, weights=synth.zipf_weights(12))
+    wantb = oracle.ivfpq_search(big, qb, 6, 7, 40)
+    lb, gbb = stripe_index(big, rank, world)
+    engb = CpuCheckerEngine(lb, gbb, shared_sigma=2.0)
+    sb = ShardedSearch(engb, dist, world, 12, 32, 8, 256, 6, 7, 40, torch, rerank=True)
+    idb, ddb = sb.step(torch.from_numpy(qb), parts=2)
+    if world > 1:
+        ok = ok and engb.shared_calls == 2 and sb.redone == 0 and bool(torch.isfinite(sb.cut).all())
+    ok = ok and np.array_equal(idb.numpy(), wantb["indices"]) and np.array_equal(ddb.numpy(), wantb["distances"])
+    # ... and a cutoff placed too low is noticed after the merge: the batch runs again with per-shard cutoffs
+    engl = CpuCheckerEngine(lb, gbb, shared_sigma=2.0, cut_scale=0.5)
+    sl = ShardedSearch(engl, dist, world, 12, 32, 8, 256, 6, 7, 40, torch, rerank=True)
+    idl, ddl = sl.step(torch.from_numpy(qb))
+    if world > 1:
+        ok = ok and sl.redone == 1
+    ok = ok and np.array_equal(idl.numpy(), wantb["indices"]) and np.array_equal(ddl.numpy(), wantb["distances"])
+    # switched off, the exchange is the plain one
+    sp = ShardedSearch(engb, dist, world, 12, 32, 8, 256, 6, 7, 40, torch, rerank=True, shared_cutoff=False)
+    idp, ddp = sp.step(torch.from_numpy(qb))
+    ok = ok and np.array_equal(idp.numpy(), wantb["indices"]) and np.array_equal(ddp.numpy(), wantb["distances"])
     # data-parallel k-means: rows split between the ranks, sums and counts all-reduced every iteration
     from fake_engine import CpuTrainEngine
     from paraselect_b200.multi import sharded_kmeans
