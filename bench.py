@@ -318,6 +318,8 @@ def main():
     ap.add_argument("--zero-copy-pct", type=int, default=0, help="hybrid transport: share of each sub-batch gathered by the kernel (0 = library default)")
     ap.add_argument("--reserve-sms", type=int, default=8, help="N > 1: SMs the scan's persistent grid leaves to the collectives")
     ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
+    ap.add_argument("--local-cutoffs", action="store_true", help="N > 1: every rank places its admission cutoffs on its own rows only "
+                    "(default: on the rows of all ranks, from exchanged sample records)")
     ap.add_argument("--serial", action="store_true", help="N = 1: no sub-batches (one scan launch per batch, then the rerank)")
     ap.add_argument("--pipeline-parts", type=int, default=0, help="N = 1: sub-batches per batch (0 = library default)")
     ap.add_argument("--cut-plan", type=int, default=0, help="N = 1, staged transport: sub-batch cut plan (see psb_options.even_cuts)")
@@ -563,7 +565,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
                            exact_mode=api.EXACT_HOST_CACHED if getattr(args, "exact_mode", "") == "cached" else api.EXACT_HOST_MAPPED)
         width = min(R, n) if R > topk else topk
         search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
-                               rerank=R > topk, parts=args.parts if nq >= 2048 else 1)
+                               rerank=R > topk, parts=args.parts if nq >= 2048 else 1, shared_cutoff=not args.local_cutoffs)
         search.step(dq, profile=True)  # first step in one piece: every workspace reaches its final size before streams overlap
         for _ in range(max(args.warmup, 3)):
             search.step(dq)
@@ -608,7 +610,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
         torch.cuda.synchronize()
         # totals over ranks
         tot = torch.tensor([float(c["pq_scanned_codes"]), float(c["scan_kernel_ms"]), float(c["scan_kernel_launches"]),
-                            float(c["kernel_launches"]), float(c["fallback_queries"]), float(c["tc_tiles"])], dtype=torch.float64, device="cuda")
+                            float(c["kernel_launches"]), float(c["fallback_queries"]), float(c["tc_tiles"]), float(c["prefilter_survivors"])], dtype=torch.float64, device="cuda")
         mx = tot.clone()
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -635,14 +637,16 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
             unit="queries/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
             higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
             config=dict(workload=args.workload, desc=cfg["desc"], rows=n, dim=dim, nlist=nlist, M=M, batch=nq, nprobe=nprobe,
-                        topk=topk, n_rerank=R, exact_rows=("device-cached fp32" if getattr(args, "exact_mode", "") == "cached" else "host-mapped fp32"), sharding="every list striped over %d ranks" % world,
+                        topk=topk, n_rerank=R, exact_rows=("device-cached fp32" if getattr(args, "exact_mode", "") == "cached" else "host-mapped fp32"), sharding="lists of at least %d x 4,096 rows striped over the %d ranks, shorter ones whole on rank (list mod %d)" % (world, world, world),
                         l2="inputs larger than L2 (codes %.2f GB per rank)" % (index["codes"].nbytes / 1e9)),
             e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
                      h2d_bytes_per_step=int(nq * dim * 4), d2h_bytes_per_step=int(nq * topk * 12),
                      pcie_gather_bytes_per_step=int(nq * width * dim * 4) if R > topk else 0),
             gpu_launches=int(tot[3].item()),
             roofline=roofline,
-            counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps)),
+            counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps),
+                          prefilter_survivors_per_step=tot[6].item() / max(1, args.steps), shared_cutoffs=bool(search.shared),
+                          batches_searched_again=int(search.redone)),
             stages_ms_rank0=stage_ms, host_numa_node_rank0=numa_node, result_checksum=checksum, clocks=clocks)
         emit(line)
     sess.close()

@@ -121,6 +121,15 @@ def lib():
     return _lib
 
 
+def load(path):
+    """Use another build of the library (e.g. build.build_nvtx_variant()'s) instead of libpsb.so; call before anything else."""
+    global _lib
+    _lib = C.CDLL(path)
+    _lib.psb_last_error.restype = C.c_char_p
+    _lib.psb_version.restype = C.c_char_p
+    return _lib
+
+
 def _check(status):
     if status != PSB_OK:
         msg = lib().psb_last_error().decode()

@@ -63,6 +63,29 @@ def build_library(verbose: bool = False, ptxas_info: bool = False) -> str:
     return LIB
 
 
+def build_nvtx_variant() -> str:
+    """libpsb_nvtx.so: the same library with NVTX ranges around the stages (-DPSB_USE_NVTX=1).  Only the session layer holds
+    ranges, so only that file is compiled again; load it with api.load(path)."""
+    build_library()
+    obj_dir = os.path.join(HERE, "_obj_nvtx")
+    os.makedirs(obj_dir, exist_ok=True)
+    src = os.path.join(CSRC, "session.cu")
+    obj = os.path.join(obj_dir, "session.o")
+    out = os.path.join(HERE, "libpsb_nvtx.so")
+    headers = [d for d in _deps() if not d.endswith(".cu")]
+    if _stale(obj, [src] + headers):
+        r = subprocess.run([NVCC] + FLAGS + ["-DPSB_USE_NVTX=1", "-I", INCLUDE, "-c", src, "-o", obj], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed (nvtx variant):\n%s\n%s" % (r.stdout, r.stderr))
+    objs = [obj if os.path.basename(s_) == "session.cu" else os.path.join(OBJ, os.path.basename(s_)[:-3] + ".o") for s_ in sources()]
+    if _stale(out, objs):
+        r = subprocess.run([NVCC, "-shared", "-o", out] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-ccbin", "g++", "-ldl"],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed (nvtx variant):\n%s\n%s" % (r.stdout, r.stderr))
+    return out
+
+
 def ensure_built() -> str:
     if _stale(LIB, _deps()):
         build_library()
@@ -71,3 +94,5 @@ def ensure_built() -> str:
 
 if __name__ == "__main__":
     print(build_library(verbose=True, ptxas_info="--ptxas" in sys.argv))
+    if "--nvtx" in sys.argv:
+        print(build_nvtx_variant())

@@ -9,6 +9,35 @@
 
 #include "../../include/psb.h"
 
+// NVTX ranges per stage, compiled in with -DPSB_USE_NVTX=1 (the names are the reference's stage names,
+// src/utils/nsight_nvtx.h:17-38 and src/search/ivfpq/pipeline/ivfpq_pipeline.cu:41-71).  NVTX 3 is header-only: without a
+// profiler attached a range costs one indirect call.
+#if defined(PSB_USE_NVTX) && PSB_USE_NVTX
+#include <nvtx3/nvToolsExt.h>
+#include <nvtx3/nvToolsExtCudaRt.h>
+namespace psb {
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
+inline void nvtx_name_stream(cudaStream_t s, const char* name) { nvtxNameCudaStreamA(s, name); }
+inline constexpr bool kNvtxCompiled = true;
+}  // namespace psb
+#else
+namespace psb {
+struct NvtxRange {
+    explicit NvtxRange(const char*) {}
+};
+inline void nvtx_name_stream(cudaStream_t, const char*) {}
+inline constexpr bool kNvtxCompiled = false;
+}  // namespace psb
+#endif
+#define PSB_RANGE_CAT2(a, b) a##b
+#define PSB_RANGE_CAT(a, b) PSB_RANGE_CAT2(a, b)
+#define PSB_RANGE(name) ::psb::NvtxRange PSB_RANGE_CAT(psb_nvtx_range_, __LINE__)(name)
+
 namespace psb {
 
 // ---- host: status and error text ---------------------------------------------------------------

@@ -680,7 +680,7 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
 extern "C" {
 
 const char* psb_last_error(void) { return last_error_ref().c_str(); }
-const char* psb_version(void) { return "paraselect-b200 0.1 (sm_100a)"; }
+const char* psb_version(void) { return kNvtxCompiled ? "paraselect-b200 0.1 (sm_100a, nvtx)" : "paraselect-b200 0.1 (sm_100a)"; }
 
 int psb_device_count(void) {
     int n = 0;
@@ -694,6 +694,7 @@ int psb_device_count(void) {
 }
 
 psb_status psb_session_create(const psb_index_view* index, const psb_options* options, psb_session** out) {
+    PSB_RANGE("ivfpq_prepare");
     if (!out) return fail(PSB_INVALID_ARGUMENT, "out is null");
     *out = nullptr;
     PSB_TRY(validate_index(index));
@@ -864,6 +865,7 @@ psb_status psb_session_set_stream(psb_session* s, void* stream, int background) 
 }
 
 psb_status psb_stage_coarse(psb_session* s, const float* d_queries, int nq, int nprobe, int* d_ids, float* d_dist) {
+    PSB_RANGE("coarse_search");
     if (!s || !d_queries || !d_ids) return fail(PSB_INVALID_ARGUMENT, "null argument");
     if (nprobe <= 0 || nprobe > s->nlist) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..nlist");
     if (nprobe > kMaxProbe) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 is not supported");
@@ -885,6 +887,7 @@ psb_status psb_stage_rotate_queries(psb_session* s, const float* d_queries, int 
 }
 
 psb_status psb_stage_build_lut(psb_session* s, const float* d_queries, int nq, float* d_lut) {
+    PSB_RANGE("pq_lut_build");
     if (!s || !d_queries || !d_lut) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
     return launch_build_lut(d_queries, nq, s->dim, s->codebook.as<float>(), s->m, s->k, d_lut, s->stream);
@@ -892,6 +895,7 @@ psb_status psb_stage_build_lut(psb_session* s, const float* d_queries, int nq, f
 
 psb_status psb_stage_build_lut_residual(psb_session* s, const float* d_queries, int nq, const int* d_probes, int nprobe,
                                         float* d_lut) {
+    PSB_RANGE("pq_lut_build");
     if (!s || !d_queries || !d_probes || !d_lut) return fail(PSB_INVALID_ARGUMENT, "null argument");
     if (nprobe <= 0 || nprobe > kMaxProbe) return fail(PSB_INVALID_ARGUMENT, "nprobe must be in 1..4096");
     PSB_CUDA(cudaSetDevice(s->device));
@@ -913,6 +917,7 @@ psb_status psb_stage_scan(psb_session* s, const float* d_lut, int nq, const int*
 
 psb_status psb_stage_scan_queries(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
                                   int nprobe, int stage1_k, int* d_rows, float* d_dist, int* d_count) {
+    PSB_RANGE("pq_adc_scan");
     if (!s || !d_probes || !d_rows) return fail(PSB_INVALID_ARGUMENT, "null argument");
     if (nprobe <= 0 || stage1_k <= 0) return fail(PSB_INVALID_ARGUMENT, "nprobe and stage1_k must be positive");
     if (nprobe > kMaxProbe || stage1_k > kMaxStage1) return fail(PSB_UNSUPPORTED_SHAPE, "nprobe above 4096 or stage1_k above 2048");
@@ -940,6 +945,7 @@ psb_status check_scan_stage(psb_session* s, const int* d_probes, int nprobe, int
 
 psb_status psb_stage_scan_sample(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
                                  int nprobe, int stage1_k, uint32_t* d_samples) {
+    PSB_RANGE("pq_adc_scan_sample");
     PSB_TRY(check_scan_stage(s, d_probes, nprobe, stage1_k));
     if (!d_samples) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
@@ -953,6 +959,7 @@ psb_status psb_stage_scan_sample(psb_session* s, const float* d_queries, const f
 psb_status psb_stage_scan_shared(psb_session* s, const float* d_queries, const float* d_lut, int nq, const int* d_probes,
                                  int nprobe, int stage1_k, const uint32_t* d_all_samples, int shards, int* d_rows, float* d_dist,
                                  int* d_count, float* d_cutoff, int64_t* d_rows_scanned) {
+    PSB_RANGE("pq_adc_scan");
     PSB_TRY(check_scan_stage(s, d_probes, nprobe, stage1_k));
     if (!d_all_samples || !d_rows || shards <= 0) return fail(PSB_INVALID_ARGUMENT, "null argument or no shards");
     PSB_CUDA(cudaSetDevice(s->device));
@@ -969,6 +976,7 @@ psb_status psb_stage_scan_shared(psb_session* s, const float* d_queries, const f
 psb_status psb_stage_rerank(psb_session* s, const float* d_queries, int nq, const int* d_candidates,
                             int candidate_count, int candidate_stride, const int* d_counts, int topk,
                             int* d_out_rows, float* d_out_dist) {
+    PSB_RANGE("pq_rerank");
     if (!s || !d_queries || !d_candidates || !d_out_rows || !d_out_dist) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
     return rerank_impl(s, d_queries, nq, d_candidates, candidate_count, candidate_stride, d_counts, topk, d_out_rows, d_out_dist);
@@ -976,6 +984,7 @@ psb_status psb_stage_rerank(psb_session* s, const float* d_queries, int nq, cons
 
 psb_status psb_stage_rerank_partial(psb_session* s, const float* d_queries, int nq, const int* d_candidates,
                                     int candidate_count, int candidate_stride, const int* d_counts, float* d_dist) {
+    PSB_RANGE("pq_rerank");
     if (!s || !d_queries || !d_candidates || !d_dist) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
     return rerank_impl(s, d_queries, nq, d_candidates, candidate_count, candidate_stride, d_counts, 1, nullptr, nullptr, d_dist);
@@ -993,6 +1002,7 @@ psb_status psb_stage_select_topk(psb_session* s, const float* d_dist, const int*
 }
 
 psb_status psb_stage_map_ids(psb_session* s, const int* d_rows, int64_t n, int64_t* d_indices) {
+    PSB_RANGE("pq_map_ids");
     if (!s || !d_rows || !d_indices) return fail(PSB_INVALID_ARGUMENT, "null argument");
     PSB_CUDA(cudaSetDevice(s->device));
     return launch_map_ids(d_rows, n, s->reordered.as<long long>(), s->row_map(), reinterpret_cast<long long*>(d_indices), s->stream);
@@ -1051,6 +1061,7 @@ struct StageTimes { double coarse = 0, lut = 0, scan = 0, rerank = 0, map = 0; }
 // selection and id map of sub-batch i-1 run on a second stream, so the transfer hides behind the scan.
 psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, int n, int nprobe, int topk, int stage1_k,
                          bool rerank, long long* d_ids, float* d_dist, int* d_probes, StageTimes* times) {
+    PSB_RANGE("ivfpq_batch");
     cudaStream_t st = s->stream;
     const bool overlap = overlap_enabled(s, n, rerank);
     // Staged transport, overlapped: a host worker thread takes each sub-batch's candidates as soon as its scan has finished,
@@ -1128,6 +1139,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         worker = std::thread([&]() {
             cudaSetDevice(s->device);
             auto process = [&](const Job& j) -> psb_status {
+                PSB_RANGE("pq_rerank");
                 PSB_CUDA(cudaEventSynchronize(j.ready));
                 const int* cand_d = s->cand_rows.as<int>() + (size_t)j.p0 * stage1_k;
                 const int* cnt_d = s->cand_count.as<int>() + j.p0;
@@ -1183,7 +1195,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     // Coarse stage for the whole batch first: one large GEMM is more efficient than four small ones, and the tensor-core
     // kernel (a full SM's shared and tensor memory per CTA) then never has to share SMs with the transfer stream.
     if (times) rc = tm_s.mark(st);
-    if (rc == PSB_OK) rc = coarse_exact(s, dq, n, nprobe, d_probes, nullptr);
+    if (rc == PSB_OK) { PSB_RANGE("coarse_search"); rc = coarse_exact(s, dq, n, nprobe, d_probes, nullptr); }
     // OPQ index: the PQ side works on the rotated queries (counted with the coarse stage's time)
     const float* dq_pq = dq;
     if (rc == PSB_OK && s->opq.p) {
@@ -1204,6 +1216,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         ScanWorkspace sws;
         if (rc == PSB_OK) rc = s->timed_scan_ws(&sws);
         if (rc == PSB_OK && !table_free) {
+            PSB_RANGE("pq_lut_build");
             if (residual && residual_tables_fused(sws, s->m, s->k)) {  // fp32 and fp16 tables in one kernel
                 rc = launch_build_tables_residual(q, m, s->dim, probes, nprobe, s->centroids.as<float>(), s->nlist,
                                                   s->codebook.as<float>(), s->m, s->k, s->cb_maxnorm.as<float>(), s->lut.as<float>(),
@@ -1217,8 +1230,11 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
             }
         }
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
-        if (rc == PSB_OK) rc = launch_scan(s->scan_index(), sws, table_free ? nullptr : s->lut.as<float>(), m, probes, nprobe, stage1_k,
-                                           rows_out, dist_out, cnt_out, s->sm_count, st, q);
+        if (rc == PSB_OK) {
+            PSB_RANGE("pq_adc_scan");
+            rc = launch_scan(s->scan_index(), sws, table_free ? nullptr : s->lut.as<float>(), m, probes, nprobe, stage1_k,
+                             rows_out, dist_out, cnt_out, s->sm_count, st, q);
+        }
         if (rc == PSB_OK && times) rc = tm_s.mark(st);
         if (rc != PSB_OK) break;
         if (staged_overlap) {  // hand the sub-batch to the worker: candidates to the host, an event marks them ready
@@ -1243,14 +1259,17 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         s->stream = sx;  // rerank_impl and the launchers below run on s->stream
         if (times) rc = tm_x.mark(sx);
         if (rc == PSB_OK && rerank) {
+            PSB_RANGE("pq_rerank");
             const unsigned char* qe = static_cast<const unsigned char*>(dq_exact) + (size_t)p0 * s->dim * s->exact_elem;
             rc = rerank_impl(s, qe, m, rows_out, stage1_k, stage1_k, cnt_out, topk, s->out_rows.as<int>() + (size_t)p0 * topk,
                              d_dist + (size_t)p0 * topk);
         }
         if (rc == PSB_OK && times) rc = tm_x.mark(sx);
-        if (rc == PSB_OK)
+        if (rc == PSB_OK) {
+            PSB_RANGE("pq_map_ids");
             rc = launch_map_ids(s->out_rows.as<int>() + (size_t)p0 * topk, (long long)m * topk, s->reordered.as<long long>(),
                                 s->row_map(), d_ids + (size_t)p0 * topk, sx);
+        }
         if (rc == PSB_OK && times) rc = tm_x.mark(sx);
         s->stream = keep;
     }
@@ -1303,6 +1322,7 @@ psb_status psb_session_search_device(psb_session* s, const float* d_queries, con
 
 psb_status psb_session_search(psb_session* s, const psb_query_batch_view* queries, const psb_search_params* params,
                               const psb_search_output_view* output, psb_stats* stats) {
+    PSB_RANGE("ivfpq_search");
     if (!s) return fail(PSB_INVALID_ARGUMENT, "session is null");
     PSB_TRY(validate_params(s, queries, params, output));
     PSB_CUDA(cudaSetDevice(s->device));
@@ -1476,6 +1496,7 @@ psb_status psb_flat_session_search_device(psb_flat_session* s, const float* d_qu
 
 psb_status psb_flat_session_search(psb_flat_session* s, const psb_query_batch_view* queries, const psb_search_params* params,
                                    const psb_search_output_view* output, psb_stats* stats) {
+    PSB_RANGE("ivfflat_search");
     PSB_TRY(flat_check(s, params));
     if (!queries || !output) return fail(PSB_INVALID_ARGUMENT, "null query or output view");
     if (queries->count < 0 || queries->dim != s->dim) return fail(PSB_INVALID_ARGUMENT, "query dim does not match the index");

@@ -123,3 +123,13 @@ def test_index_build_glue_layout_and_reorder():
     bad = rid.copy(); bad[0] = bad[1]
     with pytest.raises(api.InvalidArgument):
         api.reorder_rows(rows, bad)
+
+
+def test_nvtx_variant_builds_and_exports_the_same_symbols(lib):
+    """-DPSB_USE_NVTX=1: stage ranges compiled in (NVTX 3 is header-only, nothing to link); same C ABI."""
+    path = build.build_nvtx_variant()
+    nv = C.CDLL(path)
+    nv.psb_version.restype = C.c_char_p
+    assert b"nvtx" in nv.psb_version() and b"nvtx" not in lib.psb_version()
+    for name in api.EXPORTS:
+        assert hasattr(nv, name), name
