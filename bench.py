@@ -316,7 +316,8 @@ def main():
                          "headline metric names: an extra data point); hybrid = staged and mapped at once, --zero-copy-pct of every "
                          "sub-batch through the kernel")
     ap.add_argument("--zero-copy-pct", type=int, default=0, help="hybrid transport: share of each sub-batch gathered by the kernel (0 = library default)")
-    ap.add_argument("--reserve-sms", type=int, default=8, help="N > 1: SMs the scan's persistent grid leaves to the collectives")
+    ap.add_argument("--reserve-sms", type=int, default=24, help="N > 1: SMs the scan's persistent grid leaves to the exchange half "
+                    "(the PCIe gather of the exact rows runs on that many SMs of its own, the collectives beside it)")
     ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
     ap.add_argument("--local-cutoffs", action="store_true", help="N > 1: every rank places its admission cutoffs on its own rows only "
                     "(default: on the rows of all ranks, from exchanged sample records)")
@@ -606,6 +607,9 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
         search.step(dq, profile=True)
         torch.cuda.synchronize()
         stage_ms = search.stage_times()
+        search.step(dq, trace=True)   # one pipelined step with events around the halves of every sub-batch: shows what overlaps
+        torch.cuda.synchronize()
+        timeline = search.timeline()
         clocks = sampler.stop()
         torch.cuda.synchronize()
         # totals over ranks
@@ -647,7 +651,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
             counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps),
                           prefilter_survivors_per_step=tot[6].item() / max(1, args.steps), shared_cutoffs=bool(search.shared),
                           batches_searched_again=int(search.redone)),
-            stages_ms_rank0=stage_ms, host_numa_node_rank0=numa_node, result_checksum=checksum, clocks=clocks)
+            stages_ms_rank0=stage_ms, pipeline_timeline_ms_rank0=timeline, host_numa_node_rank0=numa_node, result_checksum=checksum, clocks=clocks)
         emit(line)
     sess.close()
     dist.barrier()

@@ -229,10 +229,11 @@ struct RowMap {
 };
 // Copies the candidate rows held here (fp32 or u8, elem_bytes 4 or 1) from src (device-visible: mapped host or
 // device) to stage [nq][candidate_count][dim].  Candidates are global rows.  compact_ctas > 0: the kernel runs beside a scan
-// on another stream and is confined to that many fat CTAs.
+// on another stream as that many lean CTAs; owned_sms > 0 (takes precedence): as that many CTAs that each keep an SM to
+// themselves.
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
-                              void* d_stage, cudaStream_t s, int sm_count, int compact_ctas = 0);
+                              void* d_stage, cudaStream_t s, int sm_count, int compact_ctas = 0, int owned_sms = 0);
 // d_out_dist [nq][candidate_count]: exact distance of each staged candidate, +inf for rows not held here.
 psb_status launch_rerank_score(const void* d_stage, const RowMap& mp, int dim, int elem_bytes, const void* d_queries,
                                const int* d_candidates, int nq, int candidate_count, int candidate_stride,

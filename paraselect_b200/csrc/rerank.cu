@@ -44,6 +44,7 @@ __device__ __forceinline__ long long local_row(const RowMap& mp, long long r) {
 // to a local row (for a striped shard that is a binary search of 16 dependent loads - done for 32 candidates at once), then
 // the warp copies the rows four at a time, all four rows' loads issued before the first store, so that a few hundred KB
 // of PCIe reads stay in flight even on a small grid.
+template <int U = 4>
 __device__ __forceinline__ void gather_rows_body(const unsigned char* __restrict__ src, const RowMap& mp, int row_bytes,
                                                  const int* __restrict__ cand, int nq, int candidate_count, int candidate_stride,
                                                  const int* __restrict__ counts, unsigned char* __restrict__ stage) {
@@ -63,19 +64,26 @@ __device__ __forceinline__ void gather_rows_body(const unsigned char* __restrict
             if (i < cand_count(counts, q, candidate_count)) mine = local_row(mp, cand[(size_t)q * candidate_stride + i]);
         }
         if (vec16 && n16 <= 32) {
+            // The rows held here, four at a time whatever their positions among the 32 candidates: on a shard most candidates
+            // belong to other shards, and the reads in flight must not thin out with them.
+            unsigned present = __ballot_sync(0xffffffffu, mine >= 0);
 #pragma unroll 1
-            for (int k0 = 0; k0 < 32; k0 += 4) {
-                long long r[4];
+            while (present) {
+                int at[U];
+                long long r[U];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) r[u] = __shfl_sync(0xffffffffu, mine, k0 + u);
-                if ((r[0] & r[1] & r[2] & r[3]) < 0) continue;  // all four absent (-1): uniform
-                uint4 v[4];
+                for (int u = 0; u < U; ++u) {
+                    at[u] = present ? __ffs(present) - 1 : -1;   // uniform across the warp
+                    if (present) present &= present - 1;
+                    r[u] = __shfl_sync(0xffffffffu, mine, at[u] < 0 ? 0 : at[u]);
+                }
+                uint4 v[U];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (r[u] >= 0 && lane < n16) v[u] = reinterpret_cast<const uint4*>(src + (size_t)r[u] * row_bytes)[lane];
+                for (int u = 0; u < U; ++u)
+                    if (at[u] >= 0 && lane < n16) v[u] = reinterpret_cast<const uint4*>(src + (size_t)r[u] * row_bytes)[lane];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (r[u] >= 0 && lane < n16) reinterpret_cast<uint4*>(stage + (size_t)(base + k0 + u) * row_bytes)[lane] = v[u];
+                for (int u = 0; u < U; ++u)
+                    if (at[u] >= 0 && lane < n16) reinterpret_cast<uint4*>(stage + (size_t)(base + at[u]) * row_bytes)[lane] = v[u];
             }
         } else {
             for (int k = 0; k < 32; ++k) {
@@ -109,6 +117,18 @@ __global__ void __launch_bounds__(256, 6) k_gather_rows_beside(const unsigned ch
                                                                int candidate_stride, const int* __restrict__ counts,
                                                                unsigned char* __restrict__ stage) {
     gather_rows_body(src, mp, row_bytes, cand, nq, candidate_count, candidate_stride, counts, stage);
+}
+
+// The same gather on SMs of its own: CTAs of 1,024 threads that also claim (without using it) nearly all the shared memory of
+// an SM, so that no kernel with a shared-memory footprint - the scan, the cutoff sampling, the selections - shares an SM with
+// them.  Reads of host memory stay in flight for microseconds; next to another kernel's warps they held up that kernel's own
+// memory traffic (its stages ran at half speed), on separate SMs they do not.  Eight such CTAs keep ~800 KB of reads in
+// flight.
+__global__ void __launch_bounds__(1024, 1) k_gather_rows_owned(const unsigned char* __restrict__ src, RowMap mp, int row_bytes,
+                                                               const int* __restrict__ cand, int nq, int candidate_count,
+                                                               int candidate_stride, const int* __restrict__ counts,
+                                                               unsigned char* __restrict__ stage) {
+    gather_rows_body<8>(src, mp, row_bytes, cand, nq, candidate_count, candidate_stride, counts, stage);   // eight rows per warp in flight
 }
 
 // fp32 squared L2 by a half-warp (16 lanes), bit-identical to the AVX-512 kernel's order.
@@ -274,11 +294,20 @@ k_merge(const int* __restrict__ rows, const float* __restrict__ dist, int parts,
 
 psb_status launch_gather_rows(const void* src, const RowMap& mp, int dim, int elem_bytes, const int* d_candidates,
                               int nq, int candidate_count, int candidate_stride, const int* d_counts,
-                              void* d_stage, cudaStream_t s, int sm_count, int compact_ctas) {
+                              void* d_stage, cudaStream_t s, int sm_count, int compact_ctas, int owned_sms) {
     if (nq <= 0) return PSB_OK;
     const long long total = (long long)nq * candidate_count;
     PSB_TRY(prefer_max_shared(k_gather_rows));
-    if (compact_ctas > 0) {
+    if (owned_sms > 0) {
+        constexpr int kOwnedSmem = 200 * 1024;   // claimed, not used: keeps every kernel that needs shared memory off the SM
+        PSB_TRY(prefer_max_shared(k_gather_rows_owned));
+        PSB_CUDA(cudaFuncSetAttribute(k_gather_rows_owned, cudaFuncAttributeMaxDynamicSharedMemorySize, kOwnedSmem));
+        long long blocks = (total * 32 + 1023) / 1024;
+        if (blocks > owned_sms) blocks = owned_sms;
+        k_gather_rows_owned<<<(unsigned)blocks, 1024, kOwnedSmem, s>>>(static_cast<const unsigned char*>(src), mp, dim * elem_bytes,
+                                                                        d_candidates, nq, candidate_count, candidate_stride, d_counts,
+                                                                        static_cast<unsigned char*>(d_stage));
+    } else if (compact_ctas > 0) {
         // Beside a scan kernel on the other stream of the overlapped pipeline: small lean CTAs on every SM (compact_ctas of them).
         PSB_TRY(prefer_max_shared(k_gather_rows_beside));
         long long blocks = (total * 32 + 127) / 128;

@@ -659,10 +659,14 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
     if (staged_mode(s)) {
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
+        // Beside a scan on the other stream the gather runs on SMs of its own: the ones the scan's persistent grid leaves free
+        // (reserve_sms), or gather_ctas lean CTAs spread over all SMs when the caller asks for that.
+        const bool beside = s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream);
+        const bool host_rows = s->opt.exact_mode == PSB_EXACT_HOST_MAPPED || s->opt.exact_mode == PSB_EXACT_HOST_HYBRID;
+        const int owned = beside && host_rows && s->opt.gather_ctas == 0 ? (s->opt.reserve_sms > 0 ? s->opt.reserve_sms : 8) : 0;
         PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand, nq, width, stride, d_counts,
                                    s->stage.p, s->stream, s->sm_count,
-                                   (s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream))
-                                       ? (s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count) : 0));
+                                   beside ? (s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count) : 0, owned));
     }
     float* score = d_score;
     if (!score) {

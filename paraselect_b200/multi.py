@@ -109,12 +109,18 @@ class SessionEngine:
 class ShardedSearch:
     def __init__(self, engine, dist, world, nq, dim, M, K, nprobe, topk, width, torch, rerank=True, parts=1, shared_cutoff=True):
         self.e, self.dist, self.world, self.torch = engine, dist, world, torch
+        self.spans = None
         # Cutoffs placed on all shards' rows: every rank then admits about 1 / world of what an unsharded scan admits instead of
         # looking for `width` rows of its own.  The merged candidates are checked after every exchange; a batch in which a
         # cutoff turned out too low (practically never) is searched again with per-shard cutoffs (self.redone counts them).
         self.shared = bool(shared_cutoff) and world > 1 and getattr(engine, "shared_cutoff", False)
         self.rank = dist.get_rank() if world > 1 else 0
         self.redone = 0
+        # The sample records travel on a communicator of their own.  On the default one their all-gather would queue behind
+        # the exchange half of the previous sub-batch (a process group runs its collectives one after the other), and the scan
+        # that waits for the records would lose its overlap with that exchange.  Every rank issues the collectives of both
+        # groups in the same order, and nothing a collective waits for depends on the other group.
+        self.front_group = dist.new_group(ranks=list(range(world))) if self.shared else None
         self.parts, self.aux = parts, None
         self.nq, self.nprobe, self.topk, self.width, self.rerank = nq, nprobe, topk, width, rerank
         t = torch
@@ -166,7 +172,7 @@ class ShardedSearch:
             mine = self.smp.view(-1)[:m * words].view(m, words)
             every = self.smp_all.view(-1)[:w * m * words].view(w, m, words)
             e.scan_sample(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, mine)
-            self.dist.all_gather_into_tensor(every.view(w * m, words), mine)
+            self.dist.all_gather_into_tensor(every.view(w * m, words), mine, group=self.front_group)
             e.scan_shared(dq[sl], self.lut[:m], m, self.probes[sl], self.nprobe, self.width, every, w, self.l_rows[sl], self.l_dist[sl],
                           self.l_cnt[sl], self.cut[sl], self.n_scan[sl])
         else:
@@ -236,7 +242,27 @@ class ShardedSearch:
             self.dist.all_reduce(self.o_ids, op=self.dist.ReduceOp.MAX)
         self._mark("all_reduce_max")
 
-    def step(self, dq, profile=False, parts=None, shared=None):
+    def _span(self, name, fn):
+        """Runs fn between two events of the current stream when a timeline is being recorded (step(trace=True))."""
+        if self.spans is None:
+            return fn()
+        a, b = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn()
+        b.record()
+        self.spans.append((name, a, b))
+        return out
+
+    def timeline(self):
+        """(name, start ms, end ms) of the halves of the last step(trace=True), relative to its first event."""
+        sp = self.spans or []
+        if not sp:
+            return []
+        t0 = sp[0][1]
+        return [(n, round(t0.elapsed_time(a), 3), round(t0.elapsed_time(b), 3)) for n, a, b in sp]
+
+    def step(self, dq, profile=False, parts=None, shared=None, trace=False):
+        self.spans = [] if trace else None
         """One batch.  parts > 1 cuts the batch into sub-batches; on an engine with streams the exchange half of
         sub-batch i (collectives, PCIe rerank) then runs on a second stream beside the scan of sub-batch i + 1.
         profile=True runs the batch serially in one piece and records per-stage times."""
@@ -279,12 +305,12 @@ class ShardedSearch:
         aux.wait_stream(main)  # the second stream starts after everything already queued
         for q0, q1 in zip(cuts[:-1], cuts[1:]):
             m = q1 - q0
-            self._front(dq, q0, m)
+            self._span("front %d" % q0, lambda: self._front(dq, q0, m))
             aux.wait_stream(main)
             e.set_stream(aux.cuda_stream, True)
             try:
                 with t.cuda.stream(aux):
-                    self._back(dq, q0, m)
+                    self._span("back %d" % q0, lambda: self._back(dq, q0, m))
             finally:
                 e.set_stream(None, False)
         main.wait_stream(aux)
