@@ -160,9 +160,10 @@ typedef struct psb_options {
                            1 = equal sub-batches, 2 = a short last sub-batch (32/32/26/10 %) */
     int gather_ctas;    /* 128-thread CTAs of the PCIe row-gather kernel when it runs beside a scan (default: two per SM) */
     int tc_min_visitors;/* lists with fewer visiting queries than this stay with the SIMT scan (default 1: none do) */
-    /* Test hooks of the time-out path of the tensor-core scan (leave 0): test_wait_limit = polls before a device-side wait
-       gives up; test_skip_mma = 1 makes the issuing warp skip its tcgen05.mma so that every waiting role runs into that limit
-       (nothing is left in flight; the kernel frees its tensor memory and returns; the call reports PSB_TIMEOUT). */
+    /* Test hooks of the time-out paths of the tensor-core kernels (leave 0): test_wait_limit = polls before a device-side wait
+       gives up; test_skip_mma bit 0 makes the scan's issuing warp skip its tcgen05.mma, bit 1 makes the coarse kernel's producer
+       skip its loads - with nothing left in flight every waiting role then runs into the limit, the kernel frees its tensor
+       memory and returns, and the call reports PSB_TIMEOUT. */
     int test_wait_limit;
     int test_skip_mma;
     int zero_copy_pct;  /* PSB_EXACT_HOST_HYBRID: share of each sub-batch gathered by the kernel, 1..99 (0 = 40) */

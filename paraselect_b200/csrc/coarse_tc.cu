@@ -70,6 +70,9 @@ struct TcArgs {
     int mwords;             // ntiles * TCOL / 32
     int* status;            // [1] != 0 after a bounded wait gave up
     int cblocks, qtiles;    // work = cblocks (512 centroids each) x qtiles (128 queries each) tile pairs
+    int wait_limit;         // polls before a wait gives up (0: kWaitLimit)
+    int skip_loads;         // test hook of the time-out path: the producer issues no load at all, so nothing is in flight when
+                            // the other roles give up
 };
 
 // Work split: the (centroid block, query tile) pairs are numbered block-major and CTA b takes the contiguous range
@@ -137,22 +140,23 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
     long long l0, l1;
     cta_range(a, l0, l1);
     const int nunits = seg_count(a, l0, l1);
+    const int wl = a.wait_limit > 0 ? a.wait_limit : kWaitLimit;
     int failed = 0;
 
     if (warp == kEpiWarps) {
-        if (lane == 0) {
+        if (lane == 0 && !a.skip_loads) {
             uint32_t it = 0, un = 0;  // query tiles issued, units issued
             for (; (int)un < nunits && !failed; ++un) {
                 int cblock, t0, t1;
                 seg_get(a, l0, l1, (int)un, cblock, t0, t1);
-                if (!mbar_wait(&b_empty, (un & 1u) ^ 1u)) { failed = 1; break; }
+                if (!mbar_wait(&b_empty, (un & 1u) ^ 1u, wl)) { failed = 1; break; }
                 mbar_expect_tx(&b_full, (uint32_t)(2 * b_bytes));
                 for (int h = 0; h < 2; ++h)
                     for (int ka = 0; ka < a.katoms; ++ka)
                         tma_load_2d(s_b + h * b_bytes + (size_t)ka * TCOL * 128, &map_c, ka * KATOM, cblock * kBlockCols + h * TCOL, &b_full);
                 for (int t = t0; t < t1; ++t, ++it) {
                     const uint32_t st = it % kStagesA;
-                    if (!mbar_wait(&a_empty[st], ((it / kStagesA) & 1u) ^ 1u)) { failed = 1; break; }
+                    if (!mbar_wait(&a_empty[st], ((it / kStagesA) & 1u) ^ 1u, wl)) { failed = 1; break; }
                     mbar_expect_tx(&a_full[st], (uint32_t)a_bytes);
                     for (int ka = 0; ka < a.katoms; ++ka)
                         tma_load_2d(s_a + st * a_bytes + (size_t)ka * TQ * 128, &map_q, ka * KATOM, t * TQ, &a_full[st]);
@@ -166,12 +170,12 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 int cblock, t0, t1;
                 seg_get(a, l0, l1, (int)un, cblock, t0, t1);
                 (void)cblock;
-                if (!mbar_wait(&b_full, un & 1u)) { failed = 1; break; }
+                if (!mbar_wait(&b_full, un & 1u, wl)) { failed = 1; break; }
                 for (int t = t0; t < t1 && !failed; ++t, ++it) {
                     const uint32_t st = it % kStagesA;
-                    if (!mbar_wait(&a_full[st], (it / kStagesA) & 1u)) { failed = 1; break; }
+                    if (!mbar_wait(&a_full[st], (it / kStagesA) & 1u, wl)) { failed = 1; break; }
                     for (int h = 0; h < 2; ++h) {
-                        if (!mbar_wait(&acc_empty[h], (nacc[h] & 1u) ^ 1u)) { failed = 1; break; }
+                        if (!mbar_wait(&acc_empty[h], (nacc[h] & 1u) ^ 1u, wl)) { failed = 1; break; }
                         tc_fence_after();
                         const uint32_t sa = smem_u32(s_a + st * a_bytes), sb = smem_u32(s_b + h * b_bytes);
                         for (int ka = 0; ka < a.katoms; ++ka)
@@ -209,7 +213,7 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                 }
                 const bool partial = (cblock + 1) * kBlockCols > a.nlist;  // block reaches past the last centroid
                 for (int h = 0; h < 2; ++h) {
-                    if (!mbar_wait(&acc_full[h], nacc[h] & 1u)) { failed = 1; break; }
+                    if (!mbar_wait(&acc_full[h], nacc[h] & 1u, wl)) { failed = 1; break; }
                     ++nacc[h];
                     tc_fence_after();
                     uint32_t r0[32], r1[32];
@@ -546,6 +550,7 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     while ((1 << a.lg_group) < group) ++a.lg_group;
     a.nprobe = nprobe; a.cn2 = ix.cn2; a.qnorm = ws.qnorm; a.cmax = ix.cmax; a.gmin = ws.gmin; a.seltop = ws.seltop;
     a.mask = reinterpret_cast<uint32_t*>(ws.cand); a.mwords = coarse_tc_mask_words(ix.nlist); a.status = ws.status;
+    a.wait_limit = ws.test_wait_limit; a.skip_loads = ws.test_skip_loads;
     const size_t smem = (size_t)katoms * (kStagesA * TQ + 2 * TCOL) * 128 + 1024;
     PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

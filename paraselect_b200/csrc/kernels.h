@@ -54,6 +54,7 @@ struct CoarseTcWorkspace {
     int* n_fail;     // [2]: count, cursor
     int* status;     // [1]
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};  // optional: begin/end of GEMM pass 1 and pass 2
+    int test_wait_limit = 0, test_skip_loads = 0;              // test hooks of the time-out path (0: off)
 };
 int coarse_tc_padded_dim(int dim);
 int coarse_tc_tiles(int nlist);

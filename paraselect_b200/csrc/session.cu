@@ -349,7 +349,7 @@ struct psb_session {
         w.reserve_ctas = opt.reserve_sms;
         w.seed_sigma = opt.seed_sigma;
         w.item_off_tc = item_off_tc.as<long long>(); w.work_cursor_tc = sc + 11; w.tc_status = reinterpret_cast<int*>(sc + 12);
-        w.tc_min_visitors = opt.tc_min_visitors; w.tc_wait_limit = opt.test_wait_limit; w.tc_skip_mma = opt.test_skip_mma;
+        w.tc_min_visitors = opt.tc_min_visitors; w.tc_wait_limit = opt.test_wait_limit; w.tc_skip_mma = opt.test_skip_mma & 1;
         w.cap_queries = ws_scan_queries; w.cap_tables = ws_scan_tables;
         return w;
     }
@@ -492,6 +492,7 @@ psb_status coarse_exact(psb_session* s, const float* d_queries, int nq, int npro
     if (mode != 1 && tc_ok) {
         PSB_TRY(s->tc_work.ensure(nq, s->nlist, s->dim, nprobe, s->stream));
         CoarseTcWorkspace tw = s->tc_work.view();
+        tw.test_wait_limit = s->opt.test_wait_limit; tw.test_skip_loads = (s->opt.test_skip_mma & 2) ? 1 : 0;
         if (s->opt.time_kernels) {
             for (int i = 0; i < 4; ++i) PSB_CUDA(cudaEventCreate(&tw.ev[i]));
             s->gemm_events.emplace_back(tw.ev[0], tw.ev[1]);

@@ -32,8 +32,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false after kWaitLimit unsuccessful polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (int i = 0; i < kWaitLimit; ++i)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = kWaitLimit) {
+    for (int i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

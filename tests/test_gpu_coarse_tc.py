@@ -125,3 +125,24 @@ def test_three_call_lloyd_iteration_equals_kmeans_train(psb):
     assert np.allclose(obj_a, obj_b, rtol=1e-9)
     assert np.allclose(cen_a.cpu().numpy(), cen_b.cpu().numpy(), rtol=1e-6, atol=1e-7)
     assert np.mean(assign_a.cpu().numpy() == assign_b.cpu().numpy()) > 0.9999
+
+
+def test_coarse_tc_bounded_wait_gives_up_cleanly(psb):
+    """The time-out path of the coarse kernel: its producer lane told to issue no load at all (nothing is left in flight), the
+    MMA lane and the epilogue warps run into the shortened poll limit, the kernel frees its tensor memory and returns, and the
+    call reports PSB_TIMEOUT.  The device stays usable: the next session's coarse stage gives the right answer."""
+    import torch
+    import synth
+    ix = synth.make_index(30000, 64, 2048, 8, seed=71)
+    q = synth.make_queries(ix, 300, seed=72)
+    out = torch.empty((300, 16), dtype=torch.int32, device="cuda")
+    with psb.Session(dict(ix, vectors=None), coarse_mode=2, test_skip_mma=2, test_wait_limit=4096) as s:
+        s.stage_coarse(torch.from_numpy(q).cuda(), 300, 16, out)
+        with pytest.raises(psb.PsbError) as e:
+            s.sync()
+        assert e.value.status == 7
+    with psb.Session(dict(ix, vectors=None), coarse_mode=2) as s:
+        s.stage_coarse(torch.from_numpy(q).cuda(), 300, 16, out)
+        s.sync()
+        want, _ = oracle.coarse(q, ix["centroids"], 16)
+        assert np.array_equal(out.cpu().numpy(), want)
