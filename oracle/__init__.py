@@ -18,6 +18,7 @@ ORACLE_SO = os.path.join(_HERE, "_build", "libpsb_oracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libpsb_ref.so")
 REF_TRAIN_SO = os.path.join(_HERE, "_ref", "libpsb_ref_train.so")
 REF_ROWCORR_SO = os.path.join(_HERE, "_ref", "libpsb_ref_rowcorr.so")
+REF_CACHE_SO = os.path.join(_HERE, "_ref", "libpsb_ref_cache.so")
 _lib = None
 _ref = None
 _ref_train = None
@@ -473,3 +474,87 @@ def ref_rc_encode(scale, offset, v):
 
 def ref_rc_decode(scale, offset, code):
     return float(ref_rowcorr().ref_rc_decode(C.c_float(scale), C.c_float(offset), C.c_uint16(code)))
+
+
+# ---------------------------------------------------------------- the reference's cache classes (oracle/ref_cache_harness.cpp)
+_ref_cache = None
+
+
+def have_ref_cache() -> bool:
+    return os.path.exists(REF_CACHE_SO)
+
+
+def ref_cache():
+    global _ref_cache
+    if _ref_cache is None:
+        _ref_cache = C.CDLL(REF_CACHE_SO)
+    return _ref_cache
+
+
+def ref_cluster_save(root, dataset, centroids, reordered, offsets, recipe_json):
+    cen = _c(centroids, np.float32); ids = _c(reordered, np.int64); off = _c(offsets, np.int64)
+    counts = np.diff(off).astype(np.int32)
+    rc = ref_cache().ref_cluster_save(root.encode(), dataset.encode(), ids.size, cen.shape[0], cen.shape[1], recipe_json.encode(),
+                                      _ptr(cen), _ptr(ids), _ptr(counts), _ptr(off))
+    if rc:
+        raise RuntimeError("reference ClusterCache::save failed")
+
+
+def ref_cluster_load(root, dataset, n, nlist, dim, recipe_json, layout_id=""):
+    """None on a miss, else dict(entry, layout_id, centroids, reordered_ids, counts, offsets)."""
+    cen = np.empty((nlist, dim), np.float32); ids = np.empty(n, np.int64)
+    counts = np.empty(nlist, np.int32); off = np.empty(nlist + 1, np.int64)
+    entry = C.create_string_buffer(4096); layout = C.create_string_buffer(4096)
+    rc = ref_cache().ref_cluster_load(root.encode(), dataset.encode(), n, nlist, dim, recipe_json.encode(), layout_id.encode(),
+                                      _ptr(cen), _ptr(ids), _ptr(counts), _ptr(off), entry, layout, 4096)
+    if rc == 2:
+        return None
+    if rc:
+        raise RuntimeError("reference ClusterCache::try_load failed")
+    return dict(entry=entry.value.decode(), layout_id=layout.value.decode(), centroids=cen, reordered_ids=ids, counts=counts, offsets=off)
+
+
+def ref_pq_save(root, dataset, n, dim, nlist, layout_id, codebook, codes, iters, residual, train_rows=0):
+    cb = _c(codebook, np.float32); cd = _c(codes, np.uint8)
+    rc = ref_cache().ref_pq_save(root.encode(), dataset.encode(), n, dim, nlist, layout_id.encode(), cb.shape[0], cb.shape[1], iters,
+                                 int(residual), train_rows, _ptr(cb), _ptr(cd))
+    if rc:
+        raise RuntimeError("reference ResidualPQCache::save failed")
+
+
+def ref_pq_load(root, dataset, n, dim, nlist, layout_id, m, k, iters, residual, train_rows=0):
+    cb = np.empty((m, k, dim // m), np.float32); cd = np.empty((n, m), np.uint8)
+    entry = C.create_string_buffer(4096)
+    rc = ref_cache().ref_pq_load(root.encode(), dataset.encode(), n, dim, nlist, layout_id.encode(), m, k, iters, int(residual), train_rows,
+                                 _ptr(cb), _ptr(cd), entry, 4096)
+    if rc == 2:
+        return None
+    if rc:
+        raise RuntimeError("reference ResidualPQCache::try_load failed")
+    return dict(entry=entry.value.decode(), codebook=cb, codes=cd)
+
+
+def ref_storage_id(manifest_json):
+    out = C.create_string_buffer(256)
+    if ref_cache().ref_storage_id(manifest_json.encode(), out, 256):
+        raise RuntimeError("reference storage_id failed")
+    return out.value.decode()
+
+
+def ref_manifest_matches(actual_json, expected_json):
+    return int(ref_cache().ref_manifest_matches(actual_json.encode(), expected_json.encode()))
+
+
+def ref_opq_save(cache_dir, dataset, n, train_n, rotation, m, k, opq_iters, pq_iters, seed):
+    """The reference's save_opq_rotation_cache under its own key; returns the key."""
+    rot = _c(rotation, np.float32)
+    key = C.create_string_buffer(1024)
+    if ref_train().psbref_opq_save(cache_dir.encode(), dataset.encode(), n, train_n, rot.shape[0], m, k, opq_iters, pq_iters, C.c_uint(seed),
+                                   _ptr(rot), key, 1024):
+        raise RuntimeError("reference save_opq_rotation_cache failed")
+    return key.value.decode()
+
+
+def ref_opq_load(cache_dir, key, dim):
+    rot = np.empty((dim, dim), np.float32)
+    return rot if ref_train().psbref_opq_load(cache_dir.encode(), key.encode(), dim, _ptr(rot)) == 0 else None

@@ -10,6 +10,7 @@
 #include "cpu/clustering/cpu_kmeans.h"
 #include "quantization/pq/pq_quantizer.cuh"
 #include "quantization/pq/pq_kmeans.h"
+#include "transform/opq_cache.cuh"
 
 #include <cstdint>
 #include <cstring>
@@ -77,6 +78,25 @@ int psbref_pq_init_rows(int n, int K, unsigned seed, int* rows) {
 // pq_kmeans_subspace itself on one sub-space.
 int psbref_pq_kmeans_subspace(const float* sub, int n, int dsub, int K, int iters, unsigned seed, float* out) {
     ivf::pq_kmeans_subspace(sub, n, dsub, K, iters, seed, out);
+    return 0;
+}
+
+// The reference's OPQ rotation file (transform/opq_cache.cu): save under its own key, and load.
+int psbref_opq_save(const char* dir, const char* dataset, int n, int train_n, int dim, int m, int k, int opq_iters, int pq_iters,
+                    unsigned seed, const float* rotation, char* key_out, int cap) {
+    try {
+        paraselect::transform::OPQTrainSpec spec;
+        spec.n = train_n; spec.dim = dim; spec.pq_m = m; spec.pq_k = k; spec.opq_iters = opq_iters; spec.pq_iters = pq_iters; spec.seed = seed;
+        const std::string key = paraselect::transform::make_opq_cache_key(dataset, n, dim, spec);
+        paraselect::transform::save_opq_rotation_cache(dir, key, spec, std::vector<float>(rotation, rotation + (size_t)dim * dim));
+        if (key_out && cap > 0) { std::strncpy(key_out, key.c_str(), (size_t)cap - 1); key_out[cap - 1] = 0; }
+        return 0;
+    } catch (const std::exception&) { return 1; }
+}
+int psbref_opq_load(const char* dir, const char* key, int dim, float* rotation) {
+    std::vector<float> r;
+    if (!paraselect::transform::load_opq_rotation_cache(dir, key, dim, r)) return 2;
+    std::memcpy(rotation, r.data(), r.size() * sizeof(float));
     return 0;
 }
 
