@@ -470,8 +470,14 @@ psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, i
 psb_status psb_residual_rows(const float* d_data, int64_t n, int dim, const float* d_centroids, const int* d_assign,
                              float* d_out, int device, void* stream);
 
-/* PQ codebooks: one k-means (codebook_size codewords) per subspace, seeded sampling for the initial
- * codewords.  Replaces train_plain_pq_codebooks_gpu (src/quantization/pq/pq_trainer.cuh:9-26,
+/* Initial centroids as the reference picks them (init_centroids_by_sampling, src/clustering/kmeans/kmeans.cu:716-862):
+ * std::mt19937(seed); policy 0 = k-means++ seeding while n * k <= 2e7, else k distinct rows by a partial Fisher-Yates shuffle;
+ * 1 = always the random rows; 2 = always k-means++.  HOST data [n][dim]; h_centroids [k][dim] out; h_rows [k] (may be NULL)
+ * receives the rows picked.  The same draws as the reference, draw for draw. */
+psb_status psb_kmeans_init(const float* h_data, int64_t n, int dim, int k, int seed, int policy, float* h_centroids, int64_t* h_rows);
+
+/* PQ codebooks: one k-means (codebook_size codewords) per subspace; subspace s starts from the rows the reference's
+ * initialisation picks with seed + s * 104729 on that subspace (the same initial codewords as the reference's trainer).  Replaces train_plain_pq_codebooks_gpu (src/quantization/pq/pq_trainer.cuh:9-26,
  * src/quantization/pq/pq_trainer.cu:30-95).  d_codebook [m][k][dim/m] out. */
 psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors, int codebook_size, int iters,
                         uint64_t seed, float* d_codebook, int device, void* stream);

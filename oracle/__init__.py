@@ -19,6 +19,7 @@ REF_SO = os.path.join(_HERE, "_ref", "libpsb_ref.so")
 REF_TRAIN_SO = os.path.join(_HERE, "_ref", "libpsb_ref_train.so")
 REF_ROWCORR_SO = os.path.join(_HERE, "_ref", "libpsb_ref_rowcorr.so")
 REF_CACHE_SO = os.path.join(_HERE, "_ref", "libpsb_ref_cache.so")
+REF_KMEANS_INIT_SO = os.path.join(_HERE, "_ref", "libpsb_ref_kmeans_init.so")
 _lib = None
 _ref = None
 _ref_train = None
@@ -558,3 +559,32 @@ def ref_opq_save(cache_dir, dataset, n, train_n, rotation, m, k, opq_iters, pq_i
 def ref_opq_load(cache_dir, key, dim):
     rot = np.empty((dim, dim), np.float32)
     return rot if ref_train().psbref_opq_load(cache_dir.encode(), key.encode(), dim, _ptr(rot)) == 0 else None
+
+
+# ---------------------------------------------------------------- the reference's k-means initialisation (oracle/ref_kmeans_init_harness.cu)
+_ref_kmeans_init = None
+
+
+def have_ref_kmeans_init() -> bool:
+    if not os.path.exists(REF_KMEANS_INIT_SO):
+        return False
+    try:   # needs the CUDA toolkit's cuBLAS at load time (the Lloyd part of the same translation unit links it)
+        _load_kmeans_init()
+        return True
+    except OSError:
+        return False
+
+
+def _load_kmeans_init():
+    global _ref_kmeans_init
+    if _ref_kmeans_init is None:
+        _ref_kmeans_init = C.CDLL(REF_KMEANS_INIT_SO)
+    return _ref_kmeans_init
+
+
+def ref_kmeans_init(data, k, seed, policy=0):
+    """init_centroids_by_sampling of the reference on host data; policy 0 auto, 1 random rows, 2 k-means++."""
+    x = _c(data, np.float32)
+    out = np.empty((k, x.shape[1]), np.float32)
+    _load_kmeans_init().psbref_kmeans_init(x.shape[0], x.shape[1], k, seed, policy, _ptr(x), _ptr(out))
+    return out

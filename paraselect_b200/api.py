@@ -102,7 +102,7 @@ EXPORTS = [
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
     "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
     "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
-    "psb_rotate_rows", "psb_stage_rotate_queries", "psb_scan_sample_words", "psb_stage_scan_sample", "psb_stage_scan_shared",
+    "psb_kmeans_init", "psb_rotate_rows", "psb_stage_rotate_queries", "psb_scan_sample_words", "psb_stage_scan_sample", "psb_stage_scan_shared",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
 
@@ -571,6 +571,14 @@ def kmeans_update(d_sums, d_counts, k, dim, d_centroids, device=0, stream=None):
 def residual_rows(d_data, n, dim, d_centroids, d_assign, d_out, device=0, stream=None):
     _check(lib().psb_residual_rows(C.c_void_p(_p(d_data)), C.c_int64(n), dim, C.c_void_p(_p(d_centroids)),
                                    C.c_void_p(_p(d_assign)), C.c_void_p(_p(d_out)), device, _stream_ptr(stream)))
+
+
+def kmeans_init(data, k, seed, policy=0):
+    """Initial centroids the reference's way (host data); returns (centroids [k][dim], rows picked [k])."""
+    x = _np(data, np.float32)
+    cen = np.empty((k, x.shape[1]), np.float32); rows = np.empty(k, np.int64)
+    _check(lib().psb_kmeans_init(C.c_void_p(_p(x)), C.c_int64(x.shape[0]), x.shape[1], k, seed, policy, C.c_void_p(_p(cen)), C.c_void_p(_p(rows))))
+    return cen, rows
 
 
 def pq_train(d_data, n, dim, M, K, iters, seed, d_codebook, device=0, stream=None):

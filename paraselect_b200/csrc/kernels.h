@@ -257,6 +257,8 @@ psb_status launch_pq_accumulate(const float* d_data, long long n, int dim, const
                                 double* d_sums, int* d_counts, cudaStream_t s);
 psb_status launch_pq_update(const double* d_sums, const int* d_counts, int m, int k, int dsub, float* d_codebook,
                             cudaStream_t s);
+// Initial codewords taken from given data rows: d_rows [m][k] (row of the data for codeword c of subspace sub).
+psb_status launch_pq_init_rows(const float* d_data, int dim, int m, int k, const long long* d_rows, float* d_codebook, cudaStream_t s);
 psb_status launch_pq_init(const float* d_data, long long n, int dim, int m, int k, uint64_t seed,
                           float* d_codebook, cudaStream_t s);
 psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign,

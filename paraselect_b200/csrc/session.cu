@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <random>
 #include <memory>
 #include <new>
 #include <condition_variable>
@@ -1807,6 +1808,84 @@ psb_status psb_residual_rows(const float* d_data, int64_t n, int dim, const floa
     return launch_residual_rows(d_data, n, dim, d_centroids, d_assign, d_out, static_cast<cudaStream_t>(stream));
 }
 
+}  // extern "C"
+
+namespace {
+
+// The reference's choice of initial centroids (init_centroids_by_sampling, src/clustering/kmeans/kmeans.cu:716-862), as the
+// data rows it picks: std::mt19937(seed); below n * k = 2e7 (policy 0) k-means++ seeding - first row uniform, every further
+// row with probability proportional to its squared distance from the nearest row picked so far (fp32 sequential sums,
+// fp64 running total) - above it k distinct rows by a partial Fisher-Yates shuffle.  The standard library's engine and
+// distributions make the draws the same as the reference's, draw for draw.  row(i) must return row i's `dim` values.
+template <typename RowFn>
+void kmeans_init_rows(long long n, int dim, int k, int seed, int policy, RowFn row, std::vector<long long>& picked) {
+    picked.assign((size_t)k, 0);
+    if (n <= 0 || k <= 0) return;
+    const int ni = (int)n;
+    const int k_eff = std::min<long long>(k, n);
+    std::mt19937 rng((unsigned)seed);
+    const bool plusplus = policy == 2 || (policy == 0 && (long long)ni * k_eff <= 20000000LL);
+    if (!plusplus) {
+        std::vector<int> idx((size_t)ni);
+        for (int i = 0; i < ni; ++i) idx[(size_t)i] = i;
+        for (int i = 0; i < k_eff; ++i) {
+            std::uniform_int_distribution<int> dist(i, ni - 1);
+            std::swap(idx[(size_t)i], idx[(size_t)dist(rng)]);
+        }
+        for (int c = 0; c < k; ++c) picked[(size_t)c] = idx[(size_t)(c < k_eff ? c : 0)];
+        return;
+    }
+    auto dist2 = [&](const float* x, const float* c) {
+        float acc = 0.0f;
+        for (int d = 0; d < dim; ++d) { const float diff = x[d] - c[d]; acc = acc + diff * diff; }
+        return acc;
+    };
+    std::uniform_int_distribution<int> uni(0, ni - 1);
+    picked[0] = uni(rng);
+    std::vector<float> best((size_t)ni);
+    for (int i = 0; i < ni; ++i) best[(size_t)i] = dist2(row(i), row(picked[0]));
+    for (int c = 1; c < k_eff; ++c) {
+        double total = 0.0;
+        for (int i = 0; i < ni; ++i) total += (double)best[(size_t)i];
+        int next = -1;
+        if (total <= 0.0) {
+            next = uni(rng);
+        } else {
+            std::uniform_real_distribution<double> urd(0.0, total);
+            const double r = urd(rng);
+            double cum = 0.0;
+            for (int i = 0; i < ni; ++i) {
+                cum += (double)best[(size_t)i];
+                if (cum >= r) { next = i; break; }
+            }
+            if (next < 0) next = ni - 1;
+        }
+        picked[(size_t)c] = next;
+        const float* cc = row(next);
+        for (int i = 0; i < ni; ++i) {
+            const float d2 = dist2(row(i), cc);
+            if (d2 < best[(size_t)i]) best[(size_t)i] = d2;
+        }
+    }
+    for (int c = k_eff; c < k; ++c) picked[(size_t)c] = picked[0];
+}
+
+}  // namespace
+
+extern "C" {
+
+psb_status psb_kmeans_init(const float* h_data, int64_t n, int dim, int k, int seed, int policy, float* h_centroids, int64_t* h_rows) {
+    if (!h_data || !h_centroids || n <= 0 || n > INT_MAX || dim <= 0 || k <= 0 || policy < 0 || policy > 2)
+        return fail(PSB_INVALID_ARGUMENT, "invalid k-means initialisation request");
+    std::vector<long long> picked;
+    kmeans_init_rows(n, dim, k, seed, policy, [&](long long i) { return h_data + (size_t)i * dim; }, picked);
+    for (int c = 0; c < k; ++c) {
+        std::memcpy(h_centroids + (size_t)c * dim, h_data + (size_t)picked[(size_t)c] * dim, sizeof(float) * (size_t)dim);
+        if (h_rows) h_rows[c] = picked[(size_t)c];
+    }
+    return PSB_OK;
+}
+
 psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors, int codebook_size, int iters,
                         uint64_t seed, float* d_codebook, int device, void* stream) {
     if (!d_data || !d_codebook || n <= 0 || dim <= 0 || subvectors <= 0 || dim % subvectors || codebook_size <= 0 ||
@@ -1819,7 +1898,31 @@ psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors,
     PSB_TRY(codes.reserve((size_t)n * subvectors));
     PSB_TRY(sums.reserve(sizeof(double) * (size_t)subvectors * codebook_size * dsub));
     PSB_TRY(counts.reserve(sizeof(int) * (size_t)subvectors * codebook_size));
-    PSB_TRY(launch_pq_init(d_data, n, dim, subvectors, codebook_size, seed, d_codebook, st));
+    // Initial codewords as the reference's GPU trainer picks them (src/quantization/pq/pq_trainer.cu:30-95): subspace `sub`
+    // runs the k-means initialisation with seed + sub * 104729 on its own sub-vectors.  The random-rows policy needs no data;
+    // the k-means++ policy (small training sets only: n * K <= 2e7) works on a host copy of the subspace.
+    if (n > INT_MAX) return fail(PSB_UNSUPPORTED_SHAPE, "PQ training on more than 2^31-1 rows");
+    {
+        std::vector<long long> rows((size_t)subvectors * codebook_size), picked;
+        const bool plusplus = (long long)n * std::min<long long>(codebook_size, n) <= 20000000LL;
+        std::vector<float> sub_host;
+        if (plusplus) sub_host.resize((size_t)n * dsub);
+        for (int sub = 0; sub < subvectors; ++sub) {
+            const int sub_seed = (int)((unsigned)seed + (unsigned)sub * 104729u);
+            if (plusplus) {
+                PSB_CUDA(cudaMemcpy2DAsync(sub_host.data(), sizeof(float) * (size_t)dsub, d_data + (size_t)sub * dsub, sizeof(float) * (size_t)dim,
+                                           sizeof(float) * (size_t)dsub, (size_t)n, cudaMemcpyDeviceToHost, st));
+                PSB_CUDA(cudaStreamSynchronize(st));
+            }
+            kmeans_init_rows(n, dsub, codebook_size, sub_seed, 0, [&](long long i) { return sub_host.data() + (size_t)i * dsub; }, picked);
+            std::copy(picked.begin(), picked.end(), rows.begin() + (size_t)sub * codebook_size);
+        }
+        DevBuf d_rows;
+        PSB_TRY(d_rows.reserve(sizeof(long long) * rows.size()));
+        PSB_CUDA(cudaMemcpyAsync(d_rows.p, rows.data(), sizeof(long long) * rows.size(), cudaMemcpyHostToDevice, st));
+        PSB_TRY(launch_pq_init_rows(d_data, dim, subvectors, codebook_size, d_rows.as<long long>(), d_codebook, st));
+        PSB_CUDA(cudaStreamSynchronize(st));   // rows and d_rows go out of scope
+    }
     for (int it = 0; it < iters; ++it) {
         PSB_TRY(launch_pq_encode(d_data, n, dim, d_codebook, subvectors, codebook_size, codes.as<uint8_t>(), st));
         PSB_CUDA(cudaMemsetAsync(sums.p, 0, sums.bytes, st));

@@ -247,6 +247,26 @@ psb_status launch_pq_update(const double* d_sums, const int* d_counts, int m, in
     return PSB_OK;
 }
 
+// codebook[sub][c] = the sub-vector `sub` of data row rows[sub * k + c]
+__global__ void k_pq_init_rows(const float* __restrict__ data, int dim, int m, int k, const long long* __restrict__ rows,
+                               float* __restrict__ codebook) {
+    const int dsub = dim / m;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)m * k * dsub) return;
+    const int d = (int)(i % dsub);
+    const long long e = i / dsub;   // sub * k + c
+    const int sub = (int)(e / k);
+    codebook[i] = data[(size_t)rows[e] * dim + (size_t)sub * dsub + d];
+}
+
+psb_status launch_pq_init_rows(const float* d_data, int dim, int m, int k, const long long* d_rows, float* d_codebook, cudaStream_t s) {
+    const long long total = (long long)m * k * (dim / m);
+    k_pq_init_rows<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(d_data, dim, m, k, d_rows, d_codebook);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
 psb_status launch_pq_init(const float* d_data, long long n, int dim, int m, int k, uint64_t seed,
                           float* d_codebook, cudaStream_t s) {
     k_pq_init<<<(m * k + 255) / 256, 256, 0, s>>>(d_data, n, dim, m, k, seed, d_codebook);

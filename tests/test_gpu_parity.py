@@ -485,6 +485,22 @@ def test_staged_transport_overlapped_by_a_host_worker_equals_mapped(psb):
         assert np.array_equal(res[name]["distances"], res["mapped"]["distances"])
 
 
+@pytest.mark.skipif(not oracle.have_ref_kmeans_init(), reason="reference k-means initialisation not compiled here")
+@pytest.mark.parametrize("n", [20000, 90000])   # n * 256 below and above the reference's k-means++ budget of 2e7
+def test_pq_train_starts_from_the_references_initial_codewords(psb, n):
+    """iters = 0 returns the initial codebook: subspace s = the rows the reference's initialisation picks with seed + s * 104729
+    on the sub-vectors of that subspace (src/quantization/pq/pq_trainer.cu:62)."""
+    torch = _torch()
+    rng = np.random.default_rng(n)
+    data = rng.standard_normal((n, 16)).astype(np.float32)
+    cb = torch.empty((4, 256, 4), dtype=torch.float32, device="cuda")
+    psb.pq_train(dev(data), n, 16, 4, 256, 0, 1234, cb)
+    got = cb.cpu().numpy()
+    for s in range(4):
+        want = oracle.ref_kmeans_init(data[:, 4 * s:4 * s + 4], 256, 1234 + s * 104729, 0)
+        assert np.array_equal(got[s], want), s
+
+
 def test_residual_rows_feed_residual_training(psb):
     """psb_residual_rows (in place) = row - centroid[assign]; PQ trained on and encoding the residuals gives an index the
     residual search accepts (codes equal the checker's encoding of the same residuals)."""

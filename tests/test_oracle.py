@@ -293,3 +293,20 @@ def test_opq_pipeline_restatement_reduces_to_the_plain_one():
     rot = np.zeros((32, 32), np.float32); rot[0, 1] = 2.0
     y = oracle.rotate_rows(q, rot)
     assert np.array_equal(y[:, 0], 2.0 * q[:, 1]) and not y[:, 1:].any()
+
+
+@pytest.mark.skipif(not oracle.have_ref_kmeans_init(), reason="reference k-means initialisation not compiled here")
+@pytest.mark.parametrize("n,dim,k,seed,policy", [(500, 8, 16, 123, 0), (3000, 4, 256, 42, 0), (3000, 4, 256, 42 + 104729, 0),
+                                                  (100000, 2, 256, 7, 0), (100000, 2, 256, 7, 2), (900, 16, 64, 5, 1),
+                                                  (40, 6, 64, 9, 0), (40, 6, 64, 9, 1)])
+def test_kmeans_init_equals_the_reference(n, dim, k, seed, policy):
+    """psb_kmeans_init (a host function of the library, no GPU) against the reference's init_centroids_by_sampling: the same
+    rows, draw for draw - k-means++ below n * k = 2e7, partial Fisher-Yates above, forced either way, and k > n."""
+    from paraselect_b200 import api
+    rng = np.random.default_rng(n + k)
+    x = rng.standard_normal((n, dim)).astype(np.float32)
+    x[::7] = x[0]   # duplicate rows: zero distances in the k-means++ weights
+    want = oracle.ref_kmeans_init(x, k, seed, policy)
+    got, rows = api.kmeans_init(x, k, seed, policy)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(x[rows], got)
