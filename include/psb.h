@@ -441,6 +441,34 @@ psb_status psb_flat_session_search_device(psb_flat_session* session, const float
                                           int64_t* d_indices, float* d_distances);
 psb_status psb_flat_session_destroy(psb_flat_session* session);
 
+/* ---- sharded search: one rank of a group of sessions (multi-GPU) ----------------------------------------------
+ *
+ * Every rank - one process or thread per GPU - holds a session over its shard of the index (psb_options.list_global_begin; any
+ * exact-row mode; psb_options.reserve_sms > 0 leaves SMs to the exchange) and passes two NCCL communicators of its own over
+ * the same ranks.  A search runs, per sub-batch and on two streams, the session's stage calls and the exchanges between the
+ * ranks: sample records -> shared cutoffs -> scan | all-to-all of the candidates -> merge of this rank's query slice ->
+ * all-gather of the merged rows -> exact scoring of the rows held here -> all-reduce MIN -> top-k -> ids, and one all-reduce
+ * MAX of the ids.  Every rank passes the same queries and receives the full result; it equals the unsharded search's.
+ * The reference has no counterpart (its search is single-GPU, src/search/ivfpq/pipeline/ivfpq_pipeline.cu:8-116).
+ *
+ * nccl_comm / nccl_comm_samples: ncclComm_t handles (the second carries the sample records beside the exchange of the
+ * previous sub-batch; NULL = use the first for both, which serialises the two).  nccl_library: path or soname of the NCCL
+ * library that created them (NULL = "libnccl.so.2"); the copy already loaded in the process is used.  The collectives of
+ * both communicators are issued in the same order on every rank.  The session must not be used for other calls while a
+ * group search is in flight, and must outlive the group. */
+typedef struct psb_group psb_group;
+psb_status psb_group_create(psb_session* session, void* nccl_comm, void* nccl_comm_samples, const char* nccl_library,
+                            int max_batch, int nprobe, int topk, psb_group** out);
+/* parts: sub-batches per batch (default 4); shared_cutoff: 0 = every rank places its cutoffs on its own rows only. */
+psb_status psb_group_set(psb_group* group, int parts, int shared_cutoff);
+/* d_queries [nq][dim] fp32 (the same on every rank), d_indices [nq][topk], d_distances [nq][topk], all DEVICE memory;
+ * asynchronous on the session's stream except for one host read per batch (the verification word of the shared cutoffs). */
+psb_status psb_group_search_device(psb_group* group, const float* d_queries, int nq, const psb_search_params* params,
+                                   int64_t* d_indices, float* d_distances);
+/* Batches that were searched a second time because a shared cutoff came out too low (expected: 0). */
+long long psb_group_searched_again(const psb_group* group);
+psb_status psb_group_destroy(psb_group* group);
+
 /* ---- training and encoding ---------------------------------------------------------------------------- */
 
 /* Lloyd k-means on DEVICE data: assign = argmin squared L2 (strict <, lowest index wins), update = mean,

@@ -102,6 +102,7 @@ EXPORTS = [
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
     "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
     "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
+    "psb_group_create", "psb_group_set", "psb_group_search_device", "psb_group_searched_again", "psb_group_destroy",
     "psb_kmeans_init", "psb_rotate_rows", "psb_stage_rotate_queries", "psb_scan_sample_words", "psb_stage_scan_sample", "psb_stage_scan_shared",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -477,6 +478,37 @@ def reorder_rows(src, reordered_ids):
     _check(lib().psb_reorder_rows(C.c_void_p(_p(src)), C.c_int64(src.shape[0]), C.c_size_t(src.strides[0]), C.c_void_p(_p(rid)),
                                   C.c_void_p(_p(dst))))
     return dst
+
+
+class Group:
+    """One rank of a sharded search driven by the library itself (psb_group_*): `session` holds this rank's shard, the two
+    communicators are ncclComm_t handles (integers) created by the caller with the NCCL library at `nccl_library`."""
+
+    def __init__(self, session, nccl_comm, nccl_comm_samples, max_batch, nprobe, topk, nccl_library=None, parts=4, shared_cutoff=True):
+        self._h = C.c_void_p()
+        self.session = session
+        _check(lib().psb_group_create(session._h, C.c_void_p(nccl_comm), C.c_void_p(nccl_comm_samples) if nccl_comm_samples else None,
+                                      nccl_library.encode() if nccl_library else None, max_batch, nprobe, topk, C.byref(self._h)))
+        _check(lib().psb_group_set(self._h, parts, int(shared_cutoff)))
+
+    def search_device(self, d_queries, nq, nprobe, topk, d_ids, d_dist):
+        p = SearchParams(nprobe=nprobe, topk=topk, batch_size=nq, distance=0, fp16_coarse=0)
+        _check(lib().psb_group_search_device(self._h, C.c_void_p(_p(d_queries)), nq, C.byref(p), C.c_void_p(_p(d_ids)), C.c_void_p(_p(d_dist))))
+
+    def searched_again(self):
+        lib().psb_group_searched_again.restype = C.c_longlong
+        return int(lib().psb_group_searched_again(self._h))
+
+    def close(self):
+        if self._h:
+            lib().psb_group_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
 
 
 class RowCorrectionHeader(C.Structure):

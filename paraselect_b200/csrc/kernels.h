@@ -275,4 +275,15 @@ psb_status launch_gen_mixture(const float* d_centres, const long long* d_offsets
 psb_status launch_gen_normal(uint64_t seed, long long first, long long n, float scale, float* d_out,
                              cudaStream_t s);
 
+// What the group layer (group.cu) needs to know of a session.
+struct SessionShape {
+    int dim = 0, m = 0, k = 0, nlist = 0, n_rerank = 0, exact_elem = 0, device = 0;
+    bool residual = false, flat = false;
+    cudaStream_t stream = nullptr;
+};
+}  // namespace psb
+struct psb_session;
+namespace psb {
+SessionShape session_shape(const psb_session* s);
+
 }  // namespace psb

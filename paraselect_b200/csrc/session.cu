@@ -683,6 +683,15 @@ psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int*
 
 }  // namespace
 
+namespace psb {
+SessionShape session_shape(const psb_session* s) {
+    SessionShape o;
+    o.dim = s->dim; o.m = s->m; o.k = s->k; o.nlist = s->nlist; o.n_rerank = s->opt.n_rerank; o.exact_elem = s->exact_elem;
+    o.device = s->device; o.residual = s->opt.adc_mode == 1; o.flat = s->flat; o.stream = s->stream;
+    return o;
+}
+}  // namespace psb
+
 extern "C" {
 
 const char* psb_last_error(void) { return last_error_ref().c_str(); }
