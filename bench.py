@@ -319,6 +319,8 @@ def main():
     ap.add_argument("--reserve-sms", type=int, default=24, help="N > 1: SMs the scan's persistent grid leaves to the exchange half "
                     "(the PCIe gather of the exact rows runs on that many SMs of its own, the collectives beside it)")
     ap.add_argument("--parts", type=int, default=4, help="N > 1: sub-batches per batch")
+    ap.add_argument("--native-group", action="store_true", help="N > 1: drive the sharded step through the C ABI's psb_group_* (NCCL "
+                    "communicators of its own) instead of the torch.distributed orchestration of paraselect_b200.multi")
     ap.add_argument("--local-cutoffs", action="store_true", help="N > 1: every rank places its admission cutoffs on its own rows only "
                     "(default: on the rows of all ranks, from exchanged sample records)")
     ap.add_argument("--serial", action="store_true", help="N = 1: no sub-batches (one scan launch per batch, then the rerank)")
@@ -567,9 +569,21 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
         width = min(R, n) if R > topk else topk
         search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
                                rerank=R > topk, parts=args.parts if nq >= 2048 else 1, shared_cutoff=not args.local_cutoffs)
+        group = None
+        if args.native_group:
+            nccl_path, comms, destroy_comms = multi.raw_nccl_comms(dist, torch, 2)
+            group = api.Group(sess, comms[0], comms[1], nq, nprobe, topk, nccl_library=nccl_path, parts=args.parts if nq >= 2048 else 1,
+                              shared_cutoff=not args.local_cutoffs)
+            g_ids = torch.empty((nq, topk), dtype=torch.int64, device="cuda")
+            g_dist = torch.empty((nq, topk), dtype=torch.float32, device="cuda")
+
+            def group_step(q):
+                group.search_device(q, nq, nprobe, topk, g_ids, g_dist)
+                return g_ids, g_dist
+        run_step = group_step if group is not None else search.step
         search.step(dq, profile=True)  # first step in one piece: every workspace reaches its final size before streams overlap
         for _ in range(max(args.warmup, 3)):
-            search.step(dq)
+            run_step(dq)
         torch.cuda.synchronize()
         sess.counters(reset=True)
         sampler = ClockSampler(local_rank)
@@ -589,7 +603,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
             return float(ms.item())
 
-        ms_dev = timed(lambda: search.step(dq))
+        ms_dev = timed(lambda: run_step(dq))
         c = sess.counters(reset=True)
         out_ids = torch.empty((nq, topk), dtype=torch.int64).pin_memory()
         out_dist = torch.empty((nq, topk), dtype=torch.float32).pin_memory()
@@ -597,7 +611,7 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
 
         def e2e_step():
             dq2.copy_(q_pinned, non_blocking=True)
-            ids, dd = search.step(dq2)
+            ids, dd = run_step(dq2)
             out_ids.copy_(ids, non_blocking=True)
             out_dist.copy_(dd, non_blocking=True)
             stream.synchronize()
@@ -650,9 +664,13 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
             roofline=roofline,
             counters=dict(scanned_codes_per_step=int(S * launches_per_step), fallback_queries_per_step=tot[4].item() / max(1, args.steps),
                           prefilter_survivors_per_step=tot[6].item() / max(1, args.steps), shared_cutoffs=bool(search.shared),
-                          batches_searched_again=int(search.redone)),
+                          batches_searched_again=int(group.searched_again() if group is not None else search.redone),
+                          driver="psb_group (C ABI)" if group is not None else "multi.ShardedSearch (torch.distributed)"),
             stages_ms_rank0=stage_ms, pipeline_timeline_ms_rank0=timeline, host_numa_node_rank0=numa_node, result_checksum=checksum, clocks=clocks)
         emit(line)
+    if group is not None:
+        group.close()
+        destroy_comms()
     sess.close()
     dist.barrier()
     dist.destroy_process_group()

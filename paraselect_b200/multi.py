@@ -52,6 +52,49 @@ def owned_mask_rows(global_begin, local_offsets, r0, r1):
     return ok
 
 
+def raw_nccl_comms(dist, torch, count=2):
+    """NCCL communicators for api.Group (psb_group_*) in a process that already runs torch.distributed: created with the NCCL
+    copy torch loaded, the unique ids carried by a broadcast of the default process group.  Returns (library path, [handles],
+    destroy function).  A C or C++ caller creates its communicators with ncclCommInitRank directly."""
+    import ctypes as C
+
+    torch.cuda.nccl.version()   # makes sure the library is loaded
+    path = "libnccl.so.2"
+    for line in open("/proc/self/maps"):
+        if "libnccl.so" in line:
+            path = line.split()[-1]
+            break
+    nccl = C.CDLL(path)
+
+    class UniqueId(C.Structure):
+        _fields_ = [("internal", C.c_char * 128)]
+
+    nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+    rank, world = dist.get_rank(), dist.get_world_size()
+    on_gpu = dist.get_backend() == "nccl"
+    comms = []
+    for _ in range(count):
+        uid = UniqueId()
+        if rank == 0 and nccl.ncclGetUniqueId(C.byref(uid)) != 0:
+            raise RuntimeError("ncclGetUniqueId failed")
+        t = torch.frombuffer(bytearray(bytes(uid)), dtype=torch.uint8).clone()
+        if on_gpu:
+            t = t.cuda()
+        dist.broadcast(t, 0)
+        C.memmove(C.byref(uid), t.cpu().numpy().tobytes(), 128)
+        comm = C.c_void_p()
+        rc = nccl.ncclCommInitRank(C.byref(comm), world, uid, rank)
+        if rc != 0:
+            raise RuntimeError("ncclCommInitRank failed (%d)" % rc)
+        comms.append(comm.value)
+
+    def destroy():
+        for c in comms:
+            nccl.ncclCommDestroy(C.c_void_p(c))
+
+    return path, comms, destroy
+
+
 class SessionEngine:
     """The CUDA library as the compute engine of ShardedSearch (device tensors are torch CUDA tensors)."""
 
