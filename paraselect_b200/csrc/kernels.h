@@ -261,9 +261,11 @@ psb_status launch_pq_update(const double* d_sums, const int* d_counts, int m, in
 psb_status launch_pq_init_rows(const float* d_data, int dim, int m, int k, const long long* d_rows, float* d_codebook, cudaStream_t s);
 psb_status launch_pq_init(const float* d_data, long long n, int dim, int m, int k, uint64_t seed,
                           float* d_codebook, cudaStream_t s);
-psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign,
-                                    const float* d_best, double* d_sums, int* d_counts, double* d_obj,
-                                    cudaStream_t s);
+// Workspace of the k-means accumulation: rows grouped by centroid (order [n], offsets [k + 1], cursor [k], all int32).
+struct KmeansAccumWs { int* order = nullptr; int* offsets = nullptr; int* cursor = nullptr; };
+// d_counts [k] and *d_obj zeroed by the caller; d_sums [k][dim] is written whole (zeros for a centroid without rows).
+psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign, const float* d_best, int k,
+                                    double* d_sums, int* d_counts, double* d_obj, const KmeansAccumWs& ws, cudaStream_t s);
 psb_status launch_residual_rows(const float* d_data, long long n, int dim, const float* d_centroids, const int* d_assign,
                                 float* d_out, cudaStream_t s);
 psb_status launch_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids,

@@ -1719,6 +1719,12 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
     if (!d_as) { PSB_TRY(assign.reserve(sizeof(int) * (size_t)n)); d_as = assign.as<int>(); }
     PSB_TRY(sums.reserve(sizeof(double) * (size_t)k * dim)); PSB_TRY(counts.reserve(sizeof(int) * (size_t)k));
     PSB_TRY(obj.reserve(sizeof(double) * ((size_t)iters + 1)));
+    DevBuf acc_order, acc_offsets, acc_cursor;   // rows grouped by centroid for the accumulation
+    PSB_TRY(acc_order.reserve(sizeof(int) * (size_t)n));
+    PSB_TRY(acc_offsets.reserve(sizeof(int) * ((size_t)k + 1)));
+    PSB_TRY(acc_cursor.reserve(sizeof(int) * (size_t)k));
+    KmeansAccumWs acc_ws;
+    acc_ws.order = acc_order.as<int>(); acc_ws.offsets = acc_offsets.as<int>(); acc_ws.cursor = acc_cursor.as<int>();
     PSB_CUDA(cudaMemsetAsync(obj.p, 0, sizeof(double) * ((size_t)iters + 1), st));
     for (int it = 0; it <= iters; ++it) {
         if (tc) {
@@ -1738,10 +1744,9 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
                 PSB_TRY(launch_select_rows(tile.as<float>(), nn, k, 1, d_as + r0, best.as<float>() + r0, st));
             }
         }
-        PSB_CUDA(cudaMemsetAsync(sums.p, 0, sizeof(double) * (size_t)k * dim, st));
         PSB_CUDA(cudaMemsetAsync(counts.p, 0, sizeof(int) * (size_t)k, st));
-        PSB_TRY(launch_kmeans_accumulate(d_data, n, dim, d_as, best.as<float>(), sums.as<double>(), counts.as<int>(),
-                                         obj.as<double>() + it, st));
+        PSB_TRY(launch_kmeans_accumulate(d_data, n, dim, d_as, best.as<float>(), k, sums.as<double>(), counts.as<int>(),
+                                         obj.as<double>() + it, acc_ws, st));
         if (it < iters) PSB_TRY(launch_kmeans_update(sums.as<double>(), counts.as<int>(), k, dim, d_centroids, st));
     }
     if (h_objective) PSB_CUDA(cudaMemcpyAsync(h_objective, obj.p, sizeof(double) * ((size_t)iters + 1), cudaMemcpyDeviceToHost, st));
@@ -1796,10 +1801,17 @@ psb_status psb_kmeans_accumulate(const float* d_data, int64_t n, int dim, const 
         return fail(PSB_INVALID_ARGUMENT, "invalid k-means accumulation request");
     PSB_TRY(check_device(device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    PSB_CUDA(cudaMemsetAsync(d_sums, 0, sizeof(double) * (size_t)k * dim, st));
     PSB_CUDA(cudaMemsetAsync(d_counts, 0, sizeof(int) * (size_t)k, st));
     PSB_CUDA(cudaMemsetAsync(d_objective, 0, sizeof(double), st));
-    return launch_kmeans_accumulate(d_data, n, dim, d_assign, d_best, d_sums, d_counts, d_objective, st);
+    DevBuf order, offsets, cursor;   // rows grouped by centroid: freed after the stream has drained below
+    PSB_TRY(order.reserve(sizeof(int) * (size_t)std::max<int64_t>(n, 1)));
+    PSB_TRY(offsets.reserve(sizeof(int) * ((size_t)k + 1)));
+    PSB_TRY(cursor.reserve(sizeof(int) * (size_t)k));
+    KmeansAccumWs ws;
+    ws.order = order.as<int>(); ws.offsets = offsets.as<int>(); ws.cursor = cursor.as<int>();
+    PSB_TRY(launch_kmeans_accumulate(d_data, n, dim, d_assign, d_best, k, d_sums, d_counts, d_objective, ws, st));
+    PSB_CUDA(cudaStreamSynchronize(st));
+    return PSB_OK;
 }
 
 psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids, int device,

@@ -105,16 +105,40 @@ k_pq_encode_tile(const float* __restrict__ data, long long n, int dim, const flo
     for (long long i = threadIdx.x; i < rows_here * m; i += kEncThreads) codes[(size_t)row0 * m + i] = s_codes[i];
 }
 
-__global__ void k_pq_accumulate(const float* __restrict__ data, long long n, int dim, const uint8_t* __restrict__ codes,
-                                int m, int k, double* __restrict__ sums, int* __restrict__ counts) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n * m) return;
-    const long long row = i / m; const int sub = (int)(i % m);
+// Codeword sums without a global atomic per element: a CTA takes a range of rows and a group of subspaces, accumulates into
+// fp64 sums and counts in shared memory (G subspaces x k codewords x dsub), and adds its non-zero entries to the global
+// sums once at the end.  grid (row ranges, subspace groups); dynamic shared memory = G * k * (dsub * 8 + 4) bytes.
+constexpr int kPqAccRows = 8192;
+__global__ void __launch_bounds__(256) k_pq_accumulate(const float* __restrict__ data, long long n, int dim, const uint8_t* __restrict__ codes,
+                                                       int m, int k, int group, double* __restrict__ sums, int* __restrict__ counts) {
+    extern __shared__ __align__(16) unsigned char s_pq_raw[];
     const int dsub = dim / m;
-    const int c = codes[i];
-    atomicAdd(&counts[sub * k + c], 1);
-    for (int d = 0; d < dsub; ++d)
-        atomicAdd(&sums[((size_t)sub * k + c) * dsub + d], (double)data[(size_t)row * dim + sub * dsub + d]);
+    const int sub0 = blockIdx.y * group;
+    const int g = min(group, m - sub0);
+    double* s_sums = reinterpret_cast<double*>(s_pq_raw);                                  // [g][k][dsub]
+    int* s_cnt = reinterpret_cast<int*>(s_pq_raw + (size_t)group * k * dsub * sizeof(double));  // [g][k]
+    for (int i = threadIdx.x; i < g * k * dsub; i += blockDim.x) s_sums[i] = 0.0;
+    for (int i = threadIdx.x; i < g * k; i += blockDim.x) s_cnt[i] = 0;
+    __syncthreads();
+    const long long r0 = (long long)blockIdx.x * kPqAccRows;
+    const long long r1 = min(n, r0 + kPqAccRows);
+    const long long pairs = (r1 - r0) * g;
+    for (long long i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const long long row = r0 + i / g;
+        const int j = (int)(i % g), sub = sub0 + j;
+        const int c = codes[(size_t)row * m + sub];
+        atomicAdd(&s_cnt[j * k + c], 1);
+        const float* x = data + (size_t)row * dim + (size_t)sub * dsub;
+        double* dst = s_sums + ((size_t)j * k + c) * dsub;
+        for (int d = 0; d < dsub; ++d) atomicAdd(&dst[d], (double)x[d]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < g * k; i += blockDim.x) {
+        const int cnt = s_cnt[i];
+        if (!cnt) continue;
+        atomicAdd(&counts[(size_t)sub0 * k + i], cnt);
+        for (int d = 0; d < dsub; ++d) atomicAdd(&sums[((size_t)sub0 * k + i) * dsub + d], s_sums[(size_t)i * dsub + d]);
+    }
 }
 
 __global__ void k_mean_update(const double* __restrict__ sums, const int* __restrict__ counts, long long n_centres,
@@ -154,18 +178,92 @@ __global__ void k_pq_init(const float* __restrict__ data, long long n, int dim, 
     for (int d = 0; d < dsub; ++d) codebook[(size_t)i * dsub + d] = data[(size_t)row * dim + sub * dsub + d];
 }
 
-__global__ void k_kmeans_accumulate(const float* __restrict__ data, long long n, int dim, const int* __restrict__ assign,
-                                    const float* __restrict__ best, double* __restrict__ sums, int* __restrict__ counts,
-                                    double* __restrict__ obj) {
-    // one warp per row
-    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (w >= n) return;
-    const int c = assign[w];
-    for (int d = lane; d < dim; d += 32) atomicAdd(&sums[(size_t)c * dim + d], (double)data[(size_t)w * dim + d]);
-    if (lane == 0) {
-        atomicAdd(&counts[c], 1);
-        if (obj && best) atomicAdd(obj, (double)best[w]);
+// ---- k-means accumulation: rows grouped by centroid, then one CTA sums each group --------------------------------------
+// (the reference sorts by assignment and accumulates segment by segment for the same reason: src/clustering/kmeans/
+// kmeans.cu:519-575, kmeans_utils.cu:541-574; per-element atomics onto k * dim fp64 words serialise on popular centroids).
+// 1. k_km_count:   counts[c] (one int atomic per row) and the objective (one fp64 atomic per CTA)
+// 2. k_km_offsets: exclusive prefix of the counts, one CTA in coalesced rounds
+// 3. k_km_fill:    order[offset[c] + slot] = row (one int atomic per row)
+// 4. k_km_sums:    CTA c sums its rows in fp64, eight rows at a time (one per warp), and writes sums[c][:] - no atomics; a
+//                  group of at most 1,024 rows is sorted first, so that its sum does not depend on the order the slots were taken
+constexpr int kKmSumThreads = 256;
+__global__ void k_km_count(const int* __restrict__ assign, const float* __restrict__ best, long long n, int* __restrict__ counts,
+                           double* __restrict__ obj) {
+    __shared__ double s_part[8];
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    double b = 0.0;
+    if (i < n) {
+        atomicAdd(&counts[assign[i]], 1);
+        if (best) b = (double)best[i];
+    }
+    if (!obj) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) b += __shfl_xor_sync(0xffffffffu, b, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s_part[w];
+        atomicAdd(obj, t);
+    }
+}
+__global__ void __launch_bounds__(1024) k_km_offsets(const int* __restrict__ counts, int k, int* __restrict__ offsets, int* __restrict__ cursor) {
+    __shared__ int s_warp[32];
+    __shared__ int s_total;
+    int carry = 0;
+    for (int base = 0; base < k; base += blockDim.x) {
+        const int c = base + threadIdx.x;
+        const int v = c < k ? counts[c] : 0;
+        const int ex = block_exclusive_scan(v, s_warp, &s_total);
+        if (c < k) { offsets[c] = carry + ex; cursor[c] = 0; }
+        carry += s_total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) offsets[k] = carry;
+}
+__global__ void k_km_fill(const int* __restrict__ assign, long long n, const int* __restrict__ offsets, int* __restrict__ cursor,
+                          int* __restrict__ order) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int c = assign[i];
+    order[offsets[c] + atomicAdd(&cursor[c], 1)] = (int)i;
+}
+__global__ void __launch_bounds__(kKmSumThreads) k_km_sums(const float* __restrict__ data, int dim, const int* __restrict__ offsets,
+                                                           int* __restrict__ order, double* __restrict__ sums) {
+    __shared__ int s_rows[1024];
+    __shared__ double s_part[kKmSumThreads / 32][256];
+    const int c = blockIdx.x;
+    const int b0 = offsets[c], cnt = offsets[c + 1] - b0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* rows = order + b0;
+    if (cnt > 1 && cnt <= 1024) {   // canonical order for the usual, small group
+        int np = 2;
+        while (np < cnt) np <<= 1;
+        for (int i = threadIdx.x; i < np; i += blockDim.x) s_rows[i] = i < cnt ? rows[i] : 0x7fffffff;
+        __syncthreads();
+        block_bitonic_sort(s_rows, np);
+        rows = s_rows;
+    }
+    for (int d0 = 0; d0 < dim; d0 += 256) {   // 256 dimensions at a time: eight per lane
+        double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int j = warp; j < cnt; j += kKmSumThreads / 32) {
+            const float* x = data + (size_t)rows[j] * dim + d0;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int d = lane + 32 * t;
+                if (d0 + d < dim) acc[t] += (double)x[d];
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) s_part[warp][lane + 32 * t] = acc[t];
+        __syncthreads();
+        for (int d = threadIdx.x; d < 256 && d0 + d < dim; d += blockDim.x) {
+            double t = 0.0;
+#pragma unroll
+            for (int w = 0; w < kKmSumThreads / 32; ++w) t += s_part[w][d];
+            sums[(size_t)c * dim + d0 + d] = t;
+        }
+        __syncthreads();
     }
 }
 
@@ -232,7 +330,14 @@ psb_status launch_pq_encode(const float* d_data, long long n, int dim, const flo
 psb_status launch_pq_accumulate(const float* d_data, long long n, int dim, const uint8_t* d_codes, int m, int k,
                                 double* d_sums, int* d_counts, cudaStream_t s) {
     if (n <= 0) return PSB_OK;
-    k_pq_accumulate<<<(unsigned)((n * m + 255) / 256), 256, 0, s>>>(d_data, n, dim, d_codes, m, k, d_sums, d_counts);
+    const int dsub = dim / m;
+    const size_t per_sub = (size_t)k * ((size_t)dsub * sizeof(double) + sizeof(int));
+    int group = (int)std::max<size_t>(1, std::min<size_t>((size_t)m, ((size_t)96 * 1024) / per_sub));
+    const size_t smem = (size_t)group * per_sub;
+    if (smem > (size_t)200 * 1024) return fail(PSB_UNSUPPORTED_SHAPE, "PQ sub-vectors too wide for the accumulation kernel");
+    if (smem > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(k_pq_accumulate, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)((n + kPqAccRows - 1) / kPqAccRows), (unsigned)((m + group - 1) / group));
+    k_pq_accumulate<<<grid, 256, smem, s>>>(d_data, n, dim, d_codes, m, k, group, d_sums, d_counts);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
@@ -275,11 +380,25 @@ psb_status launch_pq_init(const float* d_data, long long n, int dim, int m, int 
     return PSB_OK;
 }
 
-psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign,
-                                    const float* d_best, double* d_sums, int* d_counts, double* d_obj,
-                                    cudaStream_t s) {
-    if (n <= 0) return PSB_OK;
-    k_kmeans_accumulate<<<(unsigned)((n * 32 + 255) / 256), 256, 0, s>>>(d_data, n, dim, d_assign, d_best, d_sums, d_counts, d_obj);
+psb_status launch_kmeans_accumulate(const float* d_data, long long n, int dim, const int* d_assign, const float* d_best, int k,
+                                    double* d_sums, int* d_counts, double* d_obj, const KmeansAccumWs& ws, cudaStream_t s) {
+    if (n > 0x7fffffffLL) return fail(PSB_UNSUPPORTED_SHAPE, "more than 2^31-1 rows in one accumulation");
+    if (!ws.order || !ws.offsets || !ws.cursor) return fail(PSB_INTERNAL, "k-means accumulation workspace missing");
+    // d_counts and *d_obj were zeroed by the caller; d_sums is written whole
+    if (n > 0) {
+        k_km_count<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_assign, d_best, n, d_counts, d_obj);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    }
+    k_km_offsets<<<1, 1024, 0, s>>>(d_counts, k, ws.offsets, ws.cursor);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    if (n > 0) {
+        k_km_fill<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_assign, n, ws.offsets, ws.cursor, ws.order);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    }
+    k_km_sums<<<k, kKmSumThreads, 0, s>>>(d_data, dim, ws.offsets, ws.order, d_sums);
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;
