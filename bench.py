@@ -228,6 +228,21 @@ def make_queries(cfg, torch, api, centres, w, device):
     return (centres[torch.from_numpy(comp).cuda()] + noise).contiguous()
 
 
+def measure_h2d_gbs(torch, mbytes=512, reps=3):
+    """Host -> device copy bandwidth of one large pinned buffer: the ceiling of any transport of the exact rows."""
+    host = torch.empty(mbytes << 20, dtype=torch.uint8).pin_memory()
+    dev = torch.empty(mbytes << 20, dtype=torch.uint8, device="cuda")
+    dev.copy_(host, non_blocking=True)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        dev.copy_(host, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    return round(reps * (mbytes << 20) / (e0.elapsed_time(e1) * 1e-3) / 1e9, 1)
+
+
 def recall_at(got, truth, k):
     hit = 0
     for g, t in zip(got[:, :k], truth[:, :k]):
@@ -393,6 +408,7 @@ def main():
         if args.impl == "reference":
             return reference_arm(args, cfg, index, q_host, gt)
 
+        h2d_gbs = measure_h2d_gbs(torch)
         t0 = time.time()
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
                            residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas, serial_pipeline=args.serial,
@@ -493,6 +509,11 @@ def main():
                  h2d_bytes_per_step=int(stats["h2d_bytes"]), d2h_bytes_per_step=int(stats["d2h_bytes"]),
                  pcie_gather_bytes_per_step=int(nq * stage1 * dim * 4) if R > topk else 0),
         gpu_launches=launches, roofline=roofline,
+        # the exact rerank moves nq * n_rerank rows from host memory per batch: what the end-to-end step is bound by
+        transport=dict(bytes_per_step=int(nq * stage1 * dim * 4) if R > topk else 0,
+                       achieved_gbs=round(nq * stage1 * dim * 4 / max(1e-9, stats["pq_rerank_ms"] * 1e-3) / 1e9, 1) if R > topk and stats["pq_rerank_ms"] > 0 else None,
+                       pinned_h2d_copy_gbs=h2d_gbs, note="achieved = gathered bytes / rerank stage time (random rows of dim * 4 bytes); "
+                       "pinned_h2d_copy_gbs = one large pinned copy on this host, the link's ceiling"),
         cpu_baseline=dict(value=round(ns / dt, 2), unit="queries/s", cores=cores, kind=kind,
                           sample="first %d queries of the batch, all %d host threads" % (ns, cores)),
         stages_ms=dict(coarse=round(stats["coarse_search_ms"], 3), lut=round(stats["pq_lut_build_ms"], 3),
