@@ -326,7 +326,7 @@ def main():
     ap.add_argument("--exact-mode", default="auto", choices=["auto", "mapped", "staged", "cached", "hybrid"],
                     help="rerank transport on one GPU: staged = host threads gather rows into pinned rings and cudaMemcpyAsync moves "
                          "them (no SM time spent on the transfer), mapped = kernels gather mapped host rows over PCIe; auto = staged "
-                         "when a batch gathers at least 2 GB (the scan is then long enough to hide the host gather), else mapped; "
+                         "auto = hybrid when a batch gathers at least 2 GB (the scan is then long enough to run beside the transfer), else mapped; "
                          "cached = the session copies the rows into device memory once (not the host-resident configuration the "
                          "headline metric names: an extra data point); hybrid = staged and mapped at once, --zero-copy-pct of every "
                          "sub-batch through the kernel")
@@ -366,7 +366,7 @@ def main():
         cfg["nq"] = args.queries
     if args.exact_mode == "auto":
         gathered = cfg["nq"] * max(cfg["n_rerank"], cfg["topk"]) * cfg["dim"] * 4
-        args.exact_mode = "staged" if gathered >= 2e9 else "mapped"
+        args.exact_mode = "hybrid" if gathered >= 2e9 else "mapped"
     if not torch.cuda.is_available() or api.device_count() < 1:
         raise SystemExit("bench.py needs a B200: the library has no CPU path")
     torch.cuda.set_device(local_rank)

@@ -119,8 +119,9 @@ enum {
                                   whose rerank rows stay on the host */
     PSB_EXACT_HOST_HYBRID = 4  /* both host transports at once: the rows are registered and mapped as in HOST_MAPPED, and of every
                                   sub-batch psb_options.zero_copy_pct percent of the queries have their rows gathered by a kernel
-                                  over PCIe while host threads stage the others through the pinned rings; neither the host
-                                  cores nor the kernel's reads fill the link alone */
+                                  over PCIe - on reserve_sms SMs of its own (default 32), which the scan's grid leaves free -
+                                  while host threads stage the others through the pinned rings; neither the host cores nor
+                                  the kernel's reads fill the link alone */
 };
 
 /* IVFPQSearchOptions (src/search/ivfpq/ivfpq_search_context.h:31-45) reduced to what this path uses,
@@ -166,7 +167,7 @@ typedef struct psb_options {
        memory and returns, and the call reports PSB_TIMEOUT. */
     int test_wait_limit;
     int test_skip_mma;
-    int zero_copy_pct;  /* PSB_EXACT_HOST_HYBRID: share of each sub-batch gathered by the kernel, 1..99 (0 = 40) */
+    int zero_copy_pct;  /* PSB_EXACT_HOST_HYBRID: share of each sub-batch gathered by the kernel, 1..99 (0 = 45) */
     /* Residual mode, optional: the per-row correction asset of the index, value[row] = |recon(row)|^2 + 2 <centroid[list(row)],
        recon(row)> (src/common/row_correction.h:37-45), as HOST arrays over the rows of the view - either fp32 or the affine u16
        form (value = rc_offset + rc_scale * u16, src/common/row_correction.h:7-20).  The residual cutoff estimate reads it;

@@ -738,6 +738,8 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if (opt.scan_mode < 0 || opt.scan_mode > 3) return fail(PSB_INVALID_ARGUMENT, "scan_mode must be in 0..3");
     if (opt.tc_min_visitors < 0) return fail(PSB_INVALID_ARGUMENT, "tc_min_visitors must not be negative");
     if (opt.zero_copy_pct < 0 || opt.zero_copy_pct > 99) return fail(PSB_INVALID_ARGUMENT, "zero_copy_pct must be in 0..99");
+    // hybrid transport: the gather kernel runs beside the scan on SMs of its own, which the scan's grid has to leave free
+    if (opt.exact_mode == PSB_EXACT_HOST_HYBRID && opt.reserve_sms == 0 && opt.gather_ctas == 0) opt.reserve_sms = 32;
     if (opt.gather_ctas < 0 || opt.gather_ctas > 1024) return fail(PSB_INVALID_ARGUMENT, "gather_ctas must be in 0..1024");
     if (opt.adc_mode == 1 && !index->exact.fp32 && !index->exact.u8)
         return fail(PSB_INVALID_ARGUMENT, "residual mode always reranks: exact rows are required");
@@ -1090,7 +1092,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     // ~60 ms of scanning), so it should start as early as possible: the first sub-batch is the small one (10/30/30/30 %).
     std::vector<int> cuts;
     const int plan = s->opt.even_cuts;
-    if (staged_overlap && !residual && sb * 4 >= n && n >= 4096 && plan != 1) {
+    if (staged_overlap && (!residual || residual_table_free(s, stage1_k)) && sb * 4 >= n && n >= 4096 && plan != 1) {
         if (plan == 2) cuts = {0, (int)(0.32 * n), (int)(0.64 * n), (int)(0.90 * n), n};  // short last sub-batch (scan-bound hosts)
         else cuts = {0, (int)(0.10 * n), (int)(0.40 * n), (int)(0.70 * n), n};
     } else {
@@ -1133,7 +1135,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     std::string worker_msg;
     std::thread worker;
     const bool hybrid = staged_overlap && s->opt.exact_mode == PSB_EXACT_HOST_HYBRID && s->exact_dev != nullptr;
-    const int zc_pct = s->opt.zero_copy_pct > 0 ? s->opt.zero_copy_pct : 40;
+    const int zc_pct = s->opt.zero_copy_pct > 0 ? s->opt.zero_copy_pct : 45;
     if (hybrid && !s->zc_stream) {
         int lo = 0, hi = 0;
         PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -1167,10 +1169,12 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
                 if (mz > 0) {
                     PSB_CUDA(cudaEventRecord(s->zc_begin, sx));
                     PSB_CUDA(cudaStreamWaitEvent(s->zc_stream, s->zc_begin, 0));
+                    // on the SMs the scan's grid leaves free (reserve_sms), unless the caller asked for lean CTAs on all SMs
                     PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, cand_d + (size_t)mh * stage1_k, mz, stage1_k,
                                                stage1_k, cnt_d + mh,
                                                static_cast<unsigned char*>(s->stage.p) + (size_t)mh * stage1_k * s->dim * s->exact_elem,
-                                               s->zc_stream, s->sm_count, s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count));
+                                               s->zc_stream, s->sm_count, s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count,
+                                               s->opt.gather_ctas > 0 ? 0 : s->opt.reserve_sms));
                     PSB_CUDA(cudaEventRecord(s->zc_end, s->zc_stream));
                 }
                 if (mh > 0) PSB_TRY(staged_gather_host(s, s->h_cand_pinned + (size_t)j.p0 * stage1_k, mh, stage1_k, stage1_k, s->stage.p, sx));
