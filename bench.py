@@ -325,7 +325,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0, help="queries in the CPU baseline sample (0 = auto)")
     ap.add_argument("--exact-mode", default="auto", choices=["auto", "mapped", "staged", "cached", "hybrid"],
                     help="rerank transport on one GPU: staged = host threads gather rows into pinned rings and cudaMemcpyAsync moves "
-                         "them (no SM time spent on the transfer), mapped = kernels gather mapped host rows over PCIe; auto = staged "
+                         "them (no SM time spent on the transfer), mapped = kernels gather mapped host rows over PCIe; "
                          "auto = hybrid when a batch gathers at least 2 GB (the scan is then long enough to run beside the transfer), else mapped; "
                          "cached = the session copies the rows into device memory once (not the host-resident configuration the "
                          "headline metric names: an extra data point); hybrid = staged and mapped at once, --zero-copy-pct of every "
