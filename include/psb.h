@@ -225,6 +225,10 @@ typedef struct psb_session psb_session;
 const char* psb_last_error(void);
 /* Number of usable sm_100 devices (0 when there is no GPU or no driver). */
 int psb_device_count(void);
+/* sizeof of a struct of this header as the library was built with it (0 psb_options, 1 psb_stats, 2 psb_index_view,
+ * 3 psb_flat_index_view, 4 psb_row_correction_u16_header, 5 psb_search_params): lets a binding in another language check its
+ * own declaration of the struct before it passes one. */
+size_t psb_sizeof(int which);
 const char* psb_version(void);
 
 /* ---- session: prepare once, search many ----------------------------------------------------------- */

@@ -697,6 +697,18 @@ extern "C" {
 const char* psb_last_error(void) { return last_error_ref().c_str(); }
 const char* psb_version(void) { return kNvtxCompiled ? "paraselect-b200 0.1 (sm_100a, nvtx)" : "paraselect-b200 0.1 (sm_100a)"; }
 
+size_t psb_sizeof(int which) {
+    switch (which) {
+        case 0: return sizeof(psb_options);
+        case 1: return sizeof(psb_stats);
+        case 2: return sizeof(psb_index_view);
+        case 3: return sizeof(psb_flat_index_view);
+        case 4: return sizeof(psb_row_correction_u16_header);
+        case 5: return sizeof(psb_search_params);
+        default: return 0;
+    }
+}
+
 int psb_device_count(void) {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }

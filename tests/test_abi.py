@@ -133,3 +133,11 @@ def test_nvtx_variant_builds_and_exports_the_same_symbols(lib):
     assert b"nvtx" in nv.psb_version() and b"nvtx" not in lib.psb_version()
     for name in api.EXPORTS:
         assert hasattr(nv, name), name
+
+
+def test_ctypes_structs_have_the_sizes_the_library_was_built_with(lib):
+    lib.psb_sizeof.restype = C.c_size_t
+    for which, struct in ((0, api.Options), (1, api.Stats), (2, api.IndexView), (3, api.FlatIndexView), (4, api.RowCorrectionHeader),
+                          (5, api.SearchParams)):
+        assert lib.psb_sizeof(which) == C.sizeof(struct), struct.__name__
+    assert lib.psb_sizeof(99) == 0
