@@ -227,7 +227,7 @@ struct psb_session {
     bool own_stream = false;
     cudaStream_t aux_stream = nullptr;  // second stream of the overlapped pipeline (created on first use)
     cudaStream_t zc_stream = nullptr;   // hybrid transport: the kernel gather runs here, beside the copies of aux_stream
-    cudaEvent_t zc_begin = nullptr, zc_end = nullptr;
+
     cudaStream_t home_stream = nullptr; // the stream the session was created with (psb_session_set_stream(NULL) returns to it)
     bool background = false;            // stage calls currently run on a caller's second stream: small-grid gather
     psb_options opt{};
@@ -296,8 +296,7 @@ struct psb_session {
         if (h_cand_pinned) cudaFreeHost(h_cand_pinned);
         if (aux_stream) { cudaStreamSynchronize(aux_stream); cudaStreamDestroy(aux_stream); }
         if (zc_stream) { cudaStreamSynchronize(zc_stream); cudaStreamDestroy(zc_stream); }
-        if (zc_begin) cudaEventDestroy(zc_begin);
-        if (zc_end) cudaEventDestroy(zc_end);
+
         if (own_stream && stream) cudaStreamDestroy(stream);
         cudaGetLastError();
     }
@@ -1138,7 +1137,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
         PSB_CUDA(cudaStreamWaitEvent(sx, e0, 0));
     }
     psb_status rc = PSB_OK;
-    struct Job { int p0, m; cudaEvent_t ready; };
+    struct Job { int p0, m; cudaEvent_t ready; int mz; cudaEvent_t gathered; };
     std::mutex mu;
     std::condition_variable cv;
     std::deque<Job> jobs;
@@ -1151,9 +1150,10 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     if (hybrid && !s->zc_stream) {
         int lo = 0, hi = 0;
         PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-        PSB_CUDA(cudaStreamCreateWithPriority(&s->zc_stream, cudaStreamNonBlocking, lo));
-        PSB_CUDA(cudaEventCreateWithFlags(&s->zc_begin, cudaEventDisableTiming));
-        PSB_CUDA(cudaEventCreateWithFlags(&s->zc_end, cudaEventDisableTiming));
+        // Highest priority: the gather of sub-batch i is queued before the kernels of sub-batch i + 1 and becomes runnable at
+        // the same moment as they do (when the scan stage of sub-batch i ends and every SM is empty); its few CTAs, which need
+        // an SM each to themselves, must be placed first.
+        PSB_CUDA(cudaStreamCreateWithPriority(&s->zc_stream, cudaStreamNonBlocking, hi));
     }
     if (staged_overlap) {
         const size_t cand_count = (size_t)n * stage1_k;
@@ -1163,7 +1163,9 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
             PSB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&s->h_cand_pinned), sizeof(int) * cand_count, cudaHostAllocDefault));
             s->h_cand_pinned_count = cand_count;
         }
-        PSB_TRY(s->stage.reserve((size_t)sb_max * stage1_k * s->dim * s->exact_elem));
+        // Hybrid transport: every sub-batch has a staging region of its own (the whole batch: nq * stage1_k rows of device
+        // memory), so that the gather kernel of a sub-batch depends on nothing but that sub-batch's scan.
+        PSB_TRY(s->stage.reserve((size_t)(hybrid ? n : sb_max) * stage1_k * s->dim * s->exact_elem));
         PSB_TRY(s->score.reserve(sizeof(float) * (size_t)sb_max * stage1_k));
         worker = std::thread([&]() {
             cudaSetDevice(s->device);
@@ -1173,26 +1175,16 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
                 const int* cand_d = s->cand_rows.as<int>() + (size_t)j.p0 * stage1_k;
                 const int* cnt_d = s->cand_count.as<int>() + j.p0;
                 if (times) PSB_TRY(tm_x.mark(sx));
-                // Hybrid transport: the last mz queries' rows are fetched by the gather kernel on a stream of its own (it may not
-                // start before the previous sub-batch's scoring has let go of the staging buffer) while the host threads and
-                // the copy engine bring the others; the scoring waits for both.
-                const int mz = hybrid ? (int)((long long)j.m * zc_pct / 100) : 0;
-                const int mh = j.m - mz;
-                if (mz > 0) {
-                    PSB_CUDA(cudaEventRecord(s->zc_begin, sx));
-                    PSB_CUDA(cudaStreamWaitEvent(s->zc_stream, s->zc_begin, 0));
-                    // on the SMs the scan's grid leaves free (reserve_sms), unless the caller asked for lean CTAs on all SMs
-                    PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, cand_d + (size_t)mh * stage1_k, mz, stage1_k,
-                                               stage1_k, cnt_d + mh,
-                                               static_cast<unsigned char*>(s->stage.p) + (size_t)mh * stage1_k * s->dim * s->exact_elem,
-                                               s->zc_stream, s->sm_count, s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count,
-                                               s->opt.gather_ctas > 0 ? 0 : s->opt.reserve_sms));
-                    PSB_CUDA(cudaEventRecord(s->zc_end, s->zc_stream));
-                }
-                if (mh > 0) PSB_TRY(staged_gather_host(s, s->h_cand_pinned + (size_t)j.p0 * stage1_k, mh, stage1_k, stage1_k, s->stage.p, sx));
-                if (mz > 0) PSB_CUDA(cudaStreamWaitEvent(sx, s->zc_end, 0));
+                // Hybrid transport: the rows of the last j.mz queries come through the gather kernel, which the main thread queued
+                // right behind this sub-batch's scan (j.gathered marks its end); the host threads and the copy engine bring the
+                // others; the scoring waits for both.
+                const int mh = j.m - j.mz;
+                unsigned char* region = static_cast<unsigned char*>(s->stage.p) +
+                                        (hybrid ? (size_t)j.p0 * stage1_k * s->dim * s->exact_elem : 0);
+                if (mh > 0) PSB_TRY(staged_gather_host(s, s->h_cand_pinned + (size_t)j.p0 * stage1_k, mh, stage1_k, stage1_k, region, sx));
+                if (j.mz > 0) PSB_CUDA(cudaStreamWaitEvent(sx, j.gathered, 0));
                 const unsigned char* qe = static_cast<const unsigned char*>(dq_exact) + (size_t)j.p0 * s->dim * s->exact_elem;
-                PSB_TRY(launch_rerank_score(s->stage.p, s->row_map(), s->dim, s->exact_elem, qe, cand_d, j.m, stage1_k, stage1_k,
+                PSB_TRY(launch_rerank_score(region, s->row_map(), s->dim, s->exact_elem, qe, cand_d, j.m, stage1_k, stage1_k,
                                             cnt_d, s->score.as<float>(), sx));
                 PSB_TRY(launch_topk_select(s->score.as<float>(), cand_d, j.m, stage1_k, stage1_k, cnt_d, topk,
                                            s->out_rows.as<int>() + (size_t)j.p0 * topk, d_dist + (size_t)j.p0 * topk, sx));
@@ -1272,9 +1264,29 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
             cudaEvent_t e;
             if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { rc = fail(PSB_CUDA_ERROR, "event creation failed"); break; }
             deps.push_back(e);
+            const int mz = hybrid ? (int)((long long)m * zc_pct / 100) : 0;
+            cudaEvent_t gathered = nullptr;
+            if (mz > 0) {   // the kernel's share of the transfer, queued now: it starts the moment this sub-batch's scan stage ends
+                cudaEvent_t scanned;
+                if (cudaEventCreateWithFlags(&scanned, cudaEventDisableTiming) != cudaSuccess ||
+                    cudaEventCreateWithFlags(&gathered, cudaEventDisableTiming) != cudaSuccess) { rc = fail(PSB_CUDA_ERROR, "event creation failed"); break; }
+                deps.push_back(scanned);
+                deps.push_back(gathered);
+                cudaEventRecord(scanned, st);
+                cudaStreamWaitEvent(s->zc_stream, scanned, 0);
+                const int mh = m - mz;
+                // on the SMs the scan's grid leaves free (reserve_sms), unless the caller asked for lean CTAs on all SMs
+                rc = launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, rows_out + (size_t)mh * stage1_k, mz, stage1_k, stage1_k,
+                                        cnt_out + mh,
+                                        static_cast<unsigned char*>(s->stage.p) + (size_t)(p0 + mh) * stage1_k * s->dim * s->exact_elem,
+                                        s->zc_stream, s->sm_count, s->opt.gather_ctas > 0 ? s->opt.gather_ctas : 2 * s->sm_count,
+                                        s->opt.gather_ctas > 0 ? 0 : s->opt.reserve_sms);
+                if (rc != PSB_OK) break;
+                cudaEventRecord(gathered, s->zc_stream);
+            }
             cudaMemcpyAsync(s->h_cand_pinned + (size_t)p0 * stage1_k, rows_out, sizeof(int) * (size_t)m * stage1_k, cudaMemcpyDeviceToHost, st);
             cudaEventRecord(e, st);
-            { std::lock_guard<std::mutex> lk(mu); jobs.push_back(Job{p0, m, e}); }
+            { std::lock_guard<std::mutex> lk(mu); jobs.push_back(Job{p0, m, e, mz, gathered}); }
             cv.notify_all();
             continue;
         }
