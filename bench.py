@@ -364,6 +364,7 @@ def main():
         cfg["nprobe"] = min(cfg["nprobe"], cfg["nlist"])
     if args.queries:
         cfg["nq"] = args.queries
+    auto_mode = args.exact_mode == "auto"
     if args.exact_mode == "auto":
         gathered = cfg["nq"] * max(cfg["n_rerank"], cfg["topk"]) * cfg["dim"] * 4
         args.exact_mode = "hybrid" if gathered >= 2e9 else "mapped"
@@ -410,13 +411,22 @@ def main():
 
         h2d_gbs = measure_h2d_gbs(torch)
         t0 = time.time()
-        sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas, serial_pipeline=args.serial,
-                           pipeline_parts=args.pipeline_parts, even_cuts=args.cut_plan,
-                           reserve_sms=max(0, args.n1_reserve_sms),
-                           zero_copy_pct=args.zero_copy_pct,
-                           exact_mode={"staged": api.EXACT_HOST_STAGED, "cached": api.EXACT_HOST_CACHED, "hybrid": api.EXACT_HOST_HYBRID}.get(args.exact_mode,
-                                                                                                            api.EXACT_HOST_MAPPED))
+        def make_session(mode):
+            return api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
+                               residual=bool(cfg.get("residual")), gather_ctas=args.gather_ctas, serial_pipeline=args.serial,
+                               pipeline_parts=args.pipeline_parts, even_cuts=args.cut_plan,
+                               reserve_sms=max(0, args.n1_reserve_sms), zero_copy_pct=args.zero_copy_pct,
+                               exact_mode={"staged": api.EXACT_HOST_STAGED, "cached": api.EXACT_HOST_CACHED,
+                                           "hybrid": api.EXACT_HOST_HYBRID}.get(mode, api.EXACT_HOST_MAPPED))
+        try:
+            sess = make_session(args.exact_mode)
+        except api.PsbError as e:
+            if not (auto_mode and args.exact_mode == "hybrid"):
+                raise
+            # a host that does not let 38 GB of rows be registered: the staged transport needs no registration
+            log("hybrid transport unavailable (%s): falling back to the staged transport" % e)
+            args.exact_mode = "staged"
+            sess = make_session("staged")
         log("session created in %.1fs" % (time.time() - t0))
         stage1 = min(R, cfg["n"]) if R > topk else topk
         d_probes = torch.empty((nq, nprobe), dtype=torch.int32, device="cuda")
