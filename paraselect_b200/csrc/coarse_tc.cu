@@ -70,6 +70,9 @@ struct TcArgs {
     int mwords;             // ntiles * TCOL / 32
     int* status;            // [1] != 0 after a bounded wait gave up
     int cblocks, qtiles;    // work = cblocks (512 centroids each) x qtiles (128 queries each) tile pairs
+    int* cand_cnt;          // pass 2, list form (nearest-centroid assignment with a known bound): [nq] candidates found so far
+    int* cand_list;         //   [nq][cand_cap] their ids; null: the bit mask above is written instead
+    int cand_cap;
     int wait_limit;         // polls before a wait gives up (0: kWaitLimit)
     int skip_loads;         // test hook of the time-out path: the producer issues no load at all, so nothing is in flight when
                             // the other roles give up
@@ -264,7 +267,18 @@ k_coarse_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                                 uint32_t bits = 0;
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) bits |= (v[j] >= cut ? 1u : 0u) << j;
-                                if (bits) a.mask[(size_t)q * a.mwords + (c0 >> 5)] = bits;
+                                if (bits) {
+                                    if (a.cand_list) {   // a handful of candidates per row: a short list instead of a mask to scan
+                                        while (bits) {
+                                            const int j = __ffs((int)bits) - 1;
+                                            bits &= bits - 1;
+                                            const int pos = atomicAdd(&a.cand_cnt[q], 1);
+                                            if (pos < a.cand_cap) a.cand_list[(size_t)q * a.cand_cap + pos] = c0 + j;
+                                        }
+                                    } else {
+                                        a.mask[(size_t)q * a.mwords + (c0 >> 5)] = bits;
+                                    }
+                                }
                             }
                         }
                     }
@@ -412,6 +426,87 @@ k_coarse_refine(const float* __restrict__ queries, const float* __restrict__ cen
     }
 }
 
+// ---- nearest-centroid assignment with a bound known beforehand (Lloyd iterations after the first) -------------------------
+// A row's distance to the centroid it was assigned to in the previous iteration, at that centroid's NEW position, bounds its
+// distance to the nearest centroid from above.  With that bound in place of pass 1's group minimum the GEMM runs once: the
+// candidates (every centroid whose bf16 estimate is within the bound plus the rounding slack - the nearest one and all its
+// ties among them) go to a short per-row list, and k_coarse_refine1 picks the exact nearest in the CPU path's arithmetic.
+constexpr int kAssignCap = 32;   // candidates kept per row (one per lane of the refining warp); more: the exact per-row kernel
+// seltop[row] = (bound on the squared distance) - |q'|^2, the quantity pass 2 compares a = |c'|^2 - 2 q'.c' against.
+__global__ void k_prev_bound(const float* __restrict__ rows, long long n, int dim, const float* __restrict__ centroids, int nlist,
+                             const int* __restrict__ prev, const float* __restrict__ qnorm, float* __restrict__ seltop) {
+    const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= n) return;
+    const int c = prev[r];
+    float acc = 0.0f;
+    const bool ok = c >= 0 && c < nlist;
+    if (ok) {
+        const float* x = rows + (size_t)r * dim;
+        const float* cp = centroids + (size_t)c * dim;
+        for (int d = lane; d < dim; d += 32) { const float diff = x[d] - __ldg(cp + d); acc = fmaf(diff, diff, acc); }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        const float qn = qnorm[r];
+        // a bound, not a result: one part in 1e5 covers the different summation order
+        seltop[r] = ok ? acc * (1.0f + 1e-5f) - qn * qn : __int_as_float(0x7f800000);
+    }
+}
+// One warp per row: lane i re-scores candidate i exactly (sequential non-fused fp32, the CPU path's arithmetic), the warp
+// takes the smallest (distance, id).  No candidate or too many: the row goes to the exact per-row kernel.
+__global__ void __launch_bounds__(256) k_coarse_refine1(const float* __restrict__ rows, const float* __restrict__ centroids, int dim,
+                                                        long long n, const int* __restrict__ cand_cnt, const int* __restrict__ cand_list,
+                                                        int* __restrict__ out_ids, float* __restrict__ out_dist,
+                                                        int* __restrict__ fail_list, int* __restrict__ n_fail) {
+    const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= n) return;
+    const int cnt = cand_cnt[r];
+    if (cnt <= 0 || cnt > kAssignCap) {
+        if (lane == 0) {
+            fail_list[atomicAdd(n_fail, 1)] = (int)r;
+            atomicAdd(n_fail + 3, 1);
+        }
+        return;
+    }
+    uint64_t key = KEY_MAX;
+    if (lane < cnt) {
+        const int c = cand_list[(size_t)r * kAssignCap + lane];
+        const float* x = rows + (size_t)r * dim;
+        const float* cp = centroids + (size_t)c * dim;
+        float sum = 0.0f;
+        if ((dim & 3) == 0) {
+            const float4* cp4 = reinterpret_cast<const float4*>(cp);
+            const float4* x4 = reinterpret_cast<const float4*>(x);
+            for (int d = 0; d < dim / 4; ++d) {
+                const float4 a = __ldg(cp4 + d);
+                const float4 b = __ldg(x4 + d);
+                float diff = __fsub_rn(b.x, a.x); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                diff = __fsub_rn(b.y, a.y); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                diff = __fsub_rn(b.z, a.z); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+                diff = __fsub_rn(b.w, a.w); sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) {
+                const float diff = __fsub_rn(__ldg(x + d), __ldg(cp + d));
+                sum = __fadd_rn(sum, __fmul_rn(diff, diff));
+            }
+        }
+        key = make_key(sum, (uint32_t)c);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const uint64_t other = __shfl_xor_sync(0xffffffffu, key, o);
+        key = other < key ? other : key;
+    }
+    if (lane == 0) {
+        out_ids[r] = (int)key_idx(key);
+        if (out_dist) out_dist[r] = key_dist(key);
+    }
+}
+
 // Whole-row exact coarse search for the queries on the fail list: running cut-off buffer, one CTA per query.
 constexpr int kExactThreads = 1024;
 __global__ void __launch_bounds__(kExactThreads)
@@ -550,6 +645,7 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
     while ((1 << a.lg_group) < group) ++a.lg_group;
     a.nprobe = nprobe; a.cn2 = ix.cn2; a.qnorm = ws.qnorm; a.cmax = ix.cmax; a.gmin = ws.gmin; a.seltop = ws.seltop;
     a.mask = reinterpret_cast<uint32_t*>(ws.cand); a.mwords = coarse_tc_mask_words(ix.nlist); a.status = ws.status;
+    a.cand_cnt = nullptr; a.cand_list = nullptr; a.cand_cap = 0;
     a.wait_limit = ws.test_wait_limit; a.skip_loads = ws.test_skip_loads;
     const size_t smem = (size_t)katoms * (kStagesA * TQ + 2 * TCOL) * 128 + 1024;
     PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -599,6 +695,65 @@ psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws
             PSB_CUDA(cudaFuncSetAttribute(k_coarse_exact_query, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)esmem));
         k_coarse_exact_query<<<sm_count, kExactThreads, esmem, s>>>(d_queries, ix.centroids, ix.dim, ix.nlist, nprobe, buf_n,
                                                                     ws.fail_list, ws.n_fail, ws.n_fail + 1, d_ids, d_dist);
+        count_launch();
+        PSB_LAUNCH_CHECK();
+    }
+    return PSB_OK;
+}
+
+// Nearest centroid of every row when a previous assignment is known (d_prev [nq], may alias d_ids): ONE GEMM pass.
+psb_status launch_coarse_tc_assign(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws, const float* d_rows, int nq, const int* d_prev,
+                                   int* d_ids, float* d_dist, int sm_count, cudaStream_t s) {
+    if (nq <= 0) return PSB_OK;
+    const int dimp = coarse_tc_padded_dim(ix.dim);
+    const int katoms = dimp / KATOM;
+    const int ntiles = coarse_tc_tiles(ix.nlist);
+    const bool aug = dimp - ix.dim >= 3;
+    if (coarse_tc_mask_words(ix.nlist) < kAssignCap) return fail(PSB_INTERNAL, "candidate buffer too small for the list form");
+    k_tc_prep_rows<<<(nq * 32 + 255) / 256, 256, 0, s>>>(d_rows, nq, ix.dim, dimp, ix.mu, static_cast<__nv_bfloat16*>(ws.qb), ws.qnorm,
+                                                         nullptr, aug ? 1 : 0);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    k_prev_bound<<<(unsigned)(((long long)nq * 32 + 255) / 256), 256, 0, s>>>(d_rows, nq, ix.dim, ix.centroids, ix.nlist, d_prev, ws.qnorm,
+                                                                              ws.seltop);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    CUtensorMap map_q, map_c;
+    PSB_TRY(encode_rows_map(&map_q, ws.qb, nq, dimp, TQ));
+    PSB_TRY(encode_rows_map(&map_c, ix.cb, ix.nlist, dimp, TCOL));
+    TcArgs a;
+    a.nq = nq; a.nlist = ix.nlist; a.katoms = katoms; a.ntiles = ntiles; a.group = 32; a.lg_group = 5; a.ngroups = ntiles * (TCOL / 32);
+    a.nprobe = 1; a.cn2 = ix.cn2; a.qnorm = ws.qnorm; a.cmax = ix.cmax; a.gmin = ws.gmin; a.seltop = ws.seltop;
+    a.mask = nullptr; a.mwords = coarse_tc_mask_words(ix.nlist); a.status = ws.status;
+    a.cand_cnt = ws.cand_cnt; a.cand_list = ws.cand; a.cand_cap = kAssignCap;
+    a.wait_limit = ws.test_wait_limit; a.skip_loads = ws.test_skip_loads;
+    const size_t smem = (size_t)katoms * (kStagesA * TQ + 2 * TCOL) * 128 + 1024;
+    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PSB_CUDA(cudaFuncSetAttribute(k_coarse_tc<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    a.qtiles = (nq + TQ - 1) / TQ;
+    a.cblocks = ntiles / 2;
+    const long long pairs = (long long)a.cblocks * a.qtiles;
+    const dim3 grid((unsigned)(pairs < sm_count ? pairs : sm_count));
+    PSB_CUDA(cudaMemsetAsync(ws.cand_cnt, 0, sizeof(int) * (size_t)nq, s));
+    PSB_CUDA(cudaMemsetAsync(ws.n_fail, 0, 2 * sizeof(int), s));  // n_fail, cursor
+    if (ws.ev[2]) PSB_CUDA(cudaEventRecord(ws.ev[2], s));
+    if (aug) k_coarse_tc<true, true><<<grid, kTcThreadsV2, smem, s>>>(map_q, map_c, a);
+    else k_coarse_tc<true, false><<<grid, kTcThreadsV2, smem, s>>>(map_q, map_c, a);
+    if (ws.ev[3]) PSB_CUDA(cudaEventRecord(ws.ev[3], s));
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    k_coarse_refine1<<<(unsigned)(((long long)nq * 32 + 255) / 256), 256, 0, s>>>(d_rows, ix.centroids, ix.dim, nq, ws.cand_cnt, ws.cand, d_ids,
+                                                                                  d_dist, ws.fail_list, ws.n_fail);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    {
+        int buf_n = 2048;
+        while (buf_n < 1 + kExactThreads) buf_n <<= 1;
+        const size_t esmem = (size_t)buf_n * 8 + (size_t)ix.dim * sizeof(float);
+        if (esmem > 32 * 1024)
+            PSB_CUDA(cudaFuncSetAttribute(k_coarse_exact_query, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)esmem));
+        k_coarse_exact_query<<<sm_count, kExactThreads, esmem, s>>>(d_rows, ix.centroids, ix.dim, ix.nlist, 1, buf_n, ws.fail_list, ws.n_fail,
+                                                                    ws.n_fail + 1, d_ids, d_dist);
         count_launch();
         PSB_LAUNCH_CHECK();
     }

@@ -68,6 +68,12 @@ psb_status launch_tc_prep_centroids(const float* d_centroids, int nlist, int dim
 psb_status launch_coarse_tc(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws, const float* d_queries, int nq,
                             int nprobe, int* d_ids, float* d_dist, int sm_count, cudaStream_t s);
 
+// Nearest centroid of every row with a previous assignment at hand (d_prev [nq]; may alias d_ids): the row's distance to its
+// previous centroid bounds the nearest distance, so the filter GEMM runs once instead of twice.  Same results as
+// launch_coarse_tc(..., nprobe = 1, ...).
+psb_status launch_coarse_tc_assign(const CoarseTcIndex& ix, const CoarseTcWorkspace& ws, const float* d_rows, int nq, const int* d_prev,
+                                   int* d_ids, float* d_dist, int sm_count, cudaStream_t s);
+
 // ---- OPQ rotation --------------------------------------------------------------------------------------
 // d_out [n][dim] = rows of d_in times the transpose of d_matrix (row-major [out][in]): out[r][o] = sum_i M[o][i] in[r][i], one
 // in-order fp32 fma chain per element.  d_out must not alias d_in.

@@ -1764,8 +1764,14 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
             const int nn = (int)std::min<long long>(chunk, n - r0);
             if (tc && coarse_tc_supported(nn, k, dim, 1)) {
                 PSB_TRY(tcw.ensure(nn, k, dim, 1, st));
-                PSB_TRY(launch_coarse_tc(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, 1,
-                                         d_as + r0, best.as<float>() + r0, prop.multiProcessorCount, st));
+                // After the first iteration every row brings a bound along - its distance to the centroid it had, where that
+                // centroid is now - and the filter GEMM runs once instead of twice.
+                if (it > 0)
+                    PSB_TRY(launch_coarse_tc_assign(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, d_as + r0,
+                                                    d_as + r0, best.as<float>() + r0, prop.multiProcessorCount, st));
+                else
+                    PSB_TRY(launch_coarse_tc(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, 1,
+                                             d_as + r0, best.as<float>() + r0, prop.multiProcessorCount, st));
             } else {
                 PSB_TRY(tile.reserve(row_bytes * (size_t)nn));
                 PSB_TRY(launch_coarse_dist_exact(d_data + (size_t)r0 * dim, nn, d_centroids, k, dim, tile.as<float>(), st));
