@@ -492,6 +492,11 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
  *   update:     centroid = sums / counts rounded once to fp32; an empty cluster keeps its centroid */
 psb_status psb_kmeans_assign(const float* d_data, int64_t n, int dim, const float* d_centroids, int k, int* d_assign,
                              float* d_best, int device, void* stream);
+/* psb_kmeans_assign with the previous iteration's assignment at hand: have_previous != 0 says d_assign holds, on entry, a valid
+ * centroid id per row (any ids in 0..k-1 do; ids outside send the row to the exact per-row path).  Each row's distance to that
+ * centroid bounds its nearest distance, and the tensor-core filter runs once instead of twice; the result is the same. */
+psb_status psb_kmeans_assign_bounded(const float* d_data, int64_t n, int dim, const float* d_centroids, int k, int* d_assign,
+                                     float* d_best, int have_previous, int device, void* stream);
 psb_status psb_kmeans_accumulate(const float* d_data, int64_t n, int dim, const int* d_assign, const float* d_best, int k,
                                  double* d_sums, int* d_counts, double* d_objective, int device, void* stream);
 psb_status psb_kmeans_update(const double* d_sums, const int* d_counts, int k, int dim, float* d_centroids, int device,

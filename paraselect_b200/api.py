@@ -102,7 +102,7 @@ EXPORTS = [
     "psb_flat_session_create", "psb_flat_session_search", "psb_flat_session_search_device", "psb_flat_session_destroy",
     "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
     "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
-    "psb_sizeof", "psb_group_create", "psb_group_set", "psb_group_search_device", "psb_group_searched_again", "psb_group_destroy",
+    "psb_sizeof", "psb_kmeans_assign_bounded", "psb_group_create", "psb_group_set", "psb_group_search_device", "psb_group_searched_again", "psb_group_destroy",
     "psb_kmeans_init", "psb_rotate_rows", "psb_stage_rotate_queries", "psb_scan_sample_words", "psb_stage_scan_sample", "psb_stage_scan_shared",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -584,9 +584,11 @@ def kmeans_train(d_data, n, dim, d_centroids, k, iters, d_assign=None, device=0,
     return obj
 
 
-def kmeans_assign(d_data, n, dim, d_centroids, k, d_assign, d_best, device=0, stream=None):
-    _check(lib().psb_kmeans_assign(C.c_void_p(_p(d_data)), C.c_int64(n), dim, C.c_void_p(_p(d_centroids)), k,
-                                   C.c_void_p(_p(d_assign)), C.c_void_p(_p(d_best)), device, _stream_ptr(stream)))
+def kmeans_assign(d_data, n, dim, d_centroids, k, d_assign, d_best, device=0, stream=None, have_previous=False):
+    """have_previous: d_assign holds the previous iteration's assignment on entry (one filter pass instead of two)."""
+    _check(lib().psb_kmeans_assign_bounded(C.c_void_p(_p(d_data)), C.c_int64(n), dim, C.c_void_p(_p(d_centroids)), k,
+                                           C.c_void_p(_p(d_assign)), C.c_void_p(_p(d_best)), int(bool(have_previous)), device,
+                                           _stream_ptr(stream)))
 
 
 def kmeans_accumulate(d_data, n, dim, d_assign, d_best, k, d_sums, d_counts, d_objective, device=0, stream=None):

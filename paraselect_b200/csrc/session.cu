@@ -1793,6 +1793,11 @@ psb_status psb_kmeans_train(const float* d_data, int64_t n, int dim, float* d_ce
 
 psb_status psb_kmeans_assign(const float* d_data, int64_t n, int dim, const float* d_centroids, int k, int* d_assign,
                              float* d_best, int device, void* stream) {
+    return psb_kmeans_assign_bounded(d_data, n, dim, d_centroids, k, d_assign, d_best, 0, device, stream);
+}
+
+psb_status psb_kmeans_assign_bounded(const float* d_data, int64_t n, int dim, const float* d_centroids, int k, int* d_assign,
+                                     float* d_best, int have_previous, int device, void* stream) {
     if (!d_data || !d_centroids || !d_assign || !d_best || n <= 0 || dim <= 0 || k <= 0)
         return fail(PSB_INVALID_ARGUMENT, "invalid k-means assignment request");
     cudaDeviceProp prop;
@@ -1816,8 +1821,12 @@ psb_status psb_kmeans_assign(const float* d_data, int64_t n, int dim, const floa
         const int nn = (int)std::min<long long>(chunk, n - r0);
         if (tc && coarse_tc_supported(nn, k, dim, 1)) {
             PSB_TRY(tcw.ensure(nn, k, dim, 1, st));
-            PSB_TRY(launch_coarse_tc(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, 1, d_assign + r0,
-                                     d_best + r0, prop.multiProcessorCount, st));
+            if (have_previous)
+                PSB_TRY(launch_coarse_tc_assign(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, d_assign + r0,
+                                                d_assign + r0, d_best + r0, prop.multiProcessorCount, st));
+            else
+                PSB_TRY(launch_coarse_tc(tci.view(d_centroids, k, dim), tcw.view(), d_data + (size_t)r0 * dim, nn, 1, d_assign + r0,
+                                         d_best + r0, prop.multiProcessorCount, st));
         } else {
             PSB_TRY(tile.reserve(row_bytes * (size_t)nn));
             PSB_TRY(launch_coarse_dist_exact(d_data + (size_t)r0 * dim, nn, d_centroids, k, dim, tile.as<float>(), st));

@@ -371,6 +371,8 @@ class ShardedSearch:
 class TrainEngine:
     """The CUDA library's three-call Lloyd iteration on torch CUDA tensors (calls run on torch's current stream)."""
 
+    bounded_assign = True   # assign() can take the previous assignment as a bound
+
     def __init__(self, api, torch, device=0):
         self.api, self.torch, self.device = api, torch, device
 
@@ -380,8 +382,8 @@ class TrainEngine:
     def empty(self, shape, dtype):
         return self.torch.empty(shape, dtype=dtype, device="cuda")
 
-    def assign(self, x, n, dim, cen, k, assign, best):
-        self.api.kmeans_assign(x, n, dim, cen, k, assign, best, device=self.device, stream=self._st())
+    def assign(self, x, n, dim, cen, k, assign, best, have_previous=False):
+        self.api.kmeans_assign(x, n, dim, cen, k, assign, best, device=self.device, stream=self._st(), have_previous=have_previous)
 
     def accumulate(self, x, n, dim, assign, best, k, sums, counts, obj):
         self.api.kmeans_accumulate(x, n, dim, assign, best, k, sums, counts, obj, device=self.device, stream=self._st())
@@ -401,7 +403,10 @@ def sharded_kmeans(engine, dist, world, x, n, dim, cen, k, iters, torch):
     obj = engine.empty((1,), torch.float64)
     history = []
     for it in range(iters + 1):
-        engine.assign(x, n, dim, cen, k, assign, best)
+        if it > 0 and getattr(engine, "bounded_assign", False):
+            engine.assign(x, n, dim, cen, k, assign, best, have_previous=True)   # the assignment of the iteration before bounds this one
+        else:
+            engine.assign(x, n, dim, cen, k, assign, best)
         engine.accumulate(x, n, dim, assign, best, k, sums, counts, obj)
         if world > 1:
             dist.all_reduce(sums)
