@@ -365,6 +365,7 @@ def main():
     if args.queries:
         cfg["nq"] = args.queries
     auto_mode = args.exact_mode == "auto"
+    args.auto_mode = auto_mode
     if args.exact_mode == "auto":
         gathered = cfg["nq"] * max(cfg["n_rerank"], cfg["topk"]) * cfg["dim"] * 4
         args.exact_mode = "hybrid" if gathered >= 2e9 else "mapped"
@@ -594,9 +595,21 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
         # The exchange half of a sub-batch (collectives, PCIe rerank) runs beside the next sub-batch's scan.  A collective's
         # CTA cannot share an SM with a scan CTA, so the scan's persistent grid leaves a few SMs free for it.
         reserve = args.reserve_sms
+        # Rerank transport per rank.  Up to four ranks the host cores can add to what a GPU's own reads of host memory bring
+        # (hybrid: the kernel takes the share its rate earns against the cores' rate divided by the ranks); at eight ranks the
+        # host's memory system is the limit either way (131 GB/s for all), and the kernel alone is simpler.
+        mode = getattr(args, "exact_mode", "auto")
+        cores = os.cpu_count() or 16
+        if mode == "cached":
+            exact_mode, zc_pct = api.EXACT_HOST_CACHED, 0
+        elif mode == "mapped" or (getattr(args, "auto_mode", True) and world > 4):
+            exact_mode, zc_pct = api.EXACT_HOST_MAPPED, 0
+        else:
+            exact_mode = api.EXACT_HOST_HYBRID
+            zc_pct = args.zero_copy_pct or int(round(100 * 28.0 / (28.0 + 32.0 / world)))
         sess = api.Session(index, n_rerank=R, device=device, max_batch=nq, stream=stream.cuda_stream, time_kernels=True,
-                           list_global_begin=gb, reserve_sms=reserve,
-                           exact_mode=api.EXACT_HOST_CACHED if getattr(args, "exact_mode", "") == "cached" else api.EXACT_HOST_MAPPED)
+                           list_global_begin=gb, reserve_sms=reserve, exact_mode=exact_mode, zero_copy_pct=zc_pct,
+                           host_threads=max(2, min(64, cores // world)))
         width = min(R, n) if R > topk else topk
         search = ShardedSearch(SessionEngine(sess, torch), dist, world, nq, dim, M, 256, nprobe, topk, width, torch,
                                rerank=R > topk, parts=args.parts if nq >= 2048 else 1, shared_cutoff=not args.local_cutoffs)
@@ -686,7 +699,8 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
             unit="queries/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms_dev, 3),
             higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
             config=dict(workload=args.workload, desc=cfg["desc"], rows=n, dim=dim, nlist=nlist, M=M, batch=nq, nprobe=nprobe,
-                        topk=topk, n_rerank=R, exact_rows=("device-cached fp32" if getattr(args, "exact_mode", "") == "cached" else "host-mapped fp32"), sharding="lists of at least %d x 4,096 rows striped over the %d ranks, shorter ones whole on rank (list mod %d)" % (world, world, world),
+                        topk=topk, n_rerank=R, exact_rows={api.EXACT_HOST_CACHED: "device-cached fp32", api.EXACT_HOST_MAPPED: "host-mapped fp32",
+                                    api.EXACT_HOST_HYBRID: "host fp32, hybrid transport (%d %% through the gather kernel)" % zc_pct}[exact_mode], sharding="lists of at least %d x 4,096 rows striped over the %d ranks, shorter ones whole on rank (list mod %d)" % (world, world, world),
                         l2="inputs larger than L2 (codes %.2f GB per rank)" % (index["codes"].nbytes / 1e9)),
             e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
                      h2d_bytes_per_step=int(nq * dim * 4), d2h_bytes_per_step=int(nq * topk * 12),

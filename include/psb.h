@@ -167,7 +167,7 @@ typedef struct psb_options {
        memory and returns, and the call reports PSB_TIMEOUT. */
     int test_wait_limit;
     int test_skip_mma;
-    int zero_copy_pct;  /* PSB_EXACT_HOST_HYBRID: share of each sub-batch gathered by the kernel, 1..99 (0 = 45) */
+    int zero_copy_pct;  /* PSB_EXACT_HOST_HYBRID: share of each sub-batch gathered by the kernel, 1..100 (0 = 45) */
     /* Residual mode, optional: the per-row correction asset of the index, value[row] = |recon(row)|^2 + 2 <centroid[list(row)],
        recon(row)> (src/common/row_correction.h:37-45), as HOST arrays over the rows of the view - either fp32 or the affine u16
        form (value = rc_offset + rc_scale * u16, src/common/row_correction.h:7-20).  The residual cutoff estimate reads it;
@@ -179,6 +179,8 @@ typedef struct psb_options {
        The PQ side of a search (tables, code scan) then works on R q while the coarse stage and the exact re-ranking keep the
        caller's q, as src/search/ivfpq/ivfpq_index.cu:205-217 and stage/ivfpq_fine_cpu_lut.cpp:29-31 do. */
     const float* opq_matrix;
+    int host_threads;   /* gather threads of the staged / hybrid transport, 1..64 (0 = all hardware threads): several sessions in
+                           one host - one per GPU - should share the cores between them */
 } psb_options;
 
 /* Counters and stage times of the last psb_session_search call; names follow the reference's

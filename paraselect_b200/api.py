@@ -75,7 +75,7 @@ class Options(C.Structure):
                 ("seed_sigma", C.c_float), ("pipeline_parts", C.c_int), ("even_cuts", C.c_int), ("gather_ctas", C.c_int),
                 ("tc_min_visitors", C.c_int), ("test_wait_limit", C.c_int), ("test_skip_mma", C.c_int), ("zero_copy_pct", C.c_int),
                 ("row_correction_fp32", C.c_void_p), ("row_correction_u16", C.c_void_p), ("rc_scale", C.c_float), ("rc_offset", C.c_float),
-                ("opq_matrix", C.c_void_p)]
+                ("opq_matrix", C.c_void_p), ("host_threads", C.c_int)]
 
 
 class Stats(C.Structure):
@@ -164,7 +164,7 @@ class Session:
     def __init__(self, index, n_rerank=0, device=0, exact_mode=EXACT_HOST_MAPPED, max_batch=0, list_begin=0,
                  list_end=0, stream=None, coarse_mode=0, time_kernels=False, list_global_begin=None, scan_mode=0, serial_pipeline=False, residual=False, reserve_sms=0,
                  seed_sigma=0.0, pipeline_parts=0, even_cuts=False, gather_ctas=0, tc_min_visitors=0, test_wait_limit=0, test_skip_mma=0,
-                 row_correction=None, rc_scale=0.0, rc_offset=0.0, opq_matrix=None, zero_copy_pct=0):
+                 row_correction=None, rc_scale=0.0, rc_offset=0.0, opq_matrix=None, zero_copy_pct=0, host_threads=0):
         self._keep = []
         cen = _np(index["centroids"], np.float32)
         off = _np(index["offsets"], np.int64)
@@ -200,7 +200,7 @@ class Session:
                       time_kernels=int(time_kernels), scan_mode=scan_mode, serial_pipeline=int(serial_pipeline), adc_mode=int(bool(residual)), reserve_sms=reserve_sms,
                       seed_sigma=float(seed_sigma), pipeline_parts=int(pipeline_parts), even_cuts=int(even_cuts),
                       gather_ctas=int(gather_ctas), tc_min_visitors=int(tc_min_visitors), test_wait_limit=int(test_wait_limit),
-                      test_skip_mma=int(test_skip_mma), zero_copy_pct=int(zero_copy_pct))
+                      test_skip_mma=int(test_skip_mma), zero_copy_pct=int(zero_copy_pct), host_threads=int(host_threads))
         if opq_matrix is not None:  # OPQ index: rotation [dim][dim], row-major [out][in]
             rot = _np(opq_matrix, np.float32)
             if rot.shape != (iv.coarse.dim, iv.coarse.dim):

@@ -140,13 +140,13 @@ struct psb_group {
     NcclApi nccl;
     SessionShape shape;
     cudaStream_t main = nullptr, aux = nullptr;
-    cudaEvent_t ev_front = nullptr, ev_back = nullptr;
+    cudaEvent_t ev_fronts[32] = {}, ev_back = nullptr;
     Buf probes, lut, l_rows, l_dist, l_cnt, s_key, r_key, g_rows, g_dist, mg_rows, mg_dist, all_rows, all_dist, p_dist, o_rows, smp, smp_all,
         cut, n_scan, low;
     long long searched_again = 0;
     ~psb_group() {
         if (aux) { cudaStreamSynchronize(aux); cudaStreamDestroy(aux); }
-        if (ev_front) cudaEventDestroy(ev_front);
+        for (auto e : ev_fronts) if (e) cudaEventDestroy(e);
         if (ev_back) cudaEventDestroy(ev_back);
     }
 };
@@ -232,18 +232,22 @@ psb_status group_step(psb_group* g, const float* dq, int nq, int nprobe, int top
         parts = (nq + sb - 1) / sb;
         for (int i = 0; i <= parts; ++i) cuts[i] = std::min(i * sb, nq);
     }
+    // The front half of sub-batch i + 1 is queued BEFORE the back half of sub-batch i: a back half may keep this thread busy (the
+    // host's share of a hybrid rerank transport), and the GPU must not run dry meanwhile.
     psb_status rc = PSB_OK;
-    for (int i = 0; i < parts && rc == PSB_OK; ++i) {
-        const int q0 = cuts[i], m = cuts[i + 1] - q0;
-        if (m <= 0) continue;
-        rc = group_front(g, dq, q0, m, nprobe, width, shared);
-        if (rc != PSB_OK) break;
-        PSB_CUDA(cudaEventRecord(g->ev_front, g->main));
-        PSB_CUDA(cudaStreamWaitEvent(g->aux, g->ev_front, 0));
-        rc = psb_session_set_stream(s, g->aux, 1);
-        if (rc == PSB_OK) rc = group_back(g, dq, q0, m, topk, width, rerank, shared, d_ids, d_dist);
-        const psb_status back = psb_session_set_stream(s, nullptr, 0);
-        if (rc == PSB_OK) rc = back;
+    for (int i = 0; i <= parts && rc == PSB_OK; ++i) {
+        if (i < parts && cuts[i + 1] > cuts[i]) {
+            rc = group_front(g, dq, cuts[i], cuts[i + 1] - cuts[i], nprobe, width, shared);
+            if (rc != PSB_OK) break;
+            PSB_CUDA(cudaEventRecord(g->ev_fronts[i], g->main));
+        }
+        if (i >= 1 && cuts[i] > cuts[i - 1]) {
+            PSB_CUDA(cudaStreamWaitEvent(g->aux, g->ev_fronts[i - 1], 0));
+            rc = psb_session_set_stream(s, g->aux, 1);
+            if (rc == PSB_OK) rc = group_back(g, dq, cuts[i - 1], cuts[i] - cuts[i - 1], topk, width, rerank, shared, d_ids, d_dist);
+            const psb_status back = psb_session_set_stream(s, nullptr, 0);
+            if (rc == PSB_OK) rc = back;
+        }
     }
     PSB_TRY(rc);
     PSB_CUDA(cudaEventRecord(g->ev_back, g->aux));
@@ -284,7 +288,7 @@ psb_status psb_group_create(psb_session* session, void* nccl_comm_main, void* nc
     int lo = 0, hi = 0;
     PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     PSB_CUDA(cudaStreamCreateWithPriority(&g->aux, cudaStreamNonBlocking, lo));
-    PSB_CUDA(cudaEventCreateWithFlags(&g->ev_front, cudaEventDisableTiming));
+    for (auto& e : g->ev_fronts) PSB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     PSB_CUDA(cudaEventCreateWithFlags(&g->ev_back, cudaEventDisableTiming));
     const int width = std::max(g->shape.n_rerank > topk ? std::min(g->shape.n_rerank, kMaxStage1) : topk, topk);
     const int w = g->world;

@@ -227,6 +227,7 @@ struct psb_session {
     bool own_stream = false;
     cudaStream_t aux_stream = nullptr;  // second stream of the overlapped pipeline (created on first use)
     cudaStream_t zc_stream = nullptr;   // hybrid transport: the kernel gather runs here, beside the copies of aux_stream
+    cudaEvent_t zc_ev_a = nullptr, zc_ev_b = nullptr;  // stage-level hybrid rerank: fork to and join from zc_stream
 
     cudaStream_t home_stream = nullptr; // the stream the session was created with (psb_session_set_stream(NULL) returns to it)
     bool background = false;            // stage calls currently run on a caller's second stream: small-grid gather
@@ -296,6 +297,8 @@ struct psb_session {
         if (h_cand_pinned) cudaFreeHost(h_cand_pinned);
         if (aux_stream) { cudaStreamSynchronize(aux_stream); cudaStreamDestroy(aux_stream); }
         if (zc_stream) { cudaStreamSynchronize(zc_stream); cudaStreamDestroy(zc_stream); }
+        if (zc_ev_a) cudaEventDestroy(zc_ev_a);
+        if (zc_ev_b) cudaEventDestroy(zc_ev_b);
 
         if (own_stream && stream) cudaStreamDestroy(stream);
         cudaGetLastError();
@@ -592,7 +595,7 @@ psb_status staged_gather_host(psb_session* s, const int* h_cand, int nq, int wid
         s->pinned_bytes = need;
     }
     if (!s->host_pool) {
-        const unsigned hc = std::max(1u, std::thread::hardware_concurrency());
+        const unsigned hc = s->opt.host_threads > 0 ? (unsigned)s->opt.host_threads : std::max(1u, std::thread::hardware_concurrency());
         s->host_pool.reset(new HostPool((int)std::min<unsigned>(hc, 64)));
     }
     const int nthreads = s->host_pool->size();
@@ -651,13 +654,43 @@ psb_status staged_gather(psb_session* s, const int* d_cand, int nq, int width, i
     return staged_gather_host(s, s->h_cand.data(), nq, width, stride, s->stage.p, s->stream);
 }
 
+// The stream of the hybrid transport's gather kernel.  Highest priority: its few CTAs each need an SM to themselves and must be
+// placed before the large grids of the scan stage that become runnable at the same moment.
+psb_status ensure_zc_stream(psb_session* s) {
+    if (s->zc_stream) return PSB_OK;
+    int lo = 0, hi = 0;
+    PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    PSB_CUDA(cudaStreamCreateWithPriority(&s->zc_stream, cudaStreamNonBlocking, hi));
+    return PSB_OK;
+}
+
 psb_status rerank_impl(psb_session* s, const void* d_queries, int nq, const int* d_cand, int width, int stride,
                        const int* d_counts, int topk, int* d_out_rows, float* d_out_dist, float* d_score = nullptr) {
     if (!s->exact_elem) return fail(PSB_INVALID_ARGUMENT, "session has no exact rows for the rerank");
     if (width <= 0 || stride < width || topk <= 0) return fail(PSB_INVALID_ARGUMENT, "invalid rerank request");
     if (width > kMaxRerankWidth || topk > kMaxTopk) return fail(PSB_UNSUPPORTED_SHAPE, "rerank width above 4096 or topk above 2048");
     PSB_TRY(s->stage.reserve((size_t)nq * width * s->dim * s->exact_elem));
-    if (staged_mode(s)) {
+    const int zc_pct = s->opt.zero_copy_pct > 0 ? s->opt.zero_copy_pct : 45;
+    const int mz = (int)((long long)nq * zc_pct / 100);
+    if (s->opt.exact_mode == PSB_EXACT_HOST_HYBRID && s->exact_dev && mz > 0 && mz < nq && (long long)nq * width >= 65536) {
+        // Both transports for one stage call (the sharded step's exchange half): the kernel gathers the rows of the last mz
+        // queries on a stream of its own while this thread gathers the others through the pinned rings.  The call blocks for
+        // the host gather; a caller that overlaps it with a scan queues that scan first.
+        const int mh = nq - mz;
+        const size_t row_bytes = (size_t)s->dim * s->exact_elem;
+        const bool beside = s->background || (s->aux_stream != nullptr && s->stream == s->aux_stream);
+        PSB_TRY(ensure_zc_stream(s));
+        if (!s->zc_ev_a) PSB_CUDA(cudaEventCreateWithFlags(&s->zc_ev_a, cudaEventDisableTiming));
+        if (!s->zc_ev_b) PSB_CUDA(cudaEventCreateWithFlags(&s->zc_ev_b, cudaEventDisableTiming));
+        PSB_CUDA(cudaEventRecord(s->zc_ev_a, s->stream));
+        PSB_CUDA(cudaStreamWaitEvent(s->zc_stream, s->zc_ev_a, 0));
+        PSB_TRY(launch_gather_rows(s->exact_dev, s->row_map(), s->dim, s->exact_elem, d_cand + (size_t)mh * stride, mz, width, stride,
+                                   d_counts ? d_counts + mh : nullptr, static_cast<unsigned char*>(s->stage.p) + (size_t)mh * width * row_bytes,
+                                   s->zc_stream, s->sm_count, 0, beside && s->opt.gather_ctas == 0 ? (s->opt.reserve_sms > 0 ? s->opt.reserve_sms : 8) : 0));
+        PSB_CUDA(cudaEventRecord(s->zc_ev_b, s->zc_stream));
+        PSB_TRY(staged_gather(s, d_cand, mh, width, stride, d_counts));
+        PSB_CUDA(cudaStreamWaitEvent(s->stream, s->zc_ev_b, 0));
+    } else if (staged_mode(s) && !(s->opt.exact_mode == PSB_EXACT_HOST_HYBRID && s->exact_dev && mz >= nq)) {
         PSB_TRY(staged_gather(s, d_cand, nq, width, stride, d_counts));
     } else {
         // Beside a scan on the other stream the gather runs on SMs of its own: the ones the scan's persistent grid leaves free
@@ -748,7 +781,8 @@ psb_status psb_session_create(const psb_index_view* index, const psb_options* op
     if (opt.pipeline_parts != 0 && (opt.pipeline_parts < 2 || opt.pipeline_parts > 32)) return fail(PSB_INVALID_ARGUMENT, "pipeline_parts must be 0 or in 2..32");
     if (opt.scan_mode < 0 || opt.scan_mode > 3) return fail(PSB_INVALID_ARGUMENT, "scan_mode must be in 0..3");
     if (opt.tc_min_visitors < 0) return fail(PSB_INVALID_ARGUMENT, "tc_min_visitors must not be negative");
-    if (opt.zero_copy_pct < 0 || opt.zero_copy_pct > 99) return fail(PSB_INVALID_ARGUMENT, "zero_copy_pct must be in 0..99");
+    if (opt.zero_copy_pct < 0 || opt.zero_copy_pct > 100) return fail(PSB_INVALID_ARGUMENT, "zero_copy_pct must be in 0..100");
+    if (opt.host_threads < 0 || opt.host_threads > 64) return fail(PSB_INVALID_ARGUMENT, "host_threads must be in 0..64");
     // hybrid transport: the gather kernel runs beside the scan on SMs of its own, which the scan's grid has to leave free
     if (opt.exact_mode == PSB_EXACT_HOST_HYBRID && opt.reserve_sms == 0 && opt.gather_ctas == 0) opt.reserve_sms = 32;
     if (opt.gather_ctas < 0 || opt.gather_ctas > 1024) return fail(PSB_INVALID_ARGUMENT, "gather_ctas must be in 0..1024");
@@ -1147,14 +1181,7 @@ psb_status search_device(psb_session* s, const float* dq, const void* dq_exact, 
     std::thread worker;
     const bool hybrid = staged_overlap && s->opt.exact_mode == PSB_EXACT_HOST_HYBRID && s->exact_dev != nullptr;
     const int zc_pct = s->opt.zero_copy_pct > 0 ? s->opt.zero_copy_pct : 45;
-    if (hybrid && !s->zc_stream) {
-        int lo = 0, hi = 0;
-        PSB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-        // Highest priority: the gather of sub-batch i is queued before the kernels of sub-batch i + 1 and becomes runnable at
-        // the same moment as they do (when the scan stage of sub-batch i ends and every SM is empty); its few CTAs, which need
-        // an SM each to themselves, must be placed first.
-        PSB_CUDA(cudaStreamCreateWithPriority(&s->zc_stream, cudaStreamNonBlocking, hi));
-    }
+    if (hybrid) PSB_TRY(ensure_zc_stream(s));
     if (staged_overlap) {
         const size_t cand_count = (size_t)n * stage1_k;
         if (s->h_cand_pinned_count < cand_count) {

@@ -346,16 +346,26 @@ class ShardedSearch:
             self.aux = t.cuda.Stream(priority=0)
         aux = self.aux
         aux.wait_stream(main)  # the second stream starts after everything already queued
-        for q0, q1 in zip(cuts[:-1], cuts[1:]):
-            m = q1 - q0
-            self._span("front %d" % q0, lambda: self._front(dq, q0, m))
-            aux.wait_stream(main)
-            e.set_stream(aux.cuda_stream, True)
-            try:
-                with t.cuda.stream(aux):
-                    self._span("back %d" % q0, lambda: self._back(dq, q0, m))
-            finally:
-                e.set_stream(None, False)
+        # The front half of sub-batch i + 1 is queued BEFORE the back half of sub-batch i: a back half may keep this thread busy
+        # (the host's share of a hybrid rerank transport), and the GPU must not run dry meanwhile.
+        spans = list(zip(cuts[:-1], cuts[1:]))
+        done = []
+        for i in range(len(spans) + 1):
+            if i < len(spans):
+                q0, q1 = spans[i]
+                self._span("front %d" % q0, lambda: self._front(dq, q0, q1 - q0))
+                ev = t.cuda.Event()
+                ev.record(main)
+                done.append(ev)
+            if i >= 1:
+                p0, p1 = spans[i - 1]
+                aux.wait_event(done[i - 1])
+                e.set_stream(aux.cuda_stream, True)
+                try:
+                    with t.cuda.stream(aux):
+                        self._span("back %d" % p0, lambda: self._back(dq, p0, p1 - p0))
+                finally:
+                    e.set_stream(None, False)
         main.wait_stream(aux)
         self._combine_ids()
         return self.o_ids, self.o_dist
