@@ -595,14 +595,14 @@ def multi_gpu_main(args, cfg, rank, world, local_rank):
         # The exchange half of a sub-batch (collectives, PCIe rerank) runs beside the next sub-batch's scan.  A collective's
         # CTA cannot share an SM with a scan CTA, so the scan's persistent grid leaves a few SMs free for it.
         reserve = args.reserve_sms
-        # Rerank transport per rank.  Up to four ranks the host cores can add to what a GPU's own reads of host memory bring
-        # (hybrid: the kernel takes the share its rate earns against the cores' rate divided by the ranks); at eight ranks the
-        # host's memory system is the limit either way (131 GB/s for all), and the kernel alone is simpler.
+        # Rerank transport per rank: the gather kernel over mapped host rows.  The hybrid transport (host cores beside the kernel)
+        # can be asked for with --exact-mode hybrid; with the cores shared between the ranks and every candidate first to be
+        # looked up in the stripe it measured slower (two ranks: 98.5 ms against 89-91.5 ms per batch).
         mode = getattr(args, "exact_mode", "auto")
         cores = os.cpu_count() or 16
         if mode == "cached":
             exact_mode, zc_pct = api.EXACT_HOST_CACHED, 0
-        elif mode == "mapped" or (getattr(args, "auto_mode", True) and world > 4):
+        elif mode == "mapped" or getattr(args, "auto_mode", True):
             exact_mode, zc_pct = api.EXACT_HOST_MAPPED, 0
         else:
             exact_mode = api.EXACT_HOST_HYBRID
