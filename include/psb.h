@@ -570,6 +570,52 @@ psb_status psb_row_correction_encode_u16(const float* h_values, int64_t n, float
 psb_status psb_row_correction_write_u16(const char* path, const psb_row_correction_u16_header* header, const uint16_t* h_u16);
 psb_status psb_row_correction_read_u16(const char* path, psb_row_correction_u16_header* header, uint16_t* h_u16, int64_t capacity);
 
+/* ---- TurboQuant 1-bit residual codec -----------------------------------------------------------------------------
+ * A row is stored as the signs of its rotated residual against its list's centroid (one bit per rotated dimension) and one
+ * reconstruction scale; the rotation is a seeded sign flip followed by a Walsh-Hadamard transform of padded_dim (the next
+ * power of two >= dim, 32..256) scaled by rsqrt(padded_dim).  These operators replace the reference's encoder
+ * (src/quantization/turboquant/turboquant_1bit_encode.cuh:12-83, turboquant_1bit_encode.cu) and the candidate search of
+ * its IVFResTurboQuant index (src/search/ivf_res_turboquant/ivf_res_turboquant_search.cuh:65-89,
+ * src/quantization/turboquant/turboquant_1bit_scan.cuh:63-74).  All pointers are device pointers. */
+#define PSB_SIGN_ROTATION_SEED 17u   /* src/search/ivf_res_turboquant/ivf_res_turboquant_search.cuh:41 */
+#define PSB_SIGN_FLOAT_STATES 0      /* TurboQuant1BitScoreMode::MseFloatQuery */
+#define PSB_SIGN_CODED_STATES 1      /* TurboQuant1BitScoreMode::BinaryQuery */
+#define PSB_SIGN_MAX_CANDIDATES 8192 /* the reference takes up to 16,384 (ivf_res_turboquant_search.cuh:16) */
+
+/* padded_dimension (ivf_res_turboquant_search.cu:24-29): 32, 64, 128 or 256; -1 when dim > 256 or dim <= 0. */
+int psb_sign_padded_dim(int dim);
+/* The rotation's scale as the device computes it, rsqrtf(padded_dim), for a checker that restates the rotation on the host. */
+psb_status psb_sign_rotation_scale(int padded_dim, float* h_scale, int device, void* stream);
+/* turboquant_1bit_encode_gpu: rotated rows [n][padded_dim], sign words [n][padded_dim / 32] (bit d % 32 of word d / 32 is set
+ * when rotated[d] >= 0), sqrt of and the sum of squares of each input row.  Any output may be NULL. */
+psb_status psb_sign_rotate(const float* d_rows, int64_t n, int dim, int padded_dim, uint32_t seed, float* d_rotated,
+                           uint32_t* d_codes, float* d_norms, float* d_norm_sq, int device, void* stream);
+/* ivf_res_turboquant_encode_database_u8_gpu: rows [row_offset, row_offset + n) of a list-contiguous index, u8 (elem_bytes 1,
+ * the reference's input) or fp32 (elem_bytes 4); d_codes [total rows][padded_dim / 32] and d_scales [total rows] are written
+ * at the global rows.  The scale is the mean magnitude of the rotated residual.  Encoding in chunks gives the same bits as
+ * encoding at once. */
+psb_status psb_sign_encode_database(const void* d_rows, int elem_bytes, int64_t n, const float* d_centroids,
+                                    const int64_t* d_list_offsets, int nlist, int dim, int padded_dim, uint32_t seed,
+                                    int64_t row_offset, uint32_t* d_codes, float* d_scales, int device, void* stream);
+/* ivf_res_turboquant_encode_queries_gpu: one state per (query, probe), the rotated residual of the query against the probed
+ * centroid: d_states [nq * nprobe][padded_dim] and d_norm_sq [nq * nprobe] (float states), d_state_codes
+ * [nq * nprobe][padded_dim / 32] and d_norms [nq * nprobe] (sign-coded states); any may be NULL.  d_probes [nq][nprobe] int32 as
+ * psb_stage_coarse writes them; a probe outside [0, nlist) gives a zero state. */
+psb_status psb_sign_encode_queries(const float* d_queries, const float* d_centroids, const int* d_probes, int nq, int nprobe,
+                                   int nlist, int dim, int padded_dim, uint32_t seed, float* d_states, float* d_norm_sq,
+                                   uint32_t* d_state_codes, float* d_norms, int device, void* stream);
+/* SearchWorkspace::search_candidates: every row of every probed list is scored against the state of its (query, probe) -
+ * float states: norm_sq + dim s^2 - 2 s sum_d(+-state[d]) with s = d_row_params[row]; sign-coded states:
+ * qn^2 + dn^2 - 2 qn dn (dim - 2 hamming) / dim with dn = d_row_params[row] - and the candidate_count smallest by (score, row)
+ * come out in ascending order: d_rows_out [nq][candidate_count] int32 (global rows, -1 when fewer rows were scanned),
+ * d_dist_out the scores (FLT_MAX there; may be NULL).  Probes outside [0, nlist) are skipped.  candidate_count <=
+ * PSB_SIGN_MAX_CANDIDATES; d_codes must be 16-byte aligned. */
+psb_status psb_sign_search_candidates(int mode, const float* d_states, const float* d_norm_sq, const uint32_t* d_state_codes,
+                                      const float* d_norms, const uint32_t* d_codes, const float* d_row_params,
+                                      const int64_t* d_list_offsets, int nlist, const int* d_probes, int nq, int nprobe,
+                                      int padded_dim, int candidate_count, int* d_rows_out, float* d_dist_out, int device,
+                                      void* stream);
+
 /* ---- synthetic data (bench and tests): counter-based generator, identical for any launch shape -------- */
 
 /* rows [row_begin, row_begin + n) of a Gaussian mixture in component-contiguous order:

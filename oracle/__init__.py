@@ -588,3 +588,143 @@ def ref_kmeans_init(data, k, seed, policy=0):
     out = np.empty((k, x.shape[1]), np.float32)
     _load_kmeans_init().psbref_kmeans_init(x.shape[0], x.shape[1], k, seed, policy, _ptr(x), _ptr(out))
     return out
+
+
+# ---- TurboQuant 1-bit residual codec (restatement: partly pinned, see oracle/psb_oracle.c) ----------------------
+REF_SIGN_SO = os.path.join(_HERE, "_ref", "libpsb_ref_sign.so")
+_ref_sign = None
+
+
+def _sign_lib():
+    L = lib()
+    for name in ("psbo_sign_scale_l2", "psbo_sign_binary_l2", "psbo_sign_score_mse", "psbo_sign_score_binary"):
+        getattr(L, name).restype = C.c_float
+    return L
+
+
+def sign_padded_dim(dim):
+    return lib().psbo_sign_padded_dim(int(dim))
+
+
+def sign_scale(padded):
+    """1/sqrt(padded) rounded to fp32 (the kernels take rsqrtf on the device; tests pass the device's value instead)."""
+    return float(np.float32(1.0) / np.sqrt(np.float32(padded)))
+
+
+def sign_pack(values):
+    v = _c(values, np.float32).reshape(-1)
+    out = np.zeros((v.size + 31) // 32, np.uint32)
+    lib().psbo_sign_pack(_ptr(v), v.size, _ptr(out))
+    return out
+
+
+def sign_hamming(a, b, dim):
+    a = _c(a, np.uint32); b = _c(b, np.uint32)
+    return lib().psbo_sign_hamming(_ptr(a), _ptr(b), int(dim))
+
+
+def sign_scale_l2(query, code, scale):
+    q = _c(query, np.float32).reshape(-1); c = _c(code, np.uint32)
+    return float(_sign_lib().psbo_sign_scale_l2(_ptr(q), _ptr(c), q.size, C.c_float(scale)))
+
+
+def sign_binary_l2(qcode, code, dim, qn, dn):
+    a = _c(qcode, np.uint32); b = _c(code, np.uint32)
+    return float(_sign_lib().psbo_sign_binary_l2(_ptr(a), _ptr(b), int(dim), C.c_float(qn), C.c_float(dn)))
+
+
+def sign_rotate(rows, padded, seed=17, scale=None):
+    """Rotated rows, sign words, sqrt and sum of squares of each row."""
+    x = _c(rows, np.float32)
+    n, dim = x.shape
+    scale = sign_scale(padded) if scale is None else scale
+    rot = np.empty((n, padded), np.float32); codes = np.empty((n, padded // 32), np.uint32)
+    norms = np.empty(n, np.float32); nsq = np.empty(n, np.float32)
+    if lib().psbo_sign_rotate(_ptr(x), C.c_int64(n), dim, int(padded), C.c_uint32(seed), C.c_float(scale),
+                              _ptr(rot), _ptr(codes), _ptr(norms), _ptr(nsq)):
+        raise ValueError("oracle sign_rotate: invalid arguments")
+    return rot, codes, norms, nsq
+
+
+def sign_encode_database(rows, centroids, offsets, padded, seed=17, scale=None, row_offset=0, total_rows=None,
+                         codes=None, scales=None):
+    """Sign words and L1 scales of the list-contiguous rows [row_offset, row_offset + len(rows)), u8 or fp32."""
+    x = np.ascontiguousarray(rows)
+    if x.dtype != np.uint8:
+        x = _c(x, np.float32)
+    cen = _c(centroids, np.float32); off = _c(offsets, np.int64)
+    n, dim = x.shape
+    total = int(off[-1]) if total_rows is None else total_rows
+    scale = sign_scale(padded) if scale is None else scale
+    if codes is None:
+        codes = np.zeros((total, padded // 32), np.uint32); scales = np.zeros(total, np.float32)
+    if lib().psbo_sign_encode_database(_ptr(x), x.dtype.itemsize, C.c_int64(n), _ptr(cen), _ptr(off), cen.shape[0], dim,
+                                       int(padded), C.c_uint32(seed), C.c_float(scale), C.c_int64(row_offset),
+                                       _ptr(codes), _ptr(scales)):
+        raise ValueError("oracle sign_encode_database: invalid arguments")
+    return codes, scales
+
+
+def sign_encode_queries(queries, centroids, probes, padded, seed=17, scale=None):
+    """Per (query, probe): rotated residual state, its sum of squares, its sign words, its norm."""
+    q = _c(queries, np.float32); cen = _c(centroids, np.float32); pr = _c(probes, np.int32)
+    nq, nprobe = pr.shape
+    scale = sign_scale(padded) if scale is None else scale
+    states = np.empty((nq * nprobe, padded), np.float32); nsq = np.empty(nq * nprobe, np.float32)
+    sc = np.empty((nq * nprobe, padded // 32), np.uint32); norms = np.empty(nq * nprobe, np.float32)
+    if lib().psbo_sign_encode_queries(_ptr(q), _ptr(cen), _ptr(pr), nq, nprobe, cen.shape[0], q.shape[1], int(padded),
+                                      C.c_uint32(seed), C.c_float(scale), _ptr(states), _ptr(nsq), _ptr(sc), _ptr(norms)):
+        raise ValueError("oracle sign_encode_queries: invalid arguments")
+    return states, nsq, sc, norms
+
+
+def sign_candidates(mode, codes, row_params, offsets, probes, candidate_count, states=None, norm_sq=None,
+                    state_codes=None, norms=None):
+    """The candidate_count rows of the probed lists with the smallest (score, row); mode 0 float states, 1 sign-coded."""
+    codes = _c(codes, np.uint32); rp = _c(row_params, np.float32); off = _c(offsets, np.int64); pr = _c(probes, np.int32)
+    nq, nprobe = pr.shape
+    padded = codes.shape[1] * 32
+    st = None if states is None else _c(states, np.float32)
+    ns = None if norm_sq is None else _c(norm_sq, np.float32)
+    sc = None if state_codes is None else _c(state_codes, np.uint32)
+    nm = None if norms is None else _c(norms, np.float32)
+    rows = np.empty((nq, candidate_count), np.int32); dist = np.empty((nq, candidate_count), np.float32)
+    if lib().psbo_sign_candidates(int(mode), _ptr(st), _ptr(ns), _ptr(sc), _ptr(nm), _ptr(codes), _ptr(rp), _ptr(off),
+                                  off.size - 1, _ptr(pr), nq, nprobe, padded, int(candidate_count), _ptr(rows), _ptr(dist)):
+        raise ValueError("oracle sign_candidates: invalid arguments")
+    return rows, dist
+
+
+def have_ref_sign() -> bool:
+    return os.path.exists(REF_SIGN_SO)
+
+
+def ref_sign():
+    global _ref_sign
+    if _ref_sign is None:
+        _ref_sign = C.CDLL(REF_SIGN_SO)
+        for name in ("ref_sign_scale_l2", "ref_sign_binary_l2", "ref_sign_mse"):
+            getattr(_ref_sign, name).restype = C.c_float
+    return _ref_sign
+
+
+def ref_sign_pack(values):
+    v = _c(values, np.float32).reshape(-1)
+    out = np.zeros(ref_sign().ref_sign_words(v.size), np.uint32)
+    ref_sign().ref_sign_pack(_ptr(v), v.size, _ptr(out))
+    return out
+
+
+def ref_sign_hamming(a, b, dim):
+    a = _c(a, np.uint32); b = _c(b, np.uint32)
+    return ref_sign().ref_sign_hamming(_ptr(a), _ptr(b), int(dim))
+
+
+def ref_sign_scale_l2(query, code, scale):
+    q = _c(query, np.float32).reshape(-1); c = _c(code, np.uint32)
+    return float(ref_sign().ref_sign_scale_l2(_ptr(q), _ptr(c), q.size, C.c_float(scale)))
+
+
+def ref_sign_binary_l2(qcode, code, dim, qn, dn):
+    a = _c(qcode, np.uint32); b = _c(code, np.uint32)
+    return float(ref_sign().ref_sign_binary_l2(_ptr(a), _ptr(b), int(dim), C.c_float(qn), C.c_float(dn)))

@@ -5,8 +5,9 @@
  * the checker by the tests, the smoke entry and the bench's cpu_baseline leg.
  * The shipped library never links or calls anything in this file.
  *
- * Parity status: PINNED.  Every function here is checked (tests/test_oracle.py) against the reference's own CPU code compiled in place
- * (oracle/_ref, built by oracle/Makefile) and against the known-answer
+ * Parity status: PINNED, with one exception stated at the block it concerns (the TurboQuant 1-bit codec at the end of the
+ * file: partly pinned).  Every other function here is checked (tests/test_oracle.py) against the reference's own CPU code
+ * compiled in place (oracle/_ref, built by oracle/Makefile) and against the known-answer
  * constructions of the reference's unit tests.
  *
  * Arithmetic conventions restated (reference file:line):
@@ -580,4 +581,247 @@ int psbo_rotate_rows(const float* in, const float* matrix, int64_t n, int dim, f
             out[(size_t)r * dim + o] = acc;
         }
     return 0;
+}
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * TurboQuant 1-bit residual codec: random sign flips + Walsh-Hadamard rotation, one sign bit per rotated dimension and
+ * one scale per row; candidates are the rows of the probed lists with the smallest reconstructed distance.
+ *
+ * Parity status of this block: PARTLY PINNED.  The reference's encoder and scan are GPU kernels that cannot run
+ * where this file is tested; what it has as host code - the bit layout, the Hamming count and the unfused distance
+ * formulas of src/quantization/turboquant/turboquant_1bit_format.h:14-117 - is compiled in place and compared bit for
+ * bit (psbo_sign_pack, psbo_sign_hamming, psbo_sign_scale_l2, psbo_sign_binary_l2), with the known answers of
+ * tests/unit/turboquant/test_turboquant_1bit_format.cpp:15-47.  The rotation, the scales and the fused scores restate
+ * the kernels' arithmetic order from their source and are unpinned:
+ *   - sign flip of lane d when the low bit of mix(seed ^ d) is set, butterflies of widths 1,2,4,... writing
+ *     (lhs+rhs, lhs-rhs), then every value times `scale` (src/quantization/turboquant/turboquant_1bit_encode.cu:13-19,
+ *     44-72).  The kernel takes scale = rsqrtf(padded_dim) on the device; here the caller passes it.
+ *   - per-row statistic: a 32-lane shuffle-down tree per group of 32 values, then the same tree over the group sums
+ *     (turboquant_1bit_encode.cu:86-108): L1 scale = sum|rotated| / padded_dim for database rows, sum original^2
+ *     for query states.
+ *   - score of a row against a float state: one chain over d = 0..dim-1 of +-state[d], then
+ *     norm_sq + dim*s*s - 2*s*dot (src/quantization/turboquant/turboquant_1bit_score.cuh:54-72), taken here with the
+ *     two products fused into the sums: fma(-(2s), dot, fma(dim*s, s, norm_sq)).
+ *   - order of candidates: (distance, row) ascending, pad -1 / FLT_MAX (turboquant_1bit_score.cuh:8-14,
+ *     turboquant_1bit_grouped_scan.cu:66,155-156). */
+static uint32_t sign_mix(uint32_t v) {
+    v ^= v >> 16; v *= 0x7feb352du; v ^= v >> 15; v *= 0x846ca68bu;
+    return v ^ (v >> 16);
+}
+
+/* What lane 0 holds after `for delta = 16..1: v += shfl_down(v, delta)` over 32 lanes. */
+static float sign_tree32(const float* in) {
+    float v[32];
+    memcpy(v, in, sizeof(v));
+    for (int delta = 16; delta > 0; delta >>= 1)
+        for (int l = 0; l + delta < 32; ++l) v[l] = v[l] + v[l + delta];
+    return v[0];
+}
+
+static float sign_block_sum(const float* per_lane, int padded) {
+    float groups[32];
+    for (int g = 0; g < 32; ++g) groups[g] = 0.0f;
+    for (int g = 0; g < padded / 32; ++g) groups[g] = sign_tree32(per_lane + 32 * g);
+    return sign_tree32(groups);
+}
+
+int psbo_sign_padded_dim(int dim) {
+    int p = 32;
+    while (p < dim) p <<= 1;
+    return (dim <= 0 || p > 256) ? -1 : p;
+}
+
+static int sign_shape_ok(int dim, int padded) {
+    return dim > 0 && dim <= padded && padded >= 32 && padded <= 256 && (padded & (padded - 1)) == 0;
+}
+
+/* values[0..padded) hold the (zero padded) original row on entry and the rotated row on return. */
+static void sign_rotate_inplace(float* values, int padded, uint32_t seed, float scale) {
+    for (int d = 0; d < padded; ++d)
+        if (sign_mix(seed ^ (uint32_t)d) & 1u) values[d] = -values[d];
+    for (int width = 1; width < padded; width <<= 1)
+        for (int t = 0; t < padded / 2; ++t) {
+            const int group = t / width, off = t - group * width;
+            const int left = group * (width << 1) + off, right = left + width;
+            const float lhs = values[left], rhs = values[right];
+            values[left] = lhs + rhs;
+            values[right] = lhs - rhs;
+        }
+    for (int d = 0; d < padded; ++d) values[d] = values[d] * scale;
+}
+
+void psbo_sign_pack(const float* values, int dim, uint32_t* words) {
+    for (int w = 0; w < (dim + 31) / 32; ++w) words[w] = 0;
+    for (int d = 0; d < dim; ++d)
+        if (values[d] >= 0.0f) words[d / 32] |= 1u << (d % 32);
+}
+
+int psbo_sign_hamming(const uint32_t* a, const uint32_t* b, int dim) {
+    int h = 0;
+    for (int w = 0; w < dim / 32; ++w) h += __builtin_popcount(a[w] ^ b[w]);
+    if (dim % 32) h += __builtin_popcount((a[dim / 32] ^ b[dim / 32]) & ((1u << (dim % 32)) - 1u));
+    return h;
+}
+
+static float sign_dot(const float* state, const uint32_t* code, int dim) {
+    float dot = 0.0f;
+    for (int d = 0; d < dim; ++d) dot += ((code[d / 32] >> (d % 32)) & 1u) ? state[d] : -state[d];
+    return dot;
+}
+
+/* The host formula (turboquant_1bit_format.h:86-103): sequential sums, no fused operations. */
+float psbo_sign_scale_l2(const float* query, const uint32_t* code, int dim, float s) {
+    float norm = 0.0f;
+    for (int d = 0; d < dim; ++d) norm += query[d] * query[d];
+    const float dot = sign_dot(query, code, dim);
+    return norm + (float)dim * s * s - 2.0f * s * dot;
+}
+
+float psbo_sign_binary_l2(const uint32_t* qcode, const uint32_t* code, int dim, float qn, float dn) {
+    if (dim == 0) return 0.0f;
+    const int h = psbo_sign_hamming(qcode, code, dim);
+    const float cosine = ((float)dim - 2.0f * (float)h) / (float)dim;
+    return qn * qn + dn * dn - 2.0f * qn * dn * cosine;
+}
+
+/* The scan kernel's scores (fused). */
+float psbo_sign_score_mse(const float* state, float norm_sq, const uint32_t* code, int dim, float s) {
+    const float dot = sign_dot(state, code, dim);
+    return fmaf(-(2.0f * s), dot, fmaf((float)dim * s, s, norm_sq));
+}
+
+float psbo_sign_score_binary(const uint32_t* qcode, const uint32_t* code, int dim, float qn, float dn) {
+    const int h = psbo_sign_hamming(qcode, code, dim);
+    const float cosine = ((float)dim - 2.0f * (float)h) / (float)dim;
+    return fmaf(-(2.0f * qn * dn), cosine, fmaf(dn, dn, qn * qn));
+}
+
+/* turboquant_1bit_encode_gpu (turboquant_1bit_encode.cu:113-172): rotated rows, sign words, sqrt and sum of squares of the
+ * original row.  Any output may be null. */
+int psbo_sign_rotate(const float* rows, int64_t n, int dim, int padded, uint32_t seed, float scale,
+                     float* rotated, uint32_t* codes, float* norms, float* norm_sq) {
+    if (!rows || n < 0 || !sign_shape_ok(dim, padded)) return 1;
+    const int words = padded / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; ++r) {
+        float v[256], sq[256];
+        for (int d = 0; d < padded; ++d) {
+            const float x = d < dim ? rows[(size_t)r * dim + d] : 0.0f;
+            v[d] = x; sq[d] = d < dim ? x * x : 0.0f;
+        }
+        sign_rotate_inplace(v, padded, seed, scale);
+        if (rotated) memcpy(rotated + (size_t)r * padded, v, sizeof(float) * (size_t)padded);
+        if (codes) psbo_sign_pack(v, padded, codes + (size_t)r * words);
+        const float sum = sign_block_sum(sq, padded);
+        if (norm_sq) norm_sq[r] = sum;
+        if (norms) norms[r] = sqrtf(sum);
+    }
+    return 0;
+}
+
+static int sign_row_list(int64_t row, const int64_t* offsets, int nlist) {
+    int lo = 0, hi = nlist;
+    while (lo + 1 < hi) {
+        const int mid = lo + (hi - lo) / 2;
+        if (offsets[mid] <= row) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+/* ivf_res_turboquant_encode_database_u8_gpu (turboquant_1bit_encode.cu:188-206): residual of row (row_offset + r)
+ * against the centroid of its list, rotated; sign words and L1 scale land at the global row.  elem_bytes 1 = u8 rows (the
+ * reference's input), 4 = fp32 rows. */
+int psbo_sign_encode_database(const void* rows, int elem_bytes, int64_t n, const float* centroids, const int64_t* offsets,
+                              int nlist, int dim, int padded, uint32_t seed, float scale, int64_t row_offset,
+                              uint32_t* codes, float* scales) {
+    if (!rows || !centroids || !offsets || !codes || n < 0 || nlist <= 0 || !sign_shape_ok(dim, padded)) return 1;
+    if (elem_bytes != 1 && elem_bytes != 4) return 1;
+    const int words = padded / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; ++r) {
+        const int64_t g = r + row_offset;
+        const int list = sign_row_list(g, offsets, nlist);
+        float v[256], mag[256];
+        for (int d = 0; d < padded; ++d) {
+            float x = 0.0f;
+            if (d < dim) {
+                const float raw = elem_bytes == 1 ? (float)((const uint8_t*)rows)[(size_t)r * dim + d]
+                                                  : ((const float*)rows)[(size_t)r * dim + d];
+                x = raw - centroids[(size_t)list * dim + d];
+            }
+            v[d] = x;
+        }
+        sign_rotate_inplace(v, padded, seed, scale);
+        psbo_sign_pack(v, padded, codes + (size_t)g * words);
+        for (int d = 0; d < padded; ++d) mag[d] = fabsf(v[d]);
+        if (scales) scales[g] = sign_block_sum(mag, padded) / (float)padded;
+    }
+    return 0;
+}
+
+/* ivf_res_turboquant_encode_queries_gpu (turboquant_1bit_encode.cu:208-228): one state per (query, probe): the rotated
+ * residual against the probed centroid, its sign words, and sqrt / sum of squares of the residual.  A probe outside
+ * [0, nlist) yields a zero state. */
+int psbo_sign_encode_queries(const float* queries, const float* centroids, const int* probes, int nq, int nprobe,
+                             int nlist, int dim, int padded, uint32_t seed, float scale, float* states, float* norm_sq,
+                             uint32_t* state_codes, float* norms) {
+    if (!queries || !centroids || !probes || nq < 0 || nprobe <= 0 || !sign_shape_ok(dim, padded)) return 1;
+    const int words = padded / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t st = 0; st < (int64_t)nq * nprobe; ++st) {
+        const int q = (int)(st / nprobe), list = probes[st];
+        float v[256], sq[256];
+        const int ok = list >= 0 && list < nlist;
+        for (int d = 0; d < padded; ++d) {
+            const float x = (ok && d < dim) ? queries[(size_t)q * dim + d] - centroids[(size_t)list * dim + d] : 0.0f;
+            v[d] = x; sq[d] = x * x;
+        }
+        sign_rotate_inplace(v, padded, seed, scale);
+        if (states) memcpy(states + (size_t)st * padded, v, sizeof(float) * (size_t)padded);
+        if (state_codes) psbo_sign_pack(v, padded, state_codes + (size_t)st * words);
+        const float sum = sign_block_sum(sq, padded);
+        if (norm_sq) norm_sq[st] = sum;
+        if (norms) norms[st] = sqrtf(sum);
+    }
+    return 0;
+}
+
+/* SearchWorkspace::search_candidates (src/search/ivf_res_turboquant/ivf_res_turboquant_search.cu:226-343): every row of
+ * every valid probed list scored against the state of its (query, probe), the candidate_count smallest by (score, row).
+ * mode 0 = float states (MseFloatQuery), 1 = sign-coded states (BinaryQuery). */
+int psbo_sign_candidates(int mode, const float* states, const float* norm_sq, const uint32_t* state_codes,
+                         const float* norms, const uint32_t* codes, const float* row_params, const int64_t* offsets,
+                         int nlist, const int* probes, int nq, int nprobe, int padded, int candidate_count,
+                         int* rows_out, float* dist_out) {
+    if (!codes || !row_params || !offsets || !probes || !rows_out || nq < 0 || nprobe <= 0 || candidate_count <= 0) return 1;
+    if (mode == 0 ? (!states || !norm_sq) : (!state_codes || !norms)) return 1;
+    if (!sign_shape_ok(padded, padded)) return 1;
+    const int words = padded / 32;
+    int bad = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int q = 0; q < nq; ++q) {
+        pair_t* heap = (pair_t*)malloc(sizeof(pair_t) * (size_t)candidate_count);
+        if (!heap) { bad = 1; continue; }
+        topk_t t;
+        topk_init(&t, heap, candidate_count);
+        for (int p = 0; p < nprobe; ++p) {
+            const int64_t st = (int64_t)q * nprobe + p;
+            const int list = probes[st];
+            if (list < 0 || list >= nlist) continue;
+            for (int64_t r = offsets[list]; r < offsets[list + 1]; ++r) {
+                const uint32_t* code = codes + (size_t)r * words;
+                const float d = mode == 0
+                    ? psbo_sign_score_mse(states + (size_t)st * padded, norm_sq[st], code, padded, row_params[r])
+                    : psbo_sign_score_binary(state_codes + (size_t)st * words, code, padded, norms[st], row_params[r]);
+                topk_push(&t, d, r);
+            }
+        }
+        topk_finish(&t);
+        for (int i = 0; i < candidate_count; ++i) {
+            rows_out[(size_t)q * candidate_count + i] = i < t.n ? (int)t.h[i].i : -1;
+            if (dist_out) dist_out[(size_t)q * candidate_count + i] = i < t.n ? t.h[i].d : FLT_MAX;
+        }
+        free(heap);
+    }
+    return bad;
 }

@@ -103,6 +103,7 @@ EXPORTS = [
     "psb_row_correction_compute", "psb_row_correction_quantize_u16", "psb_row_correction_write_u16", "psb_row_correction_read_u16",
     "psb_row_correction_model_u16", "psb_row_correction_encode_u16",
     "psb_sizeof", "psb_kmeans_assign_bounded", "psb_group_create", "psb_group_set", "psb_group_search_device", "psb_group_searched_again", "psb_group_destroy",
+    "psb_sign_padded_dim", "psb_sign_rotation_scale", "psb_sign_rotate", "psb_sign_encode_database", "psb_sign_encode_queries", "psb_sign_search_candidates",
     "psb_kmeans_init", "psb_rotate_rows", "psb_stage_rotate_queries", "psb_scan_sample_words", "psb_stage_scan_sample", "psb_stage_scan_shared",
     "psb_ivf_layout_from_assignment", "psb_reorder_rows", "psb_coarse_host", "psb_coarse_search_static", "psb_knn_exact", "psb_kmeans_train", "psb_kmeans_assign", "psb_kmeans_accumulate", "psb_kmeans_update", "psb_residual_rows", "psb_pq_train", "psb_pq_encode", "psb_gen_mixture_rows", "psb_gen_normal",
 ]
@@ -564,6 +565,155 @@ def rotate_rows(d_in, d_matrix, n, dim, d_out, device=0, stream=None):
     """d_out[r] = matrix @ d_in[r] on the device (matrix row-major [out][in])."""
     _check(lib().psb_rotate_rows(C.c_void_p(_p(d_in)), C.c_void_p(_p(d_matrix)), C.c_int64(n), dim, C.c_void_p(_p(d_out)), device,
                                  _stream_ptr(stream)))
+
+
+# ---- TurboQuant 1-bit residual codec --------------------------------------------------------------------
+SIGN_ROTATION_SEED = 17
+SIGN_FLOAT_STATES, SIGN_CODED_STATES = 0, 1   # TurboQuant1BitScoreMode::MseFloatQuery / BinaryQuery
+SIGN_MAX_CANDIDATES = 8192
+
+
+def _vp(a):
+    return C.c_void_p(_p(a)) if a is not None else None
+
+
+def sign_padded_dim(dim):
+    return lib().psb_sign_padded_dim(int(dim))
+
+
+def sign_rotation_scale(padded_dim, device=0, stream=None):
+    """rsqrtf(padded_dim) as the device computes it."""
+    out = C.c_float(0)
+    _check(lib().psb_sign_rotation_scale(int(padded_dim), C.byref(out), device, _stream_ptr(stream)))
+    return out.value
+
+
+def sign_rotate(d_rows, n, dim, padded_dim, d_rotated=None, d_codes=None, d_norms=None, d_norm_sq=None,
+                seed=SIGN_ROTATION_SEED, device=0, stream=None):
+    _check(lib().psb_sign_rotate(_vp(d_rows), C.c_int64(n), dim, padded_dim, C.c_uint32(seed), _vp(d_rotated), _vp(d_codes),
+                                 _vp(d_norms), _vp(d_norm_sq), device, _stream_ptr(stream)))
+
+
+def sign_encode_database(d_rows, elem_bytes, n, d_centroids, d_offsets, nlist, dim, padded_dim, d_codes, d_scales,
+                         row_offset=0, seed=SIGN_ROTATION_SEED, device=0, stream=None):
+    _check(lib().psb_sign_encode_database(_vp(d_rows), elem_bytes, C.c_int64(n), _vp(d_centroids), _vp(d_offsets), nlist, dim,
+                                          padded_dim, C.c_uint32(seed), C.c_int64(row_offset), _vp(d_codes), _vp(d_scales),
+                                          device, _stream_ptr(stream)))
+
+
+def sign_encode_queries(d_queries, d_centroids, d_probes, nq, nprobe, nlist, dim, padded_dim, d_states=None, d_norm_sq=None,
+                        d_state_codes=None, d_norms=None, seed=SIGN_ROTATION_SEED, device=0, stream=None):
+    _check(lib().psb_sign_encode_queries(_vp(d_queries), _vp(d_centroids), _vp(d_probes), nq, nprobe, nlist, dim, padded_dim,
+                                         C.c_uint32(seed), _vp(d_states), _vp(d_norm_sq), _vp(d_state_codes), _vp(d_norms),
+                                         device, _stream_ptr(stream)))
+
+
+def sign_search_candidates(mode, d_codes, d_row_params, d_offsets, nlist, d_probes, nq, nprobe, padded_dim, candidate_count,
+                           d_rows_out, d_dist_out=None, d_states=None, d_norm_sq=None, d_state_codes=None, d_norms=None,
+                           device=0, stream=None):
+    _check(lib().psb_sign_search_candidates(int(mode), _vp(d_states), _vp(d_norm_sq), _vp(d_state_codes), _vp(d_norms),
+                                            _vp(d_codes), _vp(d_row_params), _vp(d_offsets), nlist, _vp(d_probes), nq, nprobe,
+                                            padded_dim, candidate_count, _vp(d_rows_out), _vp(d_dist_out), device,
+                                            _stream_ptr(stream)))
+
+
+class SignIndex:
+    """The reference's IVFResTurboQuant index and search workspace in one object
+    (src/search/ivf_res_turboquant/ivf_res_turboquant_search.cuh:25-112): build_u8 / build_cached_u32 put sign codes, scales,
+    centroids and list offsets on the device; search_candidates takes host queries and probe ids and returns candidate rows."""
+
+    ENCODE_CHUNK_ROWS = 1 << 20   # the host corpus goes through the device in bounded chunks, as in residual_encoding.cu:24
+
+    def __init__(self, device=0):
+        import torch
+        self._t = torch
+        self.device = device
+        self.dev = torch.device("cuda", device)
+        self.n_vectors = self.n_clusters = self.dim = self.padded_dim = 0
+        self.rotation_seed = SIGN_ROTATION_SEED
+        self.codes = self.scales = self.centroids = self.offsets = None
+
+    @property
+    def bytes_per_vector(self):
+        return self.padded_dim // 32 * 4 + 4
+
+    def _place(self, centroids, offsets, n_vectors, dim):
+        t = self._t
+        centroids = np.ascontiguousarray(centroids, np.float32)
+        offsets = np.ascontiguousarray(offsets, np.int64)
+        padded = sign_padded_dim(dim)
+        if n_vectors <= 0 or centroids.ndim != 2 or centroids.shape[1] != dim or offsets.size != centroids.shape[0] + 1 or padded < 0:
+            raise InvalidArgument(1, "IVFResTurboQuant index build received invalid input")
+        self.n_vectors, self.n_clusters, self.dim, self.padded_dim = int(n_vectors), centroids.shape[0], int(dim), padded
+        self.centroids = t.from_numpy(centroids).to(self.dev)
+        self.offsets = t.from_numpy(offsets).to(self.dev)
+        self.host_offsets = offsets
+        self.codes = t.empty((self.n_vectors, padded // 32), dtype=t.int32, device=self.dev)
+        self.scales = t.empty(self.n_vectors, dtype=t.float32, device=self.dev)
+
+    def build_u8(self, host_vectors, host_centroids, host_cluster_offsets, rotation_seed=SIGN_ROTATION_SEED):
+        t = self._t
+        rows = np.ascontiguousarray(host_vectors)
+        if rows.dtype != np.uint8 and rows.dtype != np.float32:
+            raise InvalidArgument(1, "rows must be uint8 or float32")
+        self._place(host_centroids, host_cluster_offsets, rows.shape[0], rows.shape[1])
+        self.rotation_seed = int(rotation_seed)
+        for start in range(0, self.n_vectors, self.ENCODE_CHUNK_ROWS):
+            chunk = t.from_numpy(rows[start:start + self.ENCODE_CHUNK_ROWS]).to(self.dev)
+            sign_encode_database(chunk, rows.dtype.itemsize, chunk.shape[0], self.centroids, self.offsets, self.n_clusters,
+                                 self.dim, self.padded_dim, self.codes, self.scales, row_offset=start, seed=self.rotation_seed,
+                                 device=self.device)
+            t.cuda.synchronize(self.dev)
+        return self
+
+    def build_cached_u32(self, host_codes, host_scales, host_centroids, host_cluster_offsets):
+        t = self._t
+        codes = np.ascontiguousarray(host_codes, np.uint32)
+        scales = np.ascontiguousarray(host_scales, np.float32)
+        dim = np.asarray(host_centroids).shape[1]
+        if dim % 32 != 0 or codes.ndim != 2 or codes.shape[0] != scales.shape[0]:
+            raise InvalidArgument(1, "IVFResTurboQuant cached build received invalid input")
+        self._place(host_centroids, host_cluster_offsets, codes.shape[0], dim)
+        if codes.shape[1] != self.padded_dim // 32:
+            raise InvalidArgument(1, "IVFResTurboQuant cached build received invalid input")
+        self.rotation_seed = SIGN_ROTATION_SEED
+        self.codes.copy_(t.from_numpy(codes.view(np.int32)))
+        self.scales.copy_(t.from_numpy(scales))
+        return self
+
+    def search_candidates(self, host_queries, host_probe_ids, candidate_count=512, score_mode=SIGN_FLOAT_STATES,
+                          want_distances=False):
+        """host_queries [nq][dim] fp32, host_probe_ids [nq][nprobe] (ids outside the index are skipped); candidate rows
+        [nq][candidate_count] int32 in ascending (score, row) order, -1 where fewer rows were scanned."""
+        t = self._t
+        if self.n_vectors <= 0:
+            raise InvalidArgument(1, "IVFResTurboQuant search received invalid input")
+        q = np.ascontiguousarray(host_queries, np.float32)
+        probes = np.ascontiguousarray(host_probe_ids)
+        if q.ndim != 2 or q.shape[1] != self.dim or probes.ndim != 2 or probes.shape[0] != q.shape[0] or q.shape[0] <= 0 \
+                or probes.shape[1] <= 0 or candidate_count <= 0:
+            raise InvalidArgument(1, "IVFResTurboQuant search received invalid input")
+        nq, nprobe = probes.shape
+        bad = (probes < 0) | (probes >= self.n_clusters)
+        d_probes = t.from_numpy(np.where(bad, -1, probes).astype(np.int32)).to(self.dev)
+        d_q = t.from_numpy(q).to(self.dev)
+        words = self.padded_dim // 32
+        st = nsq = sc = nm = None
+        if score_mode == SIGN_FLOAT_STATES:
+            st = t.empty((nq * nprobe, self.padded_dim), dtype=t.float32, device=self.dev)
+            nsq = t.empty(nq * nprobe, dtype=t.float32, device=self.dev)
+        else:
+            sc = t.empty((nq * nprobe, words), dtype=t.int32, device=self.dev)
+            nm = t.empty(nq * nprobe, dtype=t.float32, device=self.dev)
+        sign_encode_queries(d_q, self.centroids, d_probes, nq, nprobe, self.n_clusters, self.dim, self.padded_dim, d_states=st,
+                            d_norm_sq=nsq, d_state_codes=sc, d_norms=nm, seed=self.rotation_seed, device=self.device)
+        rows = t.empty((nq, candidate_count), dtype=t.int32, device=self.dev)
+        dist = t.empty((nq, candidate_count), dtype=t.float32, device=self.dev) if want_distances else None
+        sign_search_candidates(score_mode, self.codes, self.scales, self.offsets, self.n_clusters, d_probes, nq, nprobe,
+                               self.padded_dim, candidate_count, rows, dist, d_states=st, d_norm_sq=nsq, d_state_codes=sc,
+                               d_norms=nm, device=self.device)
+        t.cuda.synchronize(self.dev)
+        return (rows.cpu().numpy(), dist.cpu().numpy()) if want_distances else rows.cpu().numpy()
 
 
 def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):

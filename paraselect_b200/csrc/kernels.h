@@ -79,6 +79,25 @@ psb_status launch_coarse_tc_assign(const CoarseTcIndex& ix, const CoarseTcWorksp
 // in-order fp32 fma chain per element.  d_out must not alias d_in.
 psb_status launch_rotate_rows(const float* d_in, const float* d_matrix, long long n, int dim, float* d_out, cudaStream_t s);
 
+// ---- TurboQuant 1-bit residual codec (sign_codec.cu) ----------------------------------------------------------
+int sign_padded_dim(int dim);   // 32, 64, 128 or 256; -1 above 256
+psb_status launch_sign_scale(int padded_dim, float* d_out, cudaStream_t s);   // the device's rsqrtf(padded_dim)
+// Any of d_rotated [n][padded], d_codes [n][padded / 32], d_norms [n], d_norm_sq [n] may be null.
+psb_status launch_sign_rotate(const float* d_rows, long long n, int dim, int padded_dim, uint32_t seed, float* d_rotated,
+                              uint32_t* d_codes, float* d_norms, float* d_norm_sq, int sm_count, cudaStream_t s);
+// Rows [row_offset, row_offset + n) of a list-contiguous index; codes and scales are indexed by global row.
+psb_status launch_sign_encode_database(const void* d_rows, int elem_bytes, long long n, const float* d_centroids,
+                                       const long long* d_offsets, int nlist, int dim, int padded_dim, uint32_t seed,
+                                       long long row_offset, uint32_t* d_codes, float* d_scales, int sm_count, cudaStream_t s);
+psb_status launch_sign_encode_queries(const float* d_queries, const float* d_centroids, const int* d_probes, int nq, int nprobe,
+                                      int nlist, int dim, int padded_dim, uint32_t seed, float* d_states, float* d_norm_sq,
+                                      uint32_t* d_state_codes, float* d_norms, int sm_count, cudaStream_t s);
+// mode 0: float states + norm_sq against reconstruction scales; mode 1: sign-coded states + norms against row norms.
+psb_status launch_sign_candidates(int mode, const float* d_states, const float* d_norm_sq, const uint32_t* d_state_codes,
+                                  const float* d_norms, const uint32_t* d_codes, const float* d_row_params,
+                                  const long long* d_offsets, int nlist, const int* d_probes, int nq, int nprobe, int padded_dim,
+                                  int candidate_count, int* d_rows_out, float* d_dist_out, int sm_count, cudaStream_t s);
+
 // ---- PQ lookup tables --------------------------------------------------------------------------------
 psb_status launch_build_lut(const float* d_queries, int nq, int dim, const float* d_codebook, int m, int k,
                             float* d_lut, cudaStream_t s);

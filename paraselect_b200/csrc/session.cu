@@ -77,6 +77,31 @@ psb_status check_device(int device, cudaDeviceProp* prop_out = nullptr) {
     return PSB_OK;
 }
 
+// The same check for operators called once per batch: attribute queries (microseconds) instead of the full property
+// block (milliseconds), and the SM count remembered per device.
+psb_status check_device_quick(int device, int* sm_count) {
+    static int known_sms[64] = {0};
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return fail(PSB_NO_DEVICE, "no CUDA device is usable; this library has no CPU path");
+    }
+    if (device < 0 || device >= n) return fail(PSB_INVALID_ARGUMENT, "device ordinal out of range");
+    if (device >= 64 || known_sms[device] == 0) {
+        int major = 0, sms = 0;
+        PSB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        PSB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        if (major != 10) return fail(PSB_NO_DEVICE, "device is not sm_100 (kernels are built for sm_100a only)");
+        if (device < 64) known_sms[device] = sms;
+        if (sm_count) *sm_count = sms;
+    } else if (sm_count) {
+        *sm_count = known_sms[device];
+    }
+    PSB_CUDA(cudaSetDevice(device));
+    return PSB_OK;
+}
+
 // Persistent fork-join pool of host threads for the staged rerank transport (the reference keeps a persistent rerank pool
 // too: src/search/ivf_common/ivf_host_rerank.cpp:42-51).  run(job) calls job(t) on every thread t and returns when all are done.
 class HostPool {
@@ -939,6 +964,73 @@ psb_status psb_rotate_rows(const float* d_in, const float* d_matrix, int64_t n, 
     if (!d_in || !d_matrix || !d_out || n < 0 || dim <= 0 || d_in == d_out) return fail(PSB_INVALID_ARGUMENT, "invalid rotation request");
     PSB_TRY(check_device(device));
     return launch_rotate_rows(d_in, d_matrix, n, dim, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int psb_sign_padded_dim(int dim) { return sign_padded_dim(dim); }
+
+psb_status psb_sign_rotation_scale(int padded_dim, float* h_scale, int device, void* stream) {
+    if (!h_scale || sign_padded_dim(padded_dim) != padded_dim) return fail(PSB_INVALID_ARGUMENT, "padded_dim must be 32, 64, 128 or 256");
+    PSB_TRY(check_device(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* d = nullptr;
+    PSB_CUDA(cudaMalloc(reinterpret_cast<void**>(&d), sizeof(float)));
+    psb_status rc = launch_sign_scale(padded_dim, d, st);
+    cudaError_t e = rc == PSB_OK ? cudaMemcpyAsync(h_scale, d, sizeof(float), cudaMemcpyDeviceToHost, st) : cudaSuccess;
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d);
+    if (rc == PSB_OK && e != cudaSuccess) rc = cuda_fail(e, "psb_sign_rotation_scale", __FILE__, __LINE__);
+    return rc;
+}
+
+psb_status psb_sign_rotate(const float* d_rows, int64_t n, int dim, int padded_dim, uint32_t seed, float* d_rotated,
+                           uint32_t* d_codes, float* d_norms, float* d_norm_sq, int device, void* stream) {
+    if (!d_rows || n < 0 || (!d_rotated && !d_codes && !d_norms && !d_norm_sq)) return fail(PSB_INVALID_ARGUMENT, "invalid sign rotation request");
+    int sms = 0;
+    PSB_TRY(check_device_quick(device, &sms));
+    return launch_sign_rotate(d_rows, n, dim, padded_dim, seed, d_rotated, d_codes, d_norms, d_norm_sq, sms,
+                              static_cast<cudaStream_t>(stream));
+}
+
+psb_status psb_sign_encode_database(const void* d_rows, int elem_bytes, int64_t n, const float* d_centroids,
+                                    const int64_t* d_list_offsets, int nlist, int dim, int padded_dim, uint32_t seed,
+                                    int64_t row_offset, uint32_t* d_codes, float* d_scales, int device, void* stream) {
+    if (!d_rows || !d_centroids || !d_list_offsets || !d_codes || n < 0 || nlist <= 0 || row_offset < 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid sign database encoding request");
+    if (elem_bytes != 1 && elem_bytes != 4) return fail(PSB_INVALID_ARGUMENT, "rows must be u8 (1) or fp32 (4)");
+    int sms = 0;
+    PSB_TRY(check_device_quick(device, &sms));
+    return launch_sign_encode_database(d_rows, elem_bytes, n, d_centroids, reinterpret_cast<const long long*>(d_list_offsets), nlist,
+                                       dim, padded_dim, seed, row_offset, d_codes, d_scales, sms,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+psb_status psb_sign_encode_queries(const float* d_queries, const float* d_centroids, const int* d_probes, int nq, int nprobe,
+                                   int nlist, int dim, int padded_dim, uint32_t seed, float* d_states, float* d_norm_sq,
+                                   uint32_t* d_state_codes, float* d_norms, int device, void* stream) {
+    if (!d_queries || !d_centroids || !d_probes || nq < 0 || nprobe <= 0 || nlist <= 0 || (!d_states && !d_state_codes))
+        return fail(PSB_INVALID_ARGUMENT, "invalid sign query encoding request");
+    int sms = 0;
+    PSB_TRY(check_device_quick(device, &sms));
+    return launch_sign_encode_queries(d_queries, d_centroids, d_probes, nq, nprobe, nlist, dim, padded_dim, seed, d_states, d_norm_sq,
+                                      d_state_codes, d_norms, sms, static_cast<cudaStream_t>(stream));
+}
+
+psb_status psb_sign_search_candidates(int mode, const float* d_states, const float* d_norm_sq, const uint32_t* d_state_codes,
+                                      const float* d_norms, const uint32_t* d_codes, const float* d_row_params,
+                                      const int64_t* d_list_offsets, int nlist, const int* d_probes, int nq, int nprobe,
+                                      int padded_dim, int candidate_count, int* d_rows_out, float* d_dist_out, int device,
+                                      void* stream) {
+    PSB_RANGE("sign_candidates");
+    if (mode != PSB_SIGN_FLOAT_STATES && mode != PSB_SIGN_CODED_STATES) return fail(PSB_INVALID_ARGUMENT, "unknown sign score mode");
+    if (mode == PSB_SIGN_FLOAT_STATES ? (!d_states || !d_norm_sq) : (!d_state_codes || !d_norms))
+        return fail(PSB_INVALID_ARGUMENT, "the states of the chosen score mode are missing");
+    if (!d_codes || !d_row_params || !d_list_offsets || !d_probes || !d_rows_out || nq < 0 || nprobe <= 0 || nlist <= 0)
+        return fail(PSB_INVALID_ARGUMENT, "invalid sign candidate search request");
+    int sms = 0;
+    PSB_TRY(check_device_quick(device, &sms));
+    return launch_sign_candidates(mode, d_states, d_norm_sq, d_state_codes, d_norms, d_codes, d_row_params,
+                                  reinterpret_cast<const long long*>(d_list_offsets), nlist, d_probes, nq, nprobe, padded_dim,
+                                  candidate_count, d_rows_out, d_dist_out, sms, static_cast<cudaStream_t>(stream));
 }
 
 psb_status psb_stage_rotate_queries(psb_session* s, const float* d_queries, int nq, float* d_rotated) {
