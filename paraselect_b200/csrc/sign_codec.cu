@@ -316,15 +316,68 @@ __device__ __forceinline__ int sign_finish(uint64_t* keys, uint64_t* spill, int 
     return n;
 }
 
+// The exact score of rows against a float state: one chain over d = 0..dim-1 per row, the rows of a thread interleaved.
+template <int W>
+__device__ __forceinline__ void exact_float_scores(const CodeWords<W> (&c)[kScanRows], const float (&param)[kScanRows],
+                                                   const float* s_state, float norm_sq, float (&score)[kScanRows]) {
+    float dot[kScanRows];
+#pragma unroll
+    for (int r = 0; r < kScanRows; ++r) dot[r] = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+#pragma unroll
+        for (int bit = 0; bit < 32; ++bit) {
+            const float qv = s_state[32 * w + bit];
+#pragma unroll
+            for (int r = 0; r < kScanRows; ++r) dot[r] = sign_step(dot[r], qv, c[r].w[w], 1u << bit);
+        }
+    }
+    const float dimf = (float)(32 * W);
+#pragma unroll
+    for (int r = 0; r < kScanRows; ++r) {
+        const float s = param[r];
+        score[r] = __fmaf_rn(-__fmul_rn(2.0f, s), dot[r], __fmaf_rn(__fmul_rn(dimf, s), s, norm_sq));
+    }
+}
+
+// The signed sum of a row from a table of the 16 possible sums of every group of four dimensions: dim / 4 look-ups instead of
+// dim additions.  The order of the additions differs from the chain's, so the value may differ from the exact dot in the last
+// bits; the caller allows for that.  lut[g * 16 + v], v = the four sign bits of group g: the 16 entries of a group lie in 16
+// different banks, so a warp's look-ups never collide.
+template <int W>
+__device__ __forceinline__ float table_dot(const CodeWords<W>& c, const float* lut) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+        const uint32_t word = c.w[w];
+#pragma unroll
+        for (int t = 0; t < 8; t += 2) {
+            a0 += lut[(8 * w + t) * 16 + ((word >> (4 * t)) & 15u)];
+            a1 += lut[(8 * w + t + 1) * 16 + ((word >> (4 * t + 4)) & 15u)];
+        }
+    }
+    return a0 + a1;
+}
+
 // Six CTAs per SM up to 128 dimensions (two at 256): the register cap also keeps the compiler from holding a whole state in
 // registers across the row loop, which would leave one CTA per SM.
+//
+// Float states, once a cutoff exists: a row's score is first taken from the table (table_dot), and only rows whose score could
+// still be below the cutoff - the table score minus a bound on its error against the exact chain - are queued and scored
+// exactly, densely, one queued row per thread.  Error bound: with A = sum |state[d]|, every partial sum on either path is at
+// most A in magnitude and every rounding at most 2^-24 of it; the chain has dim <= 256 roundings, the table path fewer than 80
+// (3 per entry, dim / 4 + 1 additions), so |table - chain| < 336 * 2^-24 * A < 2^-15 * A for every dim here.  The queue test
+// uses 2^-14 * A (twice that) on the dot and 2^-20 relative on the final fused multiply-adds.
 template <int W, int MODE>
 __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(const SignScanArgs a) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(s_raw);
     uint64_t* spill = keys + a.cap;                                       // k keys
-    float* s_state = reinterpret_cast<float*>(spill + ((a.k + 1) & ~1));  // W * 32 floats (MODE 0), 16-byte aligned
+    float* s_state = reinterpret_cast<float*>(spill + ((a.k + 1) & ~1));  // 256 floats: the state (MODE 0), 16-byte aligned
+    float* s_lut = s_state + 256;                                         // W * 128 floats: the table (MODE 0)
     __shared__ SignSelectScratch s_sel;
+    __shared__ uint32_t s_queue[kScanStep];
+    __shared__ int s_qn;
     uint32_t qcode[W];                                                   // the state's sign words (MODE 1)
 #pragma unroll
     for (int w = 0; w < W; ++w) qcode[w] = 0u;
@@ -333,15 +386,32 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
     const int q = blockIdx.x / a.split, slice = blockIdx.x % a.split;
     const int tid = threadIdx.x;
     const float dimf = (float)(32 * W);
-    if (tid == 0) { s_cnt = 0; s_thr = KEY_MAX; }
+    if (tid == 0) { s_cnt = 0; s_thr = KEY_MAX; s_qn = 0; }
     __syncthreads();
     for (int p = slice; p < a.nprobe; p += a.split) {
         const long long st = (long long)q * a.nprobe + p;
         const int list = a.probes[st];
         if (list < 0 || list >= a.nlist) continue;   // uniform
         __syncthreads();
+        float abs_sum = 0.f;   // MODE 0: sum |state[d]|, rounded up a little
         if (MODE == 0) {
             for (int d = tid; d < 32 * W; d += kScanThreads) s_state[d] = a.states[(size_t)st * (32 * W) + d];
+            __syncthreads();
+            for (int e = tid; e < W * 128; e += kScanThreads) {   // entry v of group g: ((+-x0 +- x1) +- x2) +- x3
+                const int g = e >> 4, v = e & 15;
+                const float* x = s_state + 4 * g;
+                float t = (v & 1) ? x[0] : -x[0];
+                t += (v & 2) ? x[1] : -x[1];
+                t += (v & 4) ? x[2] : -x[2];
+                t += (v & 8) ? x[3] : -x[3];
+                s_lut[e] = t;
+            }
+            const int lane = tid & 31;
+#pragma unroll
+            for (int j = 0; j < W; ++j) abs_sum += fabsf(s_state[lane + 32 * j]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) abs_sum += __shfl_xor_sync(kFull, abs_sum, o);
+            abs_sum *= 1.001f;
         } else {
 #pragma unroll
             for (int w = 0; w < W; ++w) qcode[w] = __ldg(a.state_codes + (size_t)st * W + w);   // the same words in every thread
@@ -358,11 +428,12 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
             CodeWords<W> c[kScanRows];
             float param[kScanRows];
             bool ok[kScanRows];
+            long long rows[kScanRows];
 #pragma unroll
             for (int r = 0; r < kScanRows; ++r) {
-                const long long row = row0 + r * kScanThreads + tid;
-                ok[r] = row < end;
-                if (ok[r]) { c[r] = load_code<W>(a.codes, row); param[r] = __ldg(a.row_params + row); }
+                rows[r] = row0 + r * kScanThreads + tid;
+                ok[r] = rows[r] < end;
+                if (ok[r]) { c[r] = load_code<W>(a.codes, rows[r]); param[r] = __ldg(a.row_params + rows[r]); }
                 else {
 #pragma unroll
                     for (int w = 0; w < W; ++w) c[r].w[w] = 0u;
@@ -370,24 +441,33 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
                 }
             }
             float score[kScanRows];
-            if (MODE == 0) {
-                float dot[kScanRows];
-#pragma unroll
-                for (int r = 0; r < kScanRows; ++r) dot[r] = 0.f;
-#pragma unroll
-                for (int w = 0; w < W; ++w) {
-#pragma unroll
-                    for (int bit = 0; bit < 32; ++bit) {
-                        const float qv = s_state[32 * w + bit];
-#pragma unroll
-                        for (int r = 0; r < kScanRows; ++r) dot[r] = sign_step(dot[r], qv, c[r].w[w], 1u << bit);
-                    }
-                }
+            if (MODE == 0 && thr != KEY_MAX) {   // uniform
+                const float cut = key_dist(thr);
+                const float dot_slack = abs_sum * (1.0f / 16384.0f);
 #pragma unroll
                 for (int r = 0; r < kScanRows; ++r) {
-                    const float s = param[r];
-                    score[r] = __fmaf_rn(-__fmul_rn(2.0f, s), dot[r], __fmaf_rn(__fmul_rn(dimf, s), s, qparam));
+                    if (!ok[r]) continue;
+                    const float s = param[r], two_s = fabsf(2.0f * s);
+                    const float base = __fmaf_rn(__fmul_rn(dimf, s), s, qparam);
+                    const float rough = __fmaf_rn(-__fmul_rn(2.0f, s), table_dot<W>(c[r], s_lut), base);
+                    const float slack = two_s * dot_slack + (fabsf(base) + two_s * abs_sum) * (1.0f / 1048576.0f);
+                    if (!(rough - slack > cut)) s_queue[atomicAdd(&s_qn, 1)] = (uint32_t)(rows[r] - beg);   // NaN queues too
                 }
+                __syncthreads();
+                const int queued = s_qn;
+#pragma unroll
+                for (int r = 0; r < kScanRows; ++r) {
+                    const int at = r * kScanThreads + tid;
+                    ok[r] = at < queued;
+                    if (ok[r]) {
+                        rows[r] = beg + s_queue[at];
+                        c[r] = load_code<W>(a.codes, rows[r]);
+                        param[r] = __ldg(a.row_params + rows[r]);
+                    }
+                }
+                if (tid < queued) exact_float_scores<W>(c, param, s_state, qparam, score);   // whole warps drop out
+            } else if (MODE == 0) {
+                exact_float_scores<W>(c, param, s_state, qparam, score);
             } else {
 #pragma unroll
                 for (int r = 0; r < kScanRows; ++r) {
@@ -402,10 +482,11 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
 #pragma unroll
             for (int r = 0; r < kScanRows; ++r) {
                 if (!ok[r]) continue;
-                const uint64_t key = make_key(score[r], (uint32_t)(row0 + r * kScanThreads + tid));
+                const uint64_t key = make_key(score[r], (uint32_t)rows[r]);
                 if (key < thr) keys[atomicAdd(&s_cnt, 1)] = key;   // room for a whole step was checked above
             }
             __syncthreads();
+            if (tid == 0) s_qn = 0;   // read by everybody before the barrier above, appended to after the next one
         }
     }
     __syncthreads();
@@ -562,7 +643,7 @@ psb_status launch_sign_candidates(int mode, const float* d_states, const float* 
         PSB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&partial), sizeof(uint64_t) * (size_t)nq * split * candidate_count, s));
         a.partial = partial;
     }
-    const size_t smem = sizeof(uint64_t) * ((size_t)a.cap + ((candidate_count + 1) & ~1)) + sizeof(float) * 256;
+    const size_t smem = sizeof(uint64_t) * ((size_t)a.cap + ((candidate_count + 1) & ~1)) + sizeof(float) * (256 + 1024);
     psb_status rc = mode == 0 ? dispatch_scan<0>(a, smem, s) : dispatch_scan<1>(a, smem, s);
     if (rc == PSB_OK && split > 1) {
         const int mcap = pow2_at_least(split * candidate_count);
