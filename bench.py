@@ -49,6 +49,9 @@ WORKLOADS = {
                seed=4, iters=20, pq_iters=25,
                desc="training: 10M x 128 rows (4,096-component mixture, sigma 0.3) -> k-means to 65,536 centroids (20 Lloyd iterations), "
                     "PQ M=32 x 8 bit on residuals (25 iterations), encode"),
+    # secondary line: the 1-bit sign codec (TurboQuant) - database encoding and candidate search over sign-coded lists
+    "sign": dict(n=20_000_000, dim=128, nlist=8192, M=0, sigma=0.0, zipf=None, nq=10000, nprobe=32, topk=512, n_rerank=0, seed=6,
+                 desc="1-bit sign codec: 20M x 128 u8 rows in 8,192 lists, 10,000 queries x 32 probes, 512 candidates, float states"),
     # benchmark configuration "coarse stage only" (secondary line: tensor-core roofline of the fused coarse GEMM)
     "c3": dict(n=65536, dim=96, nlist=65536, M=8, sigma=0.0, zipf=None, nq=100000, nprobe=64, topk=64, n_rerank=0, seed=2,
                desc="coarse only: 100,000 queries x 65,536 centroids, d=96, unit-mean-norm N(0,1), top-64"),
@@ -377,8 +380,8 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's banner and warnings go to stderr: stdout is one JSON line
         dist.init_process_group("nccl")
-    if args.impl == "ours" and world > 1 and args.workload in ("c3", "c5"):
-        raise SystemExit("workloads c3 and c5 are single-GPU lines")
+    if args.impl == "ours" and world > 1 and args.workload in ("c3", "c5", "sign"):
+        raise SystemExit("workloads c3, c5 and sign are single-GPU lines")
     if args.impl == "ours" and world > 1:
         return multi_gpu_main(args, cfg, rank, world, local_rank)
 
@@ -390,6 +393,8 @@ def main():
         return coarse_only(args, cfg, torch, api, device)
     if args.workload == "c5":
         return training(args, cfg, torch, api, device)
+    if args.workload == "sign":
+        return sign_codec(args, cfg, torch, api, device)
 
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -1032,6 +1037,167 @@ def training(args, cfg, torch, api, device):
                 residual_s=round(t1 - t0, 3), total_training_estimate_s=round((ms_first + ms * cfg["iters"]) * 1e-3 + (t3 - t0), 2),
                 parity=dict(sample_rows=ns, assign_equal=assign_equal), clocks=clocks)
     emit(line)
+    return 0
+
+
+def sign_codec(args, cfg, torch, api, device):
+    """Secondary workload: the 1-bit sign codec.  A step = query states + candidate search for one batch of queries over
+    sign-coded lists (probes given); the database encoding is timed once.  Rows, centroids and queries are uniform / normal
+    noise: the scan's work does not depend on the values."""
+    import oracle
+    n, dim, nlist, nq, nprobe, k = cfg["n"], cfg["dim"], cfg["nlist"], cfg["nq"], cfg["nprobe"], cfg["topk"]
+    padded = api.sign_padded_dim(dim) if args.impl == "ours" else oracle.sign_padded_dim(dim)
+    words = padded // 32
+    rng = np.random.default_rng(cfg["seed"])
+    sizes = rng.multinomial(n, rng.dirichlet(np.full(nlist, 3.0)))
+    off_h = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    cen_h = (rng.standard_normal((nlist, dim)) * 20 + 100).astype(np.float32)
+    q_h = (rng.standard_normal((nq, dim)) * 20 + 100).astype(np.float32)
+    probes_h = np.stack([rng.permutation(nlist)[:nprobe] for _ in range(min(nq, 256))])
+    probes_h = np.tile(probes_h, ((nq + probes_h.shape[0] - 1) // probes_h.shape[0], 1))[:nq].astype(np.int32)
+    visits = int(sizes[probes_h].sum())
+    cores = os.cpu_count() or 1
+
+    def cpu_sample(ns, seed_rows=200_000):
+        """The restatement on a bounded sample: ns queries against an index of the first lists holding ~seed_rows rows."""
+        nl = max(nprobe, int(np.searchsorted(off_h, seed_rows)))
+        rows = rng.integers(0, 256, (int(off_h[nl]), dim)).astype(np.uint8)
+        codes, scales = oracle.sign_encode_database(rows, cen_h[:nl], off_h[:nl + 1], padded)
+        pr = np.stack([rng.permutation(nl)[:nprobe] for _ in range(ns)]).astype(np.int32)
+        t0 = time.time()
+        st, nsq, _, _ = oracle.sign_encode_queries(q_h[:ns], cen_h[:nl], pr, padded)
+        oracle.sign_candidates(0, codes, scales, off_h[:nl + 1], pr, k, states=st, norm_sq=nsq)
+        dt = time.time() - t0
+        v = int(np.diff(off_h[:nl + 1])[pr].sum())
+        return ns / dt, v / dt, "%d queries x %d probes over %d rows, all %d host threads" % (ns, nprobe, rows.shape[0], cores)
+
+    if args.impl == "reference":
+        # the reference's scan is a GPU kernel: the restatement of its arithmetic on the host cores, a bounded sample per step
+        times, vals = [], []
+        for i in range(args.warmup + args.steps):
+            qps, vps, sample = cpu_sample(args.cpu_sample or 64)
+            if i >= args.warmup:
+                times.append(1.0 / qps); vals.append(qps)
+        v = round(float(np.mean(vals)), 2)
+        emit(dict(impl="reference", metric="sign-codec candidate search queries/s", value=v, unit="queries/s", n_gpus=args.gpus,
+                  steps=args.steps, warmup=args.warmup, ms_per_step=round(1e3 * (args.cpu_sample or 64) / v, 3), higher_is_better=True,
+                  scaling="strong", vs_baseline=None, dtype="f32", data="synthetic", config=dict(workload="sign", desc=cfg["desc"]),
+                  cpu_baseline=dict(value=v, unit="queries/s", cores=cores, kind="port", sample=sample),
+                  e2e=dict(value=v, unit="queries/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0)))
+        return 0
+
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    with torch.cuda.stream(stream):
+        off = torch.from_numpy(off_h).cuda(); cen = torch.from_numpy(cen_h).cuda()
+        codes = torch.empty((n, words), dtype=torch.int32, device="cuda")
+        scales = torch.empty(n, dtype=torch.float32, device="cuda")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        enc_ms = []
+        chunk = 4_000_000   # the corpus passes through the device in chunks, as a host-resident one would
+        gen = torch.Generator(device="cuda"); gen.manual_seed(cfg["seed"])
+        for start in range(0, n, chunk):
+            m = min(chunk, n - start)
+            rows = torch.randint(0, 256, (m, dim), dtype=torch.uint8, device="cuda", generator=gen)
+            stream.synchronize()
+            e0.record(stream)
+            api.sign_encode_database(rows, 1, m, cen, off, nlist, dim, padded, codes, scales, row_offset=start, device=device, stream=sp)
+            e1.record(stream)
+            stream.synchronize()
+            enc_ms.append(e0.elapsed_time(e1))
+            if start == 0:   # the first chunk against the restatement, bit for bit
+                ns = 4096
+                scale = api.sign_rotation_scale(padded, device=device)
+                wc, ws = oracle.sign_encode_database(rows[:ns].cpu().numpy(), cen_h, off_h, padded, scale=scale)
+                enc_equal = bool(np.array_equal(codes[:ns].cpu().numpy().view(np.uint32), wc[:ns]) and
+                                 np.array_equal(scales[:ns].cpu().numpy().view(np.uint32), ws[:ns].view(np.uint32)))
+            del rows
+        q = torch.from_numpy(q_h).cuda(); probes = torch.from_numpy(probes_h).cuda()
+        st = torch.empty((nq * nprobe, padded), dtype=torch.float32, device="cuda")
+        nsq = torch.empty(nq * nprobe, dtype=torch.float32, device="cuda")
+        out_r = torch.empty((nq, k), dtype=torch.int32, device="cuda")
+        out_d = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+
+        def step():
+            api.sign_encode_queries(q, cen, probes, nq, nprobe, nlist, dim, padded, d_states=st, d_norm_sq=nsq, device=device, stream=sp)
+            api.sign_search_candidates(api.SIGN_FLOAT_STATES, codes, scales, off, nlist, probes, nq, nprobe, padded, k, out_r, out_d,
+                                       d_states=st, d_norm_sq=nsq, device=device, stream=sp)
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        sampler = ClockSampler(device)
+        sampler.start()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        # the scan alone
+        e0.record(stream)
+        for _ in range(args.steps):
+            api.sign_search_candidates(api.SIGN_FLOAT_STATES, codes, scales, off, nlist, probes, nq, nprobe, padded, k, out_r, out_d,
+                                       d_states=st, d_norm_sq=nsq, device=device, stream=sp)
+        e1.record(stream)
+        stream.synchronize()
+        scan_ms = e0.elapsed_time(e1) / args.steps
+        # end to end: host queries and probe ids in, host candidate rows out
+        qp = torch.empty((nq, dim), dtype=torch.float32).pin_memory(); qp.copy_(q)
+        pp = torch.empty((nq, nprobe), dtype=torch.int32).pin_memory(); pp.copy_(probes)
+        oi = torch.empty((nq, k), dtype=torch.int32).pin_memory()
+        q2 = torch.empty_like(q); p2 = torch.empty_like(probes)
+
+        def e2e_step():
+            q2.copy_(qp, non_blocking=True); p2.copy_(pp, non_blocking=True)
+            api.sign_encode_queries(q2, cen, p2, nq, nprobe, nlist, dim, padded, d_states=st, d_norm_sq=nsq, device=device, stream=sp)
+            api.sign_search_candidates(api.SIGN_FLOAT_STATES, codes, scales, off, nlist, p2, nq, nprobe, padded, k, out_r, None,
+                                       d_states=st, d_norm_sq=nsq, device=device, stream=sp)
+            oi.copy_(out_r, non_blocking=True)
+            stream.synchronize()
+        e2e_step()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record(stream)
+        stream.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+        # parity on a sample of queries: codes and scales of the whole index from the device, candidates from the restatement
+        ns = args.cpu_sample or 8
+        scale = api.sign_rotation_scale(padded, device=device)
+        codes_h = codes.cpu().numpy().view(np.uint32); scales_h = scales.cpu().numpy()
+        w_st, w_nsq, _, _ = oracle.sign_encode_queries(q_h[:ns], cen_h, probes_h[:ns], padded, scale=scale)
+        w_rows, w_dist = oracle.sign_candidates(0, codes_h, scales_h, off_h, probes_h[:ns], k, states=w_st, norm_sq=w_nsq)
+        got_r, got_d = out_r[:ns].cpu().numpy(), out_d[:ns].cpu().numpy()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    qps_cpu, vps_cpu, sample = cpu_sample(256)
+    bytes_per_launch = visits * (words * 4 + 4)
+    achieved = bytes_per_launch / (scan_ms * 1e-3) / 1e9
+    emit(dict(metric="sign-codec candidate search queries/s", value=round(nq / (ms * 1e-3), 1), unit="queries/s", n_gpus=1,
+              steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms, 3), higher_is_better=True, scaling="strong",
+              vs_baseline=None, dtype="f32 chains over 1-bit codes", data="synthetic",
+              config=dict(workload="sign", desc=cfg["desc"], rows=n, queries=nq, row_visits_per_step=visits,
+                          l2="codes + scales %.0f MB, larger than L2" % (n * (words * 4 + 4) / 1e6)),
+              e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 3),
+                       h2d_bytes_per_step=nq * dim * 4 + nq * nprobe * 4, d2h_bytes_per_step=nq * k * 4),
+              gpu_launches=2 * args.steps,
+              roofline=dict(bound="hbm", kernel="k_sign_scan<4,0>", achieved=round(achieved, 1), peak=peak, unit="GB/s",
+                            frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
+                            ms_per_launch=round(scan_ms, 3), algorithmic_bytes_per_launch=bytes_per_launch,
+                            bytes_per_row_visit=words * 4 + 4, row_visits_per_s=round(visits / (scan_ms * 1e-3), 1), traffic=None,
+                            note="instruction-issue bound, not memory bound: see profiles/"),
+              encode=dict(rows=n, ms=round(float(np.sum(enc_ms)), 3), rows_per_s=round(n / (float(np.sum(enc_ms)) * 1e-3), 1),
+                          gbs=round(n * (dim + words * 4 + 4) / (float(np.sum(enc_ms)) * 1e-3) / 1e9, 1), equal_to_checker=enc_equal),
+              cpu_baseline=dict(value=round(qps_cpu, 2), unit="queries/s", cores=cores, kind="port", sample=sample,
+                                row_visits_per_s=round(vps_cpu, 1)),
+              parity=dict(sample_queries=ns, rows_equal=bool(np.array_equal(got_r, w_rows)),
+                          scores_equal=bool(np.array_equal(got_d.view(np.uint32), w_dist.view(np.uint32)))),
+              clocks=clocks))
     return 0
 
 

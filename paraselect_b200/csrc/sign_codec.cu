@@ -316,10 +316,12 @@ __device__ __forceinline__ int sign_finish(uint64_t* keys, uint64_t* spill, int 
     return n;
 }
 
-// The exact score of rows against a float state: one chain over d = 0..dim-1 per row, the rows of a thread interleaved.
+// The exact scores of up to kScanRows rows per thread, each against the float state `state[r]` points to (global memory: the
+// rows of a thread may belong to different probes): one chain over d = 0..dim-1 per row, the chains interleaved.
 template <int W>
 __device__ __forceinline__ void exact_float_scores(const CodeWords<W> (&c)[kScanRows], const float (&param)[kScanRows],
-                                                   const float* s_state, float norm_sq, float (&score)[kScanRows]) {
+                                                   const float* const (&state)[kScanRows], const float (&norm_sq)[kScanRows],
+                                                   float (&score)[kScanRows]) {
     float dot[kScanRows];
 #pragma unroll
     for (int r = 0; r < kScanRows; ++r) dot[r] = 0.f;
@@ -327,16 +329,15 @@ __device__ __forceinline__ void exact_float_scores(const CodeWords<W> (&c)[kScan
     for (int w = 0; w < W; ++w) {
 #pragma unroll
         for (int bit = 0; bit < 32; ++bit) {
-            const float qv = s_state[32 * w + bit];
 #pragma unroll
-            for (int r = 0; r < kScanRows; ++r) dot[r] = sign_step(dot[r], qv, c[r].w[w], 1u << bit);
+            for (int r = 0; r < kScanRows; ++r) dot[r] = sign_step(dot[r], __ldg(state[r] + 32 * w + bit), c[r].w[w], 1u << bit);
         }
     }
     const float dimf = (float)(32 * W);
 #pragma unroll
     for (int r = 0; r < kScanRows; ++r) {
         const float s = param[r];
-        score[r] = __fmaf_rn(-__fmul_rn(2.0f, s), dot[r], __fmaf_rn(__fmul_rn(dimf, s), s, norm_sq));
+        score[r] = __fmaf_rn(-__fmul_rn(2.0f, s), dot[r], __fmaf_rn(__fmul_rn(dimf, s), s, norm_sq[r]));
     }
 }
 
@@ -359,28 +360,33 @@ __device__ __forceinline__ float table_dot(const CodeWords<W>& c, const float* l
     return a0 + a1;
 }
 
-// Six CTAs per SM up to 128 dimensions (two at 256): the register cap also keeps the compiler from holding a whole state in
-// registers across the row loop, which would leave one CTA per SM.
+constexpr int kQueueCap = 2 * kScanStep;   // rows waiting for their exact score
+
+// Scan of one (query, slice of probes) per CTA.
 //
-// Float states, once a cutoff exists: a row's score is first taken from the table (table_dot), and only rows whose score could
-// still be below the cutoff - the table score minus a bound on its error against the exact chain - are queued and scored
-// exactly, densely, one queued row per thread.  Error bound: with A = sum |state[d]|, every partial sum on either path is at
-// most A in magnitude and every rounding at most 2^-24 of it; the chain has dim <= 256 roundings, the table path fewer than 80
-// (3 per entry, dim / 4 + 1 additions), so |table - chain| < 336 * 2^-24 * A < 2^-15 * A for every dim here.  The queue test
-// uses 2^-14 * A (twice that) on the dot and 2^-20 relative on the final fused multiply-adds.
+// Sign-coded states (MODE 1): every row's score is a popcount; keys below the cutoff go to the buffer.
+//
+// Float states (MODE 0): a row's score is first taken from the table (table_dot), and only rows whose score could still be
+// below the cutoff - the table score minus a bound on its error against the exact chain - are queued, (row, probe), for the
+// exact chain.  The queue is worked off 1,024 rows at a time, four interleaved chains per thread on all threads, whenever it
+// holds that many (and once at the end), so the chains - 128 dependent additions each - always run with full warps.  Until
+// the first cutoff exists every row is queued.  A queued row is tested against the cutoff of the time its exact score is
+// taken; cutoffs only fall, so nothing is lost by waiting.
+// Error bound of the table score: with A = sum |state[d]|, every partial sum on either path is at most A in magnitude and
+// every rounding at most 2^-24 of it; the chain has dim <= 256 roundings, the table path fewer than 80 (3 per entry,
+// dim / 4 + 1 additions), so |table - chain| < 336 * 2^-24 * A < 2^-15 * A for every dim here.  The queue test uses
+// 2^-14 * A (twice that) on the dot and 2^-20 relative on the final fused multiply-adds.
 template <int W, int MODE>
-__global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(const SignScanArgs a) {
+__global__ void __launch_bounds__(kScanThreads, W > 4 ? 2 : (MODE == 1 ? 6 : 4)) k_sign_scan(const SignScanArgs a) {
     extern __shared__ __align__(16) unsigned char s_raw[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(s_raw);
     uint64_t* spill = keys + a.cap;                                       // k keys
     float* s_state = reinterpret_cast<float*>(spill + ((a.k + 1) & ~1));  // 256 floats: the state (MODE 0), 16-byte aligned
     float* s_lut = s_state + 256;                                         // W * 128 floats: the table (MODE 0)
     __shared__ SignSelectScratch s_sel;
-    __shared__ uint32_t s_queue[kScanStep];
+    __shared__ uint32_t s_qrow[MODE == 0 ? kQueueCap : 1];
+    __shared__ uint16_t s_qprobe[MODE == 0 ? kQueueCap : 1];
     __shared__ int s_qn;
-    uint32_t qcode[W];                                                   // the state's sign words (MODE 1)
-#pragma unroll
-    for (int w = 0; w < W; ++w) qcode[w] = 0u;
     __shared__ int s_cnt;
     __shared__ unsigned long long s_thr;
     const int q = blockIdx.x / a.split, slice = blockIdx.x % a.split;
@@ -388,12 +394,67 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
     const float dimf = (float)(32 * W);
     if (tid == 0) { s_cnt = 0; s_thr = KEY_MAX; s_qn = 0; }
     __syncthreads();
+
+    // MODE 0: takes the exact scores of queued rows, 1,024 per round; with `all` also the last, partial round.  Called by
+    // all threads after a barrier that follows the last append to the queue.
+    auto work_off_queue = [&](bool all) {
+        const int queued = s_qn;
+        int done = 0;
+        while (queued - done >= (all ? 1 : kScanStep)) {
+            const int take = min(kScanStep, queued - done);
+            const int held = s_cnt;
+            __syncthreads();
+            if (held > a.cap - kScanStep) sign_compact(keys, spill, a.k, &s_cnt, &s_thr, &s_sel);   // uniform
+            const unsigned long long thr = s_thr;
+            CodeWords<W> c[kScanRows];
+            float param[kScanRows], norm_sq[kScanRows], score[kScanRows];
+            const float* state[kScanRows];
+            uint32_t row[kScanRows];
+            bool ok[kScanRows];
+#pragma unroll
+            for (int r = 0; r < kScanRows; ++r) {   // four consecutive entries per thread: whole warps work or rest
+                const int at = kScanRows * tid + r;
+                ok[r] = at < take;
+                row[r] = 0u; param[r] = 0.f; norm_sq[r] = 0.f; state[r] = a.states;
+#pragma unroll
+                for (int w = 0; w < W; ++w) c[r].w[w] = 0u;
+                if (ok[r]) {
+                    row[r] = s_qrow[done + at];
+                    const long long st = (long long)q * a.nprobe + s_qprobe[done + at];
+                    c[r] = load_code<W>(a.codes, row[r]);
+                    param[r] = __ldg(a.row_params + row[r]);
+                    norm_sq[r] = __ldg(a.norm_sq + st);
+                    state[r] = a.states + (size_t)st * (32 * W);
+                }
+            }
+            if (ok[0]) {
+                exact_float_scores<W>(c, param, state, norm_sq, score);
+#pragma unroll
+                for (int r = 0; r < kScanRows; ++r) {
+                    if (!ok[r]) continue;
+                    const uint64_t key = make_key(score[r], row[r]);
+                    if (key < thr) keys[atomicAdd(&s_cnt, 1)] = key;   // room for a whole round was made above
+                }
+            }
+            __syncthreads();
+            done += take;
+        }
+        const int rest = queued - done;   // < 1,024 <= done whenever done > 0: source and destination do not overlap
+        if (done > 0) {
+            for (int i = tid; i < rest; i += kScanThreads) { s_qrow[i] = s_qrow[done + i]; s_qprobe[i] = s_qprobe[done + i]; }
+            __syncthreads();
+            if (tid == 0) s_qn = rest;
+            __syncthreads();
+        }
+    };
+
     for (int p = slice; p < a.nprobe; p += a.split) {
         const long long st = (long long)q * a.nprobe + p;
         const int list = a.probes[st];
         if (list < 0 || list >= a.nlist) continue;   // uniform
         __syncthreads();
         float abs_sum = 0.f;   // MODE 0: sum |state[d]|, rounded up a little
+        uint32_t qcode[W];     // MODE 1: the state's sign words
         if (MODE == 0) {
             for (int d = tid; d < 32 * W; d += kScanThreads) s_state[d] = a.states[(size_t)st * (32 * W) + d];
             __syncthreads();
@@ -412,19 +473,20 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) abs_sum += __shfl_xor_sync(kFull, abs_sum, o);
             abs_sum *= 1.001f;
-        } else {
-#pragma unroll
-            for (int w = 0; w < W; ++w) qcode[w] = __ldg(a.state_codes + (size_t)st * W + w);   // the same words in every thread
         }
+#pragma unroll
+        for (int w = 0; w < W; ++w) qcode[w] = MODE == 1 ? __ldg(a.state_codes + (size_t)st * W + w) : 0u;   // same in every thread
         const float qparam = MODE == 0 ? a.norm_sq[st] : a.norms[st];
         __syncthreads();
         const long long beg = a.offsets[list], end = a.offsets[list + 1];
         for (long long row0 = beg; row0 < end; row0 += kScanStep) {
-            const int held = s_cnt;   // settled: the previous step ended with a barrier
-            __syncthreads();          // ... and nobody appends before everybody has read it
-            if (held > a.cap - kScanStep) sign_compact(keys, spill, a.k, &s_cnt, &s_thr, &s_sel);   // uniform
-            const unsigned long long thr = s_thr;
-            asm volatile("" ::: "memory");   // the state is read from shared memory in every step, not held in registers
+            unsigned long long thr;
+            if (MODE == 1) {
+                const int held = s_cnt;   // settled: the previous step ended with a barrier
+                __syncthreads();          // ... and nobody appends before everybody has read it
+                if (held > a.cap - kScanStep) sign_compact(keys, spill, a.k, &s_cnt, &s_thr, &s_sel);   // uniform
+            }
+            thr = s_thr;   // MODE 0: changed only inside work_off_queue, between barriers
             CodeWords<W> c[kScanRows];
             float param[kScanRows];
             bool ok[kScanRows];
@@ -440,56 +502,52 @@ __global__ void __launch_bounds__(kScanThreads, W <= 4 ? 6 : 2) k_sign_scan(cons
                     param[r] = 0.f;
                 }
             }
-            float score[kScanRows];
-            if (MODE == 0 && thr != KEY_MAX) {   // uniform
+            if (MODE == 0) {
+                const bool have_cut = thr != KEY_MAX;   // uniform
                 const float cut = key_dist(thr);
                 const float dot_slack = abs_sum * (1.0f / 16384.0f);
+                bool filled = false;   // one of this thread's rows took the queue's 1,024th place
 #pragma unroll
                 for (int r = 0; r < kScanRows; ++r) {
                     if (!ok[r]) continue;
-                    const float s = param[r], two_s = fabsf(2.0f * s);
-                    const float base = __fmaf_rn(__fmul_rn(dimf, s), s, qparam);
-                    const float rough = __fmaf_rn(-__fmul_rn(2.0f, s), table_dot<W>(c[r], s_lut), base);
-                    const float slack = two_s * dot_slack + (fabsf(base) + two_s * abs_sum) * (1.0f / 1048576.0f);
-                    if (!(rough - slack > cut)) s_queue[atomicAdd(&s_qn, 1)] = (uint32_t)(rows[r] - beg);   // NaN queues too
-                }
-                __syncthreads();
-                const int queued = s_qn;
-#pragma unroll
-                for (int r = 0; r < kScanRows; ++r) {
-                    const int at = r * kScanThreads + tid;
-                    ok[r] = at < queued;
-                    if (ok[r]) {
-                        rows[r] = beg + s_queue[at];
-                        c[r] = load_code<W>(a.codes, rows[r]);
-                        param[r] = __ldg(a.row_params + rows[r]);
+                    bool queue = true;
+                    if (have_cut) {
+                        const float s = param[r], two_s = fabsf(2.0f * s);
+                        const float base = __fmaf_rn(__fmul_rn(dimf, s), s, qparam);
+                        const float rough = __fmaf_rn(-__fmul_rn(2.0f, s), table_dot<W>(c[r], s_lut), base);
+                        const float slack = two_s * dot_slack + (fabsf(base) + two_s * abs_sum) * (1.0f / 1048576.0f);
+                        queue = !(rough - slack > cut);   // NaN queues too
+                    }
+                    if (queue) {
+                        const int at = atomicAdd(&s_qn, 1);   // at most 1,024 join a queue that held fewer than 1,024
+                        s_qrow[at] = (uint32_t)rows[r];
+                        s_qprobe[at] = (uint16_t)p;
+                        filled |= at == kScanStep - 1;
                     }
                 }
-                if (tid < queued) exact_float_scores<W>(c, param, s_state, qparam, score);   // whole warps drop out
-            } else if (MODE == 0) {
-                exact_float_scores<W>(c, param, s_state, qparam, score);
+                // The queue held fewer than 1,024 rows before this step, so it holds that many now exactly when that place
+                // was taken in this step: every thread learns it from the barrier itself (reading the counter after the
+                // barrier would race with the next step's appends).
+                if (__syncthreads_or(filled)) work_off_queue(false);
             } else {
 #pragma unroll
                 for (int r = 0; r < kScanRows; ++r) {
+                    if (!ok[r]) continue;
                     int h = 0;
 #pragma unroll
                     for (int w = 0; w < W; ++w) h += __popc(qcode[w] ^ c[r].w[w]);
                     const float cosine = __fdiv_rn(__fsub_rn(dimf, __fmul_rn(2.0f, (float)h)), dimf);
                     const float dn = param[r];
-                    score[r] = __fmaf_rn(-__fmul_rn(__fmul_rn(2.0f, qparam), dn), cosine, __fmaf_rn(dn, dn, __fmul_rn(qparam, qparam)));
+                    const float score = __fmaf_rn(-__fmul_rn(__fmul_rn(2.0f, qparam), dn), cosine, __fmaf_rn(dn, dn, __fmul_rn(qparam, qparam)));
+                    const uint64_t key = make_key(score, (uint32_t)rows[r]);
+                    if (key < thr) keys[atomicAdd(&s_cnt, 1)] = key;   // room for a whole step was checked above
                 }
+                __syncthreads();
             }
-#pragma unroll
-            for (int r = 0; r < kScanRows; ++r) {
-                if (!ok[r]) continue;
-                const uint64_t key = make_key(score[r], (uint32_t)rows[r]);
-                if (key < thr) keys[atomicAdd(&s_cnt, 1)] = key;   // room for a whole step was checked above
-            }
-            __syncthreads();
-            if (tid == 0) s_qn = 0;   // read by everybody before the barrier above, appended to after the next one
         }
     }
     __syncthreads();
+    if (MODE == 0) work_off_queue(true);
     const int n = sign_finish(keys, spill, a.k, a.kp2, &s_cnt, &s_thr, &s_sel);
     if (a.split > 1) {
         uint64_t* out = a.partial + ((size_t)q * a.split + slice) * a.k;
@@ -621,6 +679,7 @@ psb_status launch_sign_candidates(int mode, const float* d_states, const float* 
                                   const long long* d_offsets, int nlist, const int* d_probes, int nq, int nprobe, int padded_dim,
                                   int candidate_count, int* d_rows_out, float* d_dist_out, int sm_count, cudaStream_t s) {
     if (!sign_shape_ok(padded_dim, padded_dim)) return fail(PSB_INVALID_ARGUMENT, "sign codec: padded_dim must be 32, 64, 128 or 256");
+    if (nprobe > 65535) return fail(PSB_INVALID_ARGUMENT, "sign codec: at most 65,535 probes per query");
     if (candidate_count <= 0 || candidate_count > kSignMaxCandidates)
         return fail(PSB_INVALID_ARGUMENT, "sign codec: candidate_count must be in 1..8192");
     if (reinterpret_cast<uintptr_t>(d_codes) % 16) return fail(PSB_INVALID_ARGUMENT, "sign codec: the code array must be 16-byte aligned");
