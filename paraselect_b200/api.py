@@ -715,6 +715,27 @@ class SignIndex:
         t.cuda.synchronize(self.dev)
         return (rows.cpu().numpy(), dist.cpu().numpy()) if want_distances else rows.cpu().numpy()
 
+    def search(self, host_queries, host_vectors, nprobe, topk, n_rerank=512, reordered_ids=None, queries_u8=None,
+               score_mode=SIGN_FLOAT_STATES):
+        """The whole search with the sign codes as the first stage: coarse top-nprobe lists (exact fp32), the n_rerank rows with
+        the smallest sign-code scores, exact re-ranking of those from the host rows (`host_vectors`, list-contiguous, fp32 or
+        u8 - u8 rows are compared with `queries_u8`, as ivf_rerank_host does), ids through `reordered_ids` when given.
+        Returns (ids [nq][topk] int64, distances [nq][topk]); -1 / FLT_MAX where fewer rows were scanned."""
+        q = np.ascontiguousarray(host_queries, np.float32)
+        base = np.ascontiguousarray(host_vectors)
+        if base.shape[0] != self.n_vectors or base.shape[1] != self.dim or n_rerank < topk or topk <= 0:
+            raise InvalidArgument(1, "IVFResTurboQuant search received invalid input")
+        if base.dtype == np.uint8 and queries_u8 is None:
+            raise InvalidArgument(1, "u8 rows are re-ranked against u8 queries")
+        probes, _ = coarse_host(q, self.centroids.cpu().numpy(), nprobe, device=self.device)
+        cand = self.search_candidates(q, probes, n_rerank, score_mode=score_mode)
+        rows, dist = rerank_host(base, queries_u8 if base.dtype == np.uint8 else q, cand, topk, device=self.device)
+        ids = rows.astype(np.int64)
+        if reordered_ids is not None:
+            rid = np.ascontiguousarray(reordered_ids, np.int64)
+            ids = np.where(ids >= 0, rid[np.maximum(ids, 0)], -1)
+        return ids, dist
+
 
 def knn_exact(d_queries, nq, d_base, n, dim, k, d_rows, d_dist, device=0, stream=None):
     _check(lib().psb_knn_exact(C.c_void_p(_p(d_queries)), nq, C.c_void_p(_p(d_base)), C.c_int64(n), dim, k,

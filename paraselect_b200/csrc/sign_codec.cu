@@ -11,9 +11,12 @@
 //                   (query, probe) - one chain over d = 0..dim-1 of +-state[d] for float states, a popcount for sign-coded
 //                   ones (src/quantization/turboquant/turboquant_1bit_score.cuh:17-72) - and the candidate_count smallest
 //                   (score, row) keys are kept in shared memory: a row enters the buffer only below the current cutoff, a full
-//                   buffer is sorted and cut back to candidate_count.  The reference sorts every group of 8 chunks of 2,048
-//                   rows and merges the groups' lists per query (turboquant_1bit_grouped_scan.cu:92-190, 45-90); the result,
-//                   the exact candidate_count smallest keys in ascending order, is the same.
+//                   buffer is cut back to candidate_count by a radix selection, and the survivors are sorted once at the end.
+//                   For float states a table of partial sums gives every row a score with a known error bound first; only
+//                   rows that could be below the cutoff get the exact chain (see the kernel).  The reference sorts every
+//                   group of 8 chunks of 2,048 rows and merges the groups' lists per query
+//                   (turboquant_1bit_grouped_scan.cu:92-190, 45-90); the result, the exact candidate_count smallest keys in
+//                   ascending order, is the same.
 //   k_sign_merge    joins the slices of one query when its probes were split over several CTAs (few queries).
 #include <algorithm>
 #include <cfloat>

@@ -294,3 +294,27 @@ def test_full_size_lists_properties(psb):
     assert np.array_equal(r2.cpu().numpy(), got[:few]) and np.array_equal(bits(d2.cpu().numpy()), bits(gd[:few]))
     w_rows, w_dist = oracle.sign_candidates(0, codes, scales, off, probes[:few], k, states=states[: few * nprobe], norm_sq=nsq[: few * nprobe])
     assert np.array_equal(got[:few], w_rows) and np.array_equal(bits(gd[:few]), bits(w_dist))
+
+
+def test_whole_search_with_sign_codes_as_first_stage(psb):
+    """coarse lists -> sign-code candidates -> exact re-ranking -> ids, against the same chain of CPU checkers."""
+    ix = make_sign_index(91, 64, 128, 128, 100, 600)
+    rng = ix["rng"]
+    nq, nprobe, topk, width = 50, 8, 10, 256
+    pick = rng.integers(0, ix["n"], nq)
+    q = (ix["rows"][pick] + rng.standard_normal((nq, 128)).astype(np.float32)).astype(np.float32)
+    rid = rng.permutation(ix["n"]).astype(np.int64)
+    index = psb.SignIndex().build_u8(ix["rows"], ix["centroids"], ix["offsets"])
+    ids, dist = index.search(q, ix["rows"], nprobe, topk, n_rerank=width, reordered_ids=rid)
+    scale = psb.sign_rotation_scale(128)
+    probes = oracle.coarse(q, ix["centroids"], nprobe)[0].astype(np.int32)
+    codes, scales = oracle.sign_encode_database(ix["rows"], ix["centroids"], ix["offsets"], 128, scale=scale)
+    states, nsq, _, _ = oracle.sign_encode_queries(q, ix["centroids"], probes, 128, scale=scale)
+    cand, _ = oracle.sign_candidates(0, codes, scales, ix["offsets"], probes, width, states=states, norm_sq=nsq)
+    w_rows, w_dist = oracle.rerank(ix["rows"], q, cand, topk)
+    w_ids = np.where(w_rows >= 0, rid[np.maximum(w_rows, 0)], -1)
+    assert np.array_equal(ids, w_ids) and np.array_equal(bits(dist), bits(w_dist))
+    # the query's own source row is found (it sits in a probed list and its residual signs match the query's)
+    assert np.mean(ids[:, 0] == rid[pick]) >= 0.9
+    with pytest.raises(psb.InvalidArgument):
+        index.search(q, ix["rows"], nprobe, topk, n_rerank=5)
