@@ -954,21 +954,23 @@ def training(args, cfg, torch, api, device):
         sampler = ClockSampler(device)
         sampler.start()
         # A step = one Lloyd iteration in steady state.  The first assignment of a training has no previous assignment to take
-        # its bounds from and runs the filter GEMM twice; every later one runs it once.  Timed: one first assignment alone,
-        # then a training of 1 + steps assignments; the difference is `steps` steady-state iterations.
+        # its bounds from and runs the filter GEMM twice; every later one runs it once.  Timed: a training of 1 + steps
+        # assignments and one of 1 + 2 * steps; their difference is `steps` steady-state iterations, and what the shorter one
+        # took beyond its steady-state iterations is the first one.
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        cen.copy_(init)
-        e0.record(stream)
-        api.kmeans_train(x, n, dim, cen, k, 0, assign, device=device, stream=st)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms_first = e0.elapsed_time(e1)
-        cen.copy_(init)
-        e0.record(stream)
-        obj = api.kmeans_train(x, n, dim, cen, k, steps, assign, device=device, stream=st)  # 1 + `steps` assignment passes
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = (e0.elapsed_time(e1) - ms_first) / steps
+
+        def timed_training(iterations):
+            cen.copy_(init)
+            e0.record(stream)
+            out = api.kmeans_train(x, n, dim, cen, k, iterations, assign, device=device, stream=st)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1), out
+        # each training twice, the faster one counts: the host thread that drives the launches shares its cores with other jobs
+        ms_long = min(timed_training(2 * steps)[0] for _ in range(2))
+        ms_short, obj = min((timed_training(steps) for _ in range(2)), key=lambda t: t[0])  # 1 + `steps` assignment passes
+        ms = (ms_long - ms_short) / steps
+        ms_first = ms_short - steps * ms
         clocks = sampler.stop()
         # end to end: host rows in, host centroids + assignment out
         xh = torch.empty((n, dim), dtype=torch.float32).pin_memory()

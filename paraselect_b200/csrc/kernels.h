@@ -278,6 +278,10 @@ psb_status launch_widen_ids(const int* d_in, long long n, long long* d_out, cuda
 // ---- training ------------------------------------------------------------------------------------------------
 psb_status launch_pq_encode(const float* d_data, long long n, int dim, const float* d_codebook, int m, int k,
                             uint8_t* d_codes, cudaStream_t s);
+// Nearest codeword per sub-vector for the Lloyd iterations of PQ training (|c|^2 - 2 x.c with fused multiply-adds; the exact
+// encoder's arithmetic is launch_pq_encode).  Falls back to launch_pq_encode for sub-vector lengths other than 2, 4, 8.
+psb_status launch_pq_assign_train(const float* d_data, long long n, int dim, const float* d_codebook, int m, int k,
+                                  uint8_t* d_codes, cudaStream_t s);
 psb_status launch_pq_accumulate(const float* d_data, long long n, int dim, const uint8_t* d_codes, int m, int k,
                                 double* d_sums, int* d_counts, cudaStream_t s);
 psb_status launch_pq_update(const double* d_sums, const int* d_counts, int m, int k, int dsub, float* d_codebook,

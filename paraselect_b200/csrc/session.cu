@@ -2107,7 +2107,7 @@ psb_status psb_pq_train(const float* d_data, int64_t n, int dim, int subvectors,
         PSB_CUDA(cudaStreamSynchronize(st));   // rows and d_rows go out of scope
     }
     for (int it = 0; it < iters; ++it) {
-        PSB_TRY(launch_pq_encode(d_data, n, dim, d_codebook, subvectors, codebook_size, codes.as<uint8_t>(), st));
+        PSB_TRY(launch_pq_assign_train(d_data, n, dim, d_codebook, subvectors, codebook_size, codes.as<uint8_t>(), st));
         PSB_CUDA(cudaMemsetAsync(sums.p, 0, sums.bytes, st));
         PSB_CUDA(cudaMemsetAsync(counts.p, 0, counts.bytes, st));
         PSB_TRY(launch_pq_accumulate(d_data, n, dim, codes.as<uint8_t>(), subvectors, codebook_size, sums.as<double>(), counts.as<int>(), st));

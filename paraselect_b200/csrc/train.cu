@@ -105,6 +105,66 @@ k_pq_encode_tile(const float* __restrict__ data, long long n, int dim, const flo
     for (long long i = threadIdx.x; i < rows_here * m; i += kEncThreads) codes[(size_t)row0 * m + i] = s_codes[i];
 }
 
+// Assignment of the Lloyd iterations of PQ training: nearest codeword by |c|^2 - 2 x.c (the row's own |x|^2 is the same for every
+// codeword and left out), four fused multiply-adds per codeword for DSUB = 4, four rows per thread sharing every codeword read.
+// Less than half the instructions of the encoder's (x - c)^2 chain, which is kept for the final encoding: that one reproduces the
+// reference encoder's arithmetic bit for bit, this one only has to pick a nearest codeword (the reference's trainer assigns
+// with a TF32 GEMM: src/quantization/pq/pq_trainer.cu:97-170); the lowest index still wins an exact tie.
+constexpr int kAssignRows = 4;   // rows per thread
+template <int DSUB>
+__global__ void __launch_bounds__(kEncThreads)
+k_pq_assign_train(const float* __restrict__ data, long long n, int dim, const float* __restrict__ codebook, int m, int k,
+                  uint8_t* __restrict__ codes) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    float* s_cb = reinterpret_cast<float*>(s_raw);                                   // [k][DSUB]: -2 c
+    float* s_nrm = s_cb + (size_t)k * DSUB;                                          // [k]: |c|^2
+    uint8_t* s_codes = reinterpret_cast<uint8_t*>(s_nrm + k);                        // [rows per CTA][m]
+    constexpr int kRowsPerCta = kEncThreads * kAssignRows;
+    const long long row0 = (long long)blockIdx.x * kRowsPerCta;
+    const long long rows_here = min((long long)kRowsPerCta, n - row0);
+    for (int sub = 0; sub < m; ++sub) {
+        __syncthreads();
+        for (int c = threadIdx.x; c < k; c += kEncThreads) {
+            float nrm = 0.f;
+#pragma unroll
+            for (int d = 0; d < DSUB; ++d) {
+                const float v = codebook[((size_t)sub * k + c) * DSUB + d];
+                s_cb[c * DSUB + d] = -2.0f * v;
+                nrm = fmaf(v, v, nrm);
+            }
+            s_nrm[c] = nrm;
+        }
+        __syncthreads();
+        float x[kAssignRows][DSUB], best[kAssignRows];
+        int bc[kAssignRows];
+#pragma unroll
+        for (int r = 0; r < kAssignRows; ++r) {
+            const long long row = row0 + threadIdx.x + (long long)r * kEncThreads;
+            best[r] = FLT_MAX; bc[r] = 0;
+#pragma unroll
+            for (int d = 0; d < DSUB; ++d) x[r][d] = row < n ? __ldg(data + (size_t)row * dim + (size_t)sub * DSUB + d) : 0.f;
+        }
+#pragma unroll 4
+        for (int c = 0; c < k; ++c) {
+            float cb[DSUB];
+#pragma unroll
+            for (int d = 0; d < DSUB; ++d) cb[d] = s_cb[c * DSUB + d];
+            const float nrm = s_nrm[c];
+#pragma unroll
+            for (int r = 0; r < kAssignRows; ++r) {
+                float dist = nrm;
+#pragma unroll
+                for (int d = 0; d < DSUB; ++d) dist = fmaf(x[r][d], cb[d], dist);
+                if (dist < best[r]) { best[r] = dist; bc[r] = c; }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kAssignRows; ++r) s_codes[(threadIdx.x + r * kEncThreads) * m + sub] = (uint8_t)bc[r];
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < rows_here * m; i += kEncThreads) codes[(size_t)row0 * m + i] = s_codes[i];
+}
+
 // Codeword sums without a global atomic per element: a CTA takes a range of rows and a group of subspaces, accumulates into
 // fp64 sums and counts in shared memory (G subspaces x k codewords x dsub), and adds its non-zero entries to the global
 // sums once at the end.  grid (row ranges, subspace groups); dynamic shared memory = G * k * (dsub * 8 + 4) bytes.
@@ -322,6 +382,30 @@ psb_status launch_pq_encode(const float* d_data, long long n, int dim, const flo
     const size_t smem = (size_t)k * dsub * sizeof(float) + (size_t)kEncThreads * m;
     if (smem > 32 * 1024) PSB_CUDA(cudaFuncSetAttribute(k_pq_encode, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_pq_encode<<<grid, kEncThreads, smem, s>>>(d_data, n, dim, d_codebook, m, k, d_codes);
+    count_launch();
+    PSB_LAUNCH_CHECK();
+    return PSB_OK;
+}
+
+psb_status launch_pq_assign_train(const float* d_data, long long n, int dim, const float* d_codebook, int m, int k,
+                                  uint8_t* d_codes, cudaStream_t s) {
+    if (n <= 0) return PSB_OK;
+    const int dsub = dim / m;
+    const int rows_per_cta = kEncThreads * kAssignRows;
+    const size_t smem = (size_t)k * (dsub + 1) * sizeof(float) + (size_t)rows_per_cta * m;
+    if ((dsub != 2 && dsub != 4 && dsub != 8) || smem > (size_t)200 * 1024 || (reinterpret_cast<uintptr_t>(d_data) % 4))
+        return launch_pq_encode(d_data, n, dim, d_codebook, m, k, d_codes, s);   // shapes this kernel is not built for
+    const unsigned grid = (unsigned)((n + rows_per_cta - 1) / rows_per_cta);
+    auto run = [&](auto kernel) -> psb_status {
+        PSB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kernel<<<grid, kEncThreads, smem, s>>>(d_data, n, dim, d_codebook, m, k, d_codes);
+        return PSB_OK;
+    };
+    switch (dsub) {
+        case 2: PSB_TRY(run(k_pq_assign_train<2>)); break;
+        case 4: PSB_TRY(run(k_pq_assign_train<4>)); break;
+        default: PSB_TRY(run(k_pq_assign_train<8>)); break;
+    }
     count_launch();
     PSB_LAUNCH_CHECK();
     return PSB_OK;

@@ -283,6 +283,31 @@ def test_pq_train_reduces_quantisation_error(psb):
     assert errs[1] < 0.8 * errs[0]
 
 
+def test_pq_train_iterations_are_lloyd_iterations(psb):
+    """Three training iterations from the initial codewords equal three Lloyd iterations on the host (nearest codeword by
+    exact distance, mean of the members, a codeword without members kept): the trainer's assignment uses |c|^2 - 2 x.c, so
+    a row within rounding of two codewords may go either way - nearly all entries agree closely, all agree loosely."""
+    torch = _torch()
+    _, data, _ = synth.mixture(20000, 32, 16, 0.5, seed=21)
+    d = dev(data)
+    cb0 = torch.empty((8, 256, 4), dtype=torch.float32, device="cuda")
+    cb3 = torch.empty((8, 256, 4), dtype=torch.float32, device="cuda")
+    psb.pq_train(d, 20000, 32, 8, 256, 0, 77, cb0)
+    psb.pq_train(d, 20000, 32, 8, 256, 3, 77, cb3)
+    want = cb0.cpu().numpy().astype(np.float64)
+    x = data.reshape(20000, 8, 4).astype(np.float64)
+    for _ in range(3):
+        for sub in range(8):
+            d2 = ((x[:, sub, None, :] - want[sub][None]) ** 2).sum(2)
+            a = d2.argmin(1)
+            for c in np.unique(a):
+                want[sub, c] = x[a == c, sub].mean(0)
+    got = cb3.cpu().numpy().astype(np.float64)
+    close = np.isclose(got, want, rtol=1e-4, atol=1e-4)
+    assert close.mean() > 0.995
+    assert np.allclose(got, want, rtol=0.05, atol=0.05)
+
+
 def test_generators_are_deterministic_and_gaussian(psb):
     torch = _torch()
     a = torch.empty((1 << 20,), dtype=torch.float32, device="cuda")
