@@ -892,7 +892,7 @@ def flat_search(args, cfg, torch, api, device):
               e2e=dict(value=round(nq / (ms_e2e * 1e-3), 1), unit="queries/s", ms_per_step=round(ms_e2e, 4),
                        h2d_bytes_per_step=int(stats["h2d_bytes"]), d2h_bytes_per_step=int(stats["d2h_bytes"])),
               gpu_launches=int(c["kernel_launches"]),
-              roofline=dict(bound="hbm", kernel="k_flat_scan", achieved=round(achieved, 1), peak=peak, unit="GB/s",
+              roofline=dict(bound="hbm", kernel="k_flat_scan_direct", achieved=round(achieved, 1), peak=peak, unit="GB/s",
                             frac=round(achieved / peak, 4), peak_source="measured" if peaks else "fallback",
                             algorithmic_bytes_per_launch=int(rows_per_launch * dim * 4), rows_per_launch=int(rows_per_launch),
                             ms_per_launch=round(scan_ms, 4), traffic=None,
