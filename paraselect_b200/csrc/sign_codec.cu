@@ -172,6 +172,136 @@ __global__ void __launch_bounds__(256) k_sign_encode(const SignEncodeArgs a) {
     }
 }
 
+// The same encoding with one row per THREAD, for padded_dim <= 128 and rows whose length is a multiple of four elements: the
+// whole (zero padded) row sits in registers, every butterfly is two register operations and nothing is exchanged between
+// lanes (the warp-per-row kernel above spends 49 shuffles per row).  Every value goes through the same operations on the
+// same operands - the sign flip, the (lhs + rhs, lhs - rhs) pairs width by width, the scale, the two reduction trees of the
+// statistic taken as register trees - so the bits are the same.  A thread reads its row with 16-byte (fp32) or 4-byte (u8)
+// loads; the row is a run of whole sectors, read once.
+constexpr int kLaneEncThreads = 128;
+
+// What lane 0 of a warp would hold after the shuffle-down tree over t[0..32): t[p] += t[p + delta], delta = 16 .. 1.
+__device__ __forceinline__ float tree32_regs(float (&t)[32]) {
+#pragma unroll
+    for (int delta = 16; delta > 0; delta >>= 1) {
+#pragma unroll
+        for (int p = 0; p < delta; ++p) t[p] = __fadd_rn(t[p], t[p + delta]);
+    }
+    return t[0];
+}
+
+template <int P>
+__global__ void __launch_bounds__(kLaneEncThreads, 2) k_sign_encode_lane(const SignEncodeArgs a) {
+    __shared__ uint32_t s_flip[P];   // 0x80000000 where the rotation flips the sign of dimension d
+    for (int d = threadIdx.x; d < P; d += kLaneEncThreads) s_flip[d] = (sign_mix(a.seed ^ (uint32_t)d) & 1u) ? 0x80000000u : 0u;
+    __syncthreads();
+    const float scale = rsqrtf((float)a.padded);   // on the device from a run-time value, as the reference's kernel takes it
+    const int dim4 = a.dim >> 2;
+    for (long long r = (long long)blockIdx.x * kLaneEncThreads + threadIdx.x; r < a.n; r += (long long)gridDim.x * kLaneEncThreads) {
+        long long out_row = r;
+        const float* cen = nullptr;
+        const float* src_f = nullptr;
+        const unsigned char* src_b = nullptr;
+        bool live = true;
+        if (a.kind == 0) {
+            src_f = static_cast<const float*>(a.rows) + (size_t)r * a.dim;
+        } else if (a.kind == 1) {
+            out_row = r + a.row_offset;
+            int lo = 0, hi = a.nlist;   // the list of the global row (turboquant_1bit_encode.cu:21-31)
+            while (lo + 1 < hi) {
+                const int mid = lo + (hi - lo) / 2;
+                if (a.offsets[mid] <= out_row) lo = mid; else hi = mid;
+            }
+            cen = a.centroids + (size_t)lo * a.dim;
+            if (a.elem_bytes == 1) src_b = static_cast<const unsigned char*>(a.rows) + (size_t)r * a.dim;
+            else src_f = static_cast<const float*>(a.rows) + (size_t)r * a.dim;
+        } else {
+            const int list = a.probes[r];
+            live = list >= 0 && list < a.nlist;
+            src_f = static_cast<const float*>(a.rows) + (size_t)(r / a.nprobe) * a.dim;
+            cen = a.centroids + (size_t)(live ? list : 0) * a.dim;
+        }
+        float v[P];
+#pragma unroll
+        for (int d4 = 0; d4 < P / 4; ++d4) {
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live && d4 < dim4) {
+                if (src_b) {
+                    const uchar4 b = __ldg(reinterpret_cast<const uchar4*>(src_b) + d4);
+                    x = make_float4((float)b.x, (float)b.y, (float)b.z, (float)b.w);
+                } else {
+                    x = __ldg(reinterpret_cast<const float4*>(src_f) + d4);
+                }
+                if (cen) {
+                    const float4 c = __ldg(reinterpret_cast<const float4*>(cen) + d4);
+                    x.x = __fsub_rn(x.x, c.x); x.y = __fsub_rn(x.y, c.y); x.z = __fsub_rn(x.z, c.z); x.w = __fsub_rn(x.w, c.w);
+                }
+            }
+            v[4 * d4] = x.x; v[4 * d4 + 1] = x.y; v[4 * d4 + 2] = x.z; v[4 * d4 + 3] = x.w;
+        }
+        float sum = 0.f;
+        if (a.kind != 1 && (a.norms || a.norm_sq)) {   // sum of squares of the row as given, group trees then the tree over groups
+            float g[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) g[i] = 0.f;
+#pragma unroll
+            for (int w = 0; w < P / 32; ++w) {
+                float t[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) t[i] = __fmul_rn(v[32 * w + i], v[32 * w + i]);
+                g[w] = tree32_regs(t);
+            }
+            sum = tree32_regs(g);
+        }
+#pragma unroll
+        for (int d = 0; d < P; ++d) v[d] = __uint_as_float(__float_as_uint(v[d]) ^ s_flip[d]);
+#pragma unroll
+        for (int width = 1; width < P; width <<= 1) {
+#pragma unroll
+            for (int t = 0; t < P / 2; ++t) {
+                const int left = (t / width) * (width << 1) + (t % width), right = left + width;
+                const float lhs = v[left], rhs = v[right];
+                v[left] = __fadd_rn(lhs, rhs);
+                v[right] = __fsub_rn(lhs, rhs);
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < P; ++d) v[d] = __fmul_rn(v[d], scale);
+        if (a.rotated) {
+            float4* out = reinterpret_cast<float4*>(a.rotated + (size_t)out_row * P);
+#pragma unroll
+            for (int d4 = 0; d4 < P / 4; ++d4) out[d4] = make_float4(v[4 * d4], v[4 * d4 + 1], v[4 * d4 + 2], v[4 * d4 + 3]);
+        }
+        if (a.codes) {
+#pragma unroll
+            for (int w = 0; w < P / 32; ++w) {
+                uint32_t word = 0u;
+#pragma unroll
+                for (int b = 0; b < 32; ++b) word |= v[32 * w + b] >= 0.0f ? (1u << b) : 0u;
+                a.codes[(size_t)out_row * (P / 32) + w] = word;
+            }
+        }
+        if (a.kind == 1) {
+            if (a.norms) {
+                float g[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) g[i] = 0.f;
+#pragma unroll
+                for (int w = 0; w < P / 32; ++w) {
+                    float t[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) t[i] = fabsf(v[32 * w + i]);
+                    g[w] = tree32_regs(t);
+                }
+                a.norms[out_row] = __fdiv_rn(tree32_regs(g), (float)P);
+            }
+        } else {
+            if (a.norm_sq) a.norm_sq[out_row] = sum;
+            if (a.norms) a.norms[out_row] = __fsqrt_rn(sum);
+        }
+    }
+}
+
 __global__ void k_sign_scale(int padded, float* out) { *out = rsqrtf((float)padded); }
 
 // ---- candidate search ------------------------------------------------------------------------------------------
@@ -593,10 +723,31 @@ psb_status run_encode(const SignEncodeArgs& a, int sm_count, cudaStream_t s) {
     return PSB_OK;
 }
 
+template <int P>
+psb_status run_encode_lane(const SignEncodeArgs& a, int sm_count, cudaStream_t s) {
+    const long long ctas = std::min<long long>((a.n + kLaneEncThreads - 1) / kLaneEncThreads, (long long)sm_count * 8);
+    k_sign_encode_lane<P><<<(unsigned)ctas, kLaneEncThreads, 0, s>>>(a);
+    PSB_LAUNCH_CHECK();
+    count_launch();
+    return PSB_OK;
+}
+
 psb_status dispatch_encode(const SignEncodeArgs& args, int padded, int sm_count, cudaStream_t s) {
     if (args.n <= 0) return PSB_OK;
     SignEncodeArgs a = args;
     a.padded = padded;
+    // one row per thread where the row fits the registers and its loads can be 16 (fp32) / 4 (u8) bytes wide
+    const bool u8 = a.kind == 1 && a.elem_bytes == 1;
+    const bool wide = a.dim % 4 == 0 && reinterpret_cast<uintptr_t>(a.rows) % (u8 ? 4 : 16) == 0 &&
+                      (!a.centroids || reinterpret_cast<uintptr_t>(a.centroids) % 16 == 0) &&
+                      (!a.rotated || reinterpret_cast<uintptr_t>(a.rotated) % 16 == 0);
+    if (wide && padded <= 128) {
+        switch (padded) {
+            case 32: return run_encode_lane<32>(a, sm_count, s);
+            case 64: return run_encode_lane<64>(a, sm_count, s);
+            case 128: return run_encode_lane<128>(a, sm_count, s);
+        }
+    }
     switch (padded) {
         case 32: return run_encode<1>(a, sm_count, s);
         case 64: return run_encode<2>(a, sm_count, s);
