@@ -197,7 +197,16 @@ __global__ void __launch_bounds__(kLaneEncThreads, 2) k_sign_encode_lane(const S
     __syncthreads();
     const float scale = rsqrtf((float)a.padded);   // on the device from a run-time value, as the reference's kernel takes it
     const int dim4 = a.dim >> 2;
-    for (long long r = (long long)blockIdx.x * kLaneEncThreads + threadIdx.x; r < a.n; r += (long long)gridDim.x * kLaneEncThreads) {
+    // A thread takes a run of consecutive rows: consecutive database rows mostly share a list, whose bounds are then at hand
+    // (the search is 16 dependent loads).
+    const long long threads = (long long)gridDim.x * kLaneEncThreads;
+    const long long per_thread = (a.n + threads - 1) / threads;
+    const long long r_begin = ((long long)blockIdx.x * kLaneEncThreads + threadIdx.x) * per_thread;
+    const long long r_end = min(a.n, r_begin + per_thread);
+    int held_list = 0;
+    long long held_beg = 0, held_end = -1;
+    const bool bytes16 = (a.dim & 15) == 0 && (reinterpret_cast<uintptr_t>(a.rows) & 15) == 0;   // u8 rows in 16-byte loads
+    for (long long r = r_begin; r < r_end; ++r) {
         long long out_row = r;
         const float* cen = nullptr;
         const float* src_f = nullptr;
@@ -207,12 +216,15 @@ __global__ void __launch_bounds__(kLaneEncThreads, 2) k_sign_encode_lane(const S
             src_f = static_cast<const float*>(a.rows) + (size_t)r * a.dim;
         } else if (a.kind == 1) {
             out_row = r + a.row_offset;
-            int lo = 0, hi = a.nlist;   // the list of the global row (turboquant_1bit_encode.cu:21-31)
-            while (lo + 1 < hi) {
-                const int mid = lo + (hi - lo) / 2;
-                if (a.offsets[mid] <= out_row) lo = mid; else hi = mid;
+            if (out_row < held_beg || out_row >= held_end) {
+                int lo = 0, hi = a.nlist;   // the list of the global row (turboquant_1bit_encode.cu:21-31)
+                while (lo + 1 < hi) {
+                    const int mid = lo + (hi - lo) / 2;
+                    if (a.offsets[mid] <= out_row) lo = mid; else hi = mid;
+                }
+                held_list = lo; held_beg = a.offsets[lo]; held_end = a.offsets[lo + 1];
             }
-            cen = a.centroids + (size_t)lo * a.dim;
+            cen = a.centroids + (size_t)held_list * a.dim;
             if (a.elem_bytes == 1) src_b = static_cast<const unsigned char*>(a.rows) + (size_t)r * a.dim;
             else src_f = static_cast<const float*>(a.rows) + (size_t)r * a.dim;
         } else {
@@ -222,13 +234,20 @@ __global__ void __launch_bounds__(kLaneEncThreads, 2) k_sign_encode_lane(const S
             cen = a.centroids + (size_t)(live ? list : 0) * a.dim;
         }
         float v[P];
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int d4 = 0; d4 < P / 4; ++d4) {
             float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
             if (live && d4 < dim4) {
                 if (src_b) {
-                    const uchar4 b = __ldg(reinterpret_cast<const uchar4*>(src_b) + d4);
-                    x = make_float4((float)b.x, (float)b.y, (float)b.z, (float)b.w);
+                    uint32_t word;
+                    if (bytes16) {   // uniform; the 16-byte load of group d4 / 4 serves four passes of this loop
+                        if ((d4 & 3) == 0) packed = __ldg(reinterpret_cast<const uint4*>(src_b) + (d4 >> 2));
+                        word = (d4 & 3) == 0 ? packed.x : (d4 & 3) == 1 ? packed.y : (d4 & 3) == 2 ? packed.z : packed.w;
+                    } else {
+                        word = __ldg(reinterpret_cast<const uint32_t*>(src_b) + d4);
+                    }
+                    x = make_float4((float)(word & 255u), (float)((word >> 8) & 255u), (float)((word >> 16) & 255u), (float)(word >> 24));
                 } else {
                     x = __ldg(reinterpret_cast<const float4*>(src_f) + d4);
                 }
