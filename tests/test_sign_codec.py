@@ -78,6 +78,27 @@ def test_rotation_is_sign_flip_then_hadamard():
     assert not np.array_equal(rot, other)
 
 
+def test_rotation_equals_flip_times_sylvester_hadamard_matrix():
+    """An independent statement of the rotation: y = H (D x) / sqrt(P), H the Sylvester (natural order) Hadamard matrix, D the
+    diagonal of seeded signs (mix(seed ^ d) odd -> -1).  The butterflies compute exactly this, up to fp32 rounding."""
+    from scipy.linalg import hadamard
+
+    def mix(v):
+        v &= 0xFFFFFFFF
+        v ^= v >> 16; v = (v * 0x7feb352d) & 0xFFFFFFFF
+        v ^= v >> 15; v = (v * 0x846ca68b) & 0xFFFFFFFF
+        return v ^ (v >> 16)
+
+    rng = np.random.default_rng(12)
+    for dim, padded, seed in ((70, 128, 17), (32, 32, 5), (200, 256, 99)):
+        x = rng.standard_normal((6, dim)).astype(np.float32)
+        rot, _, _, _ = oracle.sign_rotate(x, padded, seed=seed)
+        xp = np.zeros((6, padded)); xp[:, :dim] = x
+        signs = np.array([-1.0 if mix(seed ^ d) & 1 else 1.0 for d in range(padded)])
+        want = (xp * signs) @ hadamard(padded).astype(np.float64) / np.sqrt(padded)
+        assert np.allclose(rot, want, rtol=1e-5, atol=1e-5)
+
+
 def small_database():
     rng = np.random.default_rng(5)
     sizes = [4, 0, 5, 1, 0, 7]
