@@ -728,3 +728,24 @@ def ref_sign_scale_l2(query, code, scale):
 def ref_sign_binary_l2(qcode, code, dim, qn, dn):
     a = _c(qcode, np.uint32); b = _c(code, np.uint32)
     return float(ref_sign().ref_sign_binary_l2(_ptr(a), _ptr(b), int(dim), C.c_float(qn), C.c_float(dn)))
+
+
+def ref_sign_cache_publish(root, dataset, staged, n, dim, nlist, seed, layout_id, codes, scales):
+    """TurboQuantCache::publish_staged of the reference over payload files written by the harness into `staged`."""
+    cd = _c(codes, np.uint32); sc = _c(scales, np.float32)
+    if ref_cache().ref_sign_cache_publish(root.encode(), dataset.encode(), staged.encode(), n, dim, nlist, seed, layout_id.encode(),
+                                          _ptr(cd), _ptr(sc)):
+        raise RuntimeError("reference TurboQuantCache::publish_staged failed")
+
+
+def ref_sign_cache_map(root, dataset, n, dim, nlist, seed, layout_id):
+    """TurboQuantCache::try_map of the reference: None on a miss."""
+    cd = np.empty((n, dim // 32), np.uint32); sc = np.empty(n, np.float32)
+    entry = C.create_string_buffer(4096)
+    rc = ref_cache().ref_sign_cache_map(root.encode(), dataset.encode(), n, dim, nlist, seed, layout_id.encode(), _ptr(cd), _ptr(sc),
+                                        entry, 4096)
+    if rc == 2:
+        return None
+    if rc:
+        raise RuntimeError("reference TurboQuantCache::try_map failed")
+    return dict(entry=entry.value.decode(), codes=cd, scales=sc)

@@ -4,12 +4,14 @@
 #include <cstdint>
 #include <cstring>
 #include <exception>
+#include <cstdio>
 #include <string>
 
 #include "dataset/cache/cache_manifest.h"
 #include "dataset/cache/cluster_cache.h"
 #include "dataset/cache/plain_pq_cache.h"
 #include "dataset/cache/residual_pq_cache.h"
+#include "dataset/cache/turboquant_cache.h"
 
 using namespace paraselect::dataset;
 
@@ -93,6 +95,45 @@ int ref_storage_id(const char* manifest_json, char* out, int cap) {
 int ref_manifest_matches(const char* actual_json, const char* expected_json) {
     try { return cache_manifest::matches(cache_manifest::Json::parse(actual_json), cache_manifest::Json::parse(expected_json)) ? 1 : 0; }
     catch (const std::exception&) { return -1; }
+}
+
+
+// TurboQuantCache: publish_staged over payload files written here in the reference's binary layout (u32 n, u32 dim, data), and
+// try_map.  `staged` must exist; it is renamed to the canonical entry.
+static int write_payload(const std::string& path, uint32_t n, uint32_t dim, const void* data, size_t elem) {
+    FILE* f = std::fopen(path.c_str(), "wb");
+    if (!f) return 1;
+    const uint32_t header[2] = {n, dim};
+    const bool ok = std::fwrite(header, sizeof(header), 1, f) == 1 && std::fwrite(data, elem, (size_t)n * dim, f) == (size_t)n * dim;
+    return (std::fclose(f) == 0 && ok) ? 0 : 1;
+}
+static TurboQuantCacheRequest sign_request(int n, int dim, int nlist, int seed, const char* layout) {
+    TurboQuantCacheRequest r;
+    r.n_vectors = n; r.dim = dim; r.n_lists = nlist; r.rotation_seed = seed; r.cluster_layout_id = layout;
+    return r;
+}
+int ref_sign_cache_publish(const char* root, const char* dataset, const char* staged, int n, int dim, int nlist, int seed, const char* layout,
+                           const uint32_t* codes, const float* scales) {
+    try {
+        const auto spec = sign_request(n, dim, nlist, seed, layout);
+        if (write_payload(std::string(staged) + "/codes.u32bin", (uint32_t)n, (uint32_t)spec.words_per_code(), codes, sizeof(uint32_t))) return 1;
+        if (write_payload(std::string(staged) + "/scales.f32bin", (uint32_t)n, 1u, scales, sizeof(float))) return 1;
+        TurboQuantCache cache(root, dataset);
+        cache.publish_staged(staged, spec);
+        return 0;
+    } catch (const std::exception&) { return 1; }
+}
+int ref_sign_cache_map(const char* root, const char* dataset, int n, int dim, int nlist, int seed, const char* layout, uint32_t* codes,
+                       float* scales, char* entry_out, int cap) {
+    try {
+        TurboQuantCache cache(root, dataset);
+        const auto r = cache.try_map(sign_request(n, dim, nlist, seed, layout));
+        if (!r.hit) return 2;
+        std::memcpy(codes, r.codes.data(), r.codes.size() * sizeof(uint32_t));
+        std::memcpy(scales, r.scales.data(), r.scales.size() * sizeof(float));
+        put(entry_out, cap, r.entry_dir);
+        return 0;
+    } catch (const std::exception&) { return 1; }
 }
 
 }  // extern "C"

@@ -326,6 +326,58 @@ def load_pq(root, request, mmap=False):
     return dict(entry=entry, codebook=cb.reshape(m, k, dsub), codes=cd)
 
 
+# ---------------------------------------------------------------------------------------------- sign-code asset
+def sign_request(dataset, n_vectors, dim, nlist, rotation_seed, cluster_layout_id_, builder="chunk-residual-l1-v1",
+                 codes_layout="cluster-reordered-[N,words]-u32") -> dict:
+    """The identity of a 1-bit sign-code asset (manifest_identity, src/dataset/cache/turboquant_cache.cpp:18-26): every field
+    that changes the encoded bytes is part of it.  The reference stores such assets for 128-dimensional rows only
+    (dim / 32 words per code); any multiple of 32 is accepted here."""
+    if dim <= 0 or dim % 32 or n_vectors <= 0 or nlist <= 0 or rotation_seed < 0:
+        raise ValueError("invalid sign-code cache request")
+    req = identity("turboquant", dataset)
+    req.update({"n_vectors": int(n_vectors), "dim": int(dim), "nlist": int(nlist), "words_per_code": dim // 32,
+                "rotation_seed": int(rotation_seed), "builder": builder, "cluster_layout_id": cluster_layout_id_,
+                "codes_layout": codes_layout})
+    return req
+
+
+def sign_cache_root(cluster_entry: str) -> str:
+    """Sign-code assets live under the cluster asset they encode (src/index/ivf_cache/turboquant.cu:46)."""
+    return os.path.join(cluster_entry, "tq")
+
+
+def save_sign(root, request, codes, scales):
+    """Writes a sign-code asset - codes.u32bin [n][words], scales.f32bin [n][1], manifest last
+    (TurboQuantCache::publish_staged); returns the entry directory."""
+    n, words = request["n_vectors"], request["words_per_code"]
+    cd = np.ascontiguousarray(codes).view(np.uint32).reshape(n, words)
+    sc = np.ascontiguousarray(scales, np.float32).reshape(n, 1)
+    entry = canonical_entry(root, request)
+    os.makedirs(entry, exist_ok=True)
+    manifest_path = os.path.join(entry, "manifest.json")
+    if os.path.exists(manifest_path):
+        os.remove(manifest_path)   # unpublish before replacing any payload
+    write_binary(os.path.join(entry, "codes.u32bin"), cd)
+    write_binary(os.path.join(entry, "scales.f32bin"), sc)
+    publish(entry, request)
+    return entry
+
+
+def load_sign(root, request, mmap=False):
+    """TurboQuantCache::try_map: None on a miss or a payload that does not fit the request, else
+    dict(entry, codes [n][words] uint32, scales [n] float32)."""
+    entry = find(root, request)
+    if not entry:
+        return None
+    n, words = request["n_vectors"], request["words_per_code"]
+    try:
+        cd = read_binary(os.path.join(entry, "codes.u32bin"), np.uint32, n, words, mmap)
+        sc = read_binary(os.path.join(entry, "scales.f32bin"), np.float32, n, 1, mmap)
+    except (RuntimeError, OSError):
+        return None
+    return dict(entry=entry, codes=cd, scales=sc.reshape(n))
+
+
 # ---------------------------------------------------------------------------------------------- an index for api.Session
 def load_index(root, dataset, n_vectors, nlist, dim, build_recipe, m, k, pq_iters, residual=False, vectors=None, mmap=False, **pq_kw):
     """The view arrays of a psb session from a cluster asset and the PQ asset encoded for its layout; None when either is

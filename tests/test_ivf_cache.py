@@ -135,3 +135,51 @@ def test_opq_rotation_file_against_the_reference(tmp_path):
     theirs = os.path.join(d1, os.path.basename(mine))
     assert open(mine, "rb").read() == open(theirs, "rb").read()
     assert np.array_equal(oracle.ref_opq_load(d2, key, 16), rot)
+
+
+def sign_asset(n=500, dim=128, seed=3):
+    rng = np.random.default_rng(seed)
+    return (rng.integers(0, 2 ** 32, (n, dim // 32), dtype=np.uint64).astype(np.uint32),
+            rng.uniform(0.1, 3.0, n).astype(np.float32))
+
+
+def test_sign_code_asset_round_trip(tmp_path):
+    codes, scales = sign_asset()
+    root = ivf_cache.sign_cache_root(str(tmp_path / "cluster-entry"))
+    req = ivf_cache.sign_request("synthetic", 500, 128, 20, 17, "layout0")
+    entry = ivf_cache.save_sign(root, req, codes, scales)
+    assert os.path.dirname(entry) == root and sorted(os.listdir(entry)) == ["codes.u32bin", "manifest.json", "scales.f32bin"]
+    got = ivf_cache.load_sign(root, req)
+    assert got["entry"] == entry and np.array_equal(got["codes"], codes) and np.array_equal(got["scales"], scales)
+    # every field that changes the encoded bytes is part of the identity
+    for other in (ivf_cache.sign_request("synthetic", 500, 128, 20, 18, "layout0"),
+                  ivf_cache.sign_request("synthetic", 500, 128, 20, 17, "layout1"),
+                  ivf_cache.sign_request("synthetic", 500, 128, 21, 17, "layout0"),
+                  ivf_cache.sign_request("synthetic", 500, 128, 20, 17, "layout0", builder="other")):
+        assert ivf_cache.load_sign(root, other) is None
+    with open(os.path.join(entry, "scales.f32bin"), "ab") as f:
+        f.write(b"\0\0\0\0")
+    assert ivf_cache.load_sign(root, req) is None   # a payload of the wrong size is a miss
+    with pytest.raises(ValueError):
+        ivf_cache.sign_request("synthetic", 500, 100, 20, 17, "layout0")
+
+
+@needs_ref
+def test_sign_code_asset_against_the_reference(tmp_path):
+    codes, scales = sign_asset(seed=4)
+    root = ivf_cache.sign_cache_root(str(tmp_path / "a"))
+    req = ivf_cache.sign_request("synthetic", 500, 128, 20, 17, "layout0")
+    entry = ivf_cache.save_sign(root, req, codes, scales)
+    ref = oracle.ref_sign_cache_map(root, "synthetic", 500, 128, 20, 17, "layout0")
+    assert ref is not None and ref["entry"] == entry
+    assert np.array_equal(ref["codes"], codes) and np.array_equal(ref["scales"], scales)
+    assert oracle.ref_sign_cache_map(root, "synthetic", 500, 128, 20, 18, "layout0") is None
+    # the other way round: the reference publishes a staged build, this package finds and reads it
+    root_b = ivf_cache.sign_cache_root(str(tmp_path / "b"))
+    staged = os.path.join(root_b, ".building-1")
+    os.makedirs(staged)
+    oracle.ref_sign_cache_publish(root_b, "synthetic", staged, 500, 128, 20, 17, "layout0", codes, scales)
+    got = ivf_cache.load_sign(root_b, req)
+    assert got is not None and os.path.basename(got["entry"]) == os.path.basename(entry)   # the same directory name on both sides
+    assert np.array_equal(got["codes"], codes) and np.array_equal(got["scales"], scales)
+    assert json.load(open(os.path.join(got["entry"], "manifest.json"))) == json.load(open(os.path.join(entry, "manifest.json")))
