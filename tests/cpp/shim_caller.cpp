@@ -4,6 +4,7 @@
 // "no device" status as an exception, not fall back to anything.
 #include "search/ivfrespq/ivfrespq_search.cuh"
 #include "search/ivfflat/ivfflat_search.cuh"
+#include "search/ivf_res_turboquant/ivf_res_turboquant_search.cuh"
 #include "psb_views.hpp"
 
 #include <cstdio>
@@ -69,6 +70,38 @@ int main() {
         std::printf("FLAT_OK\n");
     } catch (const std::runtime_error& e) {
         std::printf("FLAT_RUNTIME_ERROR %s\n", e.what());
+    }
+    // the 1-bit sign codec index of the reference, its members defined by the shim
+    {
+        const int sdim = 32, srows = 200, slists = 4, k = 16;
+        std::vector<std::uint8_t> vec((size_t)srows * sdim);
+        for (size_t i = 0; i < vec.size(); ++i) vec[i] = (std::uint8_t)((i * 37 + (i >> 5) * 11) & 255);
+        std::vector<float> cen((size_t)slists * sdim, 100.f), q((size_t)2 * sdim, 90.f);
+        std::vector<long long> off = {0, 50, 50, 120, 200}, pr = {0, 3, 2, 7};
+        std::vector<int> cand((size_t)2 * k, -2);
+        try {
+            ivf_res_turboquant::Index index;
+            index.build_u8(vec.data(), cen.data(), off.data(), srows, slists, sdim);
+            ivf_res_turboquant::SearchWorkspace ws;
+            ivf_res_turboquant::SearchTiming timing;
+            ws.search_candidates(index, q.data(), pr.data(), off.data(), 2, 2, cand.data(), k, &timing);
+            bool ok = index.bytes_per_vector() == 8;
+            for (int i = 0; i < k; ++i) ok = ok && cand[(size_t)i] >= 0 && cand[(size_t)i] < srows;                       // lists 0 and 3: 130 rows
+            for (int i = 0; i < k; ++i) ok = ok && cand[(size_t)k + i] >= 50 && cand[(size_t)k + i] < 120;                // list 2 only (7 is skipped)
+            std::printf(ok ? "SIGN_OK\n" : "SIGN_WRONG\n");
+        } catch (const std::invalid_argument& e) {
+            std::printf("SIGN_INVALID_ARGUMENT %s\n", e.what());
+        } catch (const std::runtime_error& e) {
+            std::printf("SIGN_RUNTIME_ERROR %s\n", e.what());
+        }
+        try {
+            ivf_res_turboquant::Index index;
+            index.build_u8(vec.data(), cen.data(), off.data(), srows, slists, 300);
+        } catch (const std::invalid_argument&) {
+            std::printf("SIGN_BAD_REQUEST_REFUSED\n");
+        } catch (const std::runtime_error& e) {
+            std::printf("SIGN_BAD_REQUEST_RUNTIME %s\n", e.what());
+        }
     }
     return rc;
 }
