@@ -609,7 +609,8 @@ psb_status psb_sign_encode_queries(const float* d_queries, const float* d_centro
  * qn^2 + dn^2 - 2 qn dn (dim - 2 hamming) / dim with dn = d_row_params[row] - and the candidate_count smallest by (score, row)
  * come out in ascending order: d_rows_out [nq][candidate_count] int32 (global rows, -1 when fewer rows were scanned),
  * d_dist_out the scores (FLT_MAX there; may be NULL).  Probes outside [0, nlist) are skipped.  candidate_count <=
- * PSB_SIGN_MAX_CANDIDATES; d_codes must be 16-byte aligned. */
+ * PSB_SIGN_MAX_CANDIDATES; at most 65,535 probes per query; the index holds fewer than 2^31 rows (rows come out as int32, as in
+ * the reference); d_codes must be 16-byte aligned. */
 psb_status psb_sign_search_candidates(int mode, const float* d_states, const float* d_norm_sq, const uint32_t* d_state_codes,
                                       const float* d_norms, const uint32_t* d_codes, const float* d_row_params,
                                       const int64_t* d_list_offsets, int nlist, const int* d_probes, int nq, int nprobe,
